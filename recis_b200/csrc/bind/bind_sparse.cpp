@@ -1,0 +1,269 @@
+// Python bindings of the sparse-path operations. Every function dispatches on the device of its inputs:
+// CUDA tensors run the sm_100a kernels on the current stream, CPU tensors run the C++ implementations.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include "../cpu/rb_cpu.h"
+#include "../kernels/rb_kernels.h"
+#include "store.h"
+
+namespace py = pybind11;
+using torch::Tensor;
+using OptT = c10::optional<Tensor>;
+
+namespace {
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream(); }
+inline const int32_t* opt_i32(const OptT& t) { return t.has_value() && t->defined() ? t->data_ptr<int32_t>() : nullptr; }
+inline const float* opt_f32(const OptT& t) { return t.has_value() && t->defined() ? t->data_ptr<float>() : nullptr; }
+
+int64_t pow2_at_least(int64_t x) { int64_t p = 64; while (p < x) p <<= 1; return p; }
+
+// ids -> (unique ids bucketed by owner rank, reverse index, per-owner counts, per-owner offsets)
+std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, int64_t world) {
+  TORCH_CHECK(ids.scalar_type() == torch::kInt64 && ids.is_contiguous(), "ids: contiguous int64 expected");
+  TORCH_CHECK(world >= 1 && world <= 1024, "world size out of range");
+  const int64_t n = ids.numel();
+  auto o = ids.options();
+  const int64_t cap = pow2_at_least(2 * std::max<int64_t>(n, 1));
+  auto set_keys = torch::empty({cap}, o);
+  auto set_pos = torch::empty({cap + 1}, o.dtype(torch::kInt32));
+  auto slot = torch::empty({std::max<int64_t>(n, 1)}, o.dtype(torch::kInt32));
+  auto counts = torch::empty({world}, o.dtype(torch::kInt32));
+  auto offsets = torch::empty({world + 1}, o.dtype(torch::kInt32));
+  auto unique_ids = torch::empty({n}, o);
+  auto reverse = torch::empty({n}, o.dtype(torch::kInt32));
+  if (ids.is_cuda()) {
+    c10::cuda::CUDAGuard g(ids.device());
+    rb_dedup_partition(ids.data_ptr<int64_t>(), n, (int)world, reinterpret_cast<uint64_t*>(set_keys.data_ptr<int64_t>()),
+                       set_pos.data_ptr<int32_t>(), cap, slot.data_ptr<int32_t>(), counts.data_ptr<int32_t>(),
+                       offsets.data_ptr<int32_t>(), unique_ids.data_ptr<int64_t>(), reverse.data_ptr<int32_t>(), cur_stream());
+  } else {
+    rbc_dedup_partition(ids.data_ptr<int64_t>(), n, (int)world, reinterpret_cast<uint64_t*>(set_keys.data_ptr<int64_t>()),
+                        set_pos.data_ptr<int32_t>(), cap, slot.data_ptr<int32_t>(), counts.data_ptr<int32_t>(),
+                        offsets.data_ptr<int32_t>(), unique_ids.data_ptr<int64_t>(), reverse.data_ptr<int32_t>());
+  }
+  return {unique_ids, reverse, counts, offsets};
+}
+
+// desc: int64 [4, F+1] (id pointers, nnz prefix, offsets pointers, segment prefix) on the target device.
+std::tuple<Tensor, Tensor> encode_merge(const Tensor& desc, const Tensor& table_idx, int64_t F, int64_t total_nnz, int64_t total_seg,
+                                        bool with_offsets) {
+  auto o = desc.options();
+  auto ids = torch::empty({total_nnz}, o.dtype(torch::kInt64));
+  Tensor offs = with_offsets ? torch::empty({total_seg + 1}, o.dtype(torch::kInt32)) : Tensor();
+  int32_t* op = with_offsets ? offs.data_ptr<int32_t>() : nullptr;
+  if (desc.is_cuda()) {
+    c10::cuda::CUDAGuard g(desc.device());
+    rb_encode_merge(desc.data_ptr<int64_t>(), table_idx.data_ptr<int64_t>(), (int)F, total_nnz, total_seg, ids.data_ptr<int64_t>(), op,
+                    cur_stream());
+  } else {
+    rbc_encode_merge(desc.data_ptr<int64_t>(), table_idx.data_ptr<int64_t>(), (int)F, total_nnz, total_seg, ids.data_ptr<int64_t>(), op);
+  }
+  return {ids, offs};
+}
+
+Tensor gather_rows(const Tensor& src, const Tensor& rows, OptT n_dev) {
+  TORCH_CHECK(src.dim() == 2 && src.is_contiguous() && src.scalar_type() == torch::kFloat32 && rows.scalar_type() == torch::kInt32);
+  const int64_t n = rows.numel(); const int D = (int)src.size(1);
+  auto out = n_dev.has_value() ? torch::zeros({n, D}, src.options()) : torch::empty({n, D}, src.options());
+  if (n == 0) return out;
+  if (src.is_cuda()) {
+    c10::cuda::CUDAGuard g(src.device());
+    rb_gather_rows(src.data_ptr<float>(), rows.data_ptr<int32_t>(), n, opt_i32(n_dev), D, out.data_ptr<float>(), cur_stream());
+  } else {
+    rbc_gather_rows(src.data_ptr<float>(), rows.data_ptr<int32_t>(), n, opt_i32(n_dev), D, out.data_ptr<float>());
+  }
+  return out;
+}
+
+void scatter_rows(Tensor dst, const Tensor& rows, const Tensor& src, bool broadcast) {
+  TORCH_CHECK(dst.dim() == 2 && dst.is_contiguous() && src.is_contiguous() && rows.scalar_type() == torch::kInt32);
+  const int64_t n = rows.numel(); const int D = (int)dst.size(1);
+  if (n == 0) return;
+  if (dst.is_cuda()) {
+    c10::cuda::CUDAGuard g(dst.device());
+    rb_scatter_rows(dst.data_ptr<float>(), rows.data_ptr<int32_t>(), n, D, src.data_ptr<float>(), broadcast, cur_stream());
+  } else {
+    rbc_scatter_rows(dst.data_ptr<float>(), rows.data_ptr<int32_t>(), n, D, src.data_ptr<float>(), broadcast);
+  }
+}
+
+void fill_rows_i64(Tensor dst, const Tensor& rows, int64_t value) {
+  const int64_t n = rows.numel();
+  if (n == 0) return;
+  if (dst.is_cuda()) {
+    c10::cuda::CUDAGuard g(dst.device());
+    rb_fill_rows_i64(dst.data_ptr<int64_t>(), rows.data_ptr<int32_t>(), n, value, cur_stream());
+  } else {
+    rbc_fill_rows_i64(dst.data_ptr<int64_t>(), rows.data_ptr<int32_t>(), n, value);
+  }
+}
+
+// Pooling forward. Returns (out, gsrc, gscale); gsrc/gscale are empty tensors unless need_grad.
+std::tuple<Tensor, Tensor, Tensor> pool_forward(const Tensor& base, OptT rows, const Tensor& rev, const Tensor& offsets, OptT weights,
+                                                int64_t mode, int64_t perm_b, int64_t perm_f, bool need_grad) {
+  TORCH_CHECK(base.dim() == 2 && base.is_contiguous() && base.scalar_type() == torch::kFloat32);
+  TORCH_CHECK(rev.scalar_type() == torch::kInt32 && offsets.scalar_type() == torch::kInt32);
+  const int64_t n_seg = offsets.numel() - 1, n = rev.numel(); const int D = (int)base.size(1);
+  if (perm_f > 0) TORCH_CHECK(perm_b * perm_f == n_seg, "permuted pooling output needs n_seg == batch * features");
+  auto out = torch::empty({n_seg, D}, base.options());
+  Tensor gsrc, gscale;
+  if (need_grad) {
+    gsrc = torch::empty({n}, rev.options());
+    gscale = torch::empty({n}, base.options());
+  }
+  int32_t* gp = need_grad ? gsrc.data_ptr<int32_t>() : nullptr;
+  float* gs = need_grad ? gscale.data_ptr<float>() : nullptr;
+  if (base.is_cuda()) {
+    c10::cuda::CUDAGuard g(base.device());
+    rb_pool_forward(base.data_ptr<float>(), opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg, D,
+                    (int)mode, (int)perm_b, (int)perm_f, out.data_ptr<float>(), gp, gs, cur_stream());
+  } else {
+    rbc_pool_forward(base.data_ptr<float>(), opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg,
+                     D, (int)mode, (int)perm_b, (int)perm_f, out.data_ptr<float>(), gp, gs);
+  }
+  return {out, gsrc, gscale};
+}
+
+std::tuple<Tensor, Tensor, Tensor> tile_forward(const Tensor& base, OptT rows, const Tensor& rev, const Tensor& offsets, OptT weights,
+                                                int64_t tile_len, bool need_grad) {
+  TORCH_CHECK(base.dim() == 2 && base.is_contiguous() && base.scalar_type() == torch::kFloat32);
+  const int64_t n_seg = offsets.numel() - 1, n = rev.numel(); const int D = (int)base.size(1);
+  auto out = torch::empty({n_seg, tile_len * D}, base.options());
+  Tensor gsrc, gscale;
+  if (need_grad) { gsrc = torch::empty({n}, rev.options()); gscale = torch::empty({n}, base.options()); }
+  int32_t* gp = need_grad ? gsrc.data_ptr<int32_t>() : nullptr;
+  float* gs = need_grad ? gscale.data_ptr<float>() : nullptr;
+  if (base.is_cuda()) {
+    c10::cuda::CUDAGuard g(base.device());
+    rb_tile_forward(base.data_ptr<float>(), opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg, D,
+                    (int)tile_len, out.data_ptr<float>(), gp, gs, cur_stream());
+  } else {
+    rbc_tile_forward(base.data_ptr<float>(), opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg,
+                     D, (int)tile_len, out.data_ptr<float>(), gp, gs);
+  }
+  return {out, gsrc, gscale};
+}
+
+// reverse index -> (csr_u, csr_elem, start): elements grouped by unique index, stable in element order.
+std::tuple<Tensor, Tensor, Tensor> build_csr(const Tensor& reverse) {
+  TORCH_CHECK(reverse.scalar_type() == torch::kInt32 && reverse.is_contiguous());
+  const int64_t n = reverse.numel();
+  auto o = reverse.options();
+  auto csr_u = torch::empty({n}, o), csr_elem = torch::empty({n}, o), start = torch::empty({n + 1}, o);
+  if (n == 0) return {csr_u, csr_elem, start};
+  if (reverse.is_cuda()) {
+    c10::cuda::CUDAGuard g(reverse.device());
+    int bits = 1; while ((1ll << bits) < n && bits < 31) ++bits;  // unique indices are < n
+    const size_t tb = rb_sort_temp_bytes(n);
+    auto temp = torch::empty({(int64_t)tb}, o.dtype(torch::kUInt8));
+    auto iota = torch::empty({n}, o);
+    rb_build_csr(reverse.data_ptr<int32_t>(), n, bits, temp.data_ptr(), tb, iota.data_ptr<int32_t>(), csr_u.data_ptr<int32_t>(),
+                 csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>(), cur_stream());
+  } else {
+    rbc_build_csr(reverse.data_ptr<int32_t>(), n, csr_u.data_ptr<int32_t>(), csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>());
+  }
+  return {csr_u, csr_elem, start};
+}
+
+RbOpt make_opt(int64_t kind, double lr, double beta1, double beta2, double eps, double decay, double alpha, double grad_scale,
+               const OptT& w, const OptT& s1, const OptT& s2) {
+  RbOpt o;
+  o.kind = (int)kind; o.lr = (float)lr; o.beta1 = (float)beta1; o.beta2 = (float)beta2; o.eps = (float)eps; o.decay = (float)decay;
+  o.alpha = (float)alpha; o.grad_scale = (float)grad_scale;
+  o.w = w.has_value() && w->defined() ? w->data_ptr<float>() : nullptr;
+  o.s1 = s1.has_value() && s1->defined() ? s1->data_ptr<float>() : nullptr;
+  o.s2 = s2.has_value() && s2->defined() ? s2->data_ptr<float>() : nullptr;
+  return o;
+}
+
+// Per-unique gradient reduction. apply=false: returns gu [n_unique_max, D] (rows beyond the unique count are undefined).
+// apply=true: runs the optimizer on row rows[u] of (w, s1, s2) in the same kernel and returns an empty tensor.
+Tensor grad_reduce(const Tensor& grad_out, const Tensor& gsrc, const Tensor& gscale, const Tensor& csr_u, const Tensor& csr_elem,
+                   const Tensor& start, int64_t D, OptT rows, bool apply, int64_t kind, double lr, double beta1, double beta2, double eps,
+                   double decay, double alpha, double grad_scale, OptT w, OptT s1, OptT s2, int64_t n_unique_max) {
+  TORCH_CHECK(grad_out.is_contiguous() && grad_out.scalar_type() == torch::kFloat32, "grad_out must be contiguous fp32");
+  const int64_t n = csr_u.numel();
+  RbOpt opt = make_opt(kind, lr, beta1, beta2, eps, decay, alpha, grad_scale, w, s1, s2);
+  if (apply) TORCH_CHECK(opt.w != nullptr, "apply needs the weight slab");
+  Tensor gu = apply ? Tensor() : torch::zeros({n_unique_max, D}, grad_out.options());
+  float* gup = apply ? nullptr : gu.data_ptr<float>();
+  if (n == 0) return gu;
+  if (grad_out.is_cuda()) {
+    c10::cuda::CUDAGuard g(grad_out.device());
+    const int64_t n_chunks = (n + rb_grad_reduce_chunk() - 1) / rb_grad_reduce_chunk();
+    auto span = torch::zeros({n_chunks, D}, grad_out.options());
+    rb_grad_reduce(grad_out.data_ptr<float>(), gsrc.data_ptr<int32_t>(), gscale.data_ptr<float>(), csr_u.data_ptr<int32_t>(),
+                   csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>(), n, (int)D, span.data_ptr<float>(), opt_i32(rows), gup,
+                   apply ? 1 : 0, opt, cur_stream());
+  } else {
+    rbc_grad_reduce(grad_out.data_ptr<float>(), gsrc.data_ptr<int32_t>(), gscale.data_ptr<float>(), csr_u.data_ptr<int32_t>(),
+                    csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>(), n, (int)D, opt_i32(rows), gup, apply ? 1 : 0, opt);
+  }
+  return gu;
+}
+
+void sparse_apply(const Tensor& rows, const Tensor& grads, OptT n_dev, int64_t kind, double lr, double beta1, double beta2, double eps,
+                  double decay, double alpha, double grad_scale, Tensor w, OptT s1, OptT s2) {
+  TORCH_CHECK(rows.scalar_type() == torch::kInt32 && grads.is_contiguous() && grads.scalar_type() == torch::kFloat32);
+  const int64_t n = rows.numel(); const int D = (int)w.size(1);
+  if (n == 0) return;
+  RbOpt opt = make_opt(kind, lr, beta1, beta2, eps, decay, alpha, grad_scale, w, s1, s2);
+  if (w.is_cuda()) {
+    c10::cuda::CUDAGuard g(w.device());
+    rb_sparse_apply(rows.data_ptr<int32_t>(), grads.data_ptr<float>(), n, opt_i32(n_dev), D, opt, cur_stream());
+  } else {
+    rbc_sparse_apply(rows.data_ptr<int32_t>(), grads.data_ptr<float>(), n, opt_i32(n_dev), D, opt);
+  }
+}
+
+}  // namespace
+
+void init_sparse(py::module& m) {
+  using rbx::EmbeddingStore;
+  py::class_<EmbeddingStore, std::shared_ptr<EmbeddingStore>>(m, "EmbeddingStore")
+      .def(py::init([](int64_t dim, int64_t capacity, const std::string& device, int init_kind, double a, double b, double lo, double hi,
+                       int64_t seed, bool track_last_seen, bool growable, OptT emb_storage) {
+             return std::make_shared<EmbeddingStore>(dim, capacity, torch::Device(device), init_kind, a, b, lo, hi, seed, track_last_seen,
+                                                     growable, emb_storage);
+           }),
+           py::arg("dim"), py::arg("capacity"), py::arg("device"), py::arg("init_kind"), py::arg("a"), py::arg("b"), py::arg("lo"),
+           py::arg("hi"), py::arg("seed"), py::arg("track_last_seen") = true, py::arg("growable") = true,
+           py::arg("emb_storage") = py::none())
+      .def("lookup_or_insert", &EmbeddingStore::lookup_or_insert, py::arg("ids"), py::arg("n_dev") = py::none(),
+           py::arg("step") = py::none(), py::arg("admit_threshold") = 1)
+      .def("find", &EmbeddingStore::find, py::arg("ids"), py::arg("n_dev") = py::none())
+      .def("erase", &EmbeddingStore::erase)
+      .def("snapshot", &EmbeddingStore::snapshot, py::arg("expired_only") = false, py::arg("threshold") = 0)
+      .def("add_slot", &EmbeddingStore::add_slot, py::arg("name"), py::arg("fill") = 0.0)
+      .def("slot", &EmbeddingStore::slot)
+      .def("has_slot", &EmbeddingStore::has_slot)
+      .def("slot_names", &EmbeddingStore::slot_names)
+      .def("emb", &EmbeddingStore::emb)
+      .def("last_seen", &EmbeddingStore::last_seen)
+      .def("keys", &EmbeddingStore::keys)
+      .def("index_rows", &EmbeddingStore::index_rows)
+      .def("ctr", &EmbeddingStore::ctr)
+      .def("free_list", &EmbeddingStore::free_list)
+      .def("counters", &EmbeddingStore::counters)
+      .def("reserve", &EmbeddingStore::reserve)
+      .def("rebuild_index", &EmbeddingStore::rebuild_index)
+      .def("clear", &EmbeddingStore::clear)
+      .def("size", &EmbeddingStore::size)
+      .def("capacity", &EmbeddingStore::capacity)
+      .def("dim", &EmbeddingStore::dim)
+      .def("set_name", &EmbeddingStore::set_name);
+
+  m.def("dedup_partition", &dedup_partition);
+  m.def("encode_merge", &encode_merge);
+  m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("rows"), py::arg("n_dev") = py::none());
+  m.def("scatter_rows", &scatter_rows);
+  m.def("fill_rows_i64", &fill_rows_i64);
+  m.def("pool_forward", &pool_forward);
+  m.def("tile_forward", &tile_forward);
+  m.def("build_csr", &build_csr);
+  m.def("grad_reduce", &grad_reduce);
+  m.def("sparse_apply", &sparse_apply);
+  m.def("grad_reduce_chunk", []() { return rb_grad_reduce_chunk(); });
+}

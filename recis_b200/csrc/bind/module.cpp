@@ -1,0 +1,9 @@
+// Python module definition: each bind_*.cpp registers its functions here.
+#include <torch/extension.h>
+
+void init_sparse(pybind11::module& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "recis_b200 native extension (sm_100a kernels + CPU implementations)";
+  init_sparse(m);
+}

@@ -1,0 +1,232 @@
+// EmbeddingStore: the native dynamic-embedding table (index + row arena + named per-row slots).
+//
+// Plays the role of the reference's Hashtable / IdMap / IdAllocator / SlotGroup stack
+// (csrc/embedding/hashtable.cc:82-313, slot_group.cc:39-174, id_allocator.cc:17-62) with a different layout:
+// one open-addressing index, one contiguous [capacity, dim] slab per slot (no vector of blocks, hence no
+// per-call pointer tables and no per-op stream synchronisation), rows initialised on admission as a pure
+// function of (seed, id). The host keeps pessimistic upper bounds of the allocator counters so that the hot
+// path never reads device memory; it synchronises only when a bound says that growth may be needed.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include "../kernels/rb_kernels.h"
+#include "../cpu/rb_cpu.h"
+#include "store.h"
+
+namespace rbx {
+
+static int64_t pow2_at_least(int64_t x) { int64_t p = 1024; while (p < x) p <<= 1; return p; }
+
+EmbeddingStore::EmbeddingStore(int64_t dim, int64_t capacity, torch::Device device, int init_kind, double a, double b,
+                               double lo, double hi, int64_t seed, bool track_last_seen, bool growable,
+                               c10::optional<torch::Tensor> emb_storage)
+    : dim_(dim), cap_rows_(std::max<int64_t>(capacity, 16)), device_(device), growable_(growable) {
+  init_.kind = init_kind; init_.a = (float)a; init_.b = (float)b; init_.lo = (float)lo; init_.hi = (float)hi;
+  init_.seed = (uint64_t)seed;
+  auto f32 = torch::TensorOptions().dtype(torch::kFloat32).device(device_);
+  if (emb_storage.has_value()) {
+    TORCH_CHECK(emb_storage->numel() >= cap_rows_ * dim_ && emb_storage->scalar_type() == torch::kFloat32, "emb_storage too small");
+    emb_ = emb_storage->view({-1}).narrow(0, 0, cap_rows_ * dim_).view({cap_rows_, dim_});
+    growable_ = false;  // externally owned (peer-mapped) storage cannot move
+  } else {
+    emb_ = torch::empty({cap_rows_, dim_}, f32);
+  }
+  if (track_last_seen) last_seen_ = torch::zeros({cap_rows_}, f32.dtype(torch::kInt64));
+  alloc_index(pow2_at_least(cap_rows_ * 2));
+  ctr_ = torch::zeros({RB_CTR_COUNT}, f32.dtype(torch::kInt64));
+  free_list_ = torch::empty({cap_rows_}, f32.dtype(torch::kInt32));
+}
+
+void EmbeddingStore::alloc_index(int64_t nslots) {
+  auto o = torch::TensorOptions().device(device_);
+  keys_ = torch::full({nslots}, -1, o.dtype(torch::kInt64));
+  rows_ = torch::full({nslots}, -1, o.dtype(torch::kInt32));
+}
+
+RbTable EmbeddingStore::view() const {
+  RbTable t;
+  t.keys = reinterpret_cast<uint64_t*>(keys_.data_ptr<int64_t>());
+  t.rows = rows_.data_ptr<int32_t>();
+  t.mask = (uint64_t)keys_.numel() - 1;
+  t.ctr = ctr_.data_ptr<int64_t>();
+  t.free_list = free_list_.data_ptr<int32_t>();
+  t.cap_rows = cap_rows_;
+  return t;
+}
+
+void EmbeddingStore::add_slot(const std::string& name, double fill) {
+  if (slots_.count(name)) return;
+  slots_[name] = torch::full({cap_rows_, dim_}, fill, emb_.options());
+  slot_fill_[name] = fill;
+  slot_order_.push_back(name);
+}
+
+torch::Tensor EmbeddingStore::slot(const std::string& name) const {
+  auto it = slots_.find(name);
+  TORCH_CHECK(it != slots_.end(), "no slot named ", name);
+  return it->second;
+}
+
+std::vector<int64_t> EmbeddingStore::counters() const {
+  auto c = ctr_.cpu();
+  std::vector<int64_t> v(c.data_ptr<int64_t>(), c.data_ptr<int64_t>() + RB_CTR_COUNT);
+  return v;
+}
+
+void EmbeddingStore::refresh_bounds() {
+  auto c = counters();
+  rows_upper_ = c[RB_CTR_BUMP] - c[RB_CTR_FREE_TOP];
+  if (rows_upper_ < 0) rows_upper_ = 0;
+  bump_upper_ = c[RB_CTR_BUMP];
+  index_upper_ = c[RB_CTR_LIVE] + c[RB_CTR_TOMBSTONES] + c[RB_CTR_PROBATION];
+  TORCH_CHECK((c[RB_CTR_STATUS] & 3) == 0, "embedding store reported status ", c[RB_CTR_STATUS],
+              " (1 = row arena exhausted, 2 = index full); raise the capacity");
+}
+
+void EmbeddingStore::ensure_room(int64_t n_incoming) {
+  // Pessimistic: every incoming id may be new. Only when the bound crosses the capacity do we look at the truth.
+  if (rows_upper_ + n_incoming > cap_rows_ || index_upper_ + n_incoming > (int64_t)(0.65 * keys_.numel())) {
+    refresh_bounds();
+    if (rows_upper_ + n_incoming > cap_rows_) {
+      TORCH_CHECK(growable_, "embedding store '", name_, "' is full (", rows_upper_, " rows of ", cap_rows_,
+                  ") and cannot grow: it was created with fixed (peer-mapped) storage");
+      int64_t nc = cap_rows_;
+      while (rows_upper_ + n_incoming > nc) nc = nc + nc / 2 + 1024;
+      reserve(nc);
+    }
+    if (index_upper_ + n_incoming > (int64_t)(0.65 * keys_.numel())) rebuild_index(pow2_at_least((index_upper_ + n_incoming) * 2));
+  }
+  rows_upper_ += n_incoming; index_upper_ += n_incoming;
+}
+
+void EmbeddingStore::rebuild_index(int64_t nslots) {
+  RbTable src = view();
+  auto old_keys = keys_, old_rows = rows_;
+  alloc_index(nslots);
+  RbTable dst = view();
+  if (device_.is_cuda()) {
+    c10::cuda::CUDAGuard g(device_);
+    rb_table_rehash(src, dst, at::cuda::getCurrentCUDAStream());
+  } else {
+    rbc_table_rehash(src, dst);
+  }
+  ctr_.select(0, RB_CTR_TOMBSTONES).zero_();
+  refresh_bounds();
+}
+
+void EmbeddingStore::reserve(int64_t new_cap) {
+  if (new_cap <= cap_rows_) return;
+  TORCH_CHECK(growable_, "store has fixed storage");
+  auto grow = [&](torch::Tensor& t, double fill, bool do_fill) {
+    std::vector<int64_t> shape = t.sizes().vec();
+    shape[0] = new_cap;
+    auto nt = torch::empty(shape, t.options());
+    nt.narrow(0, 0, cap_rows_).copy_(t);
+    if (do_fill) nt.narrow(0, cap_rows_, new_cap - cap_rows_).fill_(fill);
+    t = nt;
+  };
+  grow(emb_, 0.0, false);
+  for (auto& kv : slots_) grow(kv.second, slot_fill_[kv.first], true);
+  if (last_seen_.defined()) grow(last_seen_, 0.0, true);
+  grow(free_list_, 0.0, false);
+  cap_rows_ = new_cap;
+  if (keys_.numel() < 2 * new_cap) rebuild_index(pow2_at_least(2 * new_cap));
+}
+
+torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::optional<torch::Tensor> n_dev,
+                                               c10::optional<torch::Tensor> step, int64_t admit_threshold) {
+  TORCH_CHECK(ids.scalar_type() == torch::kInt64 && ids.is_contiguous() && ids.device() == device_, "ids must be contiguous int64 on the store's device");
+  const int64_t n = ids.numel();
+  auto i32 = torch::TensorOptions().dtype(torch::kInt32).device(device_);
+  auto rows_out = torch::empty({n}, i32);
+  if (n == 0) return rows_out;
+  ensure_room(n);
+  auto slot_scratch = torch::empty({n}, i32);
+  auto new_rows = torch::empty({n}, i32);
+  auto new_keys = torch::empty({n}, i32.dtype(torch::kInt64));
+  const int32_t* nd = n_dev.has_value() ? n_dev->data_ptr<int32_t>() : nullptr;
+  const int64_t* sd = (step.has_value() && last_seen_.defined()) ? step->data_ptr<int64_t>() : nullptr;
+  int64_t* ls = last_seen_.defined() && sd ? last_seen_.data_ptr<int64_t>() : nullptr;
+  if (device_.is_cuda()) {
+    c10::cuda::CUDAGuard g(device_);
+    rb_table_lookup_or_insert(view(), ids.data_ptr<int64_t>(), n, nd, slot_scratch.data_ptr<int32_t>(), new_rows.data_ptr<int32_t>(),
+                              new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr<float>(), (int)dim_, init_, ls,
+                              sd, (int)admit_threshold, at::cuda::getCurrentCUDAStream());
+  } else {
+    rbc_table_lookup_or_insert(view(), ids.data_ptr<int64_t>(), n, nd, slot_scratch.data_ptr<int32_t>(), new_rows.data_ptr<int32_t>(),
+                               new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr<float>(), (int)dim_, init_, ls,
+                               sd, (int)admit_threshold);
+  }
+  return rows_out;
+}
+
+torch::Tensor EmbeddingStore::find(const torch::Tensor& ids, c10::optional<torch::Tensor> n_dev) {
+  TORCH_CHECK(ids.scalar_type() == torch::kInt64 && ids.is_contiguous() && ids.device() == device_);
+  const int64_t n = ids.numel();
+  auto rows_out = torch::empty({n}, torch::TensorOptions().dtype(torch::kInt32).device(device_));
+  const int32_t* nd = n_dev.has_value() ? n_dev->data_ptr<int32_t>() : nullptr;
+  if (n == 0) return rows_out;
+  if (device_.is_cuda()) {
+    c10::cuda::CUDAGuard g(device_);
+    rb_table_find(view(), ids.data_ptr<int64_t>(), n, nd, rows_out.data_ptr<int32_t>(), at::cuda::getCurrentCUDAStream());
+  } else {
+    rbc_table_find(view(), ids.data_ptr<int64_t>(), n, nd, rows_out.data_ptr<int32_t>());
+  }
+  return rows_out;
+}
+
+torch::Tensor EmbeddingStore::erase(const torch::Tensor& ids) {
+  TORCH_CHECK(ids.scalar_type() == torch::kInt64 && ids.is_contiguous() && ids.device() == device_);
+  const int64_t n = ids.numel();
+  auto erased = torch::empty({n}, torch::TensorOptions().dtype(torch::kInt32).device(device_));
+  if (n == 0) return erased;
+  if (device_.is_cuda()) {
+    c10::cuda::CUDAGuard g(device_);
+    auto st = at::cuda::getCurrentCUDAStream();
+    rb_table_erase(view(), ids.data_ptr<int64_t>(), n, nullptr, erased.data_ptr<int32_t>(), st);
+    for (auto& kv : slots_) {
+      auto fillv = torch::full({dim_}, slot_fill_[kv.first], emb_.options());
+      rb_scatter_rows(kv.second.data_ptr<float>(), erased.data_ptr<int32_t>(), n, (int)dim_, fillv.data_ptr<float>(), 1, st);
+    }
+  } else {
+    rbc_table_erase(view(), ids.data_ptr<int64_t>(), n, nullptr, erased.data_ptr<int32_t>());
+    for (auto& kv : slots_) {
+      auto fillv = torch::full({dim_}, slot_fill_[kv.first], emb_.options());
+      rbc_scatter_rows(kv.second.data_ptr<float>(), erased.data_ptr<int32_t>(), n, (int)dim_, fillv.data_ptr<float>(), 1);
+    }
+  }
+  return erased;
+}
+
+std::tuple<torch::Tensor, torch::Tensor> EmbeddingStore::snapshot(bool expired_only, int64_t threshold) {
+  // Size of the result is data dependent: this is a checkpoint / eviction-time call, one host read is fine.
+  auto c = counters();
+  const int64_t cap = std::max<int64_t>(c[RB_CTR_LIVE], 1);
+  auto o = torch::TensorOptions().device(device_);
+  auto ids = torch::empty({cap}, o.dtype(torch::kInt64));
+  auto rows = torch::empty({cap}, o.dtype(torch::kInt32));
+  auto counter = torch::zeros({1}, o.dtype(torch::kInt64));
+  const bool use_filter = expired_only && last_seen_.defined();
+  const int64_t* ls = use_filter ? last_seen_.data_ptr<int64_t>() : nullptr;
+  if (device_.is_cuda()) {
+    c10::cuda::CUDAGuard g(device_);
+    rb_table_snapshot(view(), ids.data_ptr<int64_t>(), rows.data_ptr<int32_t>(), cap, counter.data_ptr<int64_t>(), ls, threshold,
+                      use_filter ? 1 : 0, at::cuda::getCurrentCUDAStream());
+  } else {
+    rbc_table_snapshot(view(), ids.data_ptr<int64_t>(), rows.data_ptr<int32_t>(), cap, counter.data_ptr<int64_t>(), ls, threshold,
+                       use_filter ? 1 : 0);
+  }
+  const int64_t n = std::min<int64_t>(counter.item<int64_t>(), cap);
+  return {ids.narrow(0, 0, n), rows.narrow(0, 0, n)};
+}
+
+void EmbeddingStore::clear() {
+  keys_.fill_(-1); rows_.fill_(-1); ctr_.zero_();
+  for (auto& kv : slots_) kv.second.fill_(slot_fill_[kv.first]);
+  if (last_seen_.defined()) last_seen_.zero_();
+  rows_upper_ = bump_upper_ = index_upper_ = 0;
+}
+
+int64_t EmbeddingStore::size() const { return counters()[RB_CTR_LIVE]; }
+
+}  // namespace rbx

@@ -1,0 +1,56 @@
+#pragma once
+#include <torch/extension.h>
+#include <map>
+#include <string>
+#include <vector>
+#include "../kernels/rb_kernels.h"
+
+namespace rbx {
+
+class EmbeddingStore {
+ public:
+  EmbeddingStore(int64_t dim, int64_t capacity, torch::Device device, int init_kind, double a, double b, double lo, double hi,
+                 int64_t seed, bool track_last_seen, bool growable, c10::optional<torch::Tensor> emb_storage);
+  torch::Tensor lookup_or_insert(const torch::Tensor& ids, c10::optional<torch::Tensor> n_dev, c10::optional<torch::Tensor> step,
+                                 int64_t admit_threshold);
+  torch::Tensor find(const torch::Tensor& ids, c10::optional<torch::Tensor> n_dev);
+  torch::Tensor erase(const torch::Tensor& ids);
+  std::tuple<torch::Tensor, torch::Tensor> snapshot(bool expired_only, int64_t threshold);
+  void add_slot(const std::string& name, double fill);
+  torch::Tensor slot(const std::string& name) const;
+  bool has_slot(const std::string& name) const { return slots_.count(name) > 0; }
+  std::vector<std::string> slot_names() const { return slot_order_; }
+  torch::Tensor emb() const { return emb_; }
+  torch::Tensor last_seen() const { return last_seen_; }
+  torch::Tensor keys() const { return keys_; }
+  torch::Tensor index_rows() const { return rows_; }
+  torch::Tensor ctr() const { return ctr_; }
+  torch::Tensor free_list() const { return free_list_; }
+  std::vector<int64_t> counters() const;
+  void reserve(int64_t new_cap);
+  void rebuild_index(int64_t nslots);
+  void ensure_room(int64_t n_incoming);
+  void clear();
+  int64_t size() const;
+  int64_t capacity() const { return cap_rows_; }
+  int64_t dim() const { return dim_; }
+  RbTable view() const;
+  RbInit init() const { return init_; }
+  void set_name(const std::string& n) { name_ = n; }
+
+ private:
+  void alloc_index(int64_t nslots);
+  void refresh_bounds();
+  int64_t dim_, cap_rows_;
+  torch::Device device_;
+  bool growable_;
+  RbInit init_;
+  std::string name_ = "store";
+  torch::Tensor keys_, rows_, ctr_, free_list_, emb_, last_seen_;
+  std::map<std::string, torch::Tensor> slots_;
+  std::map<std::string, double> slot_fill_;
+  std::vector<std::string> slot_order_;
+  int64_t rows_upper_ = 0, bump_upper_ = 0, index_upper_ = 0;
+};
+
+}  // namespace rbx

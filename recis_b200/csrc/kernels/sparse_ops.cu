@@ -1,0 +1,594 @@
+// Sparse-path kernels (sm_100a): id dedup + owner bucketing, multi-tensor id encode / offset merge,
+// row gather / scatter, ragged pooling (sum / mean / tile), and the chunked segmented gradient
+// reduction that can apply the row-wise optimizer in the same pass.
+//
+// Reference behaviour covered (by path inside the reference project):
+//   csrc/ops/ids_partition_kernel.cu:23-165        dedup + shard routing (there: rotate + radix sort + unique)
+//   csrc/ops/ids_encode_kernel.cu:16-59             12-bit table prefix
+//   csrc/ops/embedding_segment_reduce_kernel.cu     merge_offsets :352-392, pooling fwd/bwd :21-350
+//   csrc/ops/segment_ops_kernel.cu:10-290           "sparse mode" pooling with weight normalisation
+//   csrc/ops/ragged_tile_kernel.cu:25-280           tile combiner
+//   csrc/ops/block_ops_kernel.cu:15-392             gather / insert
+// The structure is different: dedup is a scratch hash set (no 64-bit sort, no host read of the
+// unique count), pooling reads the row arena directly, and the backward pass is a segmented reduction
+// over a (unique, element) sorted list that updates each touched row exactly once, so there is no
+// per-element atomic traffic and no intermediate gradient tensor on the single-GPU path.
+#include "../common/rb_common.cuh"
+#include "rb_kernels.h"
+#include <cub/device/device_radix_sort.cuh>
+
+using namespace rb;
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kChunk = 32;  // CSR positions per work item of the gradient reduction
+
+inline int grid_stride_blocks(int64_t work_items, int threads = kThreads) {
+  int64_t b = (work_items + threads - 1) / threads;
+  if (b < 1) b = 1;
+  const int64_t cap = 148 * 16;
+  return (int)(b < cap ? b : cap);
+}
+
+// ------------------------------------------------------------------ dedup + owner bucketing
+__global__ void __launch_bounds__(kThreads)
+dedup_claim_kernel(const int64_t* __restrict__ ids, int64_t n, int world, uint64_t* __restrict__ set_keys,
+                   int32_t* __restrict__ set_pos, uint64_t mask, int32_t* __restrict__ slot_out, int32_t* __restrict__ counts) {
+  extern __shared__ int32_t sm[];  // [world] block histogram, [world] block base
+  int32_t* hist = sm; int32_t* base = sm + world;
+  for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x; i0 < n; i0 += (int64_t)gridDim.x * blockDim.x) {
+    for (int w = threadIdx.x; w < world; w += blockDim.x) hist[w] = 0;
+    __syncthreads();
+    const int64_t i = i0 + threadIdx.x;
+    int32_t slot = -1, local = 0, owner = 0; bool won = false;
+    if (i < n) {
+      const uint64_t key = (uint64_t)ids[i];
+      uint64_t h = mix64(key) & mask;
+      for (uint64_t probe = 0; probe <= mask; ++probe, h = (h + 1) & mask) {
+        uint64_t k = *reinterpret_cast<volatile uint64_t*>(&set_keys[h]);
+        if (k == kEmptyKey && key != kEmptyKey) {
+          k = atomicCAS(reinterpret_cast<unsigned long long*>(&set_keys[h]), (unsigned long long)kEmptyKey, (unsigned long long)key);
+          if (k == kEmptyKey) { won = true; k = key; }
+        }
+        if (k == key) { slot = (int32_t)h; break; }
+      }
+      if (key == kEmptyKey) {  // the sentinel itself cannot live in the set: treat every occurrence as the same id in slot 0's shadow
+        slot = (int32_t)(mask + 1);                    // one spare cell past the end
+        won = atomicCAS(&set_pos[mask + 1], -1, -2) == -1;
+      }
+      if (won) { owner = owner_of(key, world); local = atomicAdd(&hist[owner], 1); }
+    }
+    __syncthreads();
+    for (int w = threadIdx.x; w < world; w += blockDim.x) base[w] = hist[w] ? atomicAdd(&counts[w], hist[w]) : 0;
+    __syncthreads();
+    if (i < n) {
+      if (won) set_pos[slot] = base[owner] + local;
+      slot_out[i] = slot | (won ? (int32_t)0x80000000 : 0);
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+dedup_assign_kernel(const int64_t* __restrict__ ids, int64_t n, int world, const int32_t* __restrict__ set_pos,
+                    const int32_t* __restrict__ slot_in, const int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                    int64_t* __restrict__ unique_ids, int32_t* __restrict__ reverse) {
+  extern __shared__ int32_t off[];  // [world+1]
+  if (threadIdx.x == 0) {
+    int32_t run = 0;
+    for (int w = 0; w < world; ++w) { off[w] = run; run += counts[w]; }
+    off[world] = run;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) for (int w = threadIdx.x; w <= world; w += blockDim.x) offsets[w] = off[w];
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t s = slot_in[i];
+    const uint64_t key = (uint64_t)ids[i];
+    const int32_t u = off[owner_of(key, world)] + set_pos[s & 0x7FFFFFFF];
+    reverse[i] = u;
+    if (s < 0) unique_ids[u] = (int64_t)key;
+  }
+}
+
+// ------------------------------------------------------------------ multi-tensor encode + offset merge
+__device__ __forceinline__ int find_tensor(const int64_t* prefix, int F, int64_t i) {
+  int lo = 0, hi = F;  // prefix[lo] <= i < prefix[hi]
+  while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (prefix[mid] <= i) lo = mid; else hi = mid; }
+  return lo;
+}
+
+__global__ void __launch_bounds__(kThreads)
+encode_merge_kernel(const int64_t* __restrict__ desc, const int64_t* __restrict__ table_idx, int F, int64_t total_nnz,
+                    int64_t total_seg, int64_t* __restrict__ ids_out, int32_t* __restrict__ offsets_out) {
+  const int64_t* id_ptr = desc; const int64_t* nnz_prefix = desc + (F + 1);
+  const int64_t* off_ptr = desc + 2 * (F + 1); const int64_t* seg_prefix = desc + 3 * (F + 1);
+  const int64_t total = total_nnz + total_seg + 1;
+  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    if (w < total_nnz) {
+      const int f = find_tensor(nnz_prefix, F, w);
+      const int64_t v = reinterpret_cast<const int64_t*>(id_ptr[f])[w - nnz_prefix[f]];
+      ids_out[w] = (int64_t)(((uint64_t)v & 0x000FFFFFFFFFFFFFull) | ((uint64_t)table_idx[f] << 52));
+    } else if (offsets_out) {
+      const int64_t j = w - total_nnz;
+      if (j == total_seg) { offsets_out[j] = (int32_t)total_nnz; continue; }
+      const int f = find_tensor(seg_prefix, F, j);
+      offsets_out[j] = reinterpret_cast<const int32_t*>(off_ptr[f])[j - seg_prefix[f]] + (int32_t)nnz_prefix[f];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ row gather / scatter
+__global__ void __launch_bounds__(kThreads)
+gather_rows_kernel(const float* __restrict__ src, const int32_t* __restrict__ rows, int64_t n_max, const int32_t* __restrict__ n_dev,
+                   int D, float* __restrict__ out) {
+  const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
+  if ((D & 3) == 0) {
+    const int q = D >> 2; const int64_t total = n * q;
+    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t r = w / q; const int c = (int)(w - r * q);
+      const int32_t row = rows[r];
+      st_f4(out + r * D + c * 4, row >= 0 ? ld_f4(src + (int64_t)row * D + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f));
+    }
+  } else {
+    const int64_t total = n * D;
+    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t r = w / D; const int c = (int)(w - r * D);
+      const int32_t row = rows[r];
+      out[w] = row >= 0 ? src[(int64_t)row * D + c] : 0.f;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+scatter_rows_kernel(float* __restrict__ dst, const int32_t* __restrict__ rows, int64_t n, int D, const float* __restrict__ src,
+                    int src_broadcast) {
+  const int64_t total = n * D;
+  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = w / D; const int c = (int)(w - r * D);
+    const int32_t row = rows[r];
+    if (row >= 0) dst[(int64_t)row * D + c] = src_broadcast ? src[c] : src[w];
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fill_rows_i64_kernel(int64_t* __restrict__ dst, const int32_t* __restrict__ rows, int64_t n, int64_t value) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    if (rows[i] >= 0) dst[rows[i]] = value;
+}
+
+// ------------------------------------------------------------------ pooling forward
+__device__ __forceinline__ int64_t out_row_of(int64_t s, int perm_b, int perm_f) {
+  if (perm_f <= 0) return s;
+  const int64_t f = s / perm_b, b = s - f * perm_b;
+  return b * perm_f + f;
+}
+
+// One group of G lanes per segment; each lane owns NACC float4 column slots (columns lane + a*G).
+template <int G, int NACC>
+__global__ void __launch_bounds__(kThreads)
+pool_forward_kernel(const float* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
+                    const int32_t* __restrict__ offsets, const float* __restrict__ weights, int64_t n_seg, int D, int mode,
+                    int perm_b, int perm_f, float* __restrict__ out, int32_t* __restrict__ gsrc, float* __restrict__ gscale) {
+  const int lane = threadIdx.x % G;
+  const int cols = D >> 2;
+  const int64_t n_groups = (int64_t)gridDim.x * (kThreads / G);
+  for (int64_t s = blockIdx.x * (int64_t)(kThreads / G) + threadIdx.x / G; s < n_seg; s += n_groups) {
+    const int32_t beg = offsets[s], end = offsets[s + 1];
+    float4 acc[NACC];
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) acc[a] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float wsum = 0.f;
+    for (int32_t i = beg; i < end; i += 4) {
+      int32_t r[4]; float w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        r[j] = -1; w[j] = 0.f;
+        if (i + j < end) {
+          const int32_t u = rev[i + j];
+          r[j] = rows ? rows[u] : u;
+          w[j] = weights ? weights[i + j] : 1.f;
+          wsum += w[j];
+        }
+      }
+      float4 v[4][NACC];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+          const int c = lane + a * G;
+          v[j][a] = (r[j] >= 0 && c < cols) ? ld_f4(base + (int64_t)r[j] * D + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) acc[a] = f4_fma(w[j], v[j][a], acc[a]);
+    }
+    float scale = 1.f;
+    if (mode == 1) scale = end > beg ? 1.f / (float)(end - beg) : 0.f;
+    else if (mode == 2) scale = wsum != 0.f ? 1.f / wsum : 0.f;
+    const int64_t orow = out_row_of(s, perm_b, perm_f);
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) {
+      const int c = lane + a * G;
+      if (c < cols) st_f4(out + orow * D + c * 4, make_float4(acc[a].x * scale, acc[a].y * scale, acc[a].z * scale, acc[a].w * scale));
+    }
+    if (gsrc) {
+      for (int32_t i = beg + lane; i < end; i += G) {
+        gsrc[i] = (int32_t)orow;
+        gscale[i] = (weights ? weights[i] : 1.f) * scale;
+      }
+    }
+  }
+}
+
+// Any D (not a multiple of 4, or wider than 512): one thread per (segment, column).
+__global__ void __launch_bounds__(kThreads)
+pool_forward_scalar_kernel(const float* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
+                           const int32_t* __restrict__ offsets, const float* __restrict__ weights, int64_t n_seg, int D, int mode,
+                           int perm_b, int perm_f, float* __restrict__ out, int32_t* __restrict__ gsrc, float* __restrict__ gscale) {
+  const int64_t total = n_seg * D;
+  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t s = w / D; const int c = (int)(w - s * D);
+    const int32_t beg = offsets[s], end = offsets[s + 1];
+    float acc = 0.f, wsum = 0.f;
+    for (int32_t i = beg; i < end; ++i) {
+      const int32_t u = rev[i]; const int32_t r = rows ? rows[u] : u;
+      const float wt = weights ? weights[i] : 1.f;
+      wsum += wt;
+      if (r >= 0) acc = fmaf(wt, base[(int64_t)r * D + c], acc);
+    }
+    float scale = 1.f;
+    if (mode == 1) scale = end > beg ? 1.f / (float)(end - beg) : 0.f;
+    else if (mode == 2) scale = wsum != 0.f ? 1.f / wsum : 0.f;
+    const int64_t orow = out_row_of(s, perm_b, perm_f);
+    out[orow * D + c] = acc * scale;
+    if (gsrc && c == 0)
+      for (int32_t i = beg; i < end; ++i) { gsrc[i] = (int32_t)orow; gscale[i] = (weights ? weights[i] : 1.f) * scale; }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+tile_forward_kernel(const float* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
+                    const int32_t* __restrict__ offsets, const float* __restrict__ weights, int64_t n_seg, int D, int tile_len,
+                    float* __restrict__ out, int32_t* __restrict__ gsrc, float* __restrict__ gscale) {
+  const int64_t total = n_seg * tile_len * (int64_t)D;
+  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t st = w / D; const int c = (int)(w - st * D);
+    const int64_t s = st / tile_len; const int t = (int)(st - s * tile_len);
+    const int32_t beg = offsets[s], end = offsets[s + 1];
+    float v = 0.f;
+    if (beg + t < end) {
+      const int32_t u = rev[beg + t]; const int32_t r = rows ? rows[u] : u;
+      const float wt = weights ? weights[beg + t] : 1.f;
+      if (r >= 0) v = wt * base[(int64_t)r * D + c];
+      if (gsrc && c == 0) { gsrc[beg + t] = (int32_t)st; gscale[beg + t] = wt; }
+    }
+    out[w] = v;
+    // elements beyond tile_len contribute nothing: mark them once (by the thread of the last tile slot)
+    if (gsrc && c == 0 && t == tile_len - 1)
+      for (int32_t i = beg + tile_len; i < end; ++i) { gsrc[i] = -1; gscale[i] = 0.f; }
+  }
+}
+
+// ------------------------------------------------------------------ backward structure
+__global__ void __launch_bounds__(kThreads) iota_kernel(int32_t* out, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) out[i] = (int32_t)i;
+}
+
+__global__ void __launch_bounds__(kThreads) csr_heads_kernel(const int32_t* __restrict__ csr_u, int64_t n, int32_t* __restrict__ start) {
+  for (int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; p < n; p += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t u = csr_u[p];
+    if (p == 0 || csr_u[p - 1] != u) start[u] = (int32_t)p;
+    if (p == n - 1) start[u + 1] = (int32_t)n;
+  }
+}
+
+// ------------------------------------------------------------------ row-wise optimizer math
+__device__ __forceinline__ void opt_update_f4(const RbOpt& o, int64_t off, float4 g) {
+  const float gs = o.grad_scale;
+  g.x *= gs; g.y *= gs; g.z *= gs; g.w *= gs;
+  float4 w = ld_f4(o.w + off);
+  if (o.kind == RB_OPT_ADAM) {
+    float4 m = ld_f4(o.s1 + off), v = ld_f4(o.s2 + off);
+    const float b1 = o.beta1, b2 = o.beta2, c1 = 1.f - o.beta1, c2 = 1.f - o.beta2;
+    m.x = b1 * m.x + c1 * g.x; m.y = b1 * m.y + c1 * g.y; m.z = b1 * m.z + c1 * g.z; m.w = b1 * m.w + c1 * g.w;
+    v.x = b2 * v.x + c2 * g.x * g.x; v.y = b2 * v.y + c2 * g.y * g.y; v.z = b2 * v.z + c2 * g.z * g.z; v.w = b2 * v.w + c2 * g.w * g.w;
+    w.x = w.x * o.decay + o.alpha * m.x / (sqrtf(v.x) + o.eps);
+    w.y = w.y * o.decay + o.alpha * m.y / (sqrtf(v.y) + o.eps);
+    w.z = w.z * o.decay + o.alpha * m.z / (sqrtf(v.z) + o.eps);
+    w.w = w.w * o.decay + o.alpha * m.w / (sqrtf(v.w) + o.eps);
+    st_f4(o.s1 + off, m); st_f4(o.s2 + off, v);
+  } else if (o.kind == RB_OPT_ADAGRAD) {
+    float4 a = ld_f4(o.s1 + off);
+    a.x += g.x * g.x; a.y += g.y * g.y; a.z += g.z * g.z; a.w += g.w * g.w;
+    w.x = w.x * o.decay - o.lr * g.x / (sqrtf(a.x) + o.eps);
+    w.y = w.y * o.decay - o.lr * g.y / (sqrtf(a.y) + o.eps);
+    w.z = w.z * o.decay - o.lr * g.z / (sqrtf(a.z) + o.eps);
+    w.w = w.w * o.decay - o.lr * g.w / (sqrtf(a.w) + o.eps);
+    st_f4(o.s1 + off, a);
+  } else {
+    w.x = w.x * o.decay - o.lr * g.x; w.y = w.y * o.decay - o.lr * g.y;
+    w.z = w.z * o.decay - o.lr * g.z; w.w = w.w * o.decay - o.lr * g.w;
+  }
+  st_f4(o.w + off, w);
+}
+
+__device__ __forceinline__ void opt_update_f1(const RbOpt& o, int64_t off, float g) {
+  g *= o.grad_scale;
+  float w = o.w[off];
+  if (o.kind == RB_OPT_ADAM) {
+    const float m = o.beta1 * o.s1[off] + (1.f - o.beta1) * g;
+    const float v = o.beta2 * o.s2[off] + (1.f - o.beta2) * g * g;
+    o.s1[off] = m; o.s2[off] = v;
+    w = w * o.decay + o.alpha * m / (sqrtf(v) + o.eps);
+  } else if (o.kind == RB_OPT_ADAGRAD) {
+    const float a = o.s1[off] + g * g;
+    o.s1[off] = a;
+    w = w * o.decay - o.lr * g / (sqrtf(a) + o.eps);
+  } else {
+    w = w * o.decay - o.lr * g;
+  }
+  o.w[off] = w;
+}
+
+// ------------------------------------------------------------------ chunked segmented gradient reduction
+// VEC = 4: float4 columns, G lanes x NACC slots per group. Work item = kChunk consecutive CSR positions.
+template <int G, int NACC>
+__global__ void __launch_bounds__(kThreads)
+grad_reduce_kernel(const float* __restrict__ grad_out, const int32_t* __restrict__ gsrc, const float* __restrict__ gscale,
+                   const int32_t* __restrict__ csr_u, const int32_t* __restrict__ csr_elem, const int32_t* __restrict__ start,
+                   int64_t n, int D, float* __restrict__ span_acc, const int32_t* __restrict__ rows, float* __restrict__ gu,
+                   int apply, RbOpt opt) {
+  const int lane = threadIdx.x % G;
+  const int cols = D >> 2;
+  const int64_t n_chunks = (n + kChunk - 1) / kChunk;
+  const int64_t n_groups = (int64_t)gridDim.x * (kThreads / G);
+  for (int64_t c = blockIdx.x * (int64_t)(kThreads / G) + threadIdx.x / G; c < n_chunks; c += n_groups) {
+    const int64_t p0 = c * kChunk, p1 = min(p0 + (int64_t)kChunk, n);
+    float4 acc[NACC];
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) acc[a] = make_float4(0.f, 0.f, 0.f, 0.f);
+    int32_t cur_u = csr_u[p0];
+    auto flush = [&](int32_t u) {
+      const int32_t s0 = start[u], s1 = start[u + 1];
+      if (s0 >= p0 && s1 <= p1) {
+        const int32_t row = rows ? rows[u] : u;
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+          const int col = lane + a * G;
+          if (col < cols) {
+            if (apply) { if (row >= 0) opt_update_f4(opt, (int64_t)row * D + col * 4, acc[a]); }
+            else st_f4(gu + (int64_t)u * D + col * 4, acc[a]);
+          }
+        }
+      } else {
+        float* dst = span_acc + (int64_t)(s0 / kChunk) * D;
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+          const int col = lane + a * G;
+          if (col < cols) red_add_f4(dst + col * 4, acc[a]);
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < NACC; ++a) acc[a] = make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    for (int64_t p = p0; p < p1; p += 4) {
+      int32_t u[4], gs[4]; float sc[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        u[j] = -1; gs[j] = -1; sc[j] = 0.f;
+        if (p + j < p1) {
+          u[j] = csr_u[p + j];
+          const int32_t e = csr_elem[p + j];
+          gs[j] = gsrc[e]; sc[j] = gscale[e];
+        }
+      }
+      float4 v[4][NACC];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+          const int col = lane + a * G;
+          v[j][a] = (gs[j] >= 0 && col < cols) ? ld_f4(grad_out + (int64_t)gs[j] * D + col * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (p + j < p1) {
+          if (u[j] != cur_u) { flush(cur_u); cur_u = u[j]; }
+#pragma unroll
+          for (int a = 0; a < NACC; ++a) acc[a] = f4_fma(sc[j], v[j][a], acc[a]);
+        }
+      }
+    }
+    flush(cur_u);
+  }
+}
+
+// Rows whose occurrences cross a chunk boundary were accumulated in span_acc[chunk of their first
+// occurrence]; finish them here and leave span_acc zeroed for the next step.
+template <int G, int NACC>
+__global__ void __launch_bounds__(kThreads)
+grad_span_finish_kernel(const int32_t* __restrict__ csr_u, const int32_t* __restrict__ start, int64_t n, int D,
+                        float* __restrict__ span_acc, const int32_t* __restrict__ rows, float* __restrict__ gu, int apply, RbOpt opt) {
+  const int lane = threadIdx.x % G;
+  const int cols = D >> 2;
+  const int64_t n_chunks = (n + kChunk - 1) / kChunk;
+  const int64_t n_groups = (int64_t)gridDim.x * (kThreads / G);
+  for (int64_t c = blockIdx.x * (int64_t)(kThreads / G) + threadIdx.x / G; c < n_chunks; c += n_groups) {
+    const int64_t p0 = c * kChunk, p1 = min(p0 + (int64_t)kChunk, n);
+    const int32_t u = csr_u[p1 - 1];
+    const int32_t s0 = start[u], s1 = start[u + 1];
+    if (!(s0 >= p0 && s1 > p1)) continue;
+    const int32_t row = rows ? rows[u] : u;
+    float* src = span_acc + c * D;
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) {
+      const int col = lane + a * G;
+      if (col < cols) {
+        const float4 g = ld_f4(src + col * 4);
+        st_f4(src + col * 4, make_float4(0.f, 0.f, 0.f, 0.f));
+        if (apply) { if (row >= 0) opt_update_f4(opt, (int64_t)row * D + col * 4, g); }
+        else st_f4(gu + (int64_t)u * D + col * 4, g);
+      }
+    }
+  }
+}
+
+// Scalar variant for D not a multiple of 4: one thread per (unique row, column) walking its CSR range.
+__global__ void __launch_bounds__(kThreads)
+grad_reduce_scalar_kernel(const float* __restrict__ grad_out, const int32_t* __restrict__ gsrc, const float* __restrict__ gscale,
+                          const int32_t* __restrict__ csr_u, const int32_t* __restrict__ csr_elem, const int32_t* __restrict__ start,
+                          int64_t n, int D, const int32_t* __restrict__ rows, float* __restrict__ gu, int apply, RbOpt opt) {
+  const int32_t n_unique = csr_u[n - 1] + 1;
+  const int64_t total = (int64_t)n_unique * D;
+  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t u = (int32_t)(w / D); const int c = (int)(w - (int64_t)u * D);
+    float acc = 0.f;
+    for (int32_t p = start[u]; p < start[u + 1]; ++p) {
+      const int32_t e = csr_elem[p]; const int32_t gs = gsrc[e];
+      if (gs >= 0) acc = fmaf(gscale[e], grad_out[(int64_t)gs * D + c], acc);
+    }
+    if (apply) { const int32_t row = rows ? rows[u] : u; if (row >= 0) opt_update_f1(opt, (int64_t)row * D + c, acc); }
+    else gu[w] = acc;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+sparse_apply_kernel(const int32_t* __restrict__ rows, const float* __restrict__ grads, int64_t n_max, const int32_t* __restrict__ n_dev,
+                    int D, RbOpt opt) {
+  const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
+  if ((D & 3) == 0) {
+    const int q = D >> 2; const int64_t total = n * q;
+    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t r = w / q; const int c = (int)(w - r * q);
+      const int32_t row = rows[r];
+      if (row >= 0) opt_update_f4(opt, (int64_t)row * D + c * 4, ld_f4(grads + r * D + c * 4));
+    }
+  } else {
+    const int64_t total = n * D;
+    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+      const int64_t r = w / D; const int c = (int)(w - r * D);
+      const int32_t row = rows[r];
+      if (row >= 0) opt_update_f1(opt, (int64_t)row * D + c, grads[w]);
+    }
+  }
+}
+
+template <typename F>
+inline bool dispatch_cols(int D, F&& f) {
+  if ((D & 3) != 0 || D > 512) return false;
+  const int cols = D >> 2;
+  if (cols <= 1) f(std::integral_constant<int, 1>{}, std::integral_constant<int, 1>{});
+  else if (cols <= 2) f(std::integral_constant<int, 2>{}, std::integral_constant<int, 1>{});
+  else if (cols <= 4) f(std::integral_constant<int, 4>{}, std::integral_constant<int, 1>{});
+  else if (cols <= 8) f(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
+  else if (cols <= 16) f(std::integral_constant<int, 16>{}, std::integral_constant<int, 1>{});
+  else if (cols <= 32) f(std::integral_constant<int, 32>{}, std::integral_constant<int, 1>{});
+  else if (cols <= 64) f(std::integral_constant<int, 32>{}, std::integral_constant<int, 2>{});
+  else f(std::integral_constant<int, 32>{}, std::integral_constant<int, 4>{});
+  return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+void rb_dedup_partition(const int64_t* ids, int64_t n, int world, uint64_t* set_keys, int32_t* set_pos, int64_t set_cap,
+                        int32_t* slot_scratch, int32_t* counts, int32_t* offsets, int64_t* unique_ids, int32_t* reverse,
+                        cudaStream_t st) {
+  cudaMemsetAsync(counts, 0, sizeof(int32_t) * world, st);
+  if (n <= 0) { cudaMemsetAsync(offsets, 0, sizeof(int32_t) * (world + 1), st); return; }
+  cudaMemsetAsync(set_keys, 0xFF, sizeof(uint64_t) * set_cap, st);
+  cudaMemsetAsync(set_pos + set_cap, 0xFF, sizeof(int32_t), st);  // spare cell for the sentinel id (-1)
+  const int g = grid_stride_blocks(n);
+  dedup_claim_kernel<<<g, kThreads, 2 * world * sizeof(int32_t), st>>>(ids, n, world, set_keys, set_pos, (uint64_t)set_cap - 1,
+                                                                      slot_scratch, counts);
+  dedup_assign_kernel<<<g, kThreads, (world + 1) * sizeof(int32_t), st>>>(ids, n, world, set_pos, slot_scratch, counts, offsets,
+                                                                         unique_ids, reverse);
+}
+
+void rb_encode_merge(const int64_t* desc, const int64_t* table_idx, int F, int64_t total_nnz, int64_t total_seg,
+                     int64_t* ids_out, int32_t* offsets_out, cudaStream_t st) {
+  encode_merge_kernel<<<grid_stride_blocks(total_nnz + total_seg + 1), kThreads, 0, st>>>(desc, table_idx, F, total_nnz, total_seg,
+                                                                                         ids_out, offsets_out);
+}
+
+void rb_gather_rows(const float* src, const int32_t* rows, int64_t n_max, const int32_t* n_dev, int D, float* out, cudaStream_t st) {
+  if (n_max <= 0) return;
+  gather_rows_kernel<<<grid_stride_blocks(n_max * ((D + 3) / 4)), kThreads, 0, st>>>(src, rows, n_max, n_dev, D, out);
+}
+
+void rb_scatter_rows(float* dst, const int32_t* rows, int64_t n, int D, const float* src, int src_broadcast, cudaStream_t st) {
+  if (n <= 0) return;
+  scatter_rows_kernel<<<grid_stride_blocks(n * D), kThreads, 0, st>>>(dst, rows, n, D, src, src_broadcast);
+}
+
+void rb_fill_rows_i64(int64_t* dst, const int32_t* rows, int64_t n, int64_t value, cudaStream_t st) {
+  if (n <= 0) return;
+  fill_rows_i64_kernel<<<grid_stride_blocks(n), kThreads, 0, st>>>(dst, rows, n, value);
+}
+
+void rb_pool_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
+                     int64_t n_seg, int D, int mode, int perm_b, int perm_f, float* out, int32_t* gsrc, float* gscale,
+                     cudaStream_t st) {
+  if (n_seg <= 0) return;
+  const bool ok = dispatch_cols(D, [&](auto g, auto nacc) {
+    constexpr int G = decltype(g)::value, NACC = decltype(nacc)::value;
+    const int64_t blocks = (n_seg + (kThreads / G) - 1) / (kThreads / G);
+    pool_forward_kernel<G, NACC><<<(int)std::min<int64_t>(blocks, 148 * 64), kThreads, 0, st>>>(
+        base, rows, rev, offsets, weights, n_seg, D, mode, perm_b, perm_f, out, gsrc, gscale);
+  });
+  if (!ok)
+    pool_forward_scalar_kernel<<<grid_stride_blocks(n_seg * D), kThreads, 0, st>>>(base, rows, rev, offsets, weights, n_seg, D, mode,
+                                                                                  perm_b, perm_f, out, gsrc, gscale);
+}
+
+void rb_tile_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
+                     int64_t n_seg, int D, int tile_len, float* out, int32_t* gsrc, float* gscale, cudaStream_t st) {
+  if (n_seg <= 0) return;
+  tile_forward_kernel<<<grid_stride_blocks(n_seg * tile_len * D), kThreads, 0, st>>>(base, rows, rev, offsets, weights, n_seg, D,
+                                                                                    tile_len, out, gsrc, gscale);
+}
+
+size_t rb_sort_temp_bytes(int64_t n) {
+  size_t bytes = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, bytes, (const int32_t*)nullptr, (int32_t*)nullptr, (const int32_t*)nullptr,
+                                  (int32_t*)nullptr, (int)n, 0, 32, (cudaStream_t)0);
+  return bytes;
+}
+
+void rb_build_csr(const int32_t* reverse, int64_t n, int key_bits, void* temp, size_t temp_bytes, int32_t* iota_scratch,
+                  int32_t* csr_u, int32_t* csr_elem, int32_t* start, cudaStream_t st) {
+  if (n <= 0) return;
+  iota_kernel<<<grid_stride_blocks(n), kThreads, 0, st>>>(iota_scratch, n);
+  cub::DeviceRadixSort::SortPairs(temp, temp_bytes, reverse, csr_u, (const int32_t*)iota_scratch, csr_elem, (int)n, 0, key_bits, st);
+  csr_heads_kernel<<<grid_stride_blocks(n), kThreads, 0, st>>>(csr_u, n, start);
+}
+
+int rb_grad_reduce_chunk() { return kChunk; }
+
+void rb_grad_reduce(const float* grad_out, const int32_t* gsrc, const float* gscale, const int32_t* csr_u, const int32_t* csr_elem,
+                    const int32_t* start, int64_t n, int D, float* span_acc, const int32_t* rows, float* gu, int apply, RbOpt opt,
+                    cudaStream_t st) {
+  if (n <= 0) return;
+  const int64_t n_chunks = (n + kChunk - 1) / kChunk;
+  const bool ok = dispatch_cols(D, [&](auto g, auto nacc) {
+    constexpr int G = decltype(g)::value, NACC = decltype(nacc)::value;
+    const int64_t blocks = (n_chunks + (kThreads / G) - 1) / (kThreads / G);
+    const int grid = (int)std::min<int64_t>(blocks, 148 * 64);
+    grad_reduce_kernel<G, NACC><<<grid, kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, span_acc, rows, gu,
+                                                           apply, opt);
+    grad_span_finish_kernel<G, NACC><<<grid, kThreads, 0, st>>>(csr_u, start, n, D, span_acc, rows, gu, apply, opt);
+  });
+  if (!ok)
+    grad_reduce_scalar_kernel<<<grid_stride_blocks(n * D), kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, rows,
+                                                                             gu, apply, opt);
+}
+
+void rb_sparse_apply(const int32_t* rows, const float* grads, int64_t n_max, const int32_t* n_dev, int D, RbOpt opt, cudaStream_t st) {
+  if (n_max <= 0) return;
+  sparse_apply_kernel<<<grid_stride_blocks(n_max * ((D + 3) / 4)), kThreads, 0, st>>>(rows, grads, n_max, n_dev, D, opt);
+}
+
+}  // extern "C"

@@ -1,0 +1,280 @@
+// GPU dynamic-embedding index: one open-addressing hash table (u64 key -> row) with
+// in-kernel row allocation, written for sm_100a.
+//
+// It provides what the reference's IdMap + IdAllocator pair provides
+// (csrc/embedding/gpu_id_map.cu:19-116, csrc/embedding/id_allocator.cc:17-62,
+// csrc/ops/hashtable_ops_kernel.cu:9-172) with a different structure: the reference
+// chains find -> cumsum -> .item() -> GenIds -> compaction -> insert with several
+// host synchronisations; here lookup-or-insert is three stream-ordered launches
+// (claim, init, resolve) that never return to the host.
+//
+// Row allocation: inside one call every newly admitted key takes a dense ticket;
+// tickets below the free-stack height reuse freed rows, the rest bump-allocate.
+// The free-stack height and the bump pointer are constant during the claim kernel
+// and are advanced by the resolve kernel, so no thread ever waits for another.
+#include "../common/rb_common.cuh"
+#include "rb_kernels.h"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+using namespace rb;
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr uint32_t kMaxProbe = 1u << 22;
+
+__device__ __forceinline__ int32_t alloc_row(const RbTable& t, uint64_t key, int32_t* new_rows, int64_t* new_keys) {
+  auto g = cg::coalesced_threads();
+  unsigned long long base = 0;
+  if (g.thread_rank() == 0) base = atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_NEW]), (unsigned long long)g.size());
+  const int64_t ticket = (int64_t)g.shfl(base, 0) + g.thread_rank();
+  const int64_t free_top = t.ctr[RB_CTR_FREE_TOP], bump = t.ctr[RB_CTR_BUMP];
+  int64_t row = ticket < free_top ? (int64_t)t.free_list[free_top - 1 - ticket] : bump + (ticket - free_top);
+  if (row >= t.cap_rows) { set_status(&t.ctr[RB_CTR_STATUS], kStatusRowsExhausted); row = -1; }
+  new_rows[ticket] = (int32_t)row; new_keys[ticket] = (int64_t)key;  // ticket < ids in this call <= buffer length
+  return (int32_t)row;
+}
+
+// Find `key`, or claim an empty slot for it. Returns the slot, or -1.
+__global__ void __launch_bounds__(kThreads)
+table_claim_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, const int32_t* __restrict__ n_dev,
+                   int32_t* __restrict__ slot_out, int32_t* __restrict__ new_rows, int64_t* __restrict__ new_keys,
+                   int admit_threshold, int insert) {
+  const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint64_t key = (uint64_t)ids[i];
+    int32_t slot = -1;
+    if (key < kErasedKey) {
+      uint64_t h = mix64(key) & t.mask;
+      for (uint32_t probe = 0; probe < kMaxProbe; ++probe, h = (h + 1) & t.mask) {
+        uint64_t k = *reinterpret_cast<volatile uint64_t*>(&t.keys[h]);
+        bool won = false;
+        if (k == kEmptyKey) {
+          if (!insert) break;
+          k = atomicCAS(reinterpret_cast<unsigned long long*>(&t.keys[h]), (unsigned long long)kEmptyKey, (unsigned long long)key);
+          won = (k == kEmptyKey);
+          if (won) k = key;
+        }
+        if (k != key) {
+          if (probe + 1 == kMaxProbe || probe >= t.mask) { set_status(&t.ctr[RB_CTR_STATUS], kStatusIndexFull); break; }
+          continue;
+        }
+        slot = (int32_t)h;
+        if (won) {
+          if (admit_threshold <= 1) {
+            const int32_t row = alloc_row(t, key, new_rows, new_keys);
+            *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = row >= 0 ? row : -1;
+          } else {
+            *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = -2;  // probation, seen once
+            atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_PROBATION]), 1ull);
+          }
+        } else if (insert && admit_threshold > 1) {
+          // key exists; if it is on probation, count this occurrence and admit at the threshold.
+          for (int spin = 0; spin < 64; ++spin) {
+            const int32_t v = *reinterpret_cast<volatile int32_t*>(&t.rows[h]);
+            if (v >= -1) break;            // admitted, or another thread is admitting it right now
+            const int32_t seen = -1 - v;   // occurrences so far
+            if (seen + 1 >= admit_threshold) {
+              if (atomicCAS(&t.rows[h], v, kRowPending) == v) {
+                const int32_t row = alloc_row(t, key, new_rows, new_keys);
+                *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = row >= 0 ? row : -1;
+                atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_PROBATION]), (unsigned long long)(-1ll));
+                break;
+              }
+            } else if (atomicCAS(&t.rows[h], v, v - 1) == v) {
+              break;
+            }
+          }
+        }
+        break;
+      }
+    }
+    slot_out[i] = slot;
+  }
+}
+
+// Initialise the embedding of every row admitted by the preceding claim kernel.
+// Values are a function of (seed, id, column), see rb_common.cuh.
+__global__ void __launch_bounds__(kThreads)
+table_init_rows_kernel(RbTable t, const int32_t* __restrict__ new_rows, const int64_t* __restrict__ new_keys,
+                       float* __restrict__ emb, int D, InitSpec spec) {
+  const int64_t n_new = t.ctr[RB_CTR_NEW];
+  const int quads = (D + 3) / 4;
+  const int64_t total = n_new * quads;
+  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = w / quads; const int q = (int)(w - r * quads);
+    const int32_t row = new_rows[r];
+    if (row < 0) continue;
+    float v[4];
+    init_quad(spec, (uint64_t)new_keys[r], (uint32_t)q, v);
+    float* dst = emb + (int64_t)row * D + q * 4;
+    if ((D & 3) == 0) st_f4(dst, make_float4(v[0], v[1], v[2], v[3]));
+    else for (int j = 0; j < 4 && q * 4 + j < D; ++j) dst[j] = v[j];
+  }
+}
+
+// slot -> row for every looked-up id; stamps the last-seen step; block 0 advances the allocator.
+__global__ void __launch_bounds__(kThreads)
+table_resolve_kernel(RbTable t, const int32_t* __restrict__ slots, int64_t n_max, const int32_t* __restrict__ n_dev,
+                     int32_t* __restrict__ rows_out, int64_t* __restrict__ last_seen, const int64_t* __restrict__ step_dev,
+                     int finalize) {
+  const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
+  const int64_t step = step_dev ? *step_dev : 0;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t s = slots[i];
+    int32_t row = -1;
+    if (s >= 0) { row = t.rows[s]; if (row < 0) row = -1; }
+    rows_out[i] = row;
+    if (last_seen && row >= 0) last_seen[row] = step;
+  }
+  if (finalize && blockIdx.x == 0 && threadIdx.x == 0) {
+    const int64_t n_new = t.ctr[RB_CTR_NEW];
+    const int64_t free_top = t.ctr[RB_CTR_FREE_TOP];
+    const int64_t reused = n_new < free_top ? n_new : free_top;
+    int64_t bump = t.ctr[RB_CTR_BUMP] + (n_new - reused);
+    if (bump > t.cap_rows) bump = t.cap_rows;
+    t.ctr[RB_CTR_FREE_TOP] = free_top - reused;
+    t.ctr[RB_CTR_BUMP] = bump;
+    t.ctr[RB_CTR_LIVE] += n_new;
+    t.ctr[RB_CTR_LAST_NEW] = n_new;
+    t.ctr[RB_CTR_NEW] = 0;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+table_find_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, const int32_t* __restrict__ n_dev,
+                  int32_t* __restrict__ rows_out) {
+  const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint64_t key = (uint64_t)ids[i];
+    int32_t row = -1;
+    if (key < kErasedKey) {
+      uint64_t h = mix64(key) & t.mask;
+      for (uint32_t probe = 0; probe < kMaxProbe && probe <= t.mask; ++probe, h = (h + 1) & t.mask) {
+        const uint64_t k = t.keys[h];
+        if (k == key) { row = t.rows[h]; if (row < 0) row = -1; break; }
+        if (k == kEmptyKey) break;
+      }
+    }
+    rows_out[i] = row;
+  }
+}
+
+// Erase ids: tombstone the slot and push the row on the free stack. Ids must be unique within a call.
+__global__ void __launch_bounds__(kThreads)
+table_erase_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, const int32_t* __restrict__ n_dev,
+                   int32_t* __restrict__ erased_rows) {
+  const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint64_t key = (uint64_t)ids[i];
+    int32_t row = -1;
+    if (key < kErasedKey) {
+      uint64_t h = mix64(key) & t.mask;
+      for (uint32_t probe = 0; probe < kMaxProbe && probe <= t.mask; ++probe, h = (h + 1) & t.mask) {
+        const uint64_t k = t.keys[h];
+        if (k == key) {
+          // exactly one thread turns the key into a tombstone
+          if (atomicCAS(reinterpret_cast<unsigned long long*>(&t.keys[h]), (unsigned long long)key, (unsigned long long)kErasedKey) == key) {
+            row = t.rows[h];
+            t.rows[h] = -1;
+            atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_TOMBSTONES]), 1ull);
+            if (row >= 0) {
+              const unsigned long long pos = atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_FREE_TOP]), 1ull);
+              if ((int64_t)pos < t.cap_rows) t.free_list[pos] = row;
+              atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_LIVE]), (unsigned long long)(-1ll));
+            } else {
+              if (row < -1) atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_PROBATION]), (unsigned long long)(-1ll));
+              row = -1;
+            }
+          }
+          break;
+        }
+        if (k == kEmptyKey) break;
+      }
+    }
+    erased_rows[i] = row;
+  }
+}
+
+// Compact (id,row) of every admitted entry; optionally only those whose last-seen step is below a threshold.
+__global__ void __launch_bounds__(kThreads)
+table_snapshot_kernel(RbTable t, int64_t* __restrict__ ids_out, int32_t* __restrict__ rows_out, int64_t out_cap,
+                      int64_t* __restrict__ counter, const int64_t* __restrict__ last_seen, int64_t threshold, int use_filter) {
+  const int64_t nslots = (int64_t)t.mask + 1;
+  for (int64_t s = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; s < nslots; s += (int64_t)gridDim.x * blockDim.x) {
+    const uint64_t k = t.keys[s];
+    if (k >= kErasedKey) continue;
+    const int32_t row = t.rows[s];
+    if (row < 0) continue;
+    if (use_filter && !(last_seen[row] < threshold)) continue;
+    auto g = cg::coalesced_threads();
+    unsigned long long base = 0;
+    if (g.thread_rank() == 0) base = atomicAdd(reinterpret_cast<unsigned long long*>(counter), (unsigned long long)g.size());
+    const int64_t pos = (int64_t)g.shfl(base, 0) + g.thread_rank();
+    if (pos < out_cap) { ids_out[pos] = (int64_t)k; if (rows_out) rows_out[pos] = row; }
+  }
+}
+
+// Re-insert every entry (admitted or on probation) of `src` into the empty index `dst`.
+__global__ void __launch_bounds__(kThreads)
+table_rehash_kernel(RbTable src, RbTable dst) {
+  const int64_t nslots = (int64_t)src.mask + 1;
+  for (int64_t s = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; s < nslots; s += (int64_t)gridDim.x * blockDim.x) {
+    const uint64_t k = src.keys[s];
+    if (k >= kErasedKey) continue;
+    const int32_t row = src.rows[s];
+    if (row == -1) continue;
+    uint64_t h = mix64(k) & dst.mask;
+    for (uint32_t probe = 0; probe < kMaxProbe && probe <= dst.mask; ++probe, h = (h + 1) & dst.mask) {
+      if (atomicCAS(reinterpret_cast<unsigned long long*>(&dst.keys[h]), (unsigned long long)kEmptyKey, (unsigned long long)k) == kEmptyKey) {
+        dst.rows[h] = row;
+        break;
+      }
+    }
+  }
+}
+
+inline int grid_for(int64_t n, int per_thread = 1) {
+  int64_t b = (n + (int64_t)kThreads * per_thread - 1) / ((int64_t)kThreads * per_thread);
+  if (b < 1) b = 1;
+  const int64_t cap = 148 * 16;  // grid-stride kernels: a few waves of resident CTAs per SM
+  return (int)(b < cap ? b : cap);
+}
+
+}  // namespace
+
+extern "C" {
+
+void rb_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* slot_scratch,
+                               int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, float* emb, int D, RbInit init,
+                               int64_t* last_seen, const int64_t* step_dev, int admit_threshold, cudaStream_t st) {
+  if (n_max <= 0) return;
+  const int g = grid_for(n_max);
+  InitSpec spec{init.kind, init.a, init.b, init.lo, init.hi, init.seed};
+  table_claim_kernel<<<g, kThreads, 0, st>>>(t, ids, n_max, n_dev, slot_scratch, new_rows, new_keys, admit_threshold, 1);
+  table_init_rows_kernel<<<grid_for(n_max * ((D + 3) / 4), 4), kThreads, 0, st>>>(t, new_rows, new_keys, emb, D, spec);
+  table_resolve_kernel<<<g, kThreads, 0, st>>>(t, slot_scratch, n_max, n_dev, rows_out, last_seen, step_dev, 1);
+}
+
+void rb_table_find(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* rows_out, cudaStream_t st) {
+  if (n_max <= 0) return;
+  table_find_kernel<<<grid_for(n_max), kThreads, 0, st>>>(t, ids, n_max, n_dev, rows_out);
+}
+
+void rb_table_erase(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* erased_rows, cudaStream_t st) {
+  if (n_max <= 0) return;
+  table_erase_kernel<<<grid_for(n_max), kThreads, 0, st>>>(t, ids, n_max, n_dev, erased_rows);
+}
+
+void rb_table_snapshot(RbTable t, int64_t* ids_out, int32_t* rows_out, int64_t out_cap, int64_t* counter,
+                       const int64_t* last_seen, int64_t threshold, int use_filter, cudaStream_t st) {
+  table_snapshot_kernel<<<grid_for((int64_t)t.mask + 1), kThreads, 0, st>>>(t, ids_out, rows_out, out_cap, counter, last_seen,
+                                                                           threshold, use_filter);
+}
+
+void rb_table_rehash(RbTable src, RbTable dst, cudaStream_t st) {
+  table_rehash_kernel<<<grid_for((int64_t)src.mask + 1), kThreads, 0, st>>>(src, dst);
+}
+
+}  // extern "C"
