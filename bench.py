@@ -1,0 +1,298 @@
+"""Headline benchmark: training throughput (samples/s) of the DLRM-style CTR configuration.
+
+Configuration (per GPU; weak scaling, 8 GPUs give the global batch of 65536):
+  batch 8192, 13 dense fp32 lognormal features, 26 multi-hot fields with Poisson(20) bag lengths clipped to [1, 100],
+  ids ~ Zipf(1.05) over a 2^40 id space folded onto 1e8 distinct ids, all fields merged into one dim-128 fp32 dynamic
+  table (sum pooling), bottom MLP 512-256-128, dot interaction, top MLP 1024-1024-512-256-1 in bf16, labels
+  Bernoulli(0.03), sparse Adam on the embeddings, Adam on the dense tower. Synthetic data, random-init weights.
+
+  python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torch.distributed.run, one rank per GPU)
+  python bench.py --impl reference ...                      (the unmodified reference installed under baseline/_ref)
+
+Prints one JSON line on rank 0. ``value`` is timed on the device (CUDA events, max over ranks) with the step's inputs
+already resident on the GPU; ``e2e.value`` repeats the measurement with, in every step, the host-to-device copy of that
+step's inputs from pinned memory and a device-to-host read of the loss inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PER_GPU_BATCH = 8192
+N_FIELDS = 26
+EMB_DIM = 128
+UNIVERSE = 100_000_000
+ID_BITS = 40
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--batch-per-gpu", type=int, default=PER_GPU_BATCH)
+    p.add_argument("--capacity", type=int, default=0, help="rows per GPU to pre-size the table for")
+    p.add_argument("--comm", default=None, help="override RECIS_COMM (fused | nccl)")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as fh:
+            for line in fh:
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1])); smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return world, rank, local
+
+
+def sync_all(world):
+    import torch
+    import torch.distributed as dist
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world) -> float:
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def timed(step_fn, first, count, world):
+    """Run ``count`` steps starting at batch index ``first``; returns elapsed ms (device time, max over ranks)."""
+    import torch
+    sync_all(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(count):
+        step_fn(first + i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    sync_all(world)
+    return max_over_ranks(ms, world)
+
+
+def spec_for(args, rank):
+    from recis_b200.io.synthetic import SparseFieldSpec, SyntheticSpec
+    fields = [f"c{i}" for i in range(N_FIELDS)]
+    sparse = [SparseFieldSpec(f, zipf_a=1.05, id_bits=ID_BITS, universe=UNIVERSE, length="poisson", mean_len=20, min_len=1, max_len=100)
+              for f in fields]
+    return fields, SyntheticSpec(batch=args.batch_per_gpu, dense_dim=13, sparse=sparse, label_rate=0.03, seed=1000 + rank)
+
+
+def run(args, arm):
+    import torch
+    world, rank, local = dist_setup(args)
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    dev = torch.device("cuda", local)
+    fields, spec = spec_for(args, rank)
+    n_batches = args.warmup + args.steps
+    capacity = args.capacity or 64_000_000
+    state = arm.build(fields, dev, world, rank, capacity)
+
+    from recis_b200.io.synthetic import make_batch_arrays
+    host = [arm.wrap_host(make_batch_arrays(spec, i), spec.batch) for i in range(n_batches)]
+    h2d_bytes = arm.nbytes(host[0])
+
+    # ---- A. device-resident inputs: kernel-path number
+    dev_batches = [arm.to_device(b, dev) for b in host]
+    sync_all(world)
+
+    def step_resident(i):
+        arm.step(state, dev_batches[i])
+
+    timed(step_resident, 0, args.warmup, world)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = arm.launches()
+    ms = timed(step_resident, args.warmup, args.steps, world)
+    launches = arm.launches() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    del dev_batches
+
+    # ---- B. end to end: per step H2D of the inputs from pinned memory + D2H read of the loss
+    losses = []
+
+    def step_e2e(i):
+        loss = arm.step(state, arm.to_device(host[i], dev))
+        losses.append(float(loss))           # device -> host read of the step's result
+
+    timed(step_e2e, 0, min(3, args.warmup), world)
+    ms_e2e = timed(step_e2e, args.warmup, args.steps, world)
+
+    global_batch = spec.batch * world
+    value = global_batch * args.steps / (ms / 1e3)
+    value_e2e = global_batch * args.steps / (ms_e2e / 1e3)
+    if rank == 0:
+        line = {
+            "metric": "train samples/s (DLRM-style CTR, device-timed, max over ranks)",
+            "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 dense tower, fp32 embeddings and optimizer state", "data": "synthetic (seeded), random-init weights",
+            "impl": arm.name,
+            "config": {
+                "model": "dlrm_ctr: 13 dense + 26 multi-hot fields (Poisson(20) in [1,100]) -> one merged dim-128 dynamic table, "
+                         "sum pooling, bottom MLP 512-256-128, dot interaction, top MLP 1024-1024-512-256-1, sparse Adam + Adam",
+                "global_batch": global_batch, "per_gpu_batch": spec.batch, "seq_len": None,
+                "ids": "Zipf(1.05) over 2^40 folded onto 1e8 distinct ids", "parallelism": f"dp{world} dense + row-sharded embeddings",
+                "l2": "no explicit flush: each step touches > 1 GB of embedding rows and optimizer state, far beyond the 126 MB L2",
+                "comm": arm.comm_mode(),
+            },
+            "clocks": clocks,
+            "e2e": {"value": value_e2e, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": 4, "last_loss": losses[-1] if losses else None},
+            "gpu_launches": launches,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ====================================================================== our arm
+class OursArm:
+    name = "ours"
+
+    def build(self, fields, dev, world, rank, capacity):
+        import torch
+        from recis_b200.models.dlrm import DLRM
+        from recis_b200.nn import filter_out_sparse_param
+        from recis_b200.optim import SparseAdam
+        from recis_b200.parallel.dense_reducer import DenseGradReducer
+        torch.manual_seed(1234)
+        model = DLRM(fields, dense_dim=13, emb_dim=EMB_DIM, device=dev, capacity=capacity).to(dev)
+        sparse_opt = SparseAdam(filter_out_sparse_param(model), lr=1e-3)
+        dense_params = [p for p in model.parameters() if p.requires_grad]
+        dense_opt = torch.optim.Adam(dense_params, lr=1e-3, fused=True)
+        reducer = DenseGradReducer(dense_params, world) if world > 1 else None
+        return dict(model=model, sparse_opt=sparse_opt, dense_opt=dense_opt, reducer=reducer)
+
+    def wrap_host(self, arrays, batch):
+        import numpy as np
+        import torch
+        from recis_b200.ragged import RaggedTensor
+        out = {}
+        for k, v in arrays.items():
+            if isinstance(v, tuple):
+                out[k] = RaggedTensor(torch.from_numpy(v[0]).pin_memory(), [torch.from_numpy(v[1]).pin_memory()], dense_shape=(batch, -1))
+            else:
+                out[k] = torch.from_numpy(np.ascontiguousarray(v)).pin_memory()
+        return out
+
+    def nbytes(self, b):
+        from recis_b200.io.synthetic import batch_nbytes
+        return batch_nbytes(b)
+
+    def to_device(self, b, dev):
+        from recis_b200.io.synthetic import to_device
+        return to_device(b, dev, non_blocking=True)
+
+    def step(self, st, batch):
+        loss, _ = st["model"](batch)
+        st["dense_opt"].zero_grad(set_to_none=False) if st["reducer"] is not None else st["dense_opt"].zero_grad()
+        st["sparse_opt"].zero_grad()
+        loss.backward()
+        if st["reducer"] is not None:
+            st["reducer"].all_reduce()
+        st["dense_opt"].step()
+        st["sparse_opt"].step()
+        return loss.detach()
+
+    def launches(self):
+        import recis_b200
+        return int(recis_b200.native().launch_count())
+
+    def comm_mode(self):
+        return os.environ.get("RECIS_COMM", "auto")
+
+
+def main():
+    args = parse()
+    if args.comm:
+        os.environ["RECIS_COMM"] = args.comm
+    if args.impl == "reference":
+        from baseline.reference_arm import ReferenceArm, unavailable_reason
+        why = unavailable_reason()
+        if why:
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+            return
+        run(args, ReferenceArm())
+    else:
+        run(args, OursArm())
+
+
+if __name__ == "__main__":
+    main()

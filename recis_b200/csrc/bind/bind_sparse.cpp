@@ -6,6 +6,7 @@
 #include "../cpu/rb_cpu.h"
 #include "../kernels/rb_kernels.h"
 #include "store.h"
+#include "../common/rb_launch.h"
 
 namespace py = pybind11;
 using torch::Tensor;
@@ -266,4 +267,5 @@ void init_sparse(py::module& m) {
   m.def("grad_reduce", &grad_reduce);
   m.def("sparse_apply", &sparse_apply);
   m.def("grad_reduce_chunk", []() { return rb_grad_reduce_chunk(); });
+  m.def("launch_count", []() { return rb_launch_count(); });
 }

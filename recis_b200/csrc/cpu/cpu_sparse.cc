@@ -99,6 +99,7 @@ void rbc_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, co
     }
   }
   const int64_t step = step_dev ? *step_dev : 0;
+  for (int64_t i = n; i < n_max; ++i) rows_out[i] = -1;
   for (int64_t i = 0; i < n; ++i) {
     const int32_t s = slot_scratch[i];
     int32_t row = -1;
@@ -117,6 +118,7 @@ void rbc_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, co
 
 void rbc_table_find(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* rows_out) {
   const int64_t n = eff_n(n_max, n_dev);
+  for (int64_t i = n; i < n_max; ++i) rows_out[i] = -1;
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; ++i) {
     const uint64_t key = (uint64_t)ids[i];

@@ -15,6 +15,7 @@
 // per-element atomic traffic and no intermediate gradient tensor on the single-GPU path.
 #include "../common/rb_common.cuh"
 #include "rb_kernels.h"
+#include "../common/rb_launch.h"
 #include <cub/device/device_radix_sort.cuh>
 
 using namespace rb;
@@ -504,29 +505,35 @@ void rb_dedup_partition(const int64_t* ids, int64_t n, int world, uint64_t* set_
   const int g = grid_stride_blocks(n);
   dedup_claim_kernel<<<g, kThreads, 2 * world * sizeof(int32_t), st>>>(ids, n, world, set_keys, set_pos, (uint64_t)set_cap - 1,
                                                                       slot_scratch, counts);
+  rb::note_launch();
   dedup_assign_kernel<<<g, kThreads, (world + 1) * sizeof(int32_t), st>>>(ids, n, world, set_pos, slot_scratch, counts, offsets,
                                                                          unique_ids, reverse);
+  rb::note_launch();
 }
 
 void rb_encode_merge(const int64_t* desc, const int64_t* table_idx, int F, int64_t total_nnz, int64_t total_seg,
                      int64_t* ids_out, int32_t* offsets_out, cudaStream_t st) {
   encode_merge_kernel<<<grid_stride_blocks(total_nnz + total_seg + 1), kThreads, 0, st>>>(desc, table_idx, F, total_nnz, total_seg,
                                                                                          ids_out, offsets_out);
+  rb::note_launch();
 }
 
 void rb_gather_rows(const float* src, const int32_t* rows, int64_t n_max, const int32_t* n_dev, int D, float* out, cudaStream_t st) {
   if (n_max <= 0) return;
   gather_rows_kernel<<<grid_stride_blocks(n_max * ((D + 3) / 4)), kThreads, 0, st>>>(src, rows, n_max, n_dev, D, out);
+  rb::note_launch();
 }
 
 void rb_scatter_rows(float* dst, const int32_t* rows, int64_t n, int D, const float* src, int src_broadcast, cudaStream_t st) {
   if (n <= 0) return;
   scatter_rows_kernel<<<grid_stride_blocks(n * D), kThreads, 0, st>>>(dst, rows, n, D, src, src_broadcast);
+  rb::note_launch();
 }
 
 void rb_fill_rows_i64(int64_t* dst, const int32_t* rows, int64_t n, int64_t value, cudaStream_t st) {
   if (n <= 0) return;
   fill_rows_i64_kernel<<<grid_stride_blocks(n), kThreads, 0, st>>>(dst, rows, n, value);
+  rb::note_launch();
 }
 
 void rb_pool_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
@@ -538,10 +545,13 @@ void rb_pool_forward(const float* base, const int32_t* rows, const int32_t* rev,
     const int64_t blocks = (n_seg + (kThreads / G) - 1) / (kThreads / G);
     pool_forward_kernel<G, NACC><<<(int)std::min<int64_t>(blocks, 148 * 64), kThreads, 0, st>>>(
         base, rows, rev, offsets, weights, n_seg, D, mode, perm_b, perm_f, out, gsrc, gscale);
+        rb::note_launch();
   });
-  if (!ok)
+  if (!ok) {
     pool_forward_scalar_kernel<<<grid_stride_blocks(n_seg * D), kThreads, 0, st>>>(base, rows, rev, offsets, weights, n_seg, D, mode,
                                                                                   perm_b, perm_f, out, gsrc, gscale);
+    rb::note_launch();
+  }
 }
 
 void rb_tile_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
@@ -549,6 +559,7 @@ void rb_tile_forward(const float* base, const int32_t* rows, const int32_t* rev,
   if (n_seg <= 0) return;
   tile_forward_kernel<<<grid_stride_blocks(n_seg * tile_len * D), kThreads, 0, st>>>(base, rows, rev, offsets, weights, n_seg, D,
                                                                                     tile_len, out, gsrc, gscale);
+  rb::note_launch();
 }
 
 size_t rb_sort_temp_bytes(int64_t n) {
@@ -562,8 +573,10 @@ void rb_build_csr(const int32_t* reverse, int64_t n, int key_bits, void* temp, s
                   int32_t* csr_u, int32_t* csr_elem, int32_t* start, cudaStream_t st) {
   if (n <= 0) return;
   iota_kernel<<<grid_stride_blocks(n), kThreads, 0, st>>>(iota_scratch, n);
+  rb::note_launch();
   cub::DeviceRadixSort::SortPairs(temp, temp_bytes, reverse, csr_u, (const int32_t*)iota_scratch, csr_elem, (int)n, 0, key_bits, st);
   csr_heads_kernel<<<grid_stride_blocks(n), kThreads, 0, st>>>(csr_u, n, start);
+  rb::note_launch();
 }
 
 int rb_grad_reduce_chunk() { return kChunk; }
@@ -579,16 +592,21 @@ void rb_grad_reduce(const float* grad_out, const int32_t* gsrc, const float* gsc
     const int grid = (int)std::min<int64_t>(blocks, 148 * 64);
     grad_reduce_kernel<G, NACC><<<grid, kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, span_acc, rows, gu,
                                                            apply, opt);
+  rb::note_launch();
     grad_span_finish_kernel<G, NACC><<<grid, kThreads, 0, st>>>(csr_u, start, n, D, span_acc, rows, gu, apply, opt);
+    rb::note_launch();
   });
-  if (!ok)
+  if (!ok) {
     grad_reduce_scalar_kernel<<<grid_stride_blocks(n * D), kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, rows,
                                                                              gu, apply, opt);
+    rb::note_launch();
+  }
 }
 
 void rb_sparse_apply(const int32_t* rows, const float* grads, int64_t n_max, const int32_t* n_dev, int D, RbOpt opt, cudaStream_t st) {
   if (n_max <= 0) return;
   sparse_apply_kernel<<<grid_stride_blocks(n_max * ((D + 3) / 4)), kThreads, 0, st>>>(rows, grads, n_max, n_dev, D, opt);
+  rb::note_launch();
 }
 
 }  // extern "C"

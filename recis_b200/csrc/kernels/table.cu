@@ -14,6 +14,7 @@
 // and are advanced by the resolve kernel, so no thread ever waits for another.
 #include "../common/rb_common.cuh"
 #include "rb_kernels.h"
+#include "../common/rb_launch.h"
 #include <cooperative_groups.h>
 
 namespace cg = cooperative_groups;
@@ -121,7 +122,8 @@ table_resolve_kernel(RbTable t, const int32_t* __restrict__ slots, int64_t n_max
                      int finalize) {
   const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
   const int64_t step = step_dev ? *step_dev : 0;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_max; i += (int64_t)gridDim.x * blockDim.x) {
+    if (i >= n) { rows_out[i] = -1; continue; }  // entries past the device-side count read as "no row"
     const int32_t s = slots[i];
     int32_t row = -1;
     if (s >= 0) { row = t.rows[s]; if (row < 0) row = -1; }
@@ -146,7 +148,8 @@ __global__ void __launch_bounds__(kThreads)
 table_find_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, const int32_t* __restrict__ n_dev,
                   int32_t* __restrict__ rows_out) {
   const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_max; i += (int64_t)gridDim.x * blockDim.x) {
+    if (i >= n) { rows_out[i] = -1; continue; }
     const uint64_t key = (uint64_t)ids[i];
     int32_t row = -1;
     if (key < kErasedKey) {
@@ -253,28 +256,35 @@ void rb_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, con
   const int g = grid_for(n_max);
   InitSpec spec{init.kind, init.a, init.b, init.lo, init.hi, init.seed};
   table_claim_kernel<<<g, kThreads, 0, st>>>(t, ids, n_max, n_dev, slot_scratch, new_rows, new_keys, admit_threshold, 1);
+  rb::note_launch();
   table_init_rows_kernel<<<grid_for(n_max * ((D + 3) / 4), 4), kThreads, 0, st>>>(t, new_rows, new_keys, emb, D, spec);
+  rb::note_launch();
   table_resolve_kernel<<<g, kThreads, 0, st>>>(t, slot_scratch, n_max, n_dev, rows_out, last_seen, step_dev, 1);
+  rb::note_launch();
 }
 
 void rb_table_find(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* rows_out, cudaStream_t st) {
   if (n_max <= 0) return;
   table_find_kernel<<<grid_for(n_max), kThreads, 0, st>>>(t, ids, n_max, n_dev, rows_out);
+  rb::note_launch();
 }
 
 void rb_table_erase(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* erased_rows, cudaStream_t st) {
   if (n_max <= 0) return;
   table_erase_kernel<<<grid_for(n_max), kThreads, 0, st>>>(t, ids, n_max, n_dev, erased_rows);
+  rb::note_launch();
 }
 
 void rb_table_snapshot(RbTable t, int64_t* ids_out, int32_t* rows_out, int64_t out_cap, int64_t* counter,
                        const int64_t* last_seen, int64_t threshold, int use_filter, cudaStream_t st) {
   table_snapshot_kernel<<<grid_for((int64_t)t.mask + 1), kThreads, 0, st>>>(t, ids_out, rows_out, out_cap, counter, last_seen,
                                                                            threshold, use_filter);
+  rb::note_launch();
 }
 
 void rb_table_rehash(RbTable src, RbTable dst, cudaStream_t st) {
   table_rehash_kernel<<<grid_for((int64_t)src.mask + 1), kThreads, 0, st>>>(src, dst);
+  rb::note_launch();
 }
 
 }  // extern "C"

@@ -1,0 +1,218 @@
+"""EmbeddingEngine: many features, few physical tables.
+
+Semantics of the reference's ``recis/nn/modules/embedding_engine.py:17-832``:
+
+* features whose ``EmbeddingOption.coalesced_info()`` (dim, dtype, device, initializer, grad_reduce_by,
+  filter_hook) agree are merged into ONE physical table named ``CoalescedHashtable_<sha256>``; each distinct
+  ``shared_name`` becomes a child with a 12-bit prefix in the top bits of the id;
+* inside a table, features with equal ``runtime_info()`` (combiner, use_weight, trainable, admit_hook, ...)
+  are concatenated so that each (table, runtime group) does one lookup/exchange per step;
+* results are split back per feature and shaped ``[batch, ..., dim]``; keys without an embedding option pass
+  through (ragged tensors become dense).
+
+The concatenation (id prefixing + offset rebasing for all features of a group) is a single multi-tensor
+kernel driven by a small descriptor table that is copied asynchronously; nothing synchronises with the host.
+With ``interleave=True`` the pooled rows of a group are written directly in ``[batch, feature, dim]`` order,
+so a model that wants the stacked tensor (``EmbeddingEngine.packed``) gets it without a copy.
+"""
+from __future__ import annotations
+
+import copy
+import hashlib
+import math
+from collections import OrderedDict, defaultdict
+
+import torch
+from torch import nn
+
+from ... import native
+from ...ragged.tensor import RaggedTensor
+from .embedding import DynamicEmbedding, EmbeddingOption
+
+
+class _Group:
+    """Features that share one physical table."""
+
+    def __init__(self, name):
+        self.name = name
+        self.opt = None
+        self.children = OrderedDict()  # shared_name -> child index
+        self.fea_runtime = {}
+        self.fea_child = {}
+
+    def add(self, fea_name, opt: EmbeddingOption):
+        if self.opt is None:
+            self.opt = copy.copy(opt)
+        if opt.shared_name not in self.children:
+            self.children[opt.shared_name] = len(self.children)
+        self.fea_runtime[fea_name] = opt.runtime_info()
+        self.fea_child[fea_name] = self.children[opt.shared_name]
+
+    def embedding_option(self, capacity):
+        o = self.opt
+        return EmbeddingOption(
+            embedding_dim=o.embedding_dim, block_size=o.block_size, dtype=o.dtype, device=o.device, shared_name=self.name,
+            children=list(self.children.keys()), coalesced=True, initializer=o.initializer, grad_reduce_by=o.grad_reduce_by,
+            fp16_enabled=o.fp16_enabled, filter_hook=o.filter_hook, pg=o.pg, max_partition_num=o.max_partition_num,
+            capacity=capacity, mean_by_weight=o.mean_by_weight,
+        )
+
+
+class EmbeddingEngine(nn.Module):
+    def __init__(self, emb_options: dict, interleave: bool = False):
+        super().__init__()
+        self._ht = nn.ModuleDict()
+        self._groups = {}
+        self._fea_to_ht = {}
+        self._emb_opts = emb_options
+        self._interleave = interleave
+        self.packed = {}
+        shared_to_ht = {}
+        capacity = defaultdict(int)
+        for fea_name, opt in emb_options.items():
+            ht_name = f"CoalescedHashtable_{hashlib.sha256(opt.coalesced_info().encode()).hexdigest()}"
+            if shared_to_ht.setdefault(opt.shared_name, ht_name) != ht_name:
+                raise RuntimeError(
+                    f"Create embedding failed, emb shared name {opt.shared_name} already created with a different "
+                    f"merge key; current: {opt.coalesced_info()}")
+            if ht_name not in self._groups:
+                self._groups[ht_name] = _Group(ht_name)
+            self._groups[ht_name].add(fea_name, opt)
+            self._fea_to_ht[fea_name] = ht_name
+        for fea_name, opt in emb_options.items():
+            capacity[self._fea_to_ht[fea_name]] += int(opt.capacity or 0)
+        for ht_name, group in self._groups.items():
+            self._ht[ht_name] = DynamicEmbedding(group.embedding_option(capacity[ht_name]))
+
+    # ------------------------------------------------------------------ helpers
+    def tables(self):
+        return {k: v for k, v in self._ht.items()}
+
+    def table_of(self, fea_name) -> DynamicEmbedding:
+        return self._ht[self._fea_to_ht[fea_name]]
+
+    @staticmethod
+    def _format(fea, opt: EmbeddingOption, device):
+        """feature tensor -> (ids int64 [n], offsets int32 [S+1], weights or None, n_segments, out shape)."""
+        dim = opt.embedding_dim
+        if isinstance(fea, RaggedTensor):
+            ids = fea.values()
+            weight = fea.weight()
+            offsets = fea.offsets()[-1]
+            n_seg = offsets.numel() - 1
+            if len(fea.offsets()) == 1:
+                lead = (n_seg,)
+            else:
+                lead = fea.real_shape(0, -1)
+                if math.prod(lead) != n_seg:
+                    raise RuntimeError(f"RaggedTensor must pad before lookup, got: {fea}")
+            if opt.combiner == "tile":
+                shape = (lead[0], opt.combiner_kwargs["tile_len"], dim) if len(lead) == 1 else lead + (opt.combiner_kwargs["tile_len"] * dim,)
+            else:
+                shape = tuple(lead) + (dim,)
+        elif isinstance(fea, torch.Tensor):
+            if fea.is_sparse:
+                raise TypeError("EmbeddingEngine doesn't support sparse ids")
+            if fea.dim() == 1:
+                fea = fea.unsqueeze(-1)
+            width = fea.shape[-1]
+            n_seg = fea.numel() // max(width, 1)
+            ids = fea.reshape(-1)
+            weight = None
+            offsets = torch.arange(0, (n_seg + 1) * width, width, dtype=torch.int32, device=fea.device)
+            if opt.combiner == "tile":
+                shape = (fea.shape[0], dim * opt.combiner_kwargs["tile_len"])
+            else:
+                shape = tuple(fea.shape[:-1]) + (dim,)
+        else:
+            raise TypeError(f"EmbeddingEngine only support tensor but get {type(fea)}")
+        if ids.dtype != torch.int64:
+            ids = ids.to(torch.int64)
+        if offsets.dtype != torch.int32:
+            offsets = offsets.to(torch.int32)
+        ids = ids.to(device).contiguous()
+        offsets = offsets.to(device).contiguous()
+        if not opt.use_weight:
+            weight = None
+        elif weight is not None:
+            weight = weight.to(device=device, dtype=torch.float32).contiguous()
+        return ids, offsets, weight, n_seg, shape
+
+    def _coalesce(self, feats, device):
+        """Concatenate formatted features: one kernel prefixes ids and rebases offsets for all of them."""
+        F = len(feats)
+        nnz = [f["ids"].numel() for f in feats]
+        segs = [f["n_seg"] for f in feats]
+        nnz_prefix = [0]
+        seg_prefix = [0]
+        for a, b in zip(nnz, segs):
+            nnz_prefix.append(nnz_prefix[-1] + a)
+            seg_prefix.append(seg_prefix[-1] + b)
+        desc = torch.tensor(
+            [[f["ids"].data_ptr() for f in feats] + [0], nnz_prefix,
+             [f["offsets"].data_ptr() for f in feats] + [0], seg_prefix], dtype=torch.int64)
+        tidx = torch.tensor([f["child"] for f in feats], dtype=torch.int64)
+        if device.type == "cuda":
+            desc = desc.pin_memory().to(device, non_blocking=True)
+            tidx = tidx.pin_memory().to(device, non_blocking=True)
+        ids, offsets = native().encode_merge(desc, tidx, F, nnz_prefix[-1], seg_prefix[-1], True)
+        weights = None
+        if any(f["weight"] is not None for f in feats):
+            ws = [f["weight"] if f["weight"] is not None else torch.ones(f["ids"].numel(), device=device) for f in feats]
+            weights = torch.cat(ws) if len(ws) > 1 else ws[0]
+        return ids, offsets, weights
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, input_features: dict):
+        grouped = defaultdict(lambda: defaultdict(list))
+        outs = {}
+        direct = {}
+        for fea_name, fea in input_features.items():
+            if fea_name not in self._fea_to_ht:
+                direct[fea_name] = fea
+                continue
+            ht_name = self._fea_to_ht[fea_name]
+            group = self._groups[ht_name]
+            opt = self._emb_opts[fea_name]
+            dev = self._ht[ht_name].impl.device
+            ids, offsets, weight, n_seg, shape = self._format(fea, opt, dev)
+            grouped[ht_name][group.fea_runtime[fea_name]].append(dict(
+                name=fea_name, ids=ids, offsets=offsets, weight=weight, n_seg=n_seg, shape=shape, child=group.fea_child[fea_name],
+                opt=opt))
+        self.packed = {}
+        for ht_name, runtimes in grouped.items():
+            ht: DynamicEmbedding = self._ht[ht_name]
+            dev = ht.impl.device
+            for run_key, feats in runtimes.items():
+                opt = feats[0]["opt"]
+                ids, offsets, weights = self._coalesce(feats, dev)
+                tile_len = opt.combiner_kwargs["tile_len"] if opt.combiner == "tile" else 0
+                segs = [f["n_seg"] for f in feats]
+                perm = None
+                if self._interleave and opt.combiner != "tile" and len(set(segs)) == 1 and len(feats) > 1:
+                    perm = (segs[0], len(feats))
+                ht.option.mean_by_weight = opt.mean_by_weight
+                pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, tile_len, perm, opt.admit_hook)
+                if not opt.trainable:
+                    pooled = pooled.detach()
+                D = opt.embedding_dim
+                if perm is not None:
+                    cube = pooled.view(segs[0], len(feats), D)
+                    self.packed[(ht_name, run_key)] = (cube, [f["name"] for f in feats])
+                    for j, f in enumerate(feats):
+                        outs[f["name"]] = cube[:, j, :].reshape(f["shape"]) if len(f["shape"]) != 2 else cube[:, j, :]
+                else:
+                    rows_per = [s * tile_len if tile_len else s for s in segs] if False else segs
+                    pooled = pooled.view(-1, (tile_len or 1) * D)
+                    start = 0
+                    for f, s in zip(feats, rows_per):
+                        outs[f["name"]] = pooled[start:start + s].reshape(f["shape"])
+                        start += s
+        for k, v in direct.items():
+            if isinstance(v, RaggedTensor):
+                outs[k] = v.to_dense()
+            elif isinstance(v, torch.Tensor) and v.is_sparse:
+                raise TypeError("EmbeddingEngine doesn't support sparse tensor")
+            else:
+                outs[k] = v
+        return outs

@@ -1,0 +1,203 @@
+"""GPU tests: every sm_100a sparse kernel against the CPU implementation of the same operation."""
+import pytest
+import torch
+
+import recis_b200
+from recis_b200.nn import EmbeddingEngine, EmbeddingOption, HashTable, filter_out_sparse_param
+from recis_b200.nn.hashtable_hook import FilterHook
+from recis_b200.nn.initializers import NormalInitializer
+from recis_b200.optim import SparseAdagrad, SparseAdam
+from recis_b200.ragged import RaggedTensor
+
+pytestmark = pytest.mark.gpu
+C = recis_b200.native()
+DEV = "cuda:0"
+
+
+def make_store(device, dim=8, cap=64, kind=2):
+    return C.EmbeddingStore(dim, cap, device, kind, 0.0, 0.05, -0.1, 0.1, 99, True, True, None)
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("n", [1, 1000, 300000])
+def test_dedup_partition_gpu(world, n):
+    torch.manual_seed(n + world)
+    ids = (torch.randint(0, max(n // 3, 2), (n,), dtype=torch.int64) * 2654435761) - 7
+    ids[::17] = -1
+    uniq, rev, counts, offs = C.dedup_partition(ids.to(DEV), world)
+    cu, crev, ccounts, coffs = C.dedup_partition(ids, world)
+    assert torch.equal(counts.cpu(), ccounts) and torch.equal(offs.cpu(), coffs)
+    nu = int(offs[-1])
+    assert torch.equal(uniq[:nu][rev.long()].cpu(), ids)
+    for r in range(world):
+        a = uniq[offs[r]:offs[r + 1]].cpu().sort().values
+        b = cu[coffs[r]:coffs[r + 1]].sort().values
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dim", [4, 16, 128, 7])
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+def test_store_gpu_matches_cpu(dim, kind):
+    torch.manual_seed(dim)
+    g, c = make_store(DEV, dim, 32, kind), make_store("cpu", dim, 32, kind)
+    ids = torch.randint(0, 1 << 40, (20000,), dtype=torch.int64)
+    ids = torch.cat([ids, ids[:5000]])           # duplicates inside one call
+    rg = g.lookup_or_insert(ids.to(DEV), None, None, 1)
+    rc = c.lookup_or_insert(ids, None, None, 1)
+    assert g.size() == c.size() == ids.unique().numel()
+    assert int(rg.min()) >= 0
+    eg = g.emb()[rg.long()].cpu(); ec = c.emb()[rc.long()]
+    assert torch.allclose(eg, ec, atol=2e-6, rtol=1e-5)
+    # same id -> same row
+    assert torch.equal(rg[:5000], rg[20000:])
+    assert torch.equal(g.find(ids.to(DEV), None), rg)
+    er = g.erase(ids[:1000].unique().to(DEV))
+    assert int(er.min()) >= 0 and g.size() == c.size() - ids[:1000].unique().numel()
+    assert int(g.find(ids[:1000].to(DEV), None).max()) == -1
+    k, r = g.snapshot(False, 0)
+    assert k.numel() == g.size()
+    assert g.counters()[3] == 0
+
+
+def test_store_device_count_and_admission():
+    g = make_store(DEV, 8, 1024)
+    ids = torch.arange(100, dtype=torch.int64, device=DEV) * 31
+    n_dev = torch.tensor([40], dtype=torch.int32, device=DEV)
+    step = torch.tensor([3], dtype=torch.int64, device=DEV)
+    r = g.lookup_or_insert(ids, n_dev, step, 1)
+    assert g.size() == 40 and int(r[40:].max()) == -1 and int(r[:40].min()) >= 0
+    assert int(g.last_seen()[r[:40].long()].min()) == 3
+    g2 = make_store(DEV, 8, 1024)
+    assert int(g2.lookup_or_insert(ids, None, step, 3).max()) == -1
+    assert int(g2.lookup_or_insert(ids, None, step, 3).max()) == -1
+    assert int(g2.lookup_or_insert(ids, None, step, 3).min()) >= 0 and g2.size() == 100
+
+
+@pytest.mark.parametrize("dim", [4, 16, 64, 128, 256, 6])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_pool_and_grad_reduce_gpu(dim, mode):
+    torch.manual_seed(dim + mode)
+    U, S = 5000, 3000
+    emb = torch.randn(U, dim)
+    lens = torch.randint(0, 30, (S,))
+    offsets = torch.zeros(S + 1, dtype=torch.int32); offsets[1:] = torch.cumsum(lens, 0)
+    n = int(offsets[-1])
+    raw = torch.randint(0, U, (n,))
+    raw[: n // 3] = 7                                 # one very hot id: exercises the chunk-spanning path
+    rev = torch.unique(raw, return_inverse=True)[1].to(torch.int32)
+    w = torch.rand(n) + 0.5
+    oc, gsrc_c, gscale_c = C.pool_forward(emb, None, rev, offsets, w, mode, 0, 0, True)
+    og, gsrc_g, gscale_g = C.pool_forward(emb.to(DEV), None, rev.to(DEV), offsets.to(DEV), w.to(DEV), mode, 0, 0, True)
+    assert torch.allclose(og.cpu(), oc, atol=1e-4, rtol=1e-4)
+    assert torch.equal(gsrc_g.cpu(), gsrc_c) and torch.allclose(gscale_g.cpu(), gscale_c)
+    cu_c = C.build_csr(rev); cu_g = C.build_csr(rev.to(DEV))
+    for a, b in zip(cu_c[:2], cu_g[:2]):
+        assert torch.equal(a, b.cpu())
+    nu = int(rev.max()) + 1
+    assert torch.equal(cu_c[2][: nu + 1], cu_g[2][: nu + 1].cpu())
+    go = torch.randn(S, dim)
+    args = (dim, None, False, 2, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 1.0, None, None, None, nu)
+    gu_c = C.grad_reduce(go, gsrc_c, gscale_c, *cu_c, *args)
+    gu_g = C.grad_reduce(go.to(DEV), gsrc_g, gscale_g, *cu_g, *args)
+    ref = torch.zeros(nu, dim, dtype=torch.float64).index_add_(0, rev.long(), (go[gsrc_c.long()] * gscale_c[:, None]).double())
+    assert torch.allclose(gu_c.double(), ref, atol=1e-3, rtol=1e-4)
+    assert torch.allclose(gu_g.cpu().double(), ref, atol=1e-3, rtol=1e-4)
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2])
+def test_fused_reduce_apply_gpu(kind):
+    torch.manual_seed(kind)
+    dim, U, S = 32, 800, 600
+    lens = torch.randint(1, 12, (S,))
+    offsets = torch.zeros(S + 1, dtype=torch.int32); offsets[1:] = torch.cumsum(lens, 0)
+    n = int(offsets[-1])
+    raw = torch.randint(0, U, (n,)); raw[: n // 4] = 3
+    rev = torch.unique(raw, return_inverse=True)[1].to(torch.int32)
+    nu = int(rev.max()) + 1
+    rows = torch.randperm(2000)[:nu].to(torch.int32)
+    rows[5] = -1                                       # a not-admitted id: no update
+    w0, m0, v0 = torch.randn(2000, dim), torch.rand(2000, dim), torch.rand(2000, dim)
+    go = torch.randn(S, dim)
+    hyper = (kind, 0.01, 0.9, 0.999, 1e-8, 0.99, -0.02, 0.5)
+    res = []
+    for dev in ("cpu", DEV):
+        w, m, v = w0.clone().to(dev), m0.clone().to(dev), v0.clone().to(dev)
+        _, gsrc, gscale = C.pool_forward(w, rows.to(dev), rev.to(dev), offsets.to(dev), None, 0, 0, 0, True)
+        csr = C.build_csr(rev.to(dev))
+        C.grad_reduce(go.to(dev), gsrc, gscale, *csr, dim, rows.to(dev), True, *hyper, w, m, v, 0)
+        res.append((w.cpu(), m.cpu(), v.cpu()))
+    for a, b in zip(*res):
+        assert torch.allclose(a, b, atol=1e-4, rtol=1e-4)
+    assert not torch.equal(res[0][0], w0)
+    # two-step path (store per-unique gradient, then apply) agrees with the fused kernel
+    w, m, v = w0.clone().to(DEV), m0.clone().to(DEV), v0.clone().to(DEV)
+    _, gsrc, gscale = C.pool_forward(w, rows.to(DEV), rev.to(DEV), offsets.to(DEV), None, 0, 0, 0, True)
+    csr = C.build_csr(rev.to(DEV))
+    gu = C.grad_reduce(go.to(DEV), gsrc, gscale, *csr, dim, None, False, 2, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 1.0, None, None, None, nu)
+    C.sparse_apply(rows.to(DEV), gu, None, *hyper, w, m, v)
+    assert torch.allclose(w.cpu(), res[1][0], atol=1e-4, rtol=1e-4)
+
+
+def test_tile_and_perm_gpu():
+    torch.manual_seed(0)
+    emb = torch.randn(50, 16)
+    B, F = 8, 3
+    lens = torch.randint(0, 6, (B * F,))
+    offsets = torch.zeros(B * F + 1, dtype=torch.int32); offsets[1:] = torch.cumsum(lens, 0)
+    rev = torch.randint(0, 50, (int(offsets[-1]),), dtype=torch.int32)
+    for fn_args in ((C.tile_forward, (4, True)), (C.pool_forward, (0, B, F, True))):
+        fn, extra = fn_args
+        c = fn(emb, None, rev, offsets, None, *extra)
+        g = fn(emb.to(DEV), None, rev.to(DEV), offsets.to(DEV), None, *extra)
+        assert torch.allclose(g[0].cpu(), c[0], atol=1e-5)
+        assert torch.equal(g[1].cpu(), c[1])
+    plain = C.pool_forward(emb, None, rev, offsets, None, 0, 0, 0, False)[0]
+    perm = C.pool_forward(emb, None, rev, offsets, None, 0, B, F, False)[0]
+    assert torch.equal(perm.view(B, F, 16).transpose(0, 1).reshape(B * F, 16), plain)
+
+
+def _run_engine(device, steps=3):
+    torch.manual_seed(0)
+    from recis_b200.nn.modules.hashtable import HashtableRegister
+    HashtableRegister().clear()
+    init = NormalInitializer(0, 0.05)
+    opts = {f"f{i}": EmbeddingOption(embedding_dim=32, shared_name=f"f{i}", combiner="sum" if i % 2 else "mean", initializer=init,
+                                     device=device) for i in range(6)}
+    eng = EmbeddingEngine(opts)
+    opt = SparseAdam(filter_out_sparse_param(eng), lr=0.01)
+    g = torch.Generator().manual_seed(1)
+    outs = []
+    for t in range(steps):
+        feats, coefs = {}, {}
+        for i in range(6):
+            lens = torch.randint(1, 8, (64,), generator=g)
+            off = torch.zeros(65, dtype=torch.int32); off[1:] = torch.cumsum(lens, 0)
+            vals = torch.randint(0, 300, (int(off[-1]),), generator=g)
+            feats[f"f{i}"] = RaggedTensor(vals, [off], weight=torch.rand(int(off[-1]), generator=g)).to(device)
+            coefs[f"f{i}"] = torch.randn(64, 32, generator=g).to(device)
+        out = eng(feats)
+        loss = sum((out[k] * coefs[k]).sum() for k in out)
+        opt.zero_grad(); loss.backward(); opt.step()
+        outs.append(torch.stack([out[f"f{i}"].detach().cpu() for i in range(6)]))
+    return outs
+
+
+def test_engine_training_gpu_matches_cpu():
+    a = _run_engine("cpu"); b = _run_engine(DEV)
+    for x, y in zip(a, b):
+        assert torch.allclose(x, y, atol=2e-4, rtol=1e-3)
+
+
+def test_filter_hook_gpu():
+    ht = HashTable([8], initializer=NormalInitializer(0, 1), name="gpu_ttl", device=DEV,
+                   filter_hook=FilterHook("GlobalStepFilter", {"filter_step": 1}))
+    ht(torch.arange(100, device=DEV))
+    for _ in range(3):
+        ht._filter_hook_impl.update_step()
+        ht(torch.arange(10, device=DEV))
+    assert ht._filter_hook_impl.do_filter() == 90 and ht.impl.size() == 10
+
+
+def test_smoke_entry():
+    import __graft_entry__ as ge
+    ge.smoke()
