@@ -43,6 +43,12 @@ class ReferenceArm:
         from recis.nn.modules.hashtable import filter_out_sparse_param
         from recis.optim import SparseAdam
 
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            # the reference's DynamicEmbedding reads the default process group even on one GPU
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29533")
+            dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
         torch.manual_seed(1234)
         D = 128
 

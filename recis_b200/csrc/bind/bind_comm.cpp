@@ -1,0 +1,125 @@
+// Symmetric (peer-mapped) memory and the Python bindings of the peer-memory exchange kernels.
+//
+// A symmetric buffer is a plain cudaMalloc allocation (outside torch's caching allocator, so that it can be exported)
+// wrapped as a tensor; its cudaIpc handle is exchanged through torch.distributed by the Python side and opened by every
+// other rank. Kernels then receive one pointer per rank. The reference has nothing comparable: all of its inter-GPU
+// traffic goes through torch.distributed collectives (recis/nn/modules/embedding.py:73-118,498-542).
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include "../kernels/rb_comm.h"
+#include "store.h"
+
+namespace py = pybind11;
+using torch::Tensor;
+using OptT = c10::optional<Tensor>;
+
+namespace {
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream(); }
+
+#define RB_CUDA_CHECK(expr)                                                                         \
+  do {                                                                                              \
+    cudaError_t e__ = (expr);                                                                       \
+    TORCH_CHECK(e__ == cudaSuccess, #expr, " failed: ", cudaGetErrorString(e__));                   \
+  } while (0)
+
+// (tensor over a fresh zeroed cudaMalloc allocation, its 64-byte IPC handle)
+std::tuple<Tensor, py::bytes> sym_alloc(int64_t nbytes, int64_t device_index) {
+  c10::cuda::CUDAGuard g(torch::Device(torch::kCUDA, (c10::DeviceIndex)device_index));
+  void* ptr = nullptr;
+  nbytes = std::max<int64_t>((nbytes + 255) / 256 * 256, 256);
+  RB_CUDA_CHECK(cudaMalloc(&ptr, (size_t)nbytes));
+  RB_CUDA_CHECK(cudaMemset(ptr, 0, (size_t)nbytes));
+  cudaIpcMemHandle_t h;
+  RB_CUDA_CHECK(cudaIpcGetMemHandle(&h, ptr));
+  auto t = torch::from_blob(ptr, {nbytes}, [](void* p) { cudaFree(p); },
+                            torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, (c10::DeviceIndex)device_index));
+  return {t, py::bytes(reinterpret_cast<const char*>(&h), sizeof(h))};
+}
+
+int64_t sym_open(const std::string& handle, int64_t device_index) {
+  TORCH_CHECK(handle.size() == sizeof(cudaIpcMemHandle_t), "bad IPC handle size");
+  c10::cuda::CUDAGuard g(torch::Device(torch::kCUDA, (c10::DeviceIndex)device_index));
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle.data(), sizeof(h));
+  void* ptr = nullptr;
+  RB_CUDA_CHECK(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return reinterpret_cast<int64_t>(ptr);
+}
+
+void sym_close(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
+
+RbPeers peers_of(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(ptrs.size() <= RB_MAX_PEERS, "at most ", RB_MAX_PEERS, " ranks per node are supported by the fused exchange");
+  RbPeers p;
+  for (int i = 0; i < RB_MAX_PEERS; ++i) p.p[i] = i < (int)ptrs.size() ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  return p;
+}
+
+void comm_signal(const std::vector<int64_t>& flag_pads, int64_t channel, int64_t me, int64_t epoch) {
+  rb_comm_signal(peers_of(flag_pads), (int)channel, (int)me, (int)flag_pads.size(), epoch, cur_stream());
+}
+
+void comm_wait(const Tensor& flags, int64_t channel, int64_t world, int64_t epoch, int64_t spin_limit, Tensor status) {
+  rb_comm_wait(flags.data_ptr<int64_t>(), (int)channel, (int)world, epoch, spin_limit, status.data_ptr<int64_t>(), cur_stream());
+}
+
+void comm_pull_ids(const std::vector<int64_t>& peer_ids, const std::vector<int64_t>& peer_offsets, int64_t me, Tensor ids_in,
+                   Tensor prefix, Tensor n_in, Tensor status) {
+  rb_comm_pull_ids(peers_of(peer_ids), peers_of(peer_offsets), (int)me, (int)peer_ids.size(), ids_in.data_ptr<int64_t>(), ids_in.numel(),
+                   prefix.data_ptr<int32_t>(), n_in.data_ptr<int32_t>(), status.data_ptr<int64_t>(), cur_stream());
+}
+
+void comm_push_emb(const Tensor& emb, const Tensor& rows_in, const Tensor& prefix, const std::vector<int64_t>& peer_uemb, int64_t me,
+                   int64_t n_in_hint) {
+  const int D = (int)emb.size(1);
+  TORCH_CHECK(D % 4 == 0, "the fused exchange needs an embedding width that is a multiple of 4");
+  rb_comm_push_emb(emb.data_ptr<float>(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), peers_of(peer_uemb), (int)me,
+                   (int)peer_uemb.size(), D, n_in_hint, cur_stream());
+}
+
+// apply: update rows of (w, s1, s2) in place. Otherwise returns (rows [n_in_max] with -1 holes, grads [n_in_max, D]).
+std::tuple<Tensor, Tensor> comm_owner_reduce(const Tensor& rows_in, Tensor head, const Tensor& prefix, const std::vector<int64_t>& peer_gu, int64_t me, int64_t D, bool mean_by_id, bool apply,
+                                             int64_t kind, double lr, double beta1, double beta2, double eps, double decay, double alpha,
+                                             double grad_scale, OptT w, OptT s1, OptT s2, int64_t n_in_hint) {
+  RbOpt o;
+  o.kind = (int)kind; o.lr = (float)lr; o.beta1 = (float)beta1; o.beta2 = (float)beta2; o.eps = (float)eps; o.decay = (float)decay;
+  o.alpha = (float)alpha; o.grad_scale = (float)grad_scale;
+  o.w = w.has_value() && w->defined() ? w->data_ptr<float>() : nullptr;
+  o.s1 = s1.has_value() && s1->defined() ? s1->data_ptr<float>() : nullptr;
+  o.s2 = s2.has_value() && s2->defined() ? s2->data_ptr<float>() : nullptr;
+  const int64_t n_max = rows_in.numel();
+  auto next = torch::empty({n_max}, rows_in.options());
+  Tensor out_rows, out_grads;
+  if (!apply) {
+    out_rows = torch::full({n_in_hint}, -1, rows_in.options());
+    out_grads = torch::zeros({n_in_hint, D}, rows_in.options().dtype(torch::kFloat32));
+  } else {
+    TORCH_CHECK(o.w != nullptr, "apply needs the weight slab");
+  }
+  rb_comm_owner_reduce(rows_in.data_ptr<int32_t>(), head.data_ptr<int32_t>(), next.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(),
+                       peers_of(peer_gu), (int)me, (int)peer_gu.size(), (int)D, mean_by_id, apply, o,
+                       apply ? nullptr : out_rows.data_ptr<int32_t>(), apply ? nullptr : out_grads.data_ptr<float>(), n_in_hint,
+                       cur_stream());
+  return {out_rows, out_grads};
+}
+
+void comm_allreduce_slice(const std::vector<int64_t>& bufs, int64_t me, int64_t n_padded, double scale) {
+  rb_comm_allreduce_slice(peers_of(bufs), (int)me, (int)bufs.size(), n_padded, (float)scale, cur_stream());
+}
+
+}  // namespace
+
+void init_comm(py::module& m) {
+  m.def("sym_alloc", &sym_alloc);
+  m.def("sym_open", &sym_open);
+  m.def("sym_close", &sym_close);
+  m.def("comm_signal", &comm_signal);
+  m.def("comm_wait", &comm_wait);
+  m.def("comm_pull_ids", &comm_pull_ids);
+  m.def("comm_push_emb", &comm_push_emb);
+  m.def("comm_owner_reduce", &comm_owner_reduce);
+  m.def("comm_allreduce_slice", &comm_allreduce_slice);
+  m.attr("MAX_PEERS") = RB_MAX_PEERS;
+}

@@ -21,7 +21,8 @@ inline const float* opt_f32(const OptT& t) { return t.has_value() && t->defined(
 int64_t pow2_at_least(int64_t x) { int64_t p = 64; while (p < x) p <<= 1; return p; }
 
 // ids -> (unique ids bucketed by owner rank, reverse index, per-owner counts, per-owner offsets)
-std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, int64_t world) {
+// unique_out / offsets_out (optional) let the caller place the results in peer-visible memory.
+std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, int64_t world, OptT unique_out, OptT offsets_out) {
   TORCH_CHECK(ids.scalar_type() == torch::kInt64 && ids.is_contiguous(), "ids: contiguous int64 expected");
   TORCH_CHECK(world >= 1 && world <= 1024, "world size out of range");
   const int64_t n = ids.numel();
@@ -31,8 +32,10 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, in
   auto set_pos = torch::empty({cap + 1}, o.dtype(torch::kInt32));
   auto slot = torch::empty({std::max<int64_t>(n, 1)}, o.dtype(torch::kInt32));
   auto counts = torch::empty({world}, o.dtype(torch::kInt32));
-  auto offsets = torch::empty({world + 1}, o.dtype(torch::kInt32));
-  auto unique_ids = torch::empty({n}, o);
+  Tensor offsets = offsets_out.has_value() && offsets_out->defined() ? *offsets_out : torch::empty({world + 1}, o.dtype(torch::kInt32));
+  Tensor unique_ids = unique_out.has_value() && unique_out->defined() ? *unique_out : torch::empty({n}, o);
+  TORCH_CHECK(offsets.numel() >= world + 1 && offsets.scalar_type() == torch::kInt32 && unique_ids.numel() >= n &&
+              unique_ids.scalar_type() == torch::kInt64, "dedup_partition: output buffers too small or of the wrong type");
   auto reverse = torch::empty({n}, o.dtype(torch::kInt32));
   if (ids.is_cuda()) {
     c10::cuda::CUDAGuard g(ids.device());
@@ -183,12 +186,12 @@ RbOpt make_opt(int64_t kind, double lr, double beta1, double beta2, double eps, 
 // apply=true: runs the optimizer on row rows[u] of (w, s1, s2) in the same kernel and returns an empty tensor.
 Tensor grad_reduce(const Tensor& grad_out, const Tensor& gsrc, const Tensor& gscale, const Tensor& csr_u, const Tensor& csr_elem,
                    const Tensor& start, int64_t D, OptT rows, bool apply, int64_t kind, double lr, double beta1, double beta2, double eps,
-                   double decay, double alpha, double grad_scale, OptT w, OptT s1, OptT s2, int64_t n_unique_max) {
+                   double decay, double alpha, double grad_scale, OptT w, OptT s1, OptT s2, int64_t n_unique_max, OptT gu_out) {
   TORCH_CHECK(grad_out.is_contiguous() && grad_out.scalar_type() == torch::kFloat32, "grad_out must be contiguous fp32");
   const int64_t n = csr_u.numel();
   RbOpt opt = make_opt(kind, lr, beta1, beta2, eps, decay, alpha, grad_scale, w, s1, s2);
   if (apply) TORCH_CHECK(opt.w != nullptr, "apply needs the weight slab");
-  Tensor gu = apply ? Tensor() : torch::zeros({n_unique_max, D}, grad_out.options());
+  Tensor gu = apply ? Tensor() : (gu_out.has_value() && gu_out->defined() ? *gu_out : torch::zeros({n_unique_max, D}, grad_out.options()));
   float* gup = apply ? nullptr : gu.data_ptr<float>();
   if (n == 0) return gu;
   if (grad_out.is_cuda()) {
@@ -256,7 +259,8 @@ void init_sparse(py::module& m) {
       .def("dim", &EmbeddingStore::dim)
       .def("set_name", &EmbeddingStore::set_name);
 
-  m.def("dedup_partition", &dedup_partition);
+  m.def("dedup_partition", &dedup_partition, py::arg("ids"), py::arg("world"), py::arg("unique_out") = py::none(),
+        py::arg("offsets_out") = py::none());
   m.def("encode_merge", &encode_merge);
   m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("rows"), py::arg("n_dev") = py::none());
   m.def("scatter_rows", &scatter_rows);
@@ -264,7 +268,10 @@ void init_sparse(py::module& m) {
   m.def("pool_forward", &pool_forward);
   m.def("tile_forward", &tile_forward);
   m.def("build_csr", &build_csr);
-  m.def("grad_reduce", &grad_reduce);
+  m.def("grad_reduce", &grad_reduce, py::arg("grad_out"), py::arg("gsrc"), py::arg("gscale"), py::arg("csr_u"), py::arg("csr_elem"), py::arg("start"),
+        py::arg("D"), py::arg("rows"), py::arg("apply"), py::arg("kind"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"),
+        py::arg("decay"), py::arg("alpha"), py::arg("grad_scale"), py::arg("w"), py::arg("s1"), py::arg("s2"), py::arg("n_unique_max"),
+        py::arg("gu_out") = py::none());
   m.def("sparse_apply", &sparse_apply);
   m.def("grad_reduce_chunk", []() { return rb_grad_reduce_chunk(); });
   m.def("launch_count", []() { return rb_launch_count(); });

@@ -2,8 +2,12 @@
 #include <torch/extension.h>
 
 void init_sparse(pybind11::module& m);
+void init_dense(pybind11::module& m);
+void init_comm(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "recis_b200 native extension (sm_100a kernels + CPU implementations)";
   init_sparse(m);
+  init_dense(m);
+  init_comm(m);
 }

@@ -1,0 +1,333 @@
+// bf16 GEMM for the dense towers on the 5th-generation tensor cores (sm_100a):
+//   D[MM, NN] = act( A[MM, KK] * B[NN, KK]^T + bias[NN] )            fp32 accumulation in tensor memory
+//
+// * operands are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no cluster multicast),
+// * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, 128 x BN x 16 per instruction),
+// * the accumulator lives in TMEM and is read back with tcgen05.ld for a fused bias + ReLU + convert epilogue,
+// * warp-specialised: warp 0 = TMA producer, warp 1 = MMA issuer (owns the TMEM allocation), warps 2..5 = epilogue,
+// * a ring of kStages shared-memory stages with full/empty mbarriers overlaps copies with math.
+//
+// Either operand may be "K-major" (reduction dimension contiguous in memory: x[MM][KK]) or "MN-major" (output
+// dimension contiguous: x[KK][MM]); the second form is what the backward GEMMs need (dgrad reads W[N][K] as its
+// B operand, wgrad reads dY[M][N] and X[M][K] with the batch as the reduction), so no transposed copies are made.
+//
+// The reference has no GEMM kernel of its own: its dense layers are nn.Linear (cuBLAS), see
+// examples/deepfm/deepfm_model.py:49-52 in the reference project.
+//
+// Every mbarrier wait is bounded; on a timeout the kernel records kStatusWaitTimeout in the status word, drains its
+// outstanding copies (bounded), frees its tensor memory and returns.
+#include "../common/rb_common.cuh"
+#include "../common/rb_launch.h"
+#include "rb_dense.h"
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <mutex>
+
+namespace {
+
+constexpr int BM = 128;       // rows of D per CTA (= UMMA M, = TMEM lanes)
+constexpr int BN = 128;       // columns of D per CTA (= UMMA N, = TMEM fp32 columns)
+constexpr int BK = 64;        // reduction elements per stage (64 bf16 = one 128-byte swizzle row)
+constexpr int UK = 16;        // reduction elements per tcgen05.mma (bf16)
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr uint32_t kTileBytes = BM * BK * 2;                    // 16 KB per operand per stage
+constexpr uint32_t kStageBytes = 2 * kTileBytes;
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;   // + slack for 1024-byte alignment
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false (and raises the CTA-wide abort flag) when the limit is hit or another thread aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading/stride byte offsets (16-byte units),
+// version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+
+template <typename OutT> struct Store;
+template <> struct Store<__nv_bfloat16> {
+  static __device__ __forceinline__ void row32(__nv_bfloat16* dst, const float (&v)[32], int valid, bool vec_ok) {
+    if (vec_ok && valid == 32) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]), p1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]), p3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
+        uint4 u;
+        u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
+        u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
+        d4[q] = u;
+      }
+    } else {
+      for (int j = 0; j < valid; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+};
+template <> struct Store<float> {
+  static __device__ __forceinline__ void row32(float* dst, const float (&v)[32], int valid, bool vec_ok) {
+    if (vec_ok && valid == 32) {
+      float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) d4[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+    } else {
+      for (int j = 0; j < valid; ++j) dst[j] = v[j];
+    }
+  }
+};
+
+template <bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         OutT* __restrict__ out, const float* __restrict__ bias, const float* __restrict__ beta_src,
+                         int MM, int NN, int KK, int ldo, int relu, int64_t* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t tmem_full_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int num_kb = (KK + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&tmem_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    int issued = 0;
+    bool ok = true;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % kStages;
+      const uint32_t ph = (uint32_t)(kb / kStages) & 1u;
+      ok = mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag);
+      if (!ok) break;
+      uint8_t* sa = smem + s * kStageBytes;
+      uint8_t* sb = sa + kTileBytes;
+      mbar_expect_tx(&full_bar[s], kStageBytes);
+      const int k0 = kb * BK;
+      if (!A_MN) tma_load_2d(sa, &map_a, k0, m0, &full_bar[s]);                      // box {BK, BM}
+      else { tma_load_2d(sa, &map_a, m0, k0, &full_bar[s]); tma_load_2d(sa + kTileBytes / 2, &map_a, m0 + 64, k0, &full_bar[s]); }  // 2 x box {64, BK}
+      if (!B_MN) tma_load_2d(sb, &map_b, k0, n0, &full_bar[s]);
+      else { tma_load_2d(sb, &map_b, n0, k0, &full_bar[s]); tma_load_2d(sb + kTileBytes / 2, &map_b, n0 + 64, k0, &full_bar[s]); }
+      ++issued;
+    }
+    if (!ok) {
+      // drain: the copies already issued must land before this CTA's shared memory goes away
+      for (int j = max(0, issued - kStages); j < issued; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (uint32_t)(j / kStages) & 1u;
+        for (uint32_t it = 0; it < kSpinLimit; ++it) if (mbar_try_wait(&full_bar[s], ph)) break;
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    // instruction descriptor: D = f32, A = B = bf16, majors, N >> 3, M >> 4
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    bool ok = true;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % kStages;
+      const uint32_t ph = (uint32_t)(kb / kStages) & 1u;
+      ok = mbar_wait(&full_bar[s], ph, &abort_flag);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t sa = smem_u32(smem + s * kStageBytes), sb = sa + kTileBytes;
+#pragma unroll
+      for (int k = 0; k < BK / UK; ++k) {
+        // K-major: 16 elements = 32 bytes further along the swizzled 128-byte row; 8-row groups are 1024 bytes apart.
+        // MN-major: 16 reduction rows = two 8-row (1024-byte) groups; 64-wide MN blocks are BK*128 bytes apart.
+        const uint64_t da = A_MN ? make_desc(sa + k * 2048, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
+        const uint64_t db = B_MN ? make_desc(sb + k * 2048, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
+        umma_bf16(tmem_base, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+      }
+      umma_commit(&empty_bar[s]);     // stage reusable once these MMAs have read it
+    }
+    if (ok) umma_commit(&tmem_full_bar);
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------------ epilogue (4 warps, one TMEM lane quarter each)
+    const bool ok = num_kb > 0 ? mbar_wait(&tmem_full_bar, 0, &abort_flag) : true;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const int q = warp & 3;
+      const int row = m0 + q * 32 + lane;
+      const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= NN) break;
+        uint32_t r[32];
+        if (num_kb > 0) {
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (row < MM) {
+          float v[32];
+          const int valid = min(32, NN - (n0 + c0));
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(r[j]);
+            if (j < valid) {
+              if (bias) x += bias[n0 + c0 + j];
+              if (beta_src) x += beta_src[(int64_t)row * ldo + n0 + c0 + j];
+            }
+            v[j] = relu ? fmaxf(x, 0.f) : x;
+          }
+          Store<OutT>::row32(out + (int64_t)row * ldo + n0 + c0, v, valid, vec_ok);
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+  }
+  if (threadIdx.x == 0 && abort_flag) rb::set_status(status, rb::kStatusWaitTimeout);
+}
+
+// ---------------------------------------------------------------------- host side
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                             const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                             CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor [rows][cols] (cols contiguous, row pitch ld elements), box {box_cols, box_rows}, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const float* bias, const float* beta_src, int MM, int NN, int KK,
+           int ldo, int relu, int64_t* status, cudaStream_t st) {
+  auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess) return 3;
+    attr_set = true;
+  }
+  dim3 grid((NN + BN - 1) / BN, (MM + BM - 1) / BM);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, reinterpret_cast<OutT*>(out), bias, beta_src, MM, NN, KK, ldo, relu, status);
+  rb::note_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+}  // namespace
+
+extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo,
+                            int out_fp32, const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int64_t* status,
+                            cudaStream_t st) {
+  if (MM <= 0 || NN <= 0) return 0;
+  // TMA constraints: 16-byte aligned base, row pitch a multiple of 16 bytes
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (lda % 8) || (ldb % 8)) return 1;
+  CUtensorMap ma, mb;
+  const bool oka = a_mn ? make_map(&ma, a, KK, MM, lda, 64, BK) : make_map(&ma, a, MM, KK, lda, BK, BM);
+  const bool okb = b_mn ? make_map(&mb, b, KK, NN, ldb, 64, BK) : make_map(&mb, b, NN, KK, ldb, BK, BN);
+  if (!oka || !okb) return 2;
+#define RB_GEMM_CASE(AM, BMJ)                                                                                                   \
+  if ((a_mn != 0) == AM && (b_mn != 0) == BMJ)                                                                                  \
+    return out_fp32 ? launch<AM, BMJ, float>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st)               \
+                    : launch<AM, BMJ, __nv_bfloat16>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st);
+  RB_GEMM_CASE(false, false)
+  RB_GEMM_CASE(false, true)
+  RB_GEMM_CASE(true, false)
+  RB_GEMM_CASE(true, true)
+#undef RB_GEMM_CASE
+  return 5;
+}

@@ -1,0 +1,19 @@
+// C launch API of the dense-tower kernels (tensor-core GEMM, interactions, element-wise helpers).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// D[MM, NN] = act(A * B^T + bias (+ beta_src)); A is [MM][KK] (a_mn = 0, pitch lda) or [KK][MM] (a_mn = 1); B is [NN][KK]
+// (b_mn = 0) or [KK][NN] (b_mn = 1); bf16 operands, fp32 accumulation, bf16 or fp32 output with row pitch ldo.
+// beta_src (nullable, fp32, same layout as the output) is added before the activation (gradient accumulation).
+// Returns 0 on success; 1 = operand alignment unsuitable for TMA, 2 = tensor-map encode failed, >2 = launch error.
+int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo, int out_fp32,
+                 const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int64_t* status, cudaStream_t st);
+
+#ifdef __cplusplus
+}
+#endif

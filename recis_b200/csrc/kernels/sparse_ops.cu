@@ -15,6 +15,7 @@
 // per-element atomic traffic and no intermediate gradient tensor on the single-GPU path.
 #include "../common/rb_common.cuh"
 #include "rb_kernels.h"
+#include "rb_comm.h"
 #include "../common/rb_launch.h"
 #include <cub/device/device_radix_sort.cuh>
 
@@ -576,6 +577,19 @@ void rb_build_csr(const int32_t* reverse, int64_t n, int key_bits, void* temp, s
   rb::note_launch();
   cub::DeviceRadixSort::SortPairs(temp, temp_bytes, reverse, csr_u, (const int32_t*)iota_scratch, csr_elem, (int)n, 0, key_bits, st);
   csr_heads_kernel<<<grid_stride_blocks(n), kThreads, 0, st>>>(csr_u, n, start);
+  rb::note_launch();
+}
+
+void rb_sort_pairs_i32(const int32_t* keys_in, int32_t* keys_out, const int32_t* vals_in, int32_t* vals_out, int64_t n, int key_bits,
+                       void* temp, size_t temp_bytes, cudaStream_t st) {
+  if (n <= 0) return;
+  cub::DeviceRadixSort::SortPairs(temp, temp_bytes, keys_in, keys_out, vals_in, vals_out, (int)n, 0, key_bits, st);
+  rb::note_launch();
+}
+
+void rb_iota_i32(int32_t* out, int64_t n, cudaStream_t st) {
+  if (n <= 0) return;
+  iota_kernel<<<grid_stride_blocks(n), kThreads, 0, st>>>(out, n);
   rb::note_launch();
 }
 

@@ -232,7 +232,7 @@ class DynamicEmbedding(torch.nn.Module):
             self.fused = FusedExchange.create(emb_opt, self.pg, self.world_size, self.rank)
             if self.fused is not None:
                 storage = self.fused.table_storage()
-                growable = False
+                growable = storage is None
         self.table = HashTable(
             embedding_shape=[emb_opt.embedding_dim], block_size=emb_opt.block_size, dtype=emb_opt.dtype,
             device=emb_opt.device, coalesced=emb_opt.coalesced, children=emb_opt.children,
@@ -245,6 +245,7 @@ class DynamicEmbedding(torch.nn.Module):
         self._holder = torch.tensor([0.0], requires_grad=True)
         if self.fused is not None:
             self.fused.attach(self)
+            self.impl.exchange = self.fused
 
     @property
     def impl(self):

@@ -216,6 +216,10 @@ class HashtableImpl:
             if r["kind"] == "rows":
                 rows_l.append(r["rows"].reshape(-1))
                 grad_l.append(r["grad"].reshape(-1, self.dim).to(torch.float32))
+            elif r["kind"] == "peer":
+                rows, grads = r["exchange"].owner_reduce(self, r, apply=False)
+                rows_l.append(rows)
+                grad_l.append(grads)
             else:
                 csr_u, csr_elem, start = C.build_csr(r["rev"])
                 gu = C.grad_reduce(r["grad_out"], r["gsrc"], r["gscale"], csr_u, csr_elem, start, self.dim, None, False,

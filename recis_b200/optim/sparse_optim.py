@@ -96,6 +96,9 @@ class SparseOptimizer(Optimizer):
                 csr_u, csr_elem, start = C.build_csr(r["rev"])
                 C.grad_reduce(r["grad_out"], r["gsrc"], r["gscale"], csr_u, csr_elem, start, impl.dim, r["rows"], True, kind, lr,
                               b1, b2, eps, decay, alpha, r.get("scale", 1.0) * inv_accum, w, s1, s2, 0)
+            elif len(recs) == 1 and recs[0]["kind"] == "peer":
+                r = recs[0]
+                r["exchange"].owner_reduce(impl, r, True, kind, lr, b1, b2, eps, decay, alpha, inv_accum, w, s1, s2)
             else:
                 rows, grads = impl.materialize()
                 if rows is not None and rows.numel():
@@ -109,6 +112,11 @@ class SparseOptimizer(Optimizer):
 
     def set_grad_accum_steps(self, steps: int):
         self._grad_accum_steps = int(steps)
+        for impl in self._tables.values():
+            # with accumulation the owner must consume each micro-batch's gradient window before the next one overwrites it
+            ex = getattr(impl, "exchange", None)
+            if ex is not None:
+                ex.immediate_reduce = steps > 1
 
     # ---- state
     def _scalar_state(self) -> dict:

@@ -1,0 +1,155 @@
+"""Fused embedding exchange: the all-to-alls of a sharded lookup done by our own kernels over peer-mapped memory.
+
+Replaces, per table group and step, the reference's counts / ids / embeddings / gradients ``all_to_all_single`` calls and
+the host read of split sizes between them (``recis/nn/modules/embedding.py:498-624``). Protocol (kernels in
+``csrc/kernels/comm.cu``):
+
+forward   requester  dedup + bucket ids by owner straight into its symmetric window ............ signal IDS
+          owner      wait IDS; pull the ids bucketed for it from every requester (peer loads); table lookup-or-insert;
+                     push each row into the requester's unique-embedding buffer (peer stores) .. signal EMB
+          requester  wait EMB; pool from its (local) unique-embedding buffer
+backward  requester  segmented reduction of the pooled gradient to one gradient per unique id, written into its symmetric
+                     gradient window ......................................................... signal GRAD
+optimizer owner      wait GRAD; ONE kernel pulls every contribution of a touched row from the requesters' windows (peer
+                     loads), adds duplicates across requesters and applies the row-wise optimizer update
+
+No split size ever reaches the host; windows are sized for the worst case (``exchange_capacity`` unique ids per rank).
+All flag waits are bounded; a timeout or a window overflow sets a bit in ``status`` which ``check()`` turns into an exception.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import native
+from .symmetric import SymmetricHeap
+
+CH_IDS, CH_EMB, CH_GRAD, CH_AR0, CH_AR1, N_CH = 0, 1, 2, 3, 4, 8
+STATUS_TIMEOUT, STATUS_OVERFLOW = 4, 8
+
+
+class FusedExchange:
+    @staticmethod
+    def create(emb_opt, pg, world, rank):
+        if emb_opt.embedding_dim % 4 != 0 or emb_opt.dtype != torch.float32:
+            return None
+        if world > native().MAX_PEERS:
+            return None
+        return FusedExchange(emb_opt, pg, world, rank)
+
+    def __init__(self, emb_opt, pg, world, rank):
+        self.opt = emb_opt
+        self.pg, self.world, self.rank = pg, world, rank
+        self.device = torch.device(emb_opt.device)
+        self.D = emb_opt.embedding_dim
+        self.heap = None
+        self.epoch = 0
+        self.send_cap = int(os.environ.get("RECIS_EXCHANGE_CAPACITY", "0")) or int(getattr(emb_opt, "exchange_capacity", 0) or 0)
+        # ~1 s at the polling cadence of comm_wait_kernel; a dead peer then surfaces as an error, never as a hang
+        self.spin_limit = int(os.environ.get("RECIS_WAIT_SPINS", str(4_000_000)))
+        self.status = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self.immediate_reduce = False
+        self._head = None
+
+    def table_storage(self):
+        return None           # rows are pushed by their owner: the table arena itself need not be peer-visible
+
+    def attach(self, emb_mod):
+        self.emb_mod = emb_mod
+
+    # ------------------------------------------------------------------ setup (collective, at the first forward)
+    def _setup(self, nnz: int):
+        if not self.send_cap:
+            t = torch.tensor([nnz], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.pg)
+            self.send_cap = max(int(t.item()) * 2, 1024)
+        W, D, cap = self.world, self.D, self.send_cap
+        self.in_cap = min(W, 2) * cap
+        self.heap = SymmetricHeap({
+            "flags": (torch.int64, N_CH * W),
+            "offsets": (torch.int32, W + 1),
+            "ids": (torch.int64, cap),
+            "uemb": (torch.float32, cap * D),
+            "gu": (torch.float32, cap * D),
+        }, self.device, self.pg)
+        self.ids_in = torch.empty(self.in_cap, dtype=torch.int64, device=self.device)
+        self.prefix = torch.zeros(2 * W + 1, dtype=torch.int32, device=self.device)
+        self.n_in = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def check(self):
+        """Raise if a bounded wait timed out or a window overflowed (one host read; call at step boundaries / in tests)."""
+        s = int(self.status.item())
+        if s & STATUS_TIMEOUT:
+            raise RuntimeError("fused exchange: a peer did not signal within the wait limit (rank missing or stalled)")
+        if s & STATUS_OVERFLOW:
+            raise RuntimeError("fused exchange: receive window overflow; raise exchange_capacity / RECIS_EXCHANGE_CAPACITY")
+
+    def _head_for(self, store):
+        cap = store.capacity()
+        if self._head is None or self._head.numel() < cap:
+            self._head = torch.full((cap,), -1, dtype=torch.int32, device=self.device)
+        return self._head
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, emb_mod, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold, step):
+        C = native()
+        n = ids.numel()
+        if self.heap is None:
+            self._setup(n)
+        if n > self.send_cap:
+            raise RuntimeError(f"batch has {n} ids but the exchange window holds {self.send_cap}; set exchange_capacity "
+                               f"(EmbeddingOption) or RECIS_EXCHANGE_CAPACITY to the largest per-rank id count")
+        h, W, me, D = self.heap, self.world, self.rank, self.D
+        self.epoch += 1
+        e = self.epoch
+        store = emb_mod.impl.store
+        _uniq, rev, _counts, _offs = C.dedup_partition(ids, W, h["ids"].tensor, h["offsets"].tensor)
+        C.comm_signal(h["flags"].ptrs, CH_IDS, me, e)
+        C.comm_wait(h["flags"].tensor, CH_IDS, W, e, self.spin_limit, self.status)
+        C.comm_pull_ids(h["ids"].ptrs, h["offsets"].ptrs, me, self.ids_in, self.prefix, self.n_in, self.status)
+        if readonly:
+            rows_in = store.find(self.ids_in, self.n_in)
+        else:
+            rows_in = store.lookup_or_insert(self.ids_in, self.n_in, step, threshold)
+        prefix = self.prefix.clone()
+        C.comm_push_emb(store.emb(), rows_in, prefix, h["uemb"].ptrs, me, self.in_cap)
+        C.comm_signal(h["flags"].ptrs, CH_EMB, me, e)
+        C.comm_wait(h["flags"].tensor, CH_EMB, W, e, self.spin_limit, self.status)
+        uemb = h["uemb"].tensor.view(self.send_cap, D)
+        if combiner == "tile":
+            out, gsrc, gscale = C.tile_forward(uemb, None, rev, offsets, weights, tile_len, train)
+        else:
+            out, gsrc, gscale = C.pool_forward(uemb, None, rev, offsets, weights, mode, perm_b, perm_f, train)
+        saved = dict(rev=rev, gsrc=gsrc, gscale=gscale, rows_in=rows_in, prefix=prefix, epoch=e) if train else None
+        return out, saved
+
+    # ------------------------------------------------------------------ backward (requester side) + staging
+    def backward(self, emb_mod, s, grad_out, worker_scale):
+        C = native()
+        h, me, D = self.heap, self.rank, self.D
+        csr_u, csr_elem, start = C.build_csr(s["rev"])
+        C.grad_reduce(grad_out, s["gsrc"], s["gscale"], csr_u, csr_elem, start, D, None, False, 2, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0,
+                      1.0, None, None, None, self.send_cap, h["gu"].tensor.view(self.send_cap, D))
+        C.comm_signal(h["flags"].ptrs, CH_GRAD, me, s["epoch"])
+        rec = dict(rows_in=s["rows_in"], prefix=s["prefix"], epoch=s["epoch"], scale=worker_scale, exchange=self,
+                   mean_by_id=emb_mod.option.grad_reduce_by == "id")
+        if self.immediate_reduce:
+            rows, grads = self.owner_reduce(emb_mod.impl, rec, apply=False)
+            emb_mod.impl.accept_grad(rows, grads)
+        else:
+            rec["kind"] = "peer"
+            emb_mod.impl.records().append(rec)
+
+    # ------------------------------------------------------------------ owner side: pull + reduce (+ update)
+    def owner_reduce(self, impl, rec, apply, kind=2, lr=0.0, b1=0.0, b2=0.0, eps=0.0, decay=1.0, alpha=0.0, grad_scale=1.0,
+                     w=None, s1=None, s2=None):
+        C = native()
+        h = self.heap
+        C.comm_wait(h["flags"].tensor, CH_GRAD, self.world, rec["epoch"], self.spin_limit, self.status)
+        head = self._head_for(impl.store)
+        rows, grads = C.comm_owner_reduce(rec["rows_in"], head, rec["prefix"], h["gu"].ptrs, self.rank, self.D, rec["mean_by_id"],
+                                          apply, kind, lr, b1, b2, eps, decay, alpha, rec["scale"] * grad_scale, w, s1, s2,
+                                          self.in_cap)
+        return rows, grads

@@ -100,8 +100,9 @@ def test_pool_and_grad_reduce_gpu(dim, mode):
     gu_c = C.grad_reduce(go, gsrc_c, gscale_c, *cu_c, *args)
     gu_g = C.grad_reduce(go.to(DEV), gsrc_g, gscale_g, *cu_g, *args)
     ref = torch.zeros(nu, dim, dtype=torch.float64).index_add_(0, rev.long(), (go[gsrc_c.long()] * gscale_c[:, None]).double())
-    assert torch.allclose(gu_c.double(), ref, atol=1e-3, rtol=1e-4)
-    assert torch.allclose(gu_g.cpu().double(), ref, atol=1e-3, rtol=1e-4)
+    tol = 1e-5 * float(ref.abs().max()) + 1e-4        # fp32 accumulation over a very hot id: error scales with the sum
+    assert torch.allclose(gu_c.double(), ref, atol=tol, rtol=1e-4)
+    assert torch.allclose(gu_g.cpu().double(), ref, atol=tol, rtol=1e-4)
 
 
 @pytest.mark.parametrize("kind", [0, 1, 2])
