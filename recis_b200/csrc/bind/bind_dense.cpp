@@ -51,6 +51,72 @@ Tensor gemm_bf16(const Tensor& a, const Tensor& b, OptT bias, bool relu, bool a_
   return out;
 }
 
+// [x | strict lower triangle of Z Z^T | 0 pad]; Z = [x; cube]. out_cols = padded width (multiple of 8).
+Tensor dot_interaction_fwd(const Tensor& x, const Tensor& cube, int64_t out_cols) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && cube.scalar_type() == torch::kFloat32 &&
+              cube.is_contiguous() && cube.dim() == 3);
+  const int B = (int)cube.size(0), F = (int)cube.size(1), D = (int)cube.size(2);
+  TORCH_CHECK(x.size(0) == B && x.size(1) == D && out_cols >= D + (F + 1) * F / 2);
+  c10::cuda::CUDAGuard g(x.device());
+  auto out = torch::empty({B, out_cols}, x.options());
+  const int rc = rb_dot_interaction_fwd(x.data_ptr(), cube.data_ptr<float>(), B, F, D, (int)out_cols, out.data_ptr(),
+                                        at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(rc == 0, "dot_interaction: too many fields or too wide for shared memory (code ", rc, ")");
+  return out;
+}
+
+std::tuple<Tensor, Tensor> dot_interaction_bwd(const Tensor& x, const Tensor& cube, const Tensor& dout) {
+  const int B = (int)cube.size(0), F = (int)cube.size(1), D = (int)cube.size(2);
+  TORCH_CHECK(dout.scalar_type() == torch::kBFloat16 && dout.is_contiguous() && dout.size(0) == B);
+  c10::cuda::CUDAGuard g(x.device());
+  auto dx = torch::empty({B, D}, cube.options());
+  auto dcube = torch::empty_like(cube);
+  const int rc = rb_dot_interaction_bwd(x.data_ptr(), cube.data_ptr<float>(), dout.data_ptr(), B, F, D, (int)dout.size(1),
+                                        dx.data_ptr<float>(), dcube.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(rc == 0, "dot_interaction backward failed (code ", rc, ")");
+  return {dx, dcube};
+}
+
+Tensor fm_fwd(const Tensor& cube) {
+  TORCH_CHECK(cube.is_cuda() && cube.scalar_type() == torch::kFloat32 && cube.is_contiguous() && cube.dim() == 3);
+  c10::cuda::CUDAGuard g(cube.device());
+  auto out = torch::empty({cube.size(0), 1}, cube.options());
+  rb_fm_fwd(cube.data_ptr<float>(), (int)cube.size(0), (int)cube.size(1), (int)cube.size(2), out.data_ptr<float>(),
+            at::cuda::getCurrentCUDAStream());
+  return out;
+}
+
+Tensor fm_bwd(const Tensor& cube, const Tensor& gout) {
+  c10::cuda::CUDAGuard g(cube.device());
+  auto go = gout.contiguous().to(torch::kFloat32);
+  auto dcube = torch::empty_like(cube);
+  rb_fm_bwd(cube.data_ptr<float>(), go.data_ptr<float>(), (int)cube.size(0), (int)cube.size(1), (int)cube.size(2), dcube.data_ptr<float>(),
+            at::cuda::getCurrentCUDAStream());
+  return dcube;
+}
+
+// returns (dy bf16 [M, N], db fp32 [N])
+std::tuple<Tensor, Tensor> relu_bwd_bias(const Tensor& y, const Tensor& dout, bool relu) {
+  TORCH_CHECK(dout.is_cuda() && dout.scalar_type() == torch::kBFloat16 && dout.is_contiguous() && dout.dim() == 2);
+  TORCH_CHECK(!relu || (y.scalar_type() == torch::kBFloat16 && y.is_contiguous() && y.sizes() == dout.sizes()));
+  c10::cuda::CUDAGuard g(dout.device());
+  const int M = (int)dout.size(0), N = (int)dout.size(1);
+  Tensor dy = relu ? torch::empty_like(dout) : dout;
+  auto db = torch::zeros({N}, dout.options().dtype(torch::kFloat32));
+  rb_relu_bwd_bias(relu ? y.data_ptr() : nullptr, dout.data_ptr(), M, N, relu, relu ? dy.data_ptr() : nullptr, db.data_ptr<float>(),
+                   at::cuda::getCurrentCUDAStream());
+  return {dy, db};
+}
+
+Tensor cast_pad_bf16(const Tensor& src, int64_t rows_p, int64_t cols_p) {
+  TORCH_CHECK(src.is_cuda() && src.scalar_type() == torch::kFloat32 && src.dim() == 2 && src.stride(1) == 1);
+  c10::cuda::CUDAGuard g(src.device());
+  auto dst = torch::empty({rows_p, cols_p}, src.options().dtype(torch::kBFloat16));
+  rb_cast_pad_bf16(src.data_ptr<float>(), (int)src.size(0), (int)src.size(1), (int)src.stride(0), dst.data_ptr(), (int)rows_p, (int)cols_p,
+                   at::cuda::getCurrentCUDAStream());
+  return dst;
+}
+
 int64_t dense_status(const std::string& device) { return status_word(torch::Device(device)).item<int64_t>(); }
 
 }  // namespace
@@ -59,4 +125,10 @@ void init_dense(py::module& m) {
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("bias") = py::none(), py::arg("relu") = false,
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none());
   m.def("dense_status", &dense_status);
+  m.def("dot_interaction_fwd", &dot_interaction_fwd);
+  m.def("dot_interaction_bwd", &dot_interaction_bwd);
+  m.def("fm_fwd", &fm_fwd);
+  m.def("fm_bwd", &fm_bwd);
+  m.def("relu_bwd_bias", &relu_bwd_bias);
+  m.def("cast_pad_bf16", &cast_pad_bf16);
 }

@@ -1,0 +1,212 @@
+// Dense-tower helper kernels (sm_100a): pairwise dot interaction and FM second-order interaction (forward + backward),
+// ReLU-backward fused with the bias gradient, and the fp32 -> padded bf16 weight cast that feeds the tcgen05 GEMM.
+//
+// In the reference these are chains of PyTorch ops inside the example models (examples/deepfm/deepfm_model.py:88-93
+// computes the FM term with sum/pow/sub; a DLRM-style dot interaction would be bmm + tril-index gather, whose backward
+// is an index_put with accumulation). Here each is one kernel per direction.
+#include "../common/rb_common.cuh"
+#include "../common/rb_launch.h"
+#include "rb_dense.h"
+#include <cuda_bf16.h>
+
+namespace {
+
+constexpr int kMaxVec = 64;   // at most 63 embedding fields + the dense vector per sample
+
+// ---------------------------------------------------------------------------------- dot interaction
+// z_0 = x[b] (bf16), z_k = cube[b][k-1] (fp32). out[b] = [x (D values), z_i . z_j for i > j (row-major lower triangle), 0 pad]
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+dot_interaction_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ cube, int B, int F, int D, int out_ld,
+                           __nv_bfloat16* __restrict__ out) {
+  extern __shared__ float z[];                    // [(F+1)][D+1]
+  const int b = blockIdx.x;
+  const int V = F + 1, ld = D + 1;
+  for (int i = threadIdx.x; i < V * D; i += THREADS) {
+    const int v = i / D, d = i - v * D;
+    z[v * ld + d] = v == 0 ? __bfloat162float(x[(int64_t)b * D + d]) : cube[((int64_t)b * F + (v - 1)) * D + d];
+  }
+  __syncthreads();
+  __nv_bfloat16* o = out + (int64_t)b * out_ld;
+  for (int d = threadIdx.x; d < D; d += THREADS) o[d] = x[(int64_t)b * D + d];
+  const int P = V * (V - 1) / 2;
+  for (int p = threadIdx.x; p < P; p += THREADS) {
+    // p -> (i, j), i > j, row-major over the strict lower triangle
+    int i = (int)((1.f + sqrtf(1.f + 8.f * (float)p)) * 0.5f);
+    while (i * (i - 1) / 2 > p) --i;
+    while ((i + 1) * i / 2 <= p) ++i;
+    const int j = p - i * (i - 1) / 2;
+    const float* zi = z + i * ld; const float* zj = z + j * ld;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int d = 0; d < D; ++d) acc = fmaf(zi[d], zj[d], acc);
+    o[D + p] = __float2bfloat16_rn(acc);
+  }
+  for (int c = D + P + threadIdx.x; c < out_ld; c += THREADS) o[c] = __float2bfloat16_rn(0.f);
+}
+
+// dz_i = sum_{j != i} g_ij z_j with g the symmetric matrix built from the lower-triangle gradients; dx also gets dout[:, :D].
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+dot_interaction_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ cube, const __nv_bfloat16* __restrict__ dout,
+                           int B, int F, int D, int out_ld, float* __restrict__ dx, float* __restrict__ dcube) {
+  extern __shared__ float sm[];
+  const int V = F + 1, ld = D + 1;
+  float* z = sm;                  // [V][D+1]
+  float* g = sm + V * ld;         // [V][V]
+  const int b = blockIdx.x;
+  for (int i = threadIdx.x; i < V * D; i += THREADS) {
+    const int v = i / D, d = i - v * D;
+    z[v * ld + d] = v == 0 ? __bfloat162float(x[(int64_t)b * D + d]) : cube[((int64_t)b * F + (v - 1)) * D + d];
+  }
+  const __nv_bfloat16* go = dout + (int64_t)b * out_ld;
+  for (int e = threadIdx.x; e < V * V; e += THREADS) {
+    const int i = e / V, j = e - i * V;
+    float v = 0.f;
+    if (i > j) v = __bfloat162float(go[D + i * (i - 1) / 2 + j]);
+    else if (j > i) v = __bfloat162float(go[D + j * (j - 1) / 2 + i]);
+    g[e] = v;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += THREADS) {
+    float col[kMaxVec];
+#pragma unroll 1
+    for (int j = 0; j < V; ++j) col[j] = z[j * ld + d];
+    for (int i = 0; i < V; ++i) {
+      float acc = 0.f;
+      const float* gi = g + i * V;
+      for (int j = 0; j < V; ++j) acc = fmaf(gi[j], col[j], acc);
+      if (i == 0) dx[(int64_t)b * D + d] = acc + __bfloat162float(go[d]);
+      else dcube[((int64_t)b * F + (i - 1)) * D + d] = acc;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------- FM second-order term
+// out[b] = 0.5 * sum_d ((sum_f w_f v_fd)^2 - sum_f (w_f v_fd)^2); cube [B, F, D] fp32 (weights already applied by the caller)
+__global__ void __launch_bounds__(128)
+fm_fwd_kernel(const float* __restrict__ cube, int B, int F, int D, float* __restrict__ out) {
+  __shared__ float red[4];
+  const int b = blockIdx.x;
+  float part = 0.f;
+  for (int d = threadIdx.x; d < D; d += 128) {
+    float s = 0.f, s2 = 0.f;
+    for (int f = 0; f < F; ++f) { const float v = cube[((int64_t)b * F + f) * D + d]; s += v; s2 = fmaf(v, v, s2); }
+    part += s * s - s2;
+  }
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+  __syncthreads();
+  if (threadIdx.x == 0) out[b] = 0.5f * (red[0] + red[1] + red[2] + red[3]);
+}
+
+// dcube[b,f,d] = g[b] * (S_d - v_fd)
+__global__ void __launch_bounds__(128)
+fm_bwd_kernel(const float* __restrict__ cube, const float* __restrict__ gout, int B, int F, int D, float* __restrict__ dcube) {
+  const int b = blockIdx.x;
+  const float g = gout[b];
+  for (int d = threadIdx.x; d < D; d += 128) {
+    float s = 0.f;
+    for (int f = 0; f < F; ++f) s += cube[((int64_t)b * F + f) * D + d];
+    for (int f = 0; f < F; ++f) {
+      const int64_t o = ((int64_t)b * F + f) * D + d;
+      dcube[o] = g * (s - cube[o]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------- ReLU backward + bias gradient
+// dy[m, n] = y[m, n] > 0 ? dout[m, n] : 0 (relu != 0), db[n] += sum_m dy[m, n]. One block handles 32 columns x 256-row slabs.
+__global__ void __launch_bounds__(256)
+relu_bwd_bias_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ dout, int M, int N, int relu,
+                     __nv_bfloat16* __restrict__ dy, float* __restrict__ db) {
+  __shared__ float part[8][33];
+  const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int rlane = threadIdx.x >> 5;                       // 8 row lanes
+  float acc = 0.f;
+  if (col < N) {
+    for (int m = blockIdx.y * 8 + rlane; m < M; m += gridDim.y * 8) {
+      const int64_t o = (int64_t)m * N + col;
+      float v = __bfloat162float(dout[o]);
+      if (relu && !(__bfloat162float(y[o]) > 0.f)) v = 0.f;
+      if (dy) dy[o] = __float2bfloat16_rn(v);
+      acc += v;
+    }
+  }
+  part[rlane][threadIdx.x & 31] = acc;
+  __syncthreads();
+  if (rlane == 0 && col < N && db) {
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) s += part[r][threadIdx.x & 31];
+    atomicAdd(db + col, s);
+  }
+}
+
+// fp32 [rows, cols] (row pitch src_ld) -> bf16 [rows_p, cols_p], zero padded
+__global__ void __launch_bounds__(256)
+cast_pad_bf16_kernel(const float* __restrict__ src, int rows, int cols, int src_ld, __nv_bfloat16* __restrict__ dst, int rows_p, int cols_p) {
+  const int64_t total = (int64_t)rows_p * cols_p;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / cols_p), c = (int)(i - (int64_t)r * cols_p);
+    dst[i] = __float2bfloat16_rn((r < rows && c < cols) ? src[(int64_t)r * src_ld + c] : 0.f);
+  }
+}
+
+inline int blocks_for(int64_t n) { int64_t b = (n + 255) / 256; return (int)std::min<int64_t>(std::max<int64_t>(b, 1), 148 * 16); }
+
+}  // namespace
+
+extern "C" {
+
+int rb_dot_interaction_fwd(const void* x, const float* cube, int B, int F, int D, int out_ld, void* out, cudaStream_t st) {
+  if (F + 1 > kMaxVec) return 1;
+  const size_t smem = (size_t)(F + 1) * (D + 1) * sizeof(float);
+  if (smem > 200 * 1024) return 2;
+  auto kern = dot_interaction_fwd_kernel<128>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  kern<<<B, 128, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), cube, B, F, D, out_ld, reinterpret_cast<__nv_bfloat16*>(out));
+  rb::note_launch();
+  return 0;
+}
+
+int rb_dot_interaction_bwd(const void* x, const float* cube, const void* dout, int B, int F, int D, int out_ld, float* dx, float* dcube,
+                           cudaStream_t st) {
+  if (F + 1 > kMaxVec) return 1;
+  const size_t smem = ((size_t)(F + 1) * (D + 1) + (size_t)(F + 1) * (F + 1)) * sizeof(float);
+  if (smem > 200 * 1024) return 2;
+  auto kern = dot_interaction_bwd_kernel<128>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  kern<<<B, 128, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), cube, reinterpret_cast<const __nv_bfloat16*>(dout), B, F, D, out_ld,
+                             dx, dcube);
+  rb::note_launch();
+  return 0;
+}
+
+void rb_fm_fwd(const float* cube, int B, int F, int D, float* out, cudaStream_t st) {
+  if (B <= 0) return;
+  fm_fwd_kernel<<<B, 128, 0, st>>>(cube, B, F, D, out);
+  rb::note_launch();
+}
+
+void rb_fm_bwd(const float* cube, const float* gout, int B, int F, int D, float* dcube, cudaStream_t st) {
+  if (B <= 0) return;
+  fm_bwd_kernel<<<B, 128, 0, st>>>(cube, gout, B, F, D, dcube);
+  rb::note_launch();
+}
+
+void rb_relu_bwd_bias(const void* y, const void* dout, int M, int N, int relu, void* dy, float* db, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return;
+  dim3 grid((N + 31) / 32, std::min(std::max(M / 256, 1), 64));
+  relu_bwd_bias_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(y), reinterpret_cast<const __nv_bfloat16*>(dout), M, N,
+                                             relu, reinterpret_cast<__nv_bfloat16*>(dy), db);
+  rb::note_launch();
+}
+
+void rb_cast_pad_bf16(const float* src, int rows, int cols, int src_ld, void* dst, int rows_p, int cols_p, cudaStream_t st) {
+  cast_pad_bf16_kernel<<<blocks_for((int64_t)rows_p * cols_p), 256, 0, st>>>(src, rows, cols, src_ld, reinterpret_cast<__nv_bfloat16*>(dst),
+                                                                             rows_p, cols_p);
+  rb::note_launch();
+}
+
+}  // extern "C"

@@ -17,3 +17,19 @@ int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b, int64_t ld
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+// x: bf16 [B, D]; cube: fp32 [B, F, D]; out: bf16 [B, out_ld] = [x, lower triangle of Z Z^T, zero pad]. Returns 0 on success.
+int rb_dot_interaction_fwd(const void* x, const float* cube, int B, int F, int D, int out_ld, void* out, cudaStream_t st);
+int rb_dot_interaction_bwd(const void* x, const float* cube, const void* dout, int B, int F, int D, int out_ld, float* dx, float* dcube,
+                           cudaStream_t st);
+void rb_fm_fwd(const float* cube, int B, int F, int D, float* out, cudaStream_t st);
+void rb_fm_bwd(const float* cube, const float* gout, int B, int F, int D, float* dcube, cudaStream_t st);
+// dy = relu ? dout * (y > 0) : dout (bf16, may be null to skip the store); db[n] += column sums of dy (fp32, may be null)
+void rb_relu_bwd_bias(const void* y, const void* dout, int M, int N, int relu, void* dy, float* db, cudaStream_t st);
+void rb_cast_pad_bf16(const float* src, int rows, int cols, int src_ld, void* dst, int rows_p, int cols_p, cudaStream_t st);
+#ifdef __cplusplus
+}
+#endif

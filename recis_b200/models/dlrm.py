@@ -41,5 +41,5 @@ class DLRM(nn.Module):
         assert names == self.fields
         x = self.bottom(dense)                                        # [B, D] compute dtype
         z = dot_interaction(x, cube)                                  # [B, D + pairs] compute dtype
-        logit = self.top(z).float()
+        logit = self.top(z)[:, :1].float()
         return self.loss_fn(logit, label), logit

@@ -1,15 +1,61 @@
-"""Dense-tower building blocks: Linear/MLP with bf16 compute and the feature interactions."""
+"""Dense-tower building blocks.
+
+On CUDA every Linear runs on the hand-written tcgen05 GEMM (``csrc/kernels/gemm_tcgen05.cu``): bf16 operands, fp32
+accumulation in tensor memory, bias + ReLU fused in the epilogue; the backward pass uses the same kernel with MN-major
+operands (no transposed copies) plus one fused ReLU-mask + bias-gradient kernel. The feature interactions (pairwise dot,
+FM second order) are single kernels per direction. On CPU (or for dtypes the kernels do not take) plain PyTorch is used,
+which is also the oracle in the tests. The reference's dense layers are ``nn.Linear`` under bf16 autocast
+(``examples/seq2seq/seq2seq_model.py:90``, ``examples/deepfm/deepfm_model.py:49-52``).
+"""
 from __future__ import annotations
 
 from typing import Sequence
 
 import torch
-from torch import nn
 import torch.nn.functional as F
+from torch import nn
+
+from .. import native
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+class _LinearFn(torch.autograd.Function):
+    """y[M, Np] = act(x[M, Kp] W^T + b) with W given as fp32 [N, K] (padded + cast to bf16 here)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, relu):
+        C = native()
+        N, K = weight.shape
+        Np, Kp = _pad8(N), _pad8(K)
+        assert x.shape[1] == Kp and x.dtype == torch.bfloat16
+        wb = C.cast_pad_bf16(weight, Np, Kp)
+        bp = bias if Np == N else F.pad(bias, (0, Np - N))
+        y = C.gemm_bf16(x, wb, bp, relu, False, False, False, None)
+        ctx.save_for_backward(x, wb, y)
+        ctx.relu, ctx.shape = relu, (N, K)
+        return y
+
+    @staticmethod
+    def backward(ctx, dout):
+        C = native()
+        x, wb, y = ctx.saved_tensors
+        N, K = ctx.shape
+        dy, db = C.relu_bwd_bias(y, dout.contiguous(), ctx.relu)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            # dx[M, Kp] = dy[M, Np] . W[Np, Kp]   (B operand read MN-major: no transposed copy of W)
+            dx = C.gemm_bf16(dy, wb, None, False, False, True, False, None)
+        # dW[Np, Kp] = dy^T . x                  (both operands MN-major, reduction over the batch)
+        dw = C.gemm_bf16(dy, x, None, False, True, True, True, None)
+        return dx, dw[:N, :K], db[:N], None
 
 
 class Linear(nn.Module):
-    """y = act(x W^T + b); fp32 master weights, bf16 compute on CUDA."""
+    """``y = act(x W^T + b)``; fp32 master weights, bf16 compute on CUDA. Output width is padded to a multiple of 8
+    (``out_pad``) so that it can feed the next layer's TMA loads directly; ``forward`` slices the padding off when asked."""
 
     def __init__(self, in_features, out_features, act: bool = False, dtype=torch.bfloat16):
         super().__init__()
@@ -18,38 +64,75 @@ class Linear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features))
         nn.init.kaiming_uniform_(self.weight, a=5 ** 0.5)
 
-    def forward(self, x):
-        if x.is_cuda and self.dtype != torch.float32:
-            y = F.linear(x.to(self.dtype), self.weight.to(self.dtype), self.bias.to(self.dtype))
-        else:
-            y = F.linear(x.float(), self.weight, self.bias)
+    def forward(self, x, keep_pad: bool = False):
+        if x.is_cuda and self.dtype == torch.bfloat16:
+            Kp = _pad8(self.in_features)
+            if x.dtype != torch.bfloat16:
+                x = x.to(torch.bfloat16)
+            if x.shape[1] != Kp:
+                x = F.pad(x, (0, Kp - x.shape[1]))
+            y = _LinearFn.apply(x.contiguous(), self.weight, self.bias, self.act)
+            return y if keep_pad or y.shape[1] == self.out_features else y[:, :self.out_features]
+        y = F.linear(x.float()[:, :self.in_features], self.weight, self.bias)
         return F.relu(y) if self.act else y
 
 
 class MLP(nn.Module):
     def __init__(self, dims: Sequence[int], final_act: bool = False, dtype=torch.bfloat16):
         super().__init__()
-        layers = []
-        for i in range(len(dims) - 1):
-            layers.append(Linear(dims[i], dims[i + 1], act=(i < len(dims) - 2) or final_act, dtype=dtype))
-        self.layers = nn.ModuleList(layers)
+        self.layers = nn.ModuleList(
+            [Linear(dims[i], dims[i + 1], act=(i < len(dims) - 2) or final_act, dtype=dtype) for i in range(len(dims) - 1)])
 
     def forward(self, x):
-        for layer in self.layers:
-            x = layer(x)
+        n = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            x = layer(x, keep_pad=i < n - 1)
         return x
 
 
+class _DotInteractionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cube):
+        C = native()
+        B, Fn, D = cube.shape
+        out = C.dot_interaction_fwd(x, cube, _pad8(D + (Fn + 1) * Fn // 2))
+        ctx.save_for_backward(x, cube)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, cube = ctx.saved_tensors
+        dx, dcube = native().dot_interaction_bwd(x, cube, dout.contiguous())
+        return dx.to(x.dtype), dcube
+
+
 def dot_interaction(x: torch.Tensor, cube: torch.Tensor) -> torch.Tensor:
-    """[B, D] dense vector + [B, F, D] embeddings -> [B, D + (F+1)F/2]: x and the strict lower triangle of Z Z^T."""
+    """``x`` [B, D] + embeddings ``cube`` [B, F, D] -> [B, D + (F+1)F/2 (+ zero pad to a multiple of 8 on CUDA)]:
+    ``x`` followed by the strict lower triangle (row-major) of ``Z Z^T`` with ``Z = [x; cube]``."""
     B, Fn, D = cube.shape
+    if x.is_cuda and x.dtype == torch.bfloat16 and cube.dtype == torch.float32:
+        return _DotInteractionFn.apply(x.contiguous(), cube.contiguous())
     z = torch.cat([x.unsqueeze(1), cube.to(x.dtype)], dim=1)
     zz = torch.bmm(z, z.transpose(1, 2))
     li, lj = torch.tril_indices(Fn + 1, Fn + 1, offset=-1, device=x.device)
     return torch.cat([x, zz[:, li, lj]], dim=1)
 
 
+class _FMFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, cube):
+        ctx.save_for_backward(cube)
+        return native().fm_fwd(cube)
+
+    @staticmethod
+    def backward(ctx, gout):
+        (cube,) = ctx.saved_tensors
+        return native().fm_bwd(cube, gout)
+
+
 def fm_interaction(cube: torch.Tensor) -> torch.Tensor:
-    """Second-order FM term: 0.5 * sum_d ((sum_f v)^2 - sum_f v^2) -> [B, 1]."""
+    """Second-order FM term ``0.5 * sum_d ((sum_f v)^2 - sum_f v^2)`` -> [B, 1]."""
+    if cube.is_cuda and cube.dtype == torch.float32:
+        return _FMFn.apply(cube.contiguous())
     s = cube.sum(dim=1)
     return 0.5 * (s * s - (cube * cube).sum(dim=1)).sum(dim=1, keepdim=True)

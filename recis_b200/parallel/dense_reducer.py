@@ -43,7 +43,7 @@ class DenseGradReducer:
             self.status = torch.zeros(1, dtype=torch.int64, device=dev)
             self.stream = torch.cuda.Stream(device=dev)
             self.rank = dist.get_rank(pg)
-            self.spin_limit = int(os.environ.get("RECIS_WAIT_SPINS", str(4_000_000)))
+            self.spin_limit = int(float(os.environ.get("RECIS_WAIT_TIMEOUT_S", "20")) * 1e6)  # microseconds
         else:
             self.flat = torch.zeros(n, dtype=torch.float32, device=dev)
         off = 0

@@ -47,8 +47,8 @@ class FusedExchange:
         self.heap = None
         self.epoch = 0
         self.send_cap = int(os.environ.get("RECIS_EXCHANGE_CAPACITY", "0")) or int(getattr(emb_opt, "exchange_capacity", 0) or 0)
-        # ~1 s at the polling cadence of comm_wait_kernel; a dead peer then surfaces as an error, never as a hang
-        self.spin_limit = int(os.environ.get("RECIS_WAIT_SPINS", str(4_000_000)))
+        # time budget of every flag wait; a dead peer then surfaces as an error, never as a hang
+        self.spin_limit = int(float(os.environ.get("RECIS_WAIT_TIMEOUT_S", "20")) * 1e6)  # microseconds
         self.status = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.immediate_reduce = False
         self._head = None
