@@ -33,9 +33,13 @@ Tensor gemm_bf16(const Tensor& a, const Tensor& b, OptT bias, bool relu, bool a_
     out = *accumulate_into;
     TORCH_CHECK(out_fp32 && out.scalar_type() == torch::kFloat32 && out.is_contiguous() && out.size(0) == MM && out.size(1) == NN);
     beta = out.data_ptr<float>();
-  } else {
-    out = torch::empty({MM, NN}, a.options().dtype(out_fp32 ? torch::kFloat32 : torch::kBFloat16));
   }
+  int splits = 1;
+  if (out_fp32 && !relu && !(bias.has_value() && bias->defined())) splits = rb_gemm_splits((int)MM, (int)NN, (int)KK);
+  if (!out.defined())
+    out = splits > 1 ? torch::zeros({MM, NN}, a.options().dtype(torch::kFloat32))
+                     : torch::empty({MM, NN}, a.options().dtype(out_fp32 ? torch::kFloat32 : torch::kBFloat16));
+  if (splits > 1) beta = nullptr;   // accumulate_into + split-K: the reductions land directly on the existing values
   const float* bp = nullptr;
   Tensor bias_f;
   if (bias.has_value() && bias->defined()) {
@@ -45,7 +49,7 @@ Tensor gemm_bf16(const Tensor& a, const Tensor& b, OptT bias, bool relu, bool a_
   }
   Tensor& st = status_word(a.device());
   const int rc = rb_gemm_bf16(a.data_ptr(), a.stride(0), a_mn, b.data_ptr(), b.stride(0), b_mn, out.data_ptr(), out.stride(0), out_fp32, bp,
-                              beta, (int)MM, (int)NN, (int)KK, relu, st.data_ptr<int64_t>(), at::cuda::getCurrentCUDAStream());
+                              beta, (int)MM, (int)NN, (int)KK, relu, splits, st.data_ptr<int64_t>(), at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(rc == 0, "rb_gemm_bf16 failed with code ", rc,
               " (1: operand base/pitch not 16-byte aligned, 2: tensor map encode failed, >2: launch error)");
   return out;

@@ -21,6 +21,7 @@
 #include "rb_dense.h"
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <algorithm>
 #include <mutex>
 
 namespace {
@@ -29,7 +30,7 @@ constexpr int BM = 128;       // rows of D per CTA (= UMMA M, = TMEM lanes)
 constexpr int BN = 128;       // columns of D per CTA (= UMMA N, = TMEM fp32 columns)
 constexpr int BK = 64;        // reduction elements per stage (64 bf16 = one 128-byte swizzle row)
 constexpr int UK = 16;        // reduction elements per tcgen05.mma (bf16)
-constexpr int kStages = 4;
+constexpr int kStages = 3;     // 3 x 32 KB: two CTAs fit on one SM, so one CTA's epilogue overlaps the other's main loop
 constexpr int kThreads = 192;
 constexpr uint32_t kTileBytes = BM * BK * 2;                    // 16 KB per operand per stage
 constexpr uint32_t kStageBytes = 2 * kTileBytes;
@@ -121,6 +122,7 @@ template <> struct Store<__nv_bfloat16> {
       for (int j = 0; j < valid; ++j) dst[j] = __float2bfloat16_rn(v[j]);
     }
   }
+  static __device__ __forceinline__ void red32(__nv_bfloat16*, const float (&)[32], int, bool) {}   // split-K needs fp32 output
 };
 template <> struct Store<float> {
   static __device__ __forceinline__ void row32(float* dst, const float (&v)[32], int valid, bool vec_ok) {
@@ -132,10 +134,18 @@ template <> struct Store<float> {
       for (int j = 0; j < valid; ++j) dst[j] = v[j];
     }
   }
+  static __device__ __forceinline__ void red32(float* dst, const float (&v)[32], int valid, bool vec_ok) {
+    if (vec_ok && valid == 32) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) atomicAdd(reinterpret_cast<float4*>(dst) + q, make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
+    } else {
+      for (int j = 0; j < valid; ++j) atomicAdd(dst + j, v[j]);
+    }
+  }
 };
 
 template <bool A_MN, bool B_MN, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          OutT* __restrict__ out, const float* __restrict__ bias, const float* __restrict__ beta_src,
                          int MM, int NN, int KK, int ldo, int relu, int64_t* __restrict__ status) {
@@ -149,7 +159,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const int num_kb = (KK + BK - 1) / BK;
+  // split-K: blockIdx.z owns a contiguous range of reduction blocks and accumulates its partial tile with fp32 reductions
+  const int total_kb = (KK + BK - 1) / BK;
+  const int kb_per = (total_kb + (int)gridDim.z - 1) / (int)gridDim.z;
+  const int kb_begin = (int)blockIdx.z * kb_per;
+  const int num_kb = max(0, min(total_kb, kb_begin + kb_per) - kb_begin);
+  const bool split = gridDim.z > 1;
+  if (split && num_kb == 0) return;           // uniform for the whole CTA, before any barrier or allocation
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -180,7 +196,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       uint8_t* sa = smem + s * kStageBytes;
       uint8_t* sb = sa + kTileBytes;
       mbar_expect_tx(&full_bar[s], kStageBytes);
-      const int k0 = kb * BK;
+      const int k0 = (kb_begin + kb) * BK;
       if (!A_MN) tma_load_2d(sa, &map_a, k0, m0, &full_bar[s]);                      // box {BK, BM}
       else { tma_load_2d(sa, &map_a, m0, k0, &full_bar[s]); tma_load_2d(sa + kTileBytes / 2, &map_a, m0 + 64, k0, &full_bar[s]); }  // 2 x box {64, BK}
       if (!B_MN) tma_load_2d(sb, &map_b, k0, n0, &full_bar[s]);
@@ -244,13 +260,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             float x = __uint_as_float(r[j]);
-            if (j < valid) {
+            if (j < valid && (!split || blockIdx.z == 0)) {
               if (bias) x += bias[n0 + c0 + j];
               if (beta_src) x += beta_src[(int64_t)row * ldo + n0 + c0 + j];
             }
             v[j] = relu ? fmaxf(x, 0.f) : x;
           }
-          Store<OutT>::row32(out + (int64_t)row * ldo + n0 + c0, v, valid, vec_ok);
+          if (split) Store<OutT>::red32(out + (int64_t)row * ldo + n0 + c0, v, valid, vec_ok);
+          else Store<OutT>::row32(out + (int64_t)row * ldo + n0 + c0, v, valid, vec_ok);
         }
       }
     }
@@ -295,14 +312,14 @@ bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, in
 
 template <bool A_MN, bool B_MN, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const float* bias, const float* beta_src, int MM, int NN, int KK,
-           int ldo, int relu, int64_t* status, cudaStream_t st) {
+           int ldo, int relu, int splits, int64_t* status, cudaStream_t st) {
   auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess) return 3;
     attr_set = true;
   }
-  dim3 grid((NN + BN - 1) / BN, (MM + BM - 1) / BM);
+  dim3 grid((NN + BN - 1) / BN, (MM + BM - 1) / BM, splits);
   kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, reinterpret_cast<OutT*>(out), bias, beta_src, MM, NN, KK, ldo, relu, status);
   rb::note_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
@@ -310,9 +327,18 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const float*
 
 }  // namespace
 
+extern "C" int rb_gemm_splits(int MM, int NN, int KK) {
+  // few output tiles and a long reduction (weight gradients): spread the reduction over about two waves of CTAs
+  const int tiles = ((NN + BN - 1) / BN) * ((MM + BM - 1) / BM);
+  const int total_kb = (KK + BK - 1) / BK;
+  int splits = (2 * 148 + tiles - 1) / tiles;
+  splits = std::min(splits, total_kb / 4);
+  return std::max(splits, 1);
+}
+
 extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo,
-                            int out_fp32, const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int64_t* status,
-                            cudaStream_t st) {
+                            int out_fp32, const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int splits,
+                            int64_t* status, cudaStream_t st) {
   if (MM <= 0 || NN <= 0) return 0;
   // TMA constraints: 16-byte aligned base, row pitch a multiple of 16 bytes
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (lda % 8) || (ldb % 8)) return 1;
@@ -320,10 +346,11 @@ extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b,
   const bool oka = a_mn ? make_map(&ma, a, KK, MM, lda, 64, BK) : make_map(&ma, a, MM, KK, lda, BK, BM);
   const bool okb = b_mn ? make_map(&mb, b, KK, NN, ldb, 64, BK) : make_map(&mb, b, NN, KK, ldb, BK, BN);
   if (!oka || !okb) return 2;
+  if (splits > 1 && (!out_fp32 || relu)) return 6;   // partial tiles are accumulated with fp32 reductions into a zeroed output
 #define RB_GEMM_CASE(AM, BMJ)                                                                                                   \
   if ((a_mn != 0) == AM && (b_mn != 0) == BMJ)                                                                                  \
-    return out_fp32 ? launch<AM, BMJ, float>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st)               \
-                    : launch<AM, BMJ, __nv_bfloat16>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st);
+    return out_fp32 ? launch<AM, BMJ, float>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, splits, status, st)               \
+                    : launch<AM, BMJ, __nv_bfloat16>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, 1, status, st);
   RB_GEMM_CASE(false, false)
   RB_GEMM_CASE(false, true)
   RB_GEMM_CASE(true, false)

@@ -11,8 +11,12 @@ extern "C" {
 // (b_mn = 0) or [KK][NN] (b_mn = 1); bf16 operands, fp32 accumulation, bf16 or fp32 output with row pitch ldo.
 // beta_src (nullable, fp32, same layout as the output) is added before the activation (gradient accumulation).
 // Returns 0 on success; 1 = operand alignment unsuitable for TMA, 2 = tensor-map encode failed, >2 = launch error.
+// splits > 1 (fp32 output without activation only): the reduction is split over gridDim.z CTAs that accumulate into `out`
+// with fp32 reductions; `out` must then be zero (or hold the value to accumulate onto) on entry.
 int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo, int out_fp32,
-                 const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int64_t* status, cudaStream_t st);
+                 const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int splits, int64_t* status,
+                 cudaStream_t st);
+int rb_gemm_splits(int MM, int NN, int KK);   // heuristic split count for a weight-gradient shaped problem
 
 #ifdef __cplusplus
 }

@@ -18,6 +18,9 @@
 #include "rb_comm.h"
 #include "../common/rb_launch.h"
 #include <cub/device/device_radix_sort.cuh>
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 using namespace rb;
 
@@ -316,6 +319,33 @@ __device__ __forceinline__ void opt_update_f4(const RbOpt& o, int64_t off, float
   st_f4(o.w + off, w);
 }
 
+// Same update with the row's state already in registers (requested when the row's segment started).
+__device__ __forceinline__ void opt_update_pre_f4(const RbOpt& o, int64_t off, float4 g, float4 w, float4 m, float4 v) {
+  const float gs = o.grad_scale;
+  g.x *= gs; g.y *= gs; g.z *= gs; g.w *= gs;
+  if (o.kind == RB_OPT_ADAM) {
+    const float b1 = o.beta1, b2 = o.beta2, c1 = 1.f - o.beta1, c2 = 1.f - o.beta2;
+    m.x = b1 * m.x + c1 * g.x; m.y = b1 * m.y + c1 * g.y; m.z = b1 * m.z + c1 * g.z; m.w = b1 * m.w + c1 * g.w;
+    v.x = b2 * v.x + c2 * g.x * g.x; v.y = b2 * v.y + c2 * g.y * g.y; v.z = b2 * v.z + c2 * g.z * g.z; v.w = b2 * v.w + c2 * g.w * g.w;
+    w.x = w.x * o.decay + o.alpha * m.x / (sqrtf(v.x) + o.eps);
+    w.y = w.y * o.decay + o.alpha * m.y / (sqrtf(v.y) + o.eps);
+    w.z = w.z * o.decay + o.alpha * m.z / (sqrtf(v.z) + o.eps);
+    w.w = w.w * o.decay + o.alpha * m.w / (sqrtf(v.w) + o.eps);
+    st_f4(o.s1 + off, m); st_f4(o.s2 + off, v);
+  } else if (o.kind == RB_OPT_ADAGRAD) {
+    m.x += g.x * g.x; m.y += g.y * g.y; m.z += g.z * g.z; m.w += g.w * g.w;
+    w.x = w.x * o.decay - o.lr * g.x / (sqrtf(m.x) + o.eps);
+    w.y = w.y * o.decay - o.lr * g.y / (sqrtf(m.y) + o.eps);
+    w.z = w.z * o.decay - o.lr * g.z / (sqrtf(m.z) + o.eps);
+    w.w = w.w * o.decay - o.lr * g.w / (sqrtf(m.w) + o.eps);
+    st_f4(o.s1 + off, m);
+  } else {
+    w.x = w.x * o.decay - o.lr * g.x; w.y = w.y * o.decay - o.lr * g.y;
+    w.z = w.z * o.decay - o.lr * g.z; w.w = w.w * o.decay - o.lr * g.w;
+  }
+  st_f4(o.w + off, w);
+}
+
 __device__ __forceinline__ void opt_update_f1(const RbOpt& o, int64_t off, float g) {
   g *= o.grad_scale;
   float w = o.w[off];
@@ -342,68 +372,89 @@ grad_reduce_kernel(const float* __restrict__ grad_out, const int32_t* __restrict
                    const int32_t* __restrict__ csr_u, const int32_t* __restrict__ csr_elem, const int32_t* __restrict__ start,
                    int64_t n, int D, float* __restrict__ span_acc, const int32_t* __restrict__ rows, float* __restrict__ gu,
                    int apply, RbOpt opt) {
+  // Phase 1 (per chunk): the lanes of the group fetch the metadata of all positions of the chunk in parallel (one
+  // dependent chain for the whole chunk instead of one per position) and park it in shared memory.
+  // Phase 2: walk the segments of the chunk; the optimizer state of a row is requested when its segment starts, so
+  // those loads are in flight together with the gradient gathers of the segment.
+  __shared__ int32_t meta[(kThreads / G) * kChunk * 5];
+  auto tile = cg::tiled_partition<G>(cg::this_thread_block());
   const int lane = threadIdx.x % G;
+  const int gid = threadIdx.x / G;
+  int32_t* m_u = meta + gid * kChunk * 5;
+  int32_t* m_gs = m_u + kChunk;
+  int32_t* m_row = m_u + 2 * kChunk;      // >= 0 row to update / unique index to store, -1 skip, -2 segment crosses the chunk
+  int32_t* m_dst = m_u + 3 * kChunk;      // chunk that owns a crossing segment
+  float* m_sc = reinterpret_cast<float*>(m_u + 4 * kChunk);
   const int cols = D >> 2;
   const int64_t n_chunks = (n + kChunk - 1) / kChunk;
   const int64_t n_groups = (int64_t)gridDim.x * (kThreads / G);
-  for (int64_t c = blockIdx.x * (int64_t)(kThreads / G) + threadIdx.x / G; c < n_chunks; c += n_groups) {
+  for (int64_t c = blockIdx.x * (int64_t)(kThreads / G) + gid; c < n_chunks; c += n_groups) {
     const int64_t p0 = c * kChunk, p1 = min(p0 + (int64_t)kChunk, n);
-    float4 acc[NACC];
-#pragma unroll
-    for (int a = 0; a < NACC; ++a) acc[a] = make_float4(0.f, 0.f, 0.f, 0.f);
-    int32_t cur_u = csr_u[p0];
-    auto flush = [&](int32_t u) {
+    const int cnt = (int)(p1 - p0);
+    for (int j = lane; j < cnt; j += G) {
+      const int32_t u = csr_u[p0 + j];
+      const int32_t e = csr_elem[p0 + j];
       const int32_t s0 = start[u], s1 = start[u + 1];
-      if (s0 >= p0 && s1 <= p1) {
-        const int32_t row = rows ? rows[u] : u;
+      const bool complete = s0 >= p0 && s1 <= p1;
+      m_u[j] = u;
+      m_gs[j] = gsrc[e];
+      m_sc[j] = gscale[e];
+      m_row[j] = complete ? (apply ? (rows ? rows[u] : u) : u) : -2;
+      m_dst[j] = s0 / kChunk;
+    }
+    tile.sync();
+    int j = 0;
+    while (j < cnt) {
+      const int32_t u = m_u[j];
+      const int32_t row = m_row[j];
+      int jend = j + 1;
+      while (jend < cnt && m_u[jend] == u) ++jend;
+      float4 sw[NACC], s1v[NACC], s2v[NACC];
+      const bool upd = apply && row >= 0;
+      if (upd) {
 #pragma unroll
         for (int a = 0; a < NACC; ++a) {
           const int col = lane + a * G;
           if (col < cols) {
-            if (apply) { if (row >= 0) opt_update_f4(opt, (int64_t)row * D + col * 4, acc[a]); }
-            else st_f4(gu + (int64_t)u * D + col * 4, acc[a]);
+            const int64_t off = (int64_t)row * D + col * 4;
+            sw[a] = ld_f4(opt.w + off);
+            if (opt.kind != RB_OPT_SGD) s1v[a] = ld_f4(opt.s1 + off);
+            if (opt.kind == RB_OPT_ADAM) s2v[a] = ld_f4(opt.s2 + off);
           }
         }
-      } else {
-        float* dst = span_acc + (int64_t)(s0 / kChunk) * D;
-#pragma unroll
-        for (int a = 0; a < NACC; ++a) {
-          const int col = lane + a * G;
-          if (col < cols) red_add_f4(dst + col * 4, acc[a]);
-        }
       }
+      float4 acc[NACC];
 #pragma unroll
       for (int a = 0; a < NACC; ++a) acc[a] = make_float4(0.f, 0.f, 0.f, 0.f);
-    };
-    for (int64_t p = p0; p < p1; p += 4) {
-      int32_t u[4], gs[4]; float sc[4];
+      for (int k = j; k < jend; k += 4) {
+        float4 v[4][NACC];
+        float sc[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        u[j] = -1; gs[j] = -1; sc[j] = 0.f;
-        if (p + j < p1) {
-          u[j] = csr_u[p + j];
-          const int32_t e = csr_elem[p + j];
-          gs[j] = gsrc[e]; sc[j] = gscale[e];
+        for (int t = 0; t < 4; ++t) {
+          const int32_t gs = (k + t < jend) ? m_gs[k + t] : -1;
+          sc[t] = (k + t < jend) ? m_sc[k + t] : 0.f;
+#pragma unroll
+          for (int a = 0; a < NACC; ++a) {
+            const int col = lane + a * G;
+            v[t][a] = (gs >= 0 && col < cols) ? ld_f4(grad_out + (int64_t)gs * D + col * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
         }
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+          for (int a = 0; a < NACC; ++a) acc[a] = f4_fma(sc[t], v[t][a], acc[a]);
       }
-      float4 v[4][NACC];
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int a = 0; a < NACC; ++a) {
-          const int col = lane + a * G;
-          v[j][a] = (gs[j] >= 0 && col < cols) ? ld_f4(grad_out + (int64_t)gs[j] * D + col * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (p + j < p1) {
-          if (u[j] != cur_u) { flush(cur_u); cur_u = u[j]; }
-#pragma unroll
-          for (int a = 0; a < NACC; ++a) acc[a] = f4_fma(sc[j], v[j][a], acc[a]);
-        }
+      for (int a = 0; a < NACC; ++a) {
+        const int col = lane + a * G;
+        if (col >= cols) continue;
+        if (row == -2) red_add_f4(span_acc + (int64_t)m_dst[j] * D + col * 4, acc[a]);
+        else if (upd) opt_update_pre_f4(opt, (int64_t)row * D + col * 4, acc[a], sw[a], s1v[a], s2v[a]);
+        else if (!apply) st_f4(gu + (int64_t)row * D + col * 4, acc[a]);
       }
+      j = jend;
     }
-    flush(cur_u);
+    tile.sync();
   }
 }
 
@@ -481,9 +532,8 @@ template <typename F>
 inline bool dispatch_cols(int D, F&& f) {
   if ((D & 3) != 0 || D > 512) return false;
   const int cols = D >> 2;
-  if (cols <= 1) f(std::integral_constant<int, 1>{}, std::integral_constant<int, 1>{});
-  else if (cols <= 2) f(std::integral_constant<int, 2>{}, std::integral_constant<int, 1>{});
-  else if (cols <= 4) f(std::integral_constant<int, 4>{}, std::integral_constant<int, 1>{});
+  // narrow rows share the 4-lane variant (lanes beyond the row width idle): keeps per-group shared-memory staging small
+  if (cols <= 4) f(std::integral_constant<int, 4>{}, std::integral_constant<int, 1>{});
   else if (cols <= 8) f(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
   else if (cols <= 16) f(std::integral_constant<int, 16>{}, std::integral_constant<int, 1>{});
   else if (cols <= 32) f(std::integral_constant<int, 32>{}, std::integral_constant<int, 1>{});

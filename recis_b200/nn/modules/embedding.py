@@ -109,7 +109,8 @@ class _LookupPoolFn(torch.autograd.Function):
     """ids/offsets/weights -> pooled embeddings; backward stages gradients on the owner table(s)."""
 
     @staticmethod
-    def forward(ctx, holder, emb_mod: "DynamicEmbedding", ids, offsets, weights, combiner, tile_len, perm, training, admit_hook):
+    def forward(ctx, holder, emb_mod: "DynamicEmbedding", ids, offsets, weights, combiner, tile_len, perm, training, admit_hook,
+                lane="default"):
         C = native()
         impl = emb_mod.impl
         store = impl.store
@@ -141,7 +142,7 @@ class _LookupPoolFn(torch.autograd.Function):
             return out
 
         if emb_mod.fused is not None:
-            out, saved = emb_mod.fused.forward(emb_mod, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train,
+            out, saved = emb_mod.fused.forward(emb_mod, lane, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train,
                                                readonly, threshold, step)
             ctx.saved = saved
             ctx.path = "fused"
@@ -174,7 +175,7 @@ class _LookupPoolFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         if not ctx.train:
-            return (None,) * 10
+            return (None,) * 11
         C = native()
         emb_mod = ctx.emb_mod
         impl = emb_mod.impl
@@ -185,10 +186,10 @@ class _LookupPoolFn(torch.autograd.Function):
         if ctx.path == "local":
             impl.stage_fused(dict(grad_out=grad_out, gsrc=s["gsrc"], gscale=s["gscale"], rev=s["rev"], rows=s["rows"],
                                   scale=worker_scale))
-            return (None,) * 10
+            return (None,) * 11
         if ctx.path == "fused":
             emb_mod.fused.backward(emb_mod, s, grad_out, worker_scale)
-            return (None,) * 10
+            return (None,) * 11
         # ---- collective path (the reference's C4 + owner-side duplicate reduction)
         csr_u, csr_elem, start = C.build_csr(s["rev"])
         gu = C.grad_reduce(grad_out, s["gsrc"], s["gscale"], csr_u, csr_elem, start, D, None, False, 2, 0.0, 0.0, 0.0, 0.0,
@@ -207,7 +208,7 @@ class _LookupPoolFn(torch.autograd.Function):
             else:
                 g_own = g_own * worker_scale
         impl.accept_grad(o_rows, g_own)
-        return (None,) * 10
+        return (None,) * 11
 
 
 class DynamicEmbedding(torch.nn.Module):
@@ -252,7 +253,7 @@ class DynamicEmbedding(torch.nn.Module):
         return self.table.impl
 
     def lookup_pool(self, ids: torch.Tensor, offsets: torch.Tensor, weights: Optional[torch.Tensor], combiner: str,
-                    tile_len: int = 0, perm=None, admit_hook=None) -> torch.Tensor:
+                    tile_len: int = 0, perm=None, admit_hook=None, lane: str = "default") -> torch.Tensor:
         """Flat ids + int32 segment offsets (+ per-id weights) -> pooled rows ``[segments, D]`` (tile: ``[segments, T*D]``)."""
         dev = self.impl.device
         ids = ids.detach().reshape(-1).to(dev).contiguous()
@@ -260,7 +261,7 @@ class DynamicEmbedding(torch.nn.Module):
         if weights is not None:
             weights = weights.detach().reshape(-1).to(device=dev, dtype=torch.float32).contiguous()
         return _LookupPoolFn.apply(self._holder, self, ids, offsets, weights, combiner, int(tile_len), perm, self.training,
-                                   admit_hook if admit_hook is not None else self._emb_opt.admit_hook)
+                                   admit_hook if admit_hook is not None else self._emb_opt.admit_hook, lane)
 
     def deal_with_tensor(self, input_tensor):
         if isinstance(input_tensor, RaggedTensor):

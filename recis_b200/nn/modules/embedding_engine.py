@@ -192,7 +192,7 @@ class EmbeddingEngine(nn.Module):
                 if self._interleave and opt.combiner != "tile" and len(set(segs)) == 1 and len(feats) > 1:
                     perm = (segs[0], len(feats))
                 ht.option.mean_by_weight = opt.mean_by_weight
-                pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, tile_len, perm, opt.admit_hook)
+                pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, tile_len, perm, opt.admit_hook, lane=run_key)
                 if not opt.trainable:
                     pooled = pooled.detach()
                 D = opt.embedding_dim

@@ -14,7 +14,10 @@ optimizer owner      wait GRAD; ONE kernel pulls every contribution of a touched
                      loads), adds duplicates across requesters and applies the row-wise optimizer update
 
 No split size ever reaches the host; windows are sized for the worst case (``exchange_capacity`` unique ids per rank).
-All flag waits are bounded; a timeout or a window overflow sets a bit in ``status`` which ``check()`` turns into an exception.
+Every (table, runtime group) pair owns one *lane*: its own windows, flag pad and epoch counter, so that the epochs written
+to a flag only ever grow and a gradient window is never rewritten before its owner consumed it.
+All flag waits are time-bounded; a timeout or a window overflow sets a bit in ``status`` which ``check()`` turns into an
+exception.
 """
 from __future__ import annotations
 
@@ -26,8 +29,34 @@ import torch.distributed as dist
 from .. import native
 from .symmetric import SymmetricHeap
 
-CH_IDS, CH_EMB, CH_GRAD, CH_AR0, CH_AR1, N_CH = 0, 1, 2, 3, 4, 8
+CH_IDS, CH_EMB, CH_GRAD, N_CH = 0, 1, 2, 8
 STATUS_TIMEOUT, STATUS_OVERFLOW = 4, 8
+
+
+class _Lane:
+    """Windows + flags of one (table, runtime group) pair."""
+
+    def __init__(self, ex: "FusedExchange", nnz: int):
+        cap = ex.send_cap
+        if not cap:
+            t = torch.tensor([nnz], dtype=torch.int64, device=ex.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ex.pg)
+            cap = max(int(t.item()) * 2, 1024)
+        W, D = ex.world, ex.D
+        self.send_cap = cap
+        self.in_cap = min(W, 2) * cap
+        self.heap = SymmetricHeap({
+            "flags": (torch.int64, N_CH * W),
+            "offsets": (torch.int32, W + 1),
+            "ids": (torch.int64, cap),
+            "uemb": (torch.float32, cap * D),
+            "gu": (torch.float32, cap * D),
+        }, ex.device, ex.pg)
+        self.ids_in = torch.empty(self.in_cap, dtype=torch.int64, device=ex.device)
+        self.prefix = torch.zeros(2 * W + 1, dtype=torch.int32, device=ex.device)
+        self.n_in = torch.zeros(1, dtype=torch.int32, device=ex.device)
+        self.epoch = 0
+        self.pending_grad_epoch = 0      # a staged, not yet consumed gradient window
 
 
 class FusedExchange:
@@ -44,11 +73,10 @@ class FusedExchange:
         self.pg, self.world, self.rank = pg, world, rank
         self.device = torch.device(emb_opt.device)
         self.D = emb_opt.embedding_dim
-        self.heap = None
-        self.epoch = 0
+        self.lanes = {}
         self.send_cap = int(os.environ.get("RECIS_EXCHANGE_CAPACITY", "0")) or int(getattr(emb_opt, "exchange_capacity", 0) or 0)
         # time budget of every flag wait; a dead peer then surfaces as an error, never as a hang
-        self.spin_limit = int(float(os.environ.get("RECIS_WAIT_TIMEOUT_S", "20")) * 1e6)  # microseconds
+        self.wait_us = int(float(os.environ.get("RECIS_WAIT_TIMEOUT_S", "20")) * 1e6)
         self.status = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.immediate_reduce = False
         self._head = None
@@ -58,25 +86,6 @@ class FusedExchange:
 
     def attach(self, emb_mod):
         self.emb_mod = emb_mod
-
-    # ------------------------------------------------------------------ setup (collective, at the first forward)
-    def _setup(self, nnz: int):
-        if not self.send_cap:
-            t = torch.tensor([nnz], dtype=torch.int64, device=self.device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.pg)
-            self.send_cap = max(int(t.item()) * 2, 1024)
-        W, D, cap = self.world, self.D, self.send_cap
-        self.in_cap = min(W, 2) * cap
-        self.heap = SymmetricHeap({
-            "flags": (torch.int64, N_CH * W),
-            "offsets": (torch.int32, W + 1),
-            "ids": (torch.int64, cap),
-            "uemb": (torch.float32, cap * D),
-            "gu": (torch.float32, cap * D),
-        }, self.device, self.pg)
-        self.ids_in = torch.empty(self.in_cap, dtype=torch.int64, device=self.device)
-        self.prefix = torch.zeros(2 * W + 1, dtype=torch.int32, device=self.device)
-        self.n_in = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def check(self):
         """Raise if a bounded wait timed out or a window overflowed (one host read; call at step boundaries / in tests)."""
@@ -93,63 +102,84 @@ class FusedExchange:
         return self._head
 
     # ------------------------------------------------------------------ forward
-    def forward(self, emb_mod, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold, step):
+    def forward(self, emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold,
+                step):
         C = native()
         n = ids.numel()
-        if self.heap is None:
-            self._setup(n)
-        if n > self.send_cap:
-            raise RuntimeError(f"batch has {n} ids but the exchange window holds {self.send_cap}; set exchange_capacity "
+        lane = self.lanes.get(lane_key)
+        if lane is None:                       # collective: every rank meets here at its first forward of this lane
+            lane = self.lanes[lane_key] = _Lane(self, n)
+        if n > lane.send_cap:
+            raise RuntimeError(f"batch has {n} ids but the exchange window holds {lane.send_cap}; set exchange_capacity "
                                f"(EmbeddingOption) or RECIS_EXCHANGE_CAPACITY to the largest per-rank id count")
-        h, W, me, D = self.heap, self.world, self.rank, self.D
-        self.epoch += 1
-        e = self.epoch
+        if lane.pending_grad_epoch and not self.immediate_reduce:
+            # the previous backward of this lane is still staged (gradient accumulation without set_grad_accum_steps):
+            # consume it now, before this step's backward rewrites the gradient window
+            self._flush_pending(emb_mod.impl, lane)
+        h, W, me, D = lane.heap, self.world, self.rank, self.D
+        lane.epoch += 1
+        e = lane.epoch
         store = emb_mod.impl.store
         _uniq, rev, _counts, _offs = C.dedup_partition(ids, W, h["ids"].tensor, h["offsets"].tensor)
         C.comm_signal(h["flags"].ptrs, CH_IDS, me, e)
-        C.comm_wait(h["flags"].tensor, CH_IDS, W, e, self.spin_limit, self.status)
-        C.comm_pull_ids(h["ids"].ptrs, h["offsets"].ptrs, me, self.ids_in, self.prefix, self.n_in, self.status)
+        C.comm_wait(h["flags"].tensor, CH_IDS, W, e, self.wait_us, self.status)
+        C.comm_pull_ids(h["ids"].ptrs, h["offsets"].ptrs, me, lane.ids_in, lane.prefix, lane.n_in, self.status)
         if readonly:
-            rows_in = store.find(self.ids_in, self.n_in)
+            rows_in = store.find(lane.ids_in, lane.n_in)
         else:
-            rows_in = store.lookup_or_insert(self.ids_in, self.n_in, step, threshold)
-        prefix = self.prefix.clone()
-        C.comm_push_emb(store.emb(), rows_in, prefix, h["uemb"].ptrs, me, self.in_cap)
+            rows_in = store.lookup_or_insert(lane.ids_in, lane.n_in, step, threshold)
+        prefix = lane.prefix.clone()
+        C.comm_push_emb(store.emb(), rows_in, prefix, h["uemb"].ptrs, me, lane.in_cap)
         C.comm_signal(h["flags"].ptrs, CH_EMB, me, e)
-        C.comm_wait(h["flags"].tensor, CH_EMB, W, e, self.spin_limit, self.status)
-        uemb = h["uemb"].tensor.view(self.send_cap, D)
+        C.comm_wait(h["flags"].tensor, CH_EMB, W, e, self.wait_us, self.status)
+        uemb = h["uemb"].tensor.view(lane.send_cap, D)
         if combiner == "tile":
             out, gsrc, gscale = C.tile_forward(uemb, None, rev, offsets, weights, tile_len, train)
         else:
             out, gsrc, gscale = C.pool_forward(uemb, None, rev, offsets, weights, mode, perm_b, perm_f, train)
-        saved = dict(rev=rev, gsrc=gsrc, gscale=gscale, rows_in=rows_in, prefix=prefix, epoch=e) if train else None
+        saved = dict(rev=rev, gsrc=gsrc, gscale=gscale, rows_in=rows_in, prefix=prefix, epoch=e, lane=lane) if train else None
         return out, saved
 
     # ------------------------------------------------------------------ backward (requester side) + staging
     def backward(self, emb_mod, s, grad_out, worker_scale):
         C = native()
-        h, me, D = self.heap, self.rank, self.D
+        lane = s["lane"]
+        h, me, D = lane.heap, self.rank, self.D
         csr_u, csr_elem, start = C.build_csr(s["rev"])
         C.grad_reduce(grad_out, s["gsrc"], s["gscale"], csr_u, csr_elem, start, D, None, False, 2, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0,
-                      1.0, None, None, None, self.send_cap, h["gu"].tensor.view(self.send_cap, D))
+                      1.0, None, None, None, lane.send_cap, h["gu"].tensor.view(lane.send_cap, D))
         C.comm_signal(h["flags"].ptrs, CH_GRAD, me, s["epoch"])
-        rec = dict(rows_in=s["rows_in"], prefix=s["prefix"], epoch=s["epoch"], scale=worker_scale, exchange=self,
+        rec = dict(rows_in=s["rows_in"], prefix=s["prefix"], epoch=s["epoch"], scale=worker_scale, exchange=self, lane=lane,
                    mean_by_id=emb_mod.option.grad_reduce_by == "id")
         if self.immediate_reduce:
             rows, grads = self.owner_reduce(emb_mod.impl, rec, apply=False)
             emb_mod.impl.accept_grad(rows, grads)
         else:
             rec["kind"] = "peer"
+            lane.pending_grad_epoch = s["epoch"]
             emb_mod.impl.records().append(rec)
+
+    def _flush_pending(self, impl, lane):
+        keep = []
+        for rec in impl.records():
+            if rec.get("kind") == "peer" and rec["lane"] is lane:
+                rows, grads = self.owner_reduce(impl, rec, apply=False)
+                keep.append({"kind": "rows", "rows": rows, "grad": grads})
+            else:
+                keep.append(rec)
+        impl.records()[:] = keep
 
     # ------------------------------------------------------------------ owner side: pull + reduce (+ update)
     def owner_reduce(self, impl, rec, apply, kind=2, lr=0.0, b1=0.0, b2=0.0, eps=0.0, decay=1.0, alpha=0.0, grad_scale=1.0,
                      w=None, s1=None, s2=None):
         C = native()
-        h = self.heap
-        C.comm_wait(h["flags"].tensor, CH_GRAD, self.world, rec["epoch"], self.spin_limit, self.status)
+        lane = rec["lane"]
+        h = lane.heap
+        C.comm_wait(h["flags"].tensor, CH_GRAD, self.world, rec["epoch"], self.wait_us, self.status)
         head = self._head_for(impl.store)
         rows, grads = C.comm_owner_reduce(rec["rows_in"], head, rec["prefix"], h["gu"].ptrs, self.rank, self.D, rec["mean_by_id"],
                                           apply, kind, lr, b1, b2, eps, decay, alpha, rec["scale"] * grad_scale, w, s1, s2,
-                                          self.in_cap)
+                                          lane.in_cap)
+        if lane.pending_grad_epoch == rec["epoch"]:
+            lane.pending_grad_epoch = 0
         return rows, grads

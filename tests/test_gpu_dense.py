@@ -50,25 +50,41 @@ def test_fm_interaction():
     assert torch.allclose(cg.grad.cpu(), cr.grad, atol=1e-4, rtol=1e-4)
 
 
+def _torch_bf16_mlp(mlp, x):
+    """The same network with plain PyTorch ops and the same rounding points (bf16 operands/activations, fp32 accumulation)."""
+    import torch.nn.functional as F
+    params = []
+    h = x.to(torch.bfloat16)
+    n = len(mlp.layers)
+    for i, layer in enumerate(mlp.layers):
+        w = layer.weight.detach().clone().requires_grad_(True)
+        b = layer.bias.detach().clone().requires_grad_(True)
+        params += [w, b]
+        h = (F.linear(h.float(), w.to(torch.bfloat16).float()) + b)
+        if layer.act:
+            h = torch.relu(h)
+        h = h.to(torch.bfloat16)
+    return h, params
+
+
 @pytest.mark.parametrize("dims", [(13, 512, 256, 128), (480, 1024, 1024, 512, 256, 1), (16, 8)])
-def test_mlp_matches_fp32(dims):
+def test_mlp_matches_reference(dims):
     torch.manual_seed(0)
     M = 1000
-    mlp = D.MLP(list(dims), final_act=False)
-    ref = D.MLP(list(dims), final_act=False, dtype=torch.float32)
-    ref.load_state_dict(mlp.state_dict())
-    mlp = mlp.to(DEV)
-    x = torch.randn(M, dims[0])
-    y = mlp(x.to(DEV)).float().cpu()
-    yr = ref(x)
+    mlp = D.MLP(list(dims), final_act=False).to(DEV)
+    x = torch.randn(M, dims[0], device=DEV)
+    y = mlp(x)
+    yr, ref_params = _torch_bf16_mlp(mlp, x)
+    rel = lambda a, b: float((a.float() - b.float()).norm() / b.float().norm().clamp(min=1e-12))
     assert y.shape == yr.shape
-    scale = max(float(yr.abs().max()), 1.0)
-    assert float((y - yr).abs().max()) / scale < 3e-2
-    go = torch.randn_like(yr)
-    (y_g := mlp(x.to(DEV))).backward(go.to(DEV).to(y_g.dtype))
+    assert rel(y, yr) < 1e-2
+    # and against a pure fp32 network (no bf16 anywhere): loose, it only guards against gross errors
+    ref32 = D.MLP(list(dims), final_act=False, dtype=torch.float32).to(DEV)
+    ref32.load_state_dict(mlp.state_dict())
+    assert rel(y, ref32(x)) < 5e-2
+    go = torch.randn(M, dims[-1], device=DEV).to(torch.bfloat16)
+    y.backward(go)
     yr.backward(go)
-    for (n1, p1), (n2, p2) in zip(mlp.named_parameters(), ref.named_parameters()):
-        g1, g2 = p1.grad.float().cpu(), p2.grad
-        denom = max(float(g2.abs().max()), 1e-3)
-        assert float((g1 - g2).abs().max()) / denom < 6e-2, (n1, float((g1 - g2).abs().max()), denom)
+    for (name, p), r in zip(mlp.named_parameters(), ref_params):
+        assert rel(p.grad, r.grad) < 3e-2, (name, rel(p.grad, r.grad))
     assert recis_b200.native().dense_status(DEV) == 0
