@@ -1,0 +1,53 @@
+"""Feature: a named chain of ops that starts with ``SelectField``/``SelectFields`` (``recis/features/feature.py:9-143``)."""
+from __future__ import annotations
+
+import hashlib
+from typing import List
+
+from torch import nn
+
+from .op import _OP, SelectField, SelectFields
+
+
+class Feature(nn.Module):
+    def __init__(self, name: str):
+        super().__init__()
+        self._name = name
+        self._compiled = False
+        self._ops = nn.ModuleList()
+
+    @property
+    def name(self):
+        return self._name
+
+    @property
+    def compiled(self):
+        return self._compiled
+
+    def compiled_(self, value: bool):
+        assert isinstance(value, bool)
+        self._compiled = value
+
+    @property
+    def ops(self) -> List[nn.Module]:
+        return self._ops
+
+    def add_op(self, op: _OP):
+        if self._compiled:
+            raise ValueError(f"feature {self.name} has been compiled")
+        if len(self._ops) == 0 and type(op) not in (SelectField, SelectFields):
+            raise ValueError(f"feature {self.name} must start with DataInputOP")
+        self._ops.append(op)
+        return self
+
+    def get_hash(self) -> int:
+        if len(self._ops) == 0:
+            return 0
+        combined = f"{self._name}:{sorted(op.get_hash() for op in self._ops)}"
+        return int.from_bytes(hashlib.sha256(combined.encode("utf-8")).digest()[:8], byteorder="big", signed=True)
+
+    def forward(self, data):
+        x = data
+        for op in self._ops:
+            x = op(x)
+        return x

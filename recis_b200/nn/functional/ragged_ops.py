@@ -1,71 +1,114 @@
-"""Ragged <-> dense / sparse conversions and ragged index utilities (filled in by ragged kernels)."""
+"""Ragged-tensor functional ops (API of the reference's ``recis/nn/functional/ragged_ops.py``), each backed by one native
+implementation that runs as sm_100a kernels on CUDA tensors and as C++ loops on CPU tensors."""
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
-
-def _row_lengths(offsets: torch.Tensor) -> torch.Tensor:
-    return offsets[1:] - offsets[:-1]
+from ... import native
 
 
 def ragged_to_dense(values: torch.Tensor, offsets: List[torch.Tensor], default_value=0.0) -> torch.Tensor:
-    """Pad a ragged tensor (any number of ragged dims) to a dense tensor."""
+    """Pad a ragged tensor (1..5 ragged dims, offsets outermost first) to a dense tensor."""
     if isinstance(offsets, torch.Tensor):
         offsets = [offsets]
-    dev = values.device
-    # flatten nested offsets from the innermost outwards
-    cur = values
-    for off in reversed(offsets):
-        off = off.to(torch.int64)
-        lens = _row_lengths(off)
-        n_rows = lens.numel()
-        max_len = int(lens.max().item()) if n_rows else 0
-        inner_shape = tuple(cur.shape[1:])
-        out = torch.full((n_rows, max_len) + inner_shape, default_value, dtype=cur.dtype, device=dev)
-        if cur.shape[0]:
-            row = torch.repeat_interleave(torch.arange(n_rows, device=dev), lens)
-            col = torch.arange(cur.shape[0], device=dev) - off[:-1][row]
-            out[row, col] = cur
-        cur = out
-    return cur
+    return native().ragged_to_dense(values, list(offsets), float(default_value))
 
 
 def dense_to_ragged(dense: torch.Tensor, check_invalid: bool = False, invalid_value=0):
-    """2-D dense -> (values, [offsets]); with ``check_invalid`` trailing ``invalid_value`` entries are stripped."""
-    assert dense.dim() == 2
-    B, L = dense.shape
-    if check_invalid:
-        valid = dense != invalid_value
-        idx = torch.arange(1, L + 1, device=dense.device).unsqueeze(0)
-        lens = (valid * idx).max(dim=1).values if L else torch.zeros(B, dtype=torch.int64, device=dense.device)
-    else:
-        lens = torch.full((B,), L, dtype=torch.int64, device=dense.device)
-    offsets = torch.zeros(B + 1, dtype=torch.int32, device=dense.device)
-    offsets[1:] = torch.cumsum(lens, 0)
-    mask = torch.arange(L, device=dense.device).unsqueeze(0) < lens.unsqueeze(1)
-    return dense[mask], [offsets]
+    """2-D dense -> ``(values, [offsets])``; with ``check_invalid`` trailing ``invalid_value`` entries are stripped."""
+    values, offsets = native().dense_to_ragged(dense, bool(check_invalid), float(invalid_value))
+    return values, [offsets]
 
 
 def ragged_to_sparse(values: torch.Tensor, offsets: List[torch.Tensor]) -> torch.Tensor:
-    """COO tensor with one index row per ragged level (row-major positions)."""
+    """COO tensor of a ragged tensor (runs on either device; the reference's op is CPU-only)."""
     if isinstance(offsets, torch.Tensor):
         offsets = [offsets]
-    dev = values.device
-    n = values.shape[0]
-    idx_rows = []
-    pos = torch.arange(n, device=dev)
-    shape = []
-    for level in range(len(offsets) - 1, -1, -1):
-        off = offsets[level].to(torch.int64)
-        lens = _row_lengths(off)
-        row = torch.repeat_interleave(torch.arange(lens.numel(), device=dev), lens)
-        col = pos - off[:-1][row]
-        idx_rows.append(col)
-        shape.append(int(lens.max().item()) if lens.numel() else 0)
-        pos = row
-    idx_rows.append(pos)
-    shape.append(offsets[0].numel() - 1)
-    indices = torch.stack(list(reversed(idx_rows)))
-    return torch.sparse_coo_tensor(indices, values, tuple(reversed(shape)))
+    indices, shape = native().ragged_to_sparse_indices(values.shape[0], list(offsets))
+    return torch.sparse_coo_tensor(indices, values, tuple(shape) + tuple(values.shape[1:]))
+
+
+def gen_segment_indices(offsets: torch.Tensor, nnz: Optional[int] = None) -> torch.Tensor:
+    return native().gen_segment_indices(offsets, int(nnz if nnz is not None else offsets[-1].item()))
+
+
+def _sides(t, n, device):
+    if t is None:
+        return torch.zeros(n, dtype=torch.bool)
+    if t.dtype != torch.bool:
+        raise ValueError(f"side tensors must be of type torch.bool, but got {t.dtype}.")
+    return t
+
+
+def fused_ragged_cutoff_2D(values: List[torch.Tensor], offsets: List[torch.Tensor], keep_lengths: torch.Tensor,
+                           drop_sides: torch.Tensor = None, pad_sides: torch.Tensor = None):
+    """Truncate the rows of several 2-D ragged tensors at once.
+
+    ``keep_lengths[t]`` values are kept per row of tensor ``t``; ``drop_sides[t]`` True drops from the left (start).
+    Returns ``(values, offsets, drop_nums, pad_nums, drop_sides, pad_sides)``; no pad values are written (``pad_nums``
+    tells a dense consumer how many it would need)."""
+    if len(offsets) != len(values):
+        raise ValueError(f"Length of 'offsets' list ({len(offsets)}) must match length of 'values' list ({len(values)}).")
+    drop_sides = _sides(drop_sides, len(values), values[0].device)
+    pad_sides = _sides(pad_sides, len(values), values[0].device)
+    v, o, d, p = native().fused_ragged_cutoff_2d(list(values), list(offsets), keep_lengths, drop_sides, pad_sides)
+    return v, o, d, p, drop_sides, pad_sides
+
+
+def fused_ragged_cutoff_3D(values: List[torch.Tensor], offsets: List[List[torch.Tensor]], keep_lengths: torch.Tensor,
+                           drop_sides: Optional[torch.Tensor] = None, pad_sides: Optional[torch.Tensor] = None):
+    """Give every sample of several 3-D ragged tensors exactly ``keep_lengths[t]`` inner rows (drop rows / pad empty rows).
+    ``offsets[t] = [outer, inner]``. Returns ``(values, [[outer, inner], ...])``."""
+    drop_sides = _sides(drop_sides, len(values), values[0].device)
+    pad_sides = _sides(pad_sides, len(values), values[0].device)
+    v, outer, inner = native().fused_ragged_cutoff_3d(list(values), [o[0] for o in offsets], [o[1] for o in offsets], keep_lengths,
+                                                      drop_sides, pad_sides)
+    return v, [[a, b] for a, b in zip(outer, inner)]
+
+
+def feature_cross_ragged(x_values, x_offsets, y_values, y_offsets, x_weight=None, y_weight=None):
+    """Per row: unique(x) x unique(y) -> ``(ids = murmur(x, y), offsets, weights = wx * wy)``."""
+    return native().feature_cross_ragged(x_values, x_offsets, y_values, y_offsets, x_weight, y_weight)
+
+
+def ragged_topk_index_cutoff(drop_num, pad_num, drop_side, pad_side, offset, topk_index, indicator):
+    """Map top-k positions inside truncated/padded rows back to indices of the original values.
+    All four drop/pad side combinations are handled (the reference implements drop-left/pad-right only)."""
+    dl = bool(drop_side.reshape(-1)[0].item()) if isinstance(drop_side, torch.Tensor) else bool(drop_side)
+    pl = bool(pad_side.reshape(-1)[0].item()) if isinstance(pad_side, torch.Tensor) else bool(pad_side)
+    return native().calc_ragged_index(drop_num, pad_num, dl, pl, offset, topk_index, indicator)
+
+
+def ragged_tile(batch: List[int], seq: List[int], indices: torch.Tensor, offset: torch.Tensor, table: torch.Tensor):
+    """Tile combiner on an explicit table: for every feature ``f`` and row, the first ``seq[f]`` rows of ``table`` addressed by
+    ``indices`` (zero padded) -> ``[sum_f batch[f] * seq[f], dim]``. Differentiable with respect to ``table``."""
+    outs = []
+    C = native()
+    row0 = 0
+    off = offset.to(torch.int32)
+    for b, s in zip(batch, seq):
+        o = (off[row0:row0 + b + 1] - off[row0]).contiguous()
+        idx = indices[int(off[row0]):int(off[row0 + b])].to(torch.int32).contiguous()
+        outs.append(_TileFn.apply(table, idx, o, int(s)).view(b * s, table.shape[1]))
+        row0 += b
+    return torch.cat(outs) if len(outs) > 1 else outs[0]
+
+
+class _TileFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, table, idx, offsets, tile_len):
+        out, gsrc, gscale = native().tile_forward(table.contiguous(), None, idx, offsets, None, tile_len, True)
+        ctx.save_for_backward(idx, gsrc)
+        ctx.shape = table.shape
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        idx, gsrc = ctx.saved_tensors
+        D = ctx.shape[1]
+        g = torch.zeros(ctx.shape, dtype=dy.dtype, device=dy.device)
+        keep = gsrc >= 0
+        g.index_add_(0, idx[keep].long(), dy.reshape(-1, D)[gsrc[keep].long()])
+        return g, None, None, None
