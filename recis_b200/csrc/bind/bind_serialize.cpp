@@ -1,0 +1,184 @@
+// Native file layer of the sparse checkpoint: streaming safetensors writer / reader.
+//
+// File format (identical to the reference's TableWriter, csrc/serialize/table_writer.cc:48-105): u64 header length,
+// JSON header padded with spaces to a multiple of 8 bytes (always at least one space), raw tensor bytes.
+// A block is either a host tensor or a "gather" block: rows of a device-resident slot slab selected by an index tensor,
+// which the writer pulls in chunks of RECIS_BLOCK_WRITE_SIZE rows (default 1 Mi, as csrc/serialize/name.cc:136-152)
+// through two pinned staging buffers, so the device-to-host copy of chunk i+1 overlaps the file write of chunk i and the
+// host never holds a full copy of a table. Several files are written concurrently, one thread each, with the GIL released.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <cstdio>
+#include <cstdlib>
+#include <fcntl.h>
+#include <thread>
+#include <unistd.h>
+#include "../kernels/rb_kernels.h"
+#include "../cpu/rb_cpu.h"
+
+namespace py = pybind11;
+using torch::Tensor;
+
+namespace {
+
+int64_t env_rows(const char* name) {
+  const char* v = std::getenv(name);
+  return v ? std::max<int64_t>(std::atoll(v), 1) : (1 << 20);
+}
+
+struct Block {
+  int kind;        // 0 host/dense tensor (copied to CPU by the caller), 1 gather rows of a slab
+  Tensor tensor;   // kind 0: contiguous CPU tensor; kind 1: slab [cap, D] fp32 or [cap] int64
+  Tensor rows;     // kind 1: int32 row indices on the slab's device
+};
+
+struct FileJob {
+  std::string path;
+  std::string header;
+  std::vector<Block> blocks;
+  std::string error;
+};
+
+void write_all(FILE* f, const void* p, size_t n, const std::string& path) {
+  if (n && std::fwrite(p, 1, n, f) != n) throw std::runtime_error("short write to " + path);
+}
+
+void write_gather_block(FILE* f, const Block& b, const std::string& path) {
+  const int64_t n = b.rows.numel();
+  if (n == 0) return;
+  const bool is_f32 = b.tensor.scalar_type() == torch::kFloat32;
+  const int64_t D = b.tensor.dim() == 2 ? b.tensor.size(1) : 1;
+  const int64_t esz = b.tensor.element_size();
+  const int64_t chunk = std::min<int64_t>(env_rows("RECIS_BLOCK_WRITE_SIZE"), n);
+  if (!b.tensor.is_cuda()) {
+    auto idx = b.rows.to(torch::kInt64);
+    for (int64_t s = 0; s < n; s += chunk) {
+      auto part = b.tensor.index_select(0, idx.narrow(0, s, std::min(chunk, n - s))).contiguous();
+      write_all(f, part.data_ptr(), (size_t)part.numel() * esz, path);
+    }
+    return;
+  }
+  c10::cuda::CUDAGuard guard(b.tensor.device());
+  auto stream = c10::cuda::getStreamFromPool(false, b.tensor.device().index());
+  c10::cuda::CUDAStreamGuard sg(stream);
+  Tensor stage_dev[2], stage_host[2];
+  cudaEvent_t done[2];
+  for (int i = 0; i < 2; ++i) {
+    stage_dev[i] = torch::empty({chunk, D}, b.tensor.options());
+    stage_host[i] = torch::empty({chunk, D}, b.tensor.options().device(torch::kCPU).pinned_memory(true));
+    cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming);
+  }
+  auto issue = [&](int64_t s, int slot) {
+    const int64_t m = std::min(chunk, n - s);
+    if (is_f32) {
+      rb_gather_rows(b.tensor.data_ptr<float>(), b.rows.data_ptr<int32_t>() + s, m, nullptr, (int)D, stage_dev[slot].data_ptr<float>(), stream);
+    } else {
+      auto part = b.tensor.index_select(0, b.rows.narrow(0, s, m).to(torch::kInt64));
+      stage_dev[slot].view({-1}).narrow(0, 0, m).copy_(part.view({-1}), true);
+    }
+    cudaMemcpyAsync(stage_host[slot].data_ptr(), stage_dev[slot].data_ptr(), (size_t)m * D * esz, cudaMemcpyDeviceToHost, stream);
+    cudaEventRecord(done[slot], stream);
+  };
+  int slot = 0;
+  issue(0, 0);
+  for (int64_t s = 0; s < n; s += chunk, slot ^= 1) {
+    if (s + chunk < n) issue(s + chunk, slot ^ 1);
+    cudaEventSynchronize(done[slot]);
+    write_all(f, stage_host[slot].data_ptr(), (size_t)std::min(chunk, n - s) * D * esz, path);
+  }
+  for (int i = 0; i < 2; ++i) cudaEventDestroy(done[i]);
+}
+
+void run_job(FileJob* job) {
+  try {
+    const std::string tmp = job->path + ".tmp";
+    FILE* f = std::fopen(tmp.c_str(), "wb");
+    if (!f) throw std::runtime_error("cannot open " + tmp);
+    std::vector<char> buf(8 << 20);
+    std::setvbuf(f, buf.data(), _IOFBF, buf.size());
+    std::string header = job->header;
+    header.append(8 - (header.size() % 8), ' ');
+    const uint64_t hlen = header.size();
+    write_all(f, &hlen, sizeof(hlen), tmp);
+    write_all(f, header.data(), header.size(), tmp);
+    for (const auto& b : job->blocks) {
+      if (b.kind == 0) write_all(f, b.tensor.data_ptr(), (size_t)b.tensor.numel() * b.tensor.element_size(), tmp);
+      else write_gather_block(f, b, tmp);
+    }
+    if (std::fflush(f) != 0 || std::fclose(f) != 0) throw std::runtime_error("flush/close failed for " + tmp);
+    if (std::rename(tmp.c_str(), job->path.c_str()) != 0) throw std::runtime_error("rename failed for " + job->path);
+  } catch (const std::exception& e) {
+    job->error = e.what();
+  }
+}
+
+// files: list of (path, header json, [ (kind, tensor, rows or None) ... ])
+void st_write_files(const std::vector<std::tuple<std::string, std::string, std::vector<std::tuple<int, Tensor, c10::optional<Tensor>>>>>& files) {
+  std::vector<FileJob> jobs(files.size());
+  for (size_t i = 0; i < files.size(); ++i) {
+    jobs[i].path = std::get<0>(files[i]);
+    jobs[i].header = std::get<1>(files[i]);
+    for (const auto& b : std::get<2>(files[i])) {
+      Block blk;
+      blk.kind = std::get<0>(b);
+      blk.tensor = std::get<1>(b);
+      if (blk.kind == 0) {
+        TORCH_CHECK(!blk.tensor.is_cuda() && blk.tensor.is_contiguous(), "dense blocks must be contiguous CPU tensors");
+      } else {
+        TORCH_CHECK(std::get<2>(b).has_value(), "gather blocks need row indices");
+        blk.rows = std::get<2>(b)->to(torch::kInt32).contiguous();
+        TORCH_CHECK(blk.tensor.is_contiguous());
+      }
+      jobs[i].blocks.push_back(std::move(blk));
+    }
+  }
+  {
+    py::gil_scoped_release nogil;
+    std::vector<std::thread> threads;
+    for (auto& j : jobs) threads.emplace_back(run_job, &j);
+    for (auto& t : threads) t.join();
+  }
+  for (auto& j : jobs) TORCH_CHECK(j.error.empty(), "checkpoint write failed: ", j.error);
+}
+
+// (header json, offset of the first data byte)
+std::tuple<std::string, int64_t> st_read_header(const std::string& path) {
+  FILE* f = std::fopen(path.c_str(), "rb");
+  TORCH_CHECK(f, "cannot open ", path);
+  uint64_t hlen = 0;
+  const bool ok = std::fread(&hlen, sizeof(hlen), 1, f) == 1;
+  TORCH_CHECK(ok && hlen < (1ull << 32), "corrupt safetensors header in ", path);
+  std::string header(hlen, '\0');
+  const bool ok2 = std::fread(header.data(), 1, hlen, f) == hlen;
+  std::fclose(f);
+  TORCH_CHECK(ok2, "truncated safetensors header in ", path);
+  return {header, (int64_t)(8 + hlen)};
+}
+
+// read `out.nbytes()` bytes at `offset` of `path` into the contiguous CPU tensor `out`
+void st_read_into(const std::string& path, int64_t offset, Tensor out) {
+  TORCH_CHECK(!out.is_cuda() && out.is_contiguous());
+  const size_t n = (size_t)out.numel() * out.element_size();
+  char* dst = reinterpret_cast<char*>(out.data_ptr());
+  py::gil_scoped_release nogil;
+  const int fd = ::open(path.c_str(), O_RDONLY);
+  TORCH_CHECK(fd >= 0, "cannot open ", path);
+  size_t got = 0;
+  while (got < n) {
+    const ssize_t r = ::pread(fd, dst + got, n - got, offset + (int64_t)got);
+    if (r <= 0) break;
+    got += (size_t)r;
+  }
+  ::close(fd);
+  TORCH_CHECK(got == n, "truncated tensor data in ", path, ": wanted ", n, " bytes at ", offset, ", got ", got);
+}
+
+}  // namespace
+
+void init_serialize(py::module& m) {
+  m.def("st_write_files", &st_write_files);
+  m.def("st_read_header", &st_read_header);
+  m.def("st_read_into", &st_read_into);
+}

@@ -5,6 +5,7 @@ void init_sparse(pybind11::module& m);
 void init_dense(pybind11::module& m);
 void init_comm(pybind11::module& m);
 void init_ragged(pybind11::module& m);
+void init_serialize(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "recis_b200 native extension (sm_100a kernels + CPU implementations)";
@@ -12,4 +13,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   init_dense(m);
   init_comm(m);
   init_ragged(m);
+  init_serialize(m);
 }

@@ -50,7 +50,7 @@ class GlobalStepFilterHookImpl(torch.nn.Module):
 
     def __init__(self, table, filter_step: int = 100, **params):
         super().__init__()
-        self._table = table
+        object.__setattr__(self, "_table", table)   # plain reference: the table is this module's parent, not a child
         self._filter_step = int(filter_step)
         dev = table.impl.device if hasattr(table, "impl") else table.device
         self.register_buffer("_global_step", torch.zeros(1, dtype=torch.int64, device=dev))

@@ -1,0 +1,156 @@
+"""Sparse checkpoint bundle: layout checked with an independent reader, save -> load -> save byte equality, resharding."""
+import json
+import os
+
+import pytest
+import torch
+
+from recis_b200.nn import EmbeddingEngine, EmbeddingOption, HashTable, filter_out_sparse_param, gen_slice
+from recis_b200.nn.hashtable_hook import FilterHook
+from recis_b200.nn.initializers import NormalInitializer
+from recis_b200.nn.modules.hashtable import HashtableRegister
+from recis_b200.optim import SparseAdamW
+from recis_b200.serialize import CheckpointReader, Loader, Saver
+
+
+def _trained_engine(steps=3, seed=0):
+    torch.manual_seed(seed)
+    init = NormalInitializer(0, 0.05)
+    opts = {"user": EmbeddingOption(embedding_dim=8, shared_name="user", initializer=init, device="cpu"),
+            "item": EmbeddingOption(embedding_dim=8, shared_name="item", initializer=init, device="cpu"),
+            "wide": EmbeddingOption(embedding_dim=4, shared_name="wide", initializer=init, device="cpu",
+                                    filter_hook=FilterHook("GlobalStepFilter", {"filter_step": 100}))}
+    eng = EmbeddingEngine(opts)
+    opt = SparseAdamW(filter_out_sparse_param(eng), lr=0.01)
+    for t in range(steps):
+        feats = {k: torch.randint(0, 500, (16, 3)) * 31 for k in opts}
+        out = eng(feats)
+        loss = sum(v.square().sum() for v in out.values())
+        opt.zero_grad(); loss.backward(); opt.step()
+    return eng, opt
+
+
+def _dump(eng):
+    out = {}
+    for name, ht in eng.tables().items():
+        ids, rows = ht.impl.ids_map()
+        order = torch.argsort(ids)
+        st = ht.impl.store
+        out[name] = dict(ids=ids[order], emb=st.emb()[rows[order]],
+                         slots={s: st.slot(s)[rows[order]] for s in st.slot_names()}, seen=st.last_seen()[rows[order]])
+    return out
+
+
+def test_layout_and_independent_reader(tmp_path):
+    eng, opt = _trained_engine()
+    dense = {"w": torch.randn(3, 5), "flag": torch.tensor([True, False]), "sparse_adamw_step": torch.tensor(3.0)}
+    Saver(0, 1, 2, filter_out_sparse_param(eng), dense, str(tmp_path)).save()
+    files = sorted(os.listdir(tmp_path))
+    assert files == ["index", "model-000000-of-000002.safetensors", "model-000001-of-000002.safetensors", "tensorkey.json",
+                     "torch_rank_weights_embs_table_multi_shard.json"]
+    index = json.load(open(tmp_path / "index"))
+    assert set(index) == {"file_index", "block_index"}
+    tk = json.load(open(tmp_path / "tensorkey.json"))
+    assert tk["user.embedding/part_0_1"] == "user@embedding^0@65536@65536"
+    assert "user.sparse_adamw_exp_avg/part_0_1" in tk and "wide.id/part_0_1" in tk and "w^ " in index["block_index"]
+    rank = json.load(open(tmp_path / "torch_rank_weights_embs_table_multi_shard.json"))
+    e = rank["item.embedding/part_0_1"]
+    assert e["is_hashmap"] and e["hashmap_key"] == "item.id/part_0_1" and e["dimension"] == 8 and e["dtype"] == "float32"
+    # raw format: u64 header length, JSON padded with at least one space to a multiple of 8
+    raw = open(tmp_path / "model-000000-of-000002.safetensors", "rb").read()
+    hlen = int.from_bytes(raw[:8], "little")
+    assert hlen % 8 == 0 and raw[8 + hlen - 1:8 + hlen] == b" "
+    # an independent implementation reads the files
+    safetensors = pytest.importorskip("safetensors")
+    from safetensors import safe_open
+    seen = {}
+    for f in files:
+        if f.endswith(".safetensors"):
+            with safe_open(str(tmp_path / f), framework="pt") as fh:
+                for k in fh.keys():
+                    seen[k] = fh.get_tensor(k)
+    ref = _dump(eng)
+    table = next(n for n, t in eng.tables().items() if t.impl.dim == 8)
+    ids = seen["user.id/part_0_1"]
+    enc = ids | (0 << 52)
+    pos = torch.searchsorted(ref[table]["ids"], enc)
+    assert torch.equal(ref[table]["ids"][pos], enc)
+    assert torch.equal(seen["user.embedding/part_0_1"], ref[table]["emb"][pos])
+    assert torch.equal(seen["w^ "], dense["w"]) and torch.equal(seen["flag^ "], dense["flag"])
+    rd = CheckpointReader(str(tmp_path))
+    assert "user@embedding" in rd.list_tensors() and "w" in rd.list_tensors()
+    assert torch.equal(rd.read_tensor("user@embedding"), seen["user.embedding/part_0_1"])
+    assert rd.tensor_shape("w") == [3, 5] and rd.tensor_dtype("user@id") == torch.int64
+
+
+def test_save_load_save_is_byte_identical(tmp_path):
+    eng, _ = _trained_engine()
+    dense = {"w": torch.randn(4, 4)}
+    a, b = tmp_path / "a", tmp_path / "b"
+    Saver(0, 1, 1, filter_out_sparse_param(eng), dense, str(a)).save()
+    ref = _dump(eng)
+    HashtableRegister().clear()
+    eng2, opt2 = _trained_engine(steps=0, seed=1)          # fresh, empty tables (optimizer slots exist)
+    dense2 = {"w": torch.zeros(4, 4)}
+    Loader(str(a), filter_out_sparse_param(eng2), dense2).load()
+    got = _dump(eng2)
+    for name in ref:
+        assert torch.equal(got[name]["ids"], ref[name]["ids"]) and torch.equal(got[name]["emb"], ref[name]["emb"])
+        assert torch.equal(got[name]["seen"], ref[name]["seen"])
+        for s in ref[name]["slots"]:
+            assert torch.equal(got[name]["slots"][s], ref[name]["slots"][s])
+    assert torch.equal(dense2["w"], dense["w"])
+    Saver(0, 1, 1, filter_out_sparse_param(eng2), dense2, str(b)).save()
+    for f in os.listdir(a):
+        assert open(a / f, "rb").read() == open(b / f, "rb").read(), f
+
+
+@pytest.mark.parametrize("w_save,w_load", [(4, 1), (1, 3), (3, 2)])
+def test_resharding(tmp_path, w_save, w_load):
+    torch.manual_seed(0)
+    all_ids = torch.randint(0, 1 << 40, (3000,)).unique()
+    emb_of = {}
+    for r in range(w_save):
+        HashtableRegister().clear()
+        sl = gen_slice(r, w_save)
+        ht = HashTable([8], initializer=NormalInitializer(0, 1), name="tbl", device="cpu", slice=sl)
+        mine = all_ids[((all_ids & 0xFFFF) >= sl.slice_begin) & ((all_ids & 0xFFFF) < sl.slice_end)]
+        e = ht(mine)
+        for i, v in zip(mine.tolist(), e.detach()):
+            emb_of[i] = v.clone()
+        Saver(r, w_save, 2, filter_out_sparse_param(ht), {"d": torch.arange(3.0)} if r == 0 else {}, str(tmp_path)).save()
+    assert os.path.exists(tmp_path / "index")
+    total = 0
+    for r in range(w_load):
+        HashtableRegister().clear()
+        sl = gen_slice(r, w_load)
+        ht = HashTable([8], initializer=NormalInitializer(0, 1), name="tbl", device="cpu", slice=sl)
+        Loader(str(tmp_path), filter_out_sparse_param(ht), {}).load()
+        ids, rows = ht.ids_map()
+        assert bool((((ids & 0xFFFF) >= sl.slice_begin) & ((ids & 0xFFFF) < sl.slice_end)).all())
+        for i, row in zip(ids.tolist(), rows.tolist()):
+            assert torch.equal(ht.embeddings()[row], emb_of[i])
+        total += ids.numel()
+    assert total == all_ids.numel()
+
+
+def test_failures_are_clean_errors(tmp_path):
+    eng, _ = _trained_engine(steps=1)
+    Saver(0, 1, 1, filter_out_sparse_param(eng), {"w": torch.ones(2)}, str(tmp_path)).save()
+    HashtableRegister().clear()
+    eng2, _ = _trained_engine(steps=0)
+    with pytest.raises(KeyError):
+        Loader(str(tmp_path), filter_out_sparse_param(eng2), {"missing": torch.zeros(1)}).load()
+    with pytest.raises(ValueError):
+        Loader(str(tmp_path), {}, {"w": torch.zeros(3)}).load()
+    # truncated shard: the loader reports it instead of reading garbage
+    f = tmp_path / "model-000000-of-000001.safetensors"
+    data = open(f, "rb").read()
+    open(f, "wb").write(data[: len(data) // 2])
+    HashtableRegister().clear()
+    eng3, _ = _trained_engine(steps=0)
+    with pytest.raises(RuntimeError):
+        Loader(str(tmp_path), filter_out_sparse_param(eng3), {}).load()
+    os.remove(tmp_path / "index")
+    with pytest.raises(FileNotFoundError):
+        Loader(str(tmp_path), {}, {})
