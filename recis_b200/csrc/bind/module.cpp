@@ -6,6 +6,8 @@ void init_dense(pybind11::module& m);
 void init_comm(pybind11::module& m);
 void init_ragged(pybind11::module& m);
 void init_serialize(pybind11::module& m);
+void init_metrics(pybind11::module& m);
+void init_io(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "recis_b200 native extension (sm_100a kernels + CPU implementations)";
@@ -14,4 +16,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   init_comm(m);
   init_ragged(m);
   init_serialize(m);
+  init_metrics(m);
+  init_io(m);
 }

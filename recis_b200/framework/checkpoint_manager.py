@@ -1,0 +1,211 @@
+"""Checkpoint saving / restoring around the training loop (``recis/framework/checkpoint_manager.py:24-505``).
+
+Directory layout (same as the reference):
+``<output_dir>/checkpoint`` (one checkpoint id per line), ``<output_dir>/ckpt_<step>/`` holding the sparse bundle
+(``model-*.safetensors``, ``index``, ``tensorkey.json``, ``torch_rank_weights_embs_table_multi_shard.json``),
+``model.pt`` (dense state dict), ``extra.pt`` (registered extras incl. ``global_step`` and the dense optimizer),
+``io_state_<rank>.pt`` + ``io_state_count``. ``load_by_config`` takes ``{"load": [...], "exclude": [...], "strict": bool}``
+over the parts ``sparse, dense, extra, sparse_opt, io_state``.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..nn.modules.hashtable import split_sparse_dense_state_dict
+from ..serialize import Loader as SLoader, Saver as SSaver
+from ..utils.logger import Logger
+
+logger = Logger(__name__)
+
+
+class Saver:
+    def __init__(self, model: torch.nn.Module, sparse_optim=None, output_dir: str = "./", max_keep: int = 1, concurrency: int = 4):
+        self._model = model
+        self._sparse_state_dict, self._dense_state_dict = split_sparse_dense_state_dict(model.state_dict())
+        self._checkpoint_file = "checkpoint"
+        self._checkpoint_version_list = []
+        self._max_keep = max_keep
+        self._extra_save_dict = {}
+        self._output_dir = output_dir
+        self._sparse_optim = sparse_optim
+        self._concurrency = concurrency
+        self._io_state = {}
+
+    def register_io_state(self, name, obj):
+        if name in self._io_state:
+            raise ValueError(f"name {name} already registered in io state")
+        self._io_state[name] = obj
+
+    def register_for_checkpointing(self, name, obj):
+        if name in self._extra_save_dict:
+            raise ValueError(f"name {name} already registered")
+        self._extra_save_dict[name] = obj
+
+    def get_extra_data(self, name: str):
+        return self._extra_save_dict.get(name)
+
+    def _sparse_parts(self):
+        """(tables, scalar tensors of the sparse optimizer) as they stand now."""
+        state = dict(self._sparse_state_dict)
+        if self._sparse_optim is not None:
+            state.update(self._sparse_optim.state_dict())
+        return split_sparse_dense_state_dict(state)
+
+    def save(self, ckpt_id: str, shard_id: int = 0, shard_num: int = 1):
+        ckpt_path = os.path.join(self._output_dir, ckpt_id)
+        os.makedirs(ckpt_path, exist_ok=True)
+        logger.info(f"Save checkpoint {ckpt_id} to {ckpt_path}")
+        tables, scalars = self._sparse_parts()
+        if tables:
+            SSaver(shard_index=shard_id, shard_num=shard_num, parallel=self._concurrency, hashtables=tables, tensors=scalars,
+                   path=ckpt_path).save()
+            if shard_num > 1 and dist.is_available() and dist.is_initialized():
+                dist.barrier()
+        io_states = {name: io.dump_io_state() for name, io in self._io_state.items()}
+        if io_states:
+            torch.save(io_states, os.path.join(ckpt_path, f"io_state_{shard_id}.pt"))
+        if shard_id == 0:
+            _tables, dense = split_sparse_dense_state_dict(self._model.state_dict())
+            if dense:
+                torch.save(dense, os.path.join(ckpt_path, "model.pt"))
+            if self._extra_save_dict:
+                extra = {k: (v.state_dict() if hasattr(v, "state_dict") else v) for k, v in self._extra_save_dict.items()}
+                torch.save(extra, os.path.join(ckpt_path, "extra.pt"))
+                if io_states:
+                    with open(os.path.join(ckpt_path, "io_state_count"), "w") as f:
+                        f.write(f"{shard_num}")
+            with open(os.path.join(self._output_dir, self._checkpoint_file), "a+") as f:
+                f.write(ckpt_id + "\n")
+            if ckpt_id not in self._checkpoint_version_list:
+                self._checkpoint_version_list.append(ckpt_id)
+            while len(self._checkpoint_version_list) > self._max_keep:
+                old = self._checkpoint_version_list.pop(0)
+                logger.info(f"Remove checkpoint {os.path.join(self._output_dir, old)}")
+                shutil.rmtree(os.path.join(self._output_dir, old), ignore_errors=True)
+                with open(os.path.join(self._output_dir, self._checkpoint_file)) as f:
+                    remains = [l.strip() for l in f.read().split("\n") if l.strip() and l.strip() != old]
+                with open(os.path.join(self._output_dir, self._checkpoint_file), "w") as f:
+                    f.writelines(r + "\n" for r in remains)
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+
+    # ---- loading
+    def load_sparse_params(self, ckpt_dir: str, strict=True, with_optim_scalars=True):
+        tables, scalars = self._sparse_parts()
+        loaded = {k: v.clone() for k, v in scalars.items()} if with_optim_scalars else {}
+        SLoader(ckpt_dir, hashtables=tables, tensors=loaded, strict=strict).load()
+        return loaded
+
+    def load_dense_params(self, ckpt_dir: str, strict: bool = True):
+        logger.info("Load dense model")
+        self._model.load_state_dict(torch.load(os.path.join(ckpt_dir, "model.pt"), weights_only=False), strict=strict)
+
+    def load_extra_params(self, ckpt_dir: str, load_io: bool, shard_id: int = 0):
+        extra = torch.load(os.path.join(ckpt_dir, "extra.pt"), weights_only=False)
+        if load_io and self._io_state:
+            count_file = os.path.join(ckpt_dir, "io_state_count")
+            io_file = os.path.join(ckpt_dir, f"io_state_{shard_id}.pt")
+            if os.path.exists(count_file) and os.path.exists(io_file):
+                io_state = torch.load(io_file, weights_only=False)
+                for name, io in self._io_state.items():
+                    if name in io_state:
+                        logger.info(f"Load io state for dataset: {name}")
+                        io.load_io_state(io_state[name])
+        for key, value in list(self._extra_save_dict.items()):
+            if key not in extra:
+                continue
+            if hasattr(value, "load_state_dict"):
+                value.load_state_dict(extra[key])
+            elif isinstance(value, torch.Tensor) and isinstance(extra[key], torch.Tensor):
+                value.copy_(extra[key])
+            else:
+                self._extra_save_dict[key] = extra[key]
+
+    def load(self, ckpt_path: Optional[str] = None, ckpt_id: Optional[str] = None, load_conf: Optional[dict] = None, shard_id: int = 0,
+             direct_path=False):
+        load_conf = load_conf or {}
+        if direct_path:
+            if not ckpt_path:
+                return False
+        else:
+            ckpt_path = ckpt_path or self._output_dir
+            if ckpt_id is None:
+                listing = os.path.join(ckpt_path, self._checkpoint_file)
+                if not os.path.exists(listing):
+                    logger.info(f"Checkpoint not found in {ckpt_path}")
+                    return False
+                lines = [l.strip() for l in open(listing).read().split("\n") if l.strip()]
+                if not lines:
+                    return False
+                ckpt_id = lines[-1]
+            ckpt_path = os.path.join(ckpt_path, ckpt_id)
+        logger.info(f"Load checkpoint conf {load_conf} from {ckpt_path}")
+        self.load_by_config(ckpt_path, load_conf, shard_id)
+        return True
+
+    def load_by_config(self, ckpt_path: str, load_conf: Optional[dict] = None, shard_id: int = 0):
+        load_conf = load_conf or {}
+        parts = ["sparse", "dense", "extra", "sparse_opt", "io_state"]
+        load_map = dict.fromkeys(parts, False)
+        for item in load_conf.get("load", ["*"]):
+            for p in (parts if item == "*" else [item]):
+                load_map[p] = True
+        for item in load_conf.get("exclude", []):
+            for p in (parts if item == "*" else [item]):
+                load_map[p] = False
+        strict = load_conf.get("strict", True)
+        scalars = {}
+        if load_map["sparse"] and self._sparse_state_dict:
+            scalars = self.load_sparse_params(ckpt_path, strict=strict, with_optim_scalars=load_map["sparse_opt"])
+        if load_map["dense"] and self._dense_state_dict and os.path.exists(os.path.join(ckpt_path, "model.pt")):
+            self.load_dense_params(ckpt_path, strict=strict)
+        if load_map["extra"] and self._extra_save_dict and os.path.exists(os.path.join(ckpt_path, "extra.pt")):
+            self.load_extra_params(ckpt_path, load_map["io_state"], shard_id)
+        if load_map["sparse_opt"] and self._sparse_optim is not None and scalars:
+            self._sparse_optim.load_state_dict(scalars)
+
+
+class CheckpointManager:
+    def __init__(self, saver: Saver, save_interval: int) -> None:
+        self._saver = saver
+        self._global_step = torch.scalar_tensor(0, dtype=torch.int64)
+        self._rank = int(os.environ.get("RANK", 0))
+        self._shard_num = int(os.environ.get("WORLD_SIZE", 1))
+        self._save_interval = save_interval
+        if self._saver.get_extra_data("global_step") is None:
+            self._saver.register_for_checkpointing("global_step", self._global_step)
+
+    @property
+    def save_interval(self):
+        return self._save_interval
+
+    @property
+    def global_step(self):
+        return self._global_step
+
+    def register_for_checkpointing(self, name, obj):
+        self._saver.register_for_checkpointing(name, obj)
+
+    def step(self):
+        self._global_step += 1
+        if self._save_interval and int(self._global_step) % self._save_interval == 0:
+            self._saver.save(f"ckpt_{int(self._global_step)}", self._rank, self._shard_num)
+
+    def save(self):
+        self._saver.save(f"ckpt_{int(self._global_step)}", self._rank, self._shard_num)
+
+    def load_model_bank(self, model_bank_conf):
+        for mbc in model_bank_conf or []:
+            self._saver.load(ckpt_path=mbc["path"], load_conf=mbc, shard_id=self._rank, direct_path=True)
+
+    def restore(self, global_step: Optional[int] = None):
+        self._saver.load(ckpt_id=None if global_step is None else f"ckpt_{global_step}", shard_id=self._rank)
+        gs = self._saver.get_extra_data("global_step")
+        if gs is not None:
+            self._global_step = gs if isinstance(gs, torch.Tensor) else torch.scalar_tensor(int(gs), dtype=torch.int64)
+        return self._global_step

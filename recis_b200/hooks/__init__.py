@@ -1,0 +1,6 @@
+from .filter_hook import HashTableFilterHook
+from .hook import Hook
+from .logger_hook import LoggerHook
+from .profiler_hook import ProfilerHook
+
+__all__ = ["Hook", "LoggerHook", "ProfilerHook", "HashTableFilterHook"]

@@ -1,0 +1,33 @@
+"""Drives table eviction from the training loop (``recis/hooks/filter_hook.py:82-117``): every step the global step of
+each table's filter advances; every ``filter_interval`` steps rows not seen for longer than the filter's TTL are erased."""
+from __future__ import annotations
+
+from ..nn.modules.hashtable import HashTable
+from ..utils.logger import Logger
+from .hook import Hook
+
+
+class HashTableFilterHook(Hook):
+    def __init__(self, filter_interval: int = 100, model=None):
+        self.filter_interval = max(int(filter_interval), 1)
+        self._filters = []
+        self._steps = 0
+        self.evicted = 0
+        self.logger = Logger("HashTableFilterHook")
+        if model is not None:
+            self.attach(model)
+
+    def attach(self, model):
+        """Collect the filter of every table inside ``model``."""
+        self._filters = [m._filter_hook_impl for m in model.modules() if isinstance(m, HashTable) and m._filter_hook_impl is not None]
+        return self
+
+    def after_step(self, metrics=None, global_step=0):
+        self._steps += 1
+        for f in self._filters:
+            f.update_step()
+        if self._steps % self.filter_interval == 0:
+            n = sum(f.do_filter() for f in self._filters)
+            self.evicted += n
+            if n:
+                self.logger.info(f"evicted {n} rows at step {self._steps}")

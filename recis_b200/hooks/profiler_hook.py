@@ -1,0 +1,51 @@
+"""torch.profiler schedule driven from the step hook; writes a chrome trace per active window
+(``recis/hooks/profiler_hook.py:46-116``). Sparse-path kernels show up under their own names; NVTX ranges can be added
+around steps with ``nvtx=True``."""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from .hook import Hook
+
+
+class ProfilerHook(Hook):
+    def __init__(self, wait=1, warmup=1, active=1, repeat=1, output_dir="./", record_shapes=True, profile_memory=False,
+                 with_stack=False, with_flops=False, nvtx=False):
+        self.output_dir = output_dir
+        self.app_id = os.environ.get("APP_ID", "recis_b200")
+        os.makedirs(output_dir, exist_ok=True)
+        acts = [torch.profiler.ProfilerActivity.CPU]
+        if torch.cuda.is_available():
+            acts.append(torch.profiler.ProfilerActivity.CUDA)
+        self.traces = []
+        self._step = 0
+        self.nvtx = nvtx and torch.cuda.is_available()
+        self.prof = torch.profiler.profile(
+            activities=acts, schedule=torch.profiler.schedule(wait=wait, warmup=warmup, active=active, repeat=repeat),
+            on_trace_ready=self._on_trace, record_shapes=record_shapes, profile_memory=profile_memory, with_stack=with_stack,
+            with_flops=with_flops)
+        self.prof.start()
+        if self.nvtx:
+            torch.cuda.nvtx.range_push("step 0")
+
+    def _on_trace(self, prof):
+        path = os.path.join(self.output_dir, f"{self.app_id}-timeline-{self._step}.json")
+        prof.export_chrome_trace(path)
+        self.traces.append(path)
+
+    def after_step(self, metrics=None, global_step=0):
+        self._step += 1
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
+            torch.cuda.nvtx.range_push(f"step {self._step}")
+        self.prof.step()
+
+    def end(self):
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
+            self.nvtx = False
+        if self.prof is not None:
+            self.prof.stop()
+            self.prof = None

@@ -1,0 +1,303 @@
+"""Datasets and dataset wrappers (``recis/io``: ``dataset_base.py``, ``orc_dataset.py``, ``state_dataset.py``,
+``map_dataset.py``, ``wrap_end_dataset.py``, ``filter_dataset.py``).
+
+A dataset is an iterable of batches (dict name -> Tensor / RaggedTensor) that can dump and restore its position
+(``dump_io_state`` / ``load_io_state``). The training loop consumes ``(stop_flag, batch)`` pairs, produced by
+``WrapEndDataset``. Sources:
+* ``SyntheticDataset``  native multi-threaded generator (``csrc/bind/bind_io.cpp``), pinned output, state = batch index;
+* ``OrcDataset``        columnar files through pyarrow (ORC or Parquet): list columns become RaggedTensors, string columns
+                        are hashed at read time (FarmHash / MurmurHash, as column-io does), rows are sharded over workers;
+* ``TensorDataset``     in-memory dict of tensors, for tests and small jobs.
+The ODPS / Lake / Pangu readers of the reference are services internal to its authors and have no counterpart here.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from .. import native
+from ..ragged.tensor import RaggedTensor
+from .synthetic import SyntheticSpec
+
+_LEN_KIND = {"fixed": 0, "poisson": 1, "geometric": 2, "uniform": 3}
+
+
+class DatasetBase:
+    """Iterable of batches with a restorable position."""
+
+    def __iter__(self):
+        raise NotImplementedError
+
+    def dump_io_state(self):
+        return {}
+
+    def load_io_state(self, state):
+        pass
+
+
+class SyntheticDataset(DatasetBase):
+    def __init__(self, spec: SyntheticSpec, steps: Optional[int] = None, threads: int = 2, prefetch: int = 4, pin: bool = False):
+        self.spec, self.steps = spec, steps
+        fields = [(f.zipf_a, f.id_bits, int(f.universe or 0), _LEN_KIND[f.length], float(f.mean_len), f.min_len, f.max_len, f.geo_p)
+                  for f in spec.sparse]
+        self._src = native().SyntheticSource(spec.batch, spec.dense_dim, fields, spec.label_rate, spec.seed, threads, prefetch, pin)
+        self._names = [f.name for f in spec.sparse]
+
+    def __iter__(self):
+        while self.steps is None or self._src.state() < self.steps:
+            dense, label, fields = self._src.next()
+            batch = {"label": label}
+            if self.spec.dense_dim:
+                batch["dense"] = dense
+            for name, (ids, off) in zip(self._names, fields):
+                batch[name] = RaggedTensor(ids, [off], dense_shape=(self.spec.batch, -1))
+            yield batch
+
+    def dump_io_state(self):
+        return {"step": self._src.state()}
+
+    def load_io_state(self, state):
+        self._src.set_state(int(state["step"]))
+
+
+class TensorDataset(DatasetBase):
+    """Batches sliced from an in-memory dict of equally long tensors."""
+
+    def __init__(self, data: Dict[str, torch.Tensor], batch_size: int, drop_remainder: bool = False, epochs: int = 1):
+        self.data, self.batch_size, self.drop_remainder, self.epochs = data, batch_size, drop_remainder, epochs
+        self._n = len(next(iter(data.values())))
+        self._pos = 0
+
+    def __iter__(self):
+        total = self._n * self.epochs
+        while self._pos < total:
+            b = self._pos % self._n
+            e = min(b + self.batch_size, self._n)
+            if self.drop_remainder and e - b < self.batch_size:
+                self._pos += e - b
+                continue
+            self._pos += e - b
+            yield {k: v[b:e] for k, v in self.data.items()}
+
+    def dump_io_state(self):
+        return {"pos": self._pos}
+
+    def load_io_state(self, state):
+        self._pos = int(state["pos"])
+
+
+class OrcDataset(DatasetBase):
+    """Columnar files -> batches. ``varlen_feature`` columns (lists of ints, or strings / lists of strings with a hash)
+    become RaggedTensors; ``fixedlen_feature`` columns become dense ``[batch, dim]`` tensors."""
+
+    def __init__(self, batch_size: int, worker_idx: int = 0, worker_num: int = 1, read_threads_num: int = 2, prefetch: int = 2,
+                 drop_remainder: bool = False, shuffle: bool = False, ragged_format: bool = True, transform_fn: Optional[Callable] = None,
+                 dtype: torch.dtype = torch.float32, device: str = "cpu", pin: bool = False, seed: int = 0):
+        self.batch_size, self.worker_idx, self.worker_num = batch_size, worker_idx, worker_num
+        self.drop_remainder, self.shuffle, self.transform_fn, self.dtype, self.device, self.pin = drop_remainder, shuffle, transform_fn, dtype, device, pin
+        self.prefetch, self.seed = prefetch, seed
+        self._paths: List[str] = []
+        self._varlen, self._fixed = {}, {}
+        self._file_idx, self._row_in_file = 0, 0
+
+    def add_path(self, path: str):
+        self._paths.append(path)
+
+    def add_paths(self, paths: List[str]):
+        self._paths.extend(paths)
+
+    def varlen_feature(self, name: str, hash_type: Optional[str] = None, hash_bucket: int = 0, trans_int8: bool = False):
+        self._varlen[name] = dict(hash_type=hash_type, hash_bucket=hash_bucket, trans_int8=trans_int8)
+
+    def fixedlen_feature(self, name: str, default_value=0.0):
+        self._fixed[name] = default_value
+
+    def _my_paths(self):
+        return [p for i, p in enumerate(sorted(self._paths)) if i % self.worker_num == self.worker_idx]
+
+    @staticmethod
+    def _read_table(path):
+        if path.endswith(".parquet"):
+            import pyarrow.parquet as pq
+            return pq.read_table(path)
+        import pyarrow.orc as orc
+        return orc.ORCFile(path).read()
+
+    def _column_to_ragged(self, col, conf):
+        import numpy as np
+        import pyarrow as pa
+        col = col.combine_chunks() if hasattr(col, "combine_chunks") else col
+        n = len(col)
+        if pa.types.is_list(col.type) or pa.types.is_large_list(col.type):
+            offsets = np.asarray(col.offsets.to_numpy(zero_copy_only=False), dtype=np.int64)
+            offsets = offsets - offsets[0]
+            flat = col.flatten()
+        else:
+            offsets = np.arange(n + 1, dtype=np.int64)
+            flat = col
+        if pa.types.is_string(flat.type) or pa.types.is_large_string(flat.type) or pa.types.is_binary(flat.type):
+            strings = [s if isinstance(s, bytes) else (s or "").encode() for s in flat.to_pylist()]
+            data = torch.frombuffer(bytearray(b"".join(strings)) or bytearray(1), dtype=torch.int8)[: sum(len(s) for s in strings)]
+            soff = torch.zeros(len(strings) + 1, dtype=torch.int32)
+            soff[1:] = torch.cumsum(torch.tensor([len(s) for s in strings], dtype=torch.int64), 0)
+            if conf["trans_int8"] or not conf["hash_type"]:
+                return RaggedTensor(data, [torch.from_numpy(offsets.astype(np.int32)), soff])
+            values = native().fused_hash([data], [soff], 0 if conf["hash_type"] == "farm" else 1)[0]
+        else:
+            values = torch.from_numpy(np.ascontiguousarray(flat.to_numpy(zero_copy_only=False))).to(torch.int64)
+        if conf["hash_bucket"]:
+            values = native().fused_mod([values], [int(conf["hash_bucket"])])[0]
+        return RaggedTensor(values, [torch.from_numpy(offsets.astype(np.int32))], dense_shape=(n, -1))
+
+    def _batches_of(self, table, start_row):
+        import numpy as np
+        n = table.num_rows
+        for b in range(start_row, n, self.batch_size):
+            e = min(b + self.batch_size, n)
+            if self.drop_remainder and e - b < self.batch_size:
+                break
+            part = table.slice(b, e - b)
+            batch = {}
+            for name, conf in self._varlen.items():
+                batch[name] = self._column_to_ragged(part.column(name), conf)
+            for name, default in self._fixed.items():
+                col = part.column(name).combine_chunks()
+                arr = np.asarray(col.fill_null(default).to_pylist() if col.null_count else col.to_pylist())
+                t = torch.as_tensor(arr)
+                batch[name] = (t.to(self.dtype) if t.is_floating_point() else t).reshape(e - b, -1)
+            if self.transform_fn is not None:
+                batch = self.transform_fn(batch)
+            self._row_in_file = e
+            yield batch
+
+    def __iter__(self):
+        paths = self._my_paths()
+        while self._file_idx < len(paths):
+            table = self._read_table(paths[self._file_idx])
+            yield from self._batches_of(table, self._row_in_file)
+            self._file_idx += 1
+            self._row_in_file = 0
+
+    def dump_io_state(self):
+        return {"file_idx": self._file_idx, "row_in_file": self._row_in_file}
+
+    def load_io_state(self, state):
+        self._file_idx, self._row_in_file = int(state["file_idx"]), int(state["row_in_file"])
+
+
+class MapDataset(DatasetBase):
+    def __init__(self, dataset, fn: Callable):
+        self.dataset, self.fn = dataset, fn
+
+    def __iter__(self):
+        for batch in self.dataset:
+            yield self.fn(batch)
+
+    def dump_io_state(self):
+        return self.dataset.dump_io_state()
+
+    def load_io_state(self, state):
+        self.dataset.load_io_state(state)
+
+
+class FilterDataset(MapDataset):
+    """Keep only the listed keys of every batch (or drop batches for which ``fn`` returns False)."""
+
+    def __init__(self, dataset, keys: Optional[List[str]] = None, fn: Optional[Callable] = None):
+        super().__init__(dataset, fn)
+        self.keys = keys
+
+    def __iter__(self):
+        for batch in self.dataset:
+            if self.fn is not None and not self.fn(batch):
+                continue
+            yield {k: batch[k] for k in self.keys} if self.keys else batch
+
+
+class PrefetchDataset(DatasetBase):
+    """Background thread that keeps ``depth`` batches ready (optionally already copied to a device on a side stream)."""
+
+    def __init__(self, dataset, depth: int = 2, device: Optional[str] = None):
+        self.dataset, self.depth, self.device = dataset, depth, device
+
+    def __iter__(self):
+        q: queue.Queue = queue.Queue(maxsize=self.depth)
+        done = object()
+
+        def work():
+            stream = torch.cuda.Stream() if self.device and str(self.device).startswith("cuda") else None
+            try:
+                for batch in self.dataset:
+                    if self.device:
+                        from ..utils.data_utils import copy_data_to_device
+                        if stream is not None:
+                            with torch.cuda.stream(stream):
+                                batch = copy_data_to_device(batch, self.device)
+                            stream.synchronize()
+                        else:
+                            batch = copy_data_to_device(batch, self.device)
+                    q.put(batch)
+            finally:
+                q.put(done)
+
+        threading.Thread(target=work, daemon=True).start()
+        while True:
+            item = q.get()
+            if item is done:
+                return
+            yield item
+
+    def dump_io_state(self):
+        return self.dataset.dump_io_state()
+
+    def load_io_state(self, state):
+        self.dataset.load_io_state(state)
+
+
+class StateDataset(DatasetBase):
+    """Remembers the source position every ``save_interval`` batches, so that a checkpoint taken between two snapshots
+    resumes from the last snapshot (``recis/io/state_dataset.py:118-137``)."""
+
+    def __init__(self, dataset, save_interval: int = 100):
+        self.dataset, self.save_interval = dataset, max(int(save_interval), 1)
+        self._snapshot = dataset.dump_io_state()
+        self._count = 0
+
+    def __iter__(self):
+        for batch in self.dataset:
+            self._count += 1
+            if self._count % self.save_interval == 0:
+                self._snapshot = self.dataset.dump_io_state()
+            yield batch
+
+    def dump_io_state(self):
+        return {"snapshot": self._snapshot, "count": self._count}
+
+    def load_io_state(self, state):
+        self._snapshot, self._count = state["snapshot"], int(state.get("count", 0))
+        self.dataset.load_io_state(self._snapshot)
+
+
+class WrapEndDataset(DatasetBase):
+    """Yields ``(stop_flag, batch)``; after the source ends it keeps yielding ``(True, last_batch)`` so that ranks whose data
+    ran out can keep taking part in collectives until every rank is done (``recis/io/wrap_end_dataset.py:38-79``)."""
+
+    def __init__(self, dataset):
+        self.dataset = dataset
+
+    def __iter__(self):
+        last = None
+        for batch in self.dataset:
+            last = batch
+            yield False, batch
+        while True:
+            yield True, last
+
+    def dump_io_state(self):
+        return self.dataset.dump_io_state()
+
+    def load_io_state(self, state):
+        self.dataset.load_io_state(state)

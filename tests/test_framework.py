@@ -1,0 +1,173 @@
+"""Trainer, checkpoint manager, hooks, metrics and datasets on CPU (DeepFM on synthetic data, 1 process)."""
+import os
+
+import pytest
+import torch
+
+from recis_b200.framework import Trainer, TrainingArguments
+from recis_b200.framework.metrics import add_metric, get_global_metrics
+from recis_b200.hooks import HashTableFilterHook, Hook, LoggerHook
+from recis_b200.io import (SparseFieldSpec, StateDataset, SyntheticDataset, SyntheticSpec, TensorDataset, WrapEndDataset)
+from recis_b200.metrics.auroc import AUROC
+from recis_b200.metrics.gauc import Gauc
+from recis_b200.models.deepfm import DeepFM
+from recis_b200.nn import filter_out_sparse_param
+from recis_b200.nn.modules.hashtable import HashtableRegister
+from recis_b200.optim import AdamWTF, SparseAdagrad
+from recis_b200.utils.parser import ArgumentParser
+
+
+def _spec(batch=64):
+    fields = [f"c{i}" for i in range(6)]
+    return fields, SyntheticSpec(batch=batch, dense_dim=13, label_rate=0.25, seed=0,
+                                 sparse=[SparseFieldSpec(f, zipf_a=1.1, id_bits=20, universe=2000, length="fixed", mean_len=1) for f in fields])
+
+
+def _build(tmp, steps, save_steps=5):
+    HashtableRegister().clear()
+    torch.manual_seed(0)
+    fields, spec = _spec()
+    model = DeepFM(fields, device="cpu", compute_dtype=torch.float32, hidden=(32, 16))
+    sparse_opt = SparseAdagrad(filter_out_sparse_param(model), lr=0.01)
+    dense_opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+    ds = WrapEndDataset(StateDataset(SyntheticDataset(spec, steps=steps), save_interval=1))
+
+    class Wrapped(torch.nn.Module):
+        def __init__(self, m):
+            super().__init__()
+            self.m = m
+
+        def forward(self, batch):
+            loss, logit = self.m(batch)
+            add_metric("mean_logit", logit.detach().mean())
+            return loss
+
+    args = TrainingArguments(output_dir=str(tmp), log_steps=2, train_steps=steps, save_steps=save_steps, max_to_keep=2)
+    return Trainer(model=Wrapped(model), args=args, train_dataset=ds, dense_optimizers=(dense_opt, None), sparse_optimizer=sparse_opt), model
+
+
+def test_trainer_trains_saves_and_resumes(tmp_path):
+    class Count(Hook):
+        n = 0
+        def after_step(self, metrics=None, global_step=0):
+            Count.n += 1
+            assert "loss" in metrics and "mean_logit" in metrics
+
+    trainer, model = _build(tmp_path, steps=12)
+    trainer.add_hook(Count())
+    trainer.train()
+    assert Count.n == 12
+    listing = open(tmp_path / "checkpoint").read().split()
+    assert listing == ["ckpt_10", "ckpt_12"]                      # retention keeps the newest two
+    assert not os.path.exists(tmp_path / "ckpt_5")
+    d = tmp_path / "ckpt_12"
+    for f in ("index", "tensorkey.json", "model.pt", "extra.pt", "io_state_0.pt", "io_state_count"):
+        assert os.path.exists(d / f), f
+    sizes = {n: t.impl.size() for n, t in model.embedding_engine.tables().items()}
+    w_ref = model.dnn.layers[0].weight.detach().clone()
+    # a fresh process-like restart resumes at step 12 with identical tables and dense weights
+    trainer2, model2 = _build(tmp_path, steps=14)
+    trainer2.restore()
+    assert int(trainer2._global_step) == 12
+    assert {n: t.impl.size() for n, t in model2.embedding_engine.tables().items()} == sizes
+    assert torch.equal(model2.dnn.layers[0].weight, w_ref)
+    assert trainer2.train_dataset.dataset.dataset.dump_io_state()["step"] == 12
+    trainer2.train(train_steps=2)
+    assert int(trainer2._global_step) == 14
+
+
+def test_deepfm_loss_decreases_on_cpu():
+    HashtableRegister().clear()
+    torch.manual_seed(0)
+    fields, spec = _spec(batch=256)
+    model = DeepFM(fields, device="cpu", compute_dtype=torch.float32, hidden=(64, 32))
+    sopt = SparseAdagrad(filter_out_sparse_param(model), lr=0.05)
+    dopt = AdamWTF(model.parameters(), lr=1e-2, weight_decay=0.0)
+    from recis_b200.io import make_batch
+    batch = make_batch(spec, 0)
+    losses = []
+    for _ in range(30):
+        loss, _ = model(batch)
+        dopt.zero_grad(); sopt.zero_grad(); loss.backward(); dopt.step(); sopt.step()
+        losses.append(float(loss))
+    assert losses[-1] < losses[0] * 0.8
+
+
+def test_auroc_matches_exact_and_gauc():
+    torch.manual_seed(0)
+    y = (torch.rand(5000) < 0.3).float()
+    p = (torch.rand(5000) * 0.6 + y * 0.3).clamp(0, 1)
+    m = AUROC(num_thresholds=400)
+    m.update(p[:2500], y[:2500]); m.update(p[2500:], y[2500:])
+    order = torch.argsort(p)
+    ranks = torch.empty_like(p); ranks[order] = torch.arange(1, 5001, dtype=torch.float32)
+    n1 = y.sum(); n0 = 5000 - n1
+    exact = (ranks[y == 1].sum() - n1 * (n1 + 1) / 2) / (n1 * n0)
+    assert abs(float(m.compute()) - float(exact)) < 5e-3
+    m.reset()
+    assert float(m.pos_hist.sum()) == 0
+    g = Gauc(dist_sync=False)
+    labels = torch.tensor([1.0, 0.0, 1.0, 0.0, 1.0, 1.0, 0.0])
+    preds = torch.tensor([0.9, 0.1, 0.2, 0.8, 0.5, 0.6, 0.4])
+    groups = torch.tensor([0, 0, 1, 1, 2, 2, 2])
+    batch, running = g(labels, preds, groups)
+    # group 0: auc 1 (2 samples), group 1: auc 0 (2), group 2: auc 1 (3) -> (2*1 + 2*0 + 3*1) / 7
+    assert abs(batch - 5.0 / 7.0) < 1e-9 and abs(running - batch) < 1e-12
+
+
+def test_datasets_state_and_parser(tmp_path):
+    _, spec = _spec(batch=8)
+    ds = SyntheticDataset(spec, steps=5)
+    it = iter(ds)
+    b0 = next(it); b1 = next(it)
+    state = ds.dump_io_state()
+    b2 = next(it)
+    ds2 = SyntheticDataset(spec, steps=5)
+    ds2.load_io_state(state)
+    c2 = next(iter(ds2))
+    assert torch.equal(b2["c0"].values(), c2["c0"].values()) and torch.equal(b2["dense"], c2["dense"])
+    assert not torch.equal(b0["c0"].values(), b1["c0"].values())
+    td = WrapEndDataset(TensorDataset({"x": torch.arange(10)}, batch_size=4))
+    flags = []
+    for i, (stop, batch) in enumerate(td):
+        flags.append(stop)
+        if i == 4:
+            break
+    assert flags == [False, False, False, True, True]
+    parser = ArgumentParser()
+    parser.add_arguments(TrainingArguments, dest="train")
+    ns = parser.parse_args(["--train.log_steps", "7", "--save_steps", "3", "--output_dir", "/tmp/x"])
+    assert ns.train.log_steps == 7 and ns.train.save_steps == 3 and ns.train.output_dir == "/tmp/x" and ns.train.max_to_keep == 5
+
+
+def test_orc_dataset_parquet(tmp_path):
+    pa = pytest.importorskip("pyarrow")
+    import pyarrow.parquet as pq
+    from recis_b200.io import OrcDataset
+    table = pa.table({"ids": [[1, 2], [], [3]], "user": ["a", "bb", "a"], "price": [1.0, 2.5, 3.0]})
+    path = str(tmp_path / "part-0.parquet")
+    pq.write_table(table, path)
+    ds = OrcDataset(batch_size=2)
+    ds.add_path(path)
+    ds.varlen_feature("ids")
+    ds.varlen_feature("user", hash_type="farm", hash_bucket=1000)
+    ds.fixedlen_feature("price", 0.0)
+    batches = list(ds)
+    assert len(batches) == 2
+    assert batches[0]["ids"].values().tolist() == [1, 2] and batches[0]["ids"].offsets()[0].tolist() == [0, 2, 2]
+    assert batches[0]["price"].tolist() == [[1.0], [2.5]]
+    u0, u1 = batches[0]["user"].values(), batches[1]["user"].values()
+    assert u0[0] == u1[0] and u0[0] != u0[1] and int(u0.max()) < 1000
+
+
+def test_filter_hook_in_loop():
+    HashtableRegister().clear()
+    from recis_b200.nn import HashTable
+    from recis_b200.nn.hashtable_hook import FilterHook
+    ht = HashTable([4], name="ttl_loop", device="cpu", filter_hook=FilterHook("GlobalStepFilter", {"filter_step": 3}))
+    hook = HashTableFilterHook(filter_interval=2, model=ht)
+    ht(torch.arange(50))
+    for step in range(8):
+        ht(torch.arange(5))
+        hook.after_step({}, step)
+    assert ht.impl.size() == 5 and hook.evicted == 45
