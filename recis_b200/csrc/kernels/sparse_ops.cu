@@ -19,6 +19,10 @@
 #include "../common/rb_launch.h"
 #include <cub/device/device_radix_sort.cuh>
 #include <cooperative_groups.h>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include "rb_noalloc.h"
 
 namespace cg = cooperative_groups;
 
@@ -674,3 +678,83 @@ void rb_sparse_apply(const int32_t* rows, const float* grads, int64_t n_max, con
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Allocation-free dedup + owner bucketing (declared in rb_noalloc.h).
+//
+// rb_dedup_partition above needs three scratch buffers (the hash set's keys and positions, and one slot index per id) which
+// its callers obtain from an allocator. Some callers cannot do that: code that runs while a CUDA graph is being captured, a
+// serving loop that must not touch cudaMalloc / the framework's caching allocator on its latency path, or a C host
+// program that links this library without any tensor framework. For them the same two kernels run on a scratch area that
+// lives in the library image itself: a file-scope __device__ array, present on every GPU that loads the library, for as long
+// as the process lives. The price is a fixed ceiling on the number of ids per call and no concurrency between calls.
+namespace {
+
+constexpr int64_t kNoAllocMaxIds = RB_NOALLOC_MAX_IDS;                 // ids per call
+constexpr int64_t kNoAllocMaxSlots = 2 * kNoAllocMaxIds;               // hash-set slots (power of two, load <= 0.5)
+constexpr size_t kNoAllocKeysBytes = sizeof(uint64_t) * kNoAllocMaxSlots;
+constexpr size_t kNoAllocPosBytes = ((sizeof(int32_t) * (kNoAllocMaxSlots + 1) + 255) / 256) * 256;
+constexpr size_t kNoAllocSlotBytes = sizeof(int32_t) * kNoAllocMaxIds;
+constexpr size_t kNoAllocBytes = kNoAllocKeysBytes + kNoAllocPosBytes + kNoAllocSlotBytes;   // about 7.3 MB
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+void* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;
+
+void noalloc_fail(char* err, size_t err_len, const char* msg) {
+  if (err && err_len) { std::strncpy(err, msg, err_len - 1); err[err_len - 1] = '\0'; }
+}
+
+}  // namespace
+
+extern "C" int rb_dedup_partition_noalloc(const int64_t* ids, int64_t n, int world, int32_t* counts, int32_t* offsets, int64_t* unique_ids,
+                                          int32_t* reverse, cudaStream_t st, char* err, size_t err_len) {
+  if (n < 0 || world < 1 || world > 1024) { noalloc_fail(err, err_len, "rb_dedup_partition_noalloc: n must be >= 0 and world in [1, 1024]"); return 1; }
+  if (n > kNoAllocMaxIds) {
+    char msg[192];
+    std::snprintf(msg, sizeof(msg), "rb_dedup_partition_noalloc: %lld ids exceed the built-in scratch limit of %lld ids per call",
+                  (long long)n, (long long)kNoAllocMaxIds);
+    noalloc_fail(err, err_len, msg);
+    return 2;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) {
+    noalloc_fail(err, err_len, "rb_dedup_partition_noalloc: no current CUDA device (or device index >= 64)");
+    return 3;
+  }
+  void* base = nullptr;
+  {
+    // Set-up, once per device, with that device current: the array's name is only a host-side handle; the device address that
+    // a kernel may dereference comes from cudaGetSymbolAddress.
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        noalloc_fail(err, err_len, cudaGetErrorString(e));
+        return 4;
+      }
+      g_noalloc_ptr[dev] = p;
+    }
+    base = g_noalloc_ptr[dev];
+  }
+  if (cudaMemsetAsync(counts, 0, sizeof(int32_t) * world, st) != cudaSuccess) { noalloc_fail(err, err_len, "memset of counts failed"); return 5; }
+  if (n == 0) { cudaMemsetAsync(offsets, 0, sizeof(int32_t) * (world + 1), st); return 0; }
+  int64_t cap = 64;
+  while (cap < 2 * n) cap <<= 1;                                        // <= kNoAllocMaxSlots because n <= kNoAllocMaxIds
+  uint64_t* set_keys = reinterpret_cast<uint64_t*>(base);
+  int32_t* set_pos = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(base) + kNoAllocKeysBytes);
+  int32_t* slot = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(base) + kNoAllocKeysBytes + kNoAllocPosBytes);
+  // the array keeps whatever the previous call left behind: everything that must start "empty" is reset here
+  cudaMemsetAsync(set_keys, 0xFF, sizeof(uint64_t) * cap, st);
+  cudaMemsetAsync(set_pos + cap, 0xFF, sizeof(int32_t), st);
+  const int g = grid_stride_blocks(n);
+  dedup_claim_kernel<<<g, kThreads, 2 * world * sizeof(int32_t), st>>>(ids, n, world, set_keys, set_pos, (uint64_t)cap - 1, slot, counts);
+  dedup_assign_kernel<<<g, kThreads, (world + 1) * sizeof(int32_t), st>>>(ids, n, world, set_pos, slot, counts, offsets, unique_ids, reverse);
+  rb::note_launch(2);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { noalloc_fail(err, err_len, cudaGetErrorString(e)); return 6; }
+  return 0;
+}
