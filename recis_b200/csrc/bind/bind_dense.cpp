@@ -121,6 +121,54 @@ Tensor cast_pad_bf16(const Tensor& src, int64_t rows_p, int64_t cols_p) {
   return dst;
 }
 
+inline int64_t pad8(int64_t n) { return (n + 7) / 8 * 8; }
+
+// Whole MLP forward in one call: per layer cast+pad the fp32 master weight to bf16, then GEMM with fused bias (+ReLU).
+// x: [M, K0] any float dtype (cast / zero-padded to bf16 [M, pad8(K0)] here). Returns (padded bf16 input, layer outputs, bf16 weights).
+std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_forward(const Tensor& x_in, const std::vector<Tensor>& weights,
+                                                                         const std::vector<Tensor>& biases, const std::vector<bool>& relu) {
+  TORCH_CHECK(x_in.is_cuda() && x_in.dim() == 2 && weights.size() == biases.size() && weights.size() == relu.size());
+  c10::cuda::CUDAGuard g(x_in.device());
+  const int64_t K0p = pad8(weights[0].size(1));
+  Tensor x = x_in.scalar_type() == torch::kBFloat16 ? x_in : x_in.to(torch::kBFloat16);
+  if (x.size(1) != K0p) x = torch::constant_pad_nd(x, {0, K0p - x.size(1)});
+  x = x.contiguous();
+  std::vector<Tensor> ys, wbs;
+  Tensor h = x;
+  for (size_t l = 0; l < weights.size(); ++l) {
+    const int64_t N = weights[l].size(0), K = weights[l].size(1), Np = pad8(N), Kp = pad8(K);
+    TORCH_CHECK(h.size(1) == Kp, "layer ", l, ": input width ", h.size(1), " does not match the padded weight width ", Kp);
+    Tensor wb = cast_pad_bf16(weights[l], Np, Kp);
+    Tensor bp = Np == N ? biases[l] : torch::constant_pad_nd(biases[l], {0, Np - N});
+    h = gemm_bf16(h, wb, bp, relu[l], false, false, false, c10::nullopt);
+    ys.push_back(h); wbs.push_back(wb);
+  }
+  return {x, ys, wbs};
+}
+
+// Whole MLP backward in one call. dout: bf16 [M, pad8(N_last)]. Returns (dx or undefined, weight grads fp32 [N, K], bias grads fp32 [N]).
+std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_backward(const Tensor& dout_in, const Tensor& x, const std::vector<Tensor>& ys,
+                                                                          const std::vector<Tensor>& wbs, const std::vector<bool>& relu,
+                                                                          const std::vector<std::vector<int64_t>>& shapes, bool need_dx) {
+  c10::cuda::CUDAGuard g(x.device());
+  const int L = (int)ys.size();
+  std::vector<Tensor> dws(L), dbs(L);
+  Tensor dout = dout_in.contiguous();
+  Tensor dx;
+  for (int l = L - 1; l >= 0; --l) {
+    auto [dy, db] = relu_bwd_bias(ys[l], dout, relu[l]);
+    const Tensor& h_in = l == 0 ? x : ys[l - 1];
+    Tensor dw = gemm_bf16(dy, h_in, c10::nullopt, false, true, true, true, c10::nullopt);   // dy^T . h  (both MN-major, split-K)
+    dws[l] = dw.narrow(0, 0, shapes[l][0]).narrow(1, 0, shapes[l][1]);
+    dbs[l] = db.narrow(0, 0, shapes[l][0]);
+    if (l > 0 || need_dx) {
+      dout = gemm_bf16(dy, wbs[l], c10::nullopt, false, false, true, false, c10::nullopt);    // dy . W  (W read MN-major)
+      if (l == 0) dx = dout;
+    }
+  }
+  return {dx, dws, dbs};
+}
+
 int64_t dense_status(const std::string& device) { return status_word(torch::Device(device)).item<int64_t>(); }
 
 }  // namespace
@@ -129,6 +177,8 @@ void init_dense(py::module& m) {
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("bias") = py::none(), py::arg("relu") = false,
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none());
   m.def("dense_status", &dense_status);
+  m.def("mlp_forward", &mlp_forward);
+  m.def("mlp_backward", &mlp_backward);
   m.def("dot_interaction_fwd", &dot_interaction_fwd);
   m.def("dot_interaction_bwd", &dot_interaction_bwd);
   m.def("fm_fwd", &fm_fwd);

@@ -79,12 +79,49 @@ void EmbeddingStore::refresh_bounds() {
   if (rows_upper_ < 0) rows_upper_ = 0;
   bump_upper_ = c[RB_CTR_BUMP];
   index_upper_ = c[RB_CTR_LIVE] + c[RB_CTR_TOMBSTONES] + c[RB_CTR_PROBATION];
+  absorbed_issued_ = issued_total_;
   TORCH_CHECK((c[RB_CTR_STATUS] & 3) == 0, "embedding store reported status ", c[RB_CTR_STATUS],
               " (1 = row arena exhausted, 2 = index full); raise the capacity");
 }
 
+// Asynchronous counter mirror: after every lookup-or-insert the 64-byte counter block is copied to pinned host memory on the
+// same stream. ensure_room() takes the newest copy that has already landed (cudaEventQuery, never a wait) as the truth and
+// only adds the ids issued since then, so the pessimistic bound is at most a step or two ahead of reality.
+void EmbeddingStore::post_mirror(int64_t n_issued) {
+  issued_total_ += n_issued;
+  if (!device_.is_cuda()) return;
+  if (mirror_host_ == nullptr) {
+    if (cudaHostAlloc(reinterpret_cast<void**>(&mirror_host_), sizeof(int64_t) * RB_CTR_COUNT * kMirror, cudaHostAllocDefault) != cudaSuccess) {
+      mirror_host_ = nullptr;
+      return;
+    }
+    for (int i = 0; i < kMirror; ++i) { cudaEventCreateWithFlags(&mirror_ev_[i], cudaEventDisableTiming); mirror_issued_[i] = -1; }
+  }
+  const int slot = (int)(mirror_head_++ % kMirror);
+  auto st = at::cuda::getCurrentCUDAStream();
+  cudaMemcpyAsync(mirror_host_ + slot * RB_CTR_COUNT, ctr_.data_ptr<int64_t>(), sizeof(int64_t) * RB_CTR_COUNT, cudaMemcpyDeviceToHost, st);
+  cudaEventRecord(mirror_ev_[slot], st);
+  mirror_issued_[slot] = issued_total_;
+}
+
+void EmbeddingStore::absorb_mirror() {
+  if (mirror_host_ == nullptr) return;
+  for (int back = 1; back <= kMirror && back <= (int)mirror_head_; ++back) {
+    const int slot = (int)((mirror_head_ - back) % kMirror);
+    if (mirror_issued_[slot] < 0 || mirror_issued_[slot] <= absorbed_issued_) break;
+    if (cudaEventQuery(mirror_ev_[slot]) != cudaSuccess) continue;
+    const int64_t* c = mirror_host_ + slot * RB_CTR_COUNT;
+    const int64_t pending = issued_total_ - mirror_issued_[slot];
+    rows_upper_ = std::max<int64_t>(c[RB_CTR_BUMP] - c[RB_CTR_FREE_TOP], 0) + pending;
+    index_upper_ = c[RB_CTR_LIVE] + c[RB_CTR_TOMBSTONES] + c[RB_CTR_PROBATION] + pending;
+    absorbed_issued_ = mirror_issued_[slot];
+    break;
+  }
+}
+
 void EmbeddingStore::ensure_room(int64_t n_incoming) {
   // Pessimistic: every incoming id may be new. Only when the bound crosses the capacity do we look at the truth.
+  absorb_mirror();
   if (rows_upper_ + n_incoming > cap_rows_ || index_upper_ + n_incoming > (int64_t)(0.65 * keys_.numel())) {
     refresh_bounds();
     if (rows_upper_ + n_incoming > cap_rows_) {
@@ -157,6 +194,7 @@ torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::op
                                new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr<float>(), (int)dim_, init_, ls,
                                sd, (int)admit_threshold);
   }
+  post_mirror(n);
   return rows_out;
 }
 
@@ -225,6 +263,7 @@ void EmbeddingStore::clear() {
   for (auto& kv : slots_) kv.second.fill_(slot_fill_[kv.first]);
   if (last_seen_.defined()) last_seen_.zero_();
   rows_upper_ = bump_upper_ = index_upper_ = 0;
+  absorbed_issued_ = issued_total_;
 }
 
 int64_t EmbeddingStore::size() const { return counters()[RB_CTR_LIVE]; }

@@ -51,6 +51,14 @@ class EmbeddingStore {
   std::map<std::string, double> slot_fill_;
   std::vector<std::string> slot_order_;
   int64_t rows_upper_ = 0, bump_upper_ = 0, index_upper_ = 0;
+  // asynchronous counter mirror (pinned host copies of the device counters, see store.cpp)
+  static constexpr int kMirror = 8;
+  void post_mirror(int64_t n_issued);
+  void absorb_mirror();
+  int64_t* mirror_host_ = nullptr;
+  cudaEvent_t mirror_ev_[kMirror];
+  int64_t mirror_issued_[kMirror];
+  int64_t mirror_head_ = 0, issued_total_ = 0, absorbed_issued_ = 0;
 };
 
 }  // namespace rbx

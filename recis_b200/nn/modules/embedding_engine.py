@@ -67,6 +67,7 @@ class EmbeddingEngine(nn.Module):
         self._emb_opts = emb_options
         self._interleave = interleave
         self.packed = {}
+        self._desc_ring = {}
         shared_to_ht = {}
         capacity = defaultdict(int)
         for fea_name, opt in emb_options.items():
@@ -148,13 +149,24 @@ class EmbeddingEngine(nn.Module):
         for a, b in zip(nnz, segs):
             nnz_prefix.append(nnz_prefix[-1] + a)
             seg_prefix.append(seg_prefix[-1] + b)
-        desc = torch.tensor(
-            [[f["ids"].data_ptr() for f in feats] + [0], nnz_prefix,
-             [f["offsets"].data_ptr() for f in feats] + [0], seg_prefix], dtype=torch.int64)
-        tidx = torch.tensor([f["child"] for f in feats], dtype=torch.int64)
+        rows = [[f["ids"].data_ptr() for f in feats] + [0], nnz_prefix, [f["offsets"].data_ptr() for f in feats] + [0], seg_prefix,
+                [f["child"] for f in feats] + [0]]
         if device.type == "cuda":
-            desc = desc.pin_memory().to(device, non_blocking=True)
-            tidx = tidx.pin_memory().to(device, non_blocking=True)
+            # descriptor table: a small ring of pinned staging buffers (no pinned allocation per step), copied asynchronously
+            ring = self._desc_ring.setdefault((F, device), dict(bufs=[torch.empty(5, F + 1, dtype=torch.int64).pin_memory() for _ in range(4)],
+                                                                evs=[None] * 4, head=0))
+            k = ring["head"] % 4
+            ring["head"] += 1
+            if ring["evs"][k] is not None:
+                ring["evs"][k].synchronize()          # the copy issued four steps ago has long finished; this never waits in practice
+            ring["bufs"][k].copy_(torch.tensor(rows, dtype=torch.int64))
+            both = ring["bufs"][k].to(device, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            ring["evs"][k] = ev
+        else:
+            both = torch.tensor(rows, dtype=torch.int64)
+        desc, tidx = both[:4], both[4, :F]
         ids, offsets = native().encode_merge(desc, tidx, F, nnz_prefix[-1], seg_prefix[-1], True)
         weights = None
         if any(f["weight"] is not None for f in feats):

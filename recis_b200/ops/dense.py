@@ -77,14 +77,47 @@ class Linear(nn.Module):
         return F.relu(y) if self.act else y
 
 
+class _MLPFn(torch.autograd.Function):
+    """All layers of an MLP in two native calls (forward, backward) instead of several per layer: the dense tower of a
+    recommendation model is many small GEMMs, and the host-side cost of issuing them one by one is comparable to their GPU time."""
+
+    @staticmethod
+    def forward(ctx, x, relu, *params):
+        n = len(params) // 2
+        weights, biases = list(params[:n]), list(params[n:])
+        xp, ys, wbs = native().mlp_forward(x, weights, biases, list(relu))
+        ctx.relu, ctx.shapes, ctx.n = list(relu), [list(w.shape) for w in weights], n
+        ctx.x_shape, ctx.x_dtype = x.shape, x.dtype
+        ctx.save_for_backward(xp, *ys, *wbs)
+        return ys[-1]
+
+    @staticmethod
+    def backward(ctx, dout):
+        saved = ctx.saved_tensors
+        n = ctx.n
+        xp, ys, wbs = saved[0], list(saved[1:1 + n]), list(saved[1 + n:1 + 2 * n])
+        dx, dws, dbs = native().mlp_backward(dout.to(torch.bfloat16), xp, ys, wbs, ctx.relu, ctx.shapes, ctx.needs_input_grad[0])
+        if dx is not None and ctx.needs_input_grad[0]:
+            dx = dx[:, :ctx.x_shape[1]].to(ctx.x_dtype)
+        else:
+            dx = None
+        return (dx, None, *dws, *dbs)
+
+
 class MLP(nn.Module):
     def __init__(self, dims: Sequence[int], final_act: bool = False, dtype=torch.bfloat16):
         super().__init__()
+        self.dtype = dtype
         self.layers = nn.ModuleList(
             [Linear(dims[i], dims[i + 1], act=(i < len(dims) - 2) or final_act, dtype=dtype) for i in range(len(dims) - 1)])
 
     def forward(self, x):
         n = len(self.layers)
+        if x.is_cuda and self.dtype == torch.bfloat16:
+            relu = tuple(bool(l.act) for l in self.layers)
+            y = _MLPFn.apply(x, relu, *[l.weight for l in self.layers], *[l.bias for l in self.layers])
+            out = self.layers[-1].out_features
+            return y if y.shape[1] == out else y[:, :out]
         for i, layer in enumerate(self.layers):
             x = layer(x, keep_pad=i < n - 1)
         return x
