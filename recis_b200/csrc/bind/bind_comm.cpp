@@ -121,5 +121,8 @@ void init_comm(py::module& m) {
   m.def("comm_push_emb", &comm_push_emb);
   m.def("comm_owner_reduce", &comm_owner_reduce);
   m.def("comm_allreduce_slice", &comm_allreduce_slice);
+  m.def("comm_copy", [](int64_t dst, int64_t src, int64_t nbytes, int64_t blocks) {
+    rb_comm_copy(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), nbytes, (int)blocks, cur_stream());
+  });
   m.attr("MAX_PEERS") = RB_MAX_PEERS;
 }

@@ -120,23 +120,34 @@ pull_ids_kernel(RbPeers peer_ids, RbPeers peer_offsets, int me, int world, int64
 }
 
 // Owner: store the embedding row of incoming id j into its requester's unique-embedding buffer.
+// A work item is (k, column): it serves the k-th id of EVERY requester, so all peer links carry traffic for the whole
+// kernel (instead of one requester after the other) and each thread has up to `world` independent load/store pairs in flight.
 __global__ void __launch_bounds__(kThreads)
 push_emb_kernel(const float* __restrict__ emb, const int32_t* __restrict__ rows_in, const int32_t* __restrict__ prefix_in,
                 RbPeers peer_uemb, int me, int world, int D) {
   __shared__ int32_t prefix[RB_MAX_PEERS + 1];
   __shared__ int32_t dst_off[RB_MAX_PEERS];
+  __shared__ int32_t max_cnt;
   if (threadIdx.x <= world) prefix[threadIdx.x] = prefix_in[threadIdx.x];
   if (threadIdx.x < world) dst_off[threadIdx.x] = prefix_in[world + 1 + threadIdx.x];
   __syncthreads();
-  const int64_t n_in = prefix[world];
+  if (threadIdx.x == 0) {
+    int32_t m = 0;
+    for (int r = 0; r < world; ++r) m = max(m, prefix[r + 1] - prefix[r]);
+    max_cnt = m;
+  }
+  __syncthreads();
   const int q = D >> 2;                        // D % 4 == 0 is required by the fused path
-  const int64_t total = n_in * q;
+  const int64_t total = (int64_t)max_cnt * q;
   for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t j = w / q; const int c = (int)(w - j * q);
-    const int r = find_src(prefix, world, j);
-    const int32_t row = rows_in[j];
-    float* dst = reinterpret_cast<float*>(peer_uemb.p[r]) + ((int64_t)dst_off[r] + (j - prefix[r])) * D + c * 4;
-    st_f4(dst, row >= 0 ? ld_f4(emb + (int64_t)row * D + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f));
+    const int64_t k = w / q; const int c = (int)(w - k * q);
+    for (int r0 = 0; r0 < world; ++r0) {
+      const int r = (r0 + me + 1) % world;    // start with the right neighbour: ranks do not all hammer rank 0 first
+      if (k >= prefix[r + 1] - prefix[r]) continue;
+      const int32_t row = rows_in[prefix[r] + k];
+      float* dst = reinterpret_cast<float*>(peer_uemb.p[r]) + ((int64_t)dst_off[r] + k) * D + c * 4;
+      st_f4(dst, row >= 0 ? ld_f4(emb + (int64_t)row * D + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f));
+    }
   }
 }
 
@@ -162,6 +173,32 @@ __device__ __forceinline__ void opt_update_f4(const RbOpt& o, int64_t off, float
     w.z = w.z * o.decay - o.lr * g.z / (sqrtf(a.z) + o.eps);
     w.w = w.w * o.decay - o.lr * g.w / (sqrtf(a.w) + o.eps);
     st_f4(o.s1 + off, a);
+  } else {
+    w.x = w.x * o.decay - o.lr * g.x; w.y = w.y * o.decay - o.lr * g.y;
+    w.z = w.z * o.decay - o.lr * g.z; w.w = w.w * o.decay - o.lr * g.w;
+  }
+  st_f4(o.w + off, w);
+}
+
+__device__ __forceinline__ void opt_update_pre_f4(const RbOpt& o, int64_t off, float4 g, float4 w, float4 m, float4 v) {
+  const float gs = o.grad_scale;
+  g.x *= gs; g.y *= gs; g.z *= gs; g.w *= gs;
+  if (o.kind == RB_OPT_ADAM) {
+    const float b1 = o.beta1, b2 = o.beta2, c1 = 1.f - o.beta1, c2 = 1.f - o.beta2;
+    m.x = b1 * m.x + c1 * g.x; m.y = b1 * m.y + c1 * g.y; m.z = b1 * m.z + c1 * g.z; m.w = b1 * m.w + c1 * g.w;
+    v.x = b2 * v.x + c2 * g.x * g.x; v.y = b2 * v.y + c2 * g.y * g.y; v.z = b2 * v.z + c2 * g.z * g.z; v.w = b2 * v.w + c2 * g.w * g.w;
+    w.x = w.x * o.decay + o.alpha * m.x / (sqrtf(v.x) + o.eps);
+    w.y = w.y * o.decay + o.alpha * m.y / (sqrtf(v.y) + o.eps);
+    w.z = w.z * o.decay + o.alpha * m.z / (sqrtf(v.z) + o.eps);
+    w.w = w.w * o.decay + o.alpha * m.w / (sqrtf(v.w) + o.eps);
+    st_f4(o.s1 + off, m); st_f4(o.s2 + off, v);
+  } else if (o.kind == RB_OPT_ADAGRAD) {
+    m.x += g.x * g.x; m.y += g.y * g.y; m.z += g.z * g.z; m.w += g.w * g.w;
+    w.x = w.x * o.decay - o.lr * g.x / (sqrtf(m.x) + o.eps);
+    w.y = w.y * o.decay - o.lr * g.y / (sqrtf(m.y) + o.eps);
+    w.z = w.z * o.decay - o.lr * g.z / (sqrtf(m.z) + o.eps);
+    w.w = w.w * o.decay - o.lr * g.w / (sqrtf(m.w) + o.eps);
+    st_f4(o.s1 + off, m);
   } else {
     w.x = w.x * o.decay - o.lr * g.x; w.y = w.y * o.decay - o.lr * g.y;
     w.z = w.z * o.decay - o.lr * g.z; w.w = w.w * o.decay - o.lr * g.w;
@@ -211,13 +248,24 @@ owner_reduce_kernel(const int32_t* __restrict__ rows_in, const int32_t* __restri
       if (!apply && c == 0) out_rows[j0] = -1;
       continue;
     }
+    // 1. the row's optimizer state is requested first: those HBM loads overlap the NVLink loads below
+    const int64_t off = (int64_t)row * D + c * 4;
+    float4 sw = make_float4(0.f, 0.f, 0.f, 0.f), s1v = sw, s2v = sw;
+    if (apply) {
+      sw = ld_f4(opt.w + off);
+      if (opt.kind != RB_OPT_SGD) s1v = ld_f4(opt.s1 + off);
+      if (opt.kind == RB_OPT_ADAM) s2v = ld_f4(opt.s2 + off);
+    }
+    // 2. contributions: one per requester that asked for this id; almost always a single one
     int32_t chain[RB_MAX_PEERS];
     int cnt = 0;
     for (int32_t j = (int32_t)j0; j >= 0 && cnt < RB_MAX_PEERS; j = next[j]) chain[cnt++] = j;
-    for (int a = 1; a < cnt; ++a) {                      // insertion sort: ascending incoming index
-      const int32_t v = chain[a]; int b = a - 1;
-      while (b >= 0 && chain[b] > v) { chain[b + 1] = chain[b]; --b; }
-      chain[b + 1] = v;
+    if (cnt > 2) {                                         // a + b is order independent; three or more are summed in index order
+      for (int a = 1; a < cnt; ++a) {
+        const int32_t v = chain[a]; int b = a - 1;
+        while (b >= 0 && chain[b] > v) { chain[b + 1] = chain[b]; --b; }
+        chain[b + 1] = v;
+      }
     }
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int a = 0; a < cnt; ++a) {
@@ -228,7 +276,7 @@ owner_reduce_kernel(const int32_t* __restrict__ rows_in, const int32_t* __restri
     }
     if (mean_by_id && cnt > 1) { const float s = 1.f / (float)cnt; acc.x *= s; acc.y *= s; acc.z *= s; acc.w *= s; }
     if (apply) {
-      opt_update_f4(opt, (int64_t)row * D + c * 4, acc);
+      opt_update_pre_f4(opt, off, acc, sw, s1v, s2v);
     } else {
       if (c == 0) out_rows[j0] = row;
       const float gs = opt.grad_scale;
@@ -302,3 +350,16 @@ void rb_comm_allreduce_slice(RbPeers bufs, int me, int world, int64_t n_padded, 
 }
 
 }  // extern "C"
+
+// Plain streaming copy between two device pointers (either may be a peer mapping): the microbenchmark that measures what
+// NVLink delivers to ordinary loads / stores issued from a kernel.
+namespace {
+__global__ void __launch_bounds__(256) peer_copy_kernel(float4* __restrict__ dst, const float4* __restrict__ src, int64_t n4) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+}  // namespace
+
+extern "C" void rb_comm_copy(void* dst, const void* src, int64_t nbytes, int blocks, cudaStream_t st) {
+  peer_copy_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<float4*>(dst), reinterpret_cast<const float4*>(src), nbytes / 16);
+  rb::note_launch();
+}

@@ -31,6 +31,7 @@ void rb_comm_allreduce_slice(RbPeers bufs, int me, int world, int64_t n_padded, 
 void rb_sort_pairs_i32(const int32_t* keys_in, int32_t* keys_out, const int32_t* vals_in, int32_t* vals_out, int64_t n, int key_bits,
                        void* temp, size_t temp_bytes, cudaStream_t st);
 void rb_iota_i32(int32_t* out, int64_t n, cudaStream_t st);
+void rb_comm_copy(void* dst, const void* src, int64_t nbytes, int blocks, cudaStream_t st);
 
 #ifdef __cplusplus
 }

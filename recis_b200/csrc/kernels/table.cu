@@ -38,60 +38,89 @@ __device__ __forceinline__ int32_t alloc_row(const RbTable& t, uint64_t key, int
 }
 
 // Find `key`, or claim an empty slot for it. Returns the slot, or -1.
+// Row tickets for newly claimed keys are handed out once per block (ballot + one global atomic per block): a step that
+// inserts a million new ids would otherwise serialise tens of thousands of atomics on the single ticket counter.
 __global__ void __launch_bounds__(kThreads)
 table_claim_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, const int32_t* __restrict__ n_dev,
                    int32_t* __restrict__ slot_out, int32_t* __restrict__ new_rows, int64_t* __restrict__ new_keys,
                    int admit_threshold, int insert) {
+  __shared__ int32_t warp_cnt[kThreads / 32];
+  __shared__ unsigned long long block_base;
   const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    const uint64_t key = (uint64_t)ids[i];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x; i0 < n; i0 += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i = i0 + threadIdx.x;
     int32_t slot = -1;
-    if (key < kErasedKey) {
-      uint64_t h = mix64(key) & t.mask;
-      for (uint32_t probe = 0; probe < kMaxProbe; ++probe, h = (h + 1) & t.mask) {
-        uint64_t k = *reinterpret_cast<volatile uint64_t*>(&t.keys[h]);
-        bool won = false;
-        if (k == kEmptyKey) {
-          if (!insert) break;
-          k = atomicCAS(reinterpret_cast<unsigned long long*>(&t.keys[h]), (unsigned long long)kEmptyKey, (unsigned long long)key);
-          won = (k == kEmptyKey);
-          if (won) k = key;
-        }
-        if (k != key) {
-          if (probe + 1 == kMaxProbe || probe >= t.mask) { set_status(&t.ctr[RB_CTR_STATUS], kStatusIndexFull); break; }
-          continue;
-        }
-        slot = (int32_t)h;
-        if (won) {
-          if (admit_threshold <= 1) {
-            const int32_t row = alloc_row(t, key, new_rows, new_keys);
-            *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = row >= 0 ? row : -1;
-          } else {
-            *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = -2;  // probation, seen once
-            atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_PROBATION]), 1ull);
+    bool need_row = false;
+    uint64_t key = kEmptyKey;
+    uint64_t h = 0;
+    if (i < n) {
+      key = (uint64_t)ids[i];
+      if (key < kErasedKey) {
+        h = mix64(key) & t.mask;
+        for (uint32_t probe = 0; probe < kMaxProbe; ++probe, h = (h + 1) & t.mask) {
+          uint64_t k = *reinterpret_cast<volatile uint64_t*>(&t.keys[h]);
+          bool won = false;
+          if (k == kEmptyKey) {
+            if (!insert) break;
+            k = atomicCAS(reinterpret_cast<unsigned long long*>(&t.keys[h]), (unsigned long long)kEmptyKey, (unsigned long long)key);
+            won = (k == kEmptyKey);
+            if (won) k = key;
           }
-        } else if (insert && admit_threshold > 1) {
-          // key exists; if it is on probation, count this occurrence and admit at the threshold.
-          for (int spin = 0; spin < 64; ++spin) {
-            const int32_t v = *reinterpret_cast<volatile int32_t*>(&t.rows[h]);
-            if (v >= -1) break;            // admitted, or another thread is admitting it right now
-            const int32_t seen = -1 - v;   // occurrences so far
-            if (seen + 1 >= admit_threshold) {
-              if (atomicCAS(&t.rows[h], v, kRowPending) == v) {
-                const int32_t row = alloc_row(t, key, new_rows, new_keys);
-                *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = row >= 0 ? row : -1;
-                atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_PROBATION]), (unsigned long long)(-1ll));
+          if (k != key) {
+            if (probe + 1 == kMaxProbe || probe >= t.mask) { set_status(&t.ctr[RB_CTR_STATUS], kStatusIndexFull); break; }
+            continue;
+          }
+          slot = (int32_t)h;
+          if (won) {
+            if (admit_threshold <= 1) {
+              need_row = true;                                       // ticket comes from the block-wide hand-out below
+            } else {
+              *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = -2;  // probation, seen once
+              atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_PROBATION]), 1ull);
+            }
+          } else if (insert && admit_threshold > 1) {
+            // key exists; if it is on probation, count this occurrence and admit at the threshold.
+            for (int spin = 0; spin < 64; ++spin) {
+              const int32_t v = *reinterpret_cast<volatile int32_t*>(&t.rows[h]);
+              if (v >= -1) break;            // admitted, or another thread is admitting it right now
+              const int32_t seen = -1 - v;   // occurrences so far
+              if (seen + 1 >= admit_threshold) {
+                if (atomicCAS(&t.rows[h], v, kRowPending) == v) {
+                  const int32_t row = alloc_row(t, key, new_rows, new_keys);
+                  *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = row >= 0 ? row : -1;
+                  atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_PROBATION]), (unsigned long long)(-1ll));
+                  break;
+                }
+              } else if (atomicCAS(&t.rows[h], v, v - 1) == v) {
                 break;
               }
-            } else if (atomicCAS(&t.rows[h], v, v - 1) == v) {
-              break;
             }
           }
+          break;
         }
-        break;
       }
+      slot_out[i] = slot;
     }
-    slot_out[i] = slot;
+    // ---- block-wide ticket hand-out
+    const unsigned ballot = __ballot_sync(0xffffffffu, need_row);
+    if (lane == 0) warp_cnt[warp] = __popc(ballot);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int total = 0;
+      for (int wv = 0; wv < kThreads / 32; ++wv) { const int cnt = warp_cnt[wv]; warp_cnt[wv] = total; total += cnt; }
+      block_base = total ? atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_NEW]), (unsigned long long)total) : 0ull;
+    }
+    __syncthreads();
+    if (need_row) {
+      const int64_t ticket = (int64_t)block_base + warp_cnt[warp] + __popc(ballot & ((1u << lane) - 1u));
+      const int64_t free_top = t.ctr[RB_CTR_FREE_TOP], bump = t.ctr[RB_CTR_BUMP];
+      int64_t row = ticket < free_top ? (int64_t)t.free_list[free_top - 1 - ticket] : bump + (ticket - free_top);
+      if (row >= t.cap_rows) { set_status(&t.ctr[RB_CTR_STATUS], kStatusRowsExhausted); row = -1; }
+      new_rows[ticket] = (int32_t)row; new_keys[ticket] = (int64_t)key;
+      *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = (int32_t)row;
+    }
+    __syncthreads();
   }
 }
 
