@@ -80,9 +80,9 @@ void comm_push_emb(const Tensor& emb, const Tensor& rows_in, const Tensor& prefi
 }
 
 // apply: update rows of (w, s1, s2) in place. Otherwise returns (rows [n_in_max] with -1 holes, grads [n_in_max, D]).
-std::tuple<Tensor, Tensor> comm_owner_reduce(const Tensor& rows_in, Tensor head, const Tensor& prefix, const std::vector<int64_t>& peer_gu, int64_t me, int64_t D, bool mean_by_id, bool apply,
+std::tuple<Tensor, Tensor> comm_owner_reduce(const Tensor& rows_in, Tensor head, const Tensor& prefix, const Tensor& g_in, int64_t world, int64_t D, bool mean_by_id, bool apply,
                                              int64_t kind, double lr, double beta1, double beta2, double eps, double decay, double alpha,
-                                             double grad_scale, OptT w, OptT s1, OptT s2, int64_t n_in_hint) {
+                                             double grad_scale, OptT w, OptT s1, OptT s2, int64_t n_in_hint, int64_t unroll) {
   RbOpt o;
   o.kind = (int)kind; o.lr = (float)lr; o.beta1 = (float)beta1; o.beta2 = (float)beta2; o.eps = (float)eps; o.decay = (float)decay;
   o.alpha = (float)alpha; o.grad_scale = (float)grad_scale;
@@ -99,10 +99,35 @@ std::tuple<Tensor, Tensor> comm_owner_reduce(const Tensor& rows_in, Tensor head,
     TORCH_CHECK(o.w != nullptr, "apply needs the weight slab");
   }
   rb_comm_owner_reduce(rows_in.data_ptr<int32_t>(), head.data_ptr<int32_t>(), next.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(),
-                       peers_of(peer_gu), (int)me, (int)peer_gu.size(), (int)D, mean_by_id, apply, o,
+                       g_in.data_ptr<float>(), (int)world, (int)D, mean_by_id, apply, o,
                        apply ? nullptr : out_rows.data_ptr<int32_t>(), apply ? nullptr : out_grads.data_ptr<float>(), n_in_hint,
-                       cur_stream());
+                       (int)unroll, cur_stream());
   return {out_rows, out_grads};
+}
+
+// Requester side of the backward exchange: reduce the pooled gradient to one gradient per unique id and store each of
+// them straight into the window of the rank that owns the id (peer stores). offsets = this rank's bucket boundaries
+// [world+1]; meta = the tensor written by comm_pull_ids (the destination bases sit at meta[2*world+1 ..]).
+void comm_grad_reduce_push(const Tensor& grad_out, const Tensor& gsrc, const Tensor& gscale, const Tensor& csr_u, const Tensor& csr_elem,
+                           const Tensor& start, int64_t D, const Tensor& offsets, const Tensor& meta,
+                           const std::vector<int64_t>& peer_gin, int64_t cap_rows) {
+  TORCH_CHECK(grad_out.is_cuda() && grad_out.is_contiguous() && grad_out.scalar_type() == torch::kFloat32, "grad_out must be contiguous fp32 on CUDA");
+  TORCH_CHECK(D % 4 == 0 && D <= 512, "the fused exchange needs an embedding width that is a multiple of 4 and at most 512");
+  const int64_t n = csr_u.numel();
+  if (n == 0) return;
+  const int world = (int)peer_gin.size();
+  TORCH_CHECK(world <= RB_MAX_PEERS && offsets.numel() >= world + 1 && meta.numel() >= 3 * world + 1);
+  c10::cuda::CUDAGuard g(grad_out.device());
+  RbGuPush push{};
+  push.off = offsets.data_ptr<int32_t>();
+  push.dst_base = meta.data_ptr<int32_t>() + 2 * world + 1;
+  for (int r = 0; r < world; ++r) push.base[r] = reinterpret_cast<void*>(peer_gin[r]);
+  push.world = world;
+  push.cap_rows = cap_rows;
+  const int64_t n_chunks = (n + rb_grad_reduce_chunk() - 1) / rb_grad_reduce_chunk();
+  auto span = torch::zeros({n_chunks, D}, grad_out.options());
+  rb_grad_reduce_push(grad_out.data_ptr<float>(), gsrc.data_ptr<int32_t>(), gscale.data_ptr<float>(), csr_u.data_ptr<int32_t>(),
+                      csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>(), n, (int)D, span.data_ptr<float>(), push, cur_stream());
 }
 
 void comm_allreduce_slice(const std::vector<int64_t>& bufs, int64_t me, int64_t n_padded, double scale) {
@@ -120,6 +145,7 @@ void init_comm(py::module& m) {
   m.def("comm_pull_ids", &comm_pull_ids);
   m.def("comm_push_emb", &comm_push_emb);
   m.def("comm_owner_reduce", &comm_owner_reduce);
+  m.def("comm_grad_reduce_push", &comm_grad_reduce_push);
   m.def("comm_allreduce_slice", &comm_allreduce_slice);
   m.def("comm_copy", [](int64_t dst, int64_t src, int64_t nbytes, int64_t blocks) {
     rb_comm_copy(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), nbytes, (int)blocks, cur_stream());

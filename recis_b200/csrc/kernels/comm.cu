@@ -110,6 +110,16 @@ pull_ids_kernel(RbPeers peer_ids, RbPeers peer_offsets, int me, int world, int64
     // requesters' offset windows are rewritten by their next forward pass.
     for (int r = threadIdx.x; r <= world; r += blockDim.x) prefix_out[r] = prefix[r];
     for (int r = threadIdx.x; r < world; r += blockDim.x) prefix_out[world + 1 + r] = src_off[r];
+    // prefix_out[2*world+1 + o]: where THIS rank's bucket for owner o starts inside o's incoming order (the sum of what the
+    // lower ranks send to o); the backward pass pushes its per-unique gradients to exactly those rows of o's window.
+    for (int o = threadIdx.x; o < world; o += blockDim.x) {
+      int32_t base = 0;
+      for (int r = 0; r < me; ++r) {
+        const int32_t* off = reinterpret_cast<const int32_t*>(peer_offsets.p[r]);
+        base += off[o + 1] - off[o];
+      }
+      prefix_out[2 * world + 1 + o] = base;
+    }
     if (threadIdx.x == 0) *n_in_dev = (int32_t)n_in;
   }
   for (int64_t j = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; j < n_in; j += (int64_t)gridDim.x * blockDim.x) {
@@ -139,14 +149,24 @@ push_emb_kernel(const float* __restrict__ emb, const int32_t* __restrict__ rows_
   __syncthreads();
   const int q = D >> 2;                        // D % 4 == 0 is required by the fused path
   const int64_t total = (int64_t)max_cnt * q;
-  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t k = w / q; const int c = (int)(w - k * q);
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  constexpr int U = 4;                       // rows in flight per thread and requester
+  for (int64_t w0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w0 < total; w0 += stride * U) {
     for (int r0 = 0; r0 < world; ++r0) {
       const int r = (r0 + me + 1) % world;    // start with the right neighbour: ranks do not all hammer rank 0 first
-      if (k >= prefix[r + 1] - prefix[r]) continue;
-      const int32_t row = rows_in[prefix[r] + k];
-      float* dst = reinterpret_cast<float*>(peer_uemb.p[r]) + ((int64_t)dst_off[r] + k) * D + c * 4;
-      st_f4(dst, row >= 0 ? ld_f4(emb + (int64_t)row * D + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f));
+      const int32_t cnt = prefix[r + 1] - prefix[r];
+      int32_t row[U]; int64_t k[U]; int c[U]; float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t w = w0 + u * stride;
+        k[u] = w / q; c[u] = (int)(w - k[u] * q);
+        row[u] = (w < total && k[u] < cnt) ? rows_in[prefix[r] + k[u]] : -2;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = row[u] >= 0 ? ld_f4(emb + (int64_t)row[u] * D + c[u] * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (row[u] != -2) st_f4(reinterpret_cast<float*>(peer_uemb.p[r]) + ((int64_t)dst_off[r] + k[u]) * D + c[u] * 4, v[u]);
     }
   }
 }
@@ -225,62 +245,79 @@ owner_unlink_kernel(const int32_t* __restrict__ rows_in, const int32_t* __restri
     if (rows_in[j] >= 0) head[rows_in[j]] = -1;
 }
 
-// Owner: one work item per (incoming id j, float4 column). The item whose j heads its row's chain walks the chain (at
-// most one entry per requester), pulls each contribution from that requester's per-unique gradient buffer over NVLink
-// in ascending j order (deterministic sum), then updates the row (apply) or stores (row, gradient) at position j
-// (apply == 0; non-head positions get row -1).
+// Owner: one work item per (incoming id j, float4 column); the gradients of all requesters already sit in this rank's
+// window g_in (row j = the j-th incoming id), pushed there by the requesters' backward kernels. The item whose j heads its
+// row's chain sums the chain (at most one entry per requester; a + b is order independent, three or more are summed in
+// ascending j order so the result does not depend on scheduling), then updates the row (apply) or stores (row, gradient)
+// at position j (apply == 0; non-head positions get row -1). U independent items are in flight per thread: their index
+// reads, optimizer-state loads and gradient loads are all issued before any of them is consumed.
+template <int U>
 __global__ void __launch_bounds__(kThreads)
 owner_reduce_kernel(const int32_t* __restrict__ rows_in, const int32_t* __restrict__ head, const int32_t* __restrict__ next,
-                    const int32_t* __restrict__ prefix_in, RbPeers peer_gu, int me, int world, int D,
+                    const int32_t* __restrict__ prefix_in, const float* __restrict__ g_in, int world, int D,
                     int mean_by_id, int apply, RbOpt opt, int32_t* __restrict__ out_rows, float* __restrict__ out_grads) {
-  __shared__ int32_t prefix[RB_MAX_PEERS + 1];
-  __shared__ int32_t src_off[RB_MAX_PEERS];
-  if (threadIdx.x <= world) prefix[threadIdx.x] = prefix_in[threadIdx.x];
-  if (threadIdx.x < world) src_off[threadIdx.x] = prefix_in[world + 1 + threadIdx.x];
-  __syncthreads();
-  const int64_t n_in = prefix[world];
+  const int64_t n_in = prefix_in[world];
   const int q = D >> 2;
   const int64_t total = n_in * q;
-  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t j0 = w / q; const int c = (int)(w - j0 * q);
-    const int32_t row = rows_in[j0];
-    if (row < 0 || head[row] != (int32_t)j0) {
-      if (!apply && c == 0) out_rows[j0] = -1;
-      continue;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t w0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w0 < total; w0 += stride * U) {
+    int64_t j0[U]; int c[U]; int32_t row[U]; int32_t nx[U]; bool is_head[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t w = w0 + u * stride;
+      j0[u] = w / q; c[u] = (int)(w - j0[u] * q);
+      row[u] = w < total ? rows_in[j0[u]] : -1;
+      if (w >= total) j0[u] = -1;
     }
-    // 1. the row's optimizer state is requested first: those HBM loads overlap the NVLink loads below
-    const int64_t off = (int64_t)row * D + c * 4;
-    float4 sw = make_float4(0.f, 0.f, 0.f, 0.f), s1v = sw, s2v = sw;
-    if (apply) {
-      sw = ld_f4(opt.w + off);
-      if (opt.kind != RB_OPT_SGD) s1v = ld_f4(opt.s1 + off);
-      if (opt.kind == RB_OPT_ADAM) s2v = ld_f4(opt.s2 + off);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      is_head[u] = row[u] >= 0 && head[row[u]] == (int32_t)j0[u];
+      nx[u] = is_head[u] ? next[j0[u]] : -1;
+      if (!apply && c[u] == 0 && j0[u] >= 0 && !is_head[u]) out_rows[j0[u]] = -1;
     }
-    // 2. contributions: one per requester that asked for this id; almost always a single one
-    int32_t chain[RB_MAX_PEERS];
-    int cnt = 0;
-    for (int32_t j = (int32_t)j0; j >= 0 && cnt < RB_MAX_PEERS; j = next[j]) chain[cnt++] = j;
-    if (cnt > 2) {                                         // a + b is order independent; three or more are summed in index order
-      for (int a = 1; a < cnt; ++a) {
-        const int32_t v = chain[a]; int b = a - 1;
-        while (b >= 0 && chain[b] > v) { chain[b + 1] = chain[b]; --b; }
-        chain[b + 1] = v;
+    float4 sw[U], s1v[U], s2v[U], acc[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f); sw[u] = acc[u]; s1v[u] = acc[u]; s2v[u] = acc[u];
+      if (!is_head[u]) continue;
+      const int64_t off = (int64_t)row[u] * D + c[u] * 4;
+      if (apply) {
+        sw[u] = ld_f4(opt.w + off);
+        if (opt.kind != RB_OPT_SGD) s1v[u] = ld_f4(opt.s1 + off);
+        if (opt.kind == RB_OPT_ADAM) s2v[u] = ld_f4(opt.s2 + off);
       }
+      acc[u] = ld_f4(g_in + j0[u] * D + c[u] * 4);
     }
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int a = 0; a < cnt; ++a) {
-      const int64_t j = chain[a];
-      const int r = find_src(prefix, world, j);
-      const float4 g = ld_f4(reinterpret_cast<const float*>(peer_gu.p[r]) + ((int64_t)src_off[r] + (j - prefix[r])) * D + c * 4);
-      acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
-    }
-    if (mean_by_id && cnt > 1) { const float s = 1.f / (float)cnt; acc.x *= s; acc.y *= s; acc.z *= s; acc.w *= s; }
-    if (apply) {
-      opt_update_pre_f4(opt, off, acc, sw, s1v, s2v);
-    } else {
-      if (c == 0) out_rows[j0] = row;
-      const float gs = opt.grad_scale;
-      st_f4(out_grads + j0 * D + c * 4, make_float4(acc.x * gs, acc.y * gs, acc.z * gs, acc.w * gs));
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!is_head[u]) continue;
+      int cnt = 1;
+      if (nx[u] >= 0) {                                   // several requesters asked for this id
+        int32_t chain[RB_MAX_PEERS];
+        chain[0] = (int32_t)j0[u];
+        for (int32_t j = nx[u]; j >= 0 && cnt < RB_MAX_PEERS; j = next[j]) chain[cnt++] = j;
+        if (cnt > 2) {
+          for (int a = 1; a < cnt; ++a) {
+            const int32_t v = chain[a]; int b = a - 1;
+            while (b >= 0 && chain[b] > v) { chain[b + 1] = chain[b]; --b; }
+            chain[b + 1] = v;
+          }
+          acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int a = (cnt > 2 ? 0 : 1); a < cnt; ++a) {
+          const float4 g = ld_f4(g_in + (int64_t)chain[a] * D + c[u] * 4);
+          acc[u].x += g.x; acc[u].y += g.y; acc[u].z += g.z; acc[u].w += g.w;
+        }
+      }
+      if (mean_by_id && cnt > 1) { const float sc = 1.f / (float)cnt; acc[u].x *= sc; acc[u].y *= sc; acc[u].z *= sc; acc[u].w *= sc; }
+      const int64_t off = (int64_t)row[u] * D + c[u] * 4;
+      if (apply) {
+        opt_update_pre_f4(opt, off, acc[u], sw[u], s1v[u], s2v[u]);
+      } else {
+        if (c[u] == 0) out_rows[j0[u]] = row[u];
+        const float gs = opt.grad_scale;
+        st_f4(out_grads + j0[u] * D + c[u] * 4, make_float4(acc[u].x * gs, acc[u].y * gs, acc[u].z * gs, acc[u].w * gs));
+      }
     }
   }
 }
@@ -330,14 +367,19 @@ void rb_comm_push_emb(const float* emb, const int32_t* rows_in, const int32_t* p
   rb::note_launch();
 }
 
-void rb_comm_owner_reduce(const int32_t* rows_in, int32_t* head, int32_t* next, const int32_t* prefix, RbPeers peer_gu, int me,
-                          int world, int D, int mean_by_id, int apply, RbOpt opt, int32_t* out_rows, float* out_grads,
-                          int64_t n_in_max, cudaStream_t st) {
+void rb_comm_owner_reduce(const int32_t* rows_in, int32_t* head, int32_t* next, const int32_t* prefix, const float* g_in, int world,
+                          int D, int mean_by_id, int apply, RbOpt opt, int32_t* out_rows, float* out_grads, int64_t n_in_max,
+                          int unroll, cudaStream_t st) {
   const int g1 = grid_stride_blocks(n_in_max / 4 + 1);
   owner_link_kernel<<<g1, kThreads, 0, st>>>(rows_in, prefix, world, head, next);
   rb::note_launch();
-  owner_reduce_kernel<<<grid_stride_blocks(n_in_max * (D / 4) / 4 + 1), kThreads, 0, st>>>(rows_in, head, next, prefix, peer_gu, me, world, D,
-                                                                                        mean_by_id, apply, opt, out_rows, out_grads);
+  const int g2 = grid_stride_blocks(n_in_max * (D / 4) / 4 + 1);
+  if (unroll >= 4)
+    owner_reduce_kernel<4><<<g2, kThreads, 0, st>>>(rows_in, head, next, prefix, g_in, world, D, mean_by_id, apply, opt, out_rows, out_grads);
+  else if (unroll >= 2)
+    owner_reduce_kernel<2><<<g2, kThreads, 0, st>>>(rows_in, head, next, prefix, g_in, world, D, mean_by_id, apply, opt, out_rows, out_grads);
+  else
+    owner_reduce_kernel<1><<<g2, kThreads, 0, st>>>(rows_in, head, next, prefix, g_in, world, D, mean_by_id, apply, opt, out_rows, out_grads);
   rb::note_launch();
   owner_unlink_kernel<<<g1, kThreads, 0, st>>>(rows_in, prefix, world, head);
   rb::note_launch();

@@ -19,13 +19,15 @@ void rb_comm_signal(RbPeers flag_pads, int channel, int me, int world, int64_t e
 void rb_comm_wait(const int64_t* flags, int channel, int world, int64_t epoch, int64_t spin_limit, int64_t* status, cudaStream_t st);
 void rb_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, int me, int world, int64_t* ids_in, int64_t in_cap, int32_t* prefix_out,
                       int32_t* n_in_dev, int64_t* status, cudaStream_t st);
-// prefix: int32[2*world+1] written by rb_comm_pull_ids = per-source prefix sums [world+1] then per-source window offsets [world]
+// prefix: int32[3*world+1] written by rb_comm_pull_ids = per-source prefix sums [world+1], per-source window offsets
+// [world], and for every owner o the first row of this rank's bucket inside o's incoming order [world]
 void rb_comm_push_emb(const float* emb, const int32_t* rows_in, const int32_t* prefix, RbPeers peer_uemb, int me, int world, int D,
                       int64_t n_in_max, cudaStream_t st);
-// head: int32[table capacity], all -1 between calls; next: int32[n_in_max] scratch.
-void rb_comm_owner_reduce(const int32_t* rows_in, int32_t* head, int32_t* next, const int32_t* prefix, RbPeers peer_gu, int me,
-                          int world, int D, int mean_by_id, int apply, RbOpt opt, int32_t* out_rows, float* out_grads,
-                          int64_t n_in_max, cudaStream_t st);
+// head: int32[table capacity], all -1 between calls; next: int32[n_in_max] scratch; g_in: this rank's gradient window
+// [n_in_max, D] filled by the requesters (rb_grad_reduce_push); unroll: 1, 2 or 4 work items in flight per thread.
+void rb_comm_owner_reduce(const int32_t* rows_in, int32_t* head, int32_t* next, const int32_t* prefix, const float* g_in, int world,
+                          int D, int mean_by_id, int apply, RbOpt opt, int32_t* out_rows, float* out_grads, int64_t n_in_max,
+                          int unroll, cudaStream_t st);
 void rb_comm_allreduce_slice(RbPeers bufs, int me, int world, int64_t n_padded, float scale, cudaStream_t st);
 // generic key/value radix sort of int32 pairs (keys need `key_bits` low bits); temp sized by rb_sort_temp_bytes
 void rb_sort_pairs_i32(const int32_t* keys_in, int32_t* keys_out, const int32_t* vals_in, int32_t* vals_out, int64_t n, int key_bits,

@@ -52,6 +52,17 @@ typedef struct RbOpt {
   float* s2;        // Adam exp_avg_sq | unused
 } RbOpt;
 
+// Where per-unique gradients go when they are pushed to the ranks that own the rows instead of being stored locally:
+// unique index u in [off[o], off[o+1]) is written to row dst_base[o] + (u - off[o]) of base[o], a (peer-mapped) window
+// of cap_rows rows on rank o. off and dst_base are device arrays; rows that would fall beyond cap_rows are dropped.
+typedef struct RbGuPush {
+  const int32_t* off;        // [world+1] bucket boundaries of this rank's unique ids
+  const int32_t* dst_base;   // [world]   first row of this rank's bucket inside owner o's window
+  void* base[16];
+  int world;
+  int64_t cap_rows;
+} RbGuPush;
+
 // ---- table.cu
 void rb_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* slot_scratch,
                                int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, float* emb, int D, RbInit init,
@@ -94,6 +105,9 @@ void rb_build_csr(const int32_t* reverse, int64_t n, int key_bits, void* temp, s
 void rb_grad_reduce(const float* grad_out, const int32_t* gsrc, const float* gscale, const int32_t* csr_u, const int32_t* csr_elem,
                     const int32_t* start, int64_t n, int D, float* span_acc /*[ceil(n/chunk), D] zeros*/, const int32_t* rows,
                     float* gu, int apply, RbOpt opt, cudaStream_t st);
+// Same reduction with apply == 0 semantics, the result rows stored through `push` (float4 rows only: D % 4 == 0, D <= 512).
+void rb_grad_reduce_push(const float* grad_out, const int32_t* gsrc, const float* gscale, const int32_t* csr_u, const int32_t* csr_elem,
+                         const int32_t* start, int64_t n, int D, float* span_acc, RbGuPush push, cudaStream_t st);
 int rb_grad_reduce_chunk();
 void rb_sparse_apply(const int32_t* rows, const float* grads, int64_t n_max, const int32_t* n_dev, int D, RbOpt opt, cudaStream_t st);
 

@@ -370,12 +370,32 @@ __device__ __forceinline__ void opt_update_f1(const RbOpt& o, int64_t off, float
 
 // ------------------------------------------------------------------ chunked segmented gradient reduction
 // VEC = 4: float4 columns, G lanes x NACC slots per group. Work item = kChunk consecutive CSR positions.
-template <int G, int NACC>
+// Shared-memory copy of a push descriptor: row_ptr(u) is where the gradient of unique index u is stored (nullptr = dropped).
+struct PushTable {
+  int32_t off[17];
+  int32_t dst[16];
+  float* base[16];
+  __device__ __forceinline__ void load(const RbGuPush& p) {
+    if (threadIdx.x <= p.world) off[threadIdx.x] = p.off[threadIdx.x];
+    if (threadIdx.x < p.world) { dst[threadIdx.x] = p.dst_base[threadIdx.x]; base[threadIdx.x] = static_cast<float*>(p.base[threadIdx.x]); }
+    __syncthreads();
+  }
+  __device__ __forceinline__ float* row_ptr(int32_t u, int world, int64_t cap_rows, int D) const {
+    int o = 0;
+    while (o + 1 < world && off[o + 1] <= u) ++o;
+    const int64_t r = (int64_t)dst[o] + (u - off[o]);
+    return r < cap_rows ? base[o] + r * D : nullptr;
+  }
+};
+
+template <int G, int NACC, bool PUSH>
 __global__ void __launch_bounds__(kThreads)
 grad_reduce_kernel(const float* __restrict__ grad_out, const int32_t* __restrict__ gsrc, const float* __restrict__ gscale,
                    const int32_t* __restrict__ csr_u, const int32_t* __restrict__ csr_elem, const int32_t* __restrict__ start,
                    int64_t n, int D, float* __restrict__ span_acc, const int32_t* __restrict__ rows, float* __restrict__ gu,
-                   int apply, RbOpt opt) {
+                   int apply, RbOpt opt, RbGuPush push) {
+  __shared__ PushTable ptab;
+  if (PUSH) ptab.load(push);
   // Phase 1 (per chunk): the lanes of the group fetch the metadata of all positions of the chunk in parallel (one
   // dependent chain for the whole chunk instead of one per position) and park it in shared memory.
   // Phase 2: walk the segments of the chunk; the optimizer state of a row is requested when its segment starts, so
@@ -454,7 +474,14 @@ grad_reduce_kernel(const float* __restrict__ grad_out, const int32_t* __restrict
         if (col >= cols) continue;
         if (row == -2) red_add_f4(span_acc + (int64_t)m_dst[j] * D + col * 4, acc[a]);
         else if (upd) opt_update_pre_f4(opt, (int64_t)row * D + col * 4, acc[a], sw[a], s1v[a], s2v[a]);
-        else if (!apply) st_f4(gu + (int64_t)row * D + col * 4, acc[a]);
+        else if (!apply) {
+          if (PUSH) {
+            float* dstp = ptab.row_ptr(row, push.world, push.cap_rows, D);
+            if (dstp) st_f4(dstp + col * 4, acc[a]);
+          } else {
+            st_f4(gu + (int64_t)row * D + col * 4, acc[a]);
+          }
+        }
       }
       j = jend;
     }
@@ -464,10 +491,13 @@ grad_reduce_kernel(const float* __restrict__ grad_out, const int32_t* __restrict
 
 // Rows whose occurrences cross a chunk boundary were accumulated in span_acc[chunk of their first
 // occurrence]; finish them here and leave span_acc zeroed for the next step.
-template <int G, int NACC>
+template <int G, int NACC, bool PUSH>
 __global__ void __launch_bounds__(kThreads)
 grad_span_finish_kernel(const int32_t* __restrict__ csr_u, const int32_t* __restrict__ start, int64_t n, int D,
-                        float* __restrict__ span_acc, const int32_t* __restrict__ rows, float* __restrict__ gu, int apply, RbOpt opt) {
+                        float* __restrict__ span_acc, const int32_t* __restrict__ rows, float* __restrict__ gu, int apply, RbOpt opt,
+                        RbGuPush push) {
+  __shared__ PushTable ptab;
+  if (PUSH) ptab.load(push);
   const int lane = threadIdx.x % G;
   const int cols = D >> 2;
   const int64_t n_chunks = (n + kChunk - 1) / kChunk;
@@ -486,7 +516,10 @@ grad_span_finish_kernel(const int32_t* __restrict__ csr_u, const int32_t* __rest
         const float4 g = ld_f4(src + col * 4);
         st_f4(src + col * 4, make_float4(0.f, 0.f, 0.f, 0.f));
         if (apply) { if (row >= 0) opt_update_f4(opt, (int64_t)row * D + col * 4, g); }
-        else st_f4(gu + (int64_t)u * D + col * 4, g);
+        else if (PUSH) {
+          float* dstp = ptab.row_ptr(u, push.world, push.cap_rows, D);
+          if (dstp) st_f4(dstp + col * 4, g);
+        } else st_f4(gu + (int64_t)u * D + col * 4, g);
       }
     }
   }
@@ -658,10 +691,10 @@ void rb_grad_reduce(const float* grad_out, const int32_t* gsrc, const float* gsc
     constexpr int G = decltype(g)::value, NACC = decltype(nacc)::value;
     const int64_t blocks = (n_chunks + (kThreads / G) - 1) / (kThreads / G);
     const int grid = (int)std::min<int64_t>(blocks, 148 * 64);
-    grad_reduce_kernel<G, NACC><<<grid, kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, span_acc, rows, gu,
-                                                           apply, opt);
-  rb::note_launch();
-    grad_span_finish_kernel<G, NACC><<<grid, kThreads, 0, st>>>(csr_u, start, n, D, span_acc, rows, gu, apply, opt);
+    grad_reduce_kernel<G, NACC, false><<<grid, kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, span_acc, rows,
+                                                                  gu, apply, opt, RbGuPush{});
+    rb::note_launch();
+    grad_span_finish_kernel<G, NACC, false><<<grid, kThreads, 0, st>>>(csr_u, start, n, D, span_acc, rows, gu, apply, opt, RbGuPush{});
     rb::note_launch();
   });
   if (!ok) {
@@ -669,6 +702,23 @@ void rb_grad_reduce(const float* grad_out, const int32_t* gsrc, const float* gsc
                                                                              gu, apply, opt);
     rb::note_launch();
   }
+}
+
+void rb_grad_reduce_push(const float* grad_out, const int32_t* gsrc, const float* gscale, const int32_t* csr_u, const int32_t* csr_elem,
+                         const int32_t* start, int64_t n, int D, float* span_acc, RbGuPush push, cudaStream_t st) {
+  if (n <= 0) return;
+  const int64_t n_chunks = (n + kChunk - 1) / kChunk;
+  RbOpt opt{};
+  dispatch_cols(D, [&](auto g, auto nacc) {
+    constexpr int G = decltype(g)::value, NACC = decltype(nacc)::value;
+    const int64_t blocks = (n_chunks + (kThreads / G) - 1) / (kThreads / G);
+    const int grid = (int)std::min<int64_t>(blocks, 148 * 64);
+    grad_reduce_kernel<G, NACC, true><<<grid, kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, span_acc, nullptr,
+                                                                 nullptr, 0, opt, push);
+    rb::note_launch();
+    grad_span_finish_kernel<G, NACC, true><<<grid, kThreads, 0, st>>>(csr_u, start, n, D, span_acc, nullptr, nullptr, 0, opt, push);
+    rb::note_launch();
+  });
 }
 
 void rb_sparse_apply(const int32_t* rows, const float* grads, int64_t n_max, const int32_t* n_dev, int D, RbOpt opt, cudaStream_t st) {

@@ -8,10 +8,10 @@ forward   requester  dedup + bucket ids by owner straight into its symmetric win
           owner      wait IDS; pull the ids bucketed for it from every requester (peer loads); table lookup-or-insert;
                      push each row into the requester's unique-embedding buffer (peer stores) .. signal EMB
           requester  wait EMB; pool from its (local) unique-embedding buffer
-backward  requester  segmented reduction of the pooled gradient to one gradient per unique id, written into its symmetric
-                     gradient window ......................................................... signal GRAD
-optimizer owner      wait GRAD; ONE kernel pulls every contribution of a touched row from the requesters' windows (peer
-                     loads), adds duplicates across requesters and applies the row-wise optimizer update
+backward  requester  ONE kernel reduces the pooled gradient to one gradient per unique id and stores it straight into the
+                     gradient window of the rank that owns the id (peer stores) ................. signal GRAD
+optimizer owner      wait GRAD; ONE kernel adds the contributions of every touched row (duplicates across requesters are
+                     chained) and applies the row-wise optimizer update, reading only local memory
 
 No split size ever reaches the host; windows are sized for the worst case (``exchange_capacity`` unique ids per rank).
 Every (table, runtime group) pair owns one *lane*: its own windows, flag pad and epoch counter, so that the epochs written
@@ -50,10 +50,10 @@ class _Lane:
             "offsets": (torch.int32, W + 1),
             "ids": (torch.int64, cap),
             "uemb": (torch.float32, cap * D),
-            "gu": (torch.float32, cap * D),
+            "gin": (torch.float32, self.in_cap * D),
         }, ex.device, ex.pg)
         self.ids_in = torch.empty(self.in_cap, dtype=torch.int64, device=ex.device)
-        self.prefix = torch.zeros(2 * W + 1, dtype=torch.int32, device=ex.device)
+        self.prefix = torch.zeros(3 * W + 1, dtype=torch.int32, device=ex.device)
         self.n_in = torch.zeros(1, dtype=torch.int32, device=ex.device)
         self.epoch = 0
         self.pending_grad_epoch = 0      # a staged, not yet consumed gradient window
@@ -62,7 +62,7 @@ class _Lane:
 class FusedExchange:
     @staticmethod
     def create(emb_opt, pg, world, rank):
-        if emb_opt.embedding_dim % 4 != 0 or emb_opt.dtype != torch.float32:
+        if emb_opt.embedding_dim % 4 != 0 or emb_opt.embedding_dim > 512 or emb_opt.dtype != torch.float32:
             return None
         if world > native().MAX_PEERS:
             return None
@@ -79,6 +79,7 @@ class FusedExchange:
         self.wait_us = int(float(os.environ.get("RECIS_WAIT_TIMEOUT_S", "20")) * 1e6)
         self.status = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.immediate_reduce = False
+        self.owner_unroll = int(os.environ.get("RECIS_OWNER_UNROLL", "2"))
         self._head = None
 
     def table_storage(self):
@@ -137,7 +138,8 @@ class FusedExchange:
             out, gsrc, gscale = C.tile_forward(uemb, None, rev, offsets, weights, tile_len, train)
         else:
             out, gsrc, gscale = C.pool_forward(uemb, None, rev, offsets, weights, mode, perm_b, perm_f, train)
-        saved = dict(rev=rev, gsrc=gsrc, gscale=gscale, rows_in=rows_in, prefix=prefix, epoch=e, lane=lane) if train else None
+        saved = dict(rev=rev, gsrc=gsrc, gscale=gscale, rows_in=rows_in, prefix=prefix, epoch=e, lane=lane,
+                     offsets=h["offsets"].tensor.clone()) if train else None
         return out, saved
 
     # ------------------------------------------------------------------ backward (requester side) + staging
@@ -146,8 +148,8 @@ class FusedExchange:
         lane = s["lane"]
         h, me, D = lane.heap, self.rank, self.D
         csr_u, csr_elem, start = C.build_csr(s["rev"])
-        C.grad_reduce(grad_out, s["gsrc"], s["gscale"], csr_u, csr_elem, start, D, None, False, 2, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0,
-                      1.0, None, None, None, lane.send_cap, h["gu"].tensor.view(lane.send_cap, D))
+        C.comm_grad_reduce_push(grad_out, s["gsrc"], s["gscale"], csr_u, csr_elem, start, D, s["offsets"], s["prefix"],
+                                h["gin"].ptrs, lane.in_cap)
         C.comm_signal(h["flags"].ptrs, CH_GRAD, me, s["epoch"])
         rec = dict(rows_in=s["rows_in"], prefix=s["prefix"], epoch=s["epoch"], scale=worker_scale, exchange=self, lane=lane,
                    mean_by_id=emb_mod.option.grad_reduce_by == "id")
@@ -177,9 +179,9 @@ class FusedExchange:
         h = lane.heap
         C.comm_wait(h["flags"].tensor, CH_GRAD, self.world, rec["epoch"], self.wait_us, self.status)
         head = self._head_for(impl.store)
-        rows, grads = C.comm_owner_reduce(rec["rows_in"], head, rec["prefix"], h["gu"].ptrs, self.rank, self.D, rec["mean_by_id"],
-                                          apply, kind, lr, b1, b2, eps, decay, alpha, rec["scale"] * grad_scale, w, s1, s2,
-                                          lane.in_cap)
+        rows, grads = C.comm_owner_reduce(rec["rows_in"], head, rec["prefix"], h["gin"].tensor, self.world, self.D,
+                                          rec["mean_by_id"], apply, kind, lr, b1, b2, eps, decay, alpha, rec["scale"] * grad_scale,
+                                          w, s1, s2, lane.in_cap, self.owner_unroll)
         if lane.pending_grad_epoch == rec["epoch"]:
             lane.pending_grad_epoch = 0
         return rows, grads
