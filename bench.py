@@ -246,7 +246,8 @@ class OursArm:
         model = DLRM(fields, dense_dim=13, emb_dim=EMB_DIM, device=dev, capacity=capacity).to(dev)
         sparse_opt = SparseAdam(filter_out_sparse_param(model), lr=1e-3)
         dense_params = [p for p in model.parameters() if p.requires_grad]
-        dense_opt = torch.optim.Adam(dense_params, lr=1e-3, fused=True)
+        from recis_b200.optim import DenseAdam
+        dense_opt = DenseAdam(dense_params, lr=1e-3)
         reducer = DenseGradReducer(dense_params, world) if world > 1 else None
         return dict(model=model, sparse_opt=sparse_opt, dense_opt=dense_opt, reducer=reducer)
 

@@ -185,4 +185,35 @@ void init_dense(py::module& m) {
   m.def("fm_bwd", &fm_bwd);
   m.def("relu_bwd_bias", &relu_bwd_bias);
   m.def("cast_pad_bf16", &cast_pad_bf16);
+  // Multi-tensor dense Adam (see rb_dense.h for the update rule); ws/gs/ms/vs are parallel lists of fp32 CUDA tensors,
+  // w_bf16 an optional parallel list (entries may be undefined) of bf16 shadows that receive the rounded weights.
+  m.def("dense_adam", [](std::vector<Tensor> ws, std::vector<Tensor> gs, std::vector<Tensor> ms, std::vector<Tensor> vs,
+                         std::vector<c10::optional<Tensor>> w_bf16, double beta1, double beta2, double eps, double decay,
+                         double step_size, double inv_sqrt_bc2, double l2) {
+    TORCH_CHECK(ws.size() == gs.size() && ws.size() == ms.size() && ws.size() == vs.size(), "parallel lists differ in length");
+    TORCH_CHECK(w_bf16.empty() || w_bf16.size() == ws.size(), "w_bf16 must be empty or parallel to the weights");
+    if (ws.empty()) return;
+    c10::cuda::CUDAGuard guard(ws[0].device());
+    for (size_t i0 = 0; i0 < ws.size(); i0 += RB_DENSE_ADAM_MAX) {
+      RbDenseAdamArgs a{};
+      a.count = (int)std::min<size_t>(RB_DENSE_ADAM_MAX, ws.size() - i0);
+      for (int k = 0; k < a.count; ++k) {
+        const Tensor &w = ws[i0 + k], &g = gs[i0 + k], &mm = ms[i0 + k], &vv = vs[i0 + k];
+        TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kFloat32 && w.is_contiguous() && g.is_contiguous() && mm.is_contiguous() &&
+                        vv.is_contiguous() && g.scalar_type() == torch::kFloat32 && g.numel() == w.numel() && mm.numel() == w.numel() &&
+                        vv.numel() == w.numel(),
+                    "dense_adam wants contiguous fp32 CUDA tensors of equal size");
+        a.w[k] = w.data_ptr<float>(); a.g[k] = g.data_ptr<float>(); a.m[k] = mm.data_ptr<float>(); a.v[k] = vv.data_ptr<float>();
+        a.n[k] = w.numel();
+        a.w_bf16[k] = nullptr;
+        if (!w_bf16.empty() && w_bf16[i0 + k].has_value() && w_bf16[i0 + k]->defined()) {
+          const Tensor& wb = *w_bf16[i0 + k];
+          TORCH_CHECK(wb.scalar_type() == torch::kBFloat16 && wb.is_contiguous() && wb.numel() == w.numel(), "bf16 shadow mismatch");
+          a.w_bf16[k] = wb.data_ptr();
+        }
+      }
+      rb_dense_adam(&a, (float)beta1, (float)beta2, (float)eps, (float)decay, (float)step_size, (float)inv_sqrt_bc2, (float)l2,
+                    at::cuda::getCurrentCUDAStream());
+    }
+  });
 }

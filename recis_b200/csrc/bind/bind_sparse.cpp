@@ -22,7 +22,8 @@ int64_t pow2_at_least(int64_t x) { int64_t p = 64; while (p < x) p <<= 1; return
 
 // ids -> (unique ids bucketed by owner rank, reverse index, per-owner counts, per-owner offsets)
 // unique_out / offsets_out (optional) let the caller place the results in peer-visible memory.
-std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, int64_t world, OptT unique_out, OptT offsets_out) {
+std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, int64_t world, OptT unique_out, OptT offsets_out,
+                                                           OptT status) {
   TORCH_CHECK(ids.scalar_type() == torch::kInt64 && ids.is_contiguous(), "ids: contiguous int64 expected");
   TORCH_CHECK(world >= 1 && world <= 1024, "world size out of range");
   const int64_t n = ids.numel();
@@ -34,14 +35,16 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, in
   auto counts = torch::empty({world}, o.dtype(torch::kInt32));
   Tensor offsets = offsets_out.has_value() && offsets_out->defined() ? *offsets_out : torch::empty({world + 1}, o.dtype(torch::kInt32));
   Tensor unique_ids = unique_out.has_value() && unique_out->defined() ? *unique_out : torch::empty({n}, o);
-  TORCH_CHECK(offsets.numel() >= world + 1 && offsets.scalar_type() == torch::kInt32 && unique_ids.numel() >= n &&
+  const bool guarded = ids.is_cuda() && status.has_value() && status->defined();   // a smaller unique buffer needs the status word
+  TORCH_CHECK(offsets.numel() >= world + 1 && offsets.scalar_type() == torch::kInt32 && (guarded || unique_ids.numel() >= n) &&
               unique_ids.scalar_type() == torch::kInt64, "dedup_partition: output buffers too small or of the wrong type");
   auto reverse = torch::empty({n}, o.dtype(torch::kInt32));
   if (ids.is_cuda()) {
     c10::cuda::CUDAGuard g(ids.device());
     rb_dedup_partition(ids.data_ptr<int64_t>(), n, (int)world, reinterpret_cast<uint64_t*>(set_keys.data_ptr<int64_t>()),
                        set_pos.data_ptr<int32_t>(), cap, slot.data_ptr<int32_t>(), counts.data_ptr<int32_t>(),
-                       offsets.data_ptr<int32_t>(), unique_ids.data_ptr<int64_t>(), reverse.data_ptr<int32_t>(), cur_stream());
+                       offsets.data_ptr<int32_t>(), unique_ids.data_ptr<int64_t>(), reverse.data_ptr<int32_t>(), unique_ids.numel(),
+                       guarded ? status->data_ptr<int64_t>() : nullptr, cur_stream());
   } else {
     rbc_dedup_partition(ids.data_ptr<int64_t>(), n, (int)world, reinterpret_cast<uint64_t*>(set_keys.data_ptr<int64_t>()),
                         set_pos.data_ptr<int32_t>(), cap, slot.data_ptr<int32_t>(), counts.data_ptr<int32_t>(),
@@ -260,7 +263,7 @@ void init_sparse(py::module& m) {
       .def("set_name", &EmbeddingStore::set_name);
 
   m.def("dedup_partition", &dedup_partition, py::arg("ids"), py::arg("world"), py::arg("unique_out") = py::none(),
-        py::arg("offsets_out") = py::none());
+        py::arg("offsets_out") = py::none(), py::arg("status") = py::none());
   m.def("encode_merge", &encode_merge);
   m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("rows"), py::arg("n_dev") = py::none());
   m.def("scatter_rows", &scatter_rows);

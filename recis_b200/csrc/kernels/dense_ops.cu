@@ -210,3 +210,59 @@ void rb_cast_pad_bf16(const float* src, int rows, int cols, int src_ld, void* ds
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ multi-tensor dense Adam (TF-style and PyTorch-style)
+namespace {
+__global__ void __launch_bounds__(256)
+dense_adam_kernel(const __grid_constant__ RbDenseAdamArgs a, float b1, float b2, float eps, float decay, float step_size,
+                  float inv_sqrt_bc2, float l2) {
+  const int t = blockIdx.y;
+  float* __restrict__ w = a.w[t];
+  const float* __restrict__ g = a.g[t];
+  float* __restrict__ m = a.m[t];
+  float* __restrict__ v = a.v[t];
+  __nv_bfloat16* __restrict__ wb = reinterpret_cast<__nv_bfloat16*>(a.w_bf16[t]);
+  const int64_t n = a.n[t];
+  const float c1 = 1.f - b1, c2 = 1.f - b2;
+  auto upd = [&](float& wi, float gi, float& mi, float& vi) {
+    gi += l2 * wi;
+    mi = b1 * mi + c1 * gi;
+    vi = b2 * vi + c2 * gi * gi;
+    wi = wi * decay - step_size * mi / (sqrtf(vi) * inv_sqrt_bc2 + eps);
+  };
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const bool vec = ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+                     reinterpret_cast<uintptr_t>(v)) & 15) == 0 && (wb == nullptr || (reinterpret_cast<uintptr_t>(wb) & 7) == 0);
+  const int64_t n4 = vec ? n >> 2 : 0;
+  for (int64_t i = tid; i < n4; i += stride) {
+    float4 wi = reinterpret_cast<float4*>(w)[i], mi = reinterpret_cast<float4*>(m)[i], vi = reinterpret_cast<float4*>(v)[i];
+    const float4 gi = reinterpret_cast<const float4*>(g)[i];
+    upd(wi.x, gi.x, mi.x, vi.x); upd(wi.y, gi.y, mi.y, vi.y); upd(wi.z, gi.z, mi.z, vi.z); upd(wi.w, gi.w, mi.w, vi.w);
+    reinterpret_cast<float4*>(w)[i] = wi; reinterpret_cast<float4*>(m)[i] = mi; reinterpret_cast<float4*>(v)[i] = vi;
+    if (wb) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(wi.x, wi.y), hi = __floats2bfloat162_rn(wi.z, wi.w);
+      uint2 pk; pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(wb)[i] = pk;
+    }
+  }
+  for (int64_t i = (n4 << 2) + tid; i < n; i += stride) {
+    float wi = w[i], mi = m[i], vi = v[i];
+    upd(wi, g[i], mi, vi);
+    w[i] = wi; m[i] = mi; v[i] = vi;
+    if (wb) wb[i] = __float2bfloat16_rn(wi);
+  }
+}
+}  // namespace
+
+extern "C" void rb_dense_adam(const RbDenseAdamArgs* args, float beta1, float beta2, float eps, float decay, float step_size,
+                              float inv_sqrt_bc2, float l2, cudaStream_t st) {
+  if (args->count <= 0) return;
+  int64_t max_n = 0;
+  for (int i = 0; i < args->count; ++i) max_n = args->n[i] > max_n ? args->n[i] : max_n;
+  if (max_n == 0) return;
+  int64_t bx = (max_n / 4 + 255) / 256;
+  bx = bx < 1 ? 1 : (bx > 148 * 4 ? 148 * 4 : bx);
+  dense_adam_kernel<<<dim3((unsigned)bx, (unsigned)args->count), 256, 0, st>>>(*args, beta1, beta2, eps, decay, step_size, inv_sqrt_bc2, l2);
+  rb::note_launch();
+}

@@ -34,6 +34,24 @@ void rb_fm_bwd(const float* cube, const float* gout, int B, int F, int D, float*
 // dy = relu ? dout * (y > 0) : dout (bf16, may be null to skip the store); db[n] += column sums of dy (fp32, may be null)
 void rb_relu_bwd_bias(const void* y, const void* dout, int M, int N, int relu, void* dy, float* db, cudaStream_t st);
 void rb_cast_pad_bf16(const float* src, int rows, int cols, int src_ld, void* dst, int rows_p, int cols_p, cudaStream_t st);
+
+// Multi-tensor dense Adam: one launch updates up to RB_DENSE_ADAM_MAX fp32 tensors (gridDim.y = tensor).
+//   m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2;  w = w * decay - step_size * m / (sqrt(v) * inv_sqrt_bc2 + eps)
+// TensorFlow-style AdamW (epsilon outside the bias correction): step_size = lr sqrt(1-b2^t)/(1-b1^t), inv_sqrt_bc2 = 1,
+// decay = 1 - wd. PyTorch Adam/AdamW: step_size = lr/(1-b1^t), inv_sqrt_bc2 = 1/sqrt(1-b2^t), decay = 1 (Adam, whose L2
+// term is `l2` added to g) or 1 - lr wd (AdamW). Also writes the updated weights as bf16 when w_bf16[i] is not null.
+#define RB_DENSE_ADAM_MAX 24
+typedef struct RbDenseAdamArgs {
+  float* w[RB_DENSE_ADAM_MAX];
+  const float* g[RB_DENSE_ADAM_MAX];
+  float* m[RB_DENSE_ADAM_MAX];
+  float* v[RB_DENSE_ADAM_MAX];
+  void* w_bf16[RB_DENSE_ADAM_MAX];
+  int64_t n[RB_DENSE_ADAM_MAX];
+  int count;
+} RbDenseAdamArgs;
+void rb_dense_adam(const RbDenseAdamArgs* args, float beta1, float beta2, float eps, float decay, float step_size, float inv_sqrt_bc2,
+                   float l2, cudaStream_t st);
 #ifdef __cplusplus
 }
 #endif

@@ -74,10 +74,11 @@ void rb_table_snapshot(RbTable t, int64_t* ids_out, int32_t* rows_out, int64_t o
 void rb_table_rehash(RbTable src, RbTable dst, cudaStream_t st);
 
 // ---- sparse_ops.cu
-// Dedup ids and bucket the unique ids by owner rank. set_keys must be filled with 0xFF bytes; counts with zeros.
+// Dedup ids and bucket the unique ids by owner rank. unique_ids holds unique_cap entries: when the batch has more unique ids
+// the overflow bit is set in *status (nullable), the surplus ids are dropped and their reverse indices point at entry 0.
 void rb_dedup_partition(const int64_t* ids, int64_t n, int world, uint64_t* set_keys, int32_t* set_pos, int64_t set_cap,
                         int32_t* slot_scratch, int32_t* counts, int32_t* offsets /*[world+1]*/, int64_t* unique_ids,
-                        int32_t* reverse, cudaStream_t st);
+                        int32_t* reverse, int64_t unique_cap, int64_t* status, cudaStream_t st);
 // Multi-tensor concat: ids get the 12-bit table prefix, offsets get the running nnz prefix.
 // desc = int64[4][F+1] on the device: id pointers, nnz prefix, offsets pointers (int32 offsets), segment prefix;
 // table_idx = int64[F].

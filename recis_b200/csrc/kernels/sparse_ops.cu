@@ -82,21 +82,25 @@ dedup_claim_kernel(const int64_t* __restrict__ ids, int64_t n, int world, uint64
 __global__ void __launch_bounds__(kThreads)
 dedup_assign_kernel(const int64_t* __restrict__ ids, int64_t n, int world, const int32_t* __restrict__ set_pos,
                     const int32_t* __restrict__ slot_in, const int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
-                    int64_t* __restrict__ unique_ids, int32_t* __restrict__ reverse) {
+                    int64_t* __restrict__ unique_ids, int32_t* __restrict__ reverse, int64_t unique_cap, int64_t* status) {
   extern __shared__ int32_t off[];  // [world+1]
   if (threadIdx.x == 0) {
     int32_t run = 0;
     for (int w = 0; w < world; ++w) { off[w] = run; run += counts[w]; }
     off[world] = run;
+    // more unique ids than the output buffer holds: flag it; positions beyond the buffer are dropped below (memory safe)
+    if (run > unique_cap && blockIdx.x == 0 && status) set_status(status, kStatusWindowOverflow);
   }
   __syncthreads();
-  if (blockIdx.x == 0) for (int w = threadIdx.x; w <= world; w += blockDim.x) offsets[w] = off[w];
+  // published boundaries are clamped to the buffer, so that nobody downstream reads or writes past it after an overflow
+  if (blockIdx.x == 0)
+    for (int w = threadIdx.x; w <= world; w += blockDim.x) offsets[w] = (int32_t)min((int64_t)off[w], unique_cap);
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const int32_t s = slot_in[i];
     const uint64_t key = (uint64_t)ids[i];
     const int32_t u = off[owner_of(key, world)] + set_pos[s & 0x7FFFFFFF];
-    reverse[i] = u;
-    if (s < 0) unique_ids[u] = (int64_t)key;
+    reverse[i] = u < unique_cap ? u : 0;
+    if (s < 0 && u < unique_cap) unique_ids[u] = (int64_t)key;
   }
 }
 
@@ -585,7 +589,7 @@ extern "C" {
 
 void rb_dedup_partition(const int64_t* ids, int64_t n, int world, uint64_t* set_keys, int32_t* set_pos, int64_t set_cap,
                         int32_t* slot_scratch, int32_t* counts, int32_t* offsets, int64_t* unique_ids, int32_t* reverse,
-                        cudaStream_t st) {
+                        int64_t unique_cap, int64_t* status, cudaStream_t st) {
   cudaMemsetAsync(counts, 0, sizeof(int32_t) * world, st);
   if (n <= 0) { cudaMemsetAsync(offsets, 0, sizeof(int32_t) * (world + 1), st); return; }
   cudaMemsetAsync(set_keys, 0xFF, sizeof(uint64_t) * set_cap, st);
@@ -595,7 +599,7 @@ void rb_dedup_partition(const int64_t* ids, int64_t n, int world, uint64_t* set_
                                                                       slot_scratch, counts);
   rb::note_launch();
   dedup_assign_kernel<<<g, kThreads, (world + 1) * sizeof(int32_t), st>>>(ids, n, world, set_pos, slot_scratch, counts, offsets,
-                                                                         unique_ids, reverse);
+                                                                         unique_ids, reverse, unique_cap, status);
   rb::note_launch();
 }
 
@@ -802,7 +806,7 @@ extern "C" int rb_dedup_partition_noalloc(const int64_t* ids, int64_t n, int wor
   cudaMemsetAsync(set_pos + cap, 0xFF, sizeof(int32_t), st);
   const int g = grid_stride_blocks(n);
   dedup_claim_kernel<<<g, kThreads, 2 * world * sizeof(int32_t), st>>>(ids, n, world, set_keys, set_pos, (uint64_t)cap - 1, slot, counts);
-  dedup_assign_kernel<<<g, kThreads, (world + 1) * sizeof(int32_t), st>>>(ids, n, world, set_pos, slot, counts, offsets, unique_ids, reverse);
+  dedup_assign_kernel<<<g, kThreads, (world + 1) * sizeof(int32_t), st>>>(ids, n, world, set_pos, slot, counts, offsets, unique_ids, reverse, n, nullptr);
   rb::note_launch(2);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { noalloc_fail(err, err_len, cudaGetErrorString(e)); return 6; }

@@ -62,6 +62,8 @@ class EmbeddingOption:
     # additions
     capacity: int = 0            # rows to pre-size the shard for (0: grow on demand)
     mean_by_weight: bool = False  # "mean" divides by the weight sum instead of the bag length
+    exchange_capacity: int = 0   # unique ids per rank and step the peer-memory exchange windows are sized for (0: twice
+                                 # the id count of the first batch); features merged into one table add up
 
     def __post_init__(self):
         if self.device is None:

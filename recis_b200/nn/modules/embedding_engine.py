@@ -48,13 +48,13 @@ class _Group:
         self.fea_runtime[fea_name] = opt.runtime_info()
         self.fea_child[fea_name] = self.children[opt.shared_name]
 
-    def embedding_option(self, capacity):
+    def embedding_option(self, capacity, exchange_capacity=0):
         o = self.opt
         return EmbeddingOption(
             embedding_dim=o.embedding_dim, block_size=o.block_size, dtype=o.dtype, device=o.device, shared_name=self.name,
             children=list(self.children.keys()), coalesced=True, initializer=o.initializer, grad_reduce_by=o.grad_reduce_by,
             fp16_enabled=o.fp16_enabled, filter_hook=o.filter_hook, pg=o.pg, max_partition_num=o.max_partition_num,
-            capacity=capacity, mean_by_weight=o.mean_by_weight,
+            capacity=capacity, mean_by_weight=o.mean_by_weight, exchange_capacity=exchange_capacity,
         )
 
 
@@ -80,10 +80,12 @@ class EmbeddingEngine(nn.Module):
                 self._groups[ht_name] = _Group(ht_name)
             self._groups[ht_name].add(fea_name, opt)
             self._fea_to_ht[fea_name] = ht_name
+        xcap = defaultdict(int)
         for fea_name, opt in emb_options.items():
             capacity[self._fea_to_ht[fea_name]] += int(opt.capacity or 0)
+            xcap[self._fea_to_ht[fea_name]] += int(opt.exchange_capacity or 0)
         for ht_name, group in self._groups.items():
-            self._ht[ht_name] = DynamicEmbedding(group.embedding_option(capacity[ht_name]))
+            self._ht[ht_name] = DynamicEmbedding(group.embedding_option(capacity[ht_name], xcap[ht_name]))
 
     # ------------------------------------------------------------------ helpers
     def tables(self):

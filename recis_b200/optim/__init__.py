@@ -1,4 +1,6 @@
 from .adamw_tf import AdamWTF
+from .dense_adam import DenseAdam, DenseAdamW
 from .sparse_optim import SparseAdagrad, SparseAdam, SparseAdamW, SparseAdamWTF, SparseOptimizer, SparseSGD
 
-__all__ = ["AdamWTF", "SparseAdam", "SparseAdamW", "SparseAdamWTF", "SparseAdagrad", "SparseSGD", "SparseOptimizer"]
+__all__ = ["AdamWTF", "DenseAdam", "DenseAdamW", "SparseAdam", "SparseAdamW", "SparseAdamWTF", "SparseAdagrad", "SparseSGD",
+           "SparseOptimizer"]

@@ -3,8 +3,9 @@
 ``param *= 1 - wd``; ``m, v`` moments; ``alpha = lr * sqrt(1 - b2^t) / (1 - b1^t)``;
 ``param -= alpha * m / (sqrt(v) + eps)`` (epsilon outside the bias correction), as the reference's
 ``recis/optim/adamw_tf.py:371-426`` and ``csrc/ops/adam_tf_op_kernel.cu:5-37``. ``fuse=True`` updates all
-parameters of a group with multi-tensor (foreach) calls: a handful of launches per step instead of several per
-parameter.
+parameters of a group together: on CUDA with ONE launch of the native multi-tensor kernel per 24 tensors
+(``csrc/kernels/dense_ops.cu``: weights, gradient and both moments are read once and written once), on CPU with
+multi-tensor (foreach) calls.
 """
 from __future__ import annotations
 
@@ -51,7 +52,12 @@ class AdamWTF(Optimizer):
                 continue
             step = self.state[params[0]]["step"]
             alpha = group["lr"] * math.sqrt(1 - beta2 ** step) / (1 - beta1 ** step)
-            if group["fuse"] and all(self.state[p]["step"] == step for p in params):
+            same_step = all(self.state[p]["step"] == step for p in params)
+            if group["fuse"] and same_step and all(p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and
+                                                   g.is_contiguous() for p, g in zip(params, grads)):
+                from .. import native
+                native().dense_adam(params, grads, ms, vs, [], beta1, beta2, group["eps"], 1 - group["weight_decay"], alpha, 1.0, 0.0)
+            elif group["fuse"] and same_step:
                 torch._foreach_mul_(params, 1 - group["weight_decay"])
                 torch._foreach_lerp_(ms, grads, 1 - beta1)
                 torch._foreach_mul_(vs, beta2)

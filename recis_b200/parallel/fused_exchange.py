@@ -110,9 +110,6 @@ class FusedExchange:
         lane = self.lanes.get(lane_key)
         if lane is None:                       # collective: every rank meets here at its first forward of this lane
             lane = self.lanes[lane_key] = _Lane(self, n)
-        if n > lane.send_cap:
-            raise RuntimeError(f"batch has {n} ids but the exchange window holds {lane.send_cap}; set exchange_capacity "
-                               f"(EmbeddingOption) or RECIS_EXCHANGE_CAPACITY to the largest per-rank id count")
         if lane.pending_grad_epoch and not self.immediate_reduce:
             # the previous backward of this lane is still staged (gradient accumulation without set_grad_accum_steps):
             # consume it now, before this step's backward rewrites the gradient window
@@ -121,7 +118,8 @@ class FusedExchange:
         lane.epoch += 1
         e = lane.epoch
         store = emb_mod.impl.store
-        _uniq, rev, _counts, _offs = C.dedup_partition(ids, W, h["ids"].tensor, h["offsets"].tensor)
+        # more unique ids than the window holds sets the overflow bit in self.status (see check()); nothing is written out of bounds
+        _uniq, rev, _counts, _offs = C.dedup_partition(ids, W, h["ids"].tensor, h["offsets"].tensor, self.status)
         C.comm_signal(h["flags"].ptrs, CH_IDS, me, e)
         C.comm_wait(h["flags"].tensor, CH_IDS, W, e, self.wait_us, self.status)
         C.comm_pull_ids(h["ids"].ptrs, h["offsets"].ptrs, me, lane.ids_in, lane.prefix, lane.n_in, self.status)

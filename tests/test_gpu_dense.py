@@ -88,3 +88,45 @@ def test_mlp_matches_reference(dims):
     for (name, p), r in zip(mlp.named_parameters(), ref_params):
         assert rel(p.grad, r.grad) < 3e-2, (name, rel(p.grad, r.grad))
     assert recis_b200.native().dense_status(DEV) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("decoupled", [False, True])
+def test_dense_adam_matches_torch(decoupled):
+    """Native multi-tensor Adam/AdamW against torch.optim on the same gradients (30 tensors: two launches, odd sizes)."""
+    from recis_b200.optim import DenseAdam
+    torch.manual_seed(0)
+    shapes = [(37,), (128, 65), (3,), (1024, 16)] * 7 + [(5, 5), (1,)]
+    ours = [torch.randn(s, device="cuda").requires_grad_() for s in shapes]
+    ref = [p.detach().clone().requires_grad_() for p in ours]
+    wd = 0.01
+    o1 = DenseAdam(ours, lr=1e-2, weight_decay=wd, decoupled=decoupled)
+    o2 = (torch.optim.AdamW if decoupled else torch.optim.Adam)(ref, lr=1e-2, weight_decay=wd)
+    for _ in range(5):
+        for a, b in zip(ours, ref):
+            g = torch.randn_like(a)
+            a.grad = g.clone()
+            b.grad = g.clone()
+        o1.step()
+        o2.step()
+    for a, b in zip(ours, ref):
+        torch.testing.assert_close(a, b, rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.gpu
+def test_adamw_tf_native_matches_cpu_foreach():
+    from recis_b200.optim import AdamWTF
+    torch.manual_seed(1)
+    shapes = [(33, 7), (256,), (2, 3, 5)]
+    cpu = [torch.randn(s).requires_grad_() for s in shapes]
+    gpu = [p.detach().cuda().requires_grad_() for p in cpu]
+    o1, o2 = AdamWTF(cpu, lr=1e-2, weight_decay=0.02), AdamWTF(gpu, lr=1e-2, weight_decay=0.02)
+    for _ in range(4):
+        for a, b in zip(cpu, gpu):
+            g = torch.randn_like(a)
+            a.grad = g.clone()
+            b.grad = g.cuda()
+        o1.step()
+        o2.step()
+    for a, b in zip(cpu, gpu):
+        torch.testing.assert_close(a, b.cpu(), rtol=2e-5, atol=2e-6)

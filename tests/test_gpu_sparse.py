@@ -202,3 +202,25 @@ def test_filter_hook_gpu():
 def test_smoke_entry():
     import __graft_entry__ as ge
     ge.smoke()
+
+
+@pytest.mark.gpu
+def test_dedup_partition_overflow_is_flagged_and_memory_safe():
+    """A unique-id buffer smaller than the batch's unique count: the status bit is set, boundaries are clamped to the
+    buffer and the guard cells behind the buffer stay untouched."""
+    C = recis_b200.native()
+    ids = torch.arange(0, 5000, dtype=torch.int64, device="cuda") * 7919
+    buf = torch.full((1200,), -7, dtype=torch.int64, device="cuda")
+    window, guard = buf[:1000], buf[1000:]
+    offsets = torch.zeros(5, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int64, device="cuda")
+    _u, rev, _c, _o = C.dedup_partition(ids, 4, window, offsets, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 8
+    assert int(offsets.max()) <= 1000 and int(rev.max()) < 1000
+    assert bool((guard == -7).all())
+    # the same call with room for every id leaves the status word clean
+    status.zero_()
+    big = torch.empty(5000, dtype=torch.int64, device="cuda")
+    C.dedup_partition(ids, 4, big, offsets, status)
+    assert int(status.item()) == 0 and int(offsets[-1]) == 5000

@@ -296,3 +296,22 @@ def test_initializers_distribution(init, check):
     ht = HashTable([16], initializer=init, name=f"t_init_{type(init).__name__}", device="cpu")
     e = ht(torch.arange(2000))
     assert check(e.detach())
+
+
+@pytest.mark.parametrize("decoupled", [False, True])
+def test_dense_adam_cpu_matches_torch(decoupled):
+    from recis_b200.optim import DenseAdam
+    torch.manual_seed(0)
+    a = [torch.randn(5, 3).requires_grad_(), torch.randn(7).requires_grad_()]
+    b = [p.detach().clone().requires_grad_() for p in a]
+    o1 = DenseAdam(a, lr=1e-2, weight_decay=0.01, decoupled=decoupled)
+    o2 = (torch.optim.AdamW if decoupled else torch.optim.Adam)(b, lr=1e-2, weight_decay=0.01)
+    for _ in range(4):
+        for x, y in zip(a, b):
+            g = torch.randn_like(x)
+            x.grad = g.clone()
+            y.grad = g.clone()
+        o1.step()
+        o2.step()
+    for x, y in zip(a, b):
+        torch.testing.assert_close(x, y, rtol=1e-6, atol=1e-7)
