@@ -80,15 +80,17 @@ def main():
 
     # ---- table: lookup-or-insert of 2 M ids into a 16 M-row, width-128 store (half of them new)
     store = C.EmbeddingStore(128, 16_000_000 // (4 * small - 3), "cuda:0", 2, 0.0, 0.01, -2.0, 2.0, 1, False, False, None)
-    ids_a = torch.randint(0, 1 << 40, (2_000_000,), device=dev)
+    n_ids = 2_000_000 // small
+    ids_a = torch.randint(0, 1 << 40, (n_ids,), device=dev)
     store.lookup_or_insert(ids_a, None, None, 0)
+    fresh = [torch.cat([ids_a[:n_ids // 2], torch.randint(0, 1 << 40, (n_ids // 2,), device=dev) + k])
+             for k in range(args.warmup + args.iters + 1)]
     state = {"k": 0}
 
     def lookup():
         state["k"] += 1
-        ids = torch.cat([ids_a[:1_000_000], torch.randint(0, 1 << 40, (1_000_000,), device=dev) + state["k"]])
-        return store.lookup_or_insert(ids, None, None, 0)
-    run("table_lookup_or_insert_2M", lookup, bytes_=1_000_000 * 512 + 2_000_000 * 28)
+        return store.lookup_or_insert(fresh[state["k"] % len(fresh)], None, None, 0)
+    run("table_lookup_or_insert_2M", lookup, bytes_=n_ids // 2 * 512 + n_ids * 28)
 
     # ---- dedup + owner bucketing of 4 M ids (Zipf-like duplicates), 8 owners
     raw = (torch.rand(4_000_000, device=dev, dtype=torch.float64) ** 6 * (1 << 34)).to(torch.int64)
@@ -136,9 +138,14 @@ def main():
     x = torch.randn(B, 128, device=dev).to(torch.bfloat16)
     cols = (128 + 27 * 26 // 2 + 7) // 8 * 8
     run("dot_interaction_fwd_b8192_f27_d128", lambda: C.dot_interaction_fwd(x, cube, cols), bytes_=B * 26 * 512 + B * cols * 2,
-        flops=2.0 * B * 27 * 27 * 128 / 2, flush_l2=True)
+        flush_l2=True)
+    dz = torch.randn(B, cols, device=dev).to(torch.bfloat16)
+    run("dot_interaction_bwd_b8192_f27_d128", lambda: C.dot_interaction_bwd(x, cube, dz), bytes_=2 * B * 26 * 512 + B * cols * 2 + B * 768,
+        flush_l2=True)
     cube_fm = torch.randn(65536, 39, 16, device=dev)
     run("fm_fwd_b65536_f39_d16", lambda: C.fm_fwd(cube_fm), bytes_=65536 * 39 * 64, flush_l2=True)
+    gfm = torch.randn(65536, 1, device=dev)
+    run("fm_bwd_b65536_f39_d16", lambda: C.fm_bwd(cube_fm, gfm), bytes_=2 * 65536 * 39 * 64, flush_l2=True)
 
     # ---- tcgen05 GEMMs of the dense tower (bf16 in, fp32 accumulate)
     def gemm_case(name, M, N, K):

@@ -63,8 +63,12 @@ Tensor dot_interaction_fwd(const Tensor& x, const Tensor& cube, int64_t out_cols
   TORCH_CHECK(x.size(0) == B && x.size(1) == D && out_cols >= D + (F + 1) * F / 2);
   c10::cuda::CUDAGuard g(x.device());
   auto out = torch::empty({B, out_cols}, x.options());
-  const int rc = rb_dot_interaction_fwd(x.data_ptr(), cube.data_ptr<float>(), B, F, D, (int)out_cols, out.data_ptr(),
-                                        at::cuda::getCurrentCUDAStream());
+  // tensor-core kernel when the shape allows (at most 31 fields, width 64 or 128), SIMT kernel otherwise
+  int rc = rb_dot_interaction_tc_fwd(x.data_ptr(), cube.data_ptr<float>(), B, F, D, (int)out_cols, out.data_ptr(),
+                                     status_word(x.device()).data_ptr<int64_t>(), at::cuda::getCurrentCUDAStream());
+  if (rc == 1)
+    rc = rb_dot_interaction_fwd(x.data_ptr(), cube.data_ptr<float>(), B, F, D, (int)out_cols, out.data_ptr(),
+                                at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(rc == 0, "dot_interaction: too many fields or too wide for shared memory (code ", rc, ")");
   return out;
 }
@@ -75,8 +79,12 @@ std::tuple<Tensor, Tensor> dot_interaction_bwd(const Tensor& x, const Tensor& cu
   c10::cuda::CUDAGuard g(x.device());
   auto dx = torch::empty({B, D}, cube.options());
   auto dcube = torch::empty_like(cube);
-  const int rc = rb_dot_interaction_bwd(x.data_ptr(), cube.data_ptr<float>(), dout.data_ptr(), B, F, D, (int)dout.size(1),
-                                        dx.data_ptr<float>(), dcube.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
+  int rc = rb_dot_interaction_tc_bwd(x.data_ptr(), cube.data_ptr<float>(), dout.data_ptr(), B, F, D, (int)dout.size(1),
+                                     dx.data_ptr<float>(), dcube.data_ptr<float>(), status_word(x.device()).data_ptr<int64_t>(),
+                                     at::cuda::getCurrentCUDAStream());
+  if (rc == 1)
+    rc = rb_dot_interaction_bwd(x.data_ptr(), cube.data_ptr<float>(), dout.data_ptr(), B, F, D, (int)dout.size(1),
+                                dx.data_ptr<float>(), dcube.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(rc == 0, "dot_interaction backward failed (code ", rc, ")");
   return {dx, dcube};
 }

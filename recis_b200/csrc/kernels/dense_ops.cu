@@ -8,6 +8,7 @@
 #include "../common/rb_launch.h"
 #include "rb_dense.h"
 #include <cuda_bf16.h>
+#include <type_traits>
 
 namespace {
 
@@ -83,7 +84,65 @@ dot_interaction_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __r
 }
 
 // ---------------------------------------------------------------------------------- FM second-order term
-// out[b] = 0.5 * sum_d ((sum_f w_f v_fd)^2 - sum_f (w_f v_fd)^2); cube [B, F, D] fp32 (weights already applied by the caller)
+// out[b] = 0.5 * sum_d ((sum_f v_fd)^2 - sum_f v_fd^2); cube [B, F, D] fp32 (weights already applied by the caller).
+// One thread owns one float4 column group of one sample, so a warp covers 32 / (D/4) samples and every 32-byte sector it
+// touches is used in full (narrow embeddings, D = 8 .. 32, are the common case for FM); the D/4 partial results of a sample
+// are combined with shuffles. Q = D/4 must be a power of two <= 32; other widths take the generic kernel below.
+template <int Q>
+__global__ void __launch_bounds__(256)
+fm_fwd_vec_kernel(const float* __restrict__ cube, int B, int F, float* __restrict__ out) {
+  constexpr int D = Q * 4;
+  const int64_t total = (int64_t)B * Q;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  // the loop bound is rounded up to a whole warp so that the shuffles below always have all lanes present
+  const int64_t total_pad = (total + 31) / 32 * 32;
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total_pad; t += stride) {
+    const bool live = t < total;
+    const int64_t b = t / Q; const int q = (int)(t - b * Q);
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    float s2 = 0.f;
+    if (live) {
+      const float* p = cube + b * F * D + q * 4;
+#pragma unroll 4
+      for (int f = 0; f < F; ++f) {
+        const float4 v = *reinterpret_cast<const float4*>(p + (int64_t)f * D);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        s2 = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, s2))));
+      }
+    }
+    float part = s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w - s2;
+#pragma unroll
+    for (int o = Q / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (live && q == 0) out[b] = 0.5f * part;
+  }
+}
+
+// dcube[b,f,d] = g[b] * (S_d - v_fd), same thread mapping
+template <int Q>
+__global__ void __launch_bounds__(256)
+fm_bwd_vec_kernel(const float* __restrict__ cube, const float* __restrict__ gout, int B, int F, float* __restrict__ dcube) {
+  constexpr int D = Q * 4;
+  const int64_t total = (int64_t)B * Q;
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t b = t / Q; const int q = (int)(t - b * Q);
+    const float* p = cube + b * F * D + q * 4;
+    float* o = dcube + b * F * D + q * 4;
+    const float g = gout[b];
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int f = 0; f < F; ++f) {
+      const float4 v = *reinterpret_cast<const float4*>(p + (int64_t)f * D);
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+#pragma unroll 4
+    for (int f = 0; f < F; ++f) {
+      const float4 v = *reinterpret_cast<const float4*>(p + (int64_t)f * D);      // second pass hits L1/L2
+      *reinterpret_cast<float4*>(o + (int64_t)f * D) = make_float4(g * (s.x - v.x), g * (s.y - v.y), g * (s.z - v.z), g * (s.w - v.w));
+    }
+  }
+}
+
+// generic widths: one block per sample
 __global__ void __launch_bounds__(128)
 fm_fwd_kernel(const float* __restrict__ cube, int B, int F, int D, float* __restrict__ out) {
   __shared__ float red[4];
@@ -100,7 +159,6 @@ fm_fwd_kernel(const float* __restrict__ cube, int B, int F, int D, float* __rest
   if (threadIdx.x == 0) out[b] = 0.5f * (red[0] + red[1] + red[2] + red[3]);
 }
 
-// dcube[b,f,d] = g[b] * (S_d - v_fd)
 __global__ void __launch_bounds__(128)
 fm_bwd_kernel(const float* __restrict__ cube, const float* __restrict__ gout, int B, int F, int D, float* __restrict__ dcube) {
   const int b = blockIdx.x;
@@ -112,6 +170,20 @@ fm_bwd_kernel(const float* __restrict__ cube, const float* __restrict__ gout, in
       const int64_t o = ((int64_t)b * F + f) * D + d;
       dcube[o] = g * (s - cube[o]);
     }
+  }
+}
+
+template <typename Fn>
+inline bool fm_dispatch_q(int D, const void* p0, const void* p1, Fn&& fn) {
+  if (D % 4 != 0 || (reinterpret_cast<uintptr_t>(p0) & 15) || (reinterpret_cast<uintptr_t>(p1) & 15)) return false;
+  switch (D / 4) {
+    case 1: fn(std::integral_constant<int, 1>{}); return true;
+    case 2: fn(std::integral_constant<int, 2>{}); return true;
+    case 4: fn(std::integral_constant<int, 4>{}); return true;
+    case 8: fn(std::integral_constant<int, 8>{}); return true;
+    case 16: fn(std::integral_constant<int, 16>{}); return true;
+    case 32: fn(std::integral_constant<int, 32>{}); return true;
+    default: return false;
   }
 }
 
@@ -185,13 +257,23 @@ int rb_dot_interaction_bwd(const void* x, const float* cube, const void* dout, i
 
 void rb_fm_fwd(const float* cube, int B, int F, int D, float* out, cudaStream_t st) {
   if (B <= 0) return;
-  fm_fwd_kernel<<<B, 128, 0, st>>>(cube, B, F, D, out);
+  const bool vec = fm_dispatch_q(D, cube, cube, [&](auto q) {
+    constexpr int Q = decltype(q)::value;
+    const int64_t blocks = ((int64_t)B * Q + 255) / 256;
+    fm_fwd_vec_kernel<Q><<<(int)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, st>>>(cube, B, F, out);
+  });
+  if (!vec) fm_fwd_kernel<<<B, 128, 0, st>>>(cube, B, F, D, out);
   rb::note_launch();
 }
 
 void rb_fm_bwd(const float* cube, const float* gout, int B, int F, int D, float* dcube, cudaStream_t st) {
   if (B <= 0) return;
-  fm_bwd_kernel<<<B, 128, 0, st>>>(cube, gout, B, F, D, dcube);
+  const bool vec = fm_dispatch_q(D, cube, dcube, [&](auto q) {
+    constexpr int Q = decltype(q)::value;
+    const int64_t blocks = ((int64_t)B * Q + 255) / 256;
+    fm_bwd_vec_kernel<Q><<<(int)(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, st>>>(cube, gout, B, F, dcube);
+  });
+  if (!vec) fm_bwd_kernel<<<B, 128, 0, st>>>(cube, gout, B, F, D, dcube);
   rb::note_launch();
 }
 

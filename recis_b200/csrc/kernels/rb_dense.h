@@ -29,6 +29,12 @@ extern "C" {
 int rb_dot_interaction_fwd(const void* x, const float* cube, int B, int F, int D, int out_ld, void* out, cudaStream_t st);
 int rb_dot_interaction_bwd(const void* x, const float* cube, const void* dout, int B, int F, int D, int out_ld, float* dx, float* dcube,
                            cudaStream_t st);
+// Tensor-core (tcgen05) versions for at most 31 fields and D in {64, 128}. Return 0 = ran, 1 = shape outside their range
+// (call the SIMT version instead), > 1 = launch error. A bounded wait that ran out sets the timeout bit in *status.
+int rb_dot_interaction_tc_fwd(const void* x, const float* cube, int B, int F, int D, int out_ld, void* out, int64_t* status,
+                              cudaStream_t st);
+int rb_dot_interaction_tc_bwd(const void* x, const float* cube, const void* dout, int B, int F, int D, int out_ld, float* dx,
+                              float* dcube, int64_t* status, cudaStream_t st);
 void rb_fm_fwd(const float* cube, int B, int F, int D, float* out, cudaStream_t st);
 void rb_fm_bwd(const float* cube, const float* gout, int B, int F, int D, float* dcube, cudaStream_t st);
 // dy = relu ? dout * (y > 0) : dout (bf16, may be null to skip the store); db[n] += column sums of dy (fp32, may be null)

@@ -17,7 +17,7 @@ def _ref_dot(x, cube):
     return torch.cat([x, zz[:, li, lj]], dim=1)
 
 
-@pytest.mark.parametrize("B,F,Dm", [(64, 26, 128), (33, 3, 16), (8, 1, 8)])
+@pytest.mark.parametrize("B,F,Dm", [(64, 26, 128), (130, 26, 64), (5, 31, 128), (33, 3, 16), (8, 1, 8)])
 def test_dot_interaction_fwd_bwd(B, F, Dm):
     torch.manual_seed(0)
     x = torch.randn(B, Dm).to(torch.bfloat16)
@@ -39,15 +39,16 @@ def test_dot_interaction_fwd_bwd(B, F, Dm):
 
 def test_fm_interaction():
     torch.manual_seed(0)
-    cube = torch.randn(50, 7, 16)
-    cr = cube.clone().requires_grad_(True)
-    ref = D.fm_interaction(cr)
-    cg = cube.to(DEV).requires_grad_(True)
-    out = D.fm_interaction(cg)
-    assert torch.allclose(out.cpu(), ref, atol=1e-4, rtol=1e-4)
-    g = torch.randn(50, 1)
-    ref.backward(g); out.backward(g.to(DEV))
-    assert torch.allclose(cg.grad.cpu(), cr.grad, atol=1e-4, rtol=1e-4)
+    for shape in [(50, 7, 16), (1000, 39, 16), (33, 5, 12), (17, 3, 128), (9, 4, 7)]:
+        cube = torch.randn(*shape)
+        cr = cube.clone().requires_grad_(True)
+        ref = D.fm_interaction(cr)
+        cg = cube.to(DEV).requires_grad_(True)
+        out = D.fm_interaction(cg)
+        assert torch.allclose(out.cpu(), ref, atol=2e-4, rtol=1e-4), shape
+        g = torch.randn(shape[0], 1)
+        ref.backward(g); out.backward(g.to(DEV))
+        assert torch.allclose(cg.grad.cpu(), cr.grad, atol=1e-4, rtol=1e-4), shape
 
 
 def _torch_bf16_mlp(mlp, x):
