@@ -458,11 +458,13 @@ std::vector<Tensor> fused_mod(const std::vector<Tensor>& values, const std::vect
   auto dev = values[0].device();
   c10::OptionalDeviceGuard guard(dev);
   std::vector<Tensor> v(T);
-  std::vector<std::vector<int64_t>> rows(3, std::vector<int64_t>(T + 1, 0));
+  std::vector<std::vector<int64_t>> rows(4, std::vector<int64_t>(T + 1, 0));
   for (int t = 0; t < T; ++t) {
     TORCH_CHECK(mods[t] > 0, "modulus must be positive");
     v[t] = as_i64(values[t]);
     rows[0][t] = (int64_t)v[t].data_ptr(); rows[1][t + 1] = rows[1][t] + v[t].numel(); rows[2][t] = mods[t];
+    // floor(2^64 / m): the kernel replaces the 64-bit division by a multiply-high with this constant
+    rows[3][t] = mods[t] == 1 ? 0 : (int64_t)(uint64_t)((((unsigned __int128)1) << 64) / (unsigned __int128)(uint64_t)mods[t]);
   }
   const int64_t total = rows[1][T];
   auto out = torch::empty({total}, torch::TensorOptions().dtype(torch::kInt64).device(dev));

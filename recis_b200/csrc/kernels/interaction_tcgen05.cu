@@ -39,7 +39,7 @@ __device__ __forceinline__ void stage_sample(uint8_t* tile, int w, int lane, con
   uint8_t* base = tile + (c >> 6) * kTileChunk;
   const int cc = c & 63;
   const bool live = b < B;
-#pragma unroll 4
+#pragma unroll 8
   for (int i = 0; i < kVP; ++i) {
     uint2 v = make_uint2(0u, 0u);
     if (live && i == 0) {
