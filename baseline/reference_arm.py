@@ -123,6 +123,12 @@ class ReferenceArm:
                 out[k] = v.to(dev, non_blocking=True)
         return out
 
+    def feeder(self, host_batches, dev):
+        # stock path: the reference's Trainer copies each batch right before its step (recis/framework/trainer.py,
+        # copy_data_to_device on the current stream); it has no device prefetcher outside its column-io packer
+        for b in host_batches:
+            yield self.to_device(b, dev)
+
     def step(self, st, batch):
         embs = st["sparse"]({f: batch[f] for f in st["fields"]})
         logit = st["dense"](batch["dense"], [embs[f] for f in st["fields"]])

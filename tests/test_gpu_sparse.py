@@ -224,3 +224,16 @@ def test_dedup_partition_overflow_is_flagged_and_memory_safe():
     big = torch.empty(5000, dtype=torch.int64, device="cuda")
     C.dedup_partition(ids, 4, big, offsets, status)
     assert int(status.item()) == 0 and int(offsets[-1]) == 5000
+
+
+@pytest.mark.gpu
+def test_device_prefetcher_orders_and_copies():
+    from recis_b200.io import DevicePrefetcher
+    src = [{"a": (torch.arange(1000) + i).pin_memory(),
+            "r": RaggedTensor((torch.arange(40) * i).pin_memory(), [torch.arange(0, 41, 4, dtype=torch.int32).pin_memory()])}
+           for i in range(7)]
+    got = []
+    for b in DevicePrefetcher(src, "cuda", depth=3):
+        assert b["a"].is_cuda and b["r"].values().is_cuda
+        got.append((int(b["a"].sum()), int(b["r"].values().sum())))
+    assert got == [(int((torch.arange(1000) + i).sum()), int((torch.arange(40) * i).sum())) for i in range(7)]
