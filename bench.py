@@ -204,6 +204,8 @@ def run(args, arm):
         feeder = arm.feeder(host[first:first + count], dev)       # created inside the region: all `count` copies are timed
         for batch in feeder:
             loss = arm.step(state, batch)
+            if hasattr(feeder, "prefetch"):
+                feeder.prefetch()            # next batches' copies are issued while the GPU works on this step
             losses.append(float(loss))       # device -> host read of the step's result
         e1.record()
         torch.cuda.synchronize()

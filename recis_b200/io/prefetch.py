@@ -6,6 +6,7 @@ stream, followed by a prefetch stage (``third_party/column-io``: ``dataset/packe
 
 * ``depth`` batches are in flight; each is copied from (ideally pinned) host memory with non-blocking copies on the copy
   stream and fenced by a CUDA event;
+* ``prefetch()`` (called by the training loop once the current step is queued) issues the copies of the next batches;
 * ``next()`` makes the consumer's stream wait for that event (no host synchronisation) and tells the caching allocator that
   the consumer's stream uses the memory (``record_stream``), so the buffers are not recycled under a running kernel.
 """
@@ -78,7 +79,10 @@ class DevicePrefetcher:
             for t in _tensors(batch):
                 if t.is_cuda:
                     t.record_stream(cur)
-        # keep the pipeline full: the copy of a later batch starts before this one is consumed
+        return batch
+
+    def prefetch(self):
+        """Top the pipeline up. Call it right after the current step's kernels have been queued: the host then issues the
+        copies of the next batches while the GPU is busy, instead of delaying the start of the next step."""
         while len(self.queue) < self.depth and not self.exhausted:
             self._issue()
-        return batch
