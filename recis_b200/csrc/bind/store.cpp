@@ -87,11 +87,12 @@ void EmbeddingStore::refresh_bounds() {
 // Asynchronous counter mirror: after every lookup-or-insert the 64-byte counter block is copied to pinned host memory on the
 // same stream. ensure_room() takes the newest copy that has already landed (cudaEventQuery, never a wait) as the truth and
 // only adds the ids issued since then, so the pessimistic bound is at most a step or two ahead of reality.
-void EmbeddingStore::post_mirror(int64_t n_issued) {
+void EmbeddingStore::post_mirror(int64_t n_issued, const int32_t* n_dev) {
   issued_total_ += n_issued;
   if (!device_.is_cuda()) return;
   if (mirror_host_ == nullptr) {
-    if (cudaHostAlloc(reinterpret_cast<void**>(&mirror_host_), sizeof(int64_t) * RB_CTR_COUNT * kMirror, cudaHostAllocDefault) != cudaSuccess) {
+    // per slot: the counter block, then one more word that receives the device-side id count of the call (int32 in its low half)
+    if (cudaHostAlloc(reinterpret_cast<void**>(&mirror_host_), sizeof(int64_t) * kMirrorStride * kMirror, cudaHostAllocDefault) != cudaSuccess) {
       mirror_host_ = nullptr;
       return;
     }
@@ -99,7 +100,13 @@ void EmbeddingStore::post_mirror(int64_t n_issued) {
   }
   const int slot = (int)(mirror_head_++ % kMirror);
   auto st = at::cuda::getCurrentCUDAStream();
-  cudaMemcpyAsync(mirror_host_ + slot * RB_CTR_COUNT, ctr_.data_ptr<int64_t>(), sizeof(int64_t) * RB_CTR_COUNT, cudaMemcpyDeviceToHost, st);
+  int64_t* dst = mirror_host_ + slot * kMirrorStride;
+  dst[RB_CTR_COUNT] = -1;                                   // "no device-side count in this slot"
+  cudaMemcpyAsync(dst, ctr_.data_ptr<int64_t>(), sizeof(int64_t) * RB_CTR_COUNT, cudaMemcpyDeviceToHost, st);
+  if (n_dev != nullptr) {
+    dst[RB_CTR_COUNT] = 0;
+    cudaMemcpyAsync(dst + RB_CTR_COUNT, n_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+  }
   cudaEventRecord(mirror_ev_[slot], st);
   mirror_issued_[slot] = issued_total_;
 }
@@ -110,7 +117,10 @@ void EmbeddingStore::absorb_mirror() {
     const int slot = (int)((mirror_head_ - back) % kMirror);
     if (mirror_issued_[slot] < 0 || mirror_issued_[slot] <= absorbed_issued_) break;
     if (cudaEventQuery(mirror_ev_[slot]) != cudaSuccess) continue;
-    const int64_t* c = mirror_host_ + slot * RB_CTR_COUNT;
+    const int64_t* c = mirror_host_ + slot * kMirrorStride;
+    TORCH_CHECK((c[RB_CTR_STATUS] & 3) == 0, "embedding store '", name_, "' reported status ", c[RB_CTR_STATUS],
+                " (1 = row arena exhausted, 2 = index full) in an earlier step; raise the capacity");
+    if (c[RB_CTR_COUNT] >= 0) seen_n_dev_ = std::max<int64_t>(seen_n_dev_ * 7 / 8, c[RB_CTR_COUNT] & 0xFFFFFFFFll);   // decaying maximum
     const int64_t pending = issued_total_ - mirror_issued_[slot];
     rows_upper_ = std::max<int64_t>(c[RB_CTR_BUMP] - c[RB_CTR_FREE_TOP], 0) + pending;
     index_upper_ = c[RB_CTR_LIVE] + c[RB_CTR_TOMBSTONES] + c[RB_CTR_PROBATION] + pending;
@@ -177,7 +187,26 @@ torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::op
   auto i32 = torch::TensorOptions().dtype(torch::kInt32).device(device_);
   auto rows_out = torch::empty({n}, i32);
   if (n == 0) return rows_out;
-  ensure_room(n);
+  // How many ids may be new? With a device-side count the buffer length n is only the window capacity, often many times
+  // the real count; budgeting room for all of it would force a (synchronising) look at the true counters, or a growth,
+  // on every call. The counts of earlier calls come back through the asynchronous mirror: budget for their recent maximum
+  // plus a quarter. Should a call exceed that AND the arena be full, the kernel's bounds guard sets the status word
+  // (no row is written out of range) and a later call reports it.
+  int64_t n_budget = n;
+  if (n_dev.has_value() && device_.is_cuda()) {
+    absorb_mirror();
+    if (seen_n_dev_ == 0) {
+      // no count has come back yet (first calls only): read this call's count directly, which synchronises once
+      int32_t now = 0;
+      c10::cuda::CUDAGuard g(device_);
+      auto st = at::cuda::getCurrentCUDAStream();
+      if (cudaMemcpyAsync(&now, n_dev->data_ptr<int32_t>(), sizeof(int32_t), cudaMemcpyDeviceToHost, st) == cudaSuccess &&
+          cudaStreamSynchronize(st) == cudaSuccess && now > 0)
+        seen_n_dev_ = now;
+    }
+    if (seen_n_dev_ > 0) n_budget = std::min<int64_t>(n, seen_n_dev_ + seen_n_dev_ / 4 + 65536);
+  }
+  ensure_room(n_budget);
   auto slot_scratch = torch::empty({n}, i32);
   auto new_rows = torch::empty({n}, i32);
   auto new_keys = torch::empty({n}, i32.dtype(torch::kInt64));
@@ -194,7 +223,7 @@ torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::op
                                new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr<float>(), (int)dim_, init_, ls,
                                sd, (int)admit_threshold);
   }
-  post_mirror(n);
+  post_mirror(n_budget, nd);
   return rows_out;
 }
 

@@ -53,7 +53,9 @@ class EmbeddingStore {
   int64_t rows_upper_ = 0, bump_upper_ = 0, index_upper_ = 0;
   // asynchronous counter mirror (pinned host copies of the device counters, see store.cpp)
   static constexpr int kMirror = 8;
-  void post_mirror(int64_t n_issued);
+  static constexpr int kMirrorStride = RB_CTR_COUNT + 1;
+  void post_mirror(int64_t n_issued, const int32_t* n_dev = nullptr);
+  int64_t seen_n_dev_ = 0;          // recent maximum of the device-side id counts of lookup_or_insert calls
   void absorb_mirror();
   int64_t* mirror_host_ = nullptr;
   cudaEvent_t mirror_ev_[kMirror];
