@@ -109,6 +109,7 @@ void EmbeddingStore::post_mirror(int64_t n_issued, const int32_t* n_dev) {
   }
   cudaEventRecord(mirror_ev_[slot], st);
   mirror_issued_[slot] = issued_total_;
+  mirror_calls_[slot] = calls_total_;
 }
 
 void EmbeddingStore::absorb_mirror() {
@@ -122,24 +123,41 @@ void EmbeddingStore::absorb_mirror() {
                 " (1 = row arena exhausted, 2 = index full) in an earlier step; raise the capacity");
     if (c[RB_CTR_COUNT] >= 0) seen_n_dev_ = std::max<int64_t>(seen_n_dev_ * 7 / 8, c[RB_CTR_COUNT] & 0xFFFFFFFFll);   // decaying maximum
     const int64_t pending = issued_total_ - mirror_issued_[slot];
-    rows_upper_ = std::max<int64_t>(c[RB_CTR_BUMP] - c[RB_CTR_FREE_TOP], 0) + pending;
-    index_upper_ = c[RB_CTR_LIVE] + c[RB_CTR_TOMBSTONES] + c[RB_CTR_PROBATION] + pending;
+    const int64_t rows_now = std::max<int64_t>(c[RB_CTR_BUMP] - c[RB_CTR_FREE_TOP], 0);
+    const int64_t index_now = c[RB_CTR_LIVE] + c[RB_CTR_TOMBSTONES] + c[RB_CTR_PROBATION];
+    // how many rows / index entries one call really adds (decaying maximum over the calls seen so far)
+    if (rows_prev_ >= 0 && mirror_calls_[slot] > calls_prev_) {
+      const int64_t calls = mirror_calls_[slot] - calls_prev_;
+      const int64_t grown = std::max<int64_t>(std::max(rows_now - rows_prev_, index_now - index_prev_), 0);
+      const int64_t per_call = (grown + calls - 1) / calls;
+      est_new_ = std::max<int64_t>(est_new_ < 0 ? 0 : est_new_ * 7 / 8, per_call);
+    }
+    rows_prev_ = rows_now; index_prev_ = index_now; calls_prev_ = mirror_calls_[slot];
+    rows_upper_ = rows_now + pending;
+    index_upper_ = index_now + pending;
     absorbed_issued_ = mirror_issued_[slot];
     break;
   }
 }
 
 void EmbeddingStore::ensure_room(int64_t n_incoming) {
-  // Pessimistic: every incoming id may be new. Only when the bound crosses the capacity do we look at the truth.
+  // rows_upper_ / index_upper_ = the newest counters that came back through the mirror + what was budgeted for the calls issued
+  // since. Without history (first calls, CPU stores) a bound that crosses the capacity makes us read the true counters, which
+  // synchronises; with history we act on the bounds as they are: growing a little early costs memory, never a stall.
   absorb_mirror();
+  const bool lagged_ok = device_.is_cuda() && est_new_ >= 0;
   if (rows_upper_ + n_incoming > cap_rows_ || index_upper_ + n_incoming > (int64_t)(0.65 * keys_.numel())) {
-    refresh_bounds();
+    if (!lagged_ok) refresh_bounds();
     if (rows_upper_ + n_incoming > cap_rows_) {
-      TORCH_CHECK(growable_, "embedding store '", name_, "' is full (", rows_upper_, " rows of ", cap_rows_,
-                  ") and cannot grow: it was created with fixed (peer-mapped) storage");
-      int64_t nc = cap_rows_;
-      while (rows_upper_ + n_incoming > nc) nc = nc + nc / 2 + 1024;
-      reserve(nc);
+      if (!growable_) {
+        if (lagged_ok) refresh_bounds();          // fixed storage: make sure before failing
+        TORCH_CHECK(rows_upper_ + n_incoming <= cap_rows_, "embedding store '", name_, "' is full (", rows_upper_, " rows of ", cap_rows_,
+                    ") and cannot grow: it was created with fixed (peer-mapped) storage");
+      } else {
+        int64_t nc = cap_rows_;
+        while (rows_upper_ + n_incoming > nc) nc = nc + nc / 2 + 1024;
+        reserve(nc);
+      }
     }
     if (index_upper_ + n_incoming > (int64_t)(0.65 * keys_.numel())) rebuild_index(pow2_at_least((index_upper_ + n_incoming) * 2));
   }
@@ -158,7 +176,8 @@ void EmbeddingStore::rebuild_index(int64_t nslots) {
     rbc_table_rehash(src, dst);
   }
   ctr_.select(0, RB_CTR_TOMBSTONES).zero_();
-  refresh_bounds();
+  // the tombstones are gone; with mirrored history the (pessimistic) bounds stay as they are until the next mirror lands
+  if (!(device_.is_cuda() && est_new_ >= 0)) refresh_bounds();
 }
 
 void EmbeddingStore::reserve(int64_t new_cap) {
@@ -206,6 +225,12 @@ torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::op
     }
     if (seen_n_dev_ > 0) n_budget = std::min<int64_t>(n, seen_n_dev_ + seen_n_dev_ / 4 + 65536);
   }
+  // ... and of those ids only some are new: twice the recent maximum of rows actually added per call, once that is known
+  if (device_.is_cuda()) {
+    absorb_mirror();
+    if (est_new_ >= 0) n_budget = std::min<int64_t>(n_budget, 2 * est_new_ + 65536);
+  }
+  ++calls_total_;
   ensure_room(n_budget);
   auto slot_scratch = torch::empty({n}, i32);
   auto new_rows = torch::empty({n}, i32);
@@ -292,6 +317,7 @@ void EmbeddingStore::clear() {
   for (auto& kv : slots_) kv.second.fill_(slot_fill_[kv.first]);
   if (last_seen_.defined()) last_seen_.zero_();
   rows_upper_ = bump_upper_ = index_upper_ = 0;
+  est_new_ = -1; rows_prev_ = -1; index_prev_ = 0; seen_n_dev_ = 0;
   absorbed_issued_ = issued_total_;
 }
 

@@ -56,6 +56,9 @@ class EmbeddingStore {
   static constexpr int kMirrorStride = RB_CTR_COUNT + 1;
   void post_mirror(int64_t n_issued, const int32_t* n_dev = nullptr);
   int64_t seen_n_dev_ = 0;          // recent maximum of the device-side id counts of lookup_or_insert calls
+  int64_t est_new_ = -1;            // recent maximum of rows (or index entries) one call really added; -1 = no history yet
+  int64_t rows_prev_ = -1, index_prev_ = 0, calls_prev_ = 0, calls_total_ = 0;
+  int64_t mirror_calls_[kMirror];
   void absorb_mirror();
   int64_t* mirror_host_ = nullptr;
   cudaEvent_t mirror_ev_[kMirror];
