@@ -13,34 +13,8 @@ namespace hash {
 
 #define RB_HD __host__ __device__ __forceinline__
 
-// Unaligned little-endian loads. On the device they are built from aligned word loads and a funnel shift (one or two load
-// instructions instead of one per byte). The second word is only touched when it holds at least one of the requested bytes,
-// and an aligned word that holds a valid byte never leaves the allocation it lives in (device allocations are aligned and
-// sized in multiples of at least 256 bytes). The host version copies bytes: host buffers carry no such guarantee.
-RB_HD uint64_t fetch64(const char* p) {
-#ifdef __CUDA_ARCH__
-  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-  const unsigned sh = (unsigned)(a & 7u) * 8u;
-  const uint64_t* w = reinterpret_cast<const uint64_t*>(a & ~(uintptr_t)7);
-  const uint64_t lo = w[0];
-  if (sh == 0) return lo;
-  return (lo >> sh) | (w[1] << (64u - sh));
-#else
-  uint64_t r; memcpy(&r, p, 8); return r;
-#endif
-}
-RB_HD uint32_t fetch32(const char* p) {
-#ifdef __CUDA_ARCH__
-  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-  const unsigned sh = (unsigned)(a & 3u) * 8u;
-  const uint32_t* w = reinterpret_cast<const uint32_t*>(a & ~(uintptr_t)3);
-  const uint32_t lo = w[0];
-  if (sh == 0) return lo;
-  return (lo >> sh) | (w[1] << (32u - sh));
-#else
-  uint32_t r; memcpy(&r, p, 4); return r;
-#endif
-}
+RB_HD uint64_t fetch64(const char* p) { uint64_t r; memcpy(&r, p, 8); return r; }
+RB_HD uint32_t fetch32(const char* p) { uint32_t r; memcpy(&r, p, 4); return r; }
 RB_HD uint64_t rot(uint64_t v, int s) { return s == 0 ? v : ((v >> s) | (v << (64 - s))); }
 RB_HD uint64_t shift_mix(uint64_t v) { return v ^ (v >> 47); }
 
@@ -162,7 +136,7 @@ RB_HD uint64_t murmur64a(const char* data, size_t n, uint64_t seed) {
 
 // 64-bit mix of a pair of ids (feature crosses): murmur-style combine of the two 8-byte words.
 RB_HD uint64_t murmur_pair(uint64_t x, uint64_t y) {
-  alignas(8) char buf[16];          // aligned: the word loads of fetch64 then never look beyond the buffer
+  char buf[16];
   memcpy(buf, &x, 8); memcpy(buf + 8, &y, 8);
   return murmur64a(buf, 16, 0);
 }
