@@ -1,0 +1,89 @@
+"""Model zoo and benchmark scripts on CPU: the sequence model's ragged attention against a per-sequence reference, and the
+benchmark scripts end to end at toy sizes (they print one JSON line)."""
+import json
+import os
+import subprocess
+import sys
+
+import torch
+
+from recis_b200.models.seq_model import EncoderLayer, SequenceModel, segment_softmax
+from recis_b200.nn import filter_out_sparse_param
+from recis_b200.nn.modules.hashtable import HashtableRegister
+from recis_b200.optim import DenseAdam, SparseAdam
+from recis_b200.ragged import RaggedTensor
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _ragged_batch(B=6, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(3, 20, (B,), generator=g)
+    offs = torch.zeros(B + 1, dtype=torch.int32)
+    offs[1:] = lens.cumsum(0)
+    return lens, offs, int(offs[-1])
+
+
+def test_segment_softmax_matches_per_segment():
+    lens, offs, T = _ragged_batch()
+    s = torch.randn(T)
+    seg = torch.repeat_interleave(torch.arange(lens.numel()), lens)
+    ref = torch.cat([torch.softmax(s[offs[i]:offs[i + 1]], 0) for i in range(lens.numel())])
+    assert torch.allclose(segment_softmax(s, seg, lens.numel()), ref, atol=1e-6)
+
+
+def test_encoder_layer_on_packed_tokens_matches_per_sequence():
+    torch.manual_seed(0)
+    lens, offs, T = _ragged_batch(B=5, seed=1)
+    layer = EncoderLayer(hidden=32, heads=4, ffn=64, dtype=torch.float32)
+    x = torch.randn(T, 32)
+    seg = torch.repeat_interleave(torch.arange(lens.numel()), lens)
+    pos = torch.arange(T) - offs[:-1].long()[seg]
+    got = layer(x, seg, pos, lens.long(), int(lens.max()) + 3)      # extra padding columns must not change anything
+    for i in range(lens.numel()):
+        xi = x[offs[i]:offs[i + 1]]
+        one = layer(xi, torch.zeros(xi.shape[0], dtype=torch.long), torch.arange(xi.shape[0]), lens[i:i + 1].long(), int(lens[i]))
+        assert torch.allclose(got[offs[i]:offs[i + 1]], one, atol=1e-5), i
+
+
+def test_sequence_model_trains_on_cpu():
+    HashtableRegister().clear()
+    torch.manual_seed(0)
+    lens, offs, T = _ragged_batch(B=8, seed=2)
+    B = lens.numel()
+    pf = ["p0", "p1"]
+    batch = {"seq_item": RaggedTensor(torch.randint(0, 500, (T,)), [offs]), "seq_cate": RaggedTensor(torch.randint(0, 20, (T,)), [offs]),
+             "tgt_item": torch.randint(0, 500, (B,)), "tgt_cate": torch.randint(0, 20, (B,)),
+             "label": (torch.rand(B, 1) < 0.4).float(), "max_len": int(lens.max()), "p0": torch.randint(0, 9, (B,)),
+             "p1": torch.randint(0, 9, (B,))}
+    m = SequenceModel(pf, emb_dim=8, profile_dim=4, hidden=32, heads=4, layers=2, ffn=64, head_mlp=(16, 1), device="cpu",
+                      compute_dtype=torch.float32, max_len=64)
+    # sequence and target features of one entity share one child table
+    assert len(m.embedding_engine.tables()) == 2
+    so = SparseAdam(filter_out_sparse_param(m), lr=1e-2)
+    do = DenseAdam([p for p in m.parameters() if p.requires_grad], lr=1e-2)
+    losses = []
+    for _ in range(25):
+        loss, logit = m(batch)
+        do.zero_grad(); so.zero_grad(); loss.backward(); so.step(); do.step()
+        losses.append(float(loss.detach()))
+    assert logit.shape == (B, 1) and losses[-1] < 0.5 * losses[0]
+
+
+def _run(script, *args):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "benchmarks", script), *args], capture_output=True, text=True, timeout=600,
+                         env=env, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    return json.loads(lines[-1])
+
+
+def test_benchmark_scripts_run_on_cpu():
+    r = _run("embedding_microbench.py", "--tables", "5", "--batch", "32", "--steps", "2", "--warmup", "1")
+    assert r["bench"] == "embedding_microbench" and r["unique_per_rank"] <= r["ids_per_rank"] and r["forward_ms"] > 0
+    r = _run("multitable.py", "--fields", "10", "--batch", "32", "--steps", "4", "--warmup", "1", "--ttl", "2", "--filter-interval", "2")
+    assert r["physical_tables"] == 5 and r["checkpoint"]["round_trip_identical"] is True and r["evicted_rows_rank0"] > 0
+    r = _run("sequence_model.py", "--batch", "8", "--min-len", "4", "--max-len", "20", "--items", "2000", "--cates", "50",
+             "--profile-fields", "2", "--hidden", "32", "--steps", "2", "--warmup", "1")
+    assert r["bench"] == "sequence_model" and r["ms_per_step"] > 0
