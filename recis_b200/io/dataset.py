@@ -147,7 +147,7 @@ class OrcDataset(DatasetBase):
                 return RaggedTensor(data, [torch.from_numpy(offsets.astype(np.int32)), soff])
             values = native().fused_hash([data], [soff], 0 if conf["hash_type"] == "farm" else 1)[0]
         else:
-            values = torch.from_numpy(np.ascontiguousarray(flat.to_numpy(zero_copy_only=False))).to(torch.int64)
+            values = torch.from_numpy(np.array(flat.to_numpy(zero_copy_only=False), copy=True)).to(torch.int64)
         if conf["hash_bucket"]:
             values = native().fused_mod([values], [int(conf["hash_bucket"])])[0]
         return RaggedTensor(values, [torch.from_numpy(offsets.astype(np.int32))], dense_shape=(n, -1))

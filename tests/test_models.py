@@ -87,3 +87,38 @@ def test_benchmark_scripts_run_on_cpu():
     r = _run("sequence_model.py", "--batch", "8", "--min-len", "4", "--max-len", "20", "--items", "2000", "--cates", "50",
              "--profile-fields", "2", "--hidden", "32", "--steps", "2", "--warmup", "1")
     assert r["bench"] == "sequence_model" and r["ms_per_step"] > 0
+
+
+def _run_example(path, *args):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, path), *args], capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    return out.stdout + out.stderr
+
+
+def test_examples_run_on_cpu(tmp_path):
+    log = _run_example("examples/deepfm/run.py", "--device", "cpu", "--steps", "6", "--batch", "64", "--output-dir", str(tmp_path / "fm"))
+    assert "trained 6 steps" in log and os.path.exists(tmp_path / "fm" / "checkpoint")
+    _run_example("examples/deepctr/make_orc_data.py", "--out", str(tmp_path / "orc"), "--shards", "2", "--rows", "256")
+    log = _run_example("examples/deepctr/run.py", "--data", str(tmp_path / "orc"), "--device", "cpu", "--batch", "64",
+                       "--output-dir", str(tmp_path / "ctr"))
+    assert "CoalescedHashtable_" in log
+    log = _run_example("examples/seq2seq/run.py", "--device", "cpu", "--steps", "3", "--batch", "4", "--max-len", "16")
+    assert "step    2" in log
+
+
+def test_csv_to_orc_round_trip(tmp_path):
+    from recis_b200.io import OrcDataset
+    from recis_b200.io.csv_to_orc import convert
+    csv = tmp_path / "d.csv"
+    csv.write_text("label,uid,seq\n1,10,1|2|3\n0,11,\n1,12,7\n0,13,4|4\n")
+    assert convert(str(csv), str(tmp_path / "out"), rows_per_shard=3, list_columns=["seq"]) == 2
+    ds = OrcDataset(batch_size=4)
+    ds.add_paths([str(tmp_path / "out" / f) for f in sorted(os.listdir(tmp_path / "out"))])
+    ds.varlen_feature("uid")
+    ds.varlen_feature("seq")
+    ds.fixedlen_feature("label")
+    batches = list(ds)
+    assert sum(b["label"].shape[0] for b in batches) == 4
+    assert batches[0]["seq"].values().tolist() == [1, 2, 3, 7] and batches[0]["seq"].offsets()[0].tolist() == [0, 3, 3, 4]
+    assert batches[1]["uid"].values().tolist() == [13]
