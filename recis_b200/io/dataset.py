@@ -95,8 +95,9 @@ class OrcDataset(DatasetBase):
 
     def __init__(self, batch_size: int, worker_idx: int = 0, worker_num: int = 1, read_threads_num: int = 2, prefetch: int = 2,
                  drop_remainder: bool = False, shuffle: bool = False, ragged_format: bool = True, transform_fn: Optional[Callable] = None,
-                 dtype: torch.dtype = torch.float32, device: str = "cpu", pin: bool = False, seed: int = 0):
+                 dtype: torch.dtype = torch.float32, device: str = "cpu", pin: bool = False, seed: int = 0, native_reader: bool = True):
         self.batch_size, self.worker_idx, self.worker_num = batch_size, worker_idx, worker_num
+        self.read_threads_num, self.native_reader = read_threads_num, native_reader
         self.drop_remainder, self.shuffle, self.transform_fn, self.dtype, self.device, self.pin = drop_remainder, shuffle, transform_fn, dtype, device, pin
         self.prefetch, self.seed = prefetch, seed
         self._paths: List[str] = []
@@ -173,8 +174,46 @@ class OrcDataset(DatasetBase):
             self._row_in_file = e
             yield batch
 
+    def _native(self, paths):
+        """The C++ reader (reader threads + packer + prefetch queue, ``csrc_io/columnar_reader.cpp``) when it applies: ORC files
+        only, no shuffling; it is built against the Arrow C++ library inside the pyarrow wheel and may be unavailable."""
+        if not self.native_reader or self.shuffle or not paths or not all(p.endswith(".orc") for p in paths):
+            return None
+        from .._ext_io import load
+        mod = load()
+        if mod is None:
+            return None
+        var = [(n, -1 if not c["hash_type"] else (0 if c["hash_type"] == "farm" else 1), int(c["hash_bucket"] or 0), bool(c["trans_int8"]))
+               for n, c in self._varlen.items()]
+        fix = [(n, float(d)) for n, d in self._fixed.items()]
+        reader = mod.ColumnarReader(paths, self.batch_size, var, fix, max(self.read_threads_num, 1), max(self.prefetch, 1),
+                                    self.drop_remainder, self.pin)
+        if self._file_idx or self._row_in_file:
+            reader.restore(self._file_idx, self._row_in_file)
+        return reader
+
     def __iter__(self):
         paths = self._my_paths()
+        reader = self._native(paths)
+        if reader is not None:
+            while True:
+                item = reader.next()
+                if item is None:
+                    return
+                rows, cols = item
+                batch = {}
+                for name in list(self._varlen) + list(self._fixed):
+                    c = cols[name]
+                    if c[0] == 0:
+                        batch[name] = RaggedTensor(c[1], [c[2]], dense_shape=(rows, -1))
+                    elif c[0] == 1:
+                        batch[name] = RaggedTensor(c[1], [c[2], c[3]])
+                    else:
+                        batch[name] = c[1].to(self.dtype) if c[1].is_floating_point() else c[1]
+                if self.transform_fn is not None:
+                    batch = self.transform_fn(batch)
+                self._file_idx, self._row_in_file = reader.state()
+                yield batch
         while self._file_idx < len(paths):
             table = self._read_table(paths[self._file_idx])
             yield from self._batches_of(table, self._row_in_file)
