@@ -194,6 +194,20 @@ class HashtableImpl:
     def size(self) -> int:
         return self.store.size()
 
+    def stats(self) -> dict:
+        """Occupancy of this shard (one device-to-host read of the 64-byte counter block): live rows, row capacity and load,
+        index slots and load, ids on admission probation, erased-but-unreclaimed index slots, rows on the free stack, rows
+        admitted by the last lookup, and the sticky status bits (0 = healthy)."""
+        c = self.store.counters()
+        bump, free_top, _new, status, live, tomb, prob, last_new = (int(x) for x in c[:8])
+        cap = int(self.store.capacity())
+        slots = int(self.store.keys().numel())
+        return {
+            "rows": live, "row_capacity": cap, "row_load": (bump - free_top) / max(cap, 1), "free_rows": free_top,
+            "index_slots": slots, "index_load": (live + tomb + prob) / max(slots, 1), "probation": prob, "tombstones": tomb,
+            "admitted_last_lookup": last_new, "status": status,
+        }
+
     # ---- gradient staging
     def accept_grad(self, index: torch.Tensor, grad: torch.Tensor):
         self._records.append({"kind": "rows", "rows": index.to(torch.int32), "grad": grad})

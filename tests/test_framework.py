@@ -171,3 +171,25 @@ def test_filter_hook_in_loop():
         ht(torch.arange(5))
         hook.after_step({}, step)
     assert ht.impl.size() == 5 and hook.evicted == 45
+
+
+def test_table_stats_and_hook():
+    from recis_b200.hooks import TableStatsHook
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption
+    from recis_b200.nn.hashtable_hook import AdmitHook
+    HashtableRegister().clear()
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=4, shared_name="a", device="cpu", capacity=64,
+                                                admit_hook=AdmitHook("CountAdmit", {"threshold": 2}))})
+    eng.train()
+    eng({"a": torch.arange(10)})
+    (table,) = eng.tables().values()
+    st = table.impl.stats()
+    assert st["rows"] == 0 and st["probation"] == 10 and st["status"] == 0          # first sighting: probation only
+    eng({"a": torch.arange(6)})
+    st = table.impl.stats()
+    assert st["rows"] == 6 and st["probation"] == 4 and st["admitted_last_lookup"] == 6
+    assert 0 < st["row_load"] <= 1 and 0 < st["index_load"] < 1
+    hook = TableStatsHook(eng, interval=1)
+    m = {}
+    hook.after_step(m, 1)
+    assert m["table0/rows"] == 6 and m["table0/rows_delta"] == 6 and m["table0/probation"] == 4
