@@ -40,6 +40,7 @@ class TrainingArguments:
     max_to_keep: int = 5
     save_concurrency_per_rank: int = 4
     stop_check_interval: int = 1
+    heartbeat_timeout: float = 0.0     # > 0: ranks exchange heartbeats; a peer silent for this many seconds raises PeerLostError
 
 
 class Trainer:
@@ -69,6 +70,11 @@ class Trainer:
         self.hooks.append(LoggerHook(self.args.log_steps))
         self._device = next((p.device for p in model.parameters()), torch.device("cpu")) if model is not None else torch.device("cpu")
         self.stop_state = torch.zeros((), dtype=torch.int64, device=self._device if self._device.type == "cuda" else "cpu")
+        self.peer_monitor = None
+        if self.world > 1 and self.args.heartbeat_timeout > 0:
+            from .health import PeerMonitor
+            self.peer_monitor = PeerMonitor(dist.get_rank(), self.world, interval=min(1.0, self.args.heartbeat_timeout / 4),
+                                            timeout=self.args.heartbeat_timeout).start()
 
     # ---- checkpointing
     def build_saver(self, model, args):
@@ -177,6 +183,8 @@ class Trainer:
                 break
             if self.data_to_cuda:
                 data = copy_data_to_device(data, "cuda")
+            if self.peer_monitor is not None:
+                self.peer_monitor.check()          # a dead or stalled peer surfaces here, before kernels that would wait for it
             for hook in self.hooks:
                 hook.before_step()
             metrics = {}

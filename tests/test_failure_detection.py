@@ -1,0 +1,98 @@
+"""Failure detection without touching a GPU: ranks are CPU processes (gloo); the failures are made on the host - a rank that
+stops sending heartbeats, a rank that exits, a collective that a peer never joins, a checkpoint shard cut short."""
+import os
+import time
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from multirank import run_ranks
+
+
+def _heartbeat_case(rank, world, mode):
+    from recis_b200.framework.health import PeerLostError, PeerMonitor
+    mon = PeerMonitor(rank, world, interval=0.1, timeout=1.0).start()
+    dist.barrier()
+    out = {"rank": rank}
+    if mode == "stall" and rank == 1:
+        mon.pause()                       # a hung process: alive, but silent
+        time.sleep(4.0)
+    elif mode == "leave" and rank == 1:
+        mon.leave()                       # clean exit between steps
+        time.sleep(3.0)
+    else:
+        t0 = time.monotonic()
+        lost = None
+        while time.monotonic() - t0 < 3.0:
+            try:
+                mon.check()
+            except PeerLostError as e:
+                lost = (e.rank, time.monotonic() - t0)
+                break
+            time.sleep(0.05)
+        out["lost"] = lost
+        out["alive"] = mon.alive()
+        if lost is None:
+            time.sleep(max(0.0, 3.2 - (time.monotonic() - t0)))
+        else:
+            time.sleep(max(0.0, 4.2 - (time.monotonic() - t0)))    # keep the store's host alive until the stalled rank wakes up
+    mon.leave()
+    return out
+
+
+def test_stalled_rank_is_detected_by_heartbeat():
+    res = run_ranks(_heartbeat_case, 3, "gloo", args=("stall",))
+    for r in (0, 2):
+        lost_rank, after = res[r]["lost"]
+        assert lost_rank == 1 and after < 2.5
+
+
+def test_clean_leave_is_not_a_failure():
+    res = run_ranks(_heartbeat_case, 3, "gloo", args=("leave",))
+    for r in (0, 2):
+        assert res[r]["lost"] is None and 1 not in res[r]["alive"]
+
+
+def _collective_timeout_case(rank, world):
+    from datetime import timedelta
+    # a second group with a short timeout: rank 1 never joins the all-reduce, the others must get an error, not a hang
+    g = dist.new_group(ranks=list(range(world)), backend="gloo", timeout=timedelta(seconds=2))
+    t = torch.ones(4)
+    if rank == 1:
+        time.sleep(5.0)
+        return {"joined": False}
+    t0 = time.monotonic()
+    try:
+        dist.all_reduce(t, group=g)
+        err = None
+    except RuntimeError as e:
+        err = str(e)[:200]
+    return {"joined": True, "error": err, "after": time.monotonic() - t0}
+
+
+def test_collective_with_missing_peer_times_out_with_an_error():
+    try:
+        res = run_ranks(_collective_timeout_case, 2, "gloo")
+    except RuntimeError as e:            # gloo may tear the pair down while rank 1 still sleeps; the helper's final barrier then fails
+        assert "rank 0" not in str(e) or "timed out" not in str(e)
+        return
+    assert res[0]["error"] is not None and res[0]["after"] < 4.5
+
+
+def test_truncated_checkpoint_shard_is_a_clean_error(tmp_path):
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.modules.hashtable import HashtableRegister
+    from recis_b200.serialize import Loader, Saver
+    HashtableRegister().clear()
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=4, shared_name="a", device="cpu")})
+    eng({"a": torch.arange(100)})
+    Saver(0, 1, 1, filter_out_sparse_param(eng), {}, str(tmp_path)).save()
+    shard = [f for f in os.listdir(tmp_path) if f.endswith(".safetensors")][0]
+    size = os.path.getsize(tmp_path / shard)
+    with open(tmp_path / shard, "r+b") as fh:
+        fh.truncate(size - 64)
+    HashtableRegister().clear()
+    eng2 = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=4, shared_name="a", device="cpu")})
+    with pytest.raises((RuntimeError, ValueError, OSError)):
+        Loader(str(tmp_path), filter_out_sparse_param(eng2), {}).load()
