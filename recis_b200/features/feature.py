@@ -40,6 +40,21 @@ class Feature(nn.Module):
         self._ops.append(op)
         return self
 
+    def id(self):
+        return id(self)
+
+    @staticmethod
+    def from_json(json_obj):
+        """``{"name": ..., "ops": [{"type": "Mod", "mod_value": 7}, ...]}`` -> Feature (the reference declares this entry point
+        without implementing it, ``recis/features/feature.py:110-111``)."""
+        from . import op as ops
+        f = Feature(json_obj["name"])
+        for spec in json_obj.get("ops", []):
+            spec = dict(spec)
+            cls = getattr(ops, spec.pop("type"))
+            f.add_op(cls(**spec))
+        return f
+
     def get_hash(self) -> int:
         if len(self._ops) == 0:
             return 0

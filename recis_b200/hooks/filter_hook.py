@@ -17,6 +17,9 @@ class HashTableFilterHook(Hook):
         if model is not None:
             self.attach(model)
 
+    def reset_filter_interval(self, interval: int = 100):
+        self.filter_interval = max(int(interval), 1)
+
     def attach(self, model):
         """Collect the filter of every table inside ``model``."""
         self._filters = [m._filter_hook_impl for m in model.modules() if isinstance(m, HashTable) and m._filter_hook_impl is not None]

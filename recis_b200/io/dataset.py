@@ -12,6 +12,8 @@ The ODPS / Lake / Pangu readers of the reference are services internal to its au
 """
 from __future__ import annotations
 
+import os
+
 import queue
 import threading
 from typing import Callable, Dict, List, Optional
@@ -26,6 +28,14 @@ _LEN_KIND = {"fixed": 0, "poisson": 1, "geometric": 2, "uniform": 3}
 
 
 class DatasetBase:
+    def map(self, fn):
+        """``dataset.map(fn)``: apply ``fn`` to every batch (chainable, as in the reference's ``DatasetBase.map``)."""
+        return MapDataset(self, fn)
+
+    def filter(self, fn):
+        """``dataset.filter(fn)``: keep the batches for which ``fn(batch)`` is true."""
+        return FilterDataset(self, fn=fn)
+
     """Iterable of batches with a restorable position."""
 
     def __iter__(self):
@@ -87,6 +97,15 @@ class TensorDataset(DatasetBase):
 
     def load_io_state(self, state):
         self._pos = int(state["pos"])
+
+
+def get_dir_size(path: str) -> int:
+    if os.path.isfile(path):
+        return os.path.getsize(path)
+    total = 0
+    for root, _dirs, files in os.walk(path):
+        total += sum(os.path.getsize(os.path.join(root, f)) for f in files)
+    return total
 
 
 class OrcDataset(DatasetBase):
@@ -219,6 +238,10 @@ class OrcDataset(DatasetBase):
             yield from self._batches_of(table, self._row_in_file)
             self._file_idx += 1
             self._row_in_file = 0
+
+    def get_dir_size(self):
+        """Bytes on disk behind every configured path (files, or directories walked recursively)."""
+        return [get_dir_size(p) for p in self._paths]
 
     def dump_io_state(self):
         return {"file_idx": self._file_idx, "row_in_file": self._row_in_file}

@@ -44,6 +44,15 @@ class AUROC(nn.Module):
         fp = neg.flip(0).cumsum(0).flip(0)[1:].double()
         return tp, fp, pos.sum().double() - tp, neg.sum().double() - fp
 
+    def sync(self, tp, fp, tn, fn):
+        """Sum confusion-matrix components over all ranks (no-op without a process group); the API of the reference's
+        ``AUROC.sync`` (``recis/metrics/auroc.py:281-316``)."""
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            both = torch.stack([tp, fp, tn, fn])
+            dist.all_reduce(both, op=dist.ReduceOp.SUM)
+            tp, fp, tn, fn = both[0], both[1], both[2], both[3]
+        return tp, fp, tn, fn
+
     def compute(self) -> torch.Tensor:
         tp, fp, fn, tn = self._counts()
         eps = 1e-6

@@ -104,7 +104,26 @@ class HashtableHookFactory:
             cls._instance = super().__new__(cls)
             cls._instance._admit = {"ReadOnly": ReadOnlyHookImpl, "CountAdmit": CountAdmitHookImpl}
             cls._instance._filter = {"GlobalStepFilter": GlobalStepFilterHookImpl}
+            cls._instance._filters, cls._instance._admits = {}, {}
         return cls._instance
+
+    # names used by the reference (recis/nn/modules/hashtable_hook_impl.py:61-75,153-200)
+    def regist_admit(self, name, impl):
+        if name in self._admit:
+            raise ValueError(f"admit hook {name} already registered")
+        self._admit[name] = impl
+
+    def regist_filter(self, name, impl):
+        if name in self._filter:
+            raise ValueError(f"filter hook {name} already registered")
+        self._filter[name] = impl
+
+    def get_filters(self):
+        """Filter hook instances created so far, by table name."""
+        return self._filters
+
+    def get_admits(self):
+        return self._admits
 
     def register_admit_hook(self, name, impl):
         self._admit[name] = impl
@@ -115,9 +134,13 @@ class HashtableHookFactory:
     def create_admit_hook(self, table, hook: AdmitHook):
         if hook.name not in self._admit:
             raise ValueError(f"unknown admit hook {hook.name}; known: {sorted(self._admit)}")
-        return self._admit[hook.name](table, **hook.params)
+        inst = self._admit[hook.name](table, **hook.params)
+        self._admits[getattr(table, "name", str(id(table)))] = inst
+        return inst
 
     def create_filter_hook(self, table, hook: FilterHook):
         if hook.name not in self._filter:
             raise ValueError(f"unknown filter hook {hook.name}; known: {sorted(self._filter)}")
-        return self._filter[hook.name](table, **hook.params)
+        inst = self._filter[hook.name](table, **hook.params)
+        self._filters[getattr(table, "name", str(id(table)))] = inst
+        return inst

@@ -87,6 +87,9 @@ class CheckpointReader:
     def list_tensors(self) -> List[str]:
         return sorted(self._index.dense_names() + [f"{c}@{s}" for c, s in self._index.table_blocks()])
 
+    def tensor_names(self) -> List[str]:
+        return self.list_tensors()
+
     def _resolve(self, name: str):
         if name in self._index.dense_names():
             return "dense", N.dense_key(name)

@@ -48,6 +48,10 @@ class Logger:
         if self._rank0():
             self._logger.info(msg, *a, **k)
 
+    def error_rank0(self, msg, *a, **k):
+        if self._rank0():
+            self._logger.error(msg, *a, **k)
+
     def warning_rank0(self, msg, *a, **k):
         if self._rank0():
             self._logger.warning(msg, *a, **k)

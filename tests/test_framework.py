@@ -193,3 +193,30 @@ def test_table_stats_and_hook():
     m = {}
     hook.after_step(m, 1)
     assert m["table0/rows"] == 6 and m["table0/rows_delta"] == 6 and m["table0/probation"] == 4
+
+
+def test_api_parity_helpers(tmp_path):
+    import recis_b200
+    from recis_b200.features import Feature, Mod
+    from recis_b200.hooks import HashTableFilterHook
+    from recis_b200.io import TensorDataset
+    from recis_b200.io.dataset import get_dir_size
+    from recis_b200.nn.modules.hashtable_hook_impl import HashtableHookFactory
+    info = recis_b200.get_build_info()
+    assert info["cuda_arch"] == "sm_100a" and recis_b200.is_internal_enabled() is False
+    f = Feature.from_json({"name": "x", "ops": [{"type": "SelectField", "name": "x"}, {"type": "Mod", "mod_value": 7}]})
+    assert len(f.ops) == 2 and isinstance(f.ops[1], Mod) and f.id() == id(f)
+    h = HashTableFilterHook(filter_interval=10)
+    h.reset_filter_interval(3)
+    assert h.filter_interval == 3
+    fac = HashtableHookFactory()
+    with pytest.raises(ValueError):
+        fac.regist_filter("GlobalStepFilter", object)
+    assert isinstance(fac.get_filters(), dict) and isinstance(fac.get_admits(), dict)
+    ds = TensorDataset({"a": torch.arange(10)}, batch_size=2).map(lambda b: {"a": b["a"] * 2}).filter(lambda b: int(b["a"][0]) % 8 == 0)
+    assert [b["a"].tolist() for b in ds] == [[0, 2], [8, 10], [16, 18]]
+    (tmp_path / "x.bin").write_bytes(b"12345")
+    assert get_dir_size(str(tmp_path)) == 5
+    m = AUROC(num_thresholds=10)
+    tp, fp, tn, fn = m.sync(torch.ones(3), torch.zeros(3), torch.ones(3), torch.zeros(3))
+    assert float(tp.sum()) == 3.0
