@@ -240,6 +240,9 @@ def run(args, arm):
                     "d2h_bytes_per_step": 4, "last_loss": losses[-1] if losses else None},
             "gpu_launches": launches,
         }
+        waits = arm.exposed_wait_ms(state) if hasattr(arm, "exposed_wait_ms") else {}
+        if waits:
+            line["exposed_wait_ms_per_wait"] = waits
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
@@ -306,6 +309,15 @@ class OursArm:
     def launches(self):
         import recis_b200
         return int(recis_b200.native().launch_count())
+
+    def exposed_wait_ms(self, st):
+        """RECIS_WAIT_STATS=1 only: mean time per flag wait until its last peer arrived, per channel, over the whole run."""
+        out = {}
+        for table in st["model"].embedding_engine.tables().values():
+            ex = getattr(table, "fused", None)
+            if ex is not None:
+                out.update(ex.exposed_wait_ms())
+        return out
 
     def comm_mode(self):
         return os.environ.get("RECIS_COMM", "auto")

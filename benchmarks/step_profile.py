@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--mode", default="kernels", choices=["kernels", "host"])
     ap.add_argument("--batch-per-gpu", type=int, default=8192)
     ap.add_argument("--capacity", type=int, default=0)
+    ap.add_argument("--all-ranks", action="store_true", help="kernels mode: every rank prints its ten heaviest kernels")
     a = ap.parse_args()
 
     import torch
@@ -82,6 +83,15 @@ def main():
             torch.cuda.synchronize()
         if rank == 0:
             print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=60))
+        if a.all_ranks:
+            # kernel durations differ between ranks (link contention, owner load): the step waits for the slowest one
+            rows = sorted(((e.self_device_time_total / 3e3, e.key) for e in prof.key_averages() if e.self_device_time_total > 0),
+                          reverse=True)[:10]
+            for r in range(world):
+                if rank == r:
+                    print(f"[rank {rank}] " + "; ".join(f"{k[:40]} {t:.3f} ms" for t, k in rows), flush=True)
+                if world > 1:
+                    dist.barrier()
     else:
         acc.clear()
         steps = []

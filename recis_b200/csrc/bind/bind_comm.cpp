@@ -142,6 +142,13 @@ void init_comm(py::module& m) {
   m.def("sym_close", &sym_close);
   m.def("comm_signal", &comm_signal);
   m.def("comm_wait", &comm_wait);
+  m.def("comm_wait_timed", [](const Tensor& flags, int64_t channel, int64_t world, int64_t epoch, int64_t spin_limit, Tensor status,
+                              Tensor stats) {
+    TORCH_CHECK(stats.scalar_type() == torch::kInt64 && stats.numel() >= RB_CH_COUNT * world + RB_CH_COUNT, "stats: int64 [channels * world + channels]");
+    rb_comm_wait_timed(flags.data_ptr<int64_t>(), (int)channel, (int)world, epoch, spin_limit, status.data_ptr<int64_t>(),
+                       stats.data_ptr<int64_t>(), cur_stream());
+  });
+  m.attr("N_CHANNELS") = (int)RB_CH_COUNT;
   m.def("comm_pull_ids", &comm_pull_ids);
   m.def("comm_push_emb", &comm_push_emb);
   m.def("comm_owner_reduce", &comm_owner_reduce);

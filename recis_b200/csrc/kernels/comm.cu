@@ -80,6 +80,36 @@ __global__ void comm_wait_kernel(const int64_t* flags, int channel, int world, i
   }
 }
 
+// The same wait with accounting: thread p adds the nanoseconds it spent until peer p's flag arrived to
+// stats[channel * world + p] (and the number of waits to stats[RB_CH_COUNT * world + channel]; RB_CH_COUNT * (world + 1) words). The time of a wait as a
+// whole is the maximum over p, i.e. the time until the last peer arrived: what a step pays for being ahead of its peers.
+// Kept apart from comm_wait_kernel so that the default path carries no extra work.
+__global__ void comm_wait_timed_kernel(const int64_t* flags, int channel, int world, int64_t epoch, int64_t spin_limit, int64_t* status,
+                                       unsigned long long* stats) {
+  const int p = threadIdx.x;
+  if (p < world) {
+    const int64_t* f = flags + (int64_t)channel * world + p;
+    bool ok = false;
+    uint64_t t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    t1 = t0;
+    const uint64_t budget_ns = (uint64_t)spin_limit * 1000ull;
+    for (int64_t it = 0; it < (int64_t)1 << 34; ++it) {
+      if (ld_acquire_sys(f) >= epoch) { ok = true; break; }
+      __nanosleep(100);
+      if ((it & 63) == 63) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > budget_ns) break;
+      }
+    }
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (!ok) set_status(status, kStatusWaitTimeout);
+    atomicAdd(stats + (int64_t)channel * world + p, (unsigned long long)(t1 - t0));
+    if (p == 0) atomicAdd(stats + (int64_t)RB_CH_COUNT * world + channel, 1ull);
+    __threadfence_system();
+  }
+}
+
 __device__ __forceinline__ int find_src(const int32_t* prefix, int world, int64_t j) {
   int r = 0;
   while (r + 1 < world && prefix[r + 1] <= j) ++r;
@@ -346,6 +376,12 @@ extern "C" {
 
 void rb_comm_signal(RbPeers flag_pads, int channel, int me, int world, int64_t epoch, cudaStream_t st) {
   comm_signal_kernel<<<1, 32, 0, st>>>(flag_pads, channel, me, world, epoch);
+  rb::note_launch();
+}
+
+void rb_comm_wait_timed(const int64_t* flags, int channel, int world, int64_t epoch, int64_t spin_limit, int64_t* status, int64_t* stats,
+                        cudaStream_t st) {
+  comm_wait_timed_kernel<<<1, 32, 0, st>>>(flags, channel, world, epoch, spin_limit, status, reinterpret_cast<unsigned long long*>(stats));
   rb::note_launch();
 }
 

@@ -17,6 +17,10 @@ enum RbChannel { RB_CH_IDS = 0, RB_CH_EMB = 1, RB_CH_GRAD = 2, RB_CH_AR0 = 3, RB
 
 void rb_comm_signal(RbPeers flag_pads, int channel, int me, int world, int64_t epoch, cudaStream_t st);
 void rb_comm_wait(const int64_t* flags, int channel, int world, int64_t epoch, int64_t spin_limit, int64_t* status, cudaStream_t st);
+// Same as rb_comm_wait, and adds the time spent per peer to stats: int64 [RB_CH_COUNT * world + RB_CH_COUNT] (nanoseconds per
+// (channel, peer), then the number of waits per channel).
+void rb_comm_wait_timed(const int64_t* flags, int channel, int world, int64_t epoch, int64_t spin_limit, int64_t* status, int64_t* stats,
+                        cudaStream_t st);
 void rb_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, int me, int world, int64_t* ids_in, int64_t in_cap, int32_t* prefix_out,
                       int32_t* n_in_dev, int64_t* status, cudaStream_t st);
 // prefix: int32[3*world+1] written by rb_comm_pull_ids = per-source prefix sums [world+1], per-source window offsets

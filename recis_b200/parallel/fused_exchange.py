@@ -80,7 +80,30 @@ class FusedExchange:
         self.status = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.immediate_reduce = False
         self.owner_unroll = int(os.environ.get("RECIS_OWNER_UNROLL", "2"))
+        # RECIS_WAIT_STATS=1: flag waits go through the accounting kernel; wait_stats holds nanoseconds per (channel, peer)
+        self.wait_stats = (torch.zeros(N_CH * world + N_CH, dtype=torch.int64, device=self.device)
+                           if os.environ.get("RECIS_WAIT_STATS") == "1" else None)
         self._head = None
+
+    def _wait(self, flags, channel, epoch):
+        C = native()
+        if self.wait_stats is None:
+            C.comm_wait(flags, channel, self.world, epoch, self.wait_us, self.status)
+        else:
+            C.comm_wait_timed(flags, channel, self.world, epoch, self.wait_us, self.status, self.wait_stats)
+
+    def exposed_wait_ms(self) -> dict:
+        """With RECIS_WAIT_STATS=1: per channel, the mean time of a wait until its last peer arrived (ms), since creation."""
+        if self.wait_stats is None:
+            return {}
+        s = self.wait_stats.cpu()
+        W = self.world
+        out = {}
+        for name, ch in (("ids", CH_IDS), ("emb", CH_EMB), ("grad", CH_GRAD)):
+            n = int(s[N_CH * W + ch])
+            if n:
+                out[name] = float(s[ch * W:(ch + 1) * W].max()) / n / 1e6
+        return out
 
     def table_storage(self):
         return None           # rows are pushed by their owner: the table arena itself need not be peer-visible
@@ -121,7 +144,7 @@ class FusedExchange:
         # more unique ids than the window holds sets the overflow bit in self.status (see check()); nothing is written out of bounds
         _uniq, rev, _counts, _offs = C.dedup_partition(ids, W, h["ids"].tensor, h["offsets"].tensor, self.status)
         C.comm_signal(h["flags"].ptrs, CH_IDS, me, e)
-        C.comm_wait(h["flags"].tensor, CH_IDS, W, e, self.wait_us, self.status)
+        self._wait(h["flags"].tensor, CH_IDS, e)
         C.comm_pull_ids(h["ids"].ptrs, h["offsets"].ptrs, me, lane.ids_in, lane.prefix, lane.n_in, self.status)
         if readonly:
             rows_in = store.find(lane.ids_in, lane.n_in)
@@ -130,7 +153,7 @@ class FusedExchange:
         prefix = lane.prefix.clone()
         C.comm_push_emb(store.emb(), rows_in, prefix, h["uemb"].ptrs, me, lane.in_cap)
         C.comm_signal(h["flags"].ptrs, CH_EMB, me, e)
-        C.comm_wait(h["flags"].tensor, CH_EMB, W, e, self.wait_us, self.status)
+        self._wait(h["flags"].tensor, CH_EMB, e)
         uemb = h["uemb"].tensor.view(lane.send_cap, D)
         if combiner == "tile":
             out, gsrc, gscale = C.tile_forward(uemb, None, rev, offsets, weights, tile_len, train)
@@ -175,7 +198,7 @@ class FusedExchange:
         C = native()
         lane = rec["lane"]
         h = lane.heap
-        C.comm_wait(h["flags"].tensor, CH_GRAD, self.world, rec["epoch"], self.wait_us, self.status)
+        self._wait(h["flags"].tensor, CH_GRAD, rec["epoch"])
         head = self._head_for(impl.store)
         rows, grads = C.comm_owner_reduce(rec["rows_in"], head, rec["prefix"], h["gin"].tensor, self.world, self.D,
                                           rec["mean_by_id"], apply, kind, lr, b1, b2, eps, decay, alpha, rec["scale"] * grad_scale,
