@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import copy
 import hashlib
+import os
 import math
 from collections import OrderedDict, defaultdict
 
@@ -59,8 +60,13 @@ class _Group:
 
 
 class EmbeddingEngine(nn.Module):
-    def __init__(self, emb_options: dict, interleave: bool = False):
+    def __init__(self, emb_options: dict, interleave: bool = False, exchange_lanes: int = 0):
         super().__init__()
+        # exchange_lanes > 1 (or RECIS_EXCHANGE_LANES): the features of one (table, runtime group) are split into that many
+        # lanes, each with its own exchange on its own CUDA stream, so that one lane's NVLink-bound kernels overlap the other
+        # lanes' HBM-bound ones. Off by default; only used on CUDA with more than one rank and the peer-memory exchange.
+        self._lanes = int(exchange_lanes or os.environ.get("RECIS_EXCHANGE_LANES", "1"))
+        self._lane_streams = {}
         self._ht = nn.ModuleDict()
         self._groups = {}
         self._fea_to_ht = {}
@@ -176,6 +182,35 @@ class EmbeddingEngine(nn.Module):
             weights = torch.cat(ws) if len(ws) > 1 else ws[0]
         return ids, offsets, weights
 
+    # ------------------------------------------------------------------ lanes (opt-in)
+    def _use_lanes(self, ht, feats, perm) -> bool:
+        return (self._lanes > 1 and perm is not None and len(feats) >= self._lanes and getattr(ht, "fused", None) is not None
+                and ht.impl.device.type == "cuda")
+
+    def _lookup_in_lanes(self, ht, feats, opt, run_key, dev):
+        """Split the features of one runtime group into lanes; every lane coalesces, exchanges and pools on its own stream.
+        Returns the pooled rows in the interleaved layout ``[segments_per_feature * n_features, D]``."""
+        L = self._lanes
+        main = torch.cuda.current_stream(dev)
+        bounds = [len(feats) * i // L for i in range(L + 1)]
+        cubes = []
+        ht.fused.multi_stream = True
+        for i in range(L):
+            part = feats[bounds[i]:bounds[i + 1]]
+            stream = self._lane_streams.get((dev, i))
+            if stream is None:
+                stream = self._lane_streams[(dev, i)] = torch.cuda.Stream(device=dev)
+            stream.wait_stream(main)
+            with torch.cuda.stream(stream):
+                ids, offsets, weights = self._coalesce(part, dev)
+                pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, 0, (part[0]["n_seg"], len(part)), opt.admit_hook,
+                                        lane=f"{run_key}#lane{i}")
+                cubes.append(pooled.view(part[0]["n_seg"], len(part), opt.embedding_dim))
+        for i, c in enumerate(cubes):
+            main.wait_stream(self._lane_streams[(dev, i)])
+            c.record_stream(main)
+        return torch.cat(cubes, dim=1).reshape(-1, opt.embedding_dim)
+
     # ------------------------------------------------------------------ forward
     def forward(self, input_features: dict):
         grouped = defaultdict(lambda: defaultdict(list))
@@ -199,14 +234,19 @@ class EmbeddingEngine(nn.Module):
             dev = ht.impl.device
             for run_key, feats in runtimes.items():
                 opt = feats[0]["opt"]
-                ids, offsets, weights = self._coalesce(feats, dev)
                 tile_len = opt.combiner_kwargs["tile_len"] if opt.combiner == "tile" else 0
                 segs = [f["n_seg"] for f in feats]
                 perm = None
                 if self._interleave and opt.combiner != "tile" and len(set(segs)) == 1 and len(feats) > 1:
                     perm = (segs[0], len(feats))
+                if not self._use_lanes(ht, feats, perm):
+                    ids, offsets, weights = self._coalesce(feats, dev)
                 ht.option.mean_by_weight = opt.mean_by_weight
-                pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, tile_len, perm, opt.admit_hook, lane=run_key)
+                if self._use_lanes(ht, feats, perm):
+                    pooled = self._lookup_in_lanes(ht, feats, opt, run_key, dev)          # [B, F, D] assembled from the lanes
+                    ids = offsets = weights = None
+                else:
+                    pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, tile_len, perm, opt.admit_hook, lane=run_key)
                 if not opt.trainable:
                     pooled = pooled.detach()
                 D = opt.embedding_dim

@@ -99,6 +99,16 @@ class SparseOptimizer(Optimizer):
             elif len(recs) == 1 and recs[0]["kind"] == "peer":
                 r = recs[0]
                 r["exchange"].owner_reduce(impl, r, True, kind, lr, b1, b2, eps, decay, alpha, inv_accum, w, s1, s2)
+            elif all(r.get("kind") == "peer" and r.get("stream") is not None for r in recs):
+                # one record per exchange lane (disjoint rows): each lane's update runs on the lane's own stream, right behind
+                # its gradient exchange, while other lanes are still exchanging
+                main = torch.cuda.current_stream(w.device)
+                for r in recs:
+                    r["stream"].wait_stream(main)
+                    with torch.cuda.stream(r["stream"]):
+                        r["exchange"].owner_reduce(impl, r, True, kind, lr, b1, b2, eps, decay, alpha, inv_accum, w, s1, s2)
+                for r in recs:
+                    main.wait_stream(r["stream"])
             else:
                 rows, grads = impl.materialize()
                 if rows is not None and rows.numel():

@@ -79,6 +79,8 @@ class FusedExchange:
         self.wait_us = int(float(os.environ.get("RECIS_WAIT_TIMEOUT_S", "20")) * 1e6)
         self.status = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.immediate_reduce = False
+        self.multi_stream = False          # set by the engine when lanes run on separate streams: table lookups are then chained
+        self._store_event = None
         self.owner_unroll = int(os.environ.get("RECIS_OWNER_UNROLL", "2"))
         # RECIS_WAIT_STATS=1: flag waits go through the accounting kernel; wait_stats holds nanoseconds per (channel, peer)
         self.wait_stats = (torch.zeros(N_CH * world + N_CH, dtype=torch.int64, device=self.device)
@@ -146,10 +148,16 @@ class FusedExchange:
         C.comm_signal(h["flags"].ptrs, CH_IDS, me, e)
         self._wait(h["flags"].tensor, CH_IDS, e)
         C.comm_pull_ids(h["ids"].ptrs, h["offsets"].ptrs, me, lane.ids_in, lane.prefix, lane.n_in, self.status)
+        if self.multi_stream and self._store_event is not None:
+            # lanes on separate streams share one table: its lookups (which allocate rows) run one after the other
+            torch.cuda.current_stream(self.device).wait_event(self._store_event)
         if readonly:
             rows_in = store.find(lane.ids_in, lane.n_in)
         else:
             rows_in = store.lookup_or_insert(lane.ids_in, lane.n_in, step, threshold)
+        if self.multi_stream:
+            self._store_event = torch.cuda.Event()
+            self._store_event.record(torch.cuda.current_stream(self.device))
         prefix = lane.prefix.clone()
         C.comm_push_emb(store.emb(), rows_in, prefix, h["uemb"].ptrs, me, lane.in_cap)
         C.comm_signal(h["flags"].ptrs, CH_EMB, me, e)
@@ -173,7 +181,8 @@ class FusedExchange:
                                 h["gin"].ptrs, lane.in_cap)
         C.comm_signal(h["flags"].ptrs, CH_GRAD, me, s["epoch"])
         rec = dict(rows_in=s["rows_in"], prefix=s["prefix"], epoch=s["epoch"], scale=worker_scale, exchange=self, lane=lane,
-                   mean_by_id=emb_mod.option.grad_reduce_by == "id")
+                   mean_by_id=emb_mod.option.grad_reduce_by == "id",
+                   stream=torch.cuda.current_stream(self.device) if self.multi_stream else None)
         if self.immediate_reduce:
             rows, grads = self.owner_reduce(emb_mod.impl, rec, apply=False)
             emb_mod.impl.accept_grad(rows, grads)
