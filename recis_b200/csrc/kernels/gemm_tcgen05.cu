@@ -22,6 +22,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 namespace {
@@ -281,6 +282,160 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (threadIdx.x == 0 && abort_flag) rb::set_status(status, rb::kStatusWaitTimeout);
 }
 
+// ---------------------------------------------------------------------- persistent variant (opt-in: RECIS_GEMM_PERSISTENT=1)
+// One CTA per tile slot walks a strided list of output tiles. Two accumulator stages live in tensor memory (2 x BN columns):
+// while the epilogue warps drain the accumulator of tile i (tcgen05.ld, bias/ReLU, stores), the MMA warp already fills the
+// other accumulator with tile i+1, and the TMA warp runs ahead through the shared-memory ring across tile boundaries. This
+// hides the per-tile prologue and epilogue that dominate the short reductions (K = 512 .. 1024) of recommendation MLPs.
+// No split-K here (weight gradients keep the kernel above).
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(kThreads, 2)
+gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                    OutT* __restrict__ out, const float* __restrict__ bias, const float* __restrict__ beta_src,
+                                    int MM, int NN, int KK, int ldo, int relu, int64_t* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t acc_full_bar[2];
+  __shared__ __align__(8) uint64_t acc_empty_bar[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (NN + BN - 1) / BN, tiles_m = (MM + BM - 1) / BM;
+  const int num_tiles = tiles_n * tiles_m;
+  const int total_kb = (KK + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full_bar[a], 1); mbar_init(&acc_empty_bar[a], 4); }   // 4 epilogue warps release a stage
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------------ TMA producer: runs ahead across tiles
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    uint32_t it = 0;
+    uint32_t issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      for (int kb = 0; kb < total_kb; ++kb, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        ok = mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag);
+        if (!ok) break;
+        uint8_t* sa = smem + s * kStageBytes;
+        uint8_t* sb = sa + kTileBytes;
+        mbar_expect_tx(&full_bar[s], kStageBytes);
+        const int k0 = kb * BK;
+        if (!A_MN) tma_load_2d(sa, &map_a, k0, m0, &full_bar[s]);
+        else { tma_load_2d(sa, &map_a, m0, k0, &full_bar[s]); tma_load_2d(sa + kTileBytes / 2, &map_a, m0 + 64, k0, &full_bar[s]); }
+        if (!B_MN) tma_load_2d(sb, &map_b, k0, n0, &full_bar[s]);
+        else { tma_load_2d(sb, &map_b, n0, k0, &full_bar[s]); tma_load_2d(sb + kTileBytes / 2, &map_b, n0 + 64, k0, &full_bar[s]); }
+        ++issued;
+      }
+    }
+    if (!ok) {
+      // drain: copies already issued must land before this CTA's shared memory goes away
+      const uint32_t first = issued > (uint32_t)kStages ? issued - kStages : 0u;
+      for (uint32_t j = first; j < issued; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (j / kStages) & 1u;
+        for (uint32_t spin = 0; spin < kSpinLimit; ++spin) if (mbar_try_wait(&full_bar[s], ph)) break;
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer: alternates between the two accumulators
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    uint32_t it = 0, j = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++j) {
+      const uint32_t acc = j & 1u, acc_ph = (j >> 1) & 1u;
+      ok = mbar_wait(&acc_empty_bar[acc], acc_ph ^ 1u, &abort_flag);      // the epilogue has drained this accumulator
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t tmem_acc = tmem_base + acc * (uint32_t)BN;
+      for (int kb = 0; kb < total_kb; ++kb, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        ok = mbar_wait(&full_bar[s], ph, &abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sa = smem_u32(smem + s * kStageBytes), sb = sa + kTileBytes;
+#pragma unroll
+        for (int k = 0; k < BK / UK; ++k) {
+          const uint64_t da = A_MN ? make_desc(sa + k * 2048, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
+          const uint64_t db = B_MN ? make_desc(sb + k * 2048, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
+          umma_bf16(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (ok) umma_commit(&acc_full_bar[acc]);
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------------ epilogue: drains accumulator j & 1 of every tile
+    const int q = warp & 3;
+    const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+    uint32_t j = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
+      const uint32_t acc = j & 1u, acc_ph = (j >> 1) & 1u;
+      if (!mbar_wait(&acc_full_bar[acc], acc_ph, &abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= NN) break;
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * (uint32_t)BN + (uint32_t)c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < MM) {
+          float v[32];
+          const int valid = min(32, NN - (n0 + c0));
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            float x = __uint_as_float(r[jj]);
+            if (jj < valid) {
+              if (bias) x += bias[n0 + c0 + jj];
+              if (beta_src) x += beta_src[(int64_t)row * ldo + n0 + c0 + jj];
+            }
+            v[jj] = relu ? fmaxf(x, 0.f) : x;
+          }
+          Store<OutT>::row32(out + (int64_t)row * ldo + n0 + c0, v, valid, vec_ok);
+        }
+      }
+      // every lane's tcgen05.ld has completed (wait::ld above); order them before the release of the accumulator
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+  }
+  if (threadIdx.x == 0 && abort_flag) rb::set_status(status, rb::kStatusWaitTimeout);
+}
+
 // ---------------------------------------------------------------------- host side
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -325,6 +480,27 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const float*
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
+template <bool A_MN, bool B_MN, typename OutT>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const float* bias, const float* beta_src, int MM, int NN,
+                      int KK, int ldo, int relu, int64_t* status, cudaStream_t st) {
+  auto kern = gemm_bf16_tcgen05_persistent_kernel<A_MN, B_MN, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess) return 3;
+    attr_set = true;
+  }
+  const int tiles = ((NN + BN - 1) / BN) * ((MM + BM - 1) / BM);
+  const int grid = std::min(tiles, 148 * 2);          // two CTAs (2 x 256 tensor-memory columns, 2 x 97 KB) per SM
+  kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, reinterpret_cast<OutT*>(out), bias, beta_src, MM, NN, KK, ldo, relu, status);
+  rb::note_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+bool persistent_enabled() {
+  static const bool on = [] { const char* e = std::getenv("RECIS_GEMM_PERSISTENT"); return e != nullptr && e[0] == '1'; }();
+  return on;
+}
+
 }  // namespace
 
 extern "C" int rb_gemm_splits(int MM, int NN, int KK) {
@@ -347,6 +523,17 @@ extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b,
   const bool okb = b_mn ? make_map(&mb, b, KK, NN, ldb, 64, BK) : make_map(&mb, b, NN, KK, ldb, BK, BN);
   if (!oka || !okb) return 2;
   if (splits > 1 && (!out_fp32 || relu)) return 6;   // partial tiles are accumulated with fp32 reductions into a zeroed output
+  if (persistent_enabled() && splits <= 1 && KK > 0) {
+#define RB_GEMM_PCASE(AM, BMJ)                                                                                                  \
+  if ((a_mn != 0) == AM && (b_mn != 0) == BMJ)                                                                                  \
+    return out_fp32 ? launch_persistent<AM, BMJ, float>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st)            \
+                    : launch_persistent<AM, BMJ, __nv_bfloat16>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st);
+    RB_GEMM_PCASE(false, false)
+    RB_GEMM_PCASE(false, true)
+    RB_GEMM_PCASE(true, false)
+    RB_GEMM_PCASE(true, true)
+#undef RB_GEMM_PCASE
+  }
 #define RB_GEMM_CASE(AM, BMJ)                                                                                                   \
   if ((a_mn != 0) == AM && (b_mn != 0) == BMJ)                                                                                  \
     return out_fp32 ? launch<AM, BMJ, float>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, splits, status, st)               \
