@@ -256,7 +256,7 @@ class EmbeddingEngine(nn.Module):
                     for j, f in enumerate(feats):
                         outs[f["name"]] = cube[:, j, :].reshape(f["shape"]) if len(f["shape"]) != 2 else cube[:, j, :]
                 else:
-                    rows_per = [s * tile_len if tile_len else s for s in segs] if False else segs
+                    rows_per = segs
                     pooled = pooled.view(-1, (tile_len or 1) * D)
                     start = 0
                     for f, s in zip(feats, rows_per):

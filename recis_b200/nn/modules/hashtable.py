@@ -40,7 +40,8 @@ class Slice:
 
     def to_string(self):
         """Zero-padded ``beg@end@size`` form used in checkpoint block names."""
-        return f"{self.slice_begin:0>6}@{self.slice_end:0>6}@{self.slice_size:0>6}"
+        width = len(str(self.slice_size))
+        return f"{self.slice_begin:0{width}d}@{self.slice_end:0{width}d}@{self.slice_size}"
 
 
 def gen_slice(shard_index=0, shard_num=1, slice_size=SLICE_SIZE) -> Slice:

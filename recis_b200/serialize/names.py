@@ -38,12 +38,15 @@ def data_file_name(idx: int, total: int) -> str:
 
 
 def slice_str(beg: int, end: int, size: int) -> str:
-    return f"{beg:0>6}@{end:0>6}@{size:0>6}" if False else f"{beg}@{end}@{size}"
+    """``beg@end@size`` with begin and end zero-padded to the width of ``size``, e.g. ``08192@16384@65536``
+    (``csrc/embedding/slice_info.cc:38-48`` in the reference)."""
+    width = len(str(size))
+    return f"{beg:0{width}d}@{end:0{width}d}@{size}"
 
 
 def block_name(child: str, slot: str, sl) -> str:
     """Internal block name ``<child>@<slot>^<beg>@<end>@<size>``."""
-    return f"{child}@{slot}^{sl.slice_begin}@{sl.slice_end}@{sl.slice_size}"
+    return f"{child}@{slot}^{slice_str(sl.slice_begin, sl.slice_end, sl.slice_size)}"
 
 
 def disk_key(child: str, slot: str, shard: int, shard_num: int) -> str:

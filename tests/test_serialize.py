@@ -51,7 +51,7 @@ def test_layout_and_independent_reader(tmp_path):
     index = json.load(open(tmp_path / "index"))
     assert set(index) == {"file_index", "block_index"}
     tk = json.load(open(tmp_path / "tensorkey.json"))
-    assert tk["user.embedding/part_0_1"] == "user@embedding^0@65536@65536"
+    assert tk["user.embedding/part_0_1"] == "user@embedding^00000@65536@65536"
     assert "user.sparse_adamw_exp_avg/part_0_1" in tk and "wide.id/part_0_1" in tk and "w^ " in index["block_index"]
     rank = json.load(open(tmp_path / "torch_rank_weights_embs_table_multi_shard.json"))
     e = rank["item.embedding/part_0_1"]
