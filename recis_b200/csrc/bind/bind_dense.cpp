@@ -193,6 +193,21 @@ void init_dense(py::module& m) {
   m.def("fm_bwd", &fm_bwd);
   m.def("relu_bwd_bias", &relu_bwd_bias);
   m.def("cast_pad_bf16", &cast_pad_bf16);
+  // Ragged self-attention forward on the tensor cores (head width 64): returns (out bf16 [T, H * 64], lse2 fp32 [T, H]).
+  m.def("ragged_attention_fwd", [](const Tensor& qkv, const Tensor& offsets, int64_t H, int64_t max_len, double scale) {
+    TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == torch::kBFloat16 && qkv.is_contiguous() && qkv.dim() == 2 &&
+                    qkv.size(1) == 3 * H * 64, "qkv: contiguous bf16 [T, 3 * H * 64] on CUDA");
+    TORCH_CHECK(offsets.is_cuda() && offsets.scalar_type() == torch::kInt32 && offsets.is_contiguous() && offsets.numel() >= 2);
+    c10::cuda::CUDAGuard g(qkv.device());
+    const int64_t T = qkv.size(0), B = offsets.numel() - 1;
+    auto out = torch::zeros({T, H * 64}, qkv.options());
+    auto lse = torch::zeros({T, H}, qkv.options().dtype(torch::kFloat32));
+    const int rc = rb_ragged_attention_fwd(qkv.data_ptr(), offsets.data_ptr<int32_t>(), (int)B, (int)H, (int)max_len, (float)scale,
+                                           out.data_ptr(), lse.data_ptr<float>(), status_word(qkv.device()).data_ptr<int64_t>(),
+                                           at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "ragged_attention_fwd failed (code ", rc, ")");
+    return std::make_tuple(out, lse);
+  });
   // Multi-tensor dense Adam (see rb_dense.h for the update rule); ws/gs/ms/vs are parallel lists of fp32 CUDA tensors,
   // w_bf16 an optional parallel list (entries may be undefined) of bf16 shadows that receive the rounded weights.
   m.def("dense_adam", [](std::vector<Tensor> ws, std::vector<Tensor> gs, std::vector<Tensor> ms, std::vector<Tensor> vs,

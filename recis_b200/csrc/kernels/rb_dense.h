@@ -35,6 +35,10 @@ int rb_dot_interaction_tc_fwd(const void* x, const float* cube, int B, int F, in
                               cudaStream_t st);
 int rb_dot_interaction_tc_bwd(const void* x, const float* cube, const void* dout, int B, int F, int D, int out_ld, float* dx,
                               float* dcube, int64_t* status, cudaStream_t st);
+// Ragged multi-head self-attention forward, head width 64 (attention_tcgen05.cu). qkv: bf16 [T, 3 * H * 64] packed, offsets:
+// int32 [B + 1] (device), out: bf16 [T, H * 64], lse2: fp32 [T, H] or null. 0 = launched, 1 = unsuitable arguments, > 1 = error.
+int rb_ragged_attention_fwd(const void* qkv, const int32_t* offsets, int B, int H, int max_len, float scale, void* out, float* lse2,
+                            int64_t* status, cudaStream_t st);
 void rb_fm_fwd(const float* cube, int B, int F, int D, float* out, cudaStream_t st);
 void rb_fm_bwd(const float* cube, const float* gout, int B, int F, int D, float* dcube, cudaStream_t st);
 // dy = relu ? dout * (y > 0) : dout (bf16, may be null to skip the store); db[n] += column sums of dy (fp32, may be null)

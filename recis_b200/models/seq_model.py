@@ -9,22 +9,23 @@ Layout decisions:
   lookup feeds the id values as a flat batch of one-id bags, so the exchange moves unique ids only and nothing is padded;
   all projections and the FFN run on the packed tokens through the tensor-core GEMM (``ops.dense.Linear``).
 * Target attention is computed on the packed layout with segment reductions (one query per sequence).
-* The encoder's attention core scatters the packed Q/K/V into ``[batch, max_len, heads, head_dim]`` and calls
-  ``F.scaled_dot_product_attention`` with a key-padding mask, then gathers the valid positions back. (The reference's
-  sequence example does the same on fully padded tensors under bf16 autocast, ``examples/seq2seq/transformer.py:36-38`` and
-  ``seq2seq_model.py:87-91``.)
+* The encoder's attention core is ``ops.attention.ragged_self_attention``: for training it scatters the packed Q/K/V into
+  ``[batch, max_len, heads, head_dim]`` and calls ``F.scaled_dot_product_attention`` with a key-padding mask, then gathers the
+  valid positions back (the reference's sequence example does the same on fully padded tensors under bf16 autocast,
+  ``examples/seq2seq/transformer.py:36-38`` and ``seq2seq_model.py:87-91``); without gradients it can run the ragged
+  tensor-core kernel instead (opt-in).
 """
 from __future__ import annotations
 
 from typing import Sequence
 
 import torch
-import torch.nn.functional as F
 from torch import nn
 
 from ..nn import EmbeddingEngine, EmbeddingOption
 from ..nn.functional.ragged_ops import gen_segment_indices
 from ..nn.initializers import NormalInitializer
+from ..ops.attention import ragged_self_attention
 from ..ops.dense import MLP, Linear
 from ..ragged import RaggedTensor
 
@@ -48,19 +49,13 @@ class EncoderLayer(nn.Module):
         self.proj = Linear(hidden, hidden, dtype=dtype)
         self.ffn = MLP([hidden, ffn, hidden], final_act=False, dtype=dtype)
 
-    def forward(self, x, seg, pos, lengths, max_len):
-        B, H, hd = lengths.numel(), self.heads, self.hidden // self.heads
+    def forward(self, x, seg, pos, lengths, max_len, offsets=None):
         h = self.norm1(x)
-        qkv = self.qkv(h).float()                                             # [T, 3 * hidden]
-        padded = qkv.new_zeros(B, max_len, 3 * self.hidden)
-        padded[seg, pos] = qkv
-        q, k, v = padded.view(B, max_len, 3, H, hd).permute(2, 0, 3, 1, 4)       # each [B, H, L, hd]
-        key_ok = torch.arange(max_len, device=x.device)[None, :] < lengths[:, None]
-        mask = key_ok[:, None, None, :]                                        # [B, 1, 1, L]
-        if x.is_cuda:
-            q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
-        o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask)             # [B, H, L, hd]
-        o = o.permute(0, 2, 1, 3).reshape(B, max_len, self.hidden)[seg, pos].float()
+        qkv = self.qkv(h)                                                      # [T, 3 * hidden] packed
+        qkv = qkv.to(torch.bfloat16) if x.is_cuda else qkv.float()
+        if offsets is None:
+            offsets = torch.cat([lengths.new_zeros(1), lengths.cumsum(0)])
+        o = ragged_self_attention(qkv, offsets, self.heads, max_len, seg, pos).float()
         x = x + self.proj(o).float()
         x = x + self.ffn(self.norm2(x)).float()
         return x
@@ -123,7 +118,7 @@ class SequenceModel(nn.Module):
         # ---- encoder over the sequence
         h = x
         for layer in self.layers:
-            h = layer(h, seg, pos, lengths, max_len)
+            h = layer(h, seg, pos, lengths, max_len, offsets)
         h = self.final_norm(h)
         pooled = torch.zeros(B, self.hidden, dtype=h.dtype, device=dev).index_add_(0, seg, h) / lengths.clamp_min(1)[:, None]
         profile = torch.cat([emb[f].view(B, -1) for f in self.profile_fields], dim=1) if self.profile_fields else h.new_zeros(B, 0)

@@ -1,0 +1,52 @@
+"""Self-attention over ragged (packed) sequences.
+
+``ragged_self_attention(qkv, offsets, heads, max_len)`` takes the packed projection output ``[total_tokens, 3 * hidden]``
+(q | k | v) of a batch of sequences stored back to back and returns ``[total_tokens, hidden]``.
+
+Two implementations:
+* the tensor-core kernel (``csrc/kernels/attention_tcgen05.cu``): no padding, one CTA per (sequence, head, 128-query tile);
+  forward only, head width 64, opt-in with ``RECIS_ATTENTION=tcgen05`` and used where no gradient is needed (evaluation /
+  serving);
+* the padded path: scatter into ``[batch, max_len, heads, head_dim]``, ``F.scaled_dot_product_attention`` with a key-padding
+  mask, gather the valid positions back. Differentiable; what training uses; runs on CPU as well.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.nn.functional as F
+
+from .. import native
+
+
+def _padded(qkv, seg, pos, lengths, max_len, heads):
+    T, width = qkv.shape
+    hidden = width // 3
+    hd = hidden // heads
+    B = lengths.numel()
+    padded = qkv.new_zeros(B, max_len, width)
+    padded[seg, pos] = qkv
+    q, k, v = padded.view(B, max_len, 3, heads, hd).permute(2, 0, 3, 1, 4)                # each [B, H, L, hd]
+    key_ok = torch.arange(max_len, device=qkv.device)[None, :] < lengths[:, None]
+    o = F.scaled_dot_product_attention(q, k, v, attn_mask=key_ok[:, None, None, :])       # [B, H, L, hd]
+    return o.permute(0, 2, 1, 3).reshape(B, max_len, hidden)[seg, pos]
+
+
+def ragged_self_attention(qkv: torch.Tensor, offsets: torch.Tensor, heads: int, max_len: int, seg: torch.Tensor = None,
+                          pos: torch.Tensor = None) -> torch.Tensor:
+    """``qkv``: ``[T, 3 * hidden]``; ``offsets``: ``[B + 1]`` sequence boundaries; returns ``[T, hidden]`` in ``qkv``'s dtype.
+    ``seg`` / ``pos`` (sequence index and position of every token) are derived from ``offsets`` when not given."""
+    hidden = qkv.shape[1] // 3
+    hd = hidden // heads
+    needs_grad = torch.is_grad_enabled() and qkv.requires_grad
+    if (os.environ.get("RECIS_ATTENTION") == "tcgen05" and qkv.is_cuda and hd == 64 and not needs_grad):
+        out, _lse = native().ragged_attention_fwd(qkv.to(torch.bfloat16).contiguous(), offsets.to(torch.int32).contiguous(), heads,
+                                                  int(max_len), float(hd) ** -0.5)
+        return out.to(qkv.dtype)
+    lengths = (offsets[1:] - offsets[:-1]).long()
+    if seg is None:
+        seg = torch.repeat_interleave(torch.arange(lengths.numel(), device=qkv.device), lengths)
+    if pos is None:
+        pos = torch.arange(qkv.shape[0], device=qkv.device) - offsets[:-1].long()[seg]
+    return _padded(qkv, seg, pos, lengths, int(max_len), heads)
