@@ -208,6 +208,24 @@ void init_dense(py::module& m) {
     TORCH_CHECK(rc == 0, "ragged_attention_fwd failed (code ", rc, ")");
     return std::make_tuple(out, lse);
   });
+  // Backward of the above: returns dqkv fp32 [T, 3 * H * 64].
+  m.def("ragged_attention_bwd", [](const Tensor& qkv, const Tensor& out, const Tensor& d_out, const Tensor& lse, const Tensor& offsets,
+                                   int64_t H, int64_t max_len, double scale) {
+    TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == torch::kBFloat16 && qkv.is_contiguous() && qkv.size(1) == 3 * H * 64);
+    TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && d_out.scalar_type() == torch::kBFloat16 &&
+                d_out.is_contiguous() && out.sizes() == d_out.sizes() && out.size(0) == qkv.size(0) && out.size(1) == H * 64);
+    TORCH_CHECK(lse.scalar_type() == torch::kFloat32 && lse.is_contiguous() && lse.numel() == qkv.size(0) * H);
+    c10::cuda::CUDAGuard g(qkv.device());
+    const int64_t T = qkv.size(0), B = offsets.numel() - 1;
+    auto dqkv = torch::zeros({T, 3 * H * 64}, qkv.options().dtype(torch::kFloat32));
+    auto delta = torch::empty({T, H}, dqkv.options());
+    const int rc = rb_ragged_attention_bwd(qkv.data_ptr(), out.data_ptr(), d_out.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
+                                           offsets.data_ptr<int32_t>(), T, (int)B, (int)H, (int)max_len, (float)scale,
+                                           dqkv.data_ptr<float>(), status_word(qkv.device()).data_ptr<int64_t>(),
+                                           at::cuda::getCurrentCUDAStream());
+    TORCH_CHECK(rc == 0, "ragged_attention_bwd failed (code ", rc, ")");
+    return dqkv;
+  });
   // Multi-tensor dense Adam (see rb_dense.h for the update rule); ws/gs/ms/vs are parallel lists of fp32 CUDA tensors,
   // w_bf16 an optional parallel list (entries may be undefined) of bf16 shadows that receive the rounded weights.
   m.def("dense_adam", [](std::vector<Tensor> ws, std::vector<Tensor> gs, std::vector<Tensor> ms, std::vector<Tensor> vs,

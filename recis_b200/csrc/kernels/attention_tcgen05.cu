@@ -186,6 +186,193 @@ ragged_attention_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t
   if (t == 0 && abort_flag) rb::set_status(status, rb::kStatusWaitTimeout);
 }
 
+// ---------------------------------------------------------------------------------------------- backward
+// delta[t, h] = sum_d dO[t, h, d] * O[t, h, d] (the row-wise correction term of the softmax backward); one warp per (t, h).
+__global__ void __launch_bounds__(256)
+attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, int64_t rows, float* __restrict__ delta) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t r = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(o + r * kHead)[lane];
+    const __nv_bfloat162 b = reinterpret_cast<const __nv_bfloat162*>(d_o + r * kHead)[lane];
+    float v = __bfloat162float(a.x) * __bfloat162float(b.x) + __bfloat162float(a.y) * __bfloat162float(b.y);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if (lane == 0) delta[r] = v;
+  }
+}
+
+// One CTA owns one (sequence, head, 128-key tile) and walks the sequence's queries in tiles of 128. Per query tile:
+//   S  = Q K^T, dP = dO V^T                          (two MMA chains, 128 x 128 x 64 each, results in tensor memory)
+//   P  = exp2(S * scale * log2 e - lse2[q]),  dS = P * (dP - delta[q]) * scale        (thread = query row; written to shared
+//                                                     memory as bf16 tiles [q][key])
+//   dV += P^T dO, dK += dS^T Q                       (the [q][key] tiles read as MN-major A operands, dO / Q as MN-major B;
+//                                                     accumulated in tensor memory over all query tiles)
+//   dQ  = dS K                                       (the dS tile read as a K-major A operand, K as an MN-major B) and added to
+//                                                     the global dQ with fp32 reductions (other key tiles add theirs)
+// dK and dV of the tile's keys are stored once at the end. Gradients go to dqkv [T, 3 * H * 64] in fp32 (the q part must be
+// zero on entry).
+constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 320, kColDQ = 384;
+
+__global__ void __launch_bounds__(128, 1)
+ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse2,
+                            const float* __restrict__ delta, const int32_t* __restrict__ offsets, int H, float scale, float scale_log2,
+                            float* __restrict__ dqkv, int64_t* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar1, bar2;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int b = blockIdx.y, h = blockIdx.z, kt = blockIdx.x;
+  const int s0 = offsets[b], L = offsets[b + 1] - s0;
+  if (kt * kTile >= L) return;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* ktile = smem;                   // [128 keys][64 d]
+  uint8_t* vtile = smem + kBlk;            // [128 keys][64 d]
+  uint8_t* qtile = smem + 2 * kBlk;        // [128 q][64 d]
+  uint8_t* dotile = smem + 3 * kBlk;       // [128 q][64 d]
+  uint8_t* ptile = smem + 4 * kBlk;        // 2 x [128 q][64 keys]
+  uint8_t* dstile = smem + 6 * kBlk;       // 2 x [128 q][64 keys]
+  const int t = threadIdx.x, warp = t >> 5;
+  const int64_t ld = (int64_t)3 * H * kHead;
+  if (t == 0) { abort_flag = 0; mbar_init(&bar1, 1); mbar_init(&bar2, 1); mbar_fence_init(); }
+  if (warp == 0) tmem_alloc(&tmem_slot, 512);
+
+  const int key = kt * kTile + t;
+  const bool key_ok = key < L;
+  {
+    const __nv_bfloat16* krow = key_ok ? qkv + (int64_t)(s0 + key) * ld + (H + h) * kHead : nullptr;
+    stage_row(ktile, t, krow);
+    stage_row(vtile, t, krow ? krow + H * kHead : nullptr);
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  const uint32_t idesc_kk = make_idesc_bf16(kTile, kTile, false, false);    // S, dP: both operands K-major
+  const uint32_t idesc_mm = make_idesc_bf16(kTile, kHead, true, true);      // dV, dK: both operands MN-major
+  const uint32_t idesc_km = make_idesc_bf16(kTile, kHead, false, true);     // dQ: A K-major, B MN-major
+  const int valid_keys = min(kTile, L - kt * kTile);
+  bool ok = true;
+
+  const int n_q = (L + kTile - 1) / kTile;
+  for (int i = 0; i < n_q && ok; ++i) {
+    const int q = i * kTile + t;
+    const bool q_ok = q < L;
+    const int64_t tok = s0 + q;
+    stage_row(qtile, t, q_ok ? qkv + tok * ld + h * kHead : nullptr);
+    stage_row(dotile, t, q_ok ? d_o + tok * H * kHead + h * kHead : nullptr);
+    const float lse_q = q_ok ? lse2[tok * H + h] : 0.f;
+    const float delta_q = q_ok ? delta[tok * H + h] : 0.f;
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    if (t == 0) {
+      const uint32_t sq = smem_u32(qtile), sk = smem_u32(ktile), sdo = smem_u32(dotile), sv = smem_u32(vtile);
+#pragma unroll
+      for (int k = 0; k < kHead / 16; ++k)
+        umma_bf16(tmem + kColS, make_desc(sq + k * 32, 16, 1024), make_desc(sk + k * 32, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
+#pragma unroll
+      for (int k = 0; k < kHead / 16; ++k)
+        umma_bf16(tmem + kColDP, make_desc(sdo + k * 32, 16, 1024), make_desc(sv + k * 32, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
+      umma_commit(&bar1);
+    }
+    ok = __syncthreads_and(mbar_wait(&bar1, (uint32_t)(i & 1), &abort_flag) ? 1 : 0) != 0;
+    fence_after_sync();
+    if (!ok) break;
+
+    for (int c0 = 0; c0 < kTile; c0 += 32) {
+      uint32_t rs[32], rp[32];
+      tmem_ld32(tmem + lane_base + kColS + (uint32_t)c0, rs);
+      tmem_ld32(tmem + lane_base + kColDP + (uint32_t)c0, rp);
+      tmem_ld_wait();
+      uint32_t pk[16], dk[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        float p[2], ds[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int c = c0 + 2 * e + u;
+          const bool on = q_ok && c < valid_keys;
+          p[u] = on ? exp2f(__uint_as_float(rs[2 * e + u]) * scale_log2 - lse_q) : 0.f;
+          ds[u] = on ? p[u] * (__uint_as_float(rp[2 * e + u]) - delta_q) * scale : 0.f;
+        }
+        const __nv_bfloat162 pb = __floats2bfloat162_rn(p[0], p[1]), db = __floats2bfloat162_rn(ds[0], ds[1]);
+        pk[e] = *reinterpret_cast<const uint32_t*>(&pb);
+        dk[e] = *reinterpret_cast<const uint32_t*>(&db);
+      }
+      const uint32_t boff = (uint32_t)(c0 >> 6) * kBlk;
+#pragma unroll
+      for (int cq = 0; cq < 4; ++cq) {
+        const uint32_t off = boff + swizzle128_offset(t, (c0 & 63) + cq * 8);
+        *reinterpret_cast<uint4*>(ptile + off) = make_uint4(pk[cq * 4], pk[cq * 4 + 1], pk[cq * 4 + 2], pk[cq * 4 + 3]);
+        *reinterpret_cast<uint4*>(dstile + off) = make_uint4(dk[cq * 4], dk[cq * 4 + 1], dk[cq * 4 + 2], dk[cq * 4 + 3]);
+      }
+    }
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    if (t == 0) {
+      const uint32_t sp = smem_u32(ptile), sds = smem_u32(dstile), sq = smem_u32(qtile), sdo = smem_u32(dotile), sk = smem_u32(ktile);
+      const uint32_t acc0 = i > 0 ? 1u : 0u;
+#pragma unroll
+      for (int k = 0; k < kTile / 16; ++k) {        // reduction over the 128 queries of this tile, 16 rows per step
+        // A = P^T / dS^T: [q][key] tiles read MN-major (M = key: two 64-wide blocks kBlk apart, 16 q rows = 2048 bytes per step)
+        // B = dO / Q:     [q][d] tiles read MN-major (N = d, one 64-wide block)
+        umma_bf16(tmem + kColDV, make_desc(sp + k * 2048, kBlk, 1024), make_desc(sdo + k * 2048, kBlk, 1024), idesc_mm, (acc0 | (k > 0 ? 1u : 0u)));
+        umma_bf16(tmem + kColDK, make_desc(sds + k * 2048, kBlk, 1024), make_desc(sq + k * 2048, kBlk, 1024), idesc_mm, (acc0 | (k > 0 ? 1u : 0u)));
+      }
+#pragma unroll
+      for (int k = 0; k < kTile / 16; ++k)          // reduction over the 128 keys: dS read K-major, K read MN-major
+        umma_bf16(tmem + kColDQ, make_desc(sds + (k >> 2) * kBlk + (k & 3) * 32, 16, 1024), make_desc(sk + k * 2048, kBlk, 1024), idesc_km,
+                  k > 0 ? 1u : 0u);
+      umma_commit(&bar2);
+    }
+    ok = __syncthreads_and(mbar_wait(&bar2, (uint32_t)(i & 1), &abort_flag) ? 1 : 0) != 0;
+    fence_after_sync();
+    if (!ok) break;
+    for (int c0 = 0; c0 < kHead; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(tmem + lane_base + kColDQ + (uint32_t)c0, r);
+      tmem_ld_wait();
+      if (q_ok) {
+        float* dst = dqkv + tok * ld + h * kHead + c0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          atomicAdd(reinterpret_cast<float4*>(dst) + e, make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]),
+                                                                    __uint_as_float(r[4 * e + 2]), __uint_as_float(r[4 * e + 3])));
+      }
+    }
+  }
+
+  if (ok) {
+    for (int c0 = 0; c0 < kHead; c0 += 32) {
+      uint32_t rv[32], rk[32];
+      tmem_ld32(tmem + lane_base + kColDV + (uint32_t)c0, rv);
+      tmem_ld32(tmem + lane_base + kColDK + (uint32_t)c0, rk);
+      tmem_ld_wait();
+      if (key_ok) {
+        float* dk_dst = dqkv + (int64_t)(s0 + key) * ld + (H + h) * kHead + c0;
+        float* dv_dst = dk_dst + H * kHead;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          reinterpret_cast<float4*>(dk_dst)[e] = make_float4(__uint_as_float(rk[4 * e]), __uint_as_float(rk[4 * e + 1]),
+                                                             __uint_as_float(rk[4 * e + 2]), __uint_as_float(rk[4 * e + 3]));
+          reinterpret_cast<float4*>(dv_dst)[e] = make_float4(__uint_as_float(rv[4 * e]), __uint_as_float(rv[4 * e + 1]),
+                                                             __uint_as_float(rv[4 * e + 2]), __uint_as_float(rv[4 * e + 3]));
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) { fence_after_sync(); tmem_dealloc(tmem, 512); }
+  if (t == 0 && abort_flag) rb::set_status(status, rb::kStatusWaitTimeout);
+}
+
 }  // namespace
 
 // qkv: bf16 [T, 3 * H * 64] packed (q | k | v, each H heads of 64), offsets: int32 [B + 1] on the device, max_len: an upper bound
@@ -204,6 +391,33 @@ extern "C" int rb_ragged_attention_fwd(const void* qkv, const int32_t* offsets, 
   dim3 grid((max_len + kTile - 1) / kTile, B, H);
   ragged_attention_fwd_kernel<<<grid, 128, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(qkv), offsets, H, scale * 1.4426950408889634f,
                                                        reinterpret_cast<__nv_bfloat16*>(out), lse2, status);
+  rb::note_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// Backward of rb_ragged_attention_fwd. out / d_out: bf16 [T, H * 64]; lse2: fp32 [T, H] from the forward; delta: fp32 [T, H]
+// scratch; dqkv: fp32 [T, 3 * H * 64], zero on entry (dQ is accumulated with reductions). Same return codes as the forward.
+extern "C" int rb_ragged_attention_bwd(const void* qkv, const void* out, const void* d_out, const float* lse2, float* delta,
+                                       const int32_t* offsets, int64_t T, int B, int H, int max_len, float scale, float* dqkv,
+                                       int64_t* status, cudaStream_t st) {
+  if (B <= 0 || H <= 0 || max_len <= 0 || T <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(d_out) & 15) || (reinterpret_cast<uintptr_t>(dqkv) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 3))
+    return 1;
+  const int64_t rows = T * H;
+  const int64_t blocks = (rows + 7) / 8;
+  attention_delta_kernel<<<(int)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(out),
+                                                                                   reinterpret_cast<const __nv_bfloat16*>(d_out), rows, delta);
+  rb::note_launch();
+  const size_t smem = 1024 + 8 * (size_t)kBlk;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(ragged_attention_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 3;
+    attr = true;
+  }
+  dim3 grid((max_len + kTile - 1) / kTile, B, H);
+  ragged_attention_bwd_kernel<<<grid, 128, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const __nv_bfloat16*>(d_out),
+                                                       lse2, delta, offsets, H, scale, scale * 1.4426950408889634f, dqkv, status);
   rb::note_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }

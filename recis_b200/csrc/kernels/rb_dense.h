@@ -39,6 +39,9 @@ int rb_dot_interaction_tc_bwd(const void* x, const float* cube, const void* dout
 // int32 [B + 1] (device), out: bf16 [T, H * 64], lse2: fp32 [T, H] or null. 0 = launched, 1 = unsuitable arguments, > 1 = error.
 int rb_ragged_attention_fwd(const void* qkv, const int32_t* offsets, int B, int H, int max_len, float scale, void* out, float* lse2,
                             int64_t* status, cudaStream_t st);
+// Backward: out / d_out bf16 [T, H * 64], lse2 from the forward, delta fp32 [T, H] scratch, dqkv fp32 [T, 3 * H * 64] zeroed.
+int rb_ragged_attention_bwd(const void* qkv, const void* out, const void* d_out, const float* lse2, float* delta, const int32_t* offsets,
+                            int64_t T, int B, int H, int max_len, float scale, float* dqkv, int64_t* status, cudaStream_t st);
 void rb_fm_fwd(const float* cube, int B, int F, int D, float* out, cudaStream_t st);
 void rb_fm_bwd(const float* cube, const float* gout, int B, int F, int D, float* dcube, cudaStream_t st);
 // dy = relu ? dout * (y > 0) : dout (bf16, may be null to skip the store); db[n] += column sums of dy (fp32, may be null)

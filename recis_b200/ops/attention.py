@@ -4,9 +4,8 @@
 (q | k | v) of a batch of sequences stored back to back and returns ``[total_tokens, hidden]``.
 
 Two implementations:
-* the tensor-core kernel (``csrc/kernels/attention_tcgen05.cu``): no padding, one CTA per (sequence, head, 128-query tile);
-  forward only, head width 64, opt-in with ``RECIS_ATTENTION=tcgen05`` and used where no gradient is needed (evaluation /
-  serving);
+* the tensor-core kernels (``csrc/kernels/attention_tcgen05.cu``): no padding, one CTA per (sequence, head, 128-row tile),
+  forward and backward, head width 64; opt-in with ``RECIS_ATTENTION=tcgen05`` (not yet validated on hardware);
 * the padded path: scatter into ``[batch, max_len, heads, head_dim]``, ``F.scaled_dot_product_attention`` with a key-padding
   mask, gather the valid positions back. Differentiable; what training uses; runs on CPU as well.
 """
@@ -33,16 +32,31 @@ def _padded(qkv, seg, pos, lengths, max_len, heads):
     return o.permute(0, 2, 1, 3).reshape(B, max_len, hidden)[seg, pos]
 
 
+class _RaggedAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, offsets, heads, max_len, scale):
+        out, lse = native().ragged_attention_fwd(qkv, offsets, heads, max_len, scale)
+        ctx.save_for_backward(qkv, out, lse, offsets)
+        ctx.args = (heads, max_len, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        qkv, out, lse, offsets = ctx.saved_tensors
+        heads, max_len, scale = ctx.args
+        dqkv = native().ragged_attention_bwd(qkv, out, d_out.to(torch.bfloat16).contiguous(), lse, offsets, heads, max_len, scale)
+        return dqkv.to(qkv.dtype), None, None, None, None
+
+
 def ragged_self_attention(qkv: torch.Tensor, offsets: torch.Tensor, heads: int, max_len: int, seg: torch.Tensor = None,
                           pos: torch.Tensor = None) -> torch.Tensor:
     """``qkv``: ``[T, 3 * hidden]``; ``offsets``: ``[B + 1]`` sequence boundaries; returns ``[T, hidden]`` in ``qkv``'s dtype.
     ``seg`` / ``pos`` (sequence index and position of every token) are derived from ``offsets`` when not given."""
     hidden = qkv.shape[1] // 3
     hd = hidden // heads
-    needs_grad = torch.is_grad_enabled() and qkv.requires_grad
-    if (os.environ.get("RECIS_ATTENTION") == "tcgen05" and qkv.is_cuda and hd == 64 and not needs_grad):
-        out, _lse = native().ragged_attention_fwd(qkv.to(torch.bfloat16).contiguous(), offsets.to(torch.int32).contiguous(), heads,
-                                                  int(max_len), float(hd) ** -0.5)
+    if os.environ.get("RECIS_ATTENTION") == "tcgen05" and qkv.is_cuda and hd == 64:
+        out = _RaggedAttnFn.apply(qkv.to(torch.bfloat16).contiguous(), offsets.to(torch.int32).contiguous(), heads, int(max_len),
+                                  float(hd) ** -0.5)
         return out.to(qkv.dtype)
     lengths = (offsets[1:] - offsets[:-1]).long()
     if seg is None:

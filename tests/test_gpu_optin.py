@@ -76,3 +76,26 @@ def test_fused_exchange_variants_match_single_process(env):
     from multirank import run_ranks
     results = run_ranks(tm._rank_fn, 2, "nccl", args=("cuda",), env=dict(env, RECIS_COMM="fused", NCCL_NVLS_ENABLE="0"))
     tm._compare(results, tm._oracle(2), 2)
+
+
+def test_ragged_attention_backward_matches_padded_path():
+    code = """
+import os, torch
+from recis_b200.ops.attention import ragged_self_attention
+torch.manual_seed(1)
+lens = [5, 128, 200, 1]; H = 2
+lens_t = torch.tensor(lens)
+offs = torch.zeros(len(lens) + 1, dtype=torch.int32); offs[1:] = lens_t.cumsum(0)
+T = int(offs[-1])
+base = (torch.randn(T, 3 * H * 64, device='cuda') * 0.5).to(torch.bfloat16)
+go = (torch.randn(T, H * 64, device='cuda') * 0.1).to(torch.bfloat16)
+a = base.clone().requires_grad_(True)
+ragged_self_attention(a, offs.cuda(), H, max(lens)).backward(go)
+os.environ['RECIS_ATTENTION'] = 'off'
+b = base.float().requires_grad_(True)
+ragged_self_attention(b, offs.cuda(), H, max(lens)).backward(go.float())
+err = (a.grad.float() - b.grad).abs().max() / b.grad.abs().max()
+assert err < 5e-2, float(err)
+print('ok')
+"""
+    assert "ok" in _child(code, {"RECIS_ATTENTION": "tcgen05"})
