@@ -220,3 +220,20 @@ def test_api_parity_helpers(tmp_path):
     m = AUROC(num_thresholds=10)
     tp, fp, tn, fn = m.sync(torch.ones(3), torch.zeros(3), torch.ones(3), torch.zeros(3))
     assert float(tp.sum()) == 3.0
+
+
+def test_crypto_and_singleton_helpers():
+    import base64
+    cryptography = pytest.importorskip("cryptography")
+    from cryptography.hazmat.primitives import serialization
+    from cryptography.hazmat.primitives.asymmetric import rsa
+    from recis_b200.common.crypto_utils import decode, encode
+    from recis_b200.common.singleton import SingletonMeta
+    key = rsa.generate_private_key(public_exponent=65537, key_size=2048)
+    pub = base64.b64encode(key.public_key().public_bytes(serialization.Encoding.DER, serialization.PublicFormat.SubjectPublicKeyInfo)).decode()
+    priv = base64.b64encode(key.private_bytes(serialization.Encoding.DER, serialization.PrivateFormat.PKCS8, serialization.NoEncryption())).decode()
+    assert decode(encode("access-key-123", pub), priv) == "access-key-123"
+
+    class Once(metaclass=SingletonMeta):
+        pass
+    assert Once() is Once()
