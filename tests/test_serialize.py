@@ -154,3 +154,53 @@ def test_failures_are_clean_errors(tmp_path):
     os.remove(tmp_path / "index")
     with pytest.raises(FileNotFoundError):
         Loader(str(tmp_path), {}, {})
+
+
+def test_resharding_chain_8_4_1_8(tmp_path):
+    """Save with 8 shards, reload into 4, save, reload into 1, save, reload into 8: every id keeps its embedding and its
+    optimizer-free slots, and lands on the shard that owns its low 16 bits."""
+    torch.manual_seed(1)
+    all_ids = torch.randint(0, 1 << 44, (4000,)).unique()
+    truth = {}
+
+    def make(world):
+        tables = []
+        for r in range(world):
+            HashtableRegister().clear()
+            tables.append(HashTable([4], initializer=NormalInitializer(0, 1), name="tbl", device="cpu", slice=gen_slice(r, world)))
+        return tables
+
+    def owned(ids, sl):
+        low = ids & 0xFFFF
+        return ids[(low >= sl.slice_begin) & (low < sl.slice_end)]
+
+    def save(tables, world, d):
+        os.makedirs(d, exist_ok=True)
+        for r, ht in enumerate(tables):
+            Saver(r, world, 2, filter_out_sparse_param(ht), {}, str(d)).save()
+
+    def load(world, d):
+        tables = make(world)
+        for ht in tables:
+            Loader(str(d), filter_out_sparse_param(ht), {}).load()
+        return tables
+
+    tables = make(8)
+    for r, ht in enumerate(tables):
+        mine = owned(all_ids, gen_slice(r, 8))
+        for i, v in zip(mine.tolist(), ht(mine).detach()):
+            truth[i] = v.clone()
+    prev_world = 8
+    for step, world in enumerate([4, 1, 8]):
+        d = tmp_path / f"ckpt{step}"
+        save(tables, prev_world, d)
+        tables = load(world, d)
+        seen = 0
+        for r, ht in enumerate(tables):
+            ids, rows = ht.ids_map()
+            assert torch.equal(owned(ids, gen_slice(r, world)).sort().values, ids.sort().values)
+            for i, row in zip(ids.tolist(), rows.tolist()):
+                assert torch.equal(ht.embeddings()[row], truth[i])
+            seen += ids.numel()
+        assert seen == all_ids.numel()
+        prev_world = world
