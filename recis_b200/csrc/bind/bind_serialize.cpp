@@ -10,6 +10,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <fcntl.h>
@@ -17,6 +18,7 @@
 #include <unistd.h>
 #include "../kernels/rb_kernels.h"
 #include "../cpu/rb_cpu.h"
+#include "../platform/rb_platform.h"
 
 namespace py = pybind11;
 using torch::Tensor;
@@ -41,11 +43,20 @@ struct FileJob {
   std::string error;
 };
 
-void write_all(FILE* f, const void* p, size_t n, const std::string& path) {
-  if (n && std::fwrite(p, 1, n, f) != n) throw std::runtime_error("short write to " + path);
+using rb::platform::Env;
+using rb::platform::FileOutputBuffer;
+using rb::platform::FileSystem;
+using rb::platform::Status;
+
+void check(const Status& s) {
+  if (!s.ok()) throw std::runtime_error(s.ToString());
 }
 
-void write_gather_block(FILE* f, const Block& b, const std::string& path) {
+void write_all(FileOutputBuffer* f, const void* p, size_t n, const std::string& path) {
+  if (n) check(f->Append(p, n));
+}
+
+void write_gather_block(FileOutputBuffer* f, const Block& b, const std::string& path) {
   const int64_t n = b.rows.numel();
   if (n == 0) return;
   const bool is_f32 = b.tensor.scalar_type() == torch::kFloat32;
@@ -93,11 +104,15 @@ void write_gather_block(FILE* f, const Block& b, const std::string& path) {
 
 void run_job(FileJob* job) {
   try {
-    const std::string tmp = job->path + ".tmp";
-    FILE* f = std::fopen(tmp.c_str(), "wb");
-    if (!f) throw std::runtime_error("cannot open " + tmp);
-    std::vector<char> buf(8 << 20);
-    std::setvbuf(f, buf.data(), _IOFBF, buf.size());
+    // written under a temporary name and renamed when complete: a failed save never leaves a half-written shard behind
+    std::shared_ptr<FileSystem> fs;
+    std::string local;
+    check(Env::Default()->GetFileSystemForFile(job->path, &fs, &local));
+    const std::string tmp = local + ".tmp";
+    std::unique_ptr<rb::platform::WritableFile> wf;
+    check(fs->NewWritableFile(tmp, &wf));
+    FileOutputBuffer out(std::move(wf), 8u << 20);
+    FileOutputBuffer* f = &out;
     std::string header = job->header;
     header.append(8 - (header.size() % 8), ' ');
     const uint64_t hlen = header.size();
@@ -107,8 +122,8 @@ void run_job(FileJob* job) {
       if (b.kind == 0) write_all(f, b.tensor.data_ptr(), (size_t)b.tensor.numel() * b.tensor.element_size(), tmp);
       else write_gather_block(f, b, tmp);
     }
-    if (std::fflush(f) != 0 || std::fclose(f) != 0) throw std::runtime_error("flush/close failed for " + tmp);
-    if (std::rename(tmp.c_str(), job->path.c_str()) != 0) throw std::runtime_error("rename failed for " + job->path);
+    check(out.Close());
+    check(fs->RenameFile(tmp, local));
   } catch (const std::exception& e) {
     job->error = e.what();
   }
@@ -143,17 +158,27 @@ void st_write_files(const std::vector<std::tuple<std::string, std::string, std::
   for (auto& j : jobs) TORCH_CHECK(j.error.empty(), "checkpoint write failed: ", j.error);
 }
 
+std::unique_ptr<rb::platform::RandomAccessFile> open_for_read(const std::string& path) {
+  std::shared_ptr<FileSystem> fs;
+  std::string local;
+  Status s = Env::Default()->GetFileSystemForFile(path, &fs, &local);
+  TORCH_CHECK(s.ok(), s.ToString());
+  std::unique_ptr<rb::platform::RandomAccessFile> f;
+  s = fs->NewRandomAccessFile(local, &f);
+  TORCH_CHECK(s.ok(), s.ToString());
+  return f;
+}
+
 // (header json, offset of the first data byte)
 std::tuple<std::string, int64_t> st_read_header(const std::string& path) {
-  FILE* f = std::fopen(path.c_str(), "rb");
-  TORCH_CHECK(f, "cannot open ", path);
+  auto f = open_for_read(path);
   uint64_t hlen = 0;
-  const bool ok = std::fread(&hlen, sizeof(hlen), 1, f) == 1;
-  TORCH_CHECK(ok && hlen < (1ull << 32), "corrupt safetensors header in ", path);
+  size_t got = 0;
+  Status s = f->Read(0, sizeof(hlen), &hlen, &got);
+  TORCH_CHECK(s.ok() && got == sizeof(hlen) && hlen < (1ull << 32), "corrupt safetensors header in ", path);
   std::string header(hlen, '\0');
-  const bool ok2 = std::fread(header.data(), 1, hlen, f) == hlen;
-  std::fclose(f);
-  TORCH_CHECK(ok2, "truncated safetensors header in ", path);
+  s = f->Read(sizeof(hlen), hlen, header.data(), &got);
+  TORCH_CHECK(s.ok() && got == hlen, "truncated safetensors header in ", path);
   return {header, (int64_t)(8 + hlen)};
 }
 
@@ -162,17 +187,81 @@ void st_read_into(const std::string& path, int64_t offset, Tensor out) {
   TORCH_CHECK(!out.is_cuda() && out.is_contiguous());
   const size_t n = (size_t)out.numel() * out.element_size();
   char* dst = reinterpret_cast<char*>(out.data_ptr());
-  py::gil_scoped_release nogil;
-  const int fd = ::open(path.c_str(), O_RDONLY);
-  TORCH_CHECK(fd >= 0, "cannot open ", path);
+  auto f = open_for_read(path);
   size_t got = 0;
-  while (got < n) {
-    const ssize_t r = ::pread(fd, dst + got, n - got, offset + (int64_t)got);
-    if (r <= 0) break;
-    got += (size_t)r;
+  Status s;
+  {
+    py::gil_scoped_release nogil;
+    s = f->Read((uint64_t)offset, n, dst, &got);
   }
-  ::close(fd);
+  TORCH_CHECK(s.ok(), s.ToString());
   TORCH_CHECK(got == n, "truncated tensor data in ", path, ": wanted ", n, " bytes at ", offset, ", got ", got);
+}
+
+// ---- thin Python access to the platform layer (path handling of the checkpoint manager, tests)
+bool fs_exists(const std::string& path) {
+  std::shared_ptr<FileSystem> fs; std::string local;
+  Status s = Env::Default()->GetFileSystemForFile(path, &fs, &local);
+  TORCH_CHECK(s.ok(), s.ToString());
+  return fs->FileExists(local);
+}
+int64_t fs_file_size(const std::string& path) {
+  std::shared_ptr<FileSystem> fs; std::string local; uint64_t size = 0;
+  Status s = Env::Default()->GetFileSystemForFile(path, &fs, &local);
+  if (s.ok()) s = fs->GetFileSize(local, &size);
+  TORCH_CHECK(s.ok(), s.ToString());
+  return (int64_t)size;
+}
+void fs_mkdirs(const std::string& path) {
+  std::shared_ptr<FileSystem> fs; std::string local;
+  Status s = Env::Default()->GetFileSystemForFile(path, &fs, &local);
+  if (s.ok()) s = fs->CreateDirRecursive(local);
+  TORCH_CHECK(s.ok(), s.ToString());
+}
+void fs_rename(const std::string& from, const std::string& to) {
+  std::shared_ptr<FileSystem> fs, fs2; std::string a, b;
+  Status s = Env::Default()->GetFileSystemForFile(from, &fs, &a);
+  if (s.ok()) s = Env::Default()->GetFileSystemForFile(to, &fs2, &b);
+  TORCH_CHECK(s.ok(), s.ToString());
+  TORCH_CHECK(fs == fs2, "rename across file systems: ", from, " -> ", to);
+  s = fs->RenameFile(a, b);
+  TORCH_CHECK(s.ok(), s.ToString());
+}
+void fs_delete(const std::string& path) {
+  std::shared_ptr<FileSystem> fs; std::string local;
+  Status s = Env::Default()->GetFileSystemForFile(path, &fs, &local);
+  if (s.ok()) s = fs->DeleteFile(local);
+  TORCH_CHECK(s.ok(), s.ToString());
+}
+std::vector<std::string> fs_list(const std::string& dir) {
+  std::shared_ptr<FileSystem> fs; std::string local; std::vector<std::string> names;
+  Status s = Env::Default()->GetFileSystemForFile(dir, &fs, &local);
+  if (s.ok()) s = fs->GetChildren(local, &names);
+  TORCH_CHECK(s.ok(), s.ToString());
+  std::sort(names.begin(), names.end());
+  return names;
+}
+void fs_write_bytes(const std::string& path, const std::string& data) {
+  std::shared_ptr<FileSystem> fs; std::string local;
+  Status s = Env::Default()->GetFileSystemForFile(path, &fs, &local);
+  TORCH_CHECK(s.ok(), s.ToString());
+  std::unique_ptr<rb::platform::WritableFile> wf;
+  s = fs->NewWritableFile(local + ".tmp", &wf);
+  TORCH_CHECK(s.ok(), s.ToString());
+  FileOutputBuffer out(std::move(wf), 1u << 16);
+  s = out.Append(data.data(), data.size());
+  if (s.ok()) s = out.Close();
+  if (s.ok()) s = fs->RenameFile(local + ".tmp", local);
+  TORCH_CHECK(s.ok(), s.ToString());
+}
+py::bytes fs_read_bytes(const std::string& path) {
+  const int64_t n = fs_file_size(path);
+  std::string buf((size_t)n, '\0');
+  auto f = open_for_read(path);
+  size_t got = 0;
+  Status s = f->Read(0, (size_t)n, buf.data(), &got);
+  TORCH_CHECK(s.ok() && got == (size_t)n, "short read of ", path);
+  return py::bytes(buf);
 }
 
 }  // namespace
@@ -181,4 +270,17 @@ void init_serialize(py::module& m) {
   m.def("st_write_files", &st_write_files);
   m.def("st_read_header", &st_read_header);
   m.def("st_read_into", &st_read_into);
+  m.def("fs_exists", &fs_exists);
+  m.def("fs_file_size", &fs_file_size);
+  m.def("fs_mkdirs", &fs_mkdirs);
+  m.def("fs_rename", &fs_rename);
+  m.def("fs_delete", &fs_delete);
+  m.def("fs_list", &fs_list);
+  m.def("fs_write_bytes", &fs_write_bytes);
+  m.def("fs_read_bytes", &fs_read_bytes);
+  m.def("fs_join", &rb::platform::JoinPath);
+  m.def("fs_dirname", &rb::platform::Dirname);
+  m.def("fs_basename", &rb::platform::Basename);
+  m.def("fs_parse_uri", [](const std::string& uri) { std::string sc, p; rb::platform::ParseURI(uri, &sc, &p); return std::make_pair(sc, p); });
+  m.def("fs_schemes", []() { return Env::Default()->Schemes(); });
 }

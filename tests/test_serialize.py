@@ -5,6 +5,7 @@ import os
 import pytest
 import torch
 
+import recis_b200
 from recis_b200.nn import EmbeddingEngine, EmbeddingOption, HashTable, filter_out_sparse_param, gen_slice
 from recis_b200.nn.hashtable_hook import FilterHook
 from recis_b200.nn.initializers import NormalInitializer
@@ -204,3 +205,44 @@ def test_resharding_chain_8_4_1_8(tmp_path):
             seen += ids.numel()
         assert seen == all_ids.numel()
         prev_world = world
+
+
+def test_native_platform_layer(tmp_path):
+    C = recis_b200.native()
+    assert C.fs_join("a/", "/b") == "a/b" and C.fs_join("a", "b") == "a/b" and C.fs_join("", "b") == "b"
+    assert C.fs_dirname("/x/y/z.txt") == "/x/y" and C.fs_basename("/x/y/z.txt") == "z.txt" and C.fs_dirname("z") == ""
+    assert C.fs_parse_uri("file:///tmp/a") == ("file", "/tmp/a") and C.fs_parse_uri("/tmp/a") == ("", "/tmp/a")
+    assert C.fs_parse_uri("weird path://x") == ("", "weird path://x")
+    assert set(C.fs_schemes()) >= {"", "file"}
+    d = str(tmp_path / "a" / "b" / "c")
+    C.fs_mkdirs(d)
+    C.fs_mkdirs(d)                                              # idempotent
+    payload = bytes(range(256)) * 1000
+    C.fs_write_bytes("file://" + d + "/blob.bin", payload)       # scheme form and plain form name the same file
+    assert C.fs_exists(d + "/blob.bin") and C.fs_file_size(d + "/blob.bin") == len(payload)
+    assert C.fs_read_bytes(d + "/blob.bin") == payload and C.fs_list(d) == ["blob.bin"]       # no ".tmp" left behind
+    C.fs_rename(d + "/blob.bin", d + "/blob2.bin")
+    assert C.fs_list(d) == ["blob2.bin"]
+    C.fs_delete(d + "/blob2.bin")
+    assert not C.fs_exists(d + "/blob2.bin")
+    with pytest.raises(RuntimeError, match="no file system registered"):
+        C.fs_exists("pangu://cluster/path")
+    with pytest.raises(RuntimeError):
+        C.fs_write_bytes(str(tmp_path / "missing_dir" / "x.bin"), b"1")
+    assert not os.path.exists(tmp_path / "missing_dir")
+
+
+def test_failed_save_leaves_no_partial_shard(tmp_path):
+    """A save whose files cannot be created fails with an error and leaves nothing behind that a later load could mistake for a
+    checkpoint (shards are written under a temporary name and renamed when complete)."""
+    HashtableRegister().clear()
+    eng, _opt = _trained_engine(steps=1)
+    good = tmp_path / "good"
+    Saver(0, 1, 1, filter_out_sparse_param(eng), {"w": torch.ones(3)}, str(good)).save()
+    before = sorted(os.listdir(good))
+    blocker = tmp_path / "blocker"
+    blocker.write_text("a regular file where a directory is expected")
+    with pytest.raises((RuntimeError, OSError)):
+        Saver(0, 1, 1, filter_out_sparse_param(eng), {"w": torch.ones(3)}, str(blocker / "ckpt")).save()
+    assert blocker.read_text().startswith("a regular file")
+    assert sorted(os.listdir(good)) == before and not any(f.endswith(".tmp") for f in before)
