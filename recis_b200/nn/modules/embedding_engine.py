@@ -28,6 +28,7 @@ from torch import nn
 
 from ... import native
 from ...ragged.tensor import RaggedTensor
+from ...utils import debug as _debug
 from .embedding import DynamicEmbedding, EmbeddingOption
 
 
@@ -135,6 +136,8 @@ class EmbeddingEngine(nn.Module):
                 shape = tuple(fea.shape[:-1]) + (dim,)
         else:
             raise TypeError(f"EmbeddingEngine only support tensor but get {type(fea)}")
+        if _debug.enabled():
+            _debug.check_ragged("embedding input", ids, offsets, weight)
         if ids.dtype != torch.int64:
             ids = ids.to(torch.int64)
         if offsets.dtype != torch.int32:

@@ -77,3 +77,14 @@ def test_empty_batch_and_empty_feature():
     off = torch.zeros(4, dtype=torch.int32)
     out = eng({"a": RaggedTensor(torch.zeros(0, dtype=torch.int64), [off]), "b": RaggedTensor(torch.tensor([1, 2, 3]), [torch.tensor([0, 1, 2, 3], dtype=torch.int32)])})
     assert out["a"].shape == (3, 4) and float(out["a"].detach().abs().sum()) == 0 and out["b"].shape == (3, 4)
+
+
+def test_debug_bounds_rejects_malformed_ragged_inputs(monkeypatch):
+    monkeypatch.setenv("RECIS_DEBUG_BOUNDS", "1")
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=4, shared_name="a", device="cpu", use_weight=False)})
+    vals = torch.arange(6)
+    ok = eng({"a": RaggedTensor(vals, [torch.tensor([0, 2, 6], dtype=torch.int32)])})["a"]
+    assert ok.shape == (2, 4)
+    for bad, msg in (([1, 2, 6], "start at 0"), ([0, 4, 3, 6], "decrease"), ([0, 2, 5], "does not match")):
+        with pytest.raises(ValueError, match=msg):
+            eng({"a": RaggedTensor(vals, [torch.tensor(bad, dtype=torch.int32)])})
