@@ -225,7 +225,7 @@ def run(args, arm):
             "metric": "train samples/s (DLRM-style CTR, device-timed, max over ranks)",
             "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16 dense tower, fp32 embeddings and optimizer state", "data": "synthetic (seeded), random-init weights",
+            "dtype": "bf16", "data": "synthetic (seeded), random-init weights",
             "impl": arm.name,
             "config": {
                 "model": "dlrm_ctr: 13 dense + 26 multi-hot fields (Poisson(20) in [1,100]) -> one merged dim-128 dynamic table, "
@@ -234,6 +234,7 @@ def run(args, arm):
                 "ids": "Zipf(1.05) over a 2^40 id space, 1e8 distinct ids in total over the 26 fields", "parallelism": f"dp{world} dense + row-sharded embeddings",
                 "l2": "no explicit flush: each step touches > 1 GB of embedding rows and optimizer state, far beyond the 126 MB L2",
                 "comm": arm.comm_mode(),
+                "precision": "bf16 dense tower (fp32 accumulation, fp32 master weights); fp32 embedding table, optimizer state and exchange",
             },
             "clocks": clocks,
             "e2e": {"value": value_e2e, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d_bytes,
