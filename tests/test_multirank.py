@@ -94,7 +94,7 @@ def _compare(results, oracle, world):
     assert torch.allclose(a, b, atol=1e-4, rtol=1e-3)
 
 
-@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
 def test_gloo_ranks_match_single_process(world):
     results = run_ranks(_rank_fn, world, "gloo", args=("cpu",))
     _compare(results, _oracle(world), world)
