@@ -109,7 +109,7 @@ def _need_gpus(n):
 @pytest.mark.parametrize("comm", ["fused", "nccl"])
 def test_gpu_ranks_match_single_process(comm):
     _need_gpus(2)
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), int(os.environ.get("RECIS_TEST_GPU_RANKS", "2")))   # 2 ranks by default; more on request
     results = run_ranks(_rank_fn, world, "nccl", args=("cuda",), env={"RECIS_COMM": comm, "NCCL_NVLS_ENABLE": "0"})
     _compare(results, _oracle(world), world)
 
@@ -137,7 +137,7 @@ def _allreduce_fn(rank, world):
 @pytest.mark.gpu
 def test_p2p_dense_allreduce():
     _need_gpus(2)
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), int(os.environ.get("RECIS_TEST_GPU_RANKS", "2")))   # 2 ranks by default; more on request
     results = run_ranks(_allreduce_fn, world, "nccl", env={"RECIS_COMM": "fused", "NCCL_NVLS_ENABLE": "0"})
     shapes = ((1000, 37), (513,), (64, 64))
     for it in range(3):
