@@ -130,6 +130,12 @@ class FusedExchange:
     # ------------------------------------------------------------------ forward
     def forward(self, emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold,
                 step):
+        with torch.profiler.record_function("recis_b200/exchange_forward"):
+            return self._forward(emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly,
+                                 threshold, step)
+
+    def _forward(self, emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold,
+                 step):
         C = native()
         n = ids.numel()
         lane = self.lanes.get(lane_key)
@@ -173,6 +179,10 @@ class FusedExchange:
 
     # ------------------------------------------------------------------ backward (requester side) + staging
     def backward(self, emb_mod, s, grad_out, worker_scale):
+        with torch.profiler.record_function("recis_b200/exchange_backward"):
+            self._backward(emb_mod, s, grad_out, worker_scale)
+
+    def _backward(self, emb_mod, s, grad_out, worker_scale):
         C = native()
         lane = s["lane"]
         h, me, D = lane.heap, self.rank, self.D
@@ -204,6 +214,10 @@ class FusedExchange:
     # ------------------------------------------------------------------ owner side: pull + reduce (+ update)
     def owner_reduce(self, impl, rec, apply, kind=2, lr=0.0, b1=0.0, b2=0.0, eps=0.0, decay=1.0, alpha=0.0, grad_scale=1.0,
                      w=None, s1=None, s2=None):
+        with torch.profiler.record_function("recis_b200/owner_reduce_update"):
+            return self._owner_reduce(impl, rec, apply, kind, lr, b1, b2, eps, decay, alpha, grad_scale, w, s1, s2)
+
+    def _owner_reduce(self, impl, rec, apply, kind, lr, b1, b2, eps, decay, alpha, grad_scale, w, s1, s2):
         C = native()
         lane = rec["lane"]
         h = lane.heap
