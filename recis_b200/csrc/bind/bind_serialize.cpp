@@ -52,6 +52,10 @@ void check(const Status& s) {
   if (!s.ok()) throw std::runtime_error(s.ToString());
 }
 
+void cuda_ok(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + " failed: " + cudaGetErrorString(e));
+}
+
 void write_all(FileOutputBuffer* f, const void* p, size_t n, const std::string& path) {
   if (n) check(f->Append(p, n));
 }
@@ -79,7 +83,7 @@ void write_gather_block(FileOutputBuffer* f, const Block& b, const std::string& 
   for (int i = 0; i < 2; ++i) {
     stage_dev[i] = torch::empty({chunk, D}, b.tensor.options());
     stage_host[i] = torch::empty({chunk, D}, b.tensor.options().device(torch::kCPU).pinned_memory(true));
-    cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming);
+    cuda_ok(cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming), "cudaEventCreate");
   }
   auto issue = [&](int64_t s, int slot) {
     const int64_t m = std::min(chunk, n - s);
@@ -89,14 +93,16 @@ void write_gather_block(FileOutputBuffer* f, const Block& b, const std::string& 
       auto part = b.tensor.index_select(0, b.rows.narrow(0, s, m).to(torch::kInt64));
       stage_dev[slot].view({-1}).narrow(0, 0, m).copy_(part.view({-1}), true);
     }
-    cudaMemcpyAsync(stage_host[slot].data_ptr(), stage_dev[slot].data_ptr(), (size_t)m * D * esz, cudaMemcpyDeviceToHost, stream);
-    cudaEventRecord(done[slot], stream);
+    cuda_ok(cudaMemcpyAsync(stage_host[slot].data_ptr(), stage_dev[slot].data_ptr(), (size_t)m * D * esz, cudaMemcpyDeviceToHost, stream),
+            "device-to-host copy of a checkpoint chunk");
+    cuda_ok(cudaEventRecord(done[slot], stream), "cudaEventRecord");
   };
   int slot = 0;
   issue(0, 0);
   for (int64_t s = 0; s < n; s += chunk, slot ^= 1) {
     if (s + chunk < n) issue(s + chunk, slot ^ 1);
-    cudaEventSynchronize(done[slot]);
+    // a failed copy must fail the save: the staging buffer would otherwise be written as if it held the rows
+    cuda_ok(cudaEventSynchronize(done[slot]), "waiting for a checkpoint chunk");
     write_all(f, stage_host[slot].data_ptr(), (size_t)std::min(chunk, n - s) * D * esz, path);
   }
   for (int i = 0; i < 2; ++i) cudaEventDestroy(done[i]);

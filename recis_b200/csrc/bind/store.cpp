@@ -102,14 +102,23 @@ void EmbeddingStore::post_mirror(int64_t n_issued, const int32_t* n_dev) {
   auto st = at::cuda::getCurrentCUDAStream();
   int64_t* dst = mirror_host_ + slot * kMirrorStride;
   dst[RB_CTR_COUNT] = -1;                                   // "no device-side count in this slot"
-  cudaMemcpyAsync(dst, ctr_.data_ptr<int64_t>(), sizeof(int64_t) * RB_CTR_COUNT, cudaMemcpyDeviceToHost, st);
-  if (n_dev != nullptr) {
+  bool posted = cudaMemcpyAsync(dst, ctr_.data_ptr<int64_t>(), sizeof(int64_t) * RB_CTR_COUNT, cudaMemcpyDeviceToHost, st) == cudaSuccess;
+  if (posted && n_dev != nullptr) {
     dst[RB_CTR_COUNT] = 0;
-    cudaMemcpyAsync(dst + RB_CTR_COUNT, n_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+    posted = cudaMemcpyAsync(dst + RB_CTR_COUNT, n_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, st) == cudaSuccess;
   }
-  cudaEventRecord(mirror_ev_[slot], st);
-  mirror_issued_[slot] = issued_total_;
+  posted = posted && cudaEventRecord(mirror_ev_[slot], st) == cudaSuccess;
+  // a slot whose copy could not be posted is never absorbed: the bounds then stay pessimistic until a later mirror lands
+  mirror_issued_[slot] = posted ? issued_total_ : -1;
   mirror_calls_[slot] = calls_total_;
+}
+
+EmbeddingStore::~EmbeddingStore() {
+  if (mirror_host_ != nullptr) {
+    for (int i = 0; i < kMirror; ++i) cudaEventDestroy(mirror_ev_[i]);
+    cudaFreeHost(mirror_host_);
+    mirror_host_ = nullptr;
+  }
 }
 
 void EmbeddingStore::absorb_mirror() {

@@ -11,6 +11,9 @@ class EmbeddingStore {
  public:
   EmbeddingStore(int64_t dim, int64_t capacity, torch::Device device, int init_kind, double a, double b, double lo, double hi,
                  int64_t seed, bool track_last_seen, bool growable, c10::optional<torch::Tensor> emb_storage);
+  ~EmbeddingStore();
+  EmbeddingStore(const EmbeddingStore&) = delete;
+  EmbeddingStore& operator=(const EmbeddingStore&) = delete;
   torch::Tensor lookup_or_insert(const torch::Tensor& ids, c10::optional<torch::Tensor> n_dev, c10::optional<torch::Tensor> step,
                                  int64_t admit_threshold);
   torch::Tensor find(const torch::Tensor& ids, c10::optional<torch::Tensor> n_dev);
