@@ -114,9 +114,11 @@ class OrcDataset(DatasetBase):
 
     def __init__(self, batch_size: int, worker_idx: int = 0, worker_num: int = 1, read_threads_num: int = 2, prefetch: int = 2,
                  drop_remainder: bool = False, shuffle: bool = False, ragged_format: bool = True, transform_fn: Optional[Callable] = None,
-                 dtype: torch.dtype = torch.float32, device: str = "cpu", pin: bool = False, seed: int = 0, native_reader: bool = True):
+                 dtype: torch.dtype = torch.float32, device: str = "cpu", pin: bool = False, seed: int = 0, native_reader: bool = True,
+                 repeat: int = 1):
         self.batch_size, self.worker_idx, self.worker_num = batch_size, worker_idx, worker_num
         self.read_threads_num, self.native_reader = read_threads_num, native_reader
+        self.repeat = max(int(repeat), 1)           # passes over this worker's files (the role of column-io's RepeatDataset)
         self.drop_remainder, self.shuffle, self.transform_fn, self.dtype, self.device, self.pin = drop_remainder, shuffle, transform_fn, dtype, device, pin
         self.prefetch, self.seed = prefetch, seed
         self._paths: List[str] = []
@@ -136,7 +138,8 @@ class OrcDataset(DatasetBase):
         self._fixed[name] = default_value
 
     def _my_paths(self):
-        return [p for i, p in enumerate(sorted(self._paths)) if i % self.worker_num == self.worker_idx]
+        mine = [p for i, p in enumerate(sorted(self._paths)) if i % self.worker_num == self.worker_idx]
+        return mine * self.repeat
 
     @staticmethod
     def _read_table(path):

@@ -102,3 +102,18 @@ def test_native_reader_reports_a_missing_file(tmp_path):
     ds.varlen_feature("uid")
     with pytest.raises(RuntimeError, match="missing.orc"):
         list(ds)
+
+
+def test_repeat_and_worker_sharding(tmp_path):
+    paths = _write(tmp_path)
+    rows_native = sum(b["label"].shape[0] for b in _dataset(paths, True, repeat=2))
+    rows_python = sum(b["label"].shape[0] for b in _dataset(paths, False, repeat=2))
+    assert rows_native == rows_python == 2 * (70 + 33 + 50)
+    # two workers split the files; together they see every row once
+    per_worker = []
+    for w in range(2):
+        ds = OrcDataset(batch_size=32, worker_idx=w, worker_num=2)
+        ds.add_paths(paths)
+        ds.varlen_feature("uid")
+        per_worker.append(sum(b["uid"].values().numel() for b in ds))
+    assert sorted(per_worker) == sorted([70 + 50, 33])
