@@ -75,6 +75,10 @@ class EmbeddingOption:
             self.initializer = ConstantInitializer(init_val=0)
         if self.fp16_enabled:
             assert self.dtype in (torch.int8,), "only int8 emb can set fp16_enabled"
+        if self.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            # rows and optimizer state are kept in fp32; float16 / bfloat16 select the dtype of the lookup result only.
+            # Quantised (int8) tables, which the reference serves read-only with an fp16 upcast, are not implemented.
+            raise NotImplementedError(f"embedding dtype {self.dtype} is not supported (float32, float16, bfloat16 are)")
         assert self.combiner in ("sum", "mean", "tile"), \
             f"Hashtable combiner only support [sum/mean/tile], but got {self.combiner}"
         assert self.grad_reduce_by in ("worker", "id")
@@ -262,8 +266,10 @@ class DynamicEmbedding(torch.nn.Module):
         offsets = offsets.to(device=dev, dtype=torch.int32).contiguous()
         if weights is not None:
             weights = weights.detach().reshape(-1).to(device=dev, dtype=torch.float32).contiguous()
-        return _LookupPoolFn.apply(self._holder, self, ids, offsets, weights, combiner, int(tile_len), perm, self.training,
-                                   admit_hook if admit_hook is not None else self._emb_opt.admit_hook, lane)
+        out = _LookupPoolFn.apply(self._holder, self, ids, offsets, weights, combiner, int(tile_len), perm, self.training,
+                                  admit_hook if admit_hook is not None else self._emb_opt.admit_hook, lane)
+        # storage and pooling are fp32; a half-precision table dtype is the dtype the model sees
+        return out if self._emb_opt.dtype == torch.float32 else out.to(self._emb_opt.dtype)
 
     def deal_with_tensor(self, input_tensor):
         if isinstance(input_tensor, RaggedTensor):

@@ -141,3 +141,18 @@ def test_non_trainable_feature_gets_no_gradient():
     emb = t.impl.store.emb()[rows]
     child = keys >> 52
     assert torch.all(emb[child == 0] == 1.0) and torch.all(emb[child == 1] != 1.0)
+
+
+def test_half_precision_table_dtype_is_the_output_dtype():
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=4, shared_name="a", device="cpu", dtype=torch.bfloat16,
+                                                initializer=ConstantInitializer(0.25))})
+    opt = SparseSGD(filter_out_sparse_param(eng), lr=0.5)
+    out = eng({"a": torch.arange(3)})["a"]
+    assert out.dtype == torch.bfloat16 and out.requires_grad
+    out.float().sum().backward()
+    opt.step()
+    (t,) = eng.tables().values()
+    assert t.impl.store.emb().dtype == torch.float32                      # rows and optimizer state stay fp32
+    assert torch.allclose(eng({"a": torch.arange(3)})["a"].float(), torch.full((3, 4), -0.25))
+    with pytest.raises(NotImplementedError):
+        EmbeddingOption(embedding_dim=4, dtype=torch.int8, device="cpu")
