@@ -27,6 +27,8 @@ def _entry(rank, world, backend, port, fn, args, outdir, env):
             dist.init_process_group("gloo", rank=rank, world_size=world)
         out = fn(rank, world, *args)
         torch.save(out, os.path.join(outdir, f"rank{rank}.pt"))
+        if env.get("RB_NO_FINAL_BARRIER") == "1":
+            os._exit(0)                          # a peer may be gone on purpose: do not wait for it in a barrier
         dist.barrier()
         dist.destroy_process_group()
     except Exception:
@@ -35,8 +37,9 @@ def _entry(rank, world, backend, port, fn, args, outdir, env):
         raise
 
 
-def run_ranks(fn, world, backend="gloo", args=(), env=None, timeout=300):
-    """Run ``fn(rank, world, *args)`` on ``world`` child processes; returns the list of per-rank results."""
+def run_ranks(fn, world, backend="gloo", args=(), env=None, timeout=300, allow_missing=False):
+    """Run ``fn(rank, world, *args)`` on ``world`` child processes; returns the list of per-rank results (``None`` for a rank that
+    left no result when ``allow_missing`` is set)."""
     outdir = tempfile.mkdtemp(prefix="rb_ranks_")
     ctx = mp.get_context("spawn")
     port = free_port()
@@ -55,4 +58,11 @@ def run_ranks(fn, world, backend="gloo", args=(), env=None, timeout=300):
             errs.append(open(err).read())
     if errs:
         raise RuntimeError("\n".join(errs))
-    return [torch.load(os.path.join(outdir, f"rank{r}.pt"), weights_only=False) for r in range(world)]
+    outs = []
+    for r in range(world):
+        f = os.path.join(outdir, f"rank{r}.pt")
+        if allow_missing and not os.path.exists(f):
+            outs.append(None)
+        else:
+            outs.append(torch.load(f, weights_only=False))
+    return outs

@@ -96,3 +96,61 @@ def test_truncated_checkpoint_shard_is_a_clean_error(tmp_path):
     eng2 = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=4, shared_name="a", device="cpu")})
     with pytest.raises((RuntimeError, ValueError, OSError)):
         Loader(str(tmp_path), filter_out_sparse_param(eng2), {}).load()
+
+
+def _trainer_case(rank, world, mode):
+    """Two ranks train DeepFM through the Trainer with heartbeats on; in ``mode == "die"`` rank 1 stops after two steps."""
+    import tempfile
+
+    from recis_b200.framework import Trainer, TrainingArguments
+    from recis_b200.framework.health import PeerLostError
+    from recis_b200.io import SparseFieldSpec, StateDataset, SyntheticDataset, SyntheticSpec, WrapEndDataset
+    from recis_b200.models.deepfm import DeepFM
+    from recis_b200.nn import filter_out_sparse_param
+    from recis_b200.optim import DenseAdam, SparseAdagrad
+    torch.manual_seed(0)
+    fields = ["c0", "c1", "c2"]
+    spec = SyntheticSpec(batch=32, dense_dim=13, label_rate=0.3, seed=rank,
+                         sparse=[SparseFieldSpec(f, zipf_a=1.1, id_bits=20, universe=500, length="fixed", mean_len=1) for f in fields])
+    model = DeepFM(fields, device="cpu", compute_dtype=torch.float32, hidden=(16,))
+
+    class Loss(torch.nn.Module):
+        def __init__(self, m):
+            super().__init__()
+            self.m = m
+            self.calls = 0
+
+        def forward(self, batch):
+            self.calls += 1
+            if mode == "die" and rank == 1 and self.calls == 3:
+                os._exit(0)                      # a crashed rank: no clean-up, no further heartbeats, between two steps
+            return self.m(batch)[0]
+
+    steps = 4 if mode == "ok" else 400
+    args = TrainingArguments(output_dir=tempfile.mkdtemp(), log_steps=100, train_steps=steps, save_steps=10_000, heartbeat_timeout=1.5,
+                             stop_check_interval=10_000)
+    wrapped = Loss(model)
+    trainer = Trainer(model=wrapped, args=args, train_dataset=WrapEndDataset(StateDataset(SyntheticDataset(spec, steps=steps), save_interval=50)),
+                      dense_optimizers=(DenseAdam([p for p in model.parameters() if p.requires_grad], lr=1e-3), None),
+                      sparse_optimizer=SparseAdagrad(filter_out_sparse_param(model), lr=0.01))
+    assert trainer.peer_monitor is not None
+    try:
+        trainer.train()
+        return {"done": True, "steps": wrapped.calls}
+    except PeerLostError as e:
+        return {"done": False, "lost": e.rank, "steps": wrapped.calls}
+    except RuntimeError as e:                 # the collective inside a step noticed first (connection closed by the dead peer)
+        return {"done": False, "lost": None, "error": str(e)[:120], "steps": wrapped.calls}
+
+
+def test_trainer_with_heartbeats_runs_clean_on_two_ranks():
+    res = run_ranks(_trainer_case, 2, "gloo", args=("ok",))
+    assert all(r["done"] and r["steps"] == 4 for r in res)
+
+
+def test_trainer_reports_a_rank_that_died_between_steps():
+    res = run_ranks(_trainer_case, 2, "gloo", args=("die",), env={"RB_NO_FINAL_BARRIER": "1"}, allow_missing=True, timeout=120)
+    assert res[1] is None                                   # the dead rank left nothing
+    survivor = res[0]
+    assert survivor is not None and survivor["done"] is False and survivor["steps"] < 400
+    assert survivor.get("lost") == 1 or survivor.get("error")
