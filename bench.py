@@ -167,7 +167,7 @@ def run(args, arm):
     fields, spec = spec_for(args, rank)
     n_batches = args.warmup + args.steps
     # rows per GPU: this rank's share of the 1e8-row table with Adam state (1536 B per row) plus head-room for the rows the
-    # allocator budgets for calls still in flight (a table that runs within a few steps' inserts of its capacity has to grow,
+    # allocator sets aside for calls still in flight (a table that runs within a few steps' inserts of its capacity has to grow,
     # which copies the whole arena); with few GPUs the shard is capped at what the benchmark's step count can touch
     capacity = args.capacity or min(int(1.15 * UNIVERSE / world) + 8_000_000, 72_000_000)
     state = arm.build(fields, dev, world, rank, capacity)

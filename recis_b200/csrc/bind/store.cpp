@@ -150,7 +150,7 @@ void EmbeddingStore::absorb_mirror() {
 }
 
 void EmbeddingStore::ensure_room(int64_t n_incoming) {
-  // rows_upper_ / index_upper_ = the newest counters that came back through the mirror + what was budgeted for the calls issued
+  // rows_upper_ / index_upper_ = the newest counters that came back through the mirror + what was set aside for the calls issued
   // since. Without history (first calls, CPU stores) a bound that crosses the capacity makes us read the true counters, which
   // synchronises; with history we act on the bounds as they are: growing a little early costs memory, never a stall.
   absorb_mirror();
@@ -216,11 +216,11 @@ torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::op
   auto rows_out = torch::empty({n}, i32);
   if (n == 0) return rows_out;
   // How many ids may be new? With a device-side count the buffer length n is only the window capacity, often many times
-  // the real count; budgeting room for all of it would force a (synchronising) look at the true counters, or a growth,
-  // on every call. The counts of earlier calls come back through the asynchronous mirror: budget for their recent maximum
+  // the real count; making room for all of it would force a (synchronising) look at the true counters, or a growth,
+  // on every call. The counts of earlier calls come back through the asynchronous mirror: make room for their recent maximum
   // plus a quarter. Should a call exceed that AND the arena be full, the kernel's bounds guard sets the status word
   // (no row is written out of range) and a later call reports it.
-  int64_t n_budget = n;
+  int64_t n_room = n;
   if (n_dev.has_value() && device_.is_cuda()) {
     absorb_mirror();
     if (seen_n_dev_ == 0) {
@@ -232,15 +232,15 @@ torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::op
           cudaStreamSynchronize(st) == cudaSuccess && now > 0)
         seen_n_dev_ = now;
     }
-    if (seen_n_dev_ > 0) n_budget = std::min<int64_t>(n, seen_n_dev_ + seen_n_dev_ / 4 + 65536);
+    if (seen_n_dev_ > 0) n_room = std::min<int64_t>(n, seen_n_dev_ + seen_n_dev_ / 4 + 65536);
   }
   // ... and of those ids only some are new: twice the recent maximum of rows actually added per call, once that is known
   if (device_.is_cuda()) {
     absorb_mirror();
-    if (est_new_ >= 0) n_budget = std::min<int64_t>(n_budget, 2 * est_new_ + 65536);
+    if (est_new_ >= 0) n_room = std::min<int64_t>(n_room, 2 * est_new_ + 65536);
   }
   ++calls_total_;
-  ensure_room(n_budget);
+  ensure_room(n_room);
   auto slot_scratch = torch::empty({n}, i32);
   auto new_rows = torch::empty({n}, i32);
   auto new_keys = torch::empty({n}, i32.dtype(torch::kInt64));
@@ -257,7 +257,7 @@ torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::op
                                new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr<float>(), (int)dim_, init_, ls,
                                sd, (int)admit_threshold);
   }
-  post_mirror(n_budget, nd);
+  post_mirror(n_room, nd);
   return rows_out;
 }
 

@@ -60,19 +60,19 @@ __global__ void comm_wait_kernel(const int64_t* flags, int channel, int world, i
   const int p = threadIdx.x;
   if (p < world) {
     const int64_t* f = flags + (int64_t)channel * world + p;
-    // spin_limit is a time budget in microseconds (measured with the global nanosecond timer), doubly bounded by an
+    // spin_limit is a time limit in microseconds (measured with the global nanosecond timer), doubly bounded by an
     // iteration count so that a stuck timer cannot turn this into an endless loop.
     bool ok = false;
     uint64_t t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-    const uint64_t budget_ns = (uint64_t)spin_limit * 1000ull;
+    const uint64_t limit_ns = (uint64_t)spin_limit * 1000ull;
     for (int64_t it = 0; it < (int64_t)1 << 34; ++it) {
       if (ld_acquire_sys(f) >= epoch) { ok = true; break; }
       __nanosleep(100);
       if ((it & 63) == 63) {
         uint64_t t1;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        if (t1 - t0 > budget_ns) break;
+        if (t1 - t0 > limit_ns) break;
       }
     }
     if (!ok) set_status(status, kStatusWaitTimeout);
@@ -93,13 +93,13 @@ __global__ void comm_wait_timed_kernel(const int64_t* flags, int channel, int wo
     uint64_t t0, t1;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     t1 = t0;
-    const uint64_t budget_ns = (uint64_t)spin_limit * 1000ull;
+    const uint64_t limit_ns = (uint64_t)spin_limit * 1000ull;
     for (int64_t it = 0; it < (int64_t)1 << 34; ++it) {
       if (ld_acquire_sys(f) >= epoch) { ok = true; break; }
       __nanosleep(100);
       if ((it & 63) == 63) {
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        if (t1 - t0 > budget_ns) break;
+        if (t1 - t0 > limit_ns) break;
       }
     }
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));

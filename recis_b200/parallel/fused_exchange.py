@@ -75,7 +75,7 @@ class FusedExchange:
         self.D = emb_opt.embedding_dim
         self.lanes = {}
         self.send_cap = int(os.environ.get("RECIS_EXCHANGE_CAPACITY", "0")) or int(getattr(emb_opt, "exchange_capacity", 0) or 0)
-        # time budget of every flag wait; a dead peer then surfaces as an error, never as a hang
+        # time limit of every flag wait; a dead peer then surfaces as an error, never as a hang
         self.wait_us = int(float(os.environ.get("RECIS_WAIT_TIMEOUT_S", "20")) * 1e6)
         self.status = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.immediate_reduce = False
