@@ -91,7 +91,7 @@ void write_gather_block(FileOutputBuffer* f, const Block& b, const std::string& 
       rb_gather_rows(b.tensor.data_ptr<float>(), b.rows.data_ptr<int32_t>() + s, m, nullptr, (int)D, stage_dev[slot].data_ptr<float>(), stream);
     } else {
       auto part = b.tensor.index_select(0, b.rows.narrow(0, s, m).to(torch::kInt64));
-      stage_dev[slot].view({-1}).narrow(0, 0, m).copy_(part.view({-1}), true);
+      stage_dev[slot].view({-1}).narrow(0, 0, m * D).copy_(part.reshape({-1}), true);
     }
     cuda_ok(cudaMemcpyAsync(stage_host[slot].data_ptr(), stage_dev[slot].data_ptr(), (size_t)m * D * esz, cudaMemcpyDeviceToHost, stream),
             "device-to-host copy of a checkpoint chunk");

@@ -95,6 +95,10 @@ class Saver:
                              hashmap_key_dtype="int64", hashmap_value=disk)
                 rank_json[disk] = entry
         jobs = [(N.join(self.path, f["name"]), json.dumps(f["header"], separators=(",", ":")), f["blocks"]) for f in files if f["blocks"]]
+        # the native writer gathers rows on streams of its own (one per writer thread): everything queued so far on this
+        # thread's streams - the last optimizer update, the row-index tensors built above - has to be complete before it starts
+        for dev in {impl.store.emb().device for impl in self.hashtables.values() if impl.store.emb().is_cuda}:
+            torch.cuda.synchronize(dev)
         native().st_write_files(jobs)
         meta = dict(files=[f["name"] for f in files if f["blocks"]], block_index=block_index, tensorkey=tensorkey, rank_json=rank_json)
         self._merge_meta(meta)
