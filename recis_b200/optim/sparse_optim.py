@@ -199,7 +199,7 @@ class SparseAdagrad(SparseOptimizer):
 
     def __init__(self, param_dict, lr=1e-2, eps=1e-10, weight_decay=0.0, initial_accumulator_value=0.0):
         self._eps, self._weight_decay = eps, weight_decay
-        type(self).slot_fill = float(initial_accumulator_value)
+        self.slot_fill = float(initial_accumulator_value)      # per instance: two optimizers may start their accumulators differently
         super().__init__(param_dict, lr=lr)
 
     def _kernel_args(self, lr):
