@@ -217,6 +217,9 @@ def run(args, arm):
     run_e2e(0, min(3, args.warmup))
     ms_e2e = run_e2e(args.warmup, args.steps)
 
+    # ---- C. exposed communication: CUDA-event spans around the exchange phases on the model's stream, a few extra steps
+    exposed = arm.exposed_comm_ms(state, host, dev, world, min(5, args.steps)) if hasattr(arm, "exposed_comm_ms") else None
+
     global_batch = spec.batch * world
     value = global_batch * args.steps / (ms / 1e3)
     value_e2e = global_batch * args.steps / (ms_e2e / 1e3)
@@ -241,6 +244,8 @@ def run(args, arm):
                     "d2h_bytes_per_step": 4, "last_loss": losses[-1] if losses else None},
             "gpu_launches": launches,
         }
+        if exposed is not None:
+            line["exposed_all_to_all_ms"] = exposed
         waits = arm.exposed_wait_ms(state) if hasattr(arm, "exposed_wait_ms") else {}
         if waits:
             line["exposed_wait_ms_per_wait"] = waits
@@ -310,6 +315,43 @@ class OursArm:
     def launches(self):
         import recis_b200
         return int(recis_b200.native().launch_count())
+
+    SPAN_LABELS = ("ids", "emb", "grad_push", "grad_wait", "dense_allreduce_wait", "total")
+
+    def exposed_comm_ms(self, st, host_batches, dev, world, steps):
+        """Milliseconds per step that the model's stream spends in the exchange phases (transfer kernels + waiting for peers)
+        and blocked on the dense all-reduce: CUDA events on the launching stream, max over ranks, measured on ``steps`` extra
+        steps after the timed regions. Every rank always runs the same steps and the same reduction, whatever happens to
+        the accounting itself."""
+        import torch
+        import torch.distributed as dist
+        if world == 1:
+            return {"total": 0.0, "note": "single GPU: no exchange"}
+        from recis_b200.parallel.spans import recorder
+        batches = [self.to_device(b, dev) for b in host_batches[-steps:]]
+        sync_all(world)
+        err = None
+        try:
+            recorder.start()
+        except Exception as e:          # accounting must never take the benchmark down
+            err = repr(e)
+        for b in batches:
+            self.step(st, b)
+        vals = [-1.0] * len(self.SPAN_LABELS)
+        try:
+            res = recorder.stop(steps=len(batches))
+            vals = [float(res.get(k, 0.0)) for k in self.SPAN_LABELS]
+        except Exception as e:
+            err = repr(e)
+            torch.cuda.synchronize()
+        t = torch.tensor(vals, dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sync_all(world)
+        out = dict(zip(self.SPAN_LABELS, [round(v, 4) for v in t.tolist()]))
+        out["how"] = "CUDA events around the exchange phases on the model's stream, max over ranks, %d extra steps" % len(batches)
+        if err:
+            out["error"] = err
+        return out
 
     def exposed_wait_ms(self, st):
         """RECIS_WAIT_STATS=1 only: mean time per flag wait until its last peer arrived, per channel, over the whole run."""

@@ -28,6 +28,7 @@ import torch
 import torch.distributed as dist
 
 from ... import native
+from ...parallel.spans import span_close, span_open
 from ...ragged.tensor import RaggedTensor
 from ..hashtable_hook import AdmitHook, FilterHook
 from ..initializers import ConstantInitializer, Initializer
@@ -156,6 +157,7 @@ class _LookupPoolFn(torch.autograd.Function):
 
         # ---- collective path (the reference's C1..C3)
         uniq, rev, counts, offs = C.dedup_partition(ids, W)
+        tok = span_open("ids")
         recv_counts = torch.empty_like(counts)
         dist.all_to_all_single(recv_counts, counts, group=pg)
         send_splits = counts.tolist()             # host read of split sizes (the fused path has none)
@@ -163,6 +165,7 @@ class _LookupPoolFn(torch.autograd.Function):
         n_u, n_in = sum(send_splits), sum(recv_splits)
         ids_in = torch.empty(n_in, dtype=torch.int64, device=ids.device)
         _a2a(ids_in, uniq[:n_u].contiguous(), recv_splits, send_splits, pg)
+        span_close(tok)
         # owner side: different requesters may ask for the same id
         o_uniq, o_rev, _c, o_offs = C.dedup_partition(ids_in, 1)
         o_n = o_offs[1:2]
@@ -170,7 +173,9 @@ class _LookupPoolFn(torch.autograd.Function):
         rows_in = o_rows[o_rev.long()] if n_in else o_rows[:0]
         emb_out = C.gather_rows(store.emb(), rows_in)
         emb_back = torch.empty(n_u, D, dtype=torch.float32, device=ids.device)
+        tok = span_open("emb")
         _a2a(emb_back, emb_out, [s for s in send_splits], [r for r in recv_splits], pg)
+        span_close(tok)
         out, gsrc, gscale = pool(emb_back, None, rev)
         if train:
             ctx.saved = dict(rev=rev, gsrc=gsrc, gscale=gscale, n_u=n_u, n_in=n_in, send_splits=send_splits,
@@ -201,7 +206,9 @@ class _LookupPoolFn(torch.autograd.Function):
         gu = C.grad_reduce(grad_out, s["gsrc"], s["gscale"], csr_u, csr_elem, start, D, None, False, 2, 0.0, 0.0, 0.0, 0.0,
                            1.0, 0.0, 1.0, None, None, None, max(s["n_u"], 1))
         g_in = torch.empty(s["n_in"], D, dtype=torch.float32, device=grad_out.device)
+        tok = span_open("grad_push")
         _a2a(g_in, gu[:s["n_u"]].contiguous(), s["recv_splits"], s["send_splits"], emb_mod.pg)
+        span_close(tok)
         o_rev = s["o_rev"].long()
         o_rows = s["o_rows"]
         g_own = torch.zeros(o_rows.numel(), D, dtype=torch.float32, device=grad_out.device)

@@ -57,8 +57,11 @@ class DenseGradReducer:
         if self.world == 1:
             return
         if not self.p2p:
+            from .spans import span_close, span_open
+            tok = span_open("dense_allreduce_wait")          # a collective on the model's stream: all of it is exposed
             dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.pg)
             self.flat.mul_(1.0 / self.world)
+            span_close(tok)
             return
         C = native()
         self.epoch += 1
@@ -74,7 +77,10 @@ class DenseGradReducer:
     def wait(self):
         """Make the main stream wait for the averaged gradients (call before the dense optimizer step)."""
         if self.world > 1 and self.p2p:
+            from .spans import span_close, span_open
+            tok = span_open("dense_allreduce_wait")
             torch.cuda.current_stream().wait_stream(self.stream)
+            span_close(tok)
 
     def all_reduce(self):
         self.all_reduce_async()

@@ -27,6 +27,7 @@ import torch
 import torch.distributed as dist
 
 from .. import native
+from .spans import span_close, span_open
 from .symmetric import SymmetricHeap
 
 CH_IDS, CH_EMB, CH_GRAD, N_CH = 0, 1, 2, 8
@@ -151,9 +152,11 @@ class FusedExchange:
         store = emb_mod.impl.store
         # more unique ids than the window holds sets the overflow bit in self.status (see check()); nothing is written out of bounds
         _uniq, rev, _counts, _offs = C.dedup_partition(ids, W, h["ids"].tensor, h["offsets"].tensor, self.status)
+        tok = span_open("ids")
         C.comm_signal(h["flags"].ptrs, CH_IDS, me, e)
         self._wait(h["flags"].tensor, CH_IDS, e)
         C.comm_pull_ids(h["ids"].ptrs, h["offsets"].ptrs, me, lane.ids_in, lane.prefix, lane.n_in, self.status)
+        span_close(tok)
         if self.multi_stream and self._store_event is not None:
             # lanes on separate streams share one table: its lookups (which allocate rows) run one after the other
             torch.cuda.current_stream(self.device).wait_event(self._store_event)
@@ -165,9 +168,11 @@ class FusedExchange:
             self._store_event = torch.cuda.Event()
             self._store_event.record(torch.cuda.current_stream(self.device))
         prefix = lane.prefix.clone()
+        tok = span_open("emb")
         C.comm_push_emb(store.emb(), rows_in, prefix, h["uemb"].ptrs, me, lane.in_cap)
         C.comm_signal(h["flags"].ptrs, CH_EMB, me, e)
         self._wait(h["flags"].tensor, CH_EMB, e)
+        span_close(tok)
         uemb = h["uemb"].tensor.view(lane.send_cap, D)
         if combiner == "tile":
             out, gsrc, gscale = C.tile_forward(uemb, None, rev, offsets, weights, tile_len, train)
@@ -187,9 +192,11 @@ class FusedExchange:
         lane = s["lane"]
         h, me, D = lane.heap, self.rank, self.D
         csr_u, csr_elem, start = C.build_csr(s["rev"])
+        tok = span_open("grad_push")
         C.comm_grad_reduce_push(grad_out, s["gsrc"], s["gscale"], csr_u, csr_elem, start, D, s["offsets"], s["prefix"],
                                 h["gin"].ptrs, lane.in_cap)
         C.comm_signal(h["flags"].ptrs, CH_GRAD, me, s["epoch"])
+        span_close(tok)
         rec = dict(rows_in=s["rows_in"], prefix=s["prefix"], epoch=s["epoch"], scale=worker_scale, exchange=self, lane=lane,
                    mean_by_id=emb_mod.option.grad_reduce_by == "id",
                    stream=torch.cuda.current_stream(self.device) if self.multi_stream else None)
@@ -221,7 +228,9 @@ class FusedExchange:
         C = native()
         lane = rec["lane"]
         h = lane.heap
+        tok = span_open("grad_wait")
         self._wait(h["flags"].tensor, CH_GRAD, rec["epoch"])
+        span_close(tok)
         head = self._head_for(impl.store)
         rows, grads = C.comm_owner_reduce(rec["rows_in"], head, rec["prefix"], h["gin"].tensor, self.world, self.D,
                                           rec["mean_by_id"], apply, kind, lr, b1, b2, eps, decay, alpha, rec["scale"] * grad_scale,

@@ -237,3 +237,38 @@ def test_crypto_and_singleton_helpers():
     class Once(metaclass=SingletonMeta):
         pass
     assert Once() is Once()
+
+
+def test_span_recorder_accounts_phases_per_step():
+    """The communication-span recorder with a fake event class: off by default (no events made), per-label sums per step."""
+    from recis_b200.parallel.spans import SpanRecorder
+
+    clock = [0.0]
+
+    class FakeEvent:
+        made = 0
+
+        def __init__(self, enable_timing=False):
+            FakeEvent.made += 1
+            self.t = None
+
+        def record(self):
+            clock[0] += 1.0
+            self.t = clock[0]
+
+        def elapsed_time(self, other):
+            return other.t - self.t
+
+    rec = SpanRecorder(event_cls=FakeEvent)
+    assert rec.open("ids") is None and FakeEvent.made == 0          # switched off: nothing is recorded
+    rec.close(None)
+    rec.start()
+    for _ in range(4):
+        for label in ("ids", "emb", "ids"):
+            tok = rec.open(label)
+            clock[0] += 2.5                                          # "device work" between the two events
+            rec.close(tok)
+    out = rec.stop(steps=4, synchronize=lambda: None)
+    assert not rec.enabled
+    assert abs(out["ids"] - 2 * 3.5) < 1e-9 and abs(out["emb"] - 3.5) < 1e-9 and abs(out["total"] - 10.5) < 1e-9
+    assert rec.stop(steps=1, synchronize=lambda: None) == {"total": 0}
