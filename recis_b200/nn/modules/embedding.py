@@ -117,7 +117,7 @@ class _LookupPoolFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, holder, emb_mod: "DynamicEmbedding", ids, offsets, weights, combiner, tile_len, perm, training, admit_hook,
-                lane="default"):
+                lane="default", prepared=None):
         C = native()
         impl = emb_mod.impl
         store = impl.store
@@ -150,21 +150,16 @@ class _LookupPoolFn(torch.autograd.Function):
 
         if emb_mod.fused is not None:
             out, saved = emb_mod.fused.forward(emb_mod, lane, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train,
-                                               readonly, threshold, step)
+                                               readonly, threshold, step, prepared["fused"] if prepared is not None else None)
             ctx.saved = saved
             ctx.path = "fused"
             return out
 
         # ---- collective path (the reference's C1..C3)
-        uniq, rev, counts, offs = C.dedup_partition(ids, W)
+        p = prepared if prepared is not None else emb_mod._begin_collective(ids)
+        rev, send_splits, recv_splits, n_u, n_in, ids_in = p["rev"], p["send_splits"], p["recv_splits"], p["n_u"], p["n_in"], p["ids_in"]
         tok = span_open("ids")
-        recv_counts = torch.empty_like(counts)
-        dist.all_to_all_single(recv_counts, counts, group=pg)
-        send_splits = counts.tolist()             # host read of split sizes (the fused path has none)
-        recv_splits = recv_counts.tolist()
-        n_u, n_in = sum(send_splits), sum(recv_splits)
-        ids_in = torch.empty(n_in, dtype=torch.int64, device=ids.device)
-        _a2a(ids_in, uniq[:n_u].contiguous(), recv_splits, send_splits, pg)
+        p["work"].wait()                          # the id all-to-all was issued asynchronously (for all groups before any wait)
         span_close(tok)
         # owner side: different requesters may ask for the same id
         o_uniq, o_rev, _c, o_offs = C.dedup_partition(ids_in, 1)
@@ -186,7 +181,7 @@ class _LookupPoolFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         if not ctx.train:
-            return (None,) * 11
+            return (None,) * 12
         C = native()
         emb_mod = ctx.emb_mod
         impl = emb_mod.impl
@@ -197,10 +192,10 @@ class _LookupPoolFn(torch.autograd.Function):
         if ctx.path == "local":
             impl.stage_fused(dict(grad_out=grad_out, gsrc=s["gsrc"], gscale=s["gscale"], rev=s["rev"], rows=s["rows"],
                                   scale=worker_scale))
-            return (None,) * 11
+            return (None,) * 12
         if ctx.path == "fused":
             emb_mod.fused.backward(emb_mod, s, grad_out, worker_scale)
-            return (None,) * 11
+            return (None,) * 12
         # ---- collective path (the reference's C4 + owner-side duplicate reduction)
         csr_u, csr_elem, start = C.build_csr(s["rev"])
         gu = C.grad_reduce(grad_out, s["gsrc"], s["gscale"], csr_u, csr_elem, start, D, None, False, 2, 0.0, 0.0, 0.0, 0.0,
@@ -221,7 +216,7 @@ class _LookupPoolFn(torch.autograd.Function):
             else:
                 g_own = g_own * worker_scale
         impl.accept_grad(o_rows, g_own)
-        return (None,) * 11
+        return (None,) * 12
 
 
 class DynamicEmbedding(torch.nn.Module):
@@ -265,16 +260,55 @@ class DynamicEmbedding(torch.nn.Module):
     def impl(self):
         return self.table.impl
 
+    def _begin_collective(self, ids: torch.Tensor) -> dict:
+        """Id phase of the collective path: dedup + bucket by owner, exchange the counts (blocking, with the host read of the
+        split sizes), then start the id all-to-all WITHOUT waiting for it (the reference's C1 and C2,
+        ``recis/nn/modules/embedding.py:498-542``)."""
+        C = native()
+        W, pg = self.world_size, self.pg
+        tok = span_open("ids")
+        uniq, rev, counts, _offs = C.dedup_partition(ids, W)
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=pg)
+        send_splits = counts.tolist()             # host read of split sizes (the fused path has none)
+        recv_splits = recv_counts.tolist()
+        n_u, n_in = sum(send_splits), sum(recv_splits)
+        ids_in = torch.empty(n_in, dtype=torch.int64, device=ids.device)
+        ids_out = uniq[:n_u].contiguous()
+        work = dist.all_to_all_single(ids_in, ids_out, recv_splits, send_splits, group=pg, async_op=True)
+        span_close(tok)
+        return dict(rev=rev, send_splits=send_splits, recv_splits=recv_splits, n_u=n_u, n_in=n_in, ids_in=ids_in, ids_out=ids_out,
+                    work=work)
+
+    def _normalise_ids(self, ids: torch.Tensor) -> torch.Tensor:
+        return ids.detach().reshape(-1).to(self.impl.device).contiguous()
+
+    def prepare_lookup(self, ids: torch.Tensor, lane: str = "default"):
+        """Start the id phase of a sharded lookup and return a token for ``lookup_pool(..., prepared=token)``, or None when
+        there is nothing to start early (one rank; the fused exchange unless its staging is switched on). A model with several
+        table groups calls this for every group before the first ``lookup_pool``, so that all id exchanges are in flight
+        before anything waits (``recis/nn/modules/embedding_engine.py:739-801`` does the same with asynchronous all-to-alls)."""
+        if self.world_size == 1:
+            return None
+        ids = self._normalise_ids(ids)
+        if self.fused is not None:
+            if not self.fused.stage_enabled:
+                return None
+            return dict(ids=ids, fused=self.fused.prepare(self, lane, ids))
+        p = self._begin_collective(ids)
+        p["ids"] = ids
+        return p
+
     def lookup_pool(self, ids: torch.Tensor, offsets: torch.Tensor, weights: Optional[torch.Tensor], combiner: str,
-                    tile_len: int = 0, perm=None, admit_hook=None, lane: str = "default") -> torch.Tensor:
+                    tile_len: int = 0, perm=None, admit_hook=None, lane: str = "default", prepared=None) -> torch.Tensor:
         """Flat ids + int32 segment offsets (+ per-id weights) -> pooled rows ``[segments, D]`` (tile: ``[segments, T*D]``)."""
         dev = self.impl.device
-        ids = ids.detach().reshape(-1).to(dev).contiguous()
+        ids = prepared["ids"] if prepared is not None else self._normalise_ids(ids)
         offsets = offsets.to(device=dev, dtype=torch.int32).contiguous()
         if weights is not None:
             weights = weights.detach().reshape(-1).to(device=dev, dtype=torch.float32).contiguous()
         out = _LookupPoolFn.apply(self._holder, self, ids, offsets, weights, combiner, int(tile_len), perm, self.training,
-                                  admit_hook if admit_hook is not None else self._emb_opt.admit_hook, lane)
+                                  admit_hook if admit_hook is not None else self._emb_opt.admit_hook, lane, prepared)
         # storage and pooling are fp32; a half-precision table dtype is the dtype the model sees
         return out if self._emb_opt.dtype == torch.float32 else out.to(self._emb_opt.dtype)
 

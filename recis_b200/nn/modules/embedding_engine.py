@@ -232,6 +232,10 @@ class EmbeddingEngine(nn.Module):
                 name=fea_name, ids=ids, offsets=offsets, weight=weight, n_seg=n_seg, shape=shape, child=group.fea_child[fea_name],
                 opt=opt))
         self.packed = {}
+        # pass 1: coalesce every (table, runtime group) and, when there are several, start the id phase of all of them before
+        # anything waits (the reference issues all its id all-to-alls up front, embedding_engine.py:739-801)
+        n_groups = sum(len(r) for r in grouped.values())
+        plan = []
         for ht_name, runtimes in grouped.items():
             ht: DynamicEmbedding = self._ht[ht_name]
             dev = ht.impl.device
@@ -242,29 +246,36 @@ class EmbeddingEngine(nn.Module):
                 perm = None
                 if self._interleave and opt.combiner != "tile" and len(set(segs)) == 1 and len(feats) > 1:
                     perm = (segs[0], len(feats))
-                if not self._use_lanes(ht, feats, perm):
+                lanes = self._use_lanes(ht, feats, perm)
+                ids = offsets = weights = prepared = None
+                if not lanes:
                     ids, offsets, weights = self._coalesce(feats, dev)
-                ht.option.mean_by_weight = opt.mean_by_weight
-                if self._use_lanes(ht, feats, perm):
-                    pooled = self._lookup_in_lanes(ht, feats, opt, run_key, dev)          # [B, F, D] assembled from the lanes
-                    ids = offsets = weights = None
-                else:
-                    pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, tile_len, perm, opt.admit_hook, lane=run_key)
-                if not opt.trainable:
-                    pooled = pooled.detach()
-                D = opt.embedding_dim
-                if perm is not None:
-                    cube = pooled.view(segs[0], len(feats), D)
-                    self.packed[(ht_name, run_key)] = (cube, [f["name"] for f in feats])
-                    for j, f in enumerate(feats):
-                        outs[f["name"]] = cube[:, j, :].reshape(f["shape"]) if len(f["shape"]) != 2 else cube[:, j, :]
-                else:
-                    rows_per = segs
-                    pooled = pooled.view(-1, (tile_len or 1) * D)
-                    start = 0
-                    for f, s in zip(feats, rows_per):
-                        outs[f["name"]] = pooled[start:start + s].reshape(f["shape"])
-                        start += s
+                    if n_groups > 1:
+                        prepared = ht.prepare_lookup(ids, lane=run_key)
+                plan.append((ht_name, ht, dev, run_key, feats, opt, tile_len, segs, perm, lanes, ids, offsets, weights, prepared))
+        # pass 2: finish the lookups in the same order
+        for ht_name, ht, dev, run_key, feats, opt, tile_len, segs, perm, lanes, ids, offsets, weights, prepared in plan:
+            ht.option.mean_by_weight = opt.mean_by_weight
+            if lanes:
+                pooled = self._lookup_in_lanes(ht, feats, opt, run_key, dev)          # [B, F, D] assembled from the lanes
+            else:
+                pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, tile_len, perm, opt.admit_hook, lane=run_key,
+                                        prepared=prepared)
+            if not opt.trainable:
+                pooled = pooled.detach()
+            D = opt.embedding_dim
+            if perm is not None:
+                cube = pooled.view(segs[0], len(feats), D)
+                self.packed[(ht_name, run_key)] = (cube, [f["name"] for f in feats])
+                for j, f in enumerate(feats):
+                    outs[f["name"]] = cube[:, j, :].reshape(f["shape"]) if len(f["shape"]) != 2 else cube[:, j, :]
+            else:
+                rows_per = segs
+                pooled = pooled.view(-1, (tile_len or 1) * D)
+                start = 0
+                for f, s in zip(feats, rows_per):
+                    outs[f["name"]] = pooled[start:start + s].reshape(f["shape"])
+                    start += s
         for k, v in direct.items():
             if isinstance(v, RaggedTensor):
                 outs[k] = v.to_dense()

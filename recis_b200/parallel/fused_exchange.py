@@ -87,6 +87,8 @@ class FusedExchange:
         self.wait_stats = (torch.zeros(N_CH * world + N_CH, dtype=torch.int64, device=self.device)
                            if os.environ.get("RECIS_WAIT_STATS") == "1" else None)
         self._head = None
+        # RECIS_STAGE_EXCHANGE=1: the engine may issue the id phase of all of a model's groups before the first wait (prepare())
+        self.stage_enabled = os.environ.get("RECIS_STAGE_EXCHANGE") == "1"
 
     def _wait(self, flags, channel, epoch):
         C = native()
@@ -130,30 +132,43 @@ class FusedExchange:
 
     # ------------------------------------------------------------------ forward
     def forward(self, emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold,
-                step):
+                step, prepared=None):
         with torch.profiler.record_function("recis_b200/exchange_forward"):
             return self._forward(emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly,
-                                 threshold, step)
+                                 threshold, step, prepared)
 
-    def _forward(self, emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold,
-                 step):
+    def prepare(self, emb_mod, lane_key, ids):
+        """Requester half of the id phase only (dedup + bucket into the window, signal IDS). A model with several (table, runtime
+        group) pairs calls this for all of them before the first ``forward``: every rank's ids are then on offer before anybody
+        waits, as the reference issues all of its id all-to-alls before the first wait
+        (``recis/nn/modules/embedding_engine.py:739-801``). Pass the result to ``forward(..., prepared=...)``."""
+        with torch.profiler.record_function("recis_b200/exchange_prepare"):
+            return self._begin(emb_mod, lane_key, ids)
+
+    def _begin(self, emb_mod, lane_key, ids):
         C = native()
-        n = ids.numel()
         lane = self.lanes.get(lane_key)
         if lane is None:                       # collective: every rank meets here at its first forward of this lane
-            lane = self.lanes[lane_key] = _Lane(self, n)
+            lane = self.lanes[lane_key] = _Lane(self, ids.numel())
         if lane.pending_grad_epoch and not self.immediate_reduce:
             # the previous backward of this lane is still staged (gradient accumulation without set_grad_accum_steps):
             # consume it now, before this step's backward rewrites the gradient window
             self._flush_pending(emb_mod.impl, lane)
-        h, W, me, D = lane.heap, self.world, self.rank, self.D
+        h = lane.heap
         lane.epoch += 1
         e = lane.epoch
-        store = emb_mod.impl.store
         # more unique ids than the window holds sets the overflow bit in self.status (see check()); nothing is written out of bounds
-        _uniq, rev, _counts, _offs = C.dedup_partition(ids, W, h["ids"].tensor, h["offsets"].tensor, self.status)
+        _uniq, rev, _counts, _offs = C.dedup_partition(ids, self.world, h["ids"].tensor, h["offsets"].tensor, self.status)
+        C.comm_signal(h["flags"].ptrs, CH_IDS, self.rank, e)
+        return lane, e, rev
+
+    def _forward(self, emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold,
+                 step, prepared=None):
+        C = native()
+        lane, e, rev = prepared if prepared is not None else self._begin(emb_mod, lane_key, ids)
+        h, me, D = lane.heap, self.rank, self.D
+        store = emb_mod.impl.store
         tok = span_open("ids")
-        C.comm_signal(h["flags"].ptrs, CH_IDS, me, e)
         self._wait(h["flags"].tensor, CH_IDS, e)
         C.comm_pull_ids(h["ids"].ptrs, h["offsets"].ptrs, me, lane.ids_in, lane.prefix, lane.n_in, self.status)
         span_close(tok)

@@ -69,7 +69,7 @@ print('ok')
     assert "ok" in _child(code, {"RECIS_ATTENTION": "tcgen05"})
 
 
-@pytest.mark.parametrize("env", [{"RECIS_EXCHANGE_LANES": "2"}, {"RECIS_WAIT_STATS": "1"}])
+@pytest.mark.parametrize("env", [{"RECIS_EXCHANGE_LANES": "2"}, {"RECIS_WAIT_STATS": "1"}, {"RECIS_STAGE_EXCHANGE": "1"}])
 def test_fused_exchange_variants_match_single_process(env):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
