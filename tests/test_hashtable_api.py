@@ -156,3 +156,26 @@ def test_half_precision_table_dtype_is_the_output_dtype():
     assert torch.allclose(eng({"a": torch.arange(3)})["a"].float(), torch.full((3, 4), -0.25))
     with pytest.raises(NotImplementedError):
         EmbeddingOption(embedding_dim=4, dtype=torch.int8, device="cpu")
+
+
+def test_reference_submodule_import_paths_exist():
+    """Module paths of the reference that user code imports from (package name aside)."""
+    import importlib
+    for mod, names in {
+        "recis_b200.io.orc_dataset": ["OrcDataset", "get_dir_size"], "recis_b200.io.dataset_base": ["DatasetBase"],
+        "recis_b200.io.state_dataset": ["StateDataset"], "recis_b200.io.map_dataset": ["MapDataset"],
+        "recis_b200.io.filter_dataset": ["FilterDataset"], "recis_b200.io.wrap_end_dataset": ["WrapEndDataset"],
+        "recis_b200.optim.sparse_adam": ["SparseAdam"], "recis_b200.optim.sparse_adamw": ["SparseAdamW"],
+        "recis_b200.optim.sparse_adamw_tf": ["SparseAdamWTF"], "recis_b200.optim.adamw_tf": ["AdamWTF"],
+        "recis_b200.info": ["is_internal_enabled", "get_build_info"],
+        "recis_b200.nn.modules.embedding": ["DynamicEmbedding", "EmbeddingOption"],
+        "recis_b200.nn.modules.embedding_engine": ["EmbeddingEngine"], "recis_b200.nn.modules.hashtable": ["HashTable", "gen_slice"],
+        "recis_b200.nn.hashtable_hook": ["AdmitHook", "FilterHook"], "recis_b200.ragged.tensor": ["RaggedTensor"],
+        "recis_b200.framework.trainer": ["Trainer", "TrainingArguments"], "recis_b200.framework.checkpoint_manager": ["CheckpointManager"],
+        "recis_b200.metrics.auroc": ["AUROC"], "recis_b200.metrics.gauc": ["Gauc"],
+        "recis_b200.serialize.checkpoint_reader": ["CheckpointReader"], "recis_b200.utils.logger": ["Logger"],
+        "recis_b200.utils.data_utils": ["copy_data_to_device"],
+    }.items():
+        m = importlib.import_module(mod)
+        for n in names:
+            assert hasattr(m, n), (mod, n)
