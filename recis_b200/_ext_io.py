@@ -26,9 +26,11 @@ def _arrow():
     inc = pa.get_include()
     libdir = pa.get_library_dirs()[0]
     libs = sorted(f for f in os.listdir(libdir) if f.startswith("libarrow.so"))
-    if not libs or not os.path.exists(os.path.join(inc, "arrow", "adapters", "orc", "adapter.h")):
-        raise RuntimeError("pyarrow ships no Arrow C++ headers / library here")
-    return inc, libdir, libs[-1]
+    pq = sorted(f for f in os.listdir(libdir) if f.startswith("libparquet.so"))
+    if not libs or not pq or not os.path.exists(os.path.join(inc, "arrow", "adapters", "orc", "adapter.h")) or not os.path.exists(
+            os.path.join(inc, "parquet", "arrow", "reader.h")):
+        raise RuntimeError("pyarrow ships no Arrow C++ headers / libraries here")
+    return inc, libdir, [libs[-1], pq[-1]]
 
 
 def _hash():
@@ -56,11 +58,11 @@ def is_built() -> bool:
 def build(verbose: bool = False):
     import torch  # noqa: F401
     from torch.utils import cpp_extension
-    inc, libdir, lib = _arrow()
+    inc, libdir, libs = _arrow()
     os.makedirs(_BUILD, exist_ok=True)
     cpp_extension.load(
         name=_NAME, sources=[_SRC], extra_cflags=["-O2", "-std=c++20", "-Wno-sign-compare", "-Wno-deprecated-declarations"],
-        extra_ldflags=[f"-L{libdir}", f"-l:{lib}", f"-Wl,-rpath,{libdir}"],
+        extra_ldflags=[f"-L{libdir}"] + [f"-l:{lib}" for lib in libs] + [f"-Wl,-rpath,{libdir}"],
         extra_include_paths=[inc, "/usr/local/cuda/include"], build_directory=_BUILD, with_cuda=False, is_python_module=True, verbose=verbose)
     with open(os.path.join(_BUILD, "source.sha256"), "w") as fh:
         fh.write(_hash())

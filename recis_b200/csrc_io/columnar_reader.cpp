@@ -1,4 +1,4 @@
-// Native columnar reader: ORC files -> training batches, with reader threads, a packer and a prefetch queue.
+// Native columnar reader: ORC and Parquet files -> training batches, with reader threads, a packer and a prefetch queue.
 //
 // Pipeline (all C++, the Python caller only pops finished batches):
 //   reader threads   decode whole files (Arrow's ORC adapter), up to `threads` files ahead of the packer, in file order;
@@ -19,6 +19,7 @@
 #include <torch/extension.h>
 
 #include <arrow/adapters/orc/adapter.h>
+#include <parquet/arrow/reader.h>
 #include <arrow/api.h>
 #include <arrow/io/file.h>
 
@@ -113,8 +114,33 @@ class ColumnarReader {
       TablePtr table;
       std::string err;
       auto file = arrow::io::ReadableFile::Open(paths_[idx]);
+      const std::string& path = paths_[idx];
+      const bool is_parquet = path.size() >= 8 && path.compare(path.size() - 8, 8, ".parquet") == 0;
       if (!file.ok()) err = file.status().ToString();
-      else {
+      else if (is_parquet) {
+        // Parquet: the declared columns are selected by name from the file's schema (top-level fields)
+        auto reader = parquet::arrow::OpenFile(*file, arrow::default_memory_pool());
+        if (!reader.ok()) err = reader.status().ToString();
+        else {
+          std::shared_ptr<arrow::Schema> schema;
+          auto st = (*reader)->GetSchema(&schema);
+          std::vector<int> cols;
+          if (st.ok()) {
+            for (auto& n : names_) {
+              const int i = schema->GetFieldIndex(n);
+              if (i < 0) { st = arrow::Status::KeyError("no column named ", n); break; }
+              cols.push_back(i);
+            }
+          }
+          std::shared_ptr<arrow::Table> t;
+          if (st.ok()) st = (*reader)->ReadTable(cols, &t);
+          if (!st.ok()) err = st.ToString();
+          else {
+            auto c = t->CombineChunks(arrow::default_memory_pool());
+            if (!c.ok()) err = c.status().ToString(); else table = *c;
+          }
+        }
+      } else {
         auto reader = arrow::adapters::orc::ORCFileReader::Open(*file, arrow::default_memory_pool());
         if (!reader.ok()) err = reader.status().ToString();
         else {

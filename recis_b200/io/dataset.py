@@ -197,9 +197,10 @@ class OrcDataset(DatasetBase):
             yield batch
 
     def _native(self, paths):
-        """The C++ reader (reader threads + packer + prefetch queue, ``csrc_io/columnar_reader.cpp``) when it applies: ORC files
-        only, no shuffling; it is built against the Arrow C++ library inside the pyarrow wheel and may be unavailable."""
-        if not self.native_reader or self.shuffle or not paths or not all(p.endswith(".orc") for p in paths):
+        """The C++ reader (reader threads + packer + prefetch queue, ``csrc_io/columnar_reader.cpp``) when it applies: ORC
+        and Parquet files, no shuffling; it is built against the Arrow C++ libraries inside the pyarrow wheel and may be
+        unavailable."""
+        if not self.native_reader or self.shuffle or not paths or not all(p.endswith((".orc", ".parquet")) for p in paths):
             return None
         from .._ext_io import load
         mod = load()

@@ -12,8 +12,9 @@ pa = pytest.importorskip("pyarrow")
 pytestmark = pytest.mark.skipif(load() is None, reason="Arrow C++ development files are not available")
 
 
-def _write(tmp_path, shards=3, rows=(70, 33, 50)):
+def _write(tmp_path, shards=3, rows=(70, 33, 50), fmt="orc"):
     import pyarrow.orc as orc
+    import pyarrow.parquet as pq
     rng = np.random.default_rng(0)
     paths = []
     for s in range(shards):
@@ -25,8 +26,11 @@ def _write(tmp_path, shards=3, rows=(70, 33, 50)):
             "uid": rng.integers(-(1 << 40), 1 << 40, n), "seq": pa.array(seq, type=pa.list_(pa.int64())),
             "city": pa.array([f"city_{int(x)}" for x in rng.integers(0, 20, n)]), "words": pa.array(words, type=pa.list_(pa.string())),
         })
-        p = str(tmp_path / f"part-{s:05d}.orc")
-        orc.write_table(t, p)
+        p = str(tmp_path / f"part-{s:05d}.{fmt}")
+        if fmt == "orc":
+            orc.write_table(t, p)
+        else:
+            pq.write_table(t, p, row_group_size=16)          # several row groups per file
         paths.append(p)
     return paths
 
@@ -117,3 +121,19 @@ def test_repeat_and_worker_sharding(tmp_path):
         ds.varlen_feature("uid")
         per_worker.append(sum(b["uid"].values().numel() for b in ds))
     assert sorted(per_worker) == sorted([70 + 50, 33])
+
+
+def test_native_reader_reads_parquet_like_the_python_reader(tmp_path):
+    """Parquet files (several row groups each) go through the same native packer; a missing column is reported by name."""
+    paths = _write(tmp_path, fmt="parquet")
+    ds = _dataset(paths, True)
+    assert ds._native(ds._my_paths()) is not None                   # the native reader takes Parquet
+    nat, ref = list(ds), list(_dataset(paths, False))
+    assert len(nat) == len(ref) == 7
+    for a, b in zip(nat, ref):
+        _same(a, b)
+    bad = OrcDataset(batch_size=8, native_reader=True)
+    bad.add_paths(paths[:1])
+    bad.varlen_feature("no_such_column")
+    with pytest.raises(RuntimeError, match="no_such_column"):
+        list(bad)
