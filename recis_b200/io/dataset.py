@@ -139,7 +139,17 @@ class OrcDataset(DatasetBase):
 
     def _my_paths(self):
         mine = [p for i, p in enumerate(sorted(self._paths)) if i % self.worker_num == self.worker_idx]
-        return mine * self.repeat
+        if not self.shuffle:
+            return mine * self.repeat
+        # file-level shuffle, as the reference's file sharding does (``recis/io/orc_dataset.py:285-293``): a new order for every
+        # pass, a pure function of (seed, pass) so that a restored iterator state points at the same file again
+        import random
+        out = []
+        for r in range(self.repeat):
+            part = list(mine)
+            random.Random(self.seed * 1000003 + r).shuffle(part)
+            out += part
+        return out
 
     @staticmethod
     def _read_table(path):
@@ -198,9 +208,9 @@ class OrcDataset(DatasetBase):
 
     def _native(self, paths):
         """The C++ reader (reader threads + packer + prefetch queue, ``csrc_io/columnar_reader.cpp``) when it applies: ORC
-        and Parquet files, no shuffling; it is built against the Arrow C++ libraries inside the pyarrow wheel and may be
+        and Parquet files; it is built against the Arrow C++ libraries inside the pyarrow wheel and may be
         unavailable."""
-        if not self.native_reader or self.shuffle or not paths or not all(p.endswith((".orc", ".parquet")) for p in paths):
+        if not self.native_reader or not paths or not all(p.endswith((".orc", ".parquet")) for p in paths):
             return None
         from .._ext_io import load
         mod = load()

@@ -137,3 +137,18 @@ def test_native_reader_reads_parquet_like_the_python_reader(tmp_path):
     bad.varlen_feature("no_such_column")
     with pytest.raises(RuntimeError, match="no_such_column"):
         list(bad)
+
+
+def test_shuffle_is_a_seeded_file_order_shared_by_both_readers(tmp_path):
+    paths = _write(tmp_path, shards=3, rows=(40, 41, 42))
+    sizes = lambda ds: [b["label"].shape[0] for b in ds]
+    plain = sizes(_dataset(paths, True))
+    orders = {seed: sizes(_dataset(paths, True, shuffle=True, seed=seed)) for seed in range(6)}
+    assert all(sorted(o) == sorted(plain) for o in orders.values())          # same batches, some other file order
+    assert any(o != plain for o in orders.values())
+    for seed, o in orders.items():
+        assert o == sizes(_dataset(paths, True, shuffle=True, seed=seed))    # deterministic
+        assert o == sizes(_dataset(paths, False, shuffle=True, seed=seed))   # both readers agree
+    # two passes are shuffled independently but cover every file twice
+    two = sizes(_dataset(paths, True, shuffle=True, seed=1, repeat=2))
+    assert sorted(two) == sorted(plain * 2)
