@@ -121,6 +121,11 @@ class OrcDataset(DatasetBase):
         self.repeat = max(int(repeat), 1)           # passes over this worker's files (the role of column-io's RepeatDataset)
         self.drop_remainder, self.shuffle, self.transform_fn, self.dtype, self.device, self.pin = drop_remainder, shuffle, transform_fn, dtype, device, pin
         self.prefetch, self.seed = prefetch, seed
+        # where batches are placed, as in the reference (``recis/io/dataset_base.py:207-212``): host memory, pinned host memory
+        # or the current CUDA device (pinned staging + asynchronous copy)
+        assert str(device) in ("cpu", "pin", "cuda"), f"Only support io result placed in `cpu|cuda|pin` but got {device}"
+        self.ragged_format = ragged_format
+        self.pin = self.pin or (str(device) in ("pin", "cuda") and torch.cuda.is_available())
         self._paths: List[str] = []
         self._varlen, self._fixed = {}, {}
         self._file_idx, self._row_in_file = 0, 0
@@ -185,6 +190,19 @@ class OrcDataset(DatasetBase):
             values = native().fused_mod([values], [int(conf["hash_bucket"])])[0]
         return RaggedTensor(values, [torch.from_numpy(offsets.astype(np.int32))], dense_shape=(n, -1))
 
+    def _place(self, batch):
+        """Output format and placement of one batch: ``ragged_format=False`` turns variable-length columns into sparse COO
+        tensors (``recis/io/dataset_base.py:82-90``); ``device`` pins or moves the tensors. Runs before ``transform_fn``."""
+        if not self.ragged_format:
+            batch = {k: (v.to_sparse() if isinstance(v, RaggedTensor) else v) for k, v in batch.items()}
+        if self.pin and torch.cuda.is_available():
+            from ..utils.data_utils import pin_data
+            batch = {k: (v if (isinstance(v, torch.Tensor) and (v.is_sparse or v.is_pinned())) else pin_data(v)) for k, v in batch.items()}
+        if str(self.device) == "cuda" and torch.cuda.is_available():
+            from ..utils.data_utils import copy_data_to_device
+            batch = copy_data_to_device(batch, "cuda", non_blocking=True)
+        return batch
+
     def _batches_of(self, table, start_row):
         import numpy as np
         n = table.num_rows
@@ -201,6 +219,7 @@ class OrcDataset(DatasetBase):
                 arr = np.asarray(col.fill_null(default).to_pylist() if col.null_count else col.to_pylist())
                 t = torch.as_tensor(arr)
                 batch[name] = (t.to(self.dtype) if t.is_floating_point() else t).reshape(e - b, -1)
+            batch = self._place(batch)
             if self.transform_fn is not None:
                 batch = self.transform_fn(batch)
             self._row_in_file = e
@@ -243,6 +262,7 @@ class OrcDataset(DatasetBase):
                         batch[name] = RaggedTensor(c[1], [c[2], c[3]])
                     else:
                         batch[name] = c[1].to(self.dtype) if c[1].is_floating_point() else c[1]
+                batch = self._place(batch)
                 if self.transform_fn is not None:
                     batch = self.transform_fn(batch)
                 self._file_idx, self._row_in_file = reader.state()

@@ -152,3 +152,22 @@ def test_shuffle_is_a_seeded_file_order_shared_by_both_readers(tmp_path):
     # two passes are shuffled independently but cover every file twice
     two = sizes(_dataset(paths, True, shuffle=True, seed=1, repeat=2))
     assert sorted(two) == sorted(plain * 2)
+
+
+@pytest.mark.parametrize("native_reader", [True, False])
+def test_ragged_format_false_gives_sparse_tensors(tmp_path, native_reader):
+    paths = _write(tmp_path, shards=1, rows=(20,))
+
+    def make(ragged_format):
+        ds = OrcDataset(batch_size=20, native_reader=native_reader, ragged_format=ragged_format)
+        ds.add_paths(paths)
+        ds.varlen_feature("seq")
+        ds.fixedlen_feature("label")
+        return next(iter(ds))
+
+    ragged, sparse = make(True), make(False)
+    assert sparse["seq"].is_sparse and not sparse["label"].is_sparse
+    dense = ragged["seq"].to_dense()
+    assert torch.equal(sparse["seq"].to_dense()[:, : dense.shape[1]], dense)
+    with pytest.raises(AssertionError):
+        OrcDataset(batch_size=4, device="tpu")
