@@ -25,6 +25,9 @@ class Loader:
         self.index = BundleIndex(checkpoint_path)
         self.hashtables, self.tensors, self.strict = hashtables, tensors, strict
         self.chunk = max(int(os.environ.get("RECIS_BLOCK_READ_SIZE", 1 << 20)), 1)
+        # slot blocks of a chunk are read by up to ``parallel`` threads (the native file reads release the GIL), the role of the
+        # reference loader's thread pool (``csrc/serialize/load_internal.cc:195-273``)
+        self.parallel = max(int(parallel), 1)
 
     def load(self):
         seen = set()
@@ -45,6 +48,11 @@ class Loader:
                 t.copy_(src.to(t.dtype))
 
     def _load_table(self, impl):
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=self.parallel) as pool:
+            self._load_table_with(impl, pool)
+
+    def _load_table_with(self, impl, pool):
         C = native()
         dev = impl.device
         sl = impl.slice
@@ -73,14 +81,17 @@ class Loader:
                         continue
                     kept = ids[keep]
                     enc = ChildrenInfo.encode(kept, ci) if coalesced else kept
-                    rows = impl.store.lookup_or_insert(enc.to(dev).contiguous(), None, None, 1)
-                    for slot in slot_names:
+                    pending = {}
+                    for slot in slot_names:                          # all slot reads of the chunk are in flight together
                         sdisk = disk.replace(f".{N.ID_SLOT}/", f".{slot}/")
                         if sdisk not in self.index.block_file:
                             if self.strict and slot == N.EMB_SLOT:
                                 raise KeyError(f"{sdisk} missing from the checkpoint")
                             continue
-                        data = self.index.read(sdisk, r0, r1)[keep]
+                        pending[slot] = pool.submit(self.index.read, sdisk, r0, r1)
+                    rows = impl.store.lookup_or_insert(enc.to(dev).contiguous(), None, None, 1)
+                    for slot, fut in pending.items():
+                        data = fut.result()[keep]
                         if slot == N.FILTER_SLOT:
                             impl.store.last_seen().index_copy_(0, rows.long(), data.view(-1).to(dev))
                         else:
