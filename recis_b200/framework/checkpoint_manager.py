@@ -35,6 +35,7 @@ class Saver:
         self._sparse_optim = sparse_optim
         self._concurrency = concurrency
         self._io_state = {}
+        self._sparse_optim_state = {}
 
     def register_io_state(self, name, obj):
         if name in self._io_state:
@@ -62,17 +63,14 @@ class Saver:
         logger.info(f"Save checkpoint {ckpt_id} to {ckpt_path}")
         tables, scalars = self._sparse_parts()
         if tables:
-            SSaver(shard_index=shard_id, shard_num=shard_num, parallel=self._concurrency, hashtables=tables, tensors=scalars,
-                   path=ckpt_path).save()
-            if shard_num > 1 and dist.is_available() and dist.is_initialized():
-                dist.barrier()
+            self.save_sparse_params(shard_id, shard_num, ckpt_path, {**tables, **scalars}, self._concurrency)
         io_states = {name: io.dump_io_state() for name, io in self._io_state.items()}
         if io_states:
             torch.save(io_states, os.path.join(ckpt_path, f"io_state_{shard_id}.pt"))
         if shard_id == 0:
             _tables, dense = split_sparse_dense_state_dict(self._model.state_dict())
             if dense:
-                torch.save(dense, os.path.join(ckpt_path, "model.pt"))
+                self.save_dense_params(ckpt_path, dense)
             if self._extra_save_dict:
                 extra = {k: (v.state_dict() if hasattr(v, "state_dict") else v) for k, v in self._extra_save_dict.items()}
                 torch.save(extra, os.path.join(ckpt_path, "extra.pt"))
@@ -94,11 +92,40 @@ class Saver:
         if torch.cuda.is_available():
             torch.cuda.synchronize()
 
+    # ---- the pieces of save(), callable on their own as in the reference (``recis/framework/checkpoint_manager.py:222-274``)
+    def save_sparse_params(self, shard_id: int, shard_num: int, ckpt_path: str, sparse_state_dict: dict, concurrent: int = 16,
+                           sync_func=None):
+        """Write this shard's tables (and the dense tensors mixed into ``sparse_state_dict``, e.g. the sparse optimizer's scalars)
+        as a safetensors bundle under ``ckpt_path``; ``sync_func`` (default: a barrier when there are several shards) runs after
+        the write."""
+        tables, tensors = split_sparse_dense_state_dict(dict(sparse_state_dict))
+        SSaver(shard_index=shard_id, shard_num=shard_num, parallel=concurrent, hashtables=tables, tensors=tensors, path=ckpt_path).save()
+        if sync_func is None:
+            if shard_num > 1 and dist.is_available() and dist.is_initialized():
+                dist.barrier()
+        else:
+            sync_func()
+
+    def save_dense_params(self, ckpt_path: str, dense_state_dict: dict):
+        torch.save(dense_state_dict, os.path.join(ckpt_path, "model.pt"))
+
+    def save_sparse_meta(self, dirname: str):
+        """Kept for API compatibility: the reference concatenates per-writer index files here; this writer merges the shards'
+        metadata into ``index`` / ``tensorkey.json`` itself (a gather on the process group), so there is nothing left to do."""
+        return None
+
+    def load_sparse_optim(self):
+        """Apply the sparse optimizer scalars read by the last ``load_sparse_params`` call."""
+        if self._sparse_optim is not None and self._sparse_optim_state:
+            logger.info("Load sparse optim")
+            self._sparse_optim.load_state_dict(self._sparse_optim_state)
+
     # ---- loading
     def load_sparse_params(self, ckpt_dir: str, strict=True, with_optim_scalars=True):
         tables, scalars = self._sparse_parts()
         loaded = {k: v.clone() for k, v in scalars.items()} if with_optim_scalars else {}
         SLoader(ckpt_dir, hashtables=tables, tensors=loaded, strict=strict).load()
+        self._sparse_optim_state = loaded
         return loaded
 
     def load_dense_params(self, ckpt_dir: str, strict: bool = True):
@@ -166,8 +193,8 @@ class Saver:
             self.load_dense_params(ckpt_path, strict=strict)
         if load_map["extra"] and self._extra_save_dict and os.path.exists(os.path.join(ckpt_path, "extra.pt")):
             self.load_extra_params(ckpt_path, load_map["io_state"], shard_id)
-        if load_map["sparse_opt"] and self._sparse_optim is not None and scalars:
-            self._sparse_optim.load_state_dict(scalars)
+        if load_map["sparse_opt"] and scalars:
+            self.load_sparse_optim()
 
 
 class CheckpointManager:

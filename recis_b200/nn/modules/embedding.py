@@ -219,6 +219,20 @@ class _LookupPoolFn(torch.autograd.Function):
         return (None,) * 12
 
 
+@dataclass
+class ExchangeIDsResults:
+    """Token of a started lookup (``DynamicEmbedding.exchange_ids``)."""
+    ids: torch.Tensor
+    offsets: torch.Tensor
+    prepared: Optional[dict] = None
+
+
+@dataclass
+class ExchangeEmbResults:
+    ids_result: ExchangeIDsResults
+    admit_hook: object = None
+
+
 class DynamicEmbedding(torch.nn.Module):
     """A distributed dynamic embedding table; ``forward`` returns pooled embeddings."""
 
@@ -311,6 +325,26 @@ class DynamicEmbedding(torch.nn.Module):
                                   admit_hook if admit_hook is not None else self._emb_opt.admit_hook, lane, prepared)
         # storage and pooling are fp32; a half-precision table dtype is the dtype the model sees
         return out if self._emb_opt.dtype == torch.float32 else out.to(self._emb_opt.dtype)
+
+    # ---- the reference's three-stage interface (``recis/nn/modules/embedding.py:498-624``) on top of prepare_lookup / lookup_pool
+    def exchange_ids(self, ids: torch.Tensor, offsets: torch.Tensor) -> "ExchangeIDsResults":
+        """Stage 1: start the id phase (dedup + routing + id exchange) of a lookup of flat ``ids`` with segment ``offsets``."""
+        return ExchangeIDsResults(ids=ids, offsets=offsets, prepared=self.prepare_lookup(ids))
+
+    def lookup_exchange_emb(self, ids_exchange_result: "ExchangeIDsResults", admit_hook=None) -> "ExchangeEmbResults":
+        """Stage 2 of the reference (owner-side lookup + embedding exchange). Here lookup, exchange and pooling are one fused
+        step, so this only records the admission hook; the work happens in ``emb_reduce``."""
+        return ExchangeEmbResults(ids_result=ids_exchange_result, admit_hook=admit_hook)
+
+    def wait_exchange_emb(self, emb_exchange_result: "ExchangeEmbResults"):
+        return emb_exchange_result
+
+    def emb_reduce(self, emb_exchange_result: "ExchangeEmbResults", weight, combiner, combiner_kwargs=None, fp16_enable=False):
+        """Stage 3: finish the lookup and pool (``sum`` / ``mean`` / ``tile``); returns ``[segments, D]`` (tile: ``[segments, T*D]``)."""
+        r = emb_exchange_result.ids_result
+        tile_len = (combiner_kwargs or {}).get("tile_len", 0) if combiner == "tile" else 0
+        out = self.lookup_pool(r.ids, r.offsets, weight, combiner, tile_len, admit_hook=emb_exchange_result.admit_hook, prepared=r.prepared)
+        return out.to(torch.float16) if fp16_enable else out
 
     def deal_with_tensor(self, input_tensor):
         if isinstance(input_tensor, RaggedTensor):

@@ -179,3 +179,19 @@ def test_reference_submodule_import_paths_exist():
         m = importlib.import_module(mod)
         for n in names:
             assert hasattr(m, n), (mod, n)
+
+
+def test_three_stage_lookup_interface_matches_forward():
+    """exchange_ids -> lookup_exchange_emb -> emb_reduce (the reference's staged interface) gives what forward() gives."""
+    from recis_b200.nn import DynamicEmbedding, EmbeddingOption
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.ragged import RaggedTensor
+    emb = DynamicEmbedding(EmbeddingOption(embedding_dim=8, shared_name="staged_api", combiner="mean", initializer=NormalInitializer(0, 0.1)))
+    ids = torch.tensor([5, 9, 5, 77, 1 << 40, 9], dtype=torch.int64)
+    offsets = torch.tensor([0, 2, 2, 5, 6], dtype=torch.int32)
+    want = emb(RaggedTensor(ids, [offsets]))
+    r1 = emb.exchange_ids(ids, offsets)
+    r2 = emb.wait_exchange_emb(emb.lookup_exchange_emb(r1))
+    got = emb.emb_reduce(r2, None, "mean", {})
+    assert torch.allclose(got.view_as(want), want)
+    assert emb.emb_reduce(emb.lookup_exchange_emb(emb.exchange_ids(ids, offsets)), None, "sum", fp16_enable=True).dtype == torch.float16
