@@ -15,6 +15,11 @@ class Feature(nn.Module):
         self._name = name
         self._compiled = False
         self._ops = nn.ModuleList()
+        self._buffers_data = None
+
+    def set_buffers_data(self, data):
+        """Attach side data to the feature (``recis/features/feature.py:58-59``); the feature itself does not read it."""
+        self._buffers_data = data
 
     @property
     def name(self):

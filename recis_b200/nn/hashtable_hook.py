@@ -14,7 +14,10 @@ from __future__ import annotations
 import json
 
 
-class _Hook:
+class BaseHook:
+    """``(name, params)`` descriptor; ``type`` tells the two kinds apart (``recis/nn/hashtable_hook.py:10-50``)."""
+    type = "base"
+
     def __init__(self, name: str, params: dict | None = None, **kwargs):
         self.name = name
         self.params = dict(params or {})
@@ -32,9 +35,14 @@ class _Hook:
         return hash(str(self))
 
 
-class AdmitHook(_Hook):
+class AdmitHook(BaseHook):
     """Admission policy descriptor."""
+    type = "admit"
 
 
-class FilterHook(_Hook):
+class FilterHook(BaseHook):
     """Eviction policy descriptor."""
+    type = "filter"
+
+
+_Hook = BaseHook          # earlier private name
