@@ -45,6 +45,7 @@ class Feature(nn.Module):
         self._ops.append(op)
         return self
 
+    @property
     def id(self):
         return id(self)
 

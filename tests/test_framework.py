@@ -205,7 +205,7 @@ def test_api_parity_helpers(tmp_path):
     info = recis_b200.get_build_info()
     assert info["cuda_arch"] == "sm_100a" and recis_b200.is_internal_enabled() is False
     f = Feature.from_json({"name": "x", "ops": [{"type": "SelectField", "name": "x"}, {"type": "Mod", "mod_value": 7}]})
-    assert len(f.ops) == 2 and isinstance(f.ops[1], Mod) and f.id() == id(f)
+    assert len(f.ops) == 2 and isinstance(f.ops[1], Mod) and f.id == id(f)
     h = HashTableFilterHook(filter_interval=10)
     h.reset_filter_interval(3)
     assert h.filter_interval == 3
