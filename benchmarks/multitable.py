@@ -234,7 +234,7 @@ def main():
     sync()
     t0 = time.perf_counter()
     dense_state = {k: v for k, v in model.state_dict().items() if isinstance(v, torch.Tensor)} if rank == 0 else {}
-    Saver(rank, world, 4, filter_out_sparse_param(model), dense_state, ckpt).save()
+    Saver(rank, world, 4, ckpt, filter_out_sparse_param(model), dense_state).save()
     sync()
     save_s = time.perf_counter() - t0
     ckpt_bytes = sum(os.path.getsize(os.path.join(ckpt, f)) for f in os.listdir(ckpt)) if rank == 0 else 0

@@ -112,10 +112,17 @@ class OrcDataset(DatasetBase):
     """Columnar files -> batches. ``varlen_feature`` columns (lists of ints, or strings / lists of strings with a hash)
     become RaggedTensors; ``fixedlen_feature`` columns become dense ``[batch, dim]`` tensors."""
 
-    def __init__(self, batch_size: int, worker_idx: int = 0, worker_num: int = 1, read_threads_num: int = 2, prefetch: int = 2,
-                 drop_remainder: bool = False, shuffle: bool = False, ragged_format: bool = True, transform_fn: Optional[Callable] = None,
-                 dtype: torch.dtype = torch.float32, device: str = "cpu", pin: bool = False, seed: int = 0, native_reader: bool = True,
-                 repeat: int = 1):
+    def __init__(self, batch_size: int, worker_idx: int = 0, worker_num: int = 1, read_threads_num: int = 2,
+                 pack_threads_num: Optional[int] = None, prefetch: int = 2, is_compressed: bool = False, drop_remainder: bool = False,
+                 worker_slice_batch_num: Optional[int] = None, shuffle: bool = False, ragged_format: bool = True,
+                 transform_fn: Optional[Callable] = None, save_interval: int = 100, dtype: torch.dtype = torch.float32,
+                 device: str = "cpu", pin: bool = False, seed: int = 0, native_reader: bool = True, repeat: int = 1):
+        # Argument order follows the reference (``recis/io/orc_dataset.py:73-90``). Accepted for compatibility, without effect
+        # here: ``pack_threads_num`` (one packer thread keeps batches in file order), ``is_compressed`` (ORC / Parquet carry their
+        # own compression), ``worker_slice_batch_num`` (files are dealt round-robin to workers) and ``save_interval`` (the
+        # iterator position is a (file, row) pair that is always current, so there is nothing to snapshot periodically).
+        self.pack_threads_num, self.is_compressed = pack_threads_num, is_compressed
+        self.worker_slice_batch_num, self.save_interval = worker_slice_batch_num, save_interval
         self.batch_size, self.worker_idx, self.worker_num = batch_size, worker_idx, worker_num
         self.read_threads_num, self.native_reader = read_threads_num, native_reader
         self.repeat = max(int(repeat), 1)           # passes over this worker's files (the role of column-io's RepeatDataset)
@@ -130,11 +137,11 @@ class OrcDataset(DatasetBase):
         self._varlen, self._fixed = {}, {}
         self._file_idx, self._row_in_file = 0, 0
 
-    def add_path(self, path: str):
-        self._paths.append(path)
+    def add_path(self, file_path: str):
+        self._paths.append(file_path)
 
-    def add_paths(self, paths: List[str]):
-        self._paths.extend(paths)
+    def add_paths(self, file_paths: List[str]):
+        self._paths.extend(file_paths)
 
     def varlen_feature(self, name: str, hash_type: Optional[str] = None, hash_bucket: int = 0, trans_int8: bool = False):
         self._varlen[name] = dict(hash_type=hash_type, hash_bucket=hash_bucket, trans_int8=trans_int8)

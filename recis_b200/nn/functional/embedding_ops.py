@@ -3,7 +3,7 @@ and ragged pooling with autograd. "Sparse mode" (mean = sum(w e) / sum(w)) and "
 the same kernel with a different normalisation flag."""
 from __future__ import annotations
 
-from typing import List, Union
+from typing import List, Optional, Union
 
 import torch
 
@@ -72,31 +72,38 @@ class _SegmentReduce(torch.autograd.Function):
         return g, None, None, None, None
 
 
-def ragged_embedding_segment_reduce(emb: torch.Tensor, weight, indices: torch.Tensor, offsets: torch.Tensor, combiner: str = "sum",
-                                    mean_by_weight: bool = False):
-    """``out[s] = reduce_{i in segment s} w_i * emb[indices[i]]`` (sum | mean), differentiable with respect to ``emb``."""
-    assert combiner in _COMBINER, "combiner must be sum or mean (tile: see ragged_ops.ragged_tile)"
+def ragged_embedding_segment_reduce(unique_emb: torch.Tensor, weight, reverse_indices: torch.Tensor, offsets: torch.Tensor,
+                                    combiner: str = "sum", combiner_kwargs: Optional[dict] = None, mean_by_weight: bool = False):
+    """``out[s] = reduce_{i in segment s} w_i * unique_emb[reverse_indices[i]]`` (sum | mean), differentiable with respect to
+    ``unique_emb``. ``combiner="tile"`` takes ``combiner_kwargs={"bs": [rows per feature], "tile_len": [rows kept per feature]}`` and
+    returns the first ``tile_len`` embeddings of every row, zero padded, ``[sum_f bs[f] * tile_len[f], dim]``
+    (argument names and the tile form follow ``recis/nn/functional/embedding_ops.py:332-420``)."""
+    assert combiner in ("sum", "mean", "tile"), f"combiner {combiner} is not supported"
+    if combiner == "tile":
+        from .ragged_ops import ragged_tile
+        kw = combiner_kwargs or {}
+        return ragged_tile(list(kw["bs"]), list(kw["tile_len"]), reverse_indices, offsets, unique_emb)
     mode = _COMBINER[combiner]
     if mode == 1 and mean_by_weight:
         mode = 2
     w = weight.float().contiguous() if weight is not None else None
-    return _SegmentReduce.apply(emb, w, indices.to(torch.int32).contiguous(), offsets.to(torch.int32).contiguous(), mode)
+    return _SegmentReduce.apply(unique_emb, w, reverse_indices.to(torch.int32).contiguous(), offsets.to(torch.int32).contiguous(), mode)
 
 
-def sparse_embedding_segment_reduce(emb: torch.Tensor, weight, indices: torch.Tensor, segment_ids: torch.Tensor, num_segments: int,
-                                    combiner: str = "sum"):
+def sparse_embedding_segment_reduce(unique_emb: torch.Tensor, weight, reverse_indices: torch.Tensor, segment_ids: torch.Tensor,
+                                    num_segments: int, combiner: str = "sum"):
     """Same reduction addressed by per-element segment ids (must be sorted); mean divides by the weight sum."""
     counts = torch.bincount(segment_ids.long(), minlength=num_segments)
-    offsets = torch.zeros(num_segments + 1, dtype=torch.int32, device=emb.device)
+    offsets = torch.zeros(num_segments + 1, dtype=torch.int32, device=unique_emb.device)
     offsets[1:] = torch.cumsum(counts, 0)
-    return ragged_embedding_segment_reduce(emb, weight, indices, offsets, combiner, mean_by_weight=True)
+    return ragged_embedding_segment_reduce(unique_emb, weight, reverse_indices, offsets, combiner, mean_by_weight=True)
 
 
-def segment_sum_sparse(data, weight, indices, segment_ids, num_segments):
+def segment_sum_sparse(data, weight, indices, segment_ids, num_segments, backend="recis"):
     return sparse_embedding_segment_reduce(data, weight, indices, segment_ids, num_segments, "sum")
 
 
-def weight_norm_sparse(data, weight, segment_ids, num_segments):
+def weight_norm_sparse(data, weight, segment_ids, num_segments, backend="recis"):
     """``data / sum of the segment's weights`` per segment."""
     ws = torch.zeros(num_segments, dtype=torch.float32, device=data.device).index_add_(0, segment_ids.long(), weight.float())
     return data / ws.clamp(min=1e-30).unsqueeze(1)

@@ -29,9 +29,9 @@ def fused_ids_encode_gpu(ids_list: List[torch.Tensor], table_ids) -> torch.Tenso
     return ids_encode(ids_list, table_ids)
 
 
-def fused_multi_hash(values: List[torch.Tensor], muls: List[torch.Tensor], primes: List[torch.Tensor],
+def fused_multi_hash(inputs: List[torch.Tensor], muls: List[torch.Tensor], primes: List[torch.Tensor],
                      bucket_nums: List[torch.Tensor]) -> List[torch.Tensor]:
     """Returns the outputs of all tensors flattened tensor-major (tensor 0's hashes first), as the reference does."""
-    res = native().fused_multi_hash(list(values), [_to_list(m) for m in muls], [_to_list(p) for p in primes],
+    res = native().fused_multi_hash(list(inputs), [_to_list(m) for m in muls], [_to_list(p) for p in primes],
                                     [_to_list(b) for b in bucket_nums])
     return [t for per_tensor in res for t in per_tensor]

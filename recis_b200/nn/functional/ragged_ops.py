@@ -16,9 +16,9 @@ def ragged_to_dense(values: torch.Tensor, offsets: List[torch.Tensor], default_v
     return native().ragged_to_dense(values, list(offsets), float(default_value))
 
 
-def dense_to_ragged(dense: torch.Tensor, check_invalid: bool = False, invalid_value=0):
+def dense_to_ragged(tensor: torch.Tensor, check_invalid: bool = False, invalid_value=0):
     """2-D dense -> ``(values, [offsets])``; with ``check_invalid`` trailing ``invalid_value`` entries are stripped."""
-    values, offsets = native().dense_to_ragged(dense, bool(check_invalid), float(invalid_value))
+    values, offsets = native().dense_to_ragged(tensor, bool(check_invalid), float(invalid_value))
     return values, [offsets]
 
 
@@ -68,9 +68,9 @@ def fused_ragged_cutoff_3D(values: List[torch.Tensor], offsets: List[List[torch.
     return v, [[a, b] for a, b in zip(outer, inner)]
 
 
-def feature_cross_ragged(x_values, x_offsets, y_values, y_offsets, x_weight=None, y_weight=None):
+def feature_cross_ragged(x_val, x_offsets, y_val, y_offsets, x_weight=None, y_weight=None):
     """Per row: unique(x) x unique(y) -> ``(ids = murmur(x, y), offsets, weights = wx * wy)``."""
-    return native().feature_cross_ragged(x_values, x_offsets, y_values, y_offsets, x_weight, y_weight)
+    return native().feature_cross_ragged(x_val, x_offsets, y_val, y_offsets, x_weight, y_weight)
 
 
 def ragged_topk_index_cutoff(drop_num, pad_num, drop_side, pad_side, offset, topk_index, indicator):
@@ -81,11 +81,13 @@ def ragged_topk_index_cutoff(drop_num, pad_num, drop_side, pad_side, offset, top
     return native().calc_ragged_index(drop_num, pad_num, dl, pl, offset, topk_index, indicator)
 
 
-def ragged_tile(batch: List[int], seq: List[int], indices: torch.Tensor, offset: torch.Tensor, table: torch.Tensor):
+def ragged_tile(batch: List[int], seq: List[int], indices: torch.Tensor, offset: torch.Tensor, table: torch.Tensor,
+                check_enable: bool = False):
     """Tile combiner on an explicit table: for every feature ``f`` and row, the first ``seq[f]`` rows of ``table`` addressed by
     ``indices`` (zero padded) -> ``[sum_f batch[f] * seq[f], dim]``. Differentiable with respect to ``table``."""
+    if check_enable:
+        check_para(batch, seq, indices, offset, table)
     outs = []
-    C = native()
     row0 = 0
     off = offset.to(torch.int32)
     for b, s in zip(batch, seq):
@@ -94,6 +96,17 @@ def ragged_tile(batch: List[int], seq: List[int], indices: torch.Tensor, offset:
         outs.append(_TileFn.apply(table, idx, o, int(s)).view(b * s, table.shape[1]))
         row0 += b
     return torch.cat(outs) if len(outs) > 1 else outs[0]
+
+
+def check_para(batch: List[int], seq: List[int], indices: torch.Tensor, offset: torch.Tensor, table: torch.Tensor):
+    """Argument validation of ``ragged_tile`` (``recis/nn/functional/ragged_ops.py:694-715``)."""
+    assert len(batch) == len(seq) and len(batch) > 0, "batch and seq must be non-empty lists of equal length"
+    assert all(int(b) > 0 for b in batch) and all(int(s) > 0 for s in seq), "batch sizes and tile lengths must be positive"
+    assert offset.dim() == 1 and offset.numel() == sum(int(b) for b in batch) + 1, "offset must hold sum(batch) + 1 boundaries"
+    assert indices.dim() == 1 and table.dim() == 2, "indices must be 1-D and table 2-D"
+    assert int(offset[-1]) <= indices.numel(), "offsets point past the end of indices"
+    if indices.numel():
+        assert int(indices.min()) >= 0 and int(indices.max()) < table.shape[0], "indices out of range of the table"
 
 
 class _TileFn(torch.autograd.Function):

@@ -100,7 +100,7 @@ class Initializer:
 
 
 class ConstantInitializer(Initializer):
-    def __init__(self, init_val: float = 0.0) -> None:
+    def __init__(self, init_val: float = 0.0, dtype: torch.dtype = torch.float32) -> None:
         super().__init__()
         self._init_val = init_val
 

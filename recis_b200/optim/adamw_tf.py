@@ -16,10 +16,13 @@ from torch.optim import Optimizer
 
 
 class AdamWTF(Optimizer):
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, amsgrad=False, *,
-                 maximize: bool = False, fuse: bool = True):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, use_nesterov: bool = False, *,
+                 maximize: bool = False, fuse: bool = True, amsgrad: bool = False):
         if amsgrad:
             raise ValueError("amsgrad is not supported")
+        if use_nesterov:
+            # the reference accepts the flag and then asserts it is off (recis/optim/adamw_tf.py:344,389)
+            raise ValueError("use_nesterov is not supported")
         if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
             raise ValueError("invalid hyper-parameter")
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, maximize=maximize, fuse=fuse))

@@ -81,8 +81,8 @@ class BundleIndex:
 
 
 class CheckpointReader:
-    def __init__(self, checkpoint_path: str):
-        self._index = BundleIndex(checkpoint_path)
+    def __init__(self, path: str):
+        self._index = BundleIndex(path)
 
     def list_tensors(self) -> List[str]:
         return sorted(self._index.dense_names() + [f"{c}@{s}" for c, s in self._index.table_blocks()])

@@ -9,7 +9,7 @@ loaded by W2 ranks. Dense tensors are copied in place."""
 from __future__ import annotations
 
 import os
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 
@@ -20,10 +20,14 @@ from .checkpoint_reader import BundleIndex
 
 
 class Loader:
-    def __init__(self, checkpoint_path: str, hashtables: Dict[str, object], tensors: Dict[str, torch.Tensor], parallel: int = 16,
-                 strict: bool = True):
+    def __init__(self, checkpoint_path: str, hashtables: Optional[Dict[str, object]] = None,
+                 tensors: Optional[Dict[str, torch.Tensor]] = None, parallel: int = 16, filter_func=lambda x: x, strict: bool = True):
+        """``filter_func`` receives the default load plan ``{"hashtables": [logical table names], "tensors": [dense names]}`` (what
+        the model asks for) and returns the plan to execute; names it drops are left untouched (the reference passes its
+        load-info JSON through the same hook, ``recis/serialize/loader.py:60-77``)."""
         self.index = BundleIndex(checkpoint_path)
-        self.hashtables, self.tensors, self.strict = hashtables, tensors, strict
+        self.hashtables, self.tensors, self.strict = hashtables or {}, tensors or {}, strict
+        self.filter_func = filter_func
         self.chunk = max(int(os.environ.get("RECIS_BLOCK_READ_SIZE", 1 << 20)), 1)
         # slot blocks of a chunk are read by up to ``parallel`` threads (the native file reads release the GIL), the role of the
         # reference loader's thread pool (``csrc/serialize/load_internal.cc:195-273``)
@@ -31,12 +35,21 @@ class Loader:
 
     def load(self):
         seen = set()
+        impls = []
         for impl in self.hashtables.values():
             if id(impl) not in seen:
                 seen.add(id(impl))
-                self._load_table(impl)
+                impls.append(impl)
+        plan = self.filter_func({"hashtables": sorted(c for impl in impls for c in impl.children_info().children()),
+                                 "tensors": sorted(self.tensors)})
+        self._wanted_children = set(plan.get("hashtables", []))
+        wanted_tensors = set(plan.get("tensors", []))
+        for impl in impls:
+            self._load_table(impl)
         dense = set(self.index.dense_names())
         for name, t in self.tensors.items():
+            if name not in wanted_tensors:
+                continue
             if name not in dense:
                 if self.strict:
                     raise KeyError(f"dense tensor {name} is missing from the checkpoint")
@@ -61,6 +74,8 @@ class Loader:
         if impl.store.last_seen() is not None and impl.store.last_seen().numel():
             slot_names.append(N.FILTER_SLOT)
         for ci, child in enumerate(impl.children_info().children()):
+            if child not in self._wanted_children:
+                continue
             parts = self.index.table_parts(child, N.ID_SLOT)
             if not parts:
                 if self.strict:

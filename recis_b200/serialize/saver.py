@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 import torch.distributed as dist
@@ -24,11 +24,16 @@ from . import names as N
 
 
 class Saver:
-    def __init__(self, shard_index: int, shard_num: int, parallel: int, hashtables: Dict[str, object], tensors: Dict[str, torch.Tensor],
-                 path: str, pg=None):
+    def __init__(self, shard_index: int = 0, shard_num: int = 1, parallel: int = 8, path: str = ".",
+                 hashtables: Optional[Dict[str, object]] = None, tensors: Optional[Dict[str, torch.Tensor]] = None,
+                 filter_func=lambda x: x, pg=None):
+        """Argument order as in the reference (``recis/serialize/saver.py:32-41``). ``filter_func`` receives the list of write
+        blocks, tuples ``(disk key, internal block name or None, dtype string, shape, is_dense, payload)``, and returns the
+        blocks to write (drop entries to leave tensors out of the bundle)."""
         assert parallel > 0 and 0 <= shard_index < shard_num
         self.shard_index, self.shard_num, self.parallel = shard_index, shard_num, parallel
-        self.hashtables, self.tensors, self.path, self.pg = hashtables, tensors, path, pg
+        self.hashtables, self.tensors, self.path, self.pg = hashtables or {}, tensors or {}, path, pg
+        self.filter_func = filter_func
 
     # ---- collect blocks: (disk key, internal name or None, dtype str, shape, dense?, native block tuple)
     def _table_blocks(self):
@@ -70,7 +75,7 @@ class Saver:
 
     def save(self):
         os.makedirs(self.path, exist_ok=True)
-        blocks = self._table_blocks() + self._dense_blocks()
+        blocks = list(self.filter_func(self._table_blocks() + self._dense_blocks()))
         total_files = self.parallel * self.shard_num
         files = [dict(name=N.data_file_name(self.shard_index * self.parallel + i, total_files), header={}, blocks=[], offset=0)
                  for i in range(self.parallel)]

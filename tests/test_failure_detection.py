@@ -87,7 +87,7 @@ def test_truncated_checkpoint_shard_is_a_clean_error(tmp_path):
     HashtableRegister().clear()
     eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=4, shared_name="a", device="cpu")})
     eng({"a": torch.arange(100)})
-    Saver(0, 1, 1, filter_out_sparse_param(eng), {}, str(tmp_path)).save()
+    Saver(0, 1, 1, str(tmp_path), filter_out_sparse_param(eng), {}).save()
     shard = [f for f in os.listdir(tmp_path) if f.endswith(".safetensors")][0]
     size = os.path.getsize(tmp_path / shard)
     with open(tmp_path / shard, "r+b") as fh:

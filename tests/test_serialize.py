@@ -45,7 +45,7 @@ def _dump(eng):
 def test_layout_and_independent_reader(tmp_path):
     eng, opt = _trained_engine()
     dense = {"w": torch.randn(3, 5), "flag": torch.tensor([True, False]), "sparse_adamw_step": torch.tensor(3.0)}
-    Saver(0, 1, 2, filter_out_sparse_param(eng), dense, str(tmp_path)).save()
+    Saver(0, 1, 2, str(tmp_path), filter_out_sparse_param(eng), dense).save()
     files = sorted(os.listdir(tmp_path))
     assert files == ["index", "model-000000-of-000002.safetensors", "model-000001-of-000002.safetensors", "tensorkey.json",
                      "torch_rank_weights_embs_table_multi_shard.json"]
@@ -88,7 +88,7 @@ def test_save_load_save_is_byte_identical(tmp_path):
     eng, _ = _trained_engine()
     dense = {"w": torch.randn(4, 4)}
     a, b = tmp_path / "a", tmp_path / "b"
-    Saver(0, 1, 1, filter_out_sparse_param(eng), dense, str(a)).save()
+    Saver(0, 1, 1, str(a), filter_out_sparse_param(eng), dense).save()
     ref = _dump(eng)
     HashtableRegister().clear()
     eng2, opt2 = _trained_engine(steps=0, seed=1)          # fresh, empty tables (optimizer slots exist)
@@ -101,7 +101,7 @@ def test_save_load_save_is_byte_identical(tmp_path):
         for s in ref[name]["slots"]:
             assert torch.equal(got[name]["slots"][s], ref[name]["slots"][s])
     assert torch.equal(dense2["w"], dense["w"])
-    Saver(0, 1, 1, filter_out_sparse_param(eng2), dense2, str(b)).save()
+    Saver(0, 1, 1, str(b), filter_out_sparse_param(eng2), dense2).save()
     for f in os.listdir(a):
         assert open(a / f, "rb").read() == open(b / f, "rb").read(), f
 
@@ -119,7 +119,7 @@ def test_resharding(tmp_path, w_save, w_load):
         e = ht(mine)
         for i, v in zip(mine.tolist(), e.detach()):
             emb_of[i] = v.clone()
-        Saver(r, w_save, 2, filter_out_sparse_param(ht), {"d": torch.arange(3.0)} if r == 0 else {}, str(tmp_path)).save()
+        Saver(r, w_save, 2, str(tmp_path), filter_out_sparse_param(ht), {"d": torch.arange(3.0)} if r == 0 else {}).save()
     assert os.path.exists(tmp_path / "index")
     total = 0
     for r in range(w_load):
@@ -137,7 +137,7 @@ def test_resharding(tmp_path, w_save, w_load):
 
 def test_failures_are_clean_errors(tmp_path):
     eng, _ = _trained_engine(steps=1)
-    Saver(0, 1, 1, filter_out_sparse_param(eng), {"w": torch.ones(2)}, str(tmp_path)).save()
+    Saver(0, 1, 1, str(tmp_path), filter_out_sparse_param(eng), {"w": torch.ones(2)}).save()
     HashtableRegister().clear()
     eng2, _ = _trained_engine(steps=0)
     with pytest.raises(KeyError):
@@ -178,7 +178,7 @@ def test_resharding_chain_8_4_1_8(tmp_path):
     def save(tables, world, d):
         os.makedirs(d, exist_ok=True)
         for r, ht in enumerate(tables):
-            Saver(r, world, 2, filter_out_sparse_param(ht), {}, str(d)).save()
+            Saver(r, world, 2, str(d), filter_out_sparse_param(ht), {}).save()
 
     def load(world, d):
         tables = make(world)
@@ -238,11 +238,42 @@ def test_failed_save_leaves_no_partial_shard(tmp_path):
     HashtableRegister().clear()
     eng, _opt = _trained_engine(steps=1)
     good = tmp_path / "good"
-    Saver(0, 1, 1, filter_out_sparse_param(eng), {"w": torch.ones(3)}, str(good)).save()
+    Saver(0, 1, 1, str(good), filter_out_sparse_param(eng), {"w": torch.ones(3)}).save()
     before = sorted(os.listdir(good))
     blocker = tmp_path / "blocker"
     blocker.write_text("a regular file where a directory is expected")
     with pytest.raises((RuntimeError, OSError)):
-        Saver(0, 1, 1, filter_out_sparse_param(eng), {"w": torch.ones(3)}, str(blocker / "ckpt")).save()
+        Saver(0, 1, 1, str(blocker / "ckpt"), filter_out_sparse_param(eng), {"w": torch.ones(3)}).save()
     assert blocker.read_text().startswith("a regular file")
     assert sorted(os.listdir(good)) == before and not any(f.endswith(".tmp") for f in before)
+
+
+def test_filter_func_leaves_tensors_out_of_save_and_load(tmp_path):
+    """``filter_func`` of Saver (write blocks) and Loader (load plan), the reference's hooks of the same name."""
+    from recis_b200.ragged import RaggedTensor
+
+    def engine(name):
+        return EmbeddingEngine({"u": EmbeddingOption(embedding_dim=4, shared_name=name, initializer=NormalInitializer(0, 0.05), device="cpu")})
+    eng = engine("ff_tab")
+    eng({"u": RaggedTensor(torch.arange(10) * 7919, [torch.arange(0, 11, 2, dtype=torch.int32)])})
+    dense = {"keep": torch.ones(3), "drop": torch.zeros(2)}
+    Saver(0, 1, 1, str(tmp_path), filter_out_sparse_param(eng), dense,
+          filter_func=lambda blocks: [b for b in blocks if not b[0].startswith("drop")]).save()
+    names = CheckpointReader(str(tmp_path)).list_tensors()
+    assert "keep" in names and "drop" not in names
+    del eng
+    import gc
+    gc.collect()
+    eng2 = engine("ff_tab")
+    target = {"keep": torch.zeros(3)}
+    seen = {}
+
+    def plan(p):
+        seen.update(p)
+        return {"hashtables": [], "tensors": p["tensors"]}              # dense only
+    Loader(str(tmp_path), filter_out_sparse_param(eng2), target, filter_func=plan).load()
+    assert torch.equal(target["keep"], torch.ones(3)) and seen["tensors"] == ["keep"] and seen["hashtables"] == ["ff_tab"]
+    table = next(iter(eng2.tables().values()))
+    assert table.impl.store.size() == 0                                   # the table was left out of the plan
+    Loader(str(tmp_path), filter_out_sparse_param(eng2), {}).load()
+    assert table.impl.store.size() == 10
