@@ -28,15 +28,45 @@ _LEN_KIND = {"fixed": 0, "poisson": 1, "geometric": 2, "uniform": 3}
 
 
 class DatasetBase:
-    def map(self, fn):
-        """``dataset.map(fn)``: apply ``fn`` to every batch (chainable, as in the reference's ``DatasetBase.map``)."""
-        return MapDataset(self, fn)
+    """Iterable of batches with a restorable position.
 
-    def filter(self, fn):
-        """``dataset.filter(fn)``: keep the batches for which ``fn(batch)`` is true."""
-        return FilterDataset(self, fn=fn)
+    ``map`` / ``filter`` register functions on the dataset itself, as in the reference (``recis/io/dataset_base.py:273-308``):
+    every batch goes through the map functions in registration order; a batch for which ANY filter function returns True is
+    skipped. Both return the dataset, so calls can be chained."""
 
-    """Iterable of batches with a restorable position."""
+    _pipeline_inline = False          # True: the class applies the registered functions itself, at its own place in __iter__
+
+    def map(self, map_func):
+        self.__dict__.setdefault("_map_funcs", []).append(map_func)
+        return self
+
+    def filter(self, filter_func):
+        self.__dict__.setdefault("_filter_funcs", []).append(filter_func)
+        return self
+
+    def _run_maps(self, batch):
+        for f in self.__dict__.get("_map_funcs", ()):
+            batch = f(batch)
+        return batch
+
+    def _filtered_out(self, batch) -> bool:
+        return any(f(batch) for f in self.__dict__.get("_filter_funcs", ()))
+
+    def _through_pipeline(self, it):
+        for batch in it:
+            batch = self._run_maps(batch)
+            if not self._filtered_out(batch):
+                yield batch
+
+    def __init_subclass__(cls, **kwargs):
+        super().__init_subclass__(**kwargs)
+        raw = cls.__dict__.get("__iter__")
+        if raw is not None and not cls.__dict__.get("_pipeline_inline", False):
+            def __iter__(self, _raw=raw):
+                if self.__dict__.get("_map_funcs") or self.__dict__.get("_filter_funcs"):
+                    return self._through_pipeline(_raw(self))
+                return _raw(self)
+            cls.__iter__ = __iter__
 
     def __iter__(self):
         raise NotImplementedError
@@ -99,11 +129,12 @@ class TensorDataset(DatasetBase):
         self._pos = int(state["pos"])
 
 
-def get_dir_size(path: str) -> int:
-    if os.path.isfile(path):
-        return os.path.getsize(path)
+def get_dir_size(dir_name: str) -> int:
+    """Bytes on disk under ``dir_name`` (a file or a directory walked recursively), ``recis/io/orc_dataset.py:17``."""
+    if os.path.isfile(dir_name):
+        return os.path.getsize(dir_name)
     total = 0
-    for root, _dirs, files in os.walk(path):
+    for root, _dirs, files in os.walk(dir_name):
         total += sum(os.path.getsize(os.path.join(root, f)) for f in files)
     return total
 
@@ -111,6 +142,8 @@ def get_dir_size(path: str) -> int:
 class OrcDataset(DatasetBase):
     """Columnar files -> batches. ``varlen_feature`` columns (lists of ints, or strings / lists of strings with a hash)
     become RaggedTensors; ``fixedlen_feature`` columns become dense ``[batch, dim]`` tensors."""
+
+    _pipeline_inline = True           # registered map functions run before transform_fn, as in the reference
 
     def __init__(self, batch_size: int, worker_idx: int = 0, worker_num: int = 1, read_threads_num: int = 2,
                  pack_threads_num: Optional[int] = None, prefetch: int = 2, is_compressed: bool = False, drop_remainder: bool = False,
@@ -210,6 +243,15 @@ class OrcDataset(DatasetBase):
             batch = copy_data_to_device(batch, "cuda", non_blocking=True)
         return batch
 
+    def _finish(self, batch):
+        """Registered map functions, then ``transform_fn`` (one callable or a list of them), then the filter functions
+        (``recis/io/dataset_base.py:453-459``). Returns None for a batch that a filter function rejects."""
+        batch = self._run_maps(batch)
+        if self.transform_fn is not None:
+            for f in (self.transform_fn if isinstance(self.transform_fn, (list, tuple)) else [self.transform_fn]):
+                batch = f(batch)
+        return None if self._filtered_out(batch) else batch
+
     def _batches_of(self, table, start_row):
         import numpy as np
         n = table.num_rows
@@ -227,10 +269,10 @@ class OrcDataset(DatasetBase):
                 t = torch.as_tensor(arr)
                 batch[name] = (t.to(self.dtype) if t.is_floating_point() else t).reshape(e - b, -1)
             batch = self._place(batch)
-            if self.transform_fn is not None:
-                batch = self.transform_fn(batch)
+            batch = self._finish(batch)
             self._row_in_file = e
-            yield batch
+            if batch is not None:
+                yield batch
 
     def _native(self, paths):
         """The C++ reader (reader threads + packer + prefetch queue, ``csrc_io/columnar_reader.cpp``) when it applies: ORC
@@ -270,10 +312,10 @@ class OrcDataset(DatasetBase):
                     else:
                         batch[name] = c[1].to(self.dtype) if c[1].is_floating_point() else c[1]
                 batch = self._place(batch)
-                if self.transform_fn is not None:
-                    batch = self.transform_fn(batch)
+                batch = self._finish(batch)
                 self._file_idx, self._row_in_file = reader.state()
-                yield batch
+                if batch is not None:
+                    yield batch
         while self._file_idx < len(paths):
             table = self._read_table(paths[self._file_idx])
             yield from self._batches_of(table, self._row_in_file)
@@ -292,12 +334,18 @@ class OrcDataset(DatasetBase):
 
 
 class MapDataset(DatasetBase):
-    def __init__(self, dataset, fn: Callable):
-        self.dataset, self.fn = dataset, fn
+    """``MapDataset(input_dataset, map_funcs)``: every item goes through the functions in order (``recis/io/map_dataset.py:117``).
+    ``map_funcs`` may be one callable or a list."""
+
+    def __init__(self, input_dataset, map_funcs):
+        self.dataset = input_dataset
+        self.map_funcs = list(map_funcs) if isinstance(map_funcs, (list, tuple)) else [map_funcs]
 
     def __iter__(self):
         for batch in self.dataset:
-            yield self.fn(batch)
+            for f in self.map_funcs:
+                batch = f(batch)
+            yield batch
 
     def dump_io_state(self):
         return self.dataset.dump_io_state()
@@ -306,18 +354,26 @@ class MapDataset(DatasetBase):
         self.dataset.load_io_state(state)
 
 
-class FilterDataset(MapDataset):
-    """Keep only the listed keys of every batch (or drop batches for which ``fn`` returns False)."""
+class FilterDataset(DatasetBase):
+    """``FilterDataset(input_dataset, filter_funcs)``: an item is skipped when ANY function returns True
+    (``recis/io/filter_dataset.py:165``). ``keys`` (an addition) keeps only the listed entries of every batch."""
 
-    def __init__(self, dataset, keys: Optional[List[str]] = None, fn: Optional[Callable] = None):
-        super().__init__(dataset, fn)
+    def __init__(self, input_dataset, filter_funcs=None, keys: Optional[List[str]] = None):
+        self.dataset = input_dataset
+        self.filter_funcs = [] if filter_funcs is None else (list(filter_funcs) if isinstance(filter_funcs, (list, tuple)) else [filter_funcs])
         self.keys = keys
 
     def __iter__(self):
         for batch in self.dataset:
-            if self.fn is not None and not self.fn(batch):
+            if any(f(batch) for f in self.filter_funcs):
                 continue
             yield {k: batch[k] for k in self.keys} if self.keys else batch
+
+    def dump_io_state(self):
+        return self.dataset.dump_io_state()
+
+    def load_io_state(self, state):
+        self.dataset.load_io_state(state)
 
 
 class PrefetchDataset(DatasetBase):

@@ -22,11 +22,11 @@ def dense_to_ragged(tensor: torch.Tensor, check_invalid: bool = False, invalid_v
     return values, [offsets]
 
 
-def ragged_to_sparse(values: torch.Tensor, offsets: List[torch.Tensor]) -> torch.Tensor:
+def ragged_to_sparse(values: torch.Tensor, row_splits: List[torch.Tensor]) -> torch.Tensor:
     """COO tensor of a ragged tensor (runs on either device; the reference's op is CPU-only)."""
-    if isinstance(offsets, torch.Tensor):
-        offsets = [offsets]
-    indices, shape = native().ragged_to_sparse_indices(values.shape[0], list(offsets))
+    if isinstance(row_splits, torch.Tensor):
+        row_splits = [row_splits]
+    indices, shape = native().ragged_to_sparse_indices(values.shape[0], list(row_splits))
     return torch.sparse_coo_tensor(indices, values, tuple(shape) + tuple(values.shape[1:]))
 
 
@@ -85,8 +85,7 @@ def ragged_tile(batch: List[int], seq: List[int], indices: torch.Tensor, offset:
                 check_enable: bool = False):
     """Tile combiner on an explicit table: for every feature ``f`` and row, the first ``seq[f]`` rows of ``table`` addressed by
     ``indices`` (zero padded) -> ``[sum_f batch[f] * seq[f], dim]``. Differentiable with respect to ``table``."""
-    if check_enable:
-        check_para(batch, seq, indices, offset, table)
+    check_para(batch, seq, indices, offset, table, check_enable)
     outs = []
     row0 = 0
     off = offset.to(torch.int32)
@@ -98,8 +97,11 @@ def ragged_tile(batch: List[int], seq: List[int], indices: torch.Tensor, offset:
     return torch.cat(outs) if len(outs) > 1 else outs[0]
 
 
-def check_para(batch: List[int], seq: List[int], indices: torch.Tensor, offset: torch.Tensor, table: torch.Tensor):
-    """Argument validation of ``ragged_tile`` (``recis/nn/functional/ragged_ops.py:694-715``)."""
+def check_para(batch: List[int], seq: List[int], indices: torch.Tensor, offset: torch.Tensor, table: torch.Tensor,
+               check_enable: bool = True):
+    """Argument validation of ``ragged_tile`` (``recis/nn/functional/ragged_ops.py:694-715``); a no-op unless ``check_enable``."""
+    if not check_enable:
+        return
     assert len(batch) == len(seq) and len(batch) > 0, "batch and seq must be non-empty lists of equal length"
     assert all(int(b) > 0 for b in batch) and all(int(s) > 0 for s in seq), "batch sizes and tile lengths must be positive"
     assert offset.dim() == 1 and offset.numel() == sum(int(b) for b in batch) + 1, "offset must hold sum(batch) + 1 boundaries"

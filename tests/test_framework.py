@@ -213,8 +213,15 @@ def test_api_parity_helpers(tmp_path):
     with pytest.raises(ValueError):
         fac.regist_filter("GlobalStepFilter", object)
     assert isinstance(fac.get_filters(), dict) and isinstance(fac.get_admits(), dict)
-    ds = TensorDataset({"a": torch.arange(10)}, batch_size=2).map(lambda b: {"a": b["a"] * 2}).filter(lambda b: int(b["a"][0]) % 8 == 0)
+    # map / filter register on the dataset itself (the return value may be ignored); a filter function returning True SKIPS
+    ds = TensorDataset({"a": torch.arange(10)}, batch_size=2)
+    ds.map(lambda b: {"a": b["a"] * 2})
+    ds.filter(lambda b: int(b["a"][0]) % 8 != 0)
     assert [b["a"].tolist() for b in ds] == [[0, 2], [8, 10], [16, 18]]
+    from recis_b200.io import FilterDataset, MapDataset
+    chained = FilterDataset(MapDataset(TensorDataset({"a": torch.arange(6)}, batch_size=2), [lambda b: {"a": b["a"] + 1}, lambda b: {"a": b["a"] * 10}]),
+                            filter_funcs=[lambda b: int(b["a"][0]) == 30])
+    assert [b["a"].tolist() for b in chained] == [[10, 20], [50, 60]]
     (tmp_path / "x.bin").write_bytes(b"12345")
     assert get_dir_size(str(tmp_path)) == 5
     m = AUROC(num_thresholds=10)
@@ -272,3 +279,18 @@ def test_span_recorder_accounts_phases_per_step():
     assert not rec.enabled
     assert abs(out["ids"] - 2 * 3.5) < 1e-9 and abs(out["emb"] - 3.5) < 1e-9 and abs(out["total"] - 10.5) < 1e-9
     assert rec.stop(steps=1, synchronize=lambda: None) == {"total": 0}
+
+
+def test_common_config_file_transforms_and_nested_lookup(tmp_path):
+    import json
+    from recis_b200.common.common_config import get_access_id, get_config, set_config
+    p = tmp_path / "conf.json"
+    p.write_text(json.dumps({"train": {"lr": 0.1, "table": "$TABLE", "cols": ["a", "$COL", {"deep": "$TABLE"}]}, "name": "job"}))
+    conf = set_config(str(p), transforms={"$TABLE": "project.table", "$COL": "b"})
+    assert conf["train"]["table"] == "project.table" and conf["train"]["cols"] == ["a", "b", {"deep": "project.table"}]
+    assert get_config("train", "lr") == 0.1 and get_config("train", "missing", default=7) == 7 and get_config("name") == "job"
+    assert get_config("name", "too_deep", default="d") == "d" and get_config()["name"] == "job"
+    set_config({"x": {"y": 1}})
+    assert get_config("x", "y") == 1
+    set_config('{"z": 2}')
+    assert get_config("z") == 2 and set_config() == {} and get_access_id() is None

@@ -171,3 +171,21 @@ def test_ragged_format_false_gives_sparse_tensors(tmp_path, native_reader):
     assert torch.equal(sparse["seq"].to_dense()[:, : dense.shape[1]], dense)
     with pytest.raises(AssertionError):
         OrcDataset(batch_size=4, device="tpu")
+
+
+def test_registered_maps_run_before_transform_fn_and_filters_skip(tmp_path):
+    paths = _write(tmp_path, shards=1, rows=(64,))
+    for native_reader in (True, False):
+        ds = OrcDataset(batch_size=16, native_reader=native_reader,
+                        transform_fn=[lambda b: dict(b, order=b["order"] + ["transform"])])
+        ds.add_paths(paths)
+        ds.fixedlen_feature("label")
+        ds.map(lambda b: dict(b, order=["map"]))
+        n = [0]
+
+        def every_other(b):
+            n[0] += 1
+            return n[0] % 2 == 0                       # True = skip
+        ds.filter(every_other)
+        got = list(ds)
+        assert len(got) == 2 and all(b["order"] == ["map", "transform"] for b in got)
