@@ -11,7 +11,7 @@ from .hook import Hook
 
 
 class ProfilerHook(Hook):
-    def __init__(self, wait=1, warmup=1, active=1, repeat=1, output_dir="./", record_shapes=True, profile_memory=False,
+    def __init__(self, wait=1, warmup=48, active=1, repeat=4, output_dir="./", record_shapes=True, profile_memory=False,
                  with_stack=False, with_flops=False, nvtx=False):
         self.output_dir = output_dir
         self.app_id = os.environ.get("APP_ID", "recis_b200")
@@ -24,11 +24,16 @@ class ProfilerHook(Hook):
         self.nvtx = nvtx and torch.cuda.is_available()
         self.prof = torch.profiler.profile(
             activities=acts, schedule=torch.profiler.schedule(wait=wait, warmup=warmup, active=active, repeat=repeat),
-            on_trace_ready=self._on_trace, record_shapes=record_shapes, profile_memory=profile_memory, with_stack=with_stack,
+            on_trace_ready=self.get_trace_handler(), record_shapes=record_shapes, profile_memory=profile_memory, with_stack=with_stack,
             with_flops=with_flops)
         self.prof.start()
         if self.nvtx:
             torch.cuda.nvtx.range_push("step 0")
+
+    def get_trace_handler(self):
+        """The ``on_trace_ready`` callback: writes ``<APP_ID>-timeline-<step>.json`` into ``output_dir``
+        (``recis/hooks/profiler_hook.py:71-116``)."""
+        return self._on_trace
 
     def _on_trace(self, prof):
         path = os.path.join(self.output_dir, f"{self.app_id}-timeline-{self._step}.json")

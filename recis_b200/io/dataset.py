@@ -145,8 +145,8 @@ class OrcDataset(DatasetBase):
 
     _pipeline_inline = True           # registered map functions run before transform_fn, as in the reference
 
-    def __init__(self, batch_size: int, worker_idx: int = 0, worker_num: int = 1, read_threads_num: int = 2,
-                 pack_threads_num: Optional[int] = None, prefetch: int = 2, is_compressed: bool = False, drop_remainder: bool = False,
+    def __init__(self, batch_size: int, worker_idx: int = 0, worker_num: int = 1, read_threads_num: int = 4,
+                 pack_threads_num: Optional[int] = None, prefetch: int = 1, is_compressed: bool = False, drop_remainder: bool = False,
                  worker_slice_batch_num: Optional[int] = None, shuffle: bool = False, ragged_format: bool = True,
                  transform_fn: Optional[Callable] = None, save_interval: int = 100, dtype: torch.dtype = torch.float32,
                  device: str = "cpu", pin: bool = False, seed: int = 0, native_reader: bool = True, repeat: int = 1):

@@ -294,3 +294,17 @@ def test_common_config_file_transforms_and_nested_lookup(tmp_path):
     assert get_config("x", "y") == 1
     set_config('{"z": 2}')
     assert get_config("z") == 2 and set_config() == {} and get_access_id() is None
+
+
+def test_profiler_hook_writes_a_chrome_trace(tmp_path):
+    from recis_b200.hooks import ProfilerHook
+    hook = ProfilerHook(wait=0, warmup=1, active=1, repeat=1, output_dir=str(tmp_path))
+    assert callable(hook.get_trace_handler())
+    x = torch.randn(64, 64)
+    for step in range(4):
+        (x @ x).sum()
+        hook.after_step({}, step)
+    hook.end()
+    traces = [f for f in os.listdir(tmp_path) if f.endswith(".json")]
+    assert len(traces) == 1 and "-timeline-" in traces[0] and os.path.getsize(tmp_path / traces[0]) > 100
+    assert hook.traces == [str(tmp_path / traces[0])]
