@@ -87,6 +87,8 @@ class SyntheticDataset(DatasetBase):
         self._names = [f.name for f in spec.sparse]
 
     def __iter__(self):
+        if self.steps is not None and self._src.state() >= self.steps:
+            self._src.set_state(0)          # a finished pass starts over (a new epoch); a restored position resumes
         while self.steps is None or self._src.state() < self.steps:
             dense, label, fields = self._src.next()
             batch = {"label": label}
@@ -113,6 +115,8 @@ class TensorDataset(DatasetBase):
 
     def __iter__(self):
         total = self._n * self.epochs
+        if self._pos >= total:
+            self._pos = 0                   # a finished pass starts over (a new epoch); a restored position resumes
         while self._pos < total:
             b = self._pos % self._n
             e = min(b + self.batch_size, self._n)
@@ -295,6 +299,10 @@ class OrcDataset(DatasetBase):
 
     def __iter__(self):
         paths = self._my_paths()
+        if self._file_idx >= len(paths):
+            # a finished pass starts over, as the reference rebuilds its reader graph on every ``__iter__`` (one epoch per
+            # iteration, ``recis/io/dataset_base.py:462-464``); a position restored from a checkpoint resumes mid-stream
+            self._file_idx, self._row_in_file = 0, 0
         reader = self._native(paths)
         if reader is not None:
             while True:
@@ -385,6 +393,16 @@ class PrefetchDataset(DatasetBase):
     def __iter__(self):
         q: queue.Queue = queue.Queue(maxsize=self.depth)
         done = object()
+        stop = threading.Event()            # set when the consumer goes away early: the worker then stops instead of blocking
+
+        def put(item):
+            while not stop.is_set():
+                try:
+                    q.put(item, timeout=0.1)
+                    return True
+                except queue.Full:
+                    continue
+            return False
 
         def work():
             stream = torch.cuda.Stream() if self.device and str(self.device).startswith("cuda") else None
@@ -398,16 +416,24 @@ class PrefetchDataset(DatasetBase):
                             stream.synchronize()
                         else:
                             batch = copy_data_to_device(batch, self.device)
-                    q.put(batch)
-            finally:
-                q.put(done)
+                    if not put(batch):
+                        return
+                put(done)
+            except BaseException as e:          # noqa: BLE001 - handed to the consumer, which re-raises it
+                put(e)
 
-        threading.Thread(target=work, daemon=True).start()
-        while True:
-            item = q.get()
-            if item is done:
-                return
-            yield item
+        worker = threading.Thread(target=work, daemon=True)
+        worker.start()
+        try:
+            while True:
+                item = q.get()
+                if item is done:
+                    return
+                if isinstance(item, BaseException):
+                    raise item              # an error in the source must not look like the end of the data
+                yield item
+        finally:
+            stop.set()
 
     def dump_io_state(self):
         return self.dataset.dump_io_state()

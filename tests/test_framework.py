@@ -308,3 +308,89 @@ def test_profiler_hook_writes_a_chrome_trace(tmp_path):
     traces = [f for f in os.listdir(tmp_path) if f.endswith(".json")]
     assert len(traces) == 1 and "-timeline-" in traces[0] and os.path.getsize(tmp_path / traces[0]) > 100
     assert hook.traces == [str(tmp_path / traces[0])]
+
+
+def test_prefetch_dataset_order_errors_and_early_exit():
+    import threading
+    import time
+    from recis_b200.io import PrefetchDataset, TensorDataset
+    src = TensorDataset({"a": torch.arange(20)}, batch_size=3)
+    assert [b["a"].tolist() for b in PrefetchDataset(src, depth=2)] == [b["a"].tolist() for b in src]
+
+    class Broken:
+        def __iter__(self):
+            yield {"a": torch.zeros(1)}
+            raise OSError("disk went away")
+    with pytest.raises(OSError, match="disk went away"):
+        list(PrefetchDataset(Broken(), depth=2))
+    # a consumer that stops early does not leave the producer thread behind
+    before = threading.active_count()
+    it = iter(PrefetchDataset(src, depth=1))
+    next(it)
+    it.close()
+    deadline = time.time() + 5
+    while threading.active_count() > before and time.time() < deadline:
+        time.sleep(0.05)
+    assert threading.active_count() <= before
+
+
+def test_small_helpers_filesystem_logger_pad_info_initializers(tmp_path, capsys):
+    from recis_b200.framework.filesystem import get_file_system
+    from recis_b200.nn.initializers import KaimingNormalInitializer, KaimingUniformInitializer, XavierNormalInitializer, XavierUniformInitializer
+    from recis_b200.ragged.tensor import RaggedPadInfo
+    from recis_b200.utils.logger import Logger
+    fs = get_file_system(str(tmp_path / "x"))
+    with fs.open(str(tmp_path / "x"), "w") as fh:
+        fh.write("hello")
+    assert fs.exists(str(tmp_path / "x")) and get_file_system("file:///tmp").protocol[0] in ("file", "local")
+    log = Logger("helper_test")
+    log.error_rank0("an error line")
+    log.info_rank0("an info line")
+    out = capsys.readouterr()
+    assert "an error line" in out.err and "an info line" in out.out          # INFO to stdout, the rest to stderr
+    pad = RaggedPadInfo(torch.tensor([1]), torch.tensor([2]), torch.tensor([True]), torch.tensor([False]))
+    assert int(pad.drop_nums[0]) == 1 and int(pad.pad_nums[0]) == 2 and "RaggedPadInfo" in repr(pad)
+    # fan-based initializers: the standard deviation follows the fan of the [block, dim] shape they are built for
+    for cls, want in ((XavierUniformInitializer, (2.0 / (1024 + 64)) ** 0.5), (XavierNormalInitializer, (2.0 / (1024 + 64)) ** 0.5)):
+        init = cls()
+        init.set_shape([1024, 64])
+        init.build()
+        e = init.generate()
+        assert e.shape == (1024, 64) and abs(float(e.std()) - want) < 0.15 * want
+    for cls in (KaimingUniformInitializer, KaimingNormalInitializer):
+        init = cls()
+        init.set_shape([1024, 64])
+        init.build()
+        assert 0 < float(init.generate().std()) < 1
+
+
+def test_trainer_runs_every_epoch_over_the_whole_dataset(tmp_path):
+    """``train_epoch=3``: the dataset is iterated three times (an exhausted dataset starts over on the next ``iter``)."""
+    HashtableRegister().clear()
+    torch.manual_seed(0)
+    fields, spec = _spec(batch=32)
+    model = DeepFM(fields, device="cpu", compute_dtype=torch.float32, hidden=(16,))
+
+    class LossOnly(torch.nn.Module):
+        def __init__(self, m):
+            super().__init__()
+            self.m = m
+
+        def forward(self, batch):
+            return self.m(batch)[0]
+
+    class Count(Hook):
+        steps, epochs = 0, 0
+
+        def after_step(self, metrics=None, global_step=0):
+            Count.steps += 1
+
+        def after_epoch(self):
+            Count.epochs += 1
+
+    ds = SyntheticDataset(spec, steps=4)
+    args = TrainingArguments(output_dir=str(tmp_path), train_epoch=3, train_steps=None, save_steps=1000, log_steps=100)
+    trainer = Trainer(model=LossOnly(model), args=args, train_dataset=ds, dense_optimizers=(torch.optim.Adam(model.parameters(), lr=1e-3), None),
+                      sparse_optimizer=SparseAdagrad(filter_out_sparse_param(model), lr=0.01), hooks=[Count()])
+    trainer.train()
+    assert Count.epochs == 3 and Count.steps == 12

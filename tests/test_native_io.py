@@ -189,3 +189,12 @@ def test_registered_maps_run_before_transform_fn_and_filters_skip(tmp_path):
         ds.filter(every_other)
         got = list(ds)
         assert len(got) == 2 and all(b["order"] == ["map", "transform"] for b in got)
+
+
+@pytest.mark.parametrize("native_reader", [True, False])
+def test_second_iteration_is_a_new_epoch(tmp_path, native_reader):
+    paths = _write(tmp_path, shards=2, rows=(20, 12))
+    ds = _dataset(paths, native_reader)
+    first = [b["label"].clone() for b in ds]
+    second = [b["label"].clone() for b in ds]
+    assert len(first) == len(second) == 2 and all(torch.equal(a, b) for a, b in zip(first, second))

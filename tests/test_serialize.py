@@ -277,3 +277,29 @@ def test_filter_func_leaves_tensors_out_of_save_and_load(tmp_path):
     assert table.impl.store.size() == 0                                   # the table was left out of the plan
     Loader(str(tmp_path), filter_out_sparse_param(eng2), {}).load()
     assert table.impl.store.size() == 10
+
+
+def test_convert_v1_directory_into_a_loadable_bundle(tmp_path):
+    """Per-shard ``torch.save`` files + ``dense.pt`` -> safetensors bundle that the Loader reshards into one table."""
+    from recis_b200.serialize.convert_v1_to_v2 import convert_v1_to_v2
+    src, dst = tmp_path / "v1", tmp_path / "v2"
+    src.mkdir()
+    torch.manual_seed(0)
+    all_ids = torch.arange(0, 400, dtype=torch.int64) * 7919
+    emb = torch.randn(400, 4)
+    world = 2
+    for r in range(world):
+        sl = gen_slice(r, world)
+        mine = ((all_ids & 0xFFFF) >= sl.slice_begin) & ((all_ids & 0xFFFF) < sl.slice_end)
+        torch.save({"ids": all_ids[mine], "embeddings": emb[mine]}, src / f"conv_tab.shard_{r}_of_{world}.pt")
+    torch.save({"w": torch.arange(6.0).view(2, 3)}, src / "dense.pt")
+    convert_v1_to_v2(str(src), str(dst))
+    reader = CheckpointReader(str(dst))
+    assert torch.equal(reader.read_tensor("w"), torch.arange(6.0).view(2, 3))
+    ht = HashTable([4], name="conv_tab", initializer=NormalInitializer(0, 0.01), slice=gen_slice(0, 1))
+    dense = {"w": torch.zeros(2, 3)}
+    Loader(str(dst), filter_out_sparse_param(ht), dense).load()
+    assert ht.impl.store.size() == 400 and torch.equal(dense["w"], torch.arange(6.0).view(2, 3))
+    ids, rows = ht.impl.ids_map()
+    order = torch.argsort(ids)
+    assert torch.equal(ids[order], all_ids) and torch.allclose(ht.impl.store.emb()[rows[order]], emb)
