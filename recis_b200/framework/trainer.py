@@ -209,7 +209,17 @@ class Trainer:
             loss = loss[0]
         metrics.update(epoch=epoch, loss=loss.detach())
         metrics.update(get_global_metrics())
-        (loss / accum if accum > 1 else loss).backward()
+        # Every micro-batch back-propagates its unscaled loss. At the boundary both parameter kinds see the MEAN over the
+        # micro-batches: the sparse optimizer divides its staged gradients by the accumulation count itself
+        # (set_grad_accum_steps), the dense gradients are divided here. (The reference sums the dense gradients and averages
+        # the sparse ones, recis/framework/trainer.py:383-397 with csrc/embedding/hashtable.cc:129.)
+        loss.backward()
+        if boundary and accum > 1 and self.dense_optimizer is not None:
+            grads = [p.grad for g in self.dense_optimizer.param_groups for p in g["params"] if p.grad is not None]
+            if self.reducer is not None:
+                self.reducer.flat.mul_(1.0 / accum)
+            elif grads:
+                torch._foreach_mul_(grads, 1.0 / accum)
         if boundary and self.reducer is not None:
             self.reducer.all_reduce_async()
         if self.sparse_optimizer is not None:

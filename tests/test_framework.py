@@ -394,3 +394,43 @@ def test_trainer_runs_every_epoch_over_the_whole_dataset(tmp_path):
                       sparse_optimizer=SparseAdagrad(filter_out_sparse_param(model), lr=0.01), hooks=[Count()])
     trainer.train()
     assert Count.epochs == 3 and Count.steps == 12
+
+
+def test_trainer_gradient_accumulation_averages_dense_and_sparse_alike(tmp_path):
+    """Two micro-batches with accumulation 2 == one step on the mean loss of the two, for dense weights AND embedding rows."""
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.optim import SparseSGD
+
+    class Tiny(torch.nn.Module):
+        def __init__(self, name):
+            super().__init__()
+            self.emb = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=4, shared_name=name, device="cpu", initializer=NormalInitializer(0, 0.1))})
+            self.lin = torch.nn.Linear(4, 1)
+
+        def forward(self, batch):
+            return self.lin(self.emb({"a": batch["a"]})["a"]).square().mean()
+
+    batches = [{"a": torch.tensor([[1], [2], [3]])}, {"a": torch.tensor([[3], [4], [5]])}]
+
+    def run(accum, name):
+        HashtableRegister().clear()
+        torch.manual_seed(0)
+        m = Tiny(name)
+        sopt = SparseSGD(filter_out_sparse_param(m), lr=0.5)
+        dopt = torch.optim.SGD(m.lin.parameters(), lr=0.5)
+        if accum == 1:
+            sopt.zero_grad(); dopt.zero_grad()
+            (sum(m(b) for b in batches) / 2).backward()
+            sopt.step(); dopt.step()
+        else:
+            args = TrainingArguments(output_dir=str(tmp_path / name), gradient_accumulation_steps=2, train_steps=2, save_steps=1000)
+            Trainer(model=m, args=args, train_dataset=list(batches), dense_optimizers=(dopt, None), sparse_optimizer=sopt).train()
+        (t,) = m.emb.tables().values()
+        keys, rows = t.impl.ids_map()
+        e = t.impl.store.emb()[rows]
+        return m.lin.weight.detach().clone(), {int(k): e[i].clone() for i, k in enumerate(keys.tolist())}
+
+    (w1, e1), (w2, e2) = run(1, "ga_one"), run(2, "ga_two")
+    assert torch.allclose(w1, w2, atol=1e-6)
+    assert e1.keys() == e2.keys() and all(torch.allclose(e1[k], e2[k], atol=1e-6) for k in e1)
