@@ -77,8 +77,11 @@ class Saver:
                 if io_states:
                     with open(os.path.join(ckpt_path, "io_state_count"), "w") as f:
                         f.write(f"{shard_num}")
-            with open(os.path.join(self._output_dir, self._checkpoint_file), "a+") as f:
-                f.write(ckpt_id + "\n")
+            listing = os.path.join(self._output_dir, self._checkpoint_file)
+            known = [l.strip() for l in open(listing).read().split("\n") if l.strip()] if os.path.exists(listing) else []
+            if ckpt_id not in known:          # saving the same step twice (interval save + final save) lists it once
+                with open(listing, "a+") as f:
+                    f.write(ckpt_id + "\n")
             if ckpt_id not in self._checkpoint_version_list:
                 self._checkpoint_version_list.append(ckpt_id)
             while len(self._checkpoint_version_list) > self._max_keep:

@@ -434,3 +434,9 @@ def test_trainer_gradient_accumulation_averages_dense_and_sparse_alike(tmp_path)
     (w1, e1), (w2, e2) = run(1, "ga_one"), run(2, "ga_two")
     assert torch.allclose(w1, w2, atol=1e-6)
     assert e1.keys() == e2.keys() and all(torch.allclose(e1[k], e2[k], atol=1e-6) for k in e1)
+
+
+def test_final_save_of_an_interval_step_is_listed_once(tmp_path):
+    trainer, _model = _build(tmp_path, steps=10, save_steps=5)       # step 10 is saved by the interval and again at the end
+    trainer.train()
+    assert open(tmp_path / "checkpoint").read().split() == ["ckpt_5", "ckpt_10"]
