@@ -25,12 +25,21 @@ class HashTableFilterHook(Hook):
         self._filters = [m._filter_hook_impl for m in model.modules() if isinstance(m, HashTable) and m._filter_hook_impl is not None]
         return self
 
+    def _live_filters(self):
+        """The attached model's filters, or - when the hook was built without a model, as in the reference - the filter of every
+        table alive in the process (``HashtableHookFactory().get_filters()``, ``recis/hooks/filter_hook.py:60-80``)."""
+        if self._filters:
+            return self._filters
+        from ..nn.modules.hashtable_hook_impl import HashtableHookFactory
+        return list(HashtableHookFactory().get_filters().values())
+
     def after_step(self, metrics=None, global_step=0):
         self._steps += 1
-        for f in self._filters:
+        filters = self._live_filters()
+        for f in filters:
             f.update_step()
         if self._steps % self.filter_interval == 0:
-            n = sum(f.do_filter() for f in self._filters)
+            n = sum(f.do_filter() for f in filters)
             self.evicted += n
             if n:
                 self.logger.info(f"evicted {n} rows at step {self._steps}")

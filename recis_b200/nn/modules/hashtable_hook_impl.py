@@ -7,6 +7,8 @@ index, and a count-based admission policy exists (``CountAdmit``).
 """
 from __future__ import annotations
 
+import weakref
+
 import torch
 
 from ..hashtable_hook import AdmitHook, FilterHook
@@ -94,6 +96,14 @@ class GlobalStepFilterHookImpl(torch.nn.Module):
         return int(ids.numel())
 
 
+def _table_key(table) -> str:
+    for attr in ("_name", "name"):
+        v = getattr(table, attr, None)
+        if isinstance(v, str):
+            return v
+    return str(id(table))
+
+
 class HashtableHookFactory:
     """Name -> implementation registry (singleton)."""
 
@@ -119,11 +129,11 @@ class HashtableHookFactory:
         self._filter[name] = impl
 
     def get_filters(self):
-        """Filter hook instances created so far, by table name."""
-        return self._filters
+        """Filter hook instances of the tables that are alive, by table name (held weakly: a table that is gone drops out)."""
+        return {k: r() for k, r in list(self._filters.items()) if r() is not None}
 
     def get_admits(self):
-        return self._admits
+        return {k: r() for k, r in list(self._admits.items()) if r() is not None}
 
     def register_admit_hook(self, name, impl):
         self._admit[name] = impl
@@ -135,12 +145,12 @@ class HashtableHookFactory:
         if hook.name not in self._admit:
             raise ValueError(f"unknown admit hook {hook.name}; known: {sorted(self._admit)}")
         inst = self._admit[hook.name](table, **hook.params)
-        self._admits[getattr(table, "name", str(id(table)))] = inst
+        self._admits[_table_key(table)] = weakref.ref(inst)
         return inst
 
     def create_filter_hook(self, table, hook: FilterHook):
         if hook.name not in self._filter:
             raise ValueError(f"unknown filter hook {hook.name}; known: {sorted(self._filter)}")
         inst = self._filter[hook.name](table, **hook.params)
-        self._filters[getattr(table, "name", str(id(table)))] = inst
+        self._filters[_table_key(table)] = weakref.ref(inst)
         return inst

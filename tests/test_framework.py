@@ -440,3 +440,24 @@ def test_final_save_of_an_interval_step_is_listed_once(tmp_path):
     trainer, _model = _build(tmp_path, steps=10, save_steps=5)       # step 10 is saved by the interval and again at the end
     trainer.train()
     assert open(tmp_path / "checkpoint").read().split() == ["ckpt_5", "ckpt_10"]
+
+
+def test_filter_hook_without_a_model_finds_the_tables_itself():
+    """``HashTableFilterHook(filter_interval=n)`` with no model, as the reference is used: the live tables' filters are found
+    through the hook factory's registry; a table that is gone drops out of it."""
+    import gc
+    from recis_b200.nn import HashTable
+    from recis_b200.nn.hashtable_hook import FilterHook
+    from recis_b200.nn.modules.hashtable_hook_impl import HashtableHookFactory
+    HashtableRegister().clear()
+    ht = HashTable([4], name="ttl_registry", device="cpu", filter_hook=FilterHook("GlobalStepFilter", {"filter_step": 3}))
+    assert "ttl_registry" in HashtableHookFactory().get_filters()
+    hook = HashTableFilterHook(filter_interval=2)
+    ht(torch.arange(50))
+    for step in range(8):
+        ht(torch.arange(5))
+        hook.after_step({}, step)
+    assert ht.impl.size() == 5 and hook.evicted >= 45
+    del ht, hook
+    gc.collect()
+    assert "ttl_registry" not in HashtableHookFactory().get_filters()
