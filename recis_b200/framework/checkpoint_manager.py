@@ -224,10 +224,15 @@ class CheckpointManager:
     def step(self):
         self._global_step += 1
         if self._save_interval and int(self._global_step) % self._save_interval == 0:
-            self._saver.save(f"ckpt_{int(self._global_step)}", self._rank, self._shard_num)
+            self.save()
 
     def save(self):
-        self._saver.save(f"ckpt_{int(self._global_step)}", self._rank, self._shard_num)
+        """Save the current step unless it has just been saved (the final save of a run whose last step hit the interval)."""
+        step = int(self._global_step)
+        if getattr(self, "_last_saved_step", None) == step:
+            return
+        self._saver.save(f"ckpt_{step}", self._rank, self._shard_num)
+        self._last_saved_step = step
 
     def load_model_bank(self, model_bank_conf):
         for mbc in model_bank_conf or []:
