@@ -5,6 +5,7 @@ import os
 import subprocess
 import sys
 
+import pytest
 import torch
 
 from recis_b200.models.seq_model import EncoderLayer, SequenceModel, segment_softmax
@@ -122,3 +123,30 @@ def test_csv_to_orc_round_trip(tmp_path):
     assert sum(b["label"].shape[0] for b in batches) == 4
     assert batches[0]["seq"].values().tolist() == [1, 2, 3, 7] and batches[0]["seq"].offsets()[0].tolist() == [0, 3, 3, 4]
     assert batches[1]["uid"].values().tolist() == [13]
+
+
+def test_quickstart_document_runs_as_written(tmp_path, monkeypatch):
+    """The first python block of docs/quickstart.md, with the data paths and sizes swapped for a generated toy set."""
+    import re
+    import numpy as np
+    pa = pytest.importorskip("pyarrow")
+    import pyarrow.orc as orc
+    from recis_b200.nn.modules.hashtable import HashtableRegister
+    HashtableRegister().clear()
+    rng = np.random.default_rng(0)
+    paths = []
+    for s in range(2):
+        n = 200
+        t = pa.table({"user": pa.array([rng.integers(0, 1 << 40, rng.integers(1, 4)).astype(np.int64) for _ in range(n)], type=pa.list_(pa.int64())),
+                      "city": pa.array([f"c{int(x)}" for x in rng.integers(0, 30, n)]),
+                      "price": (rng.random(n) * 100).astype(np.float32), "label": (rng.random(n) < 0.3).astype(np.float32)})
+        p = str(tmp_path / f"part-{s:05d}.orc")
+        orc.write_table(t, p)
+        paths.append(p)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = re.search(r"```python\n(.*?)```", open(os.path.join(root, "docs", "quickstart.md")).read(), re.S).group(1)
+    code = code.replace('["/data/part-00000.orc", "/data/part-00001.orc"]', repr(paths)).replace("batch_size=4096", "batch_size=50")
+    code = code.replace("train_steps=1000, save_steps=500", "train_steps=4, save_steps=2").replace('output_dir="out"', f'output_dir={str(tmp_path / "out")!r}')
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)          # the document picks the device; keep this test on CPU
+    exec(compile(code, "quickstart.md", "exec"), {"__name__": "quickstart"})
+    assert sorted(os.listdir(tmp_path / "out")) == ["checkpoint", "ckpt_2", "ckpt_4"]
