@@ -84,6 +84,7 @@ class ColumnarReader {
     pos_file_ = file_idx; pos_row_ = row;
     next_file_to_read_ = file_idx;
     next_file_to_pack_ = file_idx;
+    start_file_ = file_idx;                 // fixed for the life of the threads started below (pos_file_ moves with next())
     first_row_ = row;
     tables_.clear();
     queue_.clear();
@@ -182,7 +183,7 @@ class ColumnarReader {
       cv_tab_.notify_all();
       if (!item.second.empty()) { Batch b; b.error = item.second; push(std::move(b)); break; }
       const int64_t n = item.first->num_rows();
-      for (int64_t r0 = (f == pos_file_ ? first_row_ : 0); r0 < n; r0 += batch_size_) {
+      for (int64_t r0 = (f == start_file_ ? first_row_ : 0); r0 < n; r0 += batch_size_) {
         const int64_t r1 = std::min(r0 + batch_size_, n);
         if (drop_remainder_ && r1 - r0 < batch_size_) break;
         Batch b;
@@ -321,7 +322,7 @@ class ColumnarReader {
   std::vector<std::thread> workers_;
   std::thread packer_;
   bool stop_ = false;
-  int64_t next_file_to_read_ = 0, next_file_to_pack_ = 0, first_row_ = 0;
+  int64_t next_file_to_read_ = 0, next_file_to_pack_ = 0, first_row_ = 0, start_file_ = 0;
   int64_t pos_file_ = 0, pos_row_ = 0;
 };
 
