@@ -109,12 +109,13 @@ void write_gather_block(FileOutputBuffer* f, const Block& b, const std::string& 
 }
 
 void run_job(FileJob* job) {
+  std::shared_ptr<FileSystem> fs;
+  std::string tmp;
   try {
     // written under a temporary name and renamed when complete: a failed save never leaves a half-written shard behind
-    std::shared_ptr<FileSystem> fs;
     std::string local;
     check(Env::Default()->GetFileSystemForFile(job->path, &fs, &local));
-    const std::string tmp = local + ".tmp";
+    tmp = local + ".tmp";
     std::unique_ptr<rb::platform::WritableFile> wf;
     check(fs->NewWritableFile(tmp, &wf));
     FileOutputBuffer out(std::move(wf), 8u << 20);
@@ -132,6 +133,7 @@ void run_job(FileJob* job) {
     check(fs->RenameFile(tmp, local));
   } catch (const std::exception& e) {
     job->error = e.what();
+    if (fs && !tmp.empty() && fs->FileExists(tmp)) (void)fs->DeleteFile(tmp);      // best effort: no stray temporary either
   }
 }
 

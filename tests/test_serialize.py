@@ -303,3 +303,25 @@ def test_convert_v1_directory_into_a_loadable_bundle(tmp_path):
     ids, rows = ht.impl.ids_map()
     order = torch.argsort(ids)
     assert torch.equal(ids[order], all_ids) and torch.allclose(ht.impl.store.emb()[rows[order]], emb)
+
+
+def test_write_that_fails_midway_removes_its_temporary_file(tmp_path):
+    """The file system refuses data beyond 64 KiB (RLIMIT_FSIZE, standing in for a full disk): the save raises, and neither a
+    shard nor a temporary file is left in the directory."""
+    import subprocess
+    import sys
+    code = f"""
+import os, resource, signal, sys, torch
+sys.path.insert(0, {os.path.dirname(os.path.dirname(os.path.abspath(__file__)))!r})
+from recis_b200.serialize import Saver
+signal.signal(signal.SIGXFSZ, signal.SIG_IGN)
+resource.setrlimit(resource.RLIMIT_FSIZE, (65536, 65536))
+try:
+    Saver(0, 1, 1, {str(tmp_path)!r}, {{}}, {{"big": torch.zeros(1 << 20)}}).save()
+except Exception as e:
+    print("raised", type(e).__name__)
+print("files", sorted(os.listdir({str(tmp_path)!r})))
+"""
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert "raised" in out.stdout, out.stdout + out.stderr
+    assert "files []" in out.stdout, out.stdout
