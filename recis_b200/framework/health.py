@@ -36,6 +36,7 @@ class PeerMonitor:
         self._last = {r: (0, time.monotonic()) for r in range(world)}
         self._left = set()
         self._thread: Optional[threading.Thread] = None
+        self._last_check = -1e30
 
     @staticmethod
     def _default_store():
@@ -72,8 +73,12 @@ class PeerMonitor:
             pass
 
     def check(self):
-        """Raise ``PeerLostError`` if a peer that has not left went silent for longer than ``timeout``."""
+        """Raise ``PeerLostError`` if a peer that has not left went silent for longer than ``timeout``. The store is asked at
+        most once per heartbeat interval (heartbeats cannot change faster), so calling this every step costs nothing between."""
         now = time.monotonic()
+        if now - self._last_check < self.interval:
+            return
+        self._last_check = now
         for r in range(self.world):
             if r == self.rank or r in self._left:
                 continue
