@@ -15,8 +15,8 @@ _COMBINER = {"sum": 0, "mean": 1}
 def ids_partition(ids: torch.Tensor, max_partition_num: int, world_size: int):
     """Dedup ids and bucket the unique ids by owner rank.
     Returns ``(unique ids ordered by owner, per-owner counts (int64), reverse index (int32))``; the owner of an id is the
-    rank whose contiguous slice range contains ``id & 0xFFFF``."""
-    assert max_partition_num == 65536, "routing uses the low 16 id bits (65536 slices)"
+    rank whose contiguous slice range contains ``id & 0xFFFF``. ``max_partition_num`` is accepted and not used, as in the
+    reference (``recis/nn/functional/embedding_ops.py:486-512``): routing always uses the 65536 slices of the low 16 id bits."""
     uniq, rev, counts, offs = native().dedup_partition(ids.reshape(-1).contiguous(), int(world_size))
     n = int(offs[-1].item())
     return uniq[:n], counts.to(torch.int64), rev
