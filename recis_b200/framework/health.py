@@ -27,13 +27,18 @@ class PeerLostError(RuntimeError):
 
 
 class PeerMonitor:
-    def __init__(self, rank: int, world: int, store=None, interval: float = 0.5, timeout: float = 10.0, prefix: str = "recis_b200"):
+    def __init__(self, rank: int, world: int, store=None, interval: float = 0.5, timeout: float = 10.0, prefix: str = "recis_b200",
+                 startup_timeout: Optional[float] = None):
         self.rank, self.world = rank, world
         self.interval, self.timeout, self.prefix = interval, timeout, prefix
+        # ranks do not start their monitors at the same moment (imports, model construction): a peer that has not published
+        # its first heartbeat yet is given this long before it counts as lost
+        self.startup_timeout = max(60.0, 10 * timeout) if startup_timeout is None else startup_timeout
         self.store = store if store is not None else self._default_store()
         self._beat = 0
         self._stop = threading.Event()
-        self._last = {r: (0, time.monotonic()) for r in range(world)}
+        self._created = time.monotonic()
+        self._last = {r: None for r in range(world)}          # (beat, time it last changed); None until the peer was first seen
         self._left = set()
         self._thread: Optional[threading.Thread] = None
         self._last_check = -1e30
@@ -86,9 +91,16 @@ class PeerMonitor:
                 if self.store.check([self._key("left", r)]):
                     self._left.add(r)
                     continue
-                beat = int(self.store.get(self._key("hb", r))) if self.store.check([self._key("hb", r)]) else 0
+                beat = int(self.store.get(self._key("hb", r))) if self.store.check([self._key("hb", r)]) else None
             except Exception as e:     # noqa: BLE001 - the store itself is gone (rank 0 hosts it)
                 raise PeerLostError(0, self.timeout) from e
+            if beat is None:           # the peer's monitor has not started yet
+                if now - self._created > self.startup_timeout:
+                    raise PeerLostError(r, now - self._created)
+                continue
+            if self._last[r] is None:  # first sight: its clock starts now
+                self._last[r] = (beat, now)
+                continue
             last_beat, last_time = self._last[r]
             if beat != last_beat:
                 self._last[r] = (beat, now)

@@ -154,3 +154,39 @@ def test_trainer_reports_a_rank_that_died_between_steps():
     survivor = res[0]
     assert survivor is not None and survivor["done"] is False and survivor["steps"] < 400
     assert survivor.get("lost") == 1 or survivor.get("error")
+
+
+def test_peer_that_starts_late_is_not_reported_lost():
+    """A fake store in one process: a peer whose first heartbeat arrives later than ``timeout`` after this rank's monitor was
+    created is given the start-up allowance; once seen, going silent for ``timeout`` reports it; never appearing at all reports
+    it after the start-up allowance."""
+    from recis_b200.framework.health import PeerLostError, PeerMonitor
+
+    class FakeStore(dict):
+        def set(self, k, v):
+            self[k] = v
+
+        def check(self, keys):
+            return all(k in self for k in keys)
+
+        def get(self, k):
+            return self[k].encode()
+
+    store = FakeStore()
+    mon = PeerMonitor(0, 2, store=store, interval=0.0, timeout=0.2, startup_timeout=1.0)
+    time.sleep(0.3)
+    mon.check()                                   # peer 1 has published nothing yet: within the start-up allowance
+    store.set("recis_b200/hb/1", "0")
+    mon.check()                                   # first sight
+    time.sleep(0.1)
+    store.set("recis_b200/hb/1", "1")
+    mon.check()
+    time.sleep(0.3)
+    with pytest.raises(PeerLostError) as e:
+        mon.check()                               # silent for longer than the timeout after having been seen
+    assert e.value.rank == 1
+    late = PeerMonitor(0, 2, store=FakeStore(), interval=0.0, timeout=0.1, startup_timeout=0.3)
+    late.check()
+    time.sleep(0.4)
+    with pytest.raises(PeerLostError):
+        late.check()                              # never showed up at all
