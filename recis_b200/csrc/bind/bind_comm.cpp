@@ -7,6 +7,11 @@
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <unistd.h>
+#include "../cpu/rb_cpu.h"
+#include "../cpu/rb_cpu_comm.h"
 #include "../kernels/rb_comm.h"
 #include "store.h"
 
@@ -50,6 +55,34 @@ int64_t sym_open(const std::string& handle, int64_t device_index) {
 
 void sym_close(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
 
+// ---- host twin of the symmetric heap: a POSIX shared-memory object per rank, mapped by every rank of the node
+// (zero-filled tensor over a fresh shared-memory object called `name`; the object is unlinked when the tensor dies)
+Tensor shm_alloc(const std::string& name, int64_t nbytes) {
+  nbytes = std::max<int64_t>((nbytes + 4095) / 4096 * 4096, 4096);
+  const int fd = shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
+  TORCH_CHECK(fd >= 0, "shm_open(", name, ") failed: ", std::strerror(errno));
+  if (ftruncate(fd, nbytes) != 0) { const int e = errno; close(fd); shm_unlink(name.c_str()); TORCH_CHECK(false, "ftruncate failed: ", std::strerror(e)); }
+  void* ptr = mmap(nullptr, (size_t)nbytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (ptr == MAP_FAILED) { shm_unlink(name.c_str()); TORCH_CHECK(false, "mmap failed: ", std::strerror(errno)); }
+  std::memset(ptr, 0, (size_t)nbytes);
+  return torch::from_blob(ptr, {nbytes}, [name, nbytes](void* p) { munmap(p, (size_t)nbytes); shm_unlink(name.c_str()); },
+                          torch::TensorOptions().dtype(torch::kUInt8));
+}
+
+// maps a peer's object; returns (address, mapped bytes) for shm_close
+std::tuple<int64_t, int64_t> shm_open_peer(const std::string& name) {
+  const int fd = shm_open(name.c_str(), O_RDWR, 0600);
+  TORCH_CHECK(fd >= 0, "shm_open(", name, ") failed: ", std::strerror(errno));
+  const off_t nbytes = lseek(fd, 0, SEEK_END);
+  void* ptr = mmap(nullptr, (size_t)nbytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  TORCH_CHECK(ptr != MAP_FAILED, "mmap failed: ", std::strerror(errno));
+  return {reinterpret_cast<int64_t>(ptr), (int64_t)nbytes};
+}
+
+void shm_close(int64_t ptr, int64_t nbytes) { munmap(reinterpret_cast<void*>(ptr), (size_t)nbytes); }
+
 RbPeers peers_of(const std::vector<int64_t>& ptrs) {
   TORCH_CHECK(ptrs.size() <= RB_MAX_PEERS, "at most ", RB_MAX_PEERS, " ranks per node are supported by the fused exchange");
   RbPeers p;
@@ -57,16 +90,28 @@ RbPeers peers_of(const std::vector<int64_t>& ptrs) {
   return p;
 }
 
-void comm_signal(const std::vector<int64_t>& flag_pads, int64_t channel, int64_t me, int64_t epoch) {
+// host = true: the pads are shared-memory mappings and the stores are done by this thread
+void comm_signal(const std::vector<int64_t>& flag_pads, int64_t channel, int64_t me, int64_t epoch, bool host) {
+  if (host) { rbc_comm_signal(peers_of(flag_pads), (int)channel, (int)me, (int)flag_pads.size(), epoch); return; }
   rb_comm_signal(peers_of(flag_pads), (int)channel, (int)me, (int)flag_pads.size(), epoch, cur_stream());
 }
 
 void comm_wait(const Tensor& flags, int64_t channel, int64_t world, int64_t epoch, int64_t spin_limit, Tensor status) {
+  if (!flags.is_cuda()) {
+    py::gil_scoped_release nogil;           // other threads of this process (heartbeats, readers) keep running while we wait
+    rbc_comm_wait(flags.data_ptr<int64_t>(), (int)channel, (int)world, epoch, spin_limit, status.data_ptr<int64_t>());
+    return;
+  }
   rb_comm_wait(flags.data_ptr<int64_t>(), (int)channel, (int)world, epoch, spin_limit, status.data_ptr<int64_t>(), cur_stream());
 }
 
 void comm_pull_ids(const std::vector<int64_t>& peer_ids, const std::vector<int64_t>& peer_offsets, int64_t me, Tensor ids_in,
                    Tensor prefix, Tensor n_in, Tensor status) {
+  if (!ids_in.is_cuda()) {
+    rbc_comm_pull_ids(peers_of(peer_ids), peers_of(peer_offsets), (int)me, (int)peer_ids.size(), ids_in.data_ptr<int64_t>(), ids_in.numel(),
+                      prefix.data_ptr<int32_t>(), n_in.data_ptr<int32_t>(), status.data_ptr<int64_t>());
+    return;
+  }
   rb_comm_pull_ids(peers_of(peer_ids), peers_of(peer_offsets), (int)me, (int)peer_ids.size(), ids_in.data_ptr<int64_t>(), ids_in.numel(),
                    prefix.data_ptr<int32_t>(), n_in.data_ptr<int32_t>(), status.data_ptr<int64_t>(), cur_stream());
 }
@@ -74,6 +119,11 @@ void comm_pull_ids(const std::vector<int64_t>& peer_ids, const std::vector<int64
 void comm_push_emb(const Tensor& emb, const Tensor& rows_in, const Tensor& prefix, const std::vector<int64_t>& peer_uemb, int64_t me,
                    int64_t n_in_hint) {
   const int D = (int)emb.size(1);
+  if (!emb.is_cuda()) {
+    rbc_comm_push_emb(emb.data_ptr<float>(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), peers_of(peer_uemb), (int)me,
+                      (int)peer_uemb.size(), D, n_in_hint);
+    return;
+  }
   TORCH_CHECK(D % 4 == 0, "the fused exchange needs an embedding width that is a multiple of 4");
   rb_comm_push_emb(emb.data_ptr<float>(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), peers_of(peer_uemb), (int)me,
                    (int)peer_uemb.size(), D, n_in_hint, cur_stream());
@@ -98,6 +148,12 @@ std::tuple<Tensor, Tensor> comm_owner_reduce(const Tensor& rows_in, Tensor head,
   } else {
     TORCH_CHECK(o.w != nullptr, "apply needs the weight slab");
   }
+  if (!rows_in.is_cuda()) {
+    rbc_comm_owner_reduce(rows_in.data_ptr<int32_t>(), head.data_ptr<int32_t>(), next.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(),
+                          g_in.data_ptr<float>(), (int)world, (int)D, mean_by_id, apply, o, apply ? nullptr : out_rows.data_ptr<int32_t>(),
+                          apply ? nullptr : out_grads.data_ptr<float>());
+    return {out_rows, out_grads};
+  }
   rb_comm_owner_reduce(rows_in.data_ptr<int32_t>(), head.data_ptr<int32_t>(), next.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(),
                        g_in.data_ptr<float>(), (int)world, (int)D, mean_by_id, apply, o,
                        apply ? nullptr : out_rows.data_ptr<int32_t>(), apply ? nullptr : out_grads.data_ptr<float>(), n_in_hint,
@@ -111,6 +167,22 @@ std::tuple<Tensor, Tensor> comm_owner_reduce(const Tensor& rows_in, Tensor head,
 void comm_grad_reduce_push(const Tensor& grad_out, const Tensor& gsrc, const Tensor& gscale, const Tensor& csr_u, const Tensor& csr_elem,
                            const Tensor& start, int64_t D, const Tensor& offsets, const Tensor& meta,
                            const std::vector<int64_t>& peer_gin, int64_t cap_rows) {
+  if (!grad_out.is_cuda()) {
+    // host twin: per-unique gradients first (the CPU reduction), then one row copy per unique id into its owner's window
+    TORCH_CHECK(grad_out.is_contiguous() && grad_out.scalar_type() == torch::kFloat32, "grad_out must be contiguous fp32");
+    const int world = (int)peer_gin.size();
+    const int32_t* off = offsets.data_ptr<int32_t>();
+    const int64_t n_u = off[world];
+    auto gu = torch::zeros({std::max<int64_t>(n_u, 1), D}, grad_out.options());
+    RbOpt none{};
+    none.kind = RB_OPT_SGD; none.grad_scale = 1.f; none.decay = 1.f;
+    if (csr_u.numel() > 0)
+      rbc_grad_reduce(grad_out.data_ptr<float>(), gsrc.data_ptr<int32_t>(), gscale.data_ptr<float>(), csr_u.data_ptr<int32_t>(),
+                      csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>(), csr_u.numel(), (int)D, nullptr, gu.data_ptr<float>(), 0, none);
+    RbPeers peers = peers_of(peer_gin);
+    rbc_comm_push_grads(gu.data_ptr<float>(), (int)D, off, meta.data_ptr<int32_t>() + 2 * world + 1, peers, world, cap_rows);
+    return;
+  }
   TORCH_CHECK(grad_out.is_cuda() && grad_out.is_contiguous() && grad_out.scalar_type() == torch::kFloat32, "grad_out must be contiguous fp32 on CUDA");
   TORCH_CHECK(D % 4 == 0 && D <= 512, "the fused exchange needs an embedding width that is a multiple of 4 and at most 512");
   const int64_t n = csr_u.numel();
@@ -130,7 +202,8 @@ void comm_grad_reduce_push(const Tensor& grad_out, const Tensor& gsrc, const Ten
                       csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>(), n, (int)D, span.data_ptr<float>(), push, cur_stream());
 }
 
-void comm_allreduce_slice(const std::vector<int64_t>& bufs, int64_t me, int64_t n_padded, double scale) {
+void comm_allreduce_slice(const std::vector<int64_t>& bufs, int64_t me, int64_t n_padded, double scale, bool host) {
+  if (host) { rbc_comm_allreduce_slice(peers_of(bufs), (int)me, (int)bufs.size(), n_padded, (float)scale); return; }
   rb_comm_allreduce_slice(peers_of(bufs), (int)me, (int)bufs.size(), n_padded, (float)scale, cur_stream());
 }
 
@@ -140,7 +213,10 @@ void init_comm(py::module& m) {
   m.def("sym_alloc", &sym_alloc);
   m.def("sym_open", &sym_open);
   m.def("sym_close", &sym_close);
-  m.def("comm_signal", &comm_signal);
+  m.def("shm_alloc", &shm_alloc);
+  m.def("shm_open_peer", &shm_open_peer);
+  m.def("shm_close", &shm_close);
+  m.def("comm_signal", &comm_signal, py::arg("flag_pads"), py::arg("channel"), py::arg("me"), py::arg("epoch"), py::arg("host") = false);
   m.def("comm_wait", &comm_wait);
   m.def("comm_wait_timed", [](const Tensor& flags, int64_t channel, int64_t world, int64_t epoch, int64_t spin_limit, Tensor status,
                               Tensor stats) {
@@ -153,7 +229,8 @@ void init_comm(py::module& m) {
   m.def("comm_push_emb", &comm_push_emb);
   m.def("comm_owner_reduce", &comm_owner_reduce);
   m.def("comm_grad_reduce_push", &comm_grad_reduce_push);
-  m.def("comm_allreduce_slice", &comm_allreduce_slice);
+  m.def("comm_allreduce_slice", &comm_allreduce_slice, py::arg("bufs"), py::arg("me"), py::arg("n_padded"), py::arg("scale"),
+        py::arg("host") = false);
   m.def("comm_copy", [](int64_t dst, int64_t src, int64_t nbytes, int64_t blocks) {
     rb_comm_copy(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), nbytes, (int)blocks, cur_stream());
   });

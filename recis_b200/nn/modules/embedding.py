@@ -250,7 +250,10 @@ class DynamicEmbedding(torch.nn.Module):
         storage = None
         growable = True
         mode = os.environ.get("RECIS_COMM", "auto")
-        if self.world_size > 1 and emb_opt.device.type == "cuda" and mode in ("auto", "fused"):
+        # CUDA: the fused exchange by default. CPU ranks of one machine: only when asked for (RECIS_COMM=fused), through the
+        # shared-memory twin of the exchange; "auto" keeps the collective path there
+        if self.world_size > 1 and ((emb_opt.device.type == "cuda" and mode in ("auto", "fused")) or
+                                    (emb_opt.device.type == "cpu" and mode == "fused")):
             from ...parallel.fused_exchange import FusedExchange
             self.fused = FusedExchange.create(emb_opt, self.pg, self.world_size, self.rank)
             if self.fused is not None:

@@ -14,6 +14,8 @@ optimizer owner      wait GRAD; ONE kernel adds the contributions of every touch
                      chained) and applies the row-wise optimizer update, reading only local memory
 
 No split size ever reaches the host; windows are sized for the worst case (``exchange_capacity`` unique ids per rank).
+The same code drives CPU ranks of one machine (``RECIS_COMM=fused`` with CPU tables): the windows then live in POSIX shared
+memory and the kernels' host twins (``csrc/cpu/cpu_comm.cc``) do the work - the oracle of this path in the multi-rank tests.
 Every (table, runtime group) pair owns one *lane*: its own windows, flag pad and epoch counter, so that the epochs written
 to a flag only ever grow and a gradient window is never rewritten before its owner consumed it.
 All flag waits are time-bounded; a timeout or a window overflow sets a bit in ``status`` which ``check()`` turns into an
@@ -74,6 +76,7 @@ class FusedExchange:
         self.pg, self.world, self.rank = pg, world, rank
         self.device = torch.device(emb_opt.device)
         self.D = emb_opt.embedding_dim
+        self.host = self.device.type != "cuda"       # CPU ranks: windows in shared memory, the exchange runs in csrc/cpu/cpu_comm.cc
         self.lanes = {}
         self.send_cap = int(os.environ.get("RECIS_EXCHANGE_CAPACITY", "0")) or int(getattr(emb_opt, "exchange_capacity", 0) or 0)
         # time limit of every flag wait; a dead peer then surfaces as an error, never as a hang
@@ -85,7 +88,7 @@ class FusedExchange:
         self.owner_unroll = int(os.environ.get("RECIS_OWNER_UNROLL", "2"))
         # RECIS_WAIT_STATS=1: flag waits go through the accounting kernel; wait_stats holds nanoseconds per (channel, peer)
         self.wait_stats = (torch.zeros(N_CH * world + N_CH, dtype=torch.int64, device=self.device)
-                           if os.environ.get("RECIS_WAIT_STATS") == "1" else None)
+                           if os.environ.get("RECIS_WAIT_STATS") == "1" and not self.host else None)
         self._head = None
         # RECIS_STAGE_EXCHANGE=1: the engine may issue the id phase of all of a model's groups before the first wait (prepare())
         self.stage_enabled = os.environ.get("RECIS_STAGE_EXCHANGE") == "1"
@@ -159,7 +162,7 @@ class FusedExchange:
         e = lane.epoch
         # more unique ids than the window holds sets the overflow bit in self.status (see check()); nothing is written out of bounds
         _uniq, rev, _counts, _offs = C.dedup_partition(ids, self.world, h["ids"].tensor, h["offsets"].tensor, self.status)
-        C.comm_signal(h["flags"].ptrs, CH_IDS, self.rank, e)
+        C.comm_signal(h["flags"].ptrs, CH_IDS, self.rank, e, self.host)
         return lane, e, rev
 
     def _forward(self, emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold,
@@ -185,7 +188,7 @@ class FusedExchange:
         prefix = lane.prefix.clone()
         tok = span_open("emb")
         C.comm_push_emb(store.emb(), rows_in, prefix, h["uemb"].ptrs, me, lane.in_cap)
-        C.comm_signal(h["flags"].ptrs, CH_EMB, me, e)
+        C.comm_signal(h["flags"].ptrs, CH_EMB, me, e, self.host)
         self._wait(h["flags"].tensor, CH_EMB, e)
         span_close(tok)
         uemb = h["uemb"].tensor.view(lane.send_cap, D)
@@ -210,7 +213,7 @@ class FusedExchange:
         tok = span_open("grad_push")
         C.comm_grad_reduce_push(grad_out, s["gsrc"], s["gscale"], csr_u, csr_elem, start, D, s["offsets"], s["prefix"],
                                 h["gin"].ptrs, lane.in_cap)
-        C.comm_signal(h["flags"].ptrs, CH_GRAD, me, s["epoch"])
+        C.comm_signal(h["flags"].ptrs, CH_GRAD, me, s["epoch"], self.host)
         span_close(tok)
         rec = dict(rows_in=s["rows_in"], prefix=s["prefix"], epoch=s["epoch"], scale=worker_scale, exchange=self, lane=lane,
                    mean_by_id=emb_mod.option.grad_reduce_by == "id",

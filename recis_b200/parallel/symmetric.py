@@ -39,18 +39,34 @@ class SymmetricHeap:
             layout[name] = (off, dtype, int(numel))
             off += nbytes
         self.nbytes = off
-        self.base, handle = C.sym_alloc(self.nbytes, self.device.index)
-        handles = [None] * self.world
-        dist.all_gather_object(handles, handle, group=pg)
         self._opened = []
         bases = []
-        for r in range(self.world):
-            if r == self.rank:
-                bases.append(self.base.data_ptr())
-            else:
-                p = C.sym_open(handles[r], self.device.index)
-                self._opened.append(p)
-                bases.append(p)
+        if self.device.type == "cuda":
+            self.base, handle = C.sym_alloc(self.nbytes, self.device.index)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle, group=pg)
+            for r in range(self.world):
+                if r == self.rank:
+                    bases.append(self.base.data_ptr())
+                else:
+                    p = C.sym_open(handles[r], self.device.index)
+                    self._opened.append(p)
+                    bases.append(p)
+        else:
+            # host twin (CPU ranks of one machine): a POSIX shared-memory object per rank, mapped by every rank
+            import os
+            import uuid
+            name = f"/recis_b200_{os.getpid()}_{uuid.uuid4().hex[:12]}"
+            self.base = C.shm_alloc(name, self.nbytes)
+            names = [None] * self.world
+            dist.all_gather_object(names, name, group=pg)
+            for r in range(self.world):
+                if r == self.rank:
+                    bases.append(self.base.data_ptr())
+                else:
+                    p, mapped = C.shm_open_peer(names[r])
+                    self._opened.append((p, mapped))
+                    bases.append(p)
         self.regions: Dict[str, SymmetricRegion] = {}
         for name, (o, dtype, numel) in layout.items():
             view = self.base[o:o + numel * _DT_SIZE[dtype]].view(dtype)
@@ -63,5 +79,8 @@ class SymmetricHeap:
     def close(self):
         C = native()
         for p in self._opened:
-            C.sym_close(p)
+            if isinstance(p, tuple):
+                C.shm_close(*p)
+            else:
+                C.sym_close(p)
         self._opened = []

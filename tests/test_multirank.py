@@ -61,9 +61,11 @@ def _train(rank, world, device_kind, batch_ranks):
         emb = ht.impl.store.emb()[rows]
         for i, e in zip(ids.tolist(), emb.cpu()):
             table[i] = e
-        for ex in [getattr(ht, "fused", None)]:
-            if ex is not None:
-                ex.check()
+        ex = getattr(ht, "fused", None)
+        if world > 1 and os.environ.get("RECIS_COMM") == "fused":
+            assert ex is not None and len(ex.lanes) == 2, "the fused exchange did not run"      # one lane per runtime group
+        if ex is not None:
+            ex.check()
     return {"outs": outs, "table": table}
 
 
@@ -98,6 +100,126 @@ def _compare(results, oracle, world):
 def test_gloo_ranks_match_single_process(world):
     results = run_ranks(_rank_fn, world, "gloo", args=("cpu",))
     _compare(results, _oracle(world), world)
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+def test_fused_exchange_on_cpu_ranks_matches_single_process(world):
+    """The fused exchange (windows, flags, id pull, row push, gradient push, owner reduce + update) through its shared-memory CPU
+    twin: same Python path as on GPUs, every world size, against the single-process oracle."""
+    results = run_ranks(_rank_fn, world, "gloo", args=("cpu",), env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    _compare(results, _oracle(world), world)
+
+
+def test_staged_fused_exchange_on_cpu_ranks():
+    """RECIS_STAGE_EXCHANGE=1: the requester half of both groups' id phases runs before the first wait; same results."""
+    results = run_ranks(_rank_fn, 3, "gloo", args=("cpu",), env={"RECIS_COMM": "fused", "RECIS_STAGE_EXCHANGE": "1", "RECIS_WAIT_TIMEOUT_S": "60"})
+    _compare(results, _oracle(3), 3)
+
+
+def _fused_variants_fn(rank, world):
+    """Gradient accumulation (two micro-batches per update), mean-by-id across requesters, and an eval lookup, on the fused
+    exchange; every rank also computes the single-process answer from all ranks' batches."""
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.nn.modules.hashtable import HashtableRegister
+    from recis_b200.optim import SparseSGD
+
+    def batch(r, step):
+        g = torch.Generator().manual_seed(100 * step + r)
+        return torch.randint(0, 40, (16, 3), generator=g) * 7919, torch.randn(16, 8, generator=g)
+
+    def run(world_here, ranks, name):
+        torch.manual_seed(5)
+        eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name=name, combiner="sum", grad_reduce_by="id",
+                                                    initializer=NormalInitializer(0, 0.05))})
+        opt = SparseSGD(filter_out_sparse_param(eng), lr=0.1)
+        opt.set_grad_accum_steps(2)
+        for step in range(4):                       # two updates of two micro-batches each
+            opt.zero_grad()
+            loss = 0.0
+            for r in ranks:
+                ids, coef = batch(r, step)
+                loss = loss + (eng({"a": ids})["a"] * coef).sum()
+            loss.backward()
+            opt.step()
+        eng.eval()
+        probe = torch.arange(0, 40).view(-1, 1) * 7919
+        with torch.no_grad():
+            return eng({"a": probe})["a"].clone(), eng
+
+    got, eng = run(world, [rank], "variants")
+    (table,) = eng.tables().values()
+    assert table.fused is not None
+    table.fused.check()
+    return got
+
+
+def test_fused_exchange_accumulation_and_mean_by_id_on_cpu_ranks():
+    world = 2
+    res = run_ranks(_fused_variants_fn, world, "gloo", env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    col = run_ranks(_fused_variants_fn_collective, world, "gloo")
+    for a, b in zip(res, col):
+        assert torch.allclose(a, b, atol=1e-5), float((a - b).abs().max())
+    assert torch.allclose(res[0], res[1], atol=1e-6)            # every rank reads the same rows back
+    assert float(res[0].abs().sum()) > 0
+
+
+def _fused_variants_fn_collective(rank, world):
+    """The same program on the collective (all-to-all) path."""
+    os.environ["RECIS_COMM"] = "nccl"
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.optim import SparseSGD
+    torch.manual_seed(5)
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name="variants", combiner="sum", grad_reduce_by="id",
+                                                initializer=NormalInitializer(0, 0.05))})
+    opt = SparseSGD(filter_out_sparse_param(eng), lr=0.1)
+    opt.set_grad_accum_steps(2)
+    for step in range(4):
+        opt.zero_grad()
+        g = torch.Generator().manual_seed(100 * step + rank)
+        ids, coef = torch.randint(0, 40, (16, 3), generator=g) * 7919, torch.randn(16, 8, generator=g)
+        (eng({"a": ids})["a"] * coef).sum().backward()
+        opt.step()
+    eng.eval()
+    (table,) = eng.tables().values()
+    assert table.fused is None
+    with torch.no_grad():
+        return eng({"a": torch.arange(0, 40).view(-1, 1) * 7919})["a"].clone()
+
+
+def _missing_peer_fn(rank, world):
+    """Step 1 runs on both ranks (it creates the windows); at step 2 rank 1 never shows up: rank 0's bounded waits run out, the
+    status word says so, and check() raises - nothing hangs."""
+    import time
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption
+    from recis_b200.nn.initializers import NormalInitializer
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name="missing_peer", initializer=NormalInitializer(0, 0.05))})
+    ids = torch.arange(20).view(-1, 1) * 7919 + rank
+    eng({"a": ids})
+    (table,) = eng.tables().values()
+    table.fused.check()
+    if rank == 1:
+        time.sleep(6.0)                           # alive, but absent from the step
+        return "absent"
+    t0 = time.monotonic()
+    eng({"a": ids})                               # two waits of one second each run out
+    took = time.monotonic() - t0
+    try:
+        table.fused.check()
+        return ("no error", took)
+    except RuntimeError as e:
+        return (str(e), took)
+
+
+def test_missing_peer_ends_in_a_timeout_status_not_a_hang():
+    res = run_ranks(_missing_peer_fn, 2, "gloo", env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "1"}, timeout=120)
+    msg, took = res[0]
+    assert "did not signal" in msg and took < 5.0
+    assert res[1] == "absent"
 
 
 def _need_gpus(n):
