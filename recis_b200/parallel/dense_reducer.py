@@ -29,9 +29,13 @@ class DenseGradReducer:
         self.pg = pg
         n = sum(p.numel() for p in self.params)
         dev = self.params[0].device
+        mode = os.environ.get("RECIS_COMM", "auto")
         if p2p is None:
-            p2p = dev.type == "cuda" and world > 1 and os.environ.get("RECIS_COMM", "auto") != "nccl" and world <= native().MAX_PEERS
+            # CUDA: our all-reduce unless NCCL is asked for. CPU ranks of one machine: only when asked for (RECIS_COMM=fused),
+            # over shared memory with the kernels' host twins
+            p2p = world > 1 and world <= native().MAX_PEERS and ((dev.type == "cuda" and mode != "nccl") or (dev.type == "cpu" and mode == "fused"))
         self.p2p = p2p
+        self.host = dev.type != "cuda"
         self.n = n
         self.epoch = 0
         if p2p:
@@ -41,7 +45,7 @@ class DenseGradReducer:
             self.heap = SymmetricHeap({"flags": (torch.int64, N_CH * world), "grads": (torch.float32, self.n_pad)}, dev, pg)
             self.flat = self.heap["grads"].tensor[:n]
             self.status = torch.zeros(1, dtype=torch.int64, device=dev)
-            self.stream = torch.cuda.Stream(device=dev)
+            self.stream = torch.cuda.Stream(device=dev) if not self.host else None
             self.rank = dist.get_rank(pg)
             self.spin_limit = int(float(os.environ.get("RECIS_WAIT_TIMEOUT_S", "20")) * 1e6)  # microseconds
         else:
@@ -66,17 +70,23 @@ class DenseGradReducer:
         C = native()
         self.epoch += 1
         e, h, W, me = self.epoch, self.heap, self.world, self.rank
+        if self.host:                      # no streams on the host: the two phases run here and now
+            self._phases(C, h, W, me, e)
+            return
         self.stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.stream):
-            C.comm_signal(h["flags"].ptrs, CH_AR0, me, e)
-            C.comm_wait(h["flags"].tensor, CH_AR0, W, e, self.spin_limit, self.status)
-            C.comm_allreduce_slice(h["grads"].ptrs, me, self.n_pad, 1.0 / W)
-            C.comm_signal(h["flags"].ptrs, CH_AR1, me, e)
-            C.comm_wait(h["flags"].tensor, CH_AR1, W, e, self.spin_limit, self.status)
+            self._phases(C, h, W, me, e)
+
+    def _phases(self, C, h, W, me, e):
+        C.comm_signal(h["flags"].ptrs, CH_AR0, me, e, self.host)
+        C.comm_wait(h["flags"].tensor, CH_AR0, W, e, self.spin_limit, self.status)
+        C.comm_allreduce_slice(h["grads"].ptrs, me, self.n_pad, 1.0 / W, self.host)
+        C.comm_signal(h["flags"].ptrs, CH_AR1, me, e, self.host)
+        C.comm_wait(h["flags"].tensor, CH_AR1, W, e, self.spin_limit, self.status)
 
     def wait(self):
         """Make the main stream wait for the averaged gradients (call before the dense optimizer step)."""
-        if self.world > 1 and self.p2p:
+        if self.world > 1 and self.p2p and not self.host:
             from .spans import span_close, span_open
             tok = span_open("dense_allreduce_wait")
             torch.cuda.current_stream().wait_stream(self.stream)

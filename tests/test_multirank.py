@@ -236,10 +236,10 @@ def test_gpu_ranks_match_single_process(comm):
     _compare(results, _oracle(world), world)
 
 
-def _allreduce_fn(rank, world):
+def _allreduce_fn(rank, world, device_kind="cuda"):
     import torch
     from recis_b200.parallel.dense_reducer import DenseGradReducer
-    dev = torch.device("cuda", rank)
+    dev = torch.device("cuda", rank) if device_kind == "cuda" else torch.device("cpu")
     torch.manual_seed(0)
     params = [torch.nn.Parameter(torch.zeros(s, device=dev)) for s in ((1000, 37), (513,), (64, 64))]
     red = DenseGradReducer(params, world)
@@ -250,26 +250,16 @@ def _allreduce_fn(rank, world):
         for p in params:
             p.grad.copy_(torch.randn(p.shape, generator=g).to(dev))
         red.all_reduce()
-        torch.cuda.synchronize()
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
         outs.append([p.grad.detach().cpu().clone() for p in params])
     red.check()
     return outs
 
 
-@pytest.mark.gpu
-def test_p2p_dense_allreduce():
-    _need_gpus(2)
-    world = min(torch.cuda.device_count(), int(os.environ.get("RECIS_TEST_GPU_RANKS", "2")))   # 2 ranks by default; more on request
-    results = run_ranks(_allreduce_fn, world, "nccl", env={"RECIS_COMM": "fused", "NCCL_NVLS_ENABLE": "0"})
+def _check_allreduce(results, world):
     shapes = ((1000, 37), (513,), (64, 64))
     for it in range(3):
-        expect = []
-        for s in shapes:
-            acc = torch.zeros(s)
-            for r in range(world):
-                pass
-            expect.append(acc)
-        # regenerate every rank's gradients in the same order as the workers did
         per_rank = []
         for r in range(world):
             g = torch.Generator().manual_seed(100 * it + r)
@@ -278,6 +268,22 @@ def test_p2p_dense_allreduce():
             mean = sum(per_rank[r][k] for r in range(world)) / world
             for r in range(world):
                 assert torch.allclose(results[r][it][k], mean, atol=1e-6)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_two_shot_dense_allreduce_on_cpu_ranks(world):
+    """The flat-buffer two-shot all-reduce (signal, wait, reduce my slice from all peers, write it back to all, signal, wait)
+    through the shared-memory twin: 3 ranks exercise the padding of the buffer to a multiple of 4 * world."""
+    results = run_ranks(_allreduce_fn, world, "gloo", args=("cpu",), env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    _check_allreduce(results, world)
+
+
+@pytest.mark.gpu
+def test_p2p_dense_allreduce():
+    _need_gpus(2)
+    world = min(torch.cuda.device_count(), int(os.environ.get("RECIS_TEST_GPU_RANKS", "2")))   # 2 ranks by default; more on request
+    results = run_ranks(_allreduce_fn, world, "nccl", env={"RECIS_COMM": "fused", "NCCL_NVLS_ENABLE": "0"})
+    _check_allreduce(results, world)
 
 
 def _staged_fn(rank, world):
