@@ -190,3 +190,9 @@ def test_peer_that_starts_late_is_not_reported_lost():
     time.sleep(0.4)
     with pytest.raises(PeerLostError):
         late.check()                              # never showed up at all
+
+
+def test_trainer_on_two_cpu_ranks_with_the_fused_exchange():
+    """The same two-rank Trainer run with the embedding exchange and the dense all-reduce on their shared-memory paths."""
+    res = run_ranks(_trainer_case, 2, "gloo", args=("ok",), env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    assert all(r["done"] and r["steps"] == 4 for r in res)
