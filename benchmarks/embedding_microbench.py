@@ -100,6 +100,10 @@ def main():
             uniq_max = max(uniq_max, int(torch.unique(key).numel()))
             del key
         del ids
+    if world > 1:                                  # sizes derived from the data must be the same on every rank
+        t = torch.tensor([nnz_max, uniq_max], dtype=torch.int64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        nnz_max, uniq_max = int(t[0]), int(t[1])
     xcap = int(uniq_max * 1.15) + 1024
     rows = args.capacity or int(min(xcap * (n_batches + 2), 120e9 / (args.dim * 8)) )
     per_table = max(rows // args.tables, 1)

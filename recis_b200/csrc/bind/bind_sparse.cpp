@@ -35,7 +35,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, in
   auto counts = torch::empty({world}, o.dtype(torch::kInt32));
   Tensor offsets = offsets_out.has_value() && offsets_out->defined() ? *offsets_out : torch::empty({world + 1}, o.dtype(torch::kInt32));
   Tensor unique_ids = unique_out.has_value() && unique_out->defined() ? *unique_out : torch::empty({n}, o);
-  const bool guarded = ids.is_cuda() && status.has_value() && status->defined();   // a smaller unique buffer needs the status word
+  const bool guarded = status.has_value() && status->defined();   // a smaller unique buffer needs the status word
   TORCH_CHECK(offsets.numel() >= world + 1 && offsets.scalar_type() == torch::kInt32 && (guarded || unique_ids.numel() >= n) &&
               unique_ids.scalar_type() == torch::kInt64, "dedup_partition: output buffers too small or of the wrong type");
   auto reverse = torch::empty({n}, o.dtype(torch::kInt32));
@@ -48,7 +48,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, in
   } else {
     rbc_dedup_partition(ids.data_ptr<int64_t>(), n, (int)world, reinterpret_cast<uint64_t*>(set_keys.data_ptr<int64_t>()),
                         set_pos.data_ptr<int32_t>(), cap, slot.data_ptr<int32_t>(), counts.data_ptr<int32_t>(),
-                        offsets.data_ptr<int32_t>(), unique_ids.data_ptr<int64_t>(), reverse.data_ptr<int32_t>());
+                        offsets.data_ptr<int32_t>(), unique_ids.data_ptr<int64_t>(), reverse.data_ptr<int32_t>(), unique_ids.numel(),
+                        guarded ? status->data_ptr<int64_t>() : nullptr);
   }
   return {unique_ids, reverse, counts, offsets};
 }

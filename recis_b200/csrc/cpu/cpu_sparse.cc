@@ -185,7 +185,8 @@ void rbc_table_rehash(RbTable src, RbTable dst) {
 }
 
 void rbc_dedup_partition(const int64_t* ids, int64_t n, int world, uint64_t* set_keys, int32_t* set_pos, int64_t set_cap,
-                         int32_t* slot_scratch, int32_t* counts, int32_t* offsets, int64_t* unique_ids, int32_t* reverse) {
+                         int32_t* slot_scratch, int32_t* counts, int32_t* offsets, int64_t* unique_ids, int32_t* reverse,
+                         int64_t unique_cap, int64_t* status) {
   std::memset(counts, 0, sizeof(int32_t) * world);
   std::memset(offsets, 0, sizeof(int32_t) * (world + 1));
   if (n <= 0) return;
@@ -206,15 +207,20 @@ void rbc_dedup_partition(const int64_t* ids, int64_t n, int world, uint64_t* set
     if (won) set_pos[slot] = counts[owner_of(key, world)]++;
     slot_scratch[i] = slot | (won ? (int32_t)0x80000000 : 0);
   }
+  // More unique ids than the output holds (an exchange window): flagged in the status word, boundaries clamped to the buffer,
+  // the ids beyond it dropped (their reverse index points at entry 0) - the device version does the same.
+  std::vector<int32_t> off((size_t)world + 1);
   int32_t run = 0;
-  for (int w = 0; w < world; ++w) { offsets[w] = run; run += counts[w]; }
-  offsets[world] = run;
+  for (int w = 0; w < world; ++w) { off[w] = run; run += counts[w]; }
+  off[world] = run;
+  if (run > unique_cap && status) __atomic_fetch_or(status, (int64_t)8, __ATOMIC_RELAXED);
+  for (int w = 0; w <= world; ++w) offsets[w] = (int32_t)std::min<int64_t>(off[w], unique_cap);
   for (int64_t i = 0; i < n; ++i) {
     const int32_t s = slot_scratch[i];
     const uint64_t key = (uint64_t)ids[i];
-    const int32_t u = offsets[owner_of(key, world)] + set_pos[s & 0x7FFFFFFF];
-    reverse[i] = u;
-    if (s < 0) unique_ids[u] = (int64_t)key;
+    const int32_t u = off[owner_of(key, world)] + set_pos[s & 0x7FFFFFFF];
+    reverse[i] = u < unique_cap ? u : 0;
+    if (s < 0 && u < unique_cap) unique_ids[u] = (int64_t)key;
   }
 }
 

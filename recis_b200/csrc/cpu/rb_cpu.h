@@ -15,7 +15,8 @@ void rbc_table_snapshot(RbTable t, int64_t* ids_out, int32_t* rows_out, int64_t 
                         const int64_t* last_seen, int64_t threshold, int use_filter);
 void rbc_table_rehash(RbTable src, RbTable dst);
 void rbc_dedup_partition(const int64_t* ids, int64_t n, int world, uint64_t* set_keys, int32_t* set_pos, int64_t set_cap,
-                         int32_t* slot_scratch, int32_t* counts, int32_t* offsets, int64_t* unique_ids, int32_t* reverse);
+                         int32_t* slot_scratch, int32_t* counts, int32_t* offsets, int64_t* unique_ids, int32_t* reverse,
+                         int64_t unique_cap, int64_t* status);
 void rbc_encode_merge(const int64_t* desc, const int64_t* table_idx, int F, int64_t total_nnz, int64_t total_seg,
                       int64_t* ids_out, int32_t* offsets_out);
 void rbc_gather_rows(const float* src, const int32_t* rows, int64_t n_max, const int32_t* n_dev, int D, float* out);

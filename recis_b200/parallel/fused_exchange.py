@@ -40,11 +40,12 @@ class _Lane:
     """Windows + flags of one (table, runtime group) pair."""
 
     def __init__(self, ex: "FusedExchange", nnz: int):
-        cap = ex.send_cap
-        if not cap:
-            t = torch.tensor([nnz], dtype=torch.int64, device=ex.device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ex.pg)
-            cap = max(int(t.item()) * 2, 1024)
+        # every rank must lay its windows out identically (peers address them by offset): the capacity is agreed on here, once,
+        # as the maximum over ranks of the configured value or of twice the first batch's id count
+        want = ex.send_cap if ex.send_cap else max(int(nnz) * 2, 1024)
+        t = torch.tensor([want], dtype=torch.int64, device=ex.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ex.pg)
+        cap = int(t.item())
         W, D = ex.world, ex.D
         self.send_cap = cap
         self.in_cap = min(W, 2) * cap

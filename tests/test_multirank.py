@@ -222,6 +222,41 @@ def test_missing_peer_ends_in_a_timeout_status_not_a_hang():
     assert res[1] == "absent"
 
 
+def _capacity_fn(rank, world, mode):
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption
+    from recis_b200.nn.initializers import NormalInitializer
+    cap = {"uneven": 300 + 200 * rank, "tiny": 8}[mode]          # per-rank window capacity in unique ids
+    torch.manual_seed(1)
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name=f"cap_{mode}", initializer=NormalInitializer(0, 0.05),
+                                                exchange_capacity=cap)})
+    g = torch.Generator().manual_seed(rank)
+    ids = torch.randint(0, 150, (40, 2), generator=g) * 7919
+    out = eng({"a": ids})["a"].detach().clone()
+    (table,) = eng.tables().values()
+    (lane,) = table.fused.lanes.values()
+    try:
+        table.fused.check()
+        err = None
+    except RuntimeError as e:
+        err = str(e)
+    # what the rows should be: the initializer is a pure function of (seed, id, column), so any table gives the reference values
+    torch.manual_seed(1)
+    from recis_b200.nn.modules.hashtable import HashtableRegister
+    os.environ["RECIS_COMM"] = "nccl"
+    ref_eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name=f"cap_{mode}_ref", initializer=NormalInitializer(0, 0.05))})
+    ref = ref_eng({"a": ids})["a"].detach().clone()
+    return {"send_cap": lane.send_cap, "err": err, "same": bool(torch.allclose(out, ref, atol=1e-6))}
+
+
+def test_window_capacity_is_agreed_across_ranks_and_overflow_is_reported():
+    res = run_ranks(_capacity_fn, 3, "gloo", args=("uneven",), env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    assert {r["send_cap"] for r in res} == {700}                 # the largest request wins on every rank: identical layouts
+    assert all(r["err"] is None and r["same"] for r in res)
+    res = run_ranks(_capacity_fn, 2, "gloo", args=("tiny",), env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    assert all(r["err"] is not None and "overflow" in r["err"] for r in res)      # flagged, nothing written out of bounds
+
+
 def _need_gpus(n):
     if not torch.cuda.is_available() or torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
