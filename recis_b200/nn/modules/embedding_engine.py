@@ -187,16 +187,24 @@ class EmbeddingEngine(nn.Module):
 
     # ------------------------------------------------------------------ lanes (opt-in)
     def _use_lanes(self, ht, feats, perm) -> bool:
-        return (self._lanes > 1 and perm is not None and len(feats) >= self._lanes and getattr(ht, "fused", None) is not None
-                and ht.impl.device.type == "cuda")
+        return self._lanes > 1 and perm is not None and len(feats) >= self._lanes and getattr(ht, "fused", None) is not None
 
     def _lookup_in_lanes(self, ht, feats, opt, run_key, dev):
         """Split the features of one runtime group into lanes; every lane coalesces, exchanges and pools on its own stream.
         Returns the pooled rows in the interleaved layout ``[segments_per_feature * n_features, D]``."""
         L = self._lanes
-        main = torch.cuda.current_stream(dev)
         bounds = [len(feats) * i // L for i in range(L + 1)]
         cubes = []
+        if dev.type != "cuda":
+            # CPU ranks (the exchange's host twin): no streams, the lanes run one after the other; same windows, same records
+            for i in range(L):
+                part = feats[bounds[i]:bounds[i + 1]]
+                ids, offsets, weights = self._coalesce(part, dev)
+                pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, 0, (part[0]["n_seg"], len(part)), opt.admit_hook,
+                                        lane=f"{run_key}#lane{i}")
+                cubes.append(pooled.view(part[0]["n_seg"], len(part), opt.embedding_dim))
+            return torch.cat(cubes, dim=1).reshape(-1, opt.embedding_dim)
+        main = torch.cuda.current_stream(dev)
         ht.fused.multi_stream = True
         for i in range(L):
             part = feats[bounds[i]:bounds[i + 1]]

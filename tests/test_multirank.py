@@ -257,6 +257,47 @@ def test_window_capacity_is_agreed_across_ranks_and_overflow_is_reported():
     assert all(r["err"] is not None and "overflow" in r["err"] for r in res)      # flagged, nothing written out of bounds
 
 
+def _lanes_fn(rank, world, lanes):
+    """Four features of one runtime group, optionally split into two exchange lanes; two training steps; returns outputs + rows."""
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.optim import SparseAdam
+    torch.manual_seed(11)
+    init = NormalInitializer(0, 0.05)
+    names = ["f0", "f1", "f2", "f3"]
+    eng = EmbeddingEngine({n: EmbeddingOption(embedding_dim=8, shared_name=n, combiner="sum", initializer=init) for n in names},
+                          interleave=True, exchange_lanes=lanes)
+    opt = SparseAdam(filter_out_sparse_param(eng), lr=0.05)
+    outs = []
+    for step in range(2):
+        g = torch.Generator().manual_seed(10 * step + rank)
+        feats = {n: torch.randint(0, 60, (12, 2), generator=g) * 7919 for n in names}
+        coef = {n: torch.randn(12, 8, generator=g) for n in names}
+        opt.zero_grad()
+        out = eng(feats)
+        sum((out[n] * coef[n]).sum() for n in names).backward()
+        opt.step()
+        outs.append({n: out[n].detach().clone() for n in names})
+    (table,) = eng.tables().values()
+    if table.fused is not None:
+        table.fused.check()
+        assert len(table.fused.lanes) == max(lanes, 1)
+    ids, rows = table.impl.ids_map()
+    order = torch.argsort(ids)
+    return {"outs": outs, "ids": ids[order], "emb": table.impl.store.emb()[rows[order]].clone()}
+
+
+def test_exchange_lanes_on_cpu_ranks_equal_the_single_lane_run():
+    env = {"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"}
+    two = run_ranks(_lanes_fn, 2, "gloo", args=(2,), env=env)
+    one = run_ranks(_lanes_fn, 2, "gloo", args=(1,), env=env)
+    for a, b in zip(two, one):
+        assert torch.equal(a["ids"], b["ids"]) and torch.allclose(a["emb"], b["emb"], atol=1e-6)
+        for x, y in zip(a["outs"], b["outs"]):
+            assert all(torch.allclose(x[n], y[n], atol=1e-6) for n in x)
+
+
 def _need_gpus(n):
     if not torch.cuda.is_available() or torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
