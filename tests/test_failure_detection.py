@@ -196,3 +196,14 @@ def test_trainer_on_two_cpu_ranks_with_the_fused_exchange():
     """The same two-rank Trainer run with the embedding exchange and the dense all-reduce on their shared-memory paths."""
     res = run_ranks(_trainer_case, 2, "gloo", args=("ok",), env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
     assert all(r["done"] and r["steps"] == 4 for r in res)
+
+
+def test_trainer_survivor_on_the_fused_exchange_gets_an_error_not_a_hang():
+    """Rank 1 dies between steps while the exchange runs over shared memory: rank 0's device-style waits run out (one second each)
+    instead of blocking, and the heartbeat monitor names the lost rank before a later step."""
+    res = run_ranks(_trainer_case, 2, "gloo", args=("die",), allow_missing=True, timeout=180,
+                    env={"RB_NO_FINAL_BARRIER": "1", "RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "1"})
+    assert res[1] is None
+    survivor = res[0]
+    assert survivor is not None and survivor["done"] is False and survivor["steps"] < 400
+    assert survivor.get("lost") == 1 or survivor.get("error")
