@@ -83,6 +83,10 @@ std::tuple<int64_t, int64_t> shm_open_peer(const std::string& name) {
 
 void shm_close(int64_t ptr, int64_t nbytes) { munmap(reinterpret_cast<void*>(ptr), (size_t)nbytes); }
 
+// removes the name; the memory lives on until the last mapping goes (called once every rank has mapped it, so that a rank
+// that dies later leaves nothing behind in the shared-memory directory)
+void shm_unlink_name(const std::string& name) { shm_unlink(name.c_str()); }
+
 RbPeers peers_of(const std::vector<int64_t>& ptrs) {
   TORCH_CHECK(ptrs.size() <= RB_MAX_PEERS, "at most ", RB_MAX_PEERS, " ranks per node are supported by the fused exchange");
   RbPeers p;
@@ -216,6 +220,7 @@ void init_comm(py::module& m) {
   m.def("shm_alloc", &shm_alloc);
   m.def("shm_open_peer", &shm_open_peer);
   m.def("shm_close", &shm_close);
+  m.def("shm_unlink_name", &shm_unlink_name);
   m.def("comm_signal", &comm_signal, py::arg("flag_pads"), py::arg("channel"), py::arg("me"), py::arg("epoch"), py::arg("host") = false);
   m.def("comm_wait", &comm_wait);
   m.def("comm_wait_timed", [](const Tensor& flags, int64_t channel, int64_t world, int64_t epoch, int64_t spin_limit, Tensor status,

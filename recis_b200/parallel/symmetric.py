@@ -56,10 +56,10 @@ class SymmetricHeap:
             # host twin (CPU ranks of one machine): a POSIX shared-memory object per rank, mapped by every rank
             import os
             import uuid
-            name = f"/recis_b200_{os.getpid()}_{uuid.uuid4().hex[:12]}"
-            self.base = C.shm_alloc(name, self.nbytes)
+            shm_name = f"/recis_b200_{os.getpid()}_{uuid.uuid4().hex[:12]}"
+            self.base = C.shm_alloc(shm_name, self.nbytes)
             names = [None] * self.world
-            dist.all_gather_object(names, name, group=pg)
+            dist.all_gather_object(names, shm_name, group=pg)
             for r in range(self.world):
                 if r == self.rank:
                     bases.append(self.base.data_ptr())
@@ -72,6 +72,8 @@ class SymmetricHeap:
             view = self.base[o:o + numel * _DT_SIZE[dtype]].view(dtype)
             self.regions[name] = SymmetricRegion(view, [b + o for b in bases])
         dist.barrier(group=pg)   # nobody touches a peer's memory before everyone has mapped it
+        if self.device.type != "cuda":
+            C.shm_unlink_name(shm_name)      # everybody holds a mapping now: the name can go
 
     def __getitem__(self, name) -> SymmetricRegion:
         return self.regions[name]
