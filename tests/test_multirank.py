@@ -298,6 +298,62 @@ def test_exchange_lanes_on_cpu_ranks_equal_the_single_lane_run():
             assert all(torch.allclose(x[n], y[n], atol=1e-6) for n in x)
 
 
+def _skewed_fn(rank, world, jitter):
+    """Many short steps with random delays in front of every flag signal and every pull / push: the ranks drift apart as far as
+    the protocol lets them. Returns the final rows."""
+    import random
+    import time
+    import torch
+    import recis_b200.parallel.fused_exchange as fx
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.optim import SparseAdagrad
+    if jitter:
+        real = fx.native()
+        rnd = random.Random(1234 + rank)
+
+        class Slow:
+            def __getattr__(self, name):
+                fn = getattr(real, name)
+                if name in ("comm_signal", "comm_pull_ids", "comm_push_emb", "comm_grad_reduce_push", "comm_owner_reduce"):
+                    def delayed(*a, **k):
+                        time.sleep(rnd.random() * 0.004)
+                        return fn(*a, **k)
+                    return delayed
+                return fn
+        slow = Slow()
+        fx.native = lambda: slow
+    torch.manual_seed(21)
+    init = NormalInitializer(0, 0.05)
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name="skew_a", combiner="sum", initializer=init),
+                           "b": EmbeddingOption(embedding_dim=8, shared_name="skew_b", combiner="mean", initializer=init)})
+    opt = SparseAdagrad(filter_out_sparse_param(eng), lr=0.05)
+    for step in range(25):
+        g = torch.Generator().manual_seed(1000 * step + rank)
+        feats = {n: torch.randint(0, 80, (10, 3), generator=g) * 7919 for n in ("a", "b")}
+        opt.zero_grad()
+        out = eng(feats)
+        sum(v.square().sum() for v in out.values()).backward()
+        opt.step()
+    rows = {}
+    for table in eng.tables().values():
+        if table.fused is not None:
+            table.fused.check()
+        ids, r = table.impl.ids_map()
+        for i, e in zip(ids.tolist(), table.impl.store.emb()[r]):
+            rows[i] = e.clone()
+    return rows
+
+
+def test_fused_exchange_under_random_skew_between_ranks():
+    env = {"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"}
+    skewed = run_ranks(_skewed_fn, 3, "gloo", args=(True,), env=env)
+    calm = run_ranks(_skewed_fn, 3, "gloo", args=(False,), env=env)
+    for a, b in zip(skewed, calm):
+        assert a.keys() == b.keys()
+        assert all(torch.allclose(a[k], b[k], atol=1e-6) for k in a)
+
+
 def _need_gpus(n):
     if not torch.cuda.is_available() or torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
