@@ -194,7 +194,23 @@ class Trainer:
             self.checkpoint_manager.step()
             self._global_step = self.checkpoint_manager.global_step
             lstep += 1
+            if lstep % max(int(self.args.log_steps), 1) == 0:
+                self.check_communication()
+        self.check_communication()
         self.checkpoint_manager.save()
+
+    def check_communication(self):
+        """Read the status words of the fused exchanges and of the dense all-reduce (one small host read each) and raise if a
+        bounded wait ran out or an exchange window overflowed. Called every ``log_steps`` steps and before the final save, so that
+        such a condition ends the run with an error instead of training on with dropped rows."""
+        seen = set()
+        for m in self.model.modules():
+            ex = getattr(m, "fused", None)
+            if ex is not None and id(ex) not in seen and hasattr(ex, "check"):
+                seen.add(id(ex))
+                ex.check()
+        if self.reducer is not None:
+            self.reducer.check()
 
     def _train_step(self, data, epoch, metrics):
         accum = self.gradient_accumulation_steps

@@ -207,3 +207,37 @@ def test_trainer_survivor_on_the_fused_exchange_gets_an_error_not_a_hang():
     survivor = res[0]
     assert survivor is not None and survivor["done"] is False and survivor["steps"] < 400
     assert survivor.get("lost") == 1 or survivor.get("error")
+
+
+def _overflow_trainer_fn(rank, world):
+    """Exchange windows far too small for the batches: the Trainer's periodic status check ends the run with an error."""
+    import tempfile
+    from recis_b200.framework import Trainer, TrainingArguments
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.optim import SparseSGD
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name="overflow_tab", exchange_capacity=4,
+                                                             initializer=NormalInitializer(0, 0.05))})
+            self.lin = torch.nn.Linear(8, 1)
+
+        def forward(self, batch):
+            return self.lin(self.emb({"a": batch["a"]})["a"]).square().mean()
+    m = M()
+    data = [{"a": torch.arange(64).view(-1, 1) * 7919 + rank} for _ in range(6)]
+    args = TrainingArguments(output_dir=tempfile.mkdtemp(), log_steps=2, train_steps=6, save_steps=1000, stop_check_interval=1000)
+    trainer = Trainer(model=m, args=args, train_dataset=data, dense_optimizers=(torch.optim.SGD(m.lin.parameters(), lr=0.1), None),
+                      sparse_optimizer=SparseSGD(filter_out_sparse_param(m), lr=0.1))
+    try:
+        trainer.train()
+        return "no error"
+    except RuntimeError as e:
+        return str(e)
+
+
+def test_trainer_stops_on_an_exchange_window_overflow():
+    res = run_ranks(_overflow_trainer_fn, 2, "gloo", env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "30"})
+    assert all("overflow" in r for r in res), res
