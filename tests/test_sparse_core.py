@@ -315,3 +315,11 @@ def test_dense_adam_cpu_matches_torch(decoupled):
         o2.step()
     for x, y in zip(a, b):
         torch.testing.assert_close(x, y, rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("world,dim", [(2, 16), (3, 8), (4, 128), (8, 64)])
+def test_exchange_host_twins_loopback(world, dim):
+    """All logical ranks of one exchange step in this process, through the host twins of the exchange kernels (the same harness
+    drives the device kernels on one GPU)."""
+    from loopback_case import run_loopback
+    run_loopback(torch.device("cpu"), world, dim)
