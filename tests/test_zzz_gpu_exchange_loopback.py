@@ -12,3 +12,29 @@ from loopback_case import run_loopback
 @pytest.mark.parametrize("world,dim", [(2, 16), (4, 128), (8, 64)])
 def test_exchange_kernels_loopback_on_one_gpu(world, dim):
     run_loopback(torch.device("cuda:0"), world, dim)
+
+
+@pytest.mark.gpu
+def test_wait_on_a_flag_that_nothing_sets_gives_up_with_a_status_bit():
+    """A bounded device-side wait that runs out: the flag pad stays at zero, the limit is 0.2 s; the kernel returns, the status
+    word carries the time-out bit, and the context goes on working."""
+    import time
+    import recis_b200
+    C = recis_b200.native()
+    dev = torch.device("cuda:0")
+    world = 4
+    flags = torch.zeros(C.N_CHANNELS * world, dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int64, device=dev)
+    torch.cuda.synchronize()
+    t0 = time.monotonic()
+    C.comm_wait(flags, 0, world, 1, 200_000, status)             # channel 0, epoch 1, limit in microseconds
+    torch.cuda.synchronize()
+    took = time.monotonic() - t0
+    assert int(status.item()) & 4
+    assert 0.15 < took < 5.0
+    # a flag that is already there is not a time-out, and the device still computes
+    flags.fill_(1)
+    status.zero_()
+    C.comm_wait(flags, 0, world, 1, 200_000, status)
+    assert int(status.item()) == 0
+    assert float((torch.ones(1000, device=dev) * 2).sum()) == 2000.0
