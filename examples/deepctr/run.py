@@ -27,6 +27,7 @@ from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_pa
 from recis_b200.nn.initializers import TruncNormalInitializer
 from recis_b200.ops.dense import MLP
 from recis_b200.optim import DenseAdamW, SparseAdamW
+from recis_b200.utils.launch import finish_distributed, init_distributed
 
 SEQ_LEN = 20
 
@@ -69,8 +70,10 @@ def main():
     ap.add_argument("--batch", type=int, default=512)
     ap.add_argument("--output-dir", default=None)
     args = ap.parse_args()
+    rank, world, dev = init_distributed(args.device)      # one process, or one per GPU / CPU rank under torch.distributed.run
+    args.device = str(dev)
     torch.manual_seed(0)
-    ds = OrcDataset(batch_size=args.batch, read_threads_num=2, prefetch=2)
+    ds = OrcDataset(batch_size=args.batch, worker_idx=rank, worker_num=world, read_threads_num=2, prefetch=2)   # files dealt to ranks
     ds.add_paths(sorted(glob.glob(os.path.join(args.data, "*.orc"))))
     for name in ("sparse1", "sparse2", "seq"):
         ds.varlen_feature(name)
@@ -79,12 +82,18 @@ def main():
         ds.fixedlen_feature(name)
     model = DeepCTR(args.device).to(args.device)
     out_dir = args.output_dir or tempfile.mkdtemp(prefix="deepctr_")
+    if world > 1:
+        box = [out_dir]
+        torch.distributed.broadcast_object_list(box, src=0)
+        out_dir = box[0]
     trainer = Trainer(model=model, args=TrainingArguments(output_dir=out_dir, log_steps=8, train_epoch=1, save_steps=1000),
                       train_dataset=WrapEndDataset(StateDataset(ds, save_interval=4)),
                       dense_optimizers=(DenseAdamW([p for p in model.parameters() if p.requires_grad], lr=1e-3), None),
-                      sparse_optimizer=SparseAdamW(filter_out_sparse_param(model), lr=1e-3), data_to_cuda=args.device == "cuda")
+                      sparse_optimizer=SparseAdamW(filter_out_sparse_param(model), lr=1e-3), data_to_cuda=dev.type == "cuda")
     trainer.train()
-    print({n: t.impl.size() for n, t in model.embedding_engine.tables().items()})
+    if rank == 0:
+        print({n: t.impl.size() for n, t in model.embedding_engine.tables().items()})
+    finish_distributed()
 
 
 if __name__ == "__main__":
