@@ -1,5 +1,6 @@
 from .data_utils import copy_data_to_device
+from .launch import finish_distributed, init_distributed
 from .logger import Logger
 from .parser import ArgumentParser
 
-__all__ = ["Logger", "copy_data_to_device", "ArgumentParser"]
+__all__ = ["Logger", "copy_data_to_device", "ArgumentParser", "init_distributed", "finish_distributed"]
