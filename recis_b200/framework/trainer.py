@@ -60,6 +60,12 @@ class Trainer:
         if self.world > 1 and self.dense_optimizer is not None:
             params = [p for g in self.dense_optimizer.param_groups for p in g["params"] if p.requires_grad]
             if params:
+                # every rank starts from rank 0's dense weights, as DistributedDataParallel does at construction (the reference
+                # wraps the model in DDP, recis/framework/trainer.py:170-184); buffers are included
+                with torch.no_grad():
+                    for t in list(model.parameters()) + list(model.buffers()):
+                        if t.is_floating_point() or t.dtype in (torch.int32, torch.int64, torch.bool, torch.uint8):
+                            dist.broadcast(t.data, src=0)
                 self.reducer = DenseGradReducer(params, self.world)
         if self.sparse_optimizer is not None:
             self.sparse_optimizer.set_grad_accum_steps(self.gradient_accumulation_steps)

@@ -241,3 +241,22 @@ def _overflow_trainer_fn(rank, world):
 def test_trainer_stops_on_an_exchange_window_overflow():
     res = run_ranks(_overflow_trainer_fn, 2, "gloo", env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "30"})
     assert all("overflow" in r for r in res), res
+
+
+def _param_sync_fn(rank, world):
+    """Ranks build their dense towers from different seeds; the Trainer starts all of them from rank 0's weights."""
+    import tempfile
+    from recis_b200.framework import Trainer, TrainingArguments
+    torch.manual_seed(100 + rank)
+    m = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.BatchNorm1d(3))
+    before = m[0].weight.detach().clone()
+    Trainer(model=m, args=TrainingArguments(output_dir=tempfile.mkdtemp()), train_dataset=[],
+            dense_optimizers=(torch.optim.SGD(m.parameters(), lr=0.1), None))
+    return before, m[0].weight.detach().clone(), m[1].running_mean.clone()
+
+
+def test_trainer_starts_every_rank_from_rank_zero_dense_weights():
+    res = run_ranks(_param_sync_fn, 2, "gloo")
+    assert not torch.equal(res[0][0], res[1][0])                 # they were built differently
+    assert torch.equal(res[0][1], res[1][1]) and torch.equal(res[0][1], res[0][0])      # rank 0's values everywhere
+    assert torch.equal(res[0][2], res[1][2])
