@@ -316,6 +316,20 @@ class DynamicEmbedding(torch.nn.Module):
         p["ids"] = ids
         return p
 
+    def serve_lookup(self, prepared, admit_hook=None):
+        """Second early phase of a prepared lookup on the fused exchange: this rank's owner-side work (wait for the ids, table
+        lookup, push of the rows, EMB signal) without waiting for the other owners. A model with several table groups calls it for
+        all of them between ``prepare_lookup`` and the first ``lookup_pool``. No-op for tokens of the collective path."""
+        if prepared is None or "fused" not in prepared or prepared["fused"]["served"] is not None:
+            return prepared
+        hook = admit_hook if admit_hook is not None else self._emb_opt.admit_hook
+        readonly, threshold = admit_params(hook)
+        if not (self.training and self.impl.trainable):
+            readonly = True
+        step = self.table.step_tensor() if not readonly else None
+        self.fused.serve(self, prepared["fused"], readonly, threshold, step)
+        return prepared
+
     def lookup_pool(self, ids: torch.Tensor, offsets: torch.Tensor, weights: Optional[torch.Tensor], combiner: str,
                     tile_len: int = 0, perm=None, admit_hook=None, lane: str = "default", prepared=None) -> torch.Tensor:
         """Flat ids + int32 segment offsets (+ per-id weights) -> pooled rows ``[segments, D]`` (tile: ``[segments, T*D]``)."""
@@ -335,8 +349,10 @@ class DynamicEmbedding(torch.nn.Module):
         return ExchangeIDsResults(ids=ids, offsets=offsets, prepared=self.prepare_lookup(ids))
 
     def lookup_exchange_emb(self, ids_exchange_result: "ExchangeIDsResults", admit_hook=None) -> "ExchangeEmbResults":
-        """Stage 2 of the reference (owner-side lookup + embedding exchange). Here lookup, exchange and pooling are one fused
-        step, so this only records the admission hook; the work happens in ``emb_reduce``."""
+        """Stage 2 of the reference (owner-side lookup + embedding exchange). On the fused exchange with staging switched on this
+        runs the owner side now (rows are pushed, nothing is waited for); otherwise it records the admission hook and the work
+        happens in ``emb_reduce``."""
+        self.serve_lookup(ids_exchange_result.prepared, admit_hook)
         return ExchangeEmbResults(ids_result=ids_exchange_result, admit_hook=admit_hook)
 
     def wait_exchange_emb(self, emb_exchange_result: "ExchangeEmbResults"):

@@ -261,6 +261,10 @@ class EmbeddingEngine(nn.Module):
                     if n_groups > 1:
                         prepared = ht.prepare_lookup(ids, lane=run_key)
                 plan.append((ht_name, ht, dev, run_key, feats, opt, tile_len, segs, perm, lanes, ids, offsets, weights, prepared))
+        # pass 1b (fused exchange with staging): every group's owner-side work and EMB signal before the first EMB wait
+        for entry in plan:
+            if entry[-1] is not None:
+                entry[1].serve_lookup(entry[-1], entry[5].admit_hook)
         # pass 2: finish the lookups in the same order
         for ht_name, ht, dev, run_key, feats, opt, tile_len, segs, perm, lanes, ids, offsets, weights, prepared in plan:
             ht.option.mean_by_weight = opt.mean_by_weight

@@ -93,6 +93,7 @@ class FusedExchange:
         self._head = None
         # RECIS_STAGE_EXCHANGE=1: the engine may issue the id phase of all of a model's groups before the first wait (prepare())
         self.stage_enabled = os.environ.get("RECIS_STAGE_EXCHANGE") == "1"
+        self.staged_serves = 0             # how many lookups had their owner side issued ahead of the first wait (serve())
 
     def _wait(self, flags, channel, epoch):
         C = native()
@@ -145,9 +146,20 @@ class FusedExchange:
         """Requester half of the id phase only (dedup + bucket into the window, signal IDS). A model with several (table, runtime
         group) pairs calls this for all of them before the first ``forward``: every rank's ids are then on offer before anybody
         waits, as the reference issues all of its id all-to-alls before the first wait
-        (``recis/nn/modules/embedding_engine.py:739-801``). Pass the result to ``forward(..., prepared=...)``."""
+        (``recis/nn/modules/embedding_engine.py:739-801``). Pass the result to ``serve`` and / or ``forward(..., prepared=...)``."""
         with torch.profiler.record_function("recis_b200/exchange_prepare"):
-            return self._begin(emb_mod, lane_key, ids)
+            lane, e, rev = self._begin(emb_mod, lane_key, ids)
+            return {"lane": lane, "e": e, "rev": rev, "served": None}
+
+    def serve(self, emb_mod, prepared, readonly, threshold, step):
+        """Owner half of a prepared lookup: wait for the ids, pull them, look the rows up (inserting unless ``readonly``), push
+        them to the requesters and signal EMB - without waiting for the other owners. Calling this for all groups before the
+        first ``forward`` leaves one rank-wide synchronisation point for the embedding phase of the whole model instead of one
+        per group."""
+        with torch.profiler.record_function("recis_b200/exchange_serve"):
+            prepared["served"] = self._serve(emb_mod, prepared["lane"], prepared["e"], readonly, threshold, step)
+            self.staged_serves += 1
+        return prepared
 
     def _begin(self, emb_mod, lane_key, ids):
         C = native()
@@ -166,11 +178,9 @@ class FusedExchange:
         C.comm_signal(h["flags"].ptrs, CH_IDS, self.rank, e, self.host)
         return lane, e, rev
 
-    def _forward(self, emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold,
-                 step, prepared=None):
+    def _serve(self, emb_mod, lane, e, readonly, threshold, step):
         C = native()
-        lane, e, rev = prepared if prepared is not None else self._begin(emb_mod, lane_key, ids)
-        h, me, D = lane.heap, self.rank, self.D
+        h, me = lane.heap, self.rank
         store = emb_mod.impl.store
         tok = span_open("ids")
         self._wait(h["flags"].tensor, CH_IDS, e)
@@ -187,9 +197,27 @@ class FusedExchange:
             self._store_event = torch.cuda.Event()
             self._store_event.record(torch.cuda.current_stream(self.device))
         prefix = lane.prefix.clone()
+        # the offsets window is rewritten by this lane's next forward; the backward needs this step's boundaries
+        offsets_now = h["offsets"].tensor.clone()
         tok = span_open("emb")
         C.comm_push_emb(store.emb(), rows_in, prefix, h["uemb"].ptrs, me, lane.in_cap)
         C.comm_signal(h["flags"].ptrs, CH_EMB, me, e, self.host)
+        span_close(tok)
+        return rows_in, prefix, offsets_now
+
+    def _forward(self, emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly, threshold,
+                 step, prepared=None):
+        C = native()
+        if prepared is None:
+            lane, e, rev = self._begin(emb_mod, lane_key, ids)
+            served = None
+        else:
+            lane, e, rev, served = prepared["lane"], prepared["e"], prepared["rev"], prepared["served"]
+        if served is None:
+            served = self._serve(emb_mod, lane, e, readonly, threshold, step)
+        rows_in, prefix, offsets_now = served
+        h, D = lane.heap, self.D
+        tok = span_open("emb")
         self._wait(h["flags"].tensor, CH_EMB, e)
         span_close(tok)
         uemb = h["uemb"].tensor.view(lane.send_cap, D)
@@ -198,7 +226,7 @@ class FusedExchange:
         else:
             out, gsrc, gscale = C.pool_forward(uemb, None, rev, offsets, weights, mode, perm_b, perm_f, train)
         saved = dict(rev=rev, gsrc=gsrc, gscale=gscale, rows_in=rows_in, prefix=prefix, epoch=e, lane=lane,
-                     offsets=h["offsets"].tensor.clone()) if train else None
+                     offsets=offsets_now) if train else None
         return out, saved
 
     # ------------------------------------------------------------------ backward (requester side) + staging

@@ -66,6 +66,7 @@ def _train(rank, world, device_kind, batch_ranks):
             assert ex is not None and len(ex.lanes) == 2, "the fused exchange did not run"      # one lane per runtime group
         if ex is not None:
             ex.check()
+            assert ex.staged_serves == (STEPS * 2 if os.environ.get("RECIS_STAGE_EXCHANGE") == "1" else 0)
     return {"outs": outs, "table": table}
 
 
