@@ -135,7 +135,11 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="table rows per rank over all tables (0: from the data)")
     ap.add_argument("--ckpt-dir", default=None)
     ap.add_argument("--comm", default=None, choices=["fused", "nccl"])
+    ap.add_argument("--stage-exchange", action="store_true",
+                    help="fused exchange: issue every table group's id phase and owner side before the first wait (RECIS_STAGE_EXCHANGE=1)")
     args = ap.parse_args()
+    if args.stage_exchange:
+        os.environ["RECIS_STAGE_EXCHANGE"] = "1"
     if args.comm:
         os.environ["RECIS_COMM"] = args.comm
 
@@ -260,7 +264,7 @@ def main():
             "physical_tables": len(tables), "rows_by_width_rank0": sizes, "evicted_rows_rank0": evict.evicted if evict else 0,
             "admit_threshold": args.admit, "ttl_steps": args.ttl, "last_loss": float(loss.detach()),
             "checkpoint": {"save_s": save_s, "load_s": load_s, "bytes": ckpt_bytes, "round_trip_identical": same},
-            "comm": os.environ.get("RECIS_COMM", "auto"),
+            "comm": os.environ.get("RECIS_COMM", "auto"), "staged_exchange": os.environ.get("RECIS_STAGE_EXCHANGE") == "1",
             "timing": "CUDA events around the timed steps, max over ranks" if on_gpu else "host clock (CPU run)",
         }), flush=True)
     if world > 1:

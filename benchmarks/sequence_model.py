@@ -54,7 +54,11 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--comm", default=None, choices=["fused", "nccl"])
+    ap.add_argument("--stage-exchange", action="store_true",
+                    help="fused exchange: issue every table group's id phase and owner side before the first wait (RECIS_STAGE_EXCHANGE=1)")
     args = ap.parse_args()
+    if args.stage_exchange:
+        os.environ["RECIS_STAGE_EXCHANGE"] = "1"
     if args.comm:
         os.environ["RECIS_COMM"] = args.comm
 
