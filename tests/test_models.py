@@ -153,8 +153,8 @@ def test_quickstart_document_runs_as_written(tmp_path, monkeypatch):
 
 
 def test_examples_run_as_two_cpu_ranks(tmp_path):
-    """The examples under torch.distributed.run: two CPU ranks, tables sharded over them; DeepFM once on the collective exchange
-    and once on the shared-memory fused exchange, the ORC example with the files dealt to the ranks."""
+    """The examples under torch.distributed.run: two CPU ranks, tables sharded over them; DeepFM on the shared-memory fused
+    exchange, the ORC example on the collective exchange with the files dealt to the ranks."""
     import socket
 
     def launch(script, *args, env=None):
@@ -167,12 +167,11 @@ def test_examples_run_as_two_cpu_ranks(tmp_path):
         assert out.returncode == 0, out.stderr[-3000:]
         return out.stdout + out.stderr
 
-    log = launch("examples/deepfm/run.py", "--device", "cpu", "--steps", "4", "--batch", "32", "--output-dir", str(tmp_path / "fm"))
+    log = launch("examples/deepfm/run.py", "--device", "cpu", "--steps", "4", "--batch", "32", "--output-dir", str(tmp_path / "fm"),
+                 env={"RECIS_COMM": "fused"})
     assert "x 2 rank(s)" in log
     files = os.listdir(tmp_path / "fm" / "ckpt_4")
     assert sum(f.endswith(".safetensors") for f in files) >= 2 and "index" in files          # both ranks' shards, merged metadata
-    log = launch("examples/deepfm/run.py", "--device", "cpu", "--steps", "4", "--batch", "32", env={"RECIS_COMM": "fused"})
-    assert "x 2 rank(s)" in log
     _run_example("examples/deepctr/make_orc_data.py", "--out", str(tmp_path / "orc"), "--shards", "2", "--rows", "128")
     log = launch("examples/deepctr/run.py", "--data", str(tmp_path / "orc"), "--device", "cpu", "--batch", "32")
     assert "CoalescedHashtable_" in log
