@@ -226,6 +226,12 @@ void init_comm(py::module& m) {
   m.def("comm_wait_timed", [](const Tensor& flags, int64_t channel, int64_t world, int64_t epoch, int64_t spin_limit, Tensor status,
                               Tensor stats) {
     TORCH_CHECK(stats.scalar_type() == torch::kInt64 && stats.numel() >= RB_CH_COUNT * world + RB_CH_COUNT, "stats: int64 [channels * world + channels]");
+    if (!flags.is_cuda()) {
+      py::gil_scoped_release nogil;
+      rbc_comm_wait_timed(flags.data_ptr<int64_t>(), (int)channel, (int)world, epoch, spin_limit, status.data_ptr<int64_t>(),
+                          stats.data_ptr<int64_t>());
+      return;
+    }
     rb_comm_wait_timed(flags.data_ptr<int64_t>(), (int)channel, (int)world, epoch, spin_limit, status.data_ptr<int64_t>(),
                        stats.data_ptr<int64_t>(), cur_stream());
   });

@@ -59,6 +59,26 @@ void rbc_comm_wait(const int64_t* flags, int channel, int world, int64_t epoch, 
   }
 }
 
+// The same wait with accounting (layout of stats as in rb_comm_wait_timed): nanoseconds until each peer's flag arrived, per
+// (channel, peer), and the number of waits per channel.
+void rbc_comm_wait_timed(const int64_t* flags, int channel, int world, int64_t epoch, int64_t limit_us, int64_t* status, int64_t* stats) {
+  const auto t0 = std::chrono::steady_clock::now();
+  bool timed_out = false;
+  for (int p = 0; p < world; ++p) {
+    const int64_t* f = flags + (int64_t)channel * world + p;
+    int64_t spins = 0;
+    while (!timed_out && __atomic_load_n(f, __ATOMIC_ACQUIRE) < epoch) {
+      if ((++spins & 1023) == 0) {
+        if (std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count() > limit_us) timed_out = true;
+        std::this_thread::yield();
+      }
+    }
+    stats[(int64_t)channel * world + p] += std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count();
+  }
+  stats[(int64_t)RB_CH_COUNT * world + channel] += 1;
+  if (timed_out) set_status(status, kStatusWaitTimeout);
+}
+
 void rbc_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, int me, int world, int64_t* ids_in, int64_t in_cap, int32_t* prefix_out,
                        int32_t* n_in_out, int64_t* status) {
   int32_t run = 0;

@@ -89,7 +89,7 @@ class FusedExchange:
         self.owner_unroll = int(os.environ.get("RECIS_OWNER_UNROLL", "2"))
         # RECIS_WAIT_STATS=1: flag waits go through the accounting kernel; wait_stats holds nanoseconds per (channel, peer)
         self.wait_stats = (torch.zeros(N_CH * world + N_CH, dtype=torch.int64, device=self.device)
-                           if os.environ.get("RECIS_WAIT_STATS") == "1" and not self.host else None)
+                           if os.environ.get("RECIS_WAIT_STATS") == "1" else None)
         self._head = None
         # RECIS_STAGE_EXCHANGE=1: the engine may issue the id phase of all of a model's groups before the first wait (prepare())
         self.stage_enabled = os.environ.get("RECIS_STAGE_EXCHANGE") == "1"

@@ -355,6 +355,30 @@ def test_fused_exchange_under_random_skew_between_ranks():
         assert all(torch.allclose(a[k], b[k], atol=1e-6) for k in a)
 
 
+def _wait_stats_fn(rank, world):
+    """RECIS_WAIT_STATS=1: rank 1 arrives 0.3 s late at one step; rank 0's accounted wait on the ids channel shows it."""
+    import time
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption
+    from recis_b200.nn.initializers import NormalInitializer
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name="wait_stats", initializer=NormalInitializer(0, 0.05))})
+    ids = torch.arange(30).view(-1, 1) * 7919 + rank
+    eng({"a": ids})
+    if rank == 1:
+        time.sleep(0.3)
+    eng({"a": ids})
+    (table,) = eng.tables().values()
+    table.fused.check()
+    return table.fused.exposed_wait_ms()
+
+
+def test_wait_accounting_on_cpu_ranks():
+    res = run_ranks(_wait_stats_fn, 2, "gloo", env={"RECIS_COMM": "fused", "RECIS_WAIT_STATS": "1", "RECIS_WAIT_TIMEOUT_S": "60"})
+    assert set(res[0]) >= {"ids", "emb"}
+    assert res[0]["ids"] > 100.0                      # mean over two waits, one of which lasted about 300 ms
+    assert res[1]["ids"] < res[0]["ids"]              # the late rank itself hardly waited
+
+
 def _need_gpus(n):
     if not torch.cuda.is_available() or torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
