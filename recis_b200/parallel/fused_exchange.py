@@ -61,6 +61,7 @@ class _Lane:
         self.n_in = torch.zeros(1, dtype=torch.int32, device=ex.device)
         self.epoch = 0
         self.pending_grad_epoch = 0      # a staged, not yet consumed gradient window
+        self.warned = False
 
 
 class FusedExchange:
@@ -173,6 +174,13 @@ class FusedExchange:
         h = lane.heap
         lane.epoch += 1
         e = lane.epoch
+        if ids.numel() > lane.send_cap and not lane.warned:
+            # the id count bounds the unique count from above: beyond the capacity an overflow becomes possible (not certain)
+            lane.warned = True
+            import warnings
+            warnings.warn(f"fused exchange '{lane_key}': a batch of {ids.numel()} ids meets windows sized for {lane.send_cap} unique ids per "
+                          "rank; if more of them are distinct the step is flagged as an overflow (raise exchange_capacity / "
+                          "RECIS_EXCHANGE_CAPACITY)", RuntimeWarning, stacklevel=3)
         # more unique ids than the window holds sets the overflow bit in self.status (see check()); nothing is written out of bounds
         _uniq, rev, _counts, _offs = C.dedup_partition(ids, self.world, h["ids"].tensor, h["offsets"].tensor, self.status)
         C.comm_signal(h["flags"].ptrs, CH_IDS, self.rank, e, self.host)
