@@ -157,6 +157,10 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    for _tb in engine.tables().values():
+        _ex = getattr(_tb, "fused", None)
+        if _ex is not None:
+            _ex.check()          # a timed-out wait or an overflowing window invalidates the measurement: fail instead of reporting it
     fwd = max_over_ranks(sum(fwd_ms) / len(fwd_ms))
     bwd = max_over_ranks(sum(bwd_ms) / len(bwd_ms))
     # bytes this rank receives in the forward phase (= sends in the backward phase): unique rows owned elsewhere

@@ -222,6 +222,10 @@ def main():
     ms = float(t.item()) / args.steps
 
     tables = model.embedding_engine.tables()
+    for _tb in tables.values():
+        _ex = getattr(_tb, "fused", None)
+        if _ex is not None:
+            _ex.check()          # a timed-out wait or an overflowing window invalidates the measurement: fail instead of reporting it
     sizes = {str(tb.impl.dim): int(tb.impl.size()) for tb in tables.values()}
 
     # ---- sparse checkpoint round trip into a freshly built model

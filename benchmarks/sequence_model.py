@@ -135,6 +135,10 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item()) / args.steps
+    for _tb in model.embedding_engine.tables().values():
+        _ex = getattr(_tb, "fused", None)
+        if _ex is not None:
+            _ex.check()          # a timed-out wait or an overflowing window invalidates the measurement: fail instead of reporting it
     if rank == 0:
         print(json.dumps({
             "bench": "sequence_model", "n_gpus": world, "per_rank_batch": args.batch, "global_batch": args.batch * world,
