@@ -220,6 +220,8 @@ def run(args, arm):
     # ---- C. exposed communication: CUDA-event spans around the exchange phases on the model's stream, a few extra steps
     exposed = arm.exposed_comm_ms(state, host, dev, world, min(5, args.steps)) if hasattr(arm, "exposed_comm_ms") else None
 
+    status_bits = arm.exchange_status(state) if hasattr(arm, "exchange_status") else None
+
     global_batch = spec.batch * world
     value = global_batch * args.steps / (ms / 1e3)
     value_e2e = global_batch * args.steps / (ms_e2e / 1e3)
@@ -246,6 +248,10 @@ def run(args, arm):
         }
         if exposed is not None:
             line["exposed_all_to_all_ms"] = exposed
+        if status_bits is not None:
+            # 0 = every bounded wait was answered and no exchange window overflowed during the whole run (4: a wait ran out,
+            # 8: a window overflowed; either would invalidate the numbers above)
+            line["exchange_status"] = status_bits
         waits = arm.exposed_wait_ms(state) if hasattr(arm, "exposed_wait_ms") else {}
         if waits:
             line["exposed_wait_ms_per_wait"] = waits
@@ -352,6 +358,20 @@ class OursArm:
         if err:
             out["error"] = err
         return out
+
+    def exchange_status(self, st):
+        """OR of the status words of the fused exchanges and the dense all-reduce (one small device read each, after all timing)."""
+        bits = 0
+        try:
+            for table in st["model"].embedding_engine.tables().values():
+                ex = getattr(table, "fused", None)
+                if ex is not None:
+                    bits |= int(ex.status.item())
+            if st["reducer"] is not None and getattr(st["reducer"], "p2p", False):
+                bits |= int(st["reducer"].status.item())
+        except Exception:                # the status read must never take the benchmark line down
+            return -1
+        return bits
 
     def exposed_wait_ms(self, st):
         """RECIS_WAIT_STATS=1 only: mean time per flag wait until its last peer arrived, per channel, over the whole run."""
