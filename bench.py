@@ -249,8 +249,8 @@ def run(args, arm):
         if exposed is not None:
             line["exposed_all_to_all_ms"] = exposed
         if status_bits is not None:
-            # 0 = every bounded wait was answered and no exchange window overflowed during the whole run (4: a wait ran out,
-            # 8: a window overflowed; either would invalidate the numbers above)
+            # largest status word over the ranks; 0 = every bounded wait was answered and no exchange window overflowed during the
+            # whole run (bit 4: a wait ran out, bit 8: a window overflowed; either would invalidate the numbers above)
             line["exchange_status"] = status_bits
         waits = arm.exposed_wait_ms(state) if hasattr(arm, "exposed_wait_ms") else {}
         if waits:
@@ -370,7 +370,13 @@ class OursArm:
             if st["reducer"] is not None and getattr(st["reducer"], "p2p", False):
                 bits |= int(st["reducer"].status.item())
         except Exception:                # the status read must never take the benchmark line down
-            return -1
+            bits = -1
+        import torch
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():      # every rank calls this: the largest value over the ranks is reported
+            t = torch.tensor([bits if bits >= 0 else 1 << 20], dtype=torch.int64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            bits = int(t.item())
         return bits
 
     def exposed_wait_ms(self, st):
