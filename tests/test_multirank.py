@@ -379,6 +379,60 @@ def test_wait_accounting_on_cpu_ranks():
     assert res[1]["ids"] < res[0]["ids"]              # the late rank itself hardly waited
 
 
+def _combiner_fn(rank, world):
+    """tile and weighted-mean combiners, count-based admission and a read-only (eval) lookup; two steps; returns all outputs."""
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.hashtable_hook import AdmitHook
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.optim import SparseSGD
+    from recis_b200.ragged import RaggedTensor
+    torch.manual_seed(31)
+    init = NormalInitializer(0, 0.05)
+    eng = EmbeddingEngine({
+        "seq": EmbeddingOption(embedding_dim=8, shared_name="cmb_seq", combiner="tile", combiner_kwargs={"tile_len": 3}, initializer=init),
+        "wm": EmbeddingOption(embedding_dim=8, shared_name="cmb_wm", combiner="mean", use_weight=True, initializer=init),
+        "adm": EmbeddingOption(embedding_dim=8, shared_name="cmb_adm", combiner="sum", initializer=init,
+                               admit_hook=AdmitHook("CountAdmit", {"threshold": 2})),
+    })
+    opt = SparseSGD(filter_out_sparse_param(eng), lr=0.1)
+    outs = []
+    for step in range(3):
+        g = torch.Generator().manual_seed(7 * step + rank)
+        lens = torch.randint(0, 5, (10,), generator=g)
+        off = torch.zeros(11, dtype=torch.int32); off[1:] = lens.cumsum(0)
+        n = int(off[-1])
+        feats = {"seq": RaggedTensor(torch.randint(0, 50, (n,), generator=g) * 7919, [off]),
+                 "wm": RaggedTensor(torch.randint(0, 50, (n,), generator=g) * 7919, [off], weight=torch.rand(n, generator=g) + 0.1),
+                 # ids of the admission table are disjoint between the ranks: how often an id that SEVERAL ranks ask for in one
+                 # step is counted differs between the two exchanges (once per asking rank on the fused one, once on the other)
+                 "adm": (torch.randint(0, 15, (10, 2), generator=g) * 2 + rank) * 7919}
+        opt.zero_grad()
+        out = eng(feats)
+        sum(v.square().sum() for v in out.values()).backward()
+        opt.step()
+        outs.append({k: v.detach().clone() for k, v in out.items()})
+    eng.eval()
+    with torch.no_grad():
+        probe = eng({"adm": torch.arange(0, 30).view(-1, 1) * 7919})["adm"].clone()      # read-only: never-admitted ids read as zeros
+    for t in eng.tables().values():
+        if t.fused is not None:
+            t.fused.check()
+    return {"outs": outs, "probe": probe, "fused": any(t.fused is not None for t in eng.tables().values())}
+
+
+def test_combiners_and_admission_agree_between_the_fused_and_the_collective_exchange():
+    fused = run_ranks(_combiner_fn, 2, "gloo", env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    coll = run_ranks(_combiner_fn, 2, "gloo", env={"RECIS_COMM": "nccl"})
+    assert all(r["fused"] for r in fused) and not any(r["fused"] for r in coll)
+    for a, b in zip(fused, coll):
+        assert torch.allclose(a["probe"], b["probe"], atol=1e-6)
+        for x, y in zip(a["outs"], b["outs"]):
+            for k in x:
+                assert x[k].shape == y[k].shape and torch.allclose(x[k], y[k], atol=1e-6), k
+    assert float(fused[0]["probe"].abs().sum()) > 0 and bool((fused[0]["probe"].abs().sum(1) == 0).any())   # some admitted, some not
+
+
 def _need_gpus(n):
     if not torch.cuda.is_available() or torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
