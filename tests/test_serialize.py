@@ -325,3 +325,19 @@ print("files", sorted(os.listdir({str(tmp_path)!r})))
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert "raised" in out.stdout, out.stdout + out.stderr
     assert "files []" in out.stdout, out.stdout
+
+
+def test_missing_index_entry_is_reported_by_name(tmp_path):
+    """A block that the tensor-key file lists but the index does not know: the load names it instead of reading another block."""
+    HashtableRegister().clear()
+    eng, _opt = _trained_engine(steps=1)
+    Saver(0, 1, 1, str(tmp_path), filter_out_sparse_param(eng), {}).save()
+    index = json.load(open(tmp_path / "index"))
+    victim = next(k for k in index["block_index"] if k.startswith("user.embedding/"))
+    del index["block_index"][victim]
+    json.dump(index, open(tmp_path / "index", "w"))
+    HashtableRegister().clear()
+    eng2, _ = _trained_engine(steps=0)
+    with pytest.raises((KeyError, RuntimeError, ValueError)) as e:
+        Loader(str(tmp_path), filter_out_sparse_param(eng2), {}).load()
+    assert "user.embedding" in str(e.value)
