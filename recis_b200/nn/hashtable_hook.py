@@ -5,10 +5,8 @@ Same two descriptor classes as the reference (``recis/nn/hashtable_hook.py:52,16
 
 * ``AdmitHook("ReadOnly")``            lookups never insert; unknown ids read as zeros.
 * ``AdmitHook("CountAdmit", {"threshold": n})``  an id gets a row only once it has been seen ``n`` times
-  (an addition: the reference has no count-based admission). A sighting is one lookup of the id on its owning shard: one per
-  step on a single rank and on the collective exchange (the owner dedups what the requesters send), one per step AND asking rank
-  on the fused exchange (the owner looks the incoming ids up as they arrive), so ids that many ranks ask for are admitted
-  earlier there.
+  (an addition: the reference has no count-based admission). A sighting is one step in which the id was asked for, by any
+  number of ranks (the owning shard dedups what the requesters send before it counts, on every exchange path).
 * ``FilterHook("GlobalStepFilter", {"filter_step": n})``  rows not seen for more than ``n`` global steps
   are evicted.
 """

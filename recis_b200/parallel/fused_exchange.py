@@ -190,6 +190,9 @@ class FusedExchange:
         C = native()
         h, me = lane.heap, self.rank
         store = emb_mod.impl.store
+        count_admit = (not readonly) and threshold > 1
+        if count_admit:
+            lane.ids_in.fill_(-1)              # the tail past this step's ids must not hold ids of earlier steps (see below)
         tok = span_open("ids")
         self._wait(h["flags"].tensor, CH_IDS, e)
         C.comm_pull_ids(h["ids"].ptrs, h["offsets"].ptrs, me, lane.ids_in, lane.prefix, lane.n_in, self.status)
@@ -199,6 +202,14 @@ class FusedExchange:
             torch.cuda.current_stream(self.device).wait_event(self._store_event)
         if readonly:
             rows_in = store.find(lane.ids_in, lane.n_in)
+        elif count_admit:
+            # Count-based admission counts ONE sighting per id and step, whoever asks (as a single rank and the collective
+            # exchange do, where the owner dedups first): the incoming ids are deduplicated before the table sees them. The whole
+            # window goes through the dedup (its size is fixed, the valid count lives on the device); the tail is the id -1, which
+            # dedup and table both ignore.
+            o_uniq, o_rev, _c, o_offs = C.dedup_partition(lane.ids_in, 1)
+            o_rows = store.lookup_or_insert(o_uniq, o_offs[1:2], step, threshold)
+            rows_in = o_rows[o_rev.long()].contiguous()
         else:
             rows_in = store.lookup_or_insert(lane.ids_in, lane.n_in, step, threshold)
         if self.multi_stream:

@@ -404,9 +404,8 @@ def _combiner_fn(rank, world):
         n = int(off[-1])
         feats = {"seq": RaggedTensor(torch.randint(0, 50, (n,), generator=g) * 7919, [off]),
                  "wm": RaggedTensor(torch.randint(0, 50, (n,), generator=g) * 7919, [off], weight=torch.rand(n, generator=g) + 0.1),
-                 # ids of the admission table are disjoint between the ranks: how often an id that SEVERAL ranks ask for in one
-                 # step is counted differs between the two exchanges (once per asking rank on the fused one, once on the other)
-                 "adm": (torch.randint(0, 15, (10, 2), generator=g) * 2 + rank) * 7919}
+                 # many of these ids are asked for by both ranks in the same step: one sighting per id and step on either exchange
+                 "adm": torch.randint(0, 30, (10, 2), generator=g) * 7919}
         opt.zero_grad()
         out = eng(feats)
         sum(v.square().sum() for v in out.values()).backward()
