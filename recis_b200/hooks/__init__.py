@@ -1,7 +1,8 @@
-from .filter_hook import HashTableFilterHook
-from .hook import Hook
-from .logger_hook import LoggerHook
-from .profiler_hook import ProfilerHook
-from .table_stats_hook import TableStatsHook
+"""Training-loop hooks: base class, metric logging, profiler traces, table eviction and table statistics."""
+import importlib as _importlib
 
-__all__ = ["Hook", "LoggerHook", "ProfilerHook", "HashTableFilterHook", "TableStatsHook"]
+_WHERE = {"Hook": "hook", "LoggerHook": "logger_hook", "ProfilerHook": "profiler_hook", "HashTableFilterHook": "filter_hook",
+          "TableStatsHook": "table_stats_hook"}
+for _name, _module in _WHERE.items():
+    globals()[_name] = getattr(_importlib.import_module(f"{__name__}.{_module}"), _name)
+__all__ = list(_WHERE)

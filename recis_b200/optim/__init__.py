@@ -1,6 +1,15 @@
-from .adamw_tf import AdamWTF
-from .dense_adam import DenseAdam, DenseAdamW
-from .sparse_optim import SparseAdagrad, SparseAdam, SparseAdamW, SparseAdamWTF, SparseOptimizer, SparseSGD
+"""Optimizers: row-wise sparse optimizers for dynamic tables, and dense Adam variants on one multi-tensor kernel."""
+from . import adamw_tf as _tf
+from . import dense_adam as _dense
+from . import sparse_optim as _sparse
 
-__all__ = ["AdamWTF", "DenseAdam", "DenseAdamW", "SparseAdam", "SparseAdamW", "SparseAdamWTF", "SparseAdagrad", "SparseSGD",
-           "SparseOptimizer"]
+_EXPORTS = {
+    _sparse: ("SparseOptimizer", "SparseAdam", "SparseAdamW", "SparseAdamWTF", "SparseAdagrad", "SparseSGD"),
+    _dense: ("DenseAdam", "DenseAdamW"),
+    _tf: ("AdamWTF",),
+}
+__all__ = []
+for _mod, _names in _EXPORTS.items():
+    for _n in _names:
+        globals()[_n] = getattr(_mod, _n)
+        __all__.append(_n)
