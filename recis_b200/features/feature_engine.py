@@ -1,134 +1,92 @@
-"""FeatureEngine (``recis/features/feature_engine.py:107-284``): features with identical configuration are computed once;
-execution is compiled step-wise (step k = k-th op of every feature) and fusable ops of one kind inside a step run as one
-multi-tensor kernel."""
+"""FeatureEngine: many op chains, few kernel launches.
+
+Behaviour of the reference's engine (``recis/features/feature_engine.py:107-284``): features with an identical configuration are
+computed once and aliased; the k-th ops of all features form step k; inside a step, ops of one fusable kind (Hash, Mod,
+Bucketize, SequenceTruncate, IDMultiHash) are executed by ONE multi-tensor call, the others one by one.
+
+Here the compiled form is a flat *plan*: a list of steps, each a list of ``_Launch`` records ``(kind, callable, feature
+names)``. Running the plan is two nested loops over those records with a plain dict as the working set; nothing else is
+allocated per call.
+"""
 from __future__ import annotations
 
-from collections import defaultdict
-from typing import Dict, List
+from typing import Dict, List, NamedTuple, Sequence
 
 from torch import nn
 
 from .feature import Feature
 from .fused_op_impl import FusedOpFactory
-from .op import _OP
+
+_SINGLE = "single"          # plan kind of ops that have no fused executor
 
 
-class RunContext:
-    def __init__(self, input_data, remain_no_use_data: bool = True):
-        self._data_buffer = {}
-        self._input_data = input_data
-        self._remain_no_use_data = remain_no_use_data
-
-    def get(self, key):
-        return self._data_buffer[key] if key in self._data_buffer else self._input_data
-
-    def set(self, key, value):
-        self._data_buffer[key] = value
-
-    @property
-    def results(self):
-        if self._remain_no_use_data:
-            for k, v in self._input_data.items():
-                self._data_buffer.setdefault(k, v)
-        return self._data_buffer
+class _Launch(NamedTuple):
+    kind: str               # fused kind ("Hash", "Mod", ...) or _SINGLE
+    fn: object              # fused executor over a list of inputs, or the op itself
+    names: tuple            # features whose current value goes in and is replaced by the result
 
 
-class FuseExecutionGroup:
-    def __init__(self, op: _OP):
-        self._feature_names = []
-        self._fused_op = FusedOpFactory.get_fused_op(op)(ops=[])
-
-    def add_op(self, feature_name: str, op: _OP):
-        self._feature_names.append(feature_name)
-        self._fused_op.add_op(op)
-
-    def run(self, data: RunContext):
-        outputs = self._fused_op([data.get(name) for name in self._feature_names])
-        for name, output in zip(self._feature_names, outputs):
-            data.set(name, output)
-        return data
-
-
-class NonFuseExecutionGroup:
-    def __init__(self):
-        self._ops, self._feature_names = [], []
-
-    def add_op(self, feature_name: str, op: _OP):
-        self._ops.append(op)
-        self._feature_names.append(feature_name)
-
-    def run(self, data: RunContext):
-        for op, name in zip(self._ops, self._feature_names):
-            data.set(name, op(data.get(name)))
-        return data
-
-
-class ExecutionStep:
-    _non_fuseable_tag = "_non_fuseable_tag"
-
-    def __init__(self):
-        self.execution_groups = {}
-
-    def add_op(self, feature_name: str, op: _OP):
+def _plan_step(column: Sequence[tuple]) -> List[_Launch]:
+    """``column`` = [(feature name, op)] of one step -> launches: one per fusable kind (in order of first appearance), then the
+    remaining ops one by one."""
+    fused: Dict[str, list] = {}
+    singles: List[_Launch] = []
+    for name, op in column:
         if FusedOpFactory.contains(op):
-            key = type(op).__name__
-            if key not in self.execution_groups:
-                self.execution_groups[key] = FuseExecutionGroup(op)
+            fused.setdefault(type(op).__name__, []).append((name, op))
         else:
-            key = self._non_fuseable_tag
-            if key not in self.execution_groups:
-                self.execution_groups[key] = NonFuseExecutionGroup()
-        self.execution_groups[key].add_op(feature_name, op)
-        return self
-
-    def run(self, data: RunContext):
-        for group in self.execution_groups.values():
-            data = group.run(data)
-        return data
+            singles.append(_Launch(_SINGLE, op, (name,)))
+    launches = []
+    for kind, members in fused.items():
+        executor = FusedOpFactory.get_fused_op(members[0][1])(ops=[])
+        for _name, op in members:
+            executor.add_op(op)
+        launches.append(_Launch(kind, executor, tuple(n for n, _ in members)))
+    return launches + singles
 
 
 class FeatureEngine(nn.Module):
     def __init__(self, feature_list: List[Feature]):
         super().__init__()
         self._features = nn.ModuleDict()
-        self._hash_cache_map = {}
-        by_hash = defaultdict(list)
+        self._alias = {}                        # name of a duplicate feature -> name of the feature that is computed
+        first_with = {}
         for feature in feature_list:
-            by_hash[feature.get_hash()].append(feature)
-        for features in by_hash.values():
-            primary = features[0]
-            if primary.name in self._features:
-                raise ValueError(f"Duplicate feature name: {primary.name}")
-            self._features[primary.name] = primary
-            for dup in features[1:]:
-                self._hash_cache_map[dup.name] = primary.name
-        self.execution_steps = self._compile(list(self._features.values()))
+            key = feature.get_hash()
+            if key in first_with:
+                self._alias[feature.name] = first_with[key]
+                continue
+            if feature.name in self._features:
+                raise ValueError(f"Duplicate feature name: {feature.name}")
+            first_with[key] = feature.name
+            self._features[feature.name] = feature
+        self.plan = self._compile(list(self._features.values()))
 
     @staticmethod
-    def _compile(features: List[Feature]):
+    def _compile(features: List[Feature]) -> List[List[_Launch]]:
         for f in features:
             if f.compiled:
                 raise ValueError(f"feature {f.name} has been compiled")
             f.compiled_(True)
-        steps, k = [], 0
-        while True:
-            step, done = ExecutionStep(), True
-            for f in features:
-                if len(f.ops) > k:
-                    step.add_op(f.name, f.ops[k])
-                    done = False
-            if done:
-                break
-            steps.append(step)
-            k += 1
-        return steps
+        depth = max((len(f.ops) for f in features), default=0)
+        return [_plan_step([(f.name, f.ops[k]) for f in features if len(f.ops) > k]) for k in range(depth)]
 
     def forward(self, data: Dict, remain_no_use_data: bool = True) -> Dict:
+        """``data``: column name -> tensor / RaggedTensor. Returns feature name -> result; with ``remain_no_use_data`` the input
+        columns that no feature overwrote are passed through."""
         assert isinstance(data, dict), "data must be a dict"
-        ctx = RunContext(data, remain_no_use_data)
-        for step in self.execution_steps:
-            ctx = step.run(ctx)
-        results = ctx.results
-        for name, primary in self._hash_cache_map.items():
-            results[name] = results[primary]
-        return results
+        cur: Dict[str, object] = {}
+        for step in self.plan:
+            for launch in step:
+                if launch.kind == _SINGLE:
+                    (name,) = launch.names
+                    cur[name] = launch.fn(cur.get(name, data))      # a chain's first op (SelectField) reads the input dict
+                else:
+                    results = launch.fn([cur.get(name, data) for name in launch.names])
+                    cur.update(zip(launch.names, results))
+        if remain_no_use_data:
+            for column, value in data.items():
+                cur.setdefault(column, value)
+        for duplicate, computed in self._alias.items():
+            cur[duplicate] = cur[computed]
+        return cur

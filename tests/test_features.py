@@ -140,10 +140,11 @@ def test_feature_engine_fuses_and_dedups():
         Feature("cross").add_op(SelectFields([SelectField("item"), SelectField("item")])).add_op(FeatureCross()),
     ]
     fe = FeatureEngine(feats)
-    assert len(fe.execution_steps) == 3
-    # step 1 holds one fused Hash group (both hash features), one fused Bucketize group, one fused Mod group, ...
-    kinds = set(fe.execution_steps[1].execution_groups)
-    assert {"Hash", "Bucketize", "Mod", "IDMultiHash"} <= kinds
+    assert len(fe.plan) == 3
+    # step 1 holds one fused Hash launch (both hash features), one fused Bucketize launch, one fused Mod launch, ...
+    kinds = [launch.kind for launch in fe.plan[1]]
+    assert {"Hash", "Bucketize", "Mod", "IDMultiHash"} <= set(kinds) and kinds.count("Hash") == 1
+    assert next(launch for launch in fe.plan[1] if launch.kind == "Hash").names == ("uid_h", "uid_m")
     out = fe(batch)
     assert out["label"] is batch["label"]
     assert out["price_b"].tolist() == [[0], [1], [2]]
