@@ -62,10 +62,13 @@ class Feature(nn.Module):
         return f
 
     def get_hash(self) -> int:
+        """Identity of the op chain: the ops' own hashes in chain order. The feature's name is not part of it, so two features
+        that run the same chain on the same input are computed once by the engine and the second becomes an alias of the first
+        (the reference mixes the name in, ``recis/features/feature.py:112-125``, which limits this to exact duplicates)."""
         if len(self._ops) == 0:
             return 0
-        combined = f"{self._name}:{sorted(op.get_hash() for op in self._ops)}"
-        return int.from_bytes(hashlib.sha256(combined.encode("utf-8")).digest()[:8], byteorder="big", signed=True)
+        chain = ",".join(str(op.get_hash()) for op in self._ops)
+        return int.from_bytes(hashlib.blake2b(chain.encode(), digest_size=8).digest(), "big", signed=True)
 
     def forward(self, data):
         x = data

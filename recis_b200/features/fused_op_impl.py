@@ -8,7 +8,7 @@ import torch
 
 from .. import native
 from ..ragged.tensor import RaggedTensor
-from .op import Bucketize, DataValueProcessor, Hash, IDMultiHash, Mod, SequenceTruncate
+from .op import Bucketize, Hash, IDMultiHash, Mod, SequenceTruncate, values_of, with_values
 
 
 class _FusedOP:
@@ -28,17 +28,14 @@ class _FusedOP:
 
 class FusedBoundaryOP(_FusedOP):
     def process(self, inputs):
-        procs = [DataValueProcessor(x) for x in inputs]
-        vals = [p.get_input_value() for p in procs]
-        outs = native().fused_bucketize(vals, [op.boundary for op in self._ops])
-        return [p.get_output_value(o) for p, o in zip(procs, outs)]
+        outs = native().fused_bucketize([values_of(x) for x in inputs], [op.boundary for op in self._ops])
+        return [with_values(x, o) for x, o in zip(inputs, outs)]
 
 
 class FusedModOP(_FusedOP):
     def process(self, inputs):
-        procs = [DataValueProcessor(x) for x in inputs]
-        outs = native().fused_mod([p.get_input_value() for p in procs], [op.mod_value for op in self._ops])
-        return [p.get_output_value(o) for p, o in zip(procs, outs)]
+        outs = native().fused_mod([values_of(x) for x in inputs], [op.mod_value for op in self._ops])
+        return [with_values(x, o) for x, o in zip(inputs, outs)]
 
 
 class FusedHashOP(_FusedOP):

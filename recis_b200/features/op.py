@@ -17,36 +17,36 @@ from ..nn.functional.ragged_ops import feature_cross_ragged, fused_ragged_cutoff
 from ..ragged.tensor import RaggedPadInfo, RaggedTensor
 
 
-class DataValueProcessor:
-    """Apply a value-wise function to a dense tensor, a sparse tensor or the values of a RaggedTensor."""
+def values_of(x) -> torch.Tensor:
+    """The flat value tensor of a RaggedTensor, a sparse COO tensor or a dense tensor (what a value-wise op works on)."""
+    if isinstance(x, RaggedTensor):
+        return x.values()
+    if isinstance(x, torch.Tensor):
+        return x._values() if x.is_sparse else x
+    raise ValueError(f"Unsupported data type: {type(x)}")
 
-    def __init__(self, data):
-        self._data = data
 
-    def get_input_value(self):
-        if isinstance(self._data, RaggedTensor):
-            return self._data.values()
-        if isinstance(self._data, torch.Tensor):
-            return self._data._values() if self._data.is_sparse else self._data
-        raise ValueError(f"Unsupported data type: {type(self._data)}")
-
-    def get_output_value(self, result):
-        if isinstance(self._data, RaggedTensor):
-            out = RaggedTensor(result, self._data.offsets(), self._data.weight(), dense_shape=self._data._dense_shape)
-            out.set_pad_info(self._data.pad_info)
-            return out
-        if self._data.is_sparse:
-            return torch.sparse_coo_tensor(indices=self._data._indices(), values=result, size=self._data.shape)
-        return result.reshape(self._data.shape)
+def with_values(x, new_values: torch.Tensor):
+    """``x`` with its values replaced: same offsets / weights / padding record (ragged), same indices (sparse), same shape
+    (dense)."""
+    if isinstance(x, RaggedTensor):
+        out = RaggedTensor(new_values, x.offsets(), x.weight(), dense_shape=x._dense_shape)
+        out.set_pad_info(x.pad_info)
+        return out
+    if x.is_sparse:
+        return torch.sparse_coo_tensor(indices=x._indices(), values=new_values, size=x.shape)
+    return new_values.reshape(x.shape)
 
 
 class _OP(nn.Module):
-    def get_hash(self) -> int:
-        config_str = f"{self.__class__.__name__}:{str(sorted(self._get_config().items()))}"
-        return int.from_bytes(hashlib.sha256(config_str.encode("utf-8")).digest()[:8], byteorder="big", signed=True)
+    """Base of the ops: ``get_hash`` identifies an op by class and configuration, so that equal chains are computed once."""
 
     def _get_config(self) -> Dict:
         raise NotImplementedError
+
+    def get_hash(self) -> int:
+        text = repr((type(self).__name__, sorted(self._get_config().items())))
+        return int.from_bytes(hashlib.blake2b(text.encode(), digest_size=8).digest(), "big", signed=True)
 
 
 class SelectField(_OP):
@@ -88,8 +88,7 @@ class Mod(_OP):
         self.mod_value = int(mod_value)
 
     def forward(self, x):
-        data = DataValueProcessor(x)
-        return data.get_output_value(bucketize_mod(data.get_input_value(), self.mod_value))
+        return with_values(x, bucketize_mod(values_of(x), self.mod_value))
 
     def _get_config(self):
         return {"mod": self.mod_value}
@@ -103,8 +102,7 @@ class Bucketize(_OP):
         self.boundary = torch.tensor(boundary, dtype=torch.float) if isinstance(boundary, (list, tuple)) else boundary.float()
 
     def forward(self, x):
-        data = DataValueProcessor(x)
-        return data.get_output_value(bucketize(data.get_input_value(), self.boundary))
+        return with_values(x, bucketize(values_of(x), self.boundary))
 
     def _get_config(self):
         return {"boundary": self.boundary.tolist()}

@@ -162,3 +162,22 @@ def test_duplicate_features_computed_once():
     b = Feature("x").add_op(SelectField("raw")).add_op(Mod(10))
     fe = FeatureEngine([a, b])
     assert len(fe._features) == 1
+
+
+def test_same_chain_under_two_names_is_computed_once_and_op_order_matters():
+    calls = []
+
+    class Probe(Mod):
+        def forward(self, x):
+            calls.append(1)
+            return super().forward(x)
+
+    a = Feature("a").add_op(SelectField("raw")).add_op(Probe(10))
+    b = Feature("b").add_op(SelectField("raw")).add_op(Probe(10))
+    c = Feature("c").add_op(SelectField("raw")).add_op(Mod(7)).add_op(Mod(5))
+    d = Feature("d").add_op(SelectField("raw")).add_op(Mod(5)).add_op(Mod(7))
+    assert a.get_hash() == b.get_hash() and c.get_hash() != d.get_hash()
+    fe = FeatureEngine([a, b, c, d])
+    out = fe({"raw": torch.arange(40).view(-1, 1)})
+    assert len(calls) == 1 and out["b"] is out["a"]
+    assert torch.equal(out["c"], (torch.arange(40).view(-1, 1) % 7) % 5) and torch.equal(out["d"], (torch.arange(40).view(-1, 1) % 5) % 7)
