@@ -255,7 +255,13 @@ class DynamicEmbedding(torch.nn.Module):
         if self.world_size > 1 and ((emb_opt.device.type == "cuda" and mode in ("auto", "fused")) or
                                     (emb_opt.device.type == "cpu" and mode == "fused")):
             from ...parallel.fused_exchange import FusedExchange
-            self.fused = FusedExchange.create(emb_opt, self.pg, self.world_size, self.rank)
+            from ...parallel.symmetric import single_node
+            if single_node(self.world_size):
+                self.fused = FusedExchange.create(emb_opt, self.pg, self.world_size, self.rank)
+            elif mode == "fused":
+                import warnings
+                warnings.warn("RECIS_COMM=fused needs all ranks on one machine (peer-mapped memory); this job spans machines, "
+                              "the collective exchange is used instead", RuntimeWarning)
             if self.fused is not None:
                 storage = self.fused.table_storage()
                 growable = storage is None

@@ -33,7 +33,8 @@ class DenseGradReducer:
         if p2p is None:
             # CUDA: our all-reduce unless NCCL is asked for. CPU ranks of one machine: only when asked for (RECIS_COMM=fused),
             # over shared memory with the kernels' host twins
-            p2p = world > 1 and world <= native().MAX_PEERS and ((dev.type == "cuda" and mode != "nccl") or (dev.type == "cpu" and mode == "fused"))
+            from .symmetric import single_node
+            p2p = world > 1 and world <= native().MAX_PEERS and single_node(world) and ((dev.type == "cuda" and mode != "nccl") or (dev.type == "cpu" and mode == "fused"))
         self.p2p = p2p
         self.host = dev.type != "cuda"
         self.n = n

@@ -17,6 +17,14 @@ from .. import native
 _DT_SIZE = {torch.int64: 8, torch.int32: 4, torch.float32: 4, torch.uint8: 1, torch.bfloat16: 2}
 
 
+def single_node(world: int) -> bool:
+    """Peer-mapped (or shared) memory needs all ranks on one machine. Launchers export ``LOCAL_WORLD_SIZE``; when it is smaller
+    than the world size the job spans machines and the exchange must use collectives. Without the variable (ranks spawned by
+    hand on one machine) the job is taken to be local."""
+    import os
+    return int(os.environ.get("LOCAL_WORLD_SIZE", world)) >= world
+
+
 class SymmetricRegion:
     def __init__(self, tensor: torch.Tensor, ptrs: List[int]):
         self.tensor = tensor      # this rank's view

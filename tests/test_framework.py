@@ -461,3 +461,11 @@ def test_filter_hook_without_a_model_finds_the_tables_itself():
     del ht, hook
     gc.collect()
     assert "ttl_registry" not in HashtableHookFactory().get_filters()
+
+
+def test_jobs_that_span_machines_do_not_use_peer_memory(monkeypatch):
+    from recis_b200.parallel.symmetric import single_node
+    monkeypatch.delenv("LOCAL_WORLD_SIZE", raising=False)
+    assert single_node(8)                                   # ranks spawned by hand on one machine
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
+    assert single_node(8) and not single_node(16)           # 2 machines x 8 ranks
