@@ -317,7 +317,8 @@ class DynamicEmbedding(torch.nn.Module):
         if self.fused is not None:
             if not self.fused.stage_enabled:
                 return None
-            return dict(ids=ids, fused=self.fused.prepare(self, lane, ids))
+            train = self.training and self.impl.trainable and self._emb_opt.trainable
+            return dict(ids=ids, fused=self.fused.prepare(self, lane, ids, train))
         p = self._begin_collective(ids)
         p["ids"] = ids
         return p

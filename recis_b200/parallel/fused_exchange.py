@@ -62,6 +62,7 @@ class _Lane:
         self.epoch = 0
         self.pending_grad_epoch = 0      # a staged, not yet consumed gradient window
         self.warned = False
+        self.last_train_epoch = 0        # epoch of the newest forward that will be back-propagated
 
 
 class FusedExchange:
@@ -143,7 +144,7 @@ class FusedExchange:
             return self._forward(emb_mod, lane_key, ids, offsets, weights, combiner, tile_len, mode, perm_b, perm_f, train, readonly,
                                  threshold, step, prepared)
 
-    def prepare(self, emb_mod, lane_key, ids):
+    def prepare(self, emb_mod, lane_key, ids, train=True):
         """Requester half of the id phase only (dedup + bucket into the window, signal IDS). A model with several (table, runtime
         group) pairs calls this for all of them before the first ``forward``: every rank's ids are then on offer before anybody
         waits, as the reference issues all of its id all-to-alls before the first wait
@@ -246,6 +247,8 @@ class FusedExchange:
             out, gsrc, gscale = C.pool_forward(uemb, None, rev, offsets, weights, mode, perm_b, perm_f, train)
         saved = dict(rev=rev, gsrc=gsrc, gscale=gscale, rows_in=rows_in, prefix=prefix, epoch=e, lane=lane,
                      offsets=offsets_now) if train else None
+        if train:
+            lane.last_train_epoch = e
         return out, saved
 
     # ------------------------------------------------------------------ backward (requester side) + staging
@@ -256,6 +259,14 @@ class FusedExchange:
     def _backward(self, emb_mod, s, grad_out, worker_scale):
         C = native()
         lane = s["lane"]
+        if s["epoch"] != lane.last_train_epoch:
+            # A newer TRAINING forward of this (table, runtime group) owns the lane's gradient window and flag epochs now: this
+            # older forward's gradients can no longer be exchanged through them (a read-only forward in between is harmless).
+            # Every rank gets here in the same step.
+            raise RuntimeError(
+                "fused exchange: the same feature group of a table was looked up again before the gradients of an earlier lookup "
+                "were back-propagated (two training lookups per step share one set of exchange windows); call the embedding "
+                "engine once per step for these features, or run with RECIS_COMM=nccl")
         h, me, D = lane.heap, self.rank, self.D
         csr_u, csr_elem, start = C.build_csr(s["rev"])
         tok = span_open("grad_push")

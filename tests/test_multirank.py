@@ -432,6 +432,46 @@ def test_combiners_and_admission_agree_between_the_fused_and_the_collective_exch
     assert float(fused[0]["probe"].abs().sum()) > 0 and bool((fused[0]["probe"].abs().sum(1) == 0).any())   # some admitted, some not
 
 
+def _two_lookups_fn(rank, world):
+    """The same feature group is looked up TWICE before the backward (two towers sharing an engine): fine on the collective
+    exchange; the fused exchange, whose windows belong to one lookup per step, must say so instead of mixing gradients up. A
+    read-only lookup between a training forward and its backward is allowed on both."""
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.optim import SparseSGD
+    torch.manual_seed(41)
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name="twice", initializer=NormalInitializer(0, 0.05))})
+    opt = SparseSGD(filter_out_sparse_param(eng), lr=0.1)
+    g = torch.Generator().manual_seed(rank)
+    left, right = (torch.randint(0, 40, (8, 2), generator=g) * 7919 for _ in range(2))
+    # a training forward, a read-only forward of the same group, then the backward of the first: allowed
+    opt.zero_grad()
+    out = eng({"a": left})["a"]
+    eng.eval()
+    with torch.no_grad():
+        eng({"a": right})
+    eng.train()
+    out.square().sum().backward()
+    opt.step()
+    # two training forwards before the backward
+    opt.zero_grad()
+    out = eng({"a": left})["a"] + eng({"a": right})["a"]
+    try:
+        out.square().sum().backward()
+        opt.step()
+        return "ok"
+    except RuntimeError as e:
+        return str(e)
+
+
+def test_two_training_lookups_of_one_group_before_the_backward():
+    coll = run_ranks(_two_lookups_fn, 2, "gloo", env={"RECIS_COMM": "nccl"})
+    assert coll == ["ok", "ok"]
+    fused = run_ranks(_two_lookups_fn, 2, "gloo", env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "30", "RB_NO_FINAL_BARRIER": "1"})
+    assert all("looked up again before the gradients" in r for r in fused), fused
+
+
 def _need_gpus(n):
     if not torch.cuda.is_available() or torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
