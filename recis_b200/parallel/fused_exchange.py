@@ -193,7 +193,10 @@ class FusedExchange:
         store = emb_mod.impl.store
         count_admit = (not readonly) and threshold > 1
         if count_admit:
-            lane.ids_in.fill_(-1)              # the tail past this step's ids must not hold ids of earlier steps (see below)
+            # The tail past this step's ids must not hold ids of earlier steps (see below). It is filled with -2, the table's
+            # tombstone value: the dedup treats it as one ordinary key (one claim, then plain re-reads of one cell), the table
+            # ignores it. (-1, the dedup's own reserved key, would send every tail element through one atomic.)
+            lane.ids_in.fill_(-2)
         tok = span_open("ids")
         self._wait(h["flags"].tensor, CH_IDS, e)
         C.comm_pull_ids(h["ids"].ptrs, h["offsets"].ptrs, me, lane.ids_in, lane.prefix, lane.n_in, self.status)
@@ -206,8 +209,8 @@ class FusedExchange:
         elif count_admit:
             # Count-based admission counts ONE sighting per id and step, whoever asks (as a single rank and the collective
             # exchange do, where the owner dedups first): the incoming ids are deduplicated before the table sees them. The whole
-            # window goes through the dedup (its size is fixed, the valid count lives on the device); the tail is the id -1, which
-            # dedup and table both ignore.
+            # window goes through the dedup (its size is fixed, the valid count lives on the device); the tail is one more "id"
+            # that resolves to no row.
             o_uniq, o_rev, _c, o_offs = C.dedup_partition(lane.ids_in, 1)
             o_rows = store.lookup_or_insert(o_uniq, o_offs[1:2], step, threshold)
             rows_in = o_rows[o_rev.long()].contiguous()
