@@ -29,6 +29,22 @@ NVCC_FLAGS = [
 CXX_FLAGS = ["-O3", "-std=c++17", "-fopenmp", "-Wno-unused-variable", "-Wno-sign-compare"]
 
 
+def _openmp_ldflags():
+    """Link flags for the OpenMP runtime. Some toolchains ship libgomp without its spec file, so ``-fopenmp`` fails at link time;
+    the compiler itself is asked where its libgomp lives instead of assuming a directory."""
+    import shutil
+    import subprocess
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    for name in ("libgomp.so", "libgomp.so.1"):
+        try:
+            path = subprocess.run([cxx, f"-print-file-name={name}"], capture_output=True, text=True, check=True).stdout.strip()
+        except Exception:
+            continue
+        if os.path.isabs(path) and os.path.exists(path):
+            return [os.path.realpath(path)]          # the shared object itself: no search path, no spec file needed
+    return ["-lgomp"]
+
+
 def _sources():
     out = []
     for root, _dirs, files in os.walk(_CSRC):
@@ -84,7 +100,7 @@ def build(verbose: bool = False):
         sources=_sources(),
         extra_cflags=CXX_FLAGS,
         extra_cuda_cflags=NVCC_FLAGS,
-        extra_ldflags=["-L/usr/lib/gcc/x86_64-linux-gnu/13", "-lgomp"],
+        extra_ldflags=_openmp_ldflags(),
         extra_include_paths=[_CSRC],
         build_directory=_BUILD,
         with_cuda=True,

@@ -109,19 +109,25 @@ void comm_wait(const Tensor& flags, int64_t channel, int64_t world, int64_t epoc
   rb_comm_wait(flags.data_ptr<int64_t>(), (int)channel, (int)world, epoch, spin_limit, status.data_ptr<int64_t>(), cur_stream());
 }
 
-void comm_pull_ids(const std::vector<int64_t>& peer_ids, const std::vector<int64_t>& peer_offsets, int64_t me, Tensor ids_in,
-                   Tensor prefix, Tensor n_in, Tensor status) {
+// peer_counts: the requesters' unclamped per-owner unique counts (may be empty); demand: int32[2] running maxima (may be undefined)
+void comm_pull_ids(const std::vector<int64_t>& peer_ids, const std::vector<int64_t>& peer_offsets, const std::vector<int64_t>& peer_counts,
+                   int64_t me, Tensor ids_in, Tensor prefix, Tensor n_in, OptT demand, Tensor status) {
+  const int world = (int)peer_ids.size();
+  TORCH_CHECK(prefix.numel() >= 3 * world + 1 && prefix.scalar_type() == torch::kInt32, "prefix: int32 [3 * world + 1]");
+  RbPeers counts = peers_of(peer_counts);
+  int32_t* dm = demand.has_value() && demand->defined() ? demand->data_ptr<int32_t>() : nullptr;
   if (!ids_in.is_cuda()) {
-    rbc_comm_pull_ids(peers_of(peer_ids), peers_of(peer_offsets), (int)me, (int)peer_ids.size(), ids_in.data_ptr<int64_t>(), ids_in.numel(),
-                      prefix.data_ptr<int32_t>(), n_in.data_ptr<int32_t>(), status.data_ptr<int64_t>());
+    rbc_comm_pull_ids(peers_of(peer_ids), peers_of(peer_offsets), counts, (int)me, world, ids_in.data_ptr<int64_t>(), ids_in.numel(),
+                      prefix.data_ptr<int32_t>(), n_in.data_ptr<int32_t>(), dm, status.data_ptr<int64_t>());
     return;
   }
-  rb_comm_pull_ids(peers_of(peer_ids), peers_of(peer_offsets), (int)me, (int)peer_ids.size(), ids_in.data_ptr<int64_t>(), ids_in.numel(),
-                   prefix.data_ptr<int32_t>(), n_in.data_ptr<int32_t>(), status.data_ptr<int64_t>(), cur_stream());
+  c10::cuda::CUDAGuard g(ids_in.device());
+  rb_comm_pull_ids(peers_of(peer_ids), peers_of(peer_offsets), counts, (int)me, world, ids_in.data_ptr<int64_t>(), ids_in.numel(),
+                   prefix.data_ptr<int32_t>(), n_in.data_ptr<int32_t>(), dm, status.data_ptr<int64_t>(), cur_stream());
 }
 
 void comm_push_emb(const Tensor& emb, const Tensor& rows_in, const Tensor& prefix, const std::vector<int64_t>& peer_uemb, int64_t me,
-                   int64_t n_in_hint) {
+                   int64_t n_in_hint, int64_t blocks) {
   const int D = (int)emb.size(1);
   if (!emb.is_cuda()) {
     rbc_comm_push_emb(emb.data_ptr<float>(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), peers_of(peer_uemb), (int)me,
@@ -129,8 +135,9 @@ void comm_push_emb(const Tensor& emb, const Tensor& rows_in, const Tensor& prefi
     return;
   }
   TORCH_CHECK(D % 4 == 0, "the fused exchange needs an embedding width that is a multiple of 4");
+  c10::cuda::CUDAGuard g(emb.device());
   rb_comm_push_emb(emb.data_ptr<float>(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), peers_of(peer_uemb), (int)me,
-                   (int)peer_uemb.size(), D, n_in_hint, cur_stream());
+                   (int)peer_uemb.size(), D, n_in_hint, (int)blocks, cur_stream());
 }
 
 // apply: update rows of (w, s1, s2) in place. Otherwise returns (rows [n_in_max] with -1 holes, grads [n_in_max, D]).
@@ -170,7 +177,7 @@ std::tuple<Tensor, Tensor> comm_owner_reduce(const Tensor& rows_in, Tensor head,
 // [world+1]; meta = the tensor written by comm_pull_ids (the destination bases sit at meta[2*world+1 ..]).
 void comm_grad_reduce_push(const Tensor& grad_out, const Tensor& gsrc, const Tensor& gscale, const Tensor& csr_u, const Tensor& csr_elem,
                            const Tensor& start, int64_t D, const Tensor& offsets, const Tensor& meta,
-                           const std::vector<int64_t>& peer_gin, int64_t cap_rows) {
+                           const std::vector<int64_t>& peer_gin, int64_t cap_rows, int64_t max_blocks) {
   if (!grad_out.is_cuda()) {
     // host twin: per-unique gradients first (the CPU reduction), then one row copy per unique id into its owner's window
     TORCH_CHECK(grad_out.is_contiguous() && grad_out.scalar_type() == torch::kFloat32, "grad_out must be contiguous fp32");
@@ -203,7 +210,7 @@ void comm_grad_reduce_push(const Tensor& grad_out, const Tensor& gsrc, const Ten
   const int64_t n_chunks = (n + rb_grad_reduce_chunk() - 1) / rb_grad_reduce_chunk();
   auto span = torch::zeros({n_chunks, D}, grad_out.options());
   rb_grad_reduce_push(grad_out.data_ptr<float>(), gsrc.data_ptr<int32_t>(), gscale.data_ptr<float>(), csr_u.data_ptr<int32_t>(),
-                      csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>(), n, (int)D, span.data_ptr<float>(), push, cur_stream());
+                      csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>(), n, (int)D, span.data_ptr<float>(), push, (int)max_blocks, cur_stream());
 }
 
 void comm_allreduce_slice(const std::vector<int64_t>& bufs, int64_t me, int64_t n_padded, double scale, bool host) {
@@ -236,10 +243,14 @@ void init_comm(py::module& m) {
                        stats.data_ptr<int64_t>(), cur_stream());
   });
   m.attr("N_CHANNELS") = (int)RB_CH_COUNT;
-  m.def("comm_pull_ids", &comm_pull_ids);
-  m.def("comm_push_emb", &comm_push_emb);
+  m.def("comm_pull_ids", &comm_pull_ids, py::arg("peer_ids"), py::arg("peer_offsets"), py::arg("peer_counts"), py::arg("me"),
+        py::arg("ids_in"), py::arg("prefix"), py::arg("n_in"), py::arg("demand"), py::arg("status"));
+  m.def("comm_push_emb", &comm_push_emb, py::arg("emb"), py::arg("rows_in"), py::arg("prefix"), py::arg("peer_uemb"), py::arg("me"),
+        py::arg("n_in_hint"), py::arg("blocks") = 0);
   m.def("comm_owner_reduce", &comm_owner_reduce);
-  m.def("comm_grad_reduce_push", &comm_grad_reduce_push);
+  m.def("comm_grad_reduce_push", &comm_grad_reduce_push, py::arg("grad_out"), py::arg("gsrc"), py::arg("gscale"), py::arg("csr_u"),
+        py::arg("csr_elem"), py::arg("start"), py::arg("D"), py::arg("offsets"), py::arg("meta"), py::arg("peer_gin"), py::arg("cap_rows"),
+        py::arg("max_blocks") = 0);
   m.def("comm_allreduce_slice", &comm_allreduce_slice, py::arg("bufs"), py::arg("me"), py::arg("n_padded"), py::arg("scale"),
         py::arg("host") = false);
   m.def("comm_copy", [](int64_t dst, int64_t src, int64_t nbytes, int64_t blocks) {

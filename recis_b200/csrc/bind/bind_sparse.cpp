@@ -23,7 +23,7 @@ int64_t pow2_at_least(int64_t x) { int64_t p = 64; while (p < x) p <<= 1; return
 // ids -> (unique ids bucketed by owner rank, reverse index, per-owner counts, per-owner offsets)
 // unique_out / offsets_out (optional) let the caller place the results in peer-visible memory.
 std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, int64_t world, OptT unique_out, OptT offsets_out,
-                                                           OptT status) {
+                                                           OptT status, OptT counts_out) {
   TORCH_CHECK(ids.scalar_type() == torch::kInt64 && ids.is_contiguous(), "ids: contiguous int64 expected");
   TORCH_CHECK(world >= 1 && world <= 1024, "world size out of range");
   const int64_t n = ids.numel();
@@ -32,7 +32,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, in
   auto set_keys = torch::empty({cap}, o);
   auto set_pos = torch::empty({cap + 1}, o.dtype(torch::kInt32));
   auto slot = torch::empty({std::max<int64_t>(n, 1)}, o.dtype(torch::kInt32));
-  auto counts = torch::empty({world}, o.dtype(torch::kInt32));
+  Tensor counts = counts_out.has_value() && counts_out->defined() ? *counts_out : torch::empty({world}, o.dtype(torch::kInt32));
+  TORCH_CHECK(counts.numel() >= world && counts.scalar_type() == torch::kInt32, "dedup_partition: counts_out: int32 [world]");
   Tensor offsets = offsets_out.has_value() && offsets_out->defined() ? *offsets_out : torch::empty({world + 1}, o.dtype(torch::kInt32));
   Tensor unique_ids = unique_out.has_value() && unique_out->defined() ? *unique_out : torch::empty({n}, o);
   const bool guarded = status.has_value() && status->defined();   // a smaller unique buffer needs the status word
@@ -108,14 +109,29 @@ void fill_rows_i64(Tensor dst, const Tensor& rows, int64_t value) {
   }
 }
 
-// Pooling forward. Returns (out, gsrc, gscale); gsrc/gscale are empty tensors unless need_grad.
+// Pooling forward. Returns (out, gsrc, gscale); gsrc/gscale are empty tensors unless need_grad. With `out` given (a
+// [batch * perm_total, D] tensor shared by several calls) the call fills features perm_off .. perm_off + perm_f - 1 of it.
 std::tuple<Tensor, Tensor, Tensor> pool_forward(const Tensor& base, OptT rows, const Tensor& rev, const Tensor& offsets, OptT weights,
-                                                int64_t mode, int64_t perm_b, int64_t perm_f, bool need_grad) {
+                                                int64_t mode, int64_t perm_b, int64_t perm_f, bool need_grad, OptT out_opt,
+                                                int64_t perm_off, int64_t perm_total) {
   TORCH_CHECK(base.dim() == 2 && base.is_contiguous() && base.scalar_type() == torch::kFloat32);
   TORCH_CHECK(rev.scalar_type() == torch::kInt32 && offsets.scalar_type() == torch::kInt32);
   const int64_t n_seg = offsets.numel() - 1, n = rev.numel(); const int D = (int)base.size(1);
   if (perm_f > 0) TORCH_CHECK(perm_b * perm_f == n_seg, "permuted pooling output needs n_seg == batch * features");
-  auto out = torch::empty({n_seg, D}, base.options());
+  Tensor out;
+  if (out_opt.has_value() && out_opt->defined()) {
+    out = *out_opt;
+    TORCH_CHECK(out.is_contiguous() && out.scalar_type() == torch::kFloat32 && out.device() == base.device() && perm_off >= 0,
+                "pool_forward: out must be contiguous fp32 on the same device");
+    if (perm_f > 0) {
+      TORCH_CHECK(perm_total >= perm_off + perm_f && out.numel() == perm_b * perm_total * D, "pool_forward: out must be [batch * perm_total, D]");
+    } else {
+      TORCH_CHECK(out.numel() >= (perm_off + n_seg) * D, "pool_forward: out is too small for rows perm_off .. perm_off + n_seg");
+    }
+  } else {
+    perm_off = 0; perm_total = perm_f;
+    out = torch::empty({n_seg, D}, base.options());
+  }
   Tensor gsrc, gscale;
   if (need_grad) {
     gsrc = torch::empty({n}, rev.options());
@@ -126,10 +142,10 @@ std::tuple<Tensor, Tensor, Tensor> pool_forward(const Tensor& base, OptT rows, c
   if (base.is_cuda()) {
     c10::cuda::CUDAGuard g(base.device());
     rb_pool_forward(base.data_ptr<float>(), opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg, D,
-                    (int)mode, (int)perm_b, (int)perm_f, out.data_ptr<float>(), gp, gs, cur_stream());
+                    (int)mode, (int)perm_b, (int)perm_f, (int)perm_off, (int)perm_total, out.data_ptr<float>(), gp, gs, cur_stream());
   } else {
     rbc_pool_forward(base.data_ptr<float>(), opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg,
-                     D, (int)mode, (int)perm_b, (int)perm_f, out.data_ptr<float>(), gp, gs);
+                     D, (int)mode, (int)perm_b, (int)perm_f, (int)perm_off, (int)perm_total, out.data_ptr<float>(), gp, gs);
   }
   return {out, gsrc, gscale};
 }
@@ -264,12 +280,14 @@ void init_sparse(py::module& m) {
       .def("set_name", &EmbeddingStore::set_name);
 
   m.def("dedup_partition", &dedup_partition, py::arg("ids"), py::arg("world"), py::arg("unique_out") = py::none(),
-        py::arg("offsets_out") = py::none(), py::arg("status") = py::none());
+        py::arg("offsets_out") = py::none(), py::arg("status") = py::none(), py::arg("counts_out") = py::none());
   m.def("encode_merge", &encode_merge);
   m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("rows"), py::arg("n_dev") = py::none());
   m.def("scatter_rows", &scatter_rows);
   m.def("fill_rows_i64", &fill_rows_i64);
-  m.def("pool_forward", &pool_forward);
+  m.def("pool_forward", &pool_forward, py::arg("base"), py::arg("rows"), py::arg("rev"), py::arg("offsets"), py::arg("weights"),
+        py::arg("mode"), py::arg("perm_b"), py::arg("perm_f"), py::arg("need_grad"), py::arg("out") = py::none(),
+        py::arg("perm_off") = 0, py::arg("perm_total") = 0);
   m.def("tile_forward", &tile_forward);
   m.def("build_csr", &build_csr);
   m.def("grad_reduce", &grad_reduce, py::arg("grad_out"), py::arg("gsrc"), py::arg("gscale"), py::arg("csr_u"), py::arg("csr_elem"), py::arg("start"),

@@ -79,17 +79,19 @@ void rbc_comm_wait_timed(const int64_t* flags, int channel, int world, int64_t e
   if (timed_out) set_status(status, kStatusWaitTimeout);
 }
 
-void rbc_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, int me, int world, int64_t* ids_in, int64_t in_cap, int32_t* prefix_out,
-                       int32_t* n_in_out, int64_t* status) {
-  int32_t run = 0;
+void rbc_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_counts, int me, int world, int64_t* ids_in, int64_t in_cap,
+                       int32_t* prefix_out, int32_t* n_in_out, int32_t* demand, int64_t* status) {
+  // everything published in prefix_out is clamped to in_cap (see pull_ids_kernel): an overflow drops ids, nothing downstream
+  // indexes past a buffer
+  int64_t run = 0;
   for (int r = 0; r < world; ++r) {
     const int32_t* off = reinterpret_cast<const int32_t*>(peer_offsets.p[r]);
     const int32_t b = off[me], e = off[me + 1];
-    prefix_out[r] = run;
+    prefix_out[r] = (int32_t)std::min<int64_t>(run, in_cap);
     prefix_out[world + 1 + r] = b;
     run += e - b;
   }
-  prefix_out[world] = run;
+  prefix_out[world] = (int32_t)std::min<int64_t>(run, in_cap);
   if (run > in_cap) set_status(status, kStatusWindowOverflow);
   for (int o = 0; o < world; ++o) {          // where this rank's bucket for owner o starts inside o's incoming order
     int32_t base = 0;
@@ -99,12 +101,21 @@ void rbc_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, int me, int world
     }
     prefix_out[2 * world + 1 + o] = base;
   }
-  const int64_t n_in = run < in_cap ? run : in_cap;
+  const int64_t n_in = prefix_out[world];
   *n_in_out = (int32_t)n_in;
+  if (demand != nullptr && peer_counts.p[0] != nullptr) {
+    for (int t = 0; t < world; ++t) {
+      int64_t out_t = 0, in_t = 0;
+      for (int o = 0; o < world; ++o) out_t += reinterpret_cast<const int32_t*>(peer_counts.p[t])[o];
+      for (int r = 0; r < world; ++r) in_t += reinterpret_cast<const int32_t*>(peer_counts.p[r])[t];
+      demand[0] = std::max<int32_t>(demand[0], (int32_t)std::min<int64_t>(out_t, 0x7FFFFFFF));
+      demand[1] = std::max<int32_t>(demand[1], (int32_t)std::min<int64_t>(in_t, 0x7FFFFFFF));
+    }
+  }
   for (int r = 0; r < world; ++r) {
     const int64_t* src = reinterpret_cast<const int64_t*>(peer_ids.p[r]) + prefix_out[world + 1 + r];
     const int64_t beg = prefix_out[r];
-    const int64_t cnt = std::max<int64_t>(std::min<int64_t>(prefix_out[r + 1], n_in) - beg, 0);
+    const int64_t cnt = (int64_t)prefix_out[r + 1] - beg;
     if (cnt > 0) std::memcpy(ids_in + beg, src, sizeof(int64_t) * (size_t)cnt);
   }
 }

@@ -44,10 +44,10 @@ inline void cpu_opt_update(const RbOpt& o, int64_t off, float g) {
   }
   o.w[off] = w;
 }
-inline int64_t out_row_of(int64_t s, int perm_b, int perm_f) {
-  if (perm_f <= 0) return s;
+inline int64_t out_row_of(int64_t s, int perm_b, int perm_f, int perm_off, int perm_total) {
+  if (perm_f <= 0) return s + perm_off;
   const int64_t f = s / perm_b, b = s - f * perm_b;
-  return b * perm_f + f;
+  return b * perm_total + perm_off + f;
 }
 }  // namespace
 
@@ -261,11 +261,13 @@ void rbc_fill_rows_i64(int64_t* dst, const int32_t* rows, int64_t n, int64_t val
 }
 
 void rbc_pool_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
-                      int64_t n_seg, int D, int mode, int perm_b, int perm_f, float* out, int32_t* gsrc, float* gscale) {
+                      int64_t n_seg, int D, int mode, int perm_b, int perm_f, int perm_off, int perm_total, float* out, int32_t* gsrc,
+                      float* gscale) {
+  if (perm_f > 0 && perm_total <= 0) { perm_total = perm_f; perm_off = 0; }
 #pragma omp parallel for schedule(static)
   for (int64_t s = 0; s < n_seg; ++s) {
     const int32_t beg = offsets[s], end = offsets[s + 1];
-    const int64_t orow = out_row_of(s, perm_b, perm_f);
+    const int64_t orow = out_row_of(s, perm_b, perm_f, perm_off, perm_total);
     float* o = out + orow * D;
     std::memset(o, 0, sizeof(float) * D);
     float wsum = 0.f;

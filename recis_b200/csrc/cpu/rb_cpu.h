@@ -23,7 +23,8 @@ void rbc_gather_rows(const float* src, const int32_t* rows, int64_t n_max, const
 void rbc_scatter_rows(float* dst, const int32_t* rows, int64_t n, int D, const float* src, int src_broadcast);
 void rbc_fill_rows_i64(int64_t* dst, const int32_t* rows, int64_t n, int64_t value);
 void rbc_pool_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
-                      int64_t n_seg, int D, int mode, int perm_b, int perm_f, float* out, int32_t* gsrc, float* gscale);
+                      int64_t n_seg, int D, int mode, int perm_b, int perm_f, int perm_off, int perm_total, float* out, int32_t* gsrc,
+                      float* gscale);
 void rbc_tile_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
                       int64_t n_seg, int D, int tile_len, float* out, int32_t* gsrc, float* gscale);
 void rbc_build_csr(const int32_t* reverse, int64_t n, int32_t* csr_u, int32_t* csr_elem, int32_t* start);

@@ -13,8 +13,8 @@ extern "C" {
 void rbc_comm_signal(RbPeers flag_pads, int channel, int me, int world, int64_t epoch);
 void rbc_comm_wait(const int64_t* flags, int channel, int world, int64_t epoch, int64_t limit_us, int64_t* status);
 void rbc_comm_wait_timed(const int64_t* flags, int channel, int world, int64_t epoch, int64_t limit_us, int64_t* status, int64_t* stats);
-void rbc_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, int me, int world, int64_t* ids_in, int64_t in_cap, int32_t* prefix_out,
-                       int32_t* n_in_out, int64_t* status);
+void rbc_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_counts, int me, int world, int64_t* ids_in, int64_t in_cap,
+                       int32_t* prefix_out, int32_t* n_in_out, int32_t* demand, int64_t* status);
 void rbc_comm_push_emb(const float* emb, const int32_t* rows_in, const int32_t* prefix, RbPeers peer_uemb, int me, int world, int D,
                        int64_t in_cap);
 // gu: [n_unique, D] per-unique gradients in this rank's bucketed order; off / dst_base as in RbGuPush

@@ -11,9 +11,10 @@
 //                        push the embedding row of every incoming id straight into the requester's
 //                        unique-embedding buffer (peer stores)                       -> signal(EMB)
 //             requester: wait(EMB), pool from its local unique-embedding buffer
-//   backward  requester: reduce pooled gradients to one gradient per unique id       -> signal(GRAD)
-//             owner:     wait(GRAD), for every touched row: pull its gradient from each requester (peer loads), add
-//                        duplicates across requesters, apply the row-wise optimizer   (one kernel)
+//   backward  requester: reduce pooled gradients to one gradient per unique id and store each of them straight into
+//                        the gradient window of the rank that owns the id (peer stores)  -> signal(GRAD)
+//             owner:     wait(GRAD), for every touched row: add the contributions of all requesters (they sit in this
+//                        rank's own window: local loads only), apply the row-wise optimizer   (one kernel)
 //   dense     two-shot all-reduce: each rank reduces 1/W of the flat gradient buffer from all peers and writes the
 //             averaged slice back to all peers.
 //
@@ -116,25 +117,31 @@ __device__ __forceinline__ int find_src(const int32_t* prefix, int world, int64_
   return r;
 }
 
-// Owner: gather the ids every requester bucketed for me. peer_offsets[r] -> int32[world+1] of requester r,
-// peer_ids[r] -> its bucketed unique ids. Writes ids_in, prefix[world+1] and n_in.
+// Owner: gather the ids every requester bucketed for me. peer_offsets[r] -> int32[world+1] of requester r (boundaries
+// clamped to its window), peer_ids[r] -> its bucketed unique ids, peer_counts[r] -> int32[world] unclamped per-owner unique
+// counts of requester r (what it wanted to send). Writes ids_in, prefix[3*world+1] and n_in. Everything published in prefix is
+// clamped to in_cap: a window that is too small drops ids (and sets the overflow bit), it never makes a later kernel index
+// past a buffer. demand[0..1] (nullable) keep running maxima over ALL ranks of (unique ids one requester wanted to send,
+// ids one owner was asked for): every rank computes the same two numbers from the same W x W counts, which is what lets the
+// hosts agree on growing the windows without a collective.
 __global__ void __launch_bounds__(kThreads)
-pull_ids_kernel(RbPeers peer_ids, RbPeers peer_offsets, int me, int world, int64_t* __restrict__ ids_in, int64_t in_cap,
-                int32_t* __restrict__ prefix_out, int32_t* __restrict__ n_in_dev, int64_t* status) {
+pull_ids_kernel(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_counts, int me, int world, int64_t* __restrict__ ids_in,
+                int64_t in_cap, int32_t* __restrict__ prefix_out, int32_t* __restrict__ n_in_dev, int32_t* __restrict__ demand,
+                int64_t* status) {
   __shared__ int32_t prefix[RB_MAX_PEERS + 1];
   __shared__ int32_t src_off[RB_MAX_PEERS];
   if (threadIdx.x == 0) {
-    int32_t run = 0;
+    int64_t run = 0;
     for (int r = 0; r < world; ++r) {
       const int32_t* off = reinterpret_cast<const int32_t*>(peer_offsets.p[r]);
       const int32_t b = off[me], e = off[me + 1];
-      prefix[r] = run; src_off[r] = b; run += (e - b);
+      prefix[r] = (int32_t)min(run, in_cap); src_off[r] = b; run += (e - b);
     }
-    prefix[world] = run;
+    prefix[world] = (int32_t)min(run, in_cap);
     if (run > in_cap) set_status(status, kStatusWindowOverflow);
   }
   __syncthreads();
-  const int64_t n_in = min((int64_t)prefix[world], in_cap);
+  const int64_t n_in = prefix[world];
   if (blockIdx.x == 0) {
     // prefix_out = [prefix[0..world], src_off[0..world-1]]: kept by the owner for the rest of the step, because the
     // requesters' offset windows are rewritten by their next forward pass.
@@ -151,6 +158,15 @@ pull_ids_kernel(RbPeers peer_ids, RbPeers peer_offsets, int me, int world, int64
       prefix_out[2 * world + 1 + o] = base;
     }
     if (threadIdx.x == 0) *n_in_dev = (int32_t)n_in;
+    if (demand != nullptr && peer_counts.p[0] != nullptr && threadIdx.x < world) {
+      // thread t: what requester t wanted to send in total, and what owner t was asked for in total
+      int64_t out_t = 0, in_t = 0;
+      const int32_t* mine = reinterpret_cast<const int32_t*>(peer_counts.p[threadIdx.x]);
+      for (int o = 0; o < world; ++o) out_t += mine[o];
+      for (int r = 0; r < world; ++r) in_t += reinterpret_cast<const int32_t*>(peer_counts.p[r])[threadIdx.x];
+      atomicMax(&demand[0], (int32_t)min(out_t, (int64_t)0x7FFFFFFF));
+      atomicMax(&demand[1], (int32_t)min(in_t, (int64_t)0x7FFFFFFF));
+    }
   }
   for (int64_t j = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; j < n_in; j += (int64_t)gridDim.x * blockDim.x) {
     const int r = find_src(prefix, world, j);
@@ -390,16 +406,20 @@ void rb_comm_wait(const int64_t* flags, int channel, int world, int64_t epoch, i
   rb::note_launch();
 }
 
-void rb_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, int me, int world, int64_t* ids_in, int64_t in_cap, int32_t* prefix_out,
-                      int32_t* n_in_dev, int64_t* status, cudaStream_t st) {
-  pull_ids_kernel<<<grid_stride_blocks(in_cap / 4 + 1), kThreads, 0, st>>>(peer_ids, peer_offsets, me, world, ids_in, in_cap, prefix_out,
-                                                                        n_in_dev, status);
+void rb_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_counts, int me, int world, int64_t* ids_in, int64_t in_cap,
+                      int32_t* prefix_out, int32_t* n_in_dev, int32_t* demand, int64_t* status, cudaStream_t st) {
+  pull_ids_kernel<<<grid_stride_blocks(in_cap / 4 + 1), kThreads, 0, st>>>(peer_ids, peer_offsets, peer_counts, me, world, ids_in, in_cap,
+                                                                        prefix_out, n_in_dev, demand, status);
   rb::note_launch();
 }
 
 void rb_comm_push_emb(const float* emb, const int32_t* rows_in, const int32_t* prefix, RbPeers peer_uemb, int me, int world, int D,
-                      int64_t n_in_max, cudaStream_t st) {
-  push_emb_kernel<<<grid_stride_blocks(n_in_max * (D / 4)), kThreads, 0, st>>>(emb, rows_in, prefix, peer_uemb, me, world, D);
+                      int64_t n_in_max, int blocks, cudaStream_t st) {
+  // blocks > 0 caps the grid: the kernel is bound by NVLink, not by the SMs, and a small grid leaves the SMs to kernels of
+  // other streams that run at the same time
+  int g = grid_stride_blocks(n_in_max * (D / 4));
+  if (blocks > 0 && blocks < g) g = blocks;
+  push_emb_kernel<<<g, kThreads, 0, st>>>(emb, rows_in, prefix, peer_uemb, me, world, D);
   rb::note_launch();
 }
 

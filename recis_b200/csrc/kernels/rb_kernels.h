@@ -88,11 +88,13 @@ void rb_gather_rows(const float* src, const int32_t* rows, int64_t n_max, const 
 void rb_scatter_rows(float* dst, const int32_t* rows, int64_t n, int D, const float* src, int src_broadcast, cudaStream_t st);
 void rb_fill_rows_i64(int64_t* dst, const int32_t* rows, int64_t n, int64_t value, cudaStream_t st);
 // Pooling: out[orow(s)] = sum_i scale_i * base[row_i]; row_i = rows ? rows[rev[i]] : rev[i].
-// mode 0 sum, 1 mean over length, 2 mean over weight sum. perm_f > 0 writes segment s=(f*perm_b+b) to row b*perm_f+f.
+// mode 0 sum, 1 mean over length, 2 mean over weight sum. perm_f > 0 writes segment s=(f*perm_b+b) to row
+// b*perm_total + perm_off + f (perm_total <= 0 means perm_total = perm_f, perm_off = 0): several calls can fill disjoint
+// feature ranges of one [batch, perm_total, D] output. perm_f <= 0: segment s goes to row perm_off + s.
 // gsrc/gscale (nullable) record, per element, the output row and the scale for the backward pass.
 void rb_pool_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
-                     int64_t n_seg, int D, int mode, int perm_b, int perm_f, float* out, int32_t* gsrc, float* gscale,
-                     cudaStream_t st);
+                     int64_t n_seg, int D, int mode, int perm_b, int perm_f, int perm_off, int perm_total, float* out, int32_t* gsrc,
+                     float* gscale, cudaStream_t st);
 // Tile combiner: out[s, t*D:(t+1)*D] = base[row of element t of segment s], t < tile_len, zero padded.
 void rb_tile_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
                      int64_t n_seg, int D, int tile_len, float* out, int32_t* gsrc, float* gscale, cudaStream_t st);
@@ -108,7 +110,7 @@ void rb_grad_reduce(const float* grad_out, const int32_t* gsrc, const float* gsc
                     float* gu, int apply, RbOpt opt, cudaStream_t st);
 // Same reduction with apply == 0 semantics, the result rows stored through `push` (float4 rows only: D % 4 == 0, D <= 512).
 void rb_grad_reduce_push(const float* grad_out, const int32_t* gsrc, const float* gscale, const int32_t* csr_u, const int32_t* csr_elem,
-                         const int32_t* start, int64_t n, int D, float* span_acc, RbGuPush push, cudaStream_t st);
+                         const int32_t* start, int64_t n, int D, float* span_acc, RbGuPush push, int max_blocks, cudaStream_t st);
 int rb_grad_reduce_chunk();
 void rb_sparse_apply(const int32_t* rows, const float* grads, int64_t n_max, const int32_t* n_dev, int D, RbOpt opt, cudaStream_t st);
 

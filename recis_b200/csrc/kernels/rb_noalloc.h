@@ -19,11 +19,13 @@
 //     on `stream` and returns without synchronising.
 //   * The first call on a device looks up the device address of the built-in scratch array (cudaGetSymbolAddress, with that
 //     device current). Make that first call outside of any stream capture; later calls only reuse the cached address.
+//     The cache is keyed by the device ordinal and assumes that the device's primary context lives as long as the process:
+//     after a cudaDeviceReset the cached address is stale and this entry point must not be used again in that process.
 //   * Every call uses the same scratch array, which still holds the previous call's contents on entry; the function resets
 //     what has to start empty. Two calls that can overlap on the GPU (different streams, or different host threads without
 //     ordering between their streams) race on that array: keep calls on one stream or order them with events.
 // Return value: 0 on success; 1 bad arguments, 2 n above the limit, 3 no usable current device, 4 symbol lookup failed,
-// 5/6 CUDA launch errors. `err` (optional, `err_len` bytes) receives a human-readable message on failure.
+// 5 a memset could not be enqueued, 6 a kernel launch failed. `err` (optional, `err_len` bytes) receives a human-readable message on failure.
 #pragma once
 #include <cuda_runtime.h>
 #include <stddef.h>

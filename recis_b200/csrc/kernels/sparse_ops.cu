@@ -171,10 +171,13 @@ fill_rows_i64_kernel(int64_t* __restrict__ dst, const int32_t* __restrict__ rows
 }
 
 // ------------------------------------------------------------------ pooling forward
-__device__ __forceinline__ int64_t out_row_of(int64_t s, int perm_b, int perm_f) {
-  if (perm_f <= 0) return s;
+// perm_f > 0: segment s = f * perm_b + b goes to row b * perm_total + perm_off + f of the output (perm_total features per
+// sample in the output, this call fills features perm_off .. perm_off + perm_f - 1)
+// perm_f <= 0: plain layout, segment s goes to row perm_off + s.
+__device__ __forceinline__ int64_t out_row_of(int64_t s, int perm_b, int perm_f, int perm_off, int perm_total) {
+  if (perm_f <= 0) return s + perm_off;
   const int64_t f = s / perm_b, b = s - f * perm_b;
-  return b * perm_f + f;
+  return b * perm_total + perm_off + f;
 }
 
 // One group of G lanes per segment; each lane owns NACC float4 column slots (columns lane + a*G).
@@ -182,7 +185,8 @@ template <int G, int NACC>
 __global__ void __launch_bounds__(kThreads)
 pool_forward_kernel(const float* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
                     const int32_t* __restrict__ offsets, const float* __restrict__ weights, int64_t n_seg, int D, int mode,
-                    int perm_b, int perm_f, float* __restrict__ out, int32_t* __restrict__ gsrc, float* __restrict__ gscale) {
+                    int perm_b, int perm_f, int perm_off, int perm_total, float* __restrict__ out, int32_t* __restrict__ gsrc,
+                    float* __restrict__ gscale) {
   const int lane = threadIdx.x % G;
   const int cols = D >> 2;
   const int64_t n_groups = (int64_t)gridDim.x * (kThreads / G);
@@ -220,7 +224,7 @@ pool_forward_kernel(const float* __restrict__ base, const int32_t* __restrict__ 
     float scale = 1.f;
     if (mode == 1) scale = end > beg ? 1.f / (float)(end - beg) : 0.f;
     else if (mode == 2) scale = wsum != 0.f ? 1.f / wsum : 0.f;
-    const int64_t orow = out_row_of(s, perm_b, perm_f);
+    const int64_t orow = out_row_of(s, perm_b, perm_f, perm_off, perm_total);
 #pragma unroll
     for (int a = 0; a < NACC; ++a) {
       const int c = lane + a * G;
@@ -239,7 +243,8 @@ pool_forward_kernel(const float* __restrict__ base, const int32_t* __restrict__ 
 __global__ void __launch_bounds__(kThreads)
 pool_forward_scalar_kernel(const float* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
                            const int32_t* __restrict__ offsets, const float* __restrict__ weights, int64_t n_seg, int D, int mode,
-                           int perm_b, int perm_f, float* __restrict__ out, int32_t* __restrict__ gsrc, float* __restrict__ gscale) {
+                           int perm_b, int perm_f, int perm_off, int perm_total, float* __restrict__ out, int32_t* __restrict__ gsrc,
+                           float* __restrict__ gscale) {
   const int64_t total = n_seg * D;
   for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
     const int64_t s = w / D; const int c = (int)(w - s * D);
@@ -254,7 +259,7 @@ pool_forward_scalar_kernel(const float* __restrict__ base, const int32_t* __rest
     float scale = 1.f;
     if (mode == 1) scale = end > beg ? 1.f / (float)(end - beg) : 0.f;
     else if (mode == 2) scale = wsum != 0.f ? 1.f / wsum : 0.f;
-    const int64_t orow = out_row_of(s, perm_b, perm_f);
+    const int64_t orow = out_row_of(s, perm_b, perm_f, perm_off, perm_total);
     out[orow * D + c] = acc * scale;
     if (gsrc && c == 0)
       for (int32_t i = beg; i < end; ++i) { gsrc[i] = (int32_t)orow; gscale[i] = (weights ? weights[i] : 1.f) * scale; }
@@ -629,19 +634,20 @@ void rb_fill_rows_i64(int64_t* dst, const int32_t* rows, int64_t n, int64_t valu
 }
 
 void rb_pool_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
-                     int64_t n_seg, int D, int mode, int perm_b, int perm_f, float* out, int32_t* gsrc, float* gscale,
-                     cudaStream_t st) {
+                     int64_t n_seg, int D, int mode, int perm_b, int perm_f, int perm_off, int perm_total, float* out, int32_t* gsrc,
+                     float* gscale, cudaStream_t st) {
   if (n_seg <= 0) return;
+  if (perm_f > 0 && perm_total <= 0) { perm_total = perm_f; perm_off = 0; }
   const bool ok = dispatch_cols(D, [&](auto g, auto nacc) {
     constexpr int G = decltype(g)::value, NACC = decltype(nacc)::value;
     const int64_t blocks = (n_seg + (kThreads / G) - 1) / (kThreads / G);
     pool_forward_kernel<G, NACC><<<(int)std::min<int64_t>(blocks, 148 * 64), kThreads, 0, st>>>(
-        base, rows, rev, offsets, weights, n_seg, D, mode, perm_b, perm_f, out, gsrc, gscale);
+        base, rows, rev, offsets, weights, n_seg, D, mode, perm_b, perm_f, perm_off, perm_total, out, gsrc, gscale);
         rb::note_launch();
   });
   if (!ok) {
     pool_forward_scalar_kernel<<<grid_stride_blocks(n_seg * D), kThreads, 0, st>>>(base, rows, rev, offsets, weights, n_seg, D, mode,
-                                                                                  perm_b, perm_f, out, gsrc, gscale);
+                                                                                  perm_b, perm_f, perm_off, perm_total, out, gsrc, gscale);
     rb::note_launch();
   }
 }
@@ -709,14 +715,15 @@ void rb_grad_reduce(const float* grad_out, const int32_t* gsrc, const float* gsc
 }
 
 void rb_grad_reduce_push(const float* grad_out, const int32_t* gsrc, const float* gscale, const int32_t* csr_u, const int32_t* csr_elem,
-                         const int32_t* start, int64_t n, int D, float* span_acc, RbGuPush push, cudaStream_t st) {
+                         const int32_t* start, int64_t n, int D, float* span_acc, RbGuPush push, int max_blocks, cudaStream_t st) {
   if (n <= 0) return;
   const int64_t n_chunks = (n + kChunk - 1) / kChunk;
   RbOpt opt{};
   dispatch_cols(D, [&](auto g, auto nacc) {
     constexpr int G = decltype(g)::value, NACC = decltype(nacc)::value;
     const int64_t blocks = (n_chunks + (kThreads / G) - 1) / (kThreads / G);
-    const int grid = (int)std::min<int64_t>(blocks, 148 * 64);
+    // max_blocks > 0 caps the grid (NVLink-bound kernel: a small grid leaves SMs to kernels of other streams)
+    const int grid = (int)std::min<int64_t>(blocks, max_blocks > 0 ? max_blocks : 148 * 64);
     grad_reduce_kernel<G, NACC, true><<<grid, kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, span_acc, nullptr,
                                                                  nullptr, 0, opt, push);
     rb::note_launch();
@@ -795,15 +802,21 @@ extern "C" int rb_dedup_partition_noalloc(const int64_t* ids, int64_t n, int wor
     base = g_noalloc_ptr[dev];
   }
   if (cudaMemsetAsync(counts, 0, sizeof(int32_t) * world, st) != cudaSuccess) { noalloc_fail(err, err_len, "memset of counts failed"); return 5; }
-  if (n == 0) { cudaMemsetAsync(offsets, 0, sizeof(int32_t) * (world + 1), st); return 0; }
+  if (n == 0) {
+    if (cudaMemsetAsync(offsets, 0, sizeof(int32_t) * (world + 1), st) != cudaSuccess) { noalloc_fail(err, err_len, "memset of offsets failed"); return 5; }
+    return 0;
+  }
   int64_t cap = 64;
   while (cap < 2 * n) cap <<= 1;                                        // <= kNoAllocMaxSlots because n <= kNoAllocMaxIds
   uint64_t* set_keys = reinterpret_cast<uint64_t*>(base);
   int32_t* set_pos = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(base) + kNoAllocKeysBytes);
   int32_t* slot = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(base) + kNoAllocKeysBytes + kNoAllocPosBytes);
   // the array keeps whatever the previous call left behind: everything that must start "empty" is reset here
-  cudaMemsetAsync(set_keys, 0xFF, sizeof(uint64_t) * cap, st);
-  cudaMemsetAsync(set_pos + cap, 0xFF, sizeof(int32_t), st);
+  if (cudaMemsetAsync(set_keys, 0xFF, sizeof(uint64_t) * cap, st) != cudaSuccess ||
+      cudaMemsetAsync(set_pos + cap, 0xFF, sizeof(int32_t), st) != cudaSuccess) {     // spare cell of the id -1; it moves with cap
+    noalloc_fail(err, err_len, "memset of the built-in scratch failed");
+    return 5;
+  }
   const int g = grid_stride_blocks(n);
   dedup_claim_kernel<<<g, kThreads, 2 * world * sizeof(int32_t), st>>>(ids, n, world, set_keys, set_pos, (uint64_t)cap - 1, slot, counts);
   dedup_assign_kernel<<<g, kThreads, (world + 1) * sizeof(int32_t), st>>>(ids, n, world, set_pos, slot, counts, offsets, unique_ids, reverse, n, nullptr);

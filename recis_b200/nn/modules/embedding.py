@@ -63,8 +63,11 @@ class EmbeddingOption:
     # additions
     capacity: int = 0            # rows to pre-size the shard for (0: grow on demand)
     mean_by_weight: bool = False  # "mean" divides by the weight sum instead of the bag length
-    exchange_capacity: int = 0   # unique ids per rank and step the peer-memory exchange windows are sized for (0: twice
-                                 # the id count of the first batch); features merged into one table add up
+    exchange_capacity: int = 0   # unique ids per rank and step the peer-memory exchange windows are sized for (0: measured on
+                                 # the first batch, plus half as much again; the windows grow with the demand either way);
+                                 # features merged into one table add up
+    exchange_strict: bool = False  # read every step's window demand before using it (one host read per lookup) and repeat
+                                   # the id phase with larger windows instead of ever dropping ids
 
     def __post_init__(self):
         if self.device is None:
@@ -219,6 +222,32 @@ class _LookupPoolFn(torch.autograd.Function):
         return (None,) * 12
 
 
+class _GroupLookupFn(torch.autograd.Function):
+    """Lookup of one runtime group split into exchange lanes (``FusedExchange.forward_group``): one shared output, one
+    backward that pushes each lane's per-unique gradients to their owners."""
+
+    @staticmethod
+    def forward(ctx, holder, emb_mod: "DynamicEmbedding", parts, mode, perm_b, perm_total, n_rows, training, admit_hook):
+        impl = emb_mod.impl
+        readonly, threshold = admit_params(admit_hook)
+        train = training and impl.trainable and emb_mod.option.trainable
+        if not (training and impl.trainable):
+            readonly = True
+        step = emb_mod.table.step_tensor() if not readonly else None
+        out, saved = emb_mod.fused.forward_group(emb_mod, parts, mode, perm_b, perm_total, n_rows, train, readonly, threshold, step)
+        ctx.train, ctx.emb_mod, ctx.saved = train, emb_mod, saved
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        if ctx.train:
+            emb_mod = ctx.emb_mod
+            grad_out = grad_out.contiguous().to(torch.float32).view(-1, emb_mod.impl.dim)
+            worker_scale = 1.0 / emb_mod.world_size if emb_mod.option.grad_reduce_by == "worker" else 1.0
+            emb_mod.fused.backward(emb_mod, ctx.saved, grad_out, worker_scale)
+        return (None,) * 9
+
+
 @dataclass
 class ExchangeIDsResults:
     """Token of a started lookup (``DynamicEmbedding.exchange_ids``)."""
@@ -348,6 +377,23 @@ class DynamicEmbedding(torch.nn.Module):
         out = _LookupPoolFn.apply(self._holder, self, ids, offsets, weights, combiner, int(tile_len), perm, self.training,
                                   admit_hook if admit_hook is not None else self._emb_opt.admit_hook, lane, prepared)
         # storage and pooling are fp32; a half-precision table dtype is the dtype the model sees
+        return out if self._emb_opt.dtype == torch.float32 else out.to(self._emb_opt.dtype)
+
+    def lookup_pool_group(self, parts, combiner: str, perm_b: int, perm_total: int, n_rows: int, admit_hook=None) -> torch.Tensor:
+        """Pooled lookup of several lanes of one runtime group into ONE output ``[n_rows, D]`` (fused exchange only). ``parts``:
+        per lane a dict with ``key``, ``ids``, ``offsets``, ``weights`` and the slice of the output it fills (``perm_f`` features
+        from feature ``perm_off`` of a ``[perm_b, perm_total, D]`` cube, or ``n_seg`` rows from row ``perm_off`` when
+        ``perm_total`` is 0)."""
+        assert self.fused is not None and combiner != "tile"
+        dev = self.impl.device
+        for p in parts:
+            p["ids"] = self._normalise_ids(p["ids"])
+            p["offsets"] = p["offsets"].to(device=dev, dtype=torch.int32).contiguous()
+            if p.get("weights") is not None:
+                p["weights"] = p["weights"].detach().reshape(-1).to(device=dev, dtype=torch.float32).contiguous()
+        mode = 0 if combiner != "mean" else (2 if self._emb_opt.mean_by_weight else 1)
+        out = _GroupLookupFn.apply(self._holder, self, parts, mode, int(perm_b), int(perm_total), int(n_rows), self.training,
+                                   admit_hook if admit_hook is not None else self._emb_opt.admit_hook)
         return out if self._emb_opt.dtype == torch.float32 else out.to(self._emb_opt.dtype)
 
     # ---- the reference's three-stage interface (``recis/nn/modules/embedding.py:498-624``) on top of prepare_lookup / lookup_pool

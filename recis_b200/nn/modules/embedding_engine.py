@@ -50,13 +50,14 @@ class _Group:
         self.fea_runtime[fea_name] = opt.runtime_info()
         self.fea_child[fea_name] = self.children[opt.shared_name]
 
-    def embedding_option(self, capacity, exchange_capacity=0):
+    def embedding_option(self, capacity, exchange_capacity=0, exchange_strict=False):
         o = self.opt
         return EmbeddingOption(
             embedding_dim=o.embedding_dim, block_size=o.block_size, dtype=o.dtype, device=o.device, shared_name=self.name,
             children=list(self.children.keys()), coalesced=True, initializer=o.initializer, grad_reduce_by=o.grad_reduce_by,
             fp16_enabled=o.fp16_enabled, filter_hook=o.filter_hook, pg=o.pg, max_partition_num=o.max_partition_num,
             capacity=capacity, mean_by_weight=o.mean_by_weight, exchange_capacity=exchange_capacity,
+            exchange_strict=exchange_strict,
         )
 
 
@@ -64,10 +65,10 @@ class EmbeddingEngine(nn.Module):
     def __init__(self, emb_options: dict, interleave: bool = False, exchange_lanes: int = 0):
         super().__init__()
         # exchange_lanes > 1 (or RECIS_EXCHANGE_LANES): the features of one (table, runtime group) are split into that many
-        # lanes, each with its own exchange on its own CUDA stream, so that one lane's NVLink-bound kernels overlap the other
-        # lanes' HBM-bound ones. Off by default; only used on CUDA with more than one rank and the peer-memory exchange.
+        # lanes (features of one shared_name stay together), each with its own exchange windows; the lanes run as a pipeline
+        # in which one lane's NVLink-bound kernels overlap the other lanes' memory-bound ones. Only used with more than one
+        # rank and the peer-memory exchange.
         self._lanes = int(exchange_lanes or os.environ.get("RECIS_EXCHANGE_LANES", "1"))
-        self._lane_streams = {}
         self._ht = nn.ModuleDict()
         self._groups = {}
         self._fea_to_ht = {}
@@ -88,11 +89,13 @@ class EmbeddingEngine(nn.Module):
             self._groups[ht_name].add(fea_name, opt)
             self._fea_to_ht[fea_name] = ht_name
         xcap = defaultdict(int)
+        strict = defaultdict(bool)
         for fea_name, opt in emb_options.items():
             capacity[self._fea_to_ht[fea_name]] += int(opt.capacity or 0)
             xcap[self._fea_to_ht[fea_name]] += int(opt.exchange_capacity or 0)
+            strict[self._fea_to_ht[fea_name]] |= bool(getattr(opt, "exchange_strict", False))
         for ht_name, group in self._groups.items():
-            self._ht[ht_name] = DynamicEmbedding(group.embedding_option(capacity[ht_name], xcap[ht_name]))
+            self._ht[ht_name] = DynamicEmbedding(group.embedding_option(capacity[ht_name], xcap[ht_name], strict[ht_name]))
 
     # ------------------------------------------------------------------ helpers
     def tables(self):
@@ -185,42 +188,57 @@ class EmbeddingEngine(nn.Module):
             weights = torch.cat(ws) if len(ws) > 1 else ws[0]
         return ids, offsets, weights
 
-    # ------------------------------------------------------------------ lanes (opt-in)
-    def _use_lanes(self, ht, feats, perm) -> bool:
-        return self._lanes > 1 and perm is not None and len(feats) >= self._lanes and getattr(ht, "fused", None) is not None
+    # ------------------------------------------------------------------ lanes
+    @staticmethod
+    def _lane_ranges(children, lanes):
+        """Split features 0..n-1 into at most ``lanes`` contiguous ranges such that no child table (``shared_name``) has features
+        in two ranges: the rows of two lanes are then disjoint, which is what lets their gradient windows be applied one after
+        the other (a row in two lanes would get two optimizer updates instead of one update of the summed gradient). Returns the
+        list of range boundaries ``[0, ..., n]``."""
+        n = len(children)
+        if lanes <= 1 or n < 2:
+            return [0, n]
+        last = {}
+        for i, c in enumerate(children):
+            last[c] = i
+        allowed, reach = [], -1
+        for i, c in enumerate(children):           # a cut in front of feature i+1 is allowed when no child seen so far comes back later
+            reach = max(reach, last[c])
+            if reach == i and i + 1 < n:
+                allowed.append(i + 1)
+        bounds = [0]
+        for k in range(1, lanes):
+            target = n * k // lanes
+            cands = [a for a in allowed if a > bounds[-1]]
+            if not cands:
+                break
+            cut = min(cands, key=lambda a: (abs(a - target), a))
+            bounds.append(cut)
+        bounds.append(n)
+        return bounds
 
-    def _lookup_in_lanes(self, ht, feats, opt, run_key, dev):
-        """Split the features of one runtime group into lanes; every lane coalesces, exchanges and pools on its own stream.
-        Returns the pooled rows in the interleaved layout ``[segments_per_feature * n_features, D]``."""
-        L = self._lanes
-        bounds = [len(feats) * i // L for i in range(L + 1)]
-        cubes = []
-        if dev.type != "cuda":
-            # CPU ranks (the exchange's host twin): no streams, the lanes run one after the other; same windows, same records
-            for i in range(L):
-                part = feats[bounds[i]:bounds[i + 1]]
-                ids, offsets, weights = self._coalesce(part, dev)
-                pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, 0, (part[0]["n_seg"], len(part)), opt.admit_hook,
-                                        lane=f"{run_key}#lane{i}")
-                cubes.append(pooled.view(part[0]["n_seg"], len(part), opt.embedding_dim))
-            return torch.cat(cubes, dim=1).reshape(-1, opt.embedding_dim)
-        main = torch.cuda.current_stream(dev)
-        ht.fused.multi_stream = True
+    def _use_lanes(self, ht, feats, opt) -> bool:
+        return (self._lanes > 1 and len(feats) >= 2 and opt.combiner != "tile" and getattr(ht, "fused", None) is not None)
+
+    def _lookup_in_lanes(self, ht, feats, opt, run_key, dev, perm):
+        """One runtime group as a pipeline of exchange lanes (``FusedExchange.forward_group``). Returns the pooled rows of the
+        whole group: ``[segments_per_feature * n_features, D]`` in the interleaved layout when ``perm`` is set, else the features'
+        segments one after the other."""
+        bounds = self._lane_ranges([f["child"] for f in feats], self._lanes)
+        L = len(bounds) - 1
+        parts, seg_off = [], 0
         for i in range(L):
             part = feats[bounds[i]:bounds[i + 1]]
-            stream = self._lane_streams.get((dev, i))
-            if stream is None:
-                stream = self._lane_streams[(dev, i)] = torch.cuda.Stream(device=dev)
-            stream.wait_stream(main)
-            with torch.cuda.stream(stream):
-                ids, offsets, weights = self._coalesce(part, dev)
-                pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, 0, (part[0]["n_seg"], len(part)), opt.admit_hook,
-                                        lane=f"{run_key}#lane{i}")
-                cubes.append(pooled.view(part[0]["n_seg"], len(part), opt.embedding_dim))
-        for i, c in enumerate(cubes):
-            main.wait_stream(self._lane_streams[(dev, i)])
-            c.record_stream(main)
-        return torch.cat(cubes, dim=1).reshape(-1, opt.embedding_dim)
+            ids, offsets, weights = self._coalesce(part, dev)
+            key = f"{run_key}#lane{i}of{L}"
+            ht.fused.lane_children[key] = frozenset(f["child"] for f in part)
+            n_seg = sum(f["n_seg"] for f in part)
+            parts.append(dict(key=key, ids=ids, offsets=offsets, weights=weights, perm_f=len(part), n_seg=n_seg,
+                              perm_off=bounds[i] if perm is not None else seg_off))
+            seg_off += n_seg
+        if perm is not None:
+            return ht.lookup_pool_group(parts, opt.combiner, perm[0], perm[1], perm[0] * perm[1], opt.admit_hook)
+        return ht.lookup_pool_group(parts, opt.combiner, 0, 0, seg_off, opt.admit_hook)
 
     # ------------------------------------------------------------------ forward
     def forward(self, input_features: dict):
@@ -254,10 +272,12 @@ class EmbeddingEngine(nn.Module):
                 perm = None
                 if self._interleave and opt.combiner != "tile" and len(set(segs)) == 1 and len(feats) > 1:
                     perm = (segs[0], len(feats))
-                lanes = self._use_lanes(ht, feats, perm)
+                lanes = self._use_lanes(ht, feats, opt)
                 ids = offsets = weights = prepared = None
                 if not lanes:
                     ids, offsets, weights = self._coalesce(feats, dev)
+                    if getattr(ht, "fused", None) is not None:
+                        ht.fused.lane_children[run_key] = frozenset(f["child"] for f in feats)
                     if n_groups > 1:
                         prepared = ht.prepare_lookup(ids, lane=run_key)
                 plan.append((ht_name, ht, dev, run_key, feats, opt, tile_len, segs, perm, lanes, ids, offsets, weights, prepared))
@@ -269,7 +289,7 @@ class EmbeddingEngine(nn.Module):
         for ht_name, ht, dev, run_key, feats, opt, tile_len, segs, perm, lanes, ids, offsets, weights, prepared in plan:
             ht.option.mean_by_weight = opt.mean_by_weight
             if lanes:
-                pooled = self._lookup_in_lanes(ht, feats, opt, run_key, dev)          # [B, F, D] assembled from the lanes
+                pooled = self._lookup_in_lanes(ht, feats, opt, run_key, dev, perm)
             else:
                 pooled = ht.lookup_pool(ids, offsets, weights, opt.combiner, tile_len, perm, opt.admit_hook, lane=run_key,
                                         prepared=prepared)

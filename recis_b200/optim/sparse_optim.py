@@ -28,6 +28,19 @@ from ..nn.modules.hashtable import split_sparse_dense_state_dict
 OPT_ADAM, OPT_ADAGRAD, OPT_SGD = 0, 1, 2
 
 
+def _row_disjoint(recs) -> bool:
+    """True when the staged exchange records are known to touch pairwise different rows: each one names the child tables its
+    ids belong to, and no child appears twice. A row that showed up in two records must get ONE update of the summed gradient
+    (the materialising path), not two updates."""
+    seen = set()
+    for r in recs:
+        ch = r.get("children")
+        if ch is None or (seen & ch):
+            return False
+        seen |= ch
+    return True
+
+
 class SparseOptimizer(Optimizer):
     slot_prefix = "sparse_opt"
     slot_names = ()
@@ -99,16 +112,12 @@ class SparseOptimizer(Optimizer):
             elif len(recs) == 1 and recs[0]["kind"] == "peer":
                 r = recs[0]
                 r["exchange"].owner_reduce(impl, r, True, kind, lr, b1, b2, eps, decay, alpha, inv_accum, w, s1, s2)
-            elif all(r.get("kind") == "peer" and r.get("stream") is not None for r in recs):
-                # one record per exchange lane (disjoint rows): each lane's update runs on the lane's own stream, right behind
-                # its gradient exchange, while other lanes are still exchanging
-                main = torch.cuda.current_stream(w.device)
+            elif all(r.get("kind") == "peer" for r in recs) and _row_disjoint(recs):
+                # one record per exchange lane and the lanes share no table row (different child tables): each lane's update is
+                # its own kernel, issued in the order the gradients were pushed, so the first ones run while the last lanes are
+                # still exchanging
                 for r in recs:
-                    r["stream"].wait_stream(main)
-                    with torch.cuda.stream(r["stream"]):
-                        r["exchange"].owner_reduce(impl, r, True, kind, lr, b1, b2, eps, decay, alpha, inv_accum, w, s1, s2)
-                for r in recs:
-                    main.wait_stream(r["stream"])
+                    r["exchange"].owner_reduce(impl, r, True, kind, lr, b1, b2, eps, decay, alpha, inv_accum, w, s1, s2)
             else:
                 rows, grads = impl.materialize()
                 if rows is not None and rows.numel():

@@ -45,7 +45,8 @@ def main():
         return float(t)
 
     res = {}
-    for blocks in (148 * 4, 148 * 16):
+    # small grids matter: the exchange runs its NVLink-bound kernels with capped grids next to other kernels
+    for blocks in (37, 74, 148, 296, 148 * 4, 148 * 16):
         res[f"store_{blocks}"] = n / timed(lambda: C.comm_copy(peer, local_buf.data_ptr(), n, blocks)) / 1e6
         res[f"load_{blocks}"] = n / timed(lambda: C.comm_copy(local_buf.data_ptr(), peer, n, blocks)) / 1e6
     res["local_copy"] = n / timed(lambda: C.comm_copy(heap["buf"].tensor.data_ptr(), local_buf.data_ptr(), n, 148 * 16)) / 1e6

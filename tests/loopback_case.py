@@ -16,6 +16,8 @@ def run_loopback(dev, world, dim):
     ids, offs, revs = [], [], []
     ids_win = [torch.zeros(cap, dtype=torch.int64, device=dev) for _ in range(W)]
     off_win = [torch.zeros(W + 1, dtype=torch.int32, device=dev) for _ in range(W)]
+    cnt_win = [torch.zeros(W, dtype=torch.int32, device=dev) for _ in range(W)]
+    demand = torch.zeros(2, dtype=torch.int32, device=dev)
     uemb = [torch.zeros(cap, D, device=dev) for _ in range(W)]
     gin = [torch.zeros(in_cap, D, device=dev) for _ in range(W)]
     ptrs = lambda ts: [t.data_ptr() for t in ts]
@@ -26,7 +28,7 @@ def run_loopback(dev, world, dim):
         x = torch.randint(0, 3000, (int(o[-1]),), dtype=torch.int64) * 7919 + (torch.randint(0, 2, (int(o[-1]),)) << 40)
         x[: x.numel() // 5] = 12345                        # an id every rank asks for many times
         ids.append(x.to(dev)); offs.append(o.to(dev))
-        _u, rev, _c, _o = C.dedup_partition(ids[r], W, ids_win[r], off_win[r], status)
+        _u, rev, _c, _o = C.dedup_partition(ids[r], W, ids_win[r], off_win[r], status, cnt_win[r])
         revs.append(rev)
     # ---- owners: pull ids, resolve rows, push rows to the requesters
     ids_in, prefix, rows_in, tables, owned = [], [], [], [], []
@@ -34,7 +36,7 @@ def run_loopback(dev, world, dim):
         buf = torch.zeros(in_cap, dtype=torch.int64, device=dev)
         meta = torch.zeros(3 * W + 1, dtype=torch.int32, device=dev)
         n_in = torch.zeros(1, dtype=torch.int32, device=dev)
-        C.comm_pull_ids(ptrs(ids_win), ptrs(off_win), o, buf, meta, n_in, status)
+        C.comm_pull_ids(ptrs(ids_win), ptrs(off_win), ptrs(cnt_win), o, buf, meta, n_in, demand, status)
         n = int(n_in.item())
         assert n == int(meta[W].item()) == sum(int(off_win[r][o + 1] - off_win[r][o]) for r in range(W))
         uniq, inv = torch.unique(buf[:n], return_inverse=True)
@@ -44,8 +46,11 @@ def run_loopback(dev, world, dim):
         ids_in.append(buf); prefix.append(meta); rows_in.append(rows); tables.append(table); owned.append(uniq)
     all_owned = torch.cat(owned)
     assert all_owned.unique().numel() == all_owned.numel()                     # every id has exactly one owner
+    # the demand every owner computed from all requesters' counts: largest unique count of a requester, largest inflow of an owner
+    assert int(demand[0]) == max(int(off_win[r][W]) for r in range(W))
+    assert int(demand[1]) == max(sum(int(off_win[r][o + 1] - off_win[r][o]) for r in range(W)) for o in range(W))
     for o in range(W):
-        C.comm_push_emb(tables[o], rows_in[o], prefix[o], ptrs(uemb), o, in_cap)
+        C.comm_push_emb(tables[o], rows_in[o], prefix[o], ptrs(uemb), o, in_cap, 37 if o % 2 else 0)   # capped and uncapped grids
     # ---- requesters: pool; oracle = rows looked up by id in the owners' tables
     order = torch.argsort(all_owned)
     keys = all_owned[order]
@@ -64,7 +69,7 @@ def run_loopback(dev, world, dim):
         go = torch.randn(S, D, device=dev)
         gsrc, gscale, seg = saved[r]
         csr_u, csr_elem, start = C.build_csr(revs[r])
-        C.comm_grad_reduce_push(go, gsrc, gscale, csr_u, csr_elem, start, D, off_win[r], prefix[r], ptrs(gin), in_cap)
+        C.comm_grad_reduce_push(go, gsrc, gscale, csr_u, csr_elem, start, D, off_win[r], prefix[r], ptrs(gin), in_cap, 53 if r % 2 else 0)
         G.index_add_(0, torch.searchsorted(keys, ids[r]), go[seg].double())
     # ---- owners: reduce across requesters (no update), then the fused update on a copy
     for o in range(W):
@@ -91,3 +96,57 @@ def run_loopback(dev, world, dim):
     for b in bufs:
         assert torch.allclose(b.double(), mean, atol=1e-5)
     assert int(status.item()) == 0
+
+
+def run_loopback_overflow(dev, world, dim):
+    """Every id belongs to logical rank 0 and its receive window is far too small: the owner-side kernels must see clamped
+    boundaries only (guard rows behind every buffer stay untouched), the overflow bit must be set, and what did fit must be right."""
+    import recis_b200
+    C = recis_b200.native()
+    torch.manual_seed(7)
+    W, D, S = world, dim, 200
+    cap, in_cap, guard = 1024, 96, 64
+    status = torch.zeros(1, dtype=torch.int64, device=dev)
+    ptrs = lambda ts: [t.data_ptr() for t in ts]
+    ids_win = [torch.zeros(cap, dtype=torch.int64, device=dev) for _ in range(W)]
+    off_win = [torch.zeros(W + 1, dtype=torch.int32, device=dev) for _ in range(W)]
+    cnt_win = [torch.zeros(W, dtype=torch.int32, device=dev) for _ in range(W)]
+    uemb = [torch.full((cap + guard, D), 7.0, device=dev) for _ in range(W)]
+    gin = [torch.full((in_cap + guard, D), 7.0, device=dev) for _ in range(W)]
+    ids, offs, revs = [], [], []
+    for r in range(W):
+        o = torch.arange(0, 2 * S + 1, 2, dtype=torch.int32)
+        x = (torch.randperm(1000)[: 2 * S] + 1000 * r).to(torch.int64) * 65536          # low 16 bits zero: owner 0, all distinct
+        ids.append(x.to(dev)); offs.append(o.to(dev))
+        _u, rev, _c, _o = C.dedup_partition(ids[r], W, ids_win[r], off_win[r], status, cnt_win[r])
+        revs.append(rev)
+    demand = torch.zeros(2, dtype=torch.int32, device=dev)
+    metas, rows_all, tables = [], [], []
+    for o in range(W):
+        buf = torch.full((in_cap + guard,), -5, dtype=torch.int64, device=dev)
+        meta = torch.zeros(3 * W + 1, dtype=torch.int32, device=dev)
+        n_in = torch.zeros(1, dtype=torch.int32, device=dev)
+        C.comm_pull_ids(ptrs(ids_win), ptrs(off_win), ptrs(cnt_win), o, buf[:in_cap], meta, n_in, demand, status)
+        n = int(n_in.item())
+        assert n == (in_cap if o == 0 else 0) and int(meta[:W + 1].max()) <= in_cap        # clamped boundaries only
+        assert bool((buf[in_cap:] == -5).all())
+        rows = torch.full((in_cap,), -1, dtype=torch.int32, device=dev)
+        rows[:n] = torch.arange(n, dtype=torch.int32, device=dev)
+        metas.append(meta); rows_all.append(rows); tables.append(torch.randn(max(n, 1), D, device=dev))
+    assert int(status.item()) & 8                                                        # overflow reported
+    assert int(demand[1]) == 2 * S * W and int(demand[0]) == 2 * S                       # the true demand, unclamped
+    for o in range(W):
+        C.comm_push_emb(tables[o], rows_all[o], metas[o], ptrs([u[:cap] for u in uemb]), o, in_cap, 0)
+    for r in range(W):
+        assert bool((uemb[r][cap:] == 7.0).all())
+        go = torch.randn(S, D, device=dev)
+        out, gsrc, gscale = C.pool_forward(uemb[r][:cap].contiguous(), None, revs[r], offs[r], None, 0, 0, 0, True)
+        csr_u, csr_elem, start = C.build_csr(revs[r])
+        C.comm_grad_reduce_push(go, gsrc, gscale, csr_u, csr_elem, start, D, off_win[r], metas[r], ptrs([g[:in_cap] for g in gin]), in_cap, 0)
+    for o in range(W):
+        assert bool((gin[o][in_cap:] == 7.0).all())                                      # no gradient row landed behind a window
+        head = torch.full((tables[o].size(0) + guard,), -1, dtype=torch.int32, device=dev)
+        rows, grads = C.comm_owner_reduce(rows_all[o], head, metas[o], gin[o][:in_cap].contiguous(), W, D, False, False, 2, 0.0, 0.0, 0.0,
+                                          0.0, 1.0, 0.0, 1.0, None, None, None, in_cap, 2)
+        assert int(head.max().item()) == -1
+        assert int((rows >= 0).sum()) == (in_cap if o == 0 else 0)

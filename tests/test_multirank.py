@@ -299,6 +299,112 @@ def test_exchange_lanes_on_cpu_ranks_equal_the_single_lane_run():
             assert all(torch.allclose(x[n], y[n], atol=1e-6) for n in x)
 
 
+def _shared_child_lanes_fn(rank, world, lanes, interleave):
+    """Six features over four child tables: f1 and f2 share ``s1``, f4 and f5 share ``s3``. Lanes must keep the features of one
+    child together; a row that landed in two lanes would be updated twice per step."""
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.optim import SparseAdam
+    torch.manual_seed(13)
+    init = NormalInitializer(0, 0.05)
+    shared = {"f0": "s0", "f1": "s1", "f2": "s1", "f3": "s2", "f4": "s3", "f5": "s3"}
+    eng = EmbeddingEngine({n: EmbeddingOption(embedding_dim=8, shared_name=sn, combiner="sum", initializer=init) for n, sn in shared.items()},
+                          interleave=interleave, exchange_lanes=lanes)
+    opt = SparseAdam(filter_out_sparse_param(eng), lr=0.05)
+    outs = []
+    for step in range(3):
+        g = torch.Generator().manual_seed(10 * step + rank)
+        feats = {n: torch.randint(0, 40, (12, 2), generator=g) * 7919 for n in shared}       # small id range: f1/f2 and f4/f5 collide a lot
+        coef = {n: torch.randn(12, 8, generator=g) for n in shared}
+        opt.zero_grad()
+        out = eng(feats)
+        sum((out[n] * coef[n]).sum() for n in shared).backward()
+        opt.step()
+        outs.append({n: out[n].detach().clone() for n in shared})
+    (table,) = eng.tables().values()
+    n_lanes = len(table.fused.lanes)
+    table.fused.check()
+    ids, rows = table.impl.ids_map()
+    order = torch.argsort(ids)
+    return {"outs": outs, "ids": ids[order], "emb": table.impl.store.emb()[rows[order]].clone(), "n_lanes": n_lanes}
+
+
+@pytest.mark.parametrize("interleave", [True, False])
+def test_lanes_keep_features_of_one_shared_name_together(interleave):
+    env = {"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"}
+    three = run_ranks(_shared_child_lanes_fn, 2, "gloo", args=(3, interleave), env=env)
+    one = run_ranks(_shared_child_lanes_fn, 2, "gloo", args=(1, interleave), env=env)
+    assert all(r["n_lanes"] == 3 for r in three) and all(r["n_lanes"] == 1 for r in one)
+    for a, b in zip(three, one):
+        assert torch.equal(a["ids"], b["ids"]) and torch.allclose(a["emb"], b["emb"], atol=1e-6)
+        for x, y in zip(a["outs"], b["outs"]):
+            assert all(torch.allclose(x[n], y[n], atol=1e-6) for n in x)
+
+
+def test_lane_ranges_never_split_a_child():
+    from recis_b200.nn.modules.embedding_engine import EmbeddingEngine
+    f = EmbeddingEngine._lane_ranges
+    assert f([0, 1, 2, 3], 2) == [0, 2, 4]
+    ch = [0, 1, 1, 2, 3, 3]
+    b = f(ch, 3)
+    assert len(b) == 4 and b[0] == 0 and b[-1] == 6
+    parts = [set(ch[x:y]) for x, y in zip(b, b[1:])]
+    assert all(not (parts[i] & parts[j]) for i in range(3) for j in range(i + 1, 3))
+    assert f([0, 1, 0, 1], 2) == [0, 4]                    # interleaved children: no legal cut, one lane
+    assert f([0, 0, 0], 4) == [0, 3]
+    b = f(list(range(26)), 4)
+    assert b[0] == 0 and b[-1] == 26 and len(b) == 5 and all(y > x for x, y in zip(b, b[1:]))
+
+
+def _skewed_ids_fn(rank, world, strict):
+    """Every id is a multiple of 65536, so rank 0 owns all of them: the receive window of rank 0 is asked for world times what
+    a balanced batch would bring. Step 1 sizes the windows from a small batch, step 2 is four times larger."""
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption
+    from recis_b200.nn.initializers import NormalInitializer
+    torch.manual_seed(3)
+    eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name=f"skewed_{strict}", initializer=NormalInitializer(0, 0.05),
+                                                exchange_strict=strict)})
+    (table,) = eng.tables().values()
+    outs, refs, errs = [], [], []
+    os.environ["RECIS_COMM"] = "nccl"
+    torch.manual_seed(3)
+    ref_eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name=f"skewed_{strict}_ref", initializer=NormalInitializer(0, 0.05))})
+    for step, n in enumerate((600, 2400, 2400, 2400, 2400)):
+        g = torch.Generator().manual_seed(100 * step + rank)
+        ids = (torch.randperm(4000, generator=g)[:n] + 4000 * rank).view(-1, 2) * 65536
+        outs.append(eng({"a": ids})["a"].detach().clone())
+        refs.append(ref_eng({"a": ids})["a"].detach().clone())
+        try:
+            table.fused.check()
+            errs.append(None)
+        except RuntimeError as e:
+            errs.append(str(e))
+    (lane,) = table.fused.lanes.values()
+    return {"same": [bool(torch.allclose(o, r, atol=1e-6)) for o, r in zip(outs, refs)], "errs": errs, "grown": lane.grown,
+            "caps": (lane.send_cap, lane.in_cap)}
+
+
+@pytest.mark.parametrize("world", [3, 4])
+def test_skewed_ids_overflow_is_memory_safe_then_windows_grow(world):
+    """Default mode: the step that outgrows the windows is flagged (ids dropped, nothing indexed out of bounds - the CPU twin
+    runs the same clamps), the measured demand makes every rank grow its windows two lookups later, and from then on the
+    results are exact again."""
+    res = run_ranks(_skewed_ids_fn, world, "gloo", args=(False,), env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    for r in res:
+        assert r["same"][0] and r["errs"][0] is None
+        assert r["errs"][1] is not None and "overflow" in r["errs"][1]
+        assert r["grown"] >= 1 and r["same"][-1] and r["errs"][-1] is None
+    assert len({r["caps"] for r in res}) == 1                      # identical layouts on every rank after growing
+
+
+def test_strict_exchange_repeats_the_id_phase_instead_of_dropping_ids():
+    res = run_ranks(_skewed_ids_fn, 3, "gloo", args=(True,), env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    for r in res:
+        assert all(r["same"]) and all(e is None for e in r["errs"]) and r["grown"] >= 1
+
+
 def _skewed_fn(rank, world, jitter):
     """Many short steps with random delays in front of every flag signal and every pull / push: the ranks drift apart as far as
     the protocol lets them. Returns the final rows."""

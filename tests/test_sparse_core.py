@@ -323,3 +323,10 @@ def test_exchange_host_twins_loopback(world, dim):
     drives the device kernels on one GPU)."""
     from loopback_case import run_loopback
     run_loopback(torch.device("cpu"), world, dim)
+
+
+@pytest.mark.parametrize("world,dim", [(3, 8), (4, 32)])
+def test_exchange_host_twins_overflow_is_clamped(world, dim):
+    """Every id goes to logical rank 0, whose receive window is too small: boundaries are clamped, guard rows stay untouched."""
+    from loopback_case import run_loopback_overflow
+    run_loopback_overflow(torch.device("cpu"), world, dim)

@@ -68,6 +68,22 @@ def test_noalloc_matches_regular_entry_point_twice():
     _check_against_regular(fn, ids1[:5], 1)
 
 
+def test_noalloc_sentinel_id_and_empty_call():
+    """The id -1 is the hash set's "empty" marker and lives in a spare cell whose position depends on the call's size: a large
+    call followed by a small one (both containing -1) exercises both positions; an empty call only clears the outputs."""
+    fn = _lib()
+    torch.manual_seed(1)
+    big = torch.randint(0, 1 << 30, (150_000,), device=DEV)
+    big[::11] = -1
+    small = torch.tensor([7, -1, 7, -1, 9, -2, -1], dtype=torch.int64, device=DEV)
+    _check_against_regular(fn, big, 4)
+    _check_against_regular(fn, small, 4)
+    rc, msg, counts, offsets, _u, _r = _call(fn, small[:0], 4)
+    assert rc == 0, msg
+    assert int(counts.abs().sum()) == 0 and int(offsets.abs().sum()) == 0
+    _check_against_regular(fn, small, 2)       # the scratch is usable after the empty call
+
+
 def test_noalloc_rejects_oversize_and_bad_arguments():
     fn = _lib()
     ids = torch.zeros(MAX_IDS + 1, dtype=torch.int64, device=DEV)

@@ -5,13 +5,21 @@ file name sorts last on purpose: it is the newest GPU test of the suite."""
 import pytest
 import torch
 
-from loopback_case import run_loopback
+from loopback_case import run_loopback, run_loopback_overflow
 
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("world,dim", [(2, 16), (4, 128), (8, 64)])
 def test_exchange_kernels_loopback_on_one_gpu(world, dim):
     run_loopback(torch.device("cuda:0"), world, dim)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,dim", [(3, 8), (4, 32)])
+def test_exchange_kernels_clamp_an_overflowing_receive_window(world, dim):
+    """Ids skewed to one owner with a receive window that is too small: the same case passes on the kernels' host twins (where
+    an out-of-range index would be caught by the guard rows), so the device kernels only ever see in-range indices here too."""
+    run_loopback_overflow(torch.device("cuda:0"), world, dim)
 
 
 @pytest.mark.gpu
