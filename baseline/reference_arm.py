@@ -141,5 +141,57 @@ class ReferenceArm:
     def launches(self):
         return 0
 
+    def table_rows(self, st, world):
+        """Rows in the reference's tables over all ranks, through its public ``HashTable.ids()`` (read between regions, outside all
+        timing); None when that call is not available."""
+        import torch
+        import torch.distributed as dist
+        try:
+            n = 0
+            for emb in st["sparse"].engine._ht.values():
+                n += int(emb._hashtable.ids().numel())
+        except Exception:
+            return None
+        if world > 1:
+            t = torch.tensor([n], dtype=torch.int64, device="cuda")
+            dist.all_reduce(t)
+            n = int(t.item())
+        return n
+
+    def exposed_comm_ms(self, st, host_batches, dev, world, steps):
+        """Device time per step of the reference's all-to-all kernels (NCCL send/receive kernels in a torch-profiler window over
+        ``steps`` extra steps after the timed regions), max over ranks: its collectives run on the model's stream, so all of that
+        time is exposed."""
+        import torch
+        import torch.distributed as dist
+        if world == 1:
+            return {"total": 0.0, "note": "single GPU: the all-to-alls are local copies"}
+        from torch.profiler import ProfilerActivity, profile
+        batches = [self.to_device(b, dev) for b in host_batches[-steps:]]
+        torch.cuda.synchronize(); dist.barrier()
+        total_us, err = -1.0, None
+        try:
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for b in batches:
+                    self.step(st, b)
+                torch.cuda.synchronize()
+            total_us = 0.0
+            for ev in prof.key_averages():
+                name = ev.key.lower()
+                if "nccl" in name and ("sendrecv" in name or "alltoall" in name):
+                    total_us += float(getattr(ev, "device_time_total", 0.0) or getattr(ev, "cuda_time_total", 0.0))
+        except Exception as e:
+            err = repr(e)
+            for b in batches[:0]:
+                pass
+        t = torch.tensor([total_us / 1e3 / max(len(batches), 1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out = {"total": round(float(t.item()), 4),
+               "how": "device time of the NCCL send/receive kernels of all_to_all_single per step (torch profiler, %d extra steps, max "
+                      "over ranks)" % len(batches)}
+        if err:
+            out["error"] = err
+        return out
+
     def comm_mode(self):
         return "torch.distributed all_to_all_single (NCCL)"

@@ -42,6 +42,7 @@ def parse():
     p.add_argument("--batch-per-gpu", type=int, default=PER_GPU_BATCH)
     p.add_argument("--capacity", type=int, default=0, help="rows per GPU to pre-size the table for")
     p.add_argument("--comm", default=None, help="override RECIS_COMM (fused | nccl)")
+    p.add_argument("--regions", type=int, default=3, help="timed regions of --steps steps each, per measurement (median is reported)")
     return p.parse_args()
 
 
@@ -165,40 +166,31 @@ def run(args, arm):
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     dev = torch.device("cuda", local)
     fields, spec = spec_for(args, rank)
-    n_batches = args.warmup + args.steps
-    # rows per GPU: this rank's share of the 1e8-row table with Adam state (1536 B per row) plus head-room for the rows the
-    # allocator sets aside for calls still in flight (a table that runs within a few steps' inserts of its capacity has to grow,
-    # which copies the whole arena); with few GPUs the shard is capped at what the benchmark's step count can touch
-    capacity = args.capacity or min(int(1.15 * UNIVERSE / world) + 8_000_000, 72_000_000)
+    R, K, W = max(args.regions, 1), args.steps, args.warmup
+    e2e_warm = min(3, W)
+    # Every step of the run, timed or not, consumes a batch that no earlier step has seen: W warm-up steps, a short warm-up of the
+    # end-to-end path, then R regions of K steps for each of the two measurements, interleaved (A1 E1 A2 E2 ...) so that the
+    # device-resident number and the end-to-end number see the same mix of known and new ids.
+    n_batches = W + e2e_warm + 2 * R * K
+    # rows per GPU: what the run can touch (with a few GPUs the run ends long before the 1e8-row universe is covered) plus head-room
+    # for the rows the allocator sets aside for calls still in flight
+    capacity = args.capacity or min(int(1.15 * UNIVERSE / world) + 8_000_000, 96_000_000)
     state = arm.build(fields, dev, world, rank, capacity)
 
     from recis_b200.io.synthetic import make_batch_arrays
     host = [arm.wrap_host(make_batch_arrays(spec, i), spec.batch) for i in range(n_batches)]
     h2d_bytes = arm.nbytes(host[0])
-
-    # ---- A. device-resident inputs: kernel-path number
-    dev_batches = [arm.to_device(b, dev) for b in host]
-    sync_all(world)
-
-    def step_resident(i):
-        arm.step(state, dev_batches[i])
-
-    timed(step_resident, 0, args.warmup, world)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    launches0 = arm.launches()
-    ms = timed(step_resident, args.warmup, args.steps, world)
-    launches = arm.launches() - launches0
-    clocks = sampler.stop() if rank == 0 else None
-    del dev_batches
-
-    # ---- B. end to end: every step's inputs are copied host -> device from pinned memory inside the timed region (the arm's
-    # feeder may run those copies on a side stream ahead of use, as a data loader does) and the step's loss is read back
     losses = []
 
-    def run_e2e(first, count):
-        import torch
+    def region_resident(first, count):
+        """Device-resident inputs: the kernel-path number."""
+        dev_batches = [arm.to_device(b, dev) for b in host[first:first + count]]
+        sync_all(world)
+        return timed(lambda i: arm.step(state, dev_batches[i]), 0, count, world)
+
+    def region_e2e(first, count):
+        """End to end: every step's inputs are copied host -> device from pinned memory inside the timed region (the arm's feeder
+        may run those copies on a side stream ahead of use, as a data loader does) and the step's loss is read back."""
         sync_all(world)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -214,23 +206,52 @@ def run(args, arm):
         sync_all(world)
         return max_over_ranks(ms_, world)
 
-    run_e2e(0, min(3, args.warmup))
-    ms_e2e = run_e2e(args.warmup, args.steps)
+    rows_seen = [arm.table_rows(state, world)]
 
-    # ---- C. exposed communication: CUDA-event spans around the exchange phases on the model's stream, a few extra steps
-    exposed = arm.exposed_comm_ms(state, host, dev, world, min(5, args.steps)) if hasattr(arm, "exposed_comm_ms") else None
+    def new_rows(count):
+        rows_seen.append(arm.table_rows(state, world))
+        a, b = rows_seen[-2], rows_seen[-1]
+        return None if a is None or b is None else (b - a) / count
 
+    pos = 0
+    region_resident(pos, W); pos += W
+    new_rows(W)
+    region_e2e(pos, e2e_warm); pos += e2e_warm
+    new_rows(max(e2e_warm, 1))
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_a, ms_e, new_a, new_e, launches = [], [], [], [], []
+    for _ in range(R):
+        l0 = arm.launches()
+        ms_a.append(region_resident(pos, K)); pos += K
+        launches.append(arm.launches() - l0)
+        new_a.append(new_rows(K))
+        ms_e.append(region_e2e(pos, K)); pos += K
+        new_e.append(new_rows(K))
+    clocks = sampler.stop() if rank == 0 else None
+
+    def median_of(xs):
+        order = sorted(range(len(xs)), key=lambda i: xs[i])
+        return order[len(xs) // 2]
+
+    ia, ie = median_of(ms_a), median_of(ms_e)
+    ms, ms_e2e = ms_a[ia], ms_e[ie]
+
+    # ---- exposed communication: a few extra steps after the timed regions
+    exposed = arm.exposed_comm_ms(state, host, dev, world, min(5, K)) if hasattr(arm, "exposed_comm_ms") else None
     status_bits = arm.exchange_status(state) if hasattr(arm, "exchange_status") else None
 
     global_batch = spec.batch * world
-    value = global_batch * args.steps / (ms / 1e3)
-    value_e2e = global_batch * args.steps / (ms_e2e / 1e3)
+    value = global_batch * K / (ms / 1e3)
+    value_e2e = global_batch * K / (ms_e2e / 1e3)
     if rank == 0:
+        per_step = lambda xs: [round(x / K, 4) for x in xs]
         line = {
             "metric": "train samples/s (DLRM-style CTR, device-timed, max over ranks)",
-            "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic (seeded), random-init weights",
+            "value": value, "unit": "samples/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded), random-init weights; every step sees a fresh batch",
             "impl": arm.name,
             "config": {
                 "model": "dlrm_ctr: 13 dense + 26 multi-hot fields (Poisson(20) in [1,100]) -> one merged dim-128 dynamic table, "
@@ -238,13 +259,19 @@ def run(args, arm):
                 "global_batch": global_batch, "per_gpu_batch": spec.batch, "seq_len": None,
                 "ids": "Zipf(1.05) over a 2^40 id space, 1e8 distinct ids in total over the 26 fields", "parallelism": f"dp{world} dense + row-sharded embeddings",
                 "l2": "no explicit flush: each step touches > 1 GB of embedding rows and optimizer state, far beyond the 126 MB L2",
-                "comm": arm.comm_mode(),
                 "precision": "bf16 dense tower (fp32 accumulation, fp32 master weights); fp32 embedding table, optimizer state and exchange",
+                "regions": f"{R} timed regions of {K} steps per measurement, device-resident and end-to-end regions interleaved; "
+                           "the median region is reported",
             },
+            "comm": arm.comm_mode(),
             "clocks": clocks,
-            "e2e": {"value": value_e2e, "unit": "samples/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d_bytes,
-                    "d2h_bytes_per_step": 4, "last_loss": losses[-1] if losses else None},
-            "gpu_launches": launches,
+            "regions": {"ms_per_step": per_step(ms_a), "spread": round((max(ms_a) - min(ms_a)) / ms, 4),
+                        "new_rows_per_step": new_a, "reported": ia},
+            "e2e": {"value": value_e2e, "unit": "samples/s", "ms_per_step": ms_e2e / K, "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": 4, "last_loss": losses[-1] if losses else None,
+                    "regions": {"ms_per_step": per_step(ms_e), "spread": round((max(ms_e) - min(ms_e)) / ms_e2e, 4),
+                                "new_rows_per_step": new_e, "reported": ie}},
+            "gpu_launches": launches[ia],
         }
         if exposed is not None:
             line["exposed_all_to_all_ms"] = exposed
@@ -252,9 +279,6 @@ def run(args, arm):
             # largest status word over the ranks; 0 = every bounded wait was answered and no exchange window overflowed during the
             # whole run (bit 4: a wait ran out, bit 8: a window overflowed; either would invalidate the numbers above)
             line["exchange_status"] = status_bits
-        waits = arm.exposed_wait_ms(state) if hasattr(arm, "exposed_wait_ms") else {}
-        if waits:
-            line["exposed_wait_ms_per_wait"] = waits
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
@@ -322,6 +346,17 @@ class OursArm:
         import recis_b200
         return int(recis_b200.native().launch_count())
 
+    def table_rows(self, st, world):
+        """Rows in the table over all ranks (device counters; read between regions, outside all timing)."""
+        import torch
+        import torch.distributed as dist
+        n = sum(int(t.impl.size()) for t in st["model"].embedding_engine.tables().values())
+        if world > 1:
+            t = torch.tensor([n], dtype=torch.int64, device="cuda")
+            dist.all_reduce(t)
+            n = int(t.item())
+        return n
+
     SPAN_LABELS = ("ids", "emb", "grad_push", "grad_wait", "dense_allreduce_wait", "total")
 
     def exposed_comm_ms(self, st, host_batches, dev, world, steps):
@@ -337,8 +372,11 @@ class OursArm:
         batches = [self.to_device(b, dev) for b in host_batches[-steps:]]
         sync_all(world)
         err = None
+        exchanges = [t.fused for t in st["model"].embedding_engine.tables().values() if getattr(t, "fused", None) is not None]
         try:
             recorder.start()
+            for ex in exchanges:            # flag waits of these extra steps go through the accounting kernel
+                ex.wait_stats = torch.zeros(8 * world + 8, dtype=torch.int64, device=dev)
         except Exception as e:          # accounting must never take the benchmark down
             err = repr(e)
         for b in batches:
@@ -354,7 +392,20 @@ class OursArm:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         sync_all(world)
         out = dict(zip(self.SPAN_LABELS, [round(v, 4) for v in t.tolist()]))
-        out["how"] = "CUDA events around the exchange phases on the model's stream, max over ranks, %d extra steps" % len(batches)
+        out["how"] = ("spans: CUDA events around the exchange phases (transfer kernels included) on the model's stream; "
+                      "flag_wait_ms_per_step: time the flag-wait kernels really spent waiting for the last peer (device timer), "
+                      "summed over the waits of a step; both max over ranks, %d extra steps" % len(batches))
+        try:
+            waited = 0.0
+            for ex in exchanges:
+                sums = ex.wait_stats.cpu()
+                ex.wait_stats = None
+                waited += sum(float(sums[ch * world:(ch + 1) * world].max()) for ch in range(3)) / 1e6 / max(len(batches), 1)
+            tw = torch.tensor([waited], dtype=torch.float64, device=dev)
+            dist.all_reduce(tw, op=dist.ReduceOp.MAX)
+            out["flag_wait_ms_per_step"] = round(float(tw.item()), 4)
+        except Exception as e:
+            err = repr(e)
         if err:
             out["error"] = err
         return out
@@ -378,15 +429,6 @@ class OursArm:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             bits = int(t.item())
         return bits
-
-    def exposed_wait_ms(self, st):
-        """RECIS_WAIT_STATS=1 only: mean time per flag wait until its last peer arrived, per channel, over the whole run."""
-        out = {}
-        for table in st["model"].embedding_engine.tables().values():
-            ex = getattr(table, "fused", None)
-            if ex is not None:
-                out.update(ex.exposed_wait_ms())
-        return out
 
     def comm_mode(self):
         return os.environ.get("RECIS_COMM", "auto")

@@ -2,6 +2,8 @@
 
 Builds the same model, optimizers and synthetic batches as ``bench.py``, warms up, then
   * ``--mode kernels``: records three steps with ``torch.profiler`` and prints the kernels by device time (rank 0);
+  * ``--mode timeline``: records two steps and prints, for rank 0, every kernel of the second step in start order with its
+    stream, start offset and duration - shows what really overlaps when the exchange lanes run on two streams;
   * ``--mode host``: wraps every function of the native module with a wall-clock timer, runs twelve steps without any
     synchronisation and prints the host time per step and per native call (ranks 0 and 3) - a call that blocks on the GPU
     shows up here as milliseconds instead of microseconds.
@@ -25,7 +27,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="kernels", choices=["kernels", "host"])
+    ap.add_argument("--mode", default="kernels", choices=["kernels", "host", "timeline"])
     ap.add_argument("--batch-per-gpu", type=int, default=8192)
     ap.add_argument("--capacity", type=int, default=0)
     ap.add_argument("--all-ranks", action="store_true", help="kernels mode: every rank prints its ten heaviest kernels")
@@ -92,6 +94,41 @@ def main():
                     print(f"[rank {rank}] " + "; ".join(f"{k[:40]} {t:.3f} ms" for t, k in rows), flush=True)
                 if world > 1:
                     dist.barrier()
+    elif a.mode == "timeline":
+        import json
+        import tempfile
+        from torch.profiler import ProfilerActivity, profile
+        marks = []
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(8, 10):
+                arm.step(st, devb[i])
+                ev = torch.cuda.Event(enable_timing=False)
+                marks.append(ev)
+            torch.cuda.synchronize()
+        if rank == 0:
+            with tempfile.TemporaryDirectory() as td:
+                path = os.path.join(td, "trace.json")
+                prof.export_chrome_trace(path)
+                with open(path) as fh:
+                    trace = json.load(fh)
+            ks = [e for e in trace["traceEvents"] if e.get("cat") in ("kernel", "gpu_memcpy", "gpu_memset") and "dur" in e]
+            ks.sort(key=lambda e: e["ts"])
+            # second step = the kernels after the midpoint gap: split at the launch of the second step's first encode/dedup kernel
+            names = [e["name"] for e in ks]
+            firsts = [i for i, n in enumerate(names) if "encode_merge" in n]
+            per_step = len(firsts) // 2 if len(firsts) >= 2 else 0
+            begin = firsts[per_step] if per_step else 0
+            t0 = ks[begin]["ts"]
+            streams = {}
+            busy = collections.defaultdict(float)
+            print(f"timeline of one step on rank 0 ({len(ks) - begin} device activities); columns: start ms, duration ms, stream, name")
+            for e in ks[begin:]:
+                sid = streams.setdefault(e["args"].get("stream", 0), len(streams))
+                busy[sid] += e["dur"] / 1e3
+                if e["dur"] >= 15:           # microseconds: list what matters, count the rest
+                    print(f"{(e['ts'] - t0) / 1e3:8.3f} {e['dur'] / 1e3:7.3f}  s{sid}  {e['name'][:70]}")
+            end = max(e["ts"] + e["dur"] for e in ks[begin:])
+            print(f"step span {(end - t0) / 1e3:.3f} ms; busy per stream: " + ", ".join(f"s{k} {v:.3f} ms" for k, v in sorted(busy.items())))
     else:
         acc.clear()
         steps = []

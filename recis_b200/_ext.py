@@ -30,19 +30,35 @@ CXX_FLAGS = ["-O3", "-std=c++17", "-fopenmp", "-Wno-unused-variable", "-Wno-sign
 
 
 def _openmp_ldflags():
-    """Link flags for the OpenMP runtime. Some toolchains ship libgomp without its spec file, so ``-fopenmp`` fails at link time;
-    the compiler itself is asked where its libgomp lives instead of assuming a directory."""
+    """Link flags for the C++ and OpenMP runtimes, resolved through the compiler instead of assuming a directory. Two things can
+    go wrong on a toolchain whose driver is wrapped: ``-fopenmp`` at link time needs libgomp's spec file, which may be missing,
+    and without the directory of the shared ``libstdc++`` on the search path the static one is linked, after which C++ exceptions
+    thrown in this library (every ``TORCH_CHECK``) no longer unwind cleanly next to libtorch's dynamic one."""
     import shutil
     import subprocess
-    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
-    for name in ("libgomp.so", "libgomp.so.1"):
-        try:
-            path = subprocess.run([cxx, f"-print-file-name={name}"], capture_output=True, text=True, check=True).stdout.strip()
-        except Exception:
-            continue
-        if os.path.isabs(path) and os.path.exists(path):
-            return [os.path.realpath(path)]          # the shared object itself: no search path, no spec file needed
-    return ["-lgomp"]
+    # every C++ driver that can be found: a wrapper in front of the real one may not know the real one's library directories
+    drivers = []
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), "/usr/bin/g++", "/usr/bin/c++"):
+        if cand and cand not in drivers and os.path.exists(cand):
+            drivers.append(cand)
+
+    def where(name):
+        for cxx in drivers:
+            try:
+                path = subprocess.run([cxx, f"-print-file-name={name}"], capture_output=True, text=True, check=True).stdout.strip()
+            except Exception:
+                continue
+            if os.path.isabs(path) and os.path.exists(path):
+                return path
+        return None
+
+    flags = []
+    stdcxx = where("libstdc++.so")
+    if stdcxx:
+        flags.append(f"-L{os.path.dirname(stdcxx)}")
+    gomp = where("libgomp.so") or where("libgomp.so.1")
+    flags.append(os.path.realpath(gomp) if gomp else "-lgomp")       # the shared object itself: no spec file needed
+    return flags
 
 
 def _sources():

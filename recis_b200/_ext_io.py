@@ -55,6 +55,12 @@ def is_built() -> bool:
     return os.path.exists(_so()) and os.path.exists(stamp) and open(stamp).read().strip() == _hash()
 
 
+def _stdcxx_dir():
+    """The directory of the shared libstdc++ (so that it, not a static copy, is linked): same lookup as the main extension."""
+    from . import _ext
+    return [f for f in _ext._openmp_ldflags() if f.startswith("-L")]
+
+
 def build(verbose: bool = False):
     import torch  # noqa: F401
     from torch.utils import cpp_extension
@@ -62,7 +68,7 @@ def build(verbose: bool = False):
     os.makedirs(_BUILD, exist_ok=True)
     cpp_extension.load(
         name=_NAME, sources=[_SRC], extra_cflags=["-O2", "-std=c++20", "-Wno-sign-compare", "-Wno-deprecated-declarations"],
-        extra_ldflags=[f"-L{libdir}"] + [f"-l:{lib}" for lib in libs] + [f"-Wl,-rpath,{libdir}"],
+        extra_ldflags=_stdcxx_dir() + [f"-L{libdir}"] + [f"-l:{lib}" for lib in libs] + [f"-Wl,-rpath,{libdir}"],
         extra_include_paths=[inc, "/usr/local/cuda/include"], build_directory=_BUILD, with_cuda=False, is_python_module=True, verbose=verbose)
     with open(os.path.join(_BUILD, "source.sha256"), "w") as fh:
         fh.write(_hash())

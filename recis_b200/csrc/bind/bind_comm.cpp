@@ -113,7 +113,7 @@ void comm_wait(const Tensor& flags, int64_t channel, int64_t world, int64_t epoc
 void comm_pull_ids(const std::vector<int64_t>& peer_ids, const std::vector<int64_t>& peer_offsets, const std::vector<int64_t>& peer_counts,
                    int64_t me, Tensor ids_in, Tensor prefix, Tensor n_in, OptT demand, Tensor status) {
   const int world = (int)peer_ids.size();
-  TORCH_CHECK(prefix.numel() >= 3 * world + 1 && prefix.scalar_type() == torch::kInt32, "prefix: int32 [3 * world + 1]");
+  TORCH_CHECK(prefix.numel() >= 4 * world + 2 && prefix.scalar_type() == torch::kInt32, "prefix: int32 [4 * world + 2]");
   RbPeers counts = peers_of(peer_counts);
   int32_t* dm = demand.has_value() && demand->defined() ? demand->data_ptr<int32_t>() : nullptr;
   if (!ids_in.is_cuda()) {

@@ -20,6 +20,10 @@ inline const float* opt_f32(const OptT& t) { return t.has_value() && t->defined(
 
 int64_t pow2_at_least(int64_t x) { int64_t p = 64; while (p < x) p <<= 1; return p; }
 
+}  // namespace
+
+namespace rbx {
+
 // ids -> (unique ids bucketed by owner rank, reverse index, per-owner counts, per-owner offsets)
 // unique_out / offsets_out (optional) let the caller place the results in peer-visible memory.
 std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, int64_t world, OptT unique_out, OptT offsets_out,
@@ -54,6 +58,11 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> dedup_partition(const Tensor& ids, in
   }
   return {unique_ids, reverse, counts, offsets};
 }
+
+}  // namespace rbx
+
+namespace {
+using rbx::dedup_partition;
 
 // desc: int64 [4, F+1] (id pointers, nnz prefix, offsets pointers, segment prefix) on the target device.
 std::tuple<Tensor, Tensor> encode_merge(const Tensor& desc, const Tensor& table_idx, int64_t F, int64_t total_nnz, int64_t total_seg,
@@ -170,6 +179,9 @@ std::tuple<Tensor, Tensor, Tensor> tile_forward(const Tensor& base, OptT rows, c
   return {out, gsrc, gscale};
 }
 
+}  // namespace
+
+namespace rbx {
 // reverse index -> (csr_u, csr_elem, start): elements grouped by unique index, stable in element order.
 std::tuple<Tensor, Tensor, Tensor> build_csr(const Tensor& reverse) {
   TORCH_CHECK(reverse.scalar_type() == torch::kInt32 && reverse.is_contiguous());
@@ -190,6 +202,10 @@ std::tuple<Tensor, Tensor, Tensor> build_csr(const Tensor& reverse) {
   }
   return {csr_u, csr_elem, start};
 }
+}  // namespace rbx
+
+namespace {
+using rbx::build_csr;
 
 RbOpt make_opt(int64_t kind, double lr, double beta1, double beta2, double eps, double decay, double alpha, double grad_scale,
                const OptT& w, const OptT& s1, const OptT& s2) {

@@ -8,6 +8,7 @@ void init_ragged(pybind11::module& m);
 void init_serialize(pybind11::module& m);
 void init_metrics(pybind11::module& m);
 void init_io(pybind11::module& m);
+void init_exchange(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "recis_b200 native extension (sm_100a kernels + CPU implementations)";
@@ -18,4 +19,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   init_serialize(m);
   init_metrics(m);
   init_io(m);
+  init_exchange(m);
 }

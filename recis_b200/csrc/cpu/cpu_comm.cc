@@ -101,6 +101,10 @@ void rbc_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_coun
     }
     prefix_out[2 * world + 1 + o] = base;
   }
+  {
+    const int32_t* own = reinterpret_cast<const int32_t*>(peer_offsets.p[me]);       // this rank's own boundaries, kept for the backward
+    for (int w = 0; w <= world; ++w) prefix_out[3 * world + 1 + w] = own[w];
+  }
   const int64_t n_in = prefix_out[world];
   *n_in_out = (int32_t)n_in;
   if (demand != nullptr && peer_counts.p[0] != nullptr) {

@@ -119,7 +119,7 @@ __device__ __forceinline__ int find_src(const int32_t* prefix, int world, int64_
 
 // Owner: gather the ids every requester bucketed for me. peer_offsets[r] -> int32[world+1] of requester r (boundaries
 // clamped to its window), peer_ids[r] -> its bucketed unique ids, peer_counts[r] -> int32[world] unclamped per-owner unique
-// counts of requester r (what it wanted to send). Writes ids_in, prefix[3*world+1] and n_in. Everything published in prefix is
+// counts of requester r (what it wanted to send). Writes ids_in, prefix[4*world+2] and n_in. Everything published in prefix is
 // clamped to in_cap: a window that is too small drops ids (and sets the overflow bit), it never makes a later kernel index
 // past a buffer. demand[0..1] (nullable) keep running maxima over ALL ranks of (unique ids one requester wanted to send,
 // ids one owner was asked for): every rank computes the same two numbers from the same W x W counts, which is what lets the
@@ -156,6 +156,12 @@ pull_ids_kernel(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_counts, int
         base += off[o + 1] - off[o];
       }
       prefix_out[2 * world + 1 + o] = base;
+    }
+    // prefix_out[3*world+1 ..]: a copy of THIS rank's own bucket boundaries [world+1] (its offsets window is rewritten by its
+    // next forward pass; the backward pass needs this step's)
+    {
+      const int32_t* own = reinterpret_cast<const int32_t*>(peer_offsets.p[me]);
+      for (int w = threadIdx.x; w <= world; w += blockDim.x) prefix_out[3 * world + 1 + w] = own[w];
     }
     if (threadIdx.x == 0) *n_in_dev = (int32_t)n_in;
     if (demand != nullptr && peer_counts.p[0] != nullptr && threadIdx.x < world) {

@@ -24,8 +24,9 @@ void rb_comm_wait_timed(const int64_t* flags, int channel, int world, int64_t ep
 // peer_counts (entries may be null) and demand (nullable, int32[2]): see pull_ids_kernel; prefix_out is clamped to in_cap
 void rb_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_counts, int me, int world, int64_t* ids_in, int64_t in_cap,
                       int32_t* prefix_out, int32_t* n_in_dev, int32_t* demand, int64_t* status, cudaStream_t st);
-// prefix: int32[3*world+1] written by rb_comm_pull_ids = per-source prefix sums [world+1], per-source window offsets
-// [world], and for every owner o the first row of this rank's bucket inside o's incoming order [world]
+// prefix: int32[4*world+2] written by rb_comm_pull_ids = per-source prefix sums [world+1], per-source window offsets
+// [world], for every owner o the first row of this rank's bucket inside o's incoming order [world], and a copy of this
+// rank's own bucket boundaries [world+1]
 // blocks > 0 caps the grid size (the kernel is NVLink-bound; a small grid leaves SMs to concurrent kernels)
 void rb_comm_push_emb(const float* emb, const int32_t* rows_in, const int32_t* prefix, RbPeers peer_uemb, int me, int world, int D,
                       int64_t n_in_max, int blocks, cudaStream_t st);

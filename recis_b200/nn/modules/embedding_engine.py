@@ -155,38 +155,48 @@ class EmbeddingEngine(nn.Module):
 
     def _coalesce(self, feats, device):
         """Concatenate formatted features: one kernel prefixes ids and rebases offsets for all of them."""
-        F = len(feats)
-        nnz = [f["ids"].numel() for f in feats]
-        segs = [f["n_seg"] for f in feats]
-        nnz_prefix = [0]
-        seg_prefix = [0]
-        for a, b in zip(nnz, segs):
-            nnz_prefix.append(nnz_prefix[-1] + a)
-            seg_prefix.append(seg_prefix[-1] + b)
-        rows = [[f["ids"].data_ptr() for f in feats] + [0], nnz_prefix, [f["offsets"].data_ptr() for f in feats] + [0], seg_prefix,
-                [f["child"] for f in feats] + [0]]
+        return self._coalesce_many([feats], device)[0]
+
+    def _coalesce_many(self, parts, device):
+        """``_coalesce`` for several feature lists at once (the lanes of one runtime group): the descriptor tables of all of them
+        travel to the device in ONE asynchronous copy, then one kernel per list prefixes ids and rebases offsets."""
+        blocks, metas = [], []
+        for feats in parts:
+            F = len(feats)
+            nnz_prefix, seg_prefix = [0], [0]
+            for f in feats:
+                nnz_prefix.append(nnz_prefix[-1] + f["ids"].numel())
+                seg_prefix.append(seg_prefix[-1] + f["n_seg"])
+            blocks.append([f["ids"].data_ptr() for f in feats] + [0] + nnz_prefix + [f["offsets"].data_ptr() for f in feats] + [0]
+                          + seg_prefix + [f["child"] for f in feats] + [0])
+            metas.append((F, nnz_prefix[-1], seg_prefix[-1]))
+        flat = [x for b in blocks for x in b]
         if device.type == "cuda":
-            # descriptor table: a small ring of pinned staging buffers (no pinned allocation per step), copied asynchronously
-            ring = self._desc_ring.setdefault((F, device), dict(bufs=[torch.empty(5, F + 1, dtype=torch.int64).pin_memory() for _ in range(4)],
-                                                                evs=[None] * 4, head=0))
+            # descriptor tables: a small ring of pinned staging buffers (no pinned allocation per step), copied asynchronously
+            ring = self._desc_ring.setdefault((len(flat), device), dict(bufs=[torch.empty(len(flat), dtype=torch.int64).pin_memory() for _ in range(4)],
+                                                                        evs=[None] * 4, head=0))
             k = ring["head"] % 4
             ring["head"] += 1
             if ring["evs"][k] is not None:
-                ring["evs"][k].synchronize()          # the copy issued four steps ago has long finished; this never waits in practice
-            ring["bufs"][k].copy_(torch.tensor(rows, dtype=torch.int64))
+                ring["evs"][k].synchronize()          # the copy issued four uses ago has long finished; this never waits in practice
+            ring["bufs"][k].copy_(torch.tensor(flat, dtype=torch.int64))
             both = ring["bufs"][k].to(device, non_blocking=True)
             ev = torch.cuda.Event()
             ev.record()
             ring["evs"][k] = ev
         else:
-            both = torch.tensor(rows, dtype=torch.int64)
-        desc, tidx = both[:4], both[4, :F]
-        ids, offsets = native().encode_merge(desc, tidx, F, nnz_prefix[-1], seg_prefix[-1], True)
-        weights = None
-        if any(f["weight"] is not None for f in feats):
-            ws = [f["weight"] if f["weight"] is not None else torch.ones(f["ids"].numel(), device=device) for f in feats]
-            weights = torch.cat(ws) if len(ws) > 1 else ws[0]
-        return ids, offsets, weights
+            both = torch.tensor(flat, dtype=torch.int64)
+        out, pos = [], 0
+        for feats, (F, nnz, segs) in zip(parts, metas):
+            blk = both[pos:pos + 5 * (F + 1)].view(5, F + 1)
+            pos += 5 * (F + 1)
+            ids, offsets = native().encode_merge(blk[:4], blk[4, :F], F, nnz, segs, True)
+            weights = None
+            if any(f["weight"] is not None for f in feats):
+                ws = [f["weight"] if f["weight"] is not None else torch.ones(f["ids"].numel(), device=device) for f in feats]
+                weights = torch.cat(ws) if len(ws) > 1 else ws[0]
+            out.append((ids, offsets, weights))
+        return out
 
     # ------------------------------------------------------------------ lanes
     @staticmethod
@@ -217,8 +227,16 @@ class EmbeddingEngine(nn.Module):
         bounds.append(n)
         return bounds
 
-    def _use_lanes(self, ht, feats, opt) -> bool:
-        return (self._lanes > 1 and len(feats) >= 2 and opt.combiner != "tile" and getattr(ht, "fused", None) is not None)
+    def _use_lanes(self, ht, feats, opt, n_groups) -> bool:
+        """The lane pipeline (one native call per forward / backward of the whole group) serves every pooled lookup of the
+        peer-memory exchange, with one lane when lanes are off; ``tile`` lookups and the staged mode for several groups
+        (``RECIS_STAGE_EXCHANGE``) take the per-group path."""
+        ex = getattr(ht, "fused", None)
+        if ex is None or opt.combiner == "tile":
+            return False
+        if ex.stage_enabled and n_groups > 1:
+            return False
+        return self._lanes > 1 or ex.native_executor
 
     def _lookup_in_lanes(self, ht, feats, opt, run_key, dev, perm):
         """One runtime group as a pipeline of exchange lanes (``FusedExchange.forward_group``). Returns the pooled rows of the
@@ -227,9 +245,10 @@ class EmbeddingEngine(nn.Module):
         bounds = self._lane_ranges([f["child"] for f in feats], self._lanes)
         L = len(bounds) - 1
         parts, seg_off = [], 0
+        merged = self._coalesce_many([feats[bounds[i]:bounds[i + 1]] for i in range(L)], dev)
         for i in range(L):
             part = feats[bounds[i]:bounds[i + 1]]
-            ids, offsets, weights = self._coalesce(part, dev)
+            ids, offsets, weights = merged[i]
             key = f"{run_key}#lane{i}of{L}"
             ht.fused.lane_children[key] = frozenset(f["child"] for f in part)
             n_seg = sum(f["n_seg"] for f in part)
@@ -272,7 +291,7 @@ class EmbeddingEngine(nn.Module):
                 perm = None
                 if self._interleave and opt.combiner != "tile" and len(set(segs)) == 1 and len(feats) > 1:
                     perm = (segs[0], len(feats))
-                lanes = self._use_lanes(ht, feats, opt)
+                lanes = self._use_lanes(ht, feats, opt, n_groups)
                 ids = offsets = weights = prepared = None
                 if not lanes:
                     ids, offsets, weights = self._coalesce(feats, dev)

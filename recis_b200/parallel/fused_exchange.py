@@ -82,13 +82,10 @@ class _Lane:
         else:
             cap = _round_up(max(need_out * HEADROOM, 1024))
             in_cap = _round_up(max(need_in * HEADROOM, 1024))
-        self.epoch = 0
-        self.steps = 0
-        self.pending_grad_epoch = 0      # a staged, not yet consumed gradient window
         self.warned = False
-        self.last_train_epoch = 0        # epoch of the newest forward that will be back-propagated
         self.grown = 0
         self.heap = None
+        self.native = None               # the C++ twin of this object: windows, peer pointers, counters, demand ring
         self.children = None             # child tables this lane's ids belong to (None: unknown)
         self._alloc(cap, in_cap)
 
@@ -104,36 +101,29 @@ class _Lane:
             "uemb": (torch.float32, self.send_cap * D),
             "gin": (torch.float32, self.in_cap * D),
         }, ex.device, ex.pg)
-        self.ids_in = torch.empty(self.in_cap, dtype=torch.int64, device=ex.device)
-        self.prefix = torch.zeros(3 * W + 1, dtype=torch.int32, device=ex.device)
-        self.n_in = torch.zeros(1, dtype=torch.int32, device=ex.device)
-        self.demand = torch.zeros(2, dtype=torch.int32, device=ex.device)       # running maxima, see pull_ids_kernel
-        if ex.device.type == "cuda":
-            self._ring = [torch.zeros(2, dtype=torch.int32).pin_memory() for _ in range(GROW_RING)]
-            self._ring_ev = [None] * GROW_RING
-        else:
-            self._ring = [torch.zeros(2, dtype=torch.int32) for _ in range(GROW_RING)]
-            self._ring_ev = [None] * GROW_RING
-        self._ring_step = [-1] * GROW_RING
+        counters = (0, 0, 0, 0) if self.native is None else (self.epoch, self.steps, self.last_train_epoch, self.pending_grad_epoch)
+        h = self.heap
+        self.native = native().ExLane(W, ex.rank, D, self.send_cap, self.in_cap, {k: h[k].tensor for k in h.regions},
+                                      {k: h[k].ptrs for k in h.regions})
+        self.epoch, self.steps, self.last_train_epoch, self.pending_grad_epoch = counters     # flag epochs only ever grow
+        self.ids_in, self.n_in, self.demand = self.native.ids_in, self.native.n_in, self.native.demand
+        self.prefix = torch.zeros(4 * W + 2, dtype=torch.int32, device=ex.device)
+
+    # counters shared with the native executor
+    epoch = property(lambda self: self.native.epoch, lambda self, v: setattr(self.native, "epoch", int(v)))
+    steps = property(lambda self: self.native.steps, lambda self, v: setattr(self.native, "steps", int(v)))
+    last_train_epoch = property(lambda self: self.native.last_train_epoch, lambda self, v: setattr(self.native, "last_train_epoch", int(v)))
+    pending_grad_epoch = property(lambda self: self.native.pending_grad_epoch,
+                                  lambda self, v: setattr(self.native, "pending_grad_epoch", int(v)))
 
     # ---- demand mirror: the device's "largest demand so far" comes back without anybody waiting for it
     def post_demand(self):
-        k = self.steps % GROW_RING
-        self._ring[k].copy_(self.demand, non_blocking=True)
-        self._ring_step[k] = self.steps
-        if self.ex.device.type == "cuda":
-            ev = torch.cuda.Event()
-            ev.record()
-            self._ring_ev[k] = ev
+        self.native.post_demand()
 
     def demand_of(self, step: int):
         """(out, in) demand as measured at lookup ``step`` of this lane, or None when that slot has been reused."""
-        k = step % GROW_RING
-        if step < 0 or self._ring_step[k] != step:
-            return None
-        if self._ring_ev[k] is not None:
-            self._ring_ev[k].synchronize()        # issued GROW_LAG lookups ago: it has landed, this does not stall
-        return int(self._ring[k][0]), int(self._ring[k][1])
+        d = self.native.demand_of(int(step))
+        return None if d[0] < 0 else d
 
     def grow(self, need_out: int, need_in: int):
         """Collective: every rank calls this at the same lookup with the same numbers. Nothing of this lane is in flight when the
@@ -186,6 +176,8 @@ class FusedExchange:
         self.push_blocks = int(os.environ.get("RECIS_PUSH_BLOCKS", "296"))
         self.grad_push_blocks = int(os.environ.get("RECIS_GRAD_PUSH_BLOCKS", "592"))
         self._link = None                  # the link stream (created with the first multi-lane lookup)
+        # RECIS_EXCHANGE_NATIVE=0 issues the lane pipeline from Python instead of the native executor (same launches, same order)
+        self.native_executor = os.environ.get("RECIS_EXCHANGE_NATIVE", "1") != "0"
         # lane key -> frozenset of child-table indices whose rows the lane can touch (set by the engine); two staged gradient
         # records may be applied one after the other only when their lanes are known to share no row
         self.lane_children = {}
@@ -354,8 +346,9 @@ class FusedExchange:
                 self._pull(lane, e, count_admit)
         rows_in = self._lookup(emb_mod, lane, readonly, threshold, step)
         prefix = lane.prefix.clone()
-        # the offsets window is rewritten by this lane's next forward; the backward needs this step's boundaries
-        offsets_now = lane.heap["offsets"].tensor.clone()
+        # the offsets window is rewritten by this lane's next forward; the backward needs this step's boundaries, which the pull
+        # kernel copied behind the prefix sums
+        offsets_now = prefix[3 * self.world + 1:]
         return rows_in, prefix, offsets_now
 
     def _push(self, emb_mod, lane, e, rows_in, prefix, blocks=0):
@@ -410,6 +403,8 @@ class FusedExchange:
             C = native()
             D = self.D
             cuda = not self.host
+            if not self.strict and self.native_executor:
+                return self._forward_group_native(emb_mod, parts, mode, perm_b, perm_total, n_rows, train, readonly, threshold, step)
             main = torch.cuda.current_stream(self.device) if cuda else None
             link = self._link_stream() if cuda and len(parts) > 1 else None
             out = torch.empty(n_rows, D, dtype=torch.float32, device=self.device)
@@ -450,6 +445,30 @@ class FusedExchange:
                     saved.append(dict(rev=rev, gsrc=gsrc, gscale=gscale, rows_in=rows_in, prefix=prefix, epoch=e, lane=lane, heap=h,
                                       offsets=offsets_now))
             return out, (saved if train else None)
+
+    def _forward_group_native(self, emb_mod, parts, mode, perm_b, perm_total, n_rows, train, readonly, threshold, step):
+        """The same launch order issued by ONE native call (``csrc/bind/bind_exchange.cpp``); growth decisions stay here."""
+        C = native()
+        lanes = []
+        for part in parts:
+            lane = self._lane(part["key"], part["ids"])
+            if lane.pending_grad_epoch and not self.immediate_reduce:
+                self._flush_pending(emb_mod.impl, lane)
+            d = lane.demand_of(lane.steps - GROW_LAG)
+            if d is not None and (d[0] > GROW_AT * lane.send_cap or d[1] > GROW_AT * lane.in_cap):
+                lane.grow(d[0], d[1])
+            lanes.append(lane)
+        link = self._link_stream().cuda_stream if (not self.host and len(parts) > 1) else 0
+        out, saved_t, epochs = C.exchange_forward_group(
+            [l.native for l in lanes], emb_mod.impl.store, [p["ids"] for p in parts], [p["offsets"] for p in parts],
+            [p["weights"] for p in parts], [int(p["perm_f"]) for p in parts], [int(p["perm_off"]) for p in parts], mode, perm_b,
+            perm_total, n_rows, train, readonly, threshold, step, self.status, self.wait_us, self.wait_stats, link, self.push_blocks)
+        if not train:
+            return out, None
+        W = self.world
+        saved = [dict(rev=t[0], gsrc=t[1], gscale=t[2], rows_in=t[3], prefix=t[4], offsets=t[4][3 * W + 1:], epoch=e, lane=lane,
+                      heap=lane.heap) for t, e, lane in zip(saved_t, epochs, lanes)]
+        return out, saved
 
     # ------------------------------------------------------------------ backward (requester side) + staging
     def backward(self, emb_mod, s, grad_out, worker_scale):
@@ -505,6 +524,14 @@ class FusedExchange:
             self._check_epoch(s)
         C = native()
         cuda = not self.host
+        if self.native_executor:
+            link = self._link_stream().cuda_stream if (cuda and len(saved) > 1) else 0
+            C.exchange_backward_group([s["lane"].native for s in saved],
+                                      [[s["rev"], s["gsrc"], s["gscale"], s["rows_in"], s["prefix"]] for s in saved],
+                                      [int(s["epoch"]) for s in saved], grad_out, self.status, link, self.grad_push_blocks)
+            for s in saved:
+                self._stage(emb_mod, s, worker_scale)
+            return
         link = self._link_stream() if cuda and len(saved) > 1 else None
         main = torch.cuda.current_stream(self.device) if cuda else None
         if link is not None:

@@ -34,7 +34,7 @@ def run_loopback(dev, world, dim):
     ids_in, prefix, rows_in, tables, owned = [], [], [], [], []
     for o in range(W):
         buf = torch.zeros(in_cap, dtype=torch.int64, device=dev)
-        meta = torch.zeros(3 * W + 1, dtype=torch.int32, device=dev)
+        meta = torch.zeros(4 * W + 2, dtype=torch.int32, device=dev)
         n_in = torch.zeros(1, dtype=torch.int32, device=dev)
         C.comm_pull_ids(ptrs(ids_win), ptrs(off_win), ptrs(cnt_win), o, buf, meta, n_in, demand, status)
         n = int(n_in.item())
@@ -124,7 +124,7 @@ def run_loopback_overflow(dev, world, dim):
     metas, rows_all, tables = [], [], []
     for o in range(W):
         buf = torch.full((in_cap + guard,), -5, dtype=torch.int64, device=dev)
-        meta = torch.zeros(3 * W + 1, dtype=torch.int32, device=dev)
+        meta = torch.zeros(4 * W + 2, dtype=torch.int32, device=dev)
         n_in = torch.zeros(1, dtype=torch.int32, device=dev)
         C.comm_pull_ids(ptrs(ids_win), ptrs(off_win), ptrs(cnt_win), o, buf[:in_cap], meta, n_in, demand, status)
         n = int(n_in.item())

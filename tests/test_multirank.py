@@ -299,7 +299,7 @@ def test_exchange_lanes_on_cpu_ranks_equal_the_single_lane_run():
             assert all(torch.allclose(x[n], y[n], atol=1e-6) for n in x)
 
 
-def _shared_child_lanes_fn(rank, world, lanes, interleave):
+def _shared_child_lanes_fn(rank, world, lanes, interleave, device_kind="cpu"):
     """Six features over four child tables: f1 and f2 share ``s1``, f4 and f5 share ``s3``. Lanes must keep the features of one
     child together; a row that landed in two lanes would be updated twice per step."""
     import torch
@@ -307,27 +307,28 @@ def _shared_child_lanes_fn(rank, world, lanes, interleave):
     from recis_b200.nn.initializers import NormalInitializer
     from recis_b200.optim import SparseAdam
     torch.manual_seed(13)
+    dev = torch.device("cuda", rank) if device_kind == "cuda" else torch.device("cpu")
     init = NormalInitializer(0, 0.05)
     shared = {"f0": "s0", "f1": "s1", "f2": "s1", "f3": "s2", "f4": "s3", "f5": "s3"}
-    eng = EmbeddingEngine({n: EmbeddingOption(embedding_dim=8, shared_name=sn, combiner="sum", initializer=init) for n, sn in shared.items()},
-                          interleave=interleave, exchange_lanes=lanes)
+    eng = EmbeddingEngine({n: EmbeddingOption(embedding_dim=8, shared_name=sn, combiner="sum", initializer=init, device=dev)
+                           for n, sn in shared.items()}, interleave=interleave, exchange_lanes=lanes)
     opt = SparseAdam(filter_out_sparse_param(eng), lr=0.05)
     outs = []
     for step in range(3):
         g = torch.Generator().manual_seed(10 * step + rank)
-        feats = {n: torch.randint(0, 40, (12, 2), generator=g) * 7919 for n in shared}       # small id range: f1/f2 and f4/f5 collide a lot
-        coef = {n: torch.randn(12, 8, generator=g) for n in shared}
+        feats = {n: (torch.randint(0, 40, (12, 2), generator=g) * 7919).to(dev) for n in shared}   # small id range: f1/f2 and f4/f5 collide a lot
+        coef = {n: torch.randn(12, 8, generator=g).to(dev) for n in shared}
         opt.zero_grad()
         out = eng(feats)
         sum((out[n] * coef[n]).sum() for n in shared).backward()
         opt.step()
-        outs.append({n: out[n].detach().clone() for n in shared})
+        outs.append({n: out[n].detach().cpu().clone() for n in shared})
     (table,) = eng.tables().values()
     n_lanes = len(table.fused.lanes)
     table.fused.check()
     ids, rows = table.impl.ids_map()
     order = torch.argsort(ids)
-    return {"outs": outs, "ids": ids[order], "emb": table.impl.store.emb()[rows[order]].clone(), "n_lanes": n_lanes}
+    return {"outs": outs, "ids": ids[order].cpu(), "emb": table.impl.store.emb()[rows[order]].cpu().clone(), "n_lanes": n_lanes}
 
 
 @pytest.mark.parametrize("interleave", [True, False])
@@ -357,25 +358,27 @@ def test_lane_ranges_never_split_a_child():
     assert b[0] == 0 and b[-1] == 26 and len(b) == 5 and all(y > x for x, y in zip(b, b[1:]))
 
 
-def _skewed_ids_fn(rank, world, strict):
+def _skewed_ids_fn(rank, world, strict, device_kind="cpu"):
     """Every id is a multiple of 65536, so rank 0 owns all of them: the receive window of rank 0 is asked for world times what
     a balanced batch would bring. Step 1 sizes the windows from a small batch, step 2 is four times larger."""
     import torch
     from recis_b200.nn import EmbeddingEngine, EmbeddingOption
     from recis_b200.nn.initializers import NormalInitializer
     torch.manual_seed(3)
+    dev = torch.device("cuda", rank) if device_kind == "cuda" else torch.device("cpu")
     eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name=f"skewed_{strict}", initializer=NormalInitializer(0, 0.05),
-                                                exchange_strict=strict)})
+                                                exchange_strict=strict, device=dev)})
     (table,) = eng.tables().values()
     outs, refs, errs = [], [], []
     os.environ["RECIS_COMM"] = "nccl"
     torch.manual_seed(3)
-    ref_eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name=f"skewed_{strict}_ref", initializer=NormalInitializer(0, 0.05))})
+    ref_eng = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=8, shared_name=f"skewed_{strict}_ref", initializer=NormalInitializer(0, 0.05),
+                                                    device=dev)})
     for step, n in enumerate((600, 2400, 2400, 2400, 2400)):
         g = torch.Generator().manual_seed(100 * step + rank)
-        ids = (torch.randperm(4000, generator=g)[:n] + 4000 * rank).view(-1, 2) * 65536
-        outs.append(eng({"a": ids})["a"].detach().clone())
-        refs.append(ref_eng({"a": ids})["a"].detach().clone())
+        ids = ((torch.randperm(4000, generator=g)[:n] + 4000 * rank).view(-1, 2) * 65536).to(dev)
+        outs.append(eng({"a": ids})["a"].detach().cpu().clone())
+        refs.append(ref_eng({"a": ids})["a"].detach().cpu().clone())
         try:
             table.fused.check()
             errs.append(None)
@@ -591,6 +594,32 @@ def test_gpu_ranks_match_single_process(comm):
     world = min(torch.cuda.device_count(), int(os.environ.get("RECIS_TEST_GPU_RANKS", "2")))   # 2 ranks by default; more on request
     results = run_ranks(_rank_fn, world, "nccl", args=("cuda",), env={"RECIS_COMM": comm, "NCCL_NVLS_ENABLE": "0"})
     _compare(results, _oracle(world), world)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("interleave", [True, False])
+def test_gpu_exchange_lanes_pipeline_matches_single_lane_cpu_ranks(interleave):
+    """Three lanes on two CUDA streams (link stream for the NVLink-bound kernels) on real peers against the single-lane run of
+    the exchange's host twin."""
+    _need_gpus(2)
+    gpu = run_ranks(_shared_child_lanes_fn, 2, "nccl", args=(3, interleave, "cuda"), env={"RECIS_COMM": "fused", "NCCL_NVLS_ENABLE": "0"})
+    cpu = run_ranks(_shared_child_lanes_fn, 2, "gloo", args=(1, interleave), env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    assert all(r["n_lanes"] == 3 for r in gpu)
+    for a, b in zip(gpu, cpu):
+        assert torch.equal(a["ids"], b["ids"]) and torch.allclose(a["emb"], b["emb"], atol=1e-5)
+        for x, y in zip(a["outs"], b["outs"]):
+            assert all(torch.allclose(x[n], y[n], atol=1e-5) for n in x)
+
+
+@pytest.mark.gpu
+def test_gpu_exchange_windows_grow_and_strict_mode_on_real_peers():
+    _need_gpus(2)
+    for strict in (False, True):
+        res = run_ranks(_skewed_ids_fn, 2, "nccl", args=(strict, "cuda"), env={"RECIS_COMM": "fused", "NCCL_NVLS_ENABLE": "0"})
+        for r in res:
+            assert r["grown"] >= 1 and r["same"][-1] and r["errs"][-1] is None
+            if strict:
+                assert all(r["same"]) and all(e is None for e in r["errs"])
 
 
 def _allreduce_fn(rank, world, device_kind="cuda"):
