@@ -306,24 +306,24 @@ class OursArm:
         return dict(model=model, sparse_opt=sparse_opt, dense_opt=dense_opt, reducer=reducer)
 
     def wrap_host(self, arrays, batch):
+        """The batch as the framework's packed host batch: every tensor of it inside one pinned buffer (``recis_b200.io.PackedBatch``)."""
         import numpy as np
         import torch
+        from recis_b200.io import PackedBatch
         from recis_b200.ragged import RaggedTensor
         out = {}
         for k, v in arrays.items():
             if isinstance(v, tuple):
-                out[k] = RaggedTensor(torch.from_numpy(v[0]).pin_memory(), [torch.from_numpy(v[1]).pin_memory()], dense_shape=(batch, -1))
+                out[k] = RaggedTensor(torch.from_numpy(v[0]), [torch.from_numpy(v[1])], dense_shape=(batch, -1))
             else:
-                out[k] = torch.from_numpy(np.ascontiguousarray(v)).pin_memory()
-        return out
+                out[k] = torch.from_numpy(np.ascontiguousarray(v))
+        return PackedBatch(out, pin=True)
 
     def nbytes(self, b):
-        from recis_b200.io.synthetic import batch_nbytes
-        return batch_nbytes(b)
+        return b.payload_bytes          # bytes of the batch's tensors (the buffer adds up to 255 bytes of padding per tensor)
 
     def to_device(self, b, dev):
-        from recis_b200.io.synthetic import to_device
-        return to_device(b, dev, non_blocking=True)
+        return b.to(dev, non_blocking=True)
 
     def feeder(self, host_batches, dev):
         from recis_b200.io import DevicePrefetcher

@@ -14,6 +14,7 @@
 #include "../cpu/rb_cpu_comm.h"
 #include "../kernels/rb_comm.h"
 #include "store.h"
+#include "bind_shared.h"
 
 namespace py = pybind11;
 using torch::Tensor;
@@ -128,28 +129,23 @@ void comm_pull_ids(const std::vector<int64_t>& peer_ids, const std::vector<int64
 
 void comm_push_emb(const Tensor& emb, const Tensor& rows_in, const Tensor& prefix, const std::vector<int64_t>& peer_uemb, int64_t me,
                    int64_t n_in_hint, int64_t blocks) {
-  const int D = (int)emb.size(1);
+  const int64_t row_bytes = emb.size(1) * emb.element_size();
   if (!emb.is_cuda()) {
-    rbc_comm_push_emb(emb.data_ptr<float>(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), peers_of(peer_uemb), (int)me,
-                      (int)peer_uemb.size(), D, n_in_hint);
+    rbc_comm_push_emb(emb.data_ptr(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), peers_of(peer_uemb), (int)me,
+                      (int)peer_uemb.size(), row_bytes, n_in_hint);
     return;
   }
-  TORCH_CHECK(D % 4 == 0, "the fused exchange needs an embedding width that is a multiple of 4");
+  TORCH_CHECK(row_bytes % 16 == 0, "the fused exchange needs rows that are a multiple of 16 bytes");
   c10::cuda::CUDAGuard g(emb.device());
-  rb_comm_push_emb(emb.data_ptr<float>(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), peers_of(peer_uemb), (int)me,
-                   (int)peer_uemb.size(), D, n_in_hint, (int)blocks, cur_stream());
+  rb_comm_push_emb(emb.data_ptr(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), peers_of(peer_uemb), (int)me,
+                   (int)peer_uemb.size(), row_bytes, n_in_hint, (int)blocks, cur_stream());
 }
 
 // apply: update rows of (w, s1, s2) in place. Otherwise returns (rows [n_in_max] with -1 holes, grads [n_in_max, D]).
 std::tuple<Tensor, Tensor> comm_owner_reduce(const Tensor& rows_in, Tensor head, const Tensor& prefix, const Tensor& g_in, int64_t world, int64_t D, bool mean_by_id, bool apply,
                                              int64_t kind, double lr, double beta1, double beta2, double eps, double decay, double alpha,
                                              double grad_scale, OptT w, OptT s1, OptT s2, int64_t n_in_hint, int64_t unroll) {
-  RbOpt o;
-  o.kind = (int)kind; o.lr = (float)lr; o.beta1 = (float)beta1; o.beta2 = (float)beta2; o.eps = (float)eps; o.decay = (float)decay;
-  o.alpha = (float)alpha; o.grad_scale = (float)grad_scale;
-  o.w = w.has_value() && w->defined() ? w->data_ptr<float>() : nullptr;
-  o.s1 = s1.has_value() && s1->defined() ? s1->data_ptr<float>() : nullptr;
-  o.s2 = s2.has_value() && s2->defined() ? s2->data_ptr<float>() : nullptr;
+  RbOpt o = rbx::make_opt(kind, lr, beta1, beta2, eps, decay, alpha, grad_scale, w, s1, s2);
   const int64_t n_max = rows_in.numel();
   auto next = torch::empty({n_max}, rows_in.options());
   Tensor out_rows, out_grads;
@@ -186,7 +182,7 @@ void comm_grad_reduce_push(const Tensor& grad_out, const Tensor& gsrc, const Ten
     const int64_t n_u = off[world];
     auto gu = torch::zeros({std::max<int64_t>(n_u, 1), D}, grad_out.options());
     RbOpt none{};
-    none.kind = RB_OPT_SGD; none.grad_scale = 1.f; none.decay = 1.f;
+    none.kind = RB_OPT_SGD; none.grad_scale = 1.f; none.decay = 1.f; none.w_dtype = 0;
     if (csr_u.numel() > 0)
       rbc_grad_reduce(grad_out.data_ptr<float>(), gsrc.data_ptr<int32_t>(), gscale.data_ptr<float>(), csr_u.data_ptr<int32_t>(),
                       csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>(), csr_u.numel(), (int)D, nullptr, gu.data_ptr<float>(), 0, none);

@@ -191,7 +191,8 @@ Tensor lane_lookup(ExLane& l, rbx::EmbeddingStore& store, bool readonly, int64_t
 // ---- owner: push the rows to the requesters (link stream when there is one), signal EMB
 void lane_push(const Ctx& c, ExLane& l, const Tensor& emb, const Tensor& rows_in, const Tensor& prefix, int64_t blocks) {
   if (!c.cuda) {
-    rbc_comm_push_emb(emb.data_ptr<float>(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), l.p_uemb, l.rank, l.world, l.D, l.in_cap);
+    rbc_comm_push_emb(emb.data_ptr(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), l.p_uemb, l.rank, l.world,
+                      (int64_t)l.D * emb.element_size(), l.in_cap);
     rbc_comm_signal(l.p_flags, RB_CH_EMB, l.rank, l.world, l.epoch);
     return;
   }
@@ -202,8 +203,8 @@ void lane_push(const Ctx& c, ExLane& l, const Tensor& emb, const Tensor& rows_in
     use_on_link(c, rows_in); use_on_link(c, prefix);
     st = c.link;
   }
-  rb_comm_push_emb(emb.data_ptr<float>(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), l.p_uemb, l.rank, l.world, l.D, l.in_cap,
-                   c.link != nullptr ? (int)blocks : 0, st);
+  rb_comm_push_emb(emb.data_ptr(), rows_in.data_ptr<int32_t>(), prefix.data_ptr<int32_t>(), l.p_uemb, l.rank, l.world,
+                   (int64_t)l.D * emb.element_size(), l.in_cap, c.link != nullptr ? (int)blocks : 0, st);
   rb_comm_signal(l.p_flags, RB_CH_EMB, l.rank, l.world, l.epoch, st);
 }
 
@@ -226,6 +227,7 @@ std::tuple<Tensor, std::vector<std::vector<Tensor>>, std::vector<int64_t>> excha
   auto out = torch::empty({n_rows, D}, torch::TensorOptions().dtype(torch::kFloat32).device(l0.flags.device()));
   std::vector<Tensor> rev(L), rows_in(L), prefix(L);
   Tensor emb = store->emb();
+  TORCH_CHECK(emb.scalar_type() == l0.uemb.scalar_type(), "the exchange windows carry ", l0.uemb.scalar_type(), " rows, the table stores ", emb.scalar_type());
   rev[0] = lane_begin(c, *lanes[0], ids[0]);
   for (size_t i = 0; i < L; ++i) {
     if (i + 1 < L) rev[i + 1] = lane_begin(c, *lanes[i + 1], ids[i + 1]);     // the next lane's ids are on offer before this lane waits
@@ -250,11 +252,11 @@ std::tuple<Tensor, std::vector<std::vector<Tensor>>, std::vector<int64_t>> excha
       TORCH_CHECK(perm_off[i] + n_seg <= n_rows, "lane rows exceed the shared output");
     }
     if (!c.cuda) {
-      rbc_pool_forward(l.uemb.data_ptr<float>(), nullptr, rev[i].data_ptr<int32_t>(), offsets[i].data_ptr<int32_t>(), wp, n_seg, D, (int)mode, pb,
+      rbc_pool_forward(l.uemb.data_ptr(), rbx::row_dtype_of(l.uemb), nullptr, rev[i].data_ptr<int32_t>(), offsets[i].data_ptr<int32_t>(), wp, n_seg, D, (int)mode, pb,
                        pf, (int)perm_off[i], (int)perm_total, out.data_ptr<float>(), train ? gsrc.data_ptr<int32_t>() : nullptr,
                        train ? gscale.data_ptr<float>() : nullptr);
     } else {
-      rb_pool_forward(l.uemb.data_ptr<float>(), nullptr, rev[i].data_ptr<int32_t>(), offsets[i].data_ptr<int32_t>(), wp, n_seg, D, (int)mode, pb,
+      rb_pool_forward(l.uemb.data_ptr(), rbx::row_dtype_of(l.uemb), nullptr, rev[i].data_ptr<int32_t>(), offsets[i].data_ptr<int32_t>(), wp, n_seg, D, (int)mode, pb,
                       pf, (int)perm_off[i], (int)perm_total, out.data_ptr<float>(), train ? gsrc.data_ptr<int32_t>() : nullptr,
                       train ? gscale.data_ptr<float>() : nullptr, c.main);
     }
@@ -292,7 +294,7 @@ void exchange_backward_group(std::vector<LanePtr> lanes, std::vector<std::vector
       const int64_t n_u = off[W];
       auto gu = torch::zeros({std::max<int64_t>(n_u, 1), D}, grad_out.options());
       RbOpt none{};
-      none.kind = RB_OPT_SGD; none.grad_scale = 1.f; none.decay = 1.f;
+      none.kind = RB_OPT_SGD; none.grad_scale = 1.f; none.decay = 1.f; none.w_dtype = 0;
       if (n > 0)
         rbc_grad_reduce(grad_out.data_ptr<float>(), gsrc.data_ptr<int32_t>(), gscale.data_ptr<float>(), csr_u.data_ptr<int32_t>(),
                         csr_elem.data_ptr<int32_t>(), start.data_ptr<int32_t>(), n, D, nullptr, gu.data_ptr<float>(), 0, none);

@@ -9,11 +9,14 @@
 //   drop/pad modes there; all four here), feature_cross_ragged (feature_cross_ragged_kernel.cu:22-418),
 //   gen_segment_indices (embedding_segment_reduce_kernel.cu:394-424), and the feature-engine fused ops' bindings.
 #include <torch/extension.h>
+#include "bind_shared.h"
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include "../common/rb_hash.cuh"
 #include "../common/rb_launch.h"
 #include "../kernels/rb_feature.h"
+#include <cub/device/device_segmented_sort.cuh>
+#include <algorithm>
 
 namespace py = pybind11;
 using torch::Tensor;
@@ -182,6 +185,11 @@ fused_ragged_cutoff_2d(const std::vector<Tensor>& values, const std::vector<Tens
   const int T = (int)values.size();
   TORCH_CHECK(T > 0 && (int)offsets.size() == T, "values / offsets length mismatch");
   auto dev = values[0].device();
+  if (dev.is_cuda()) {
+    // all features in three launches and one host read (kernels/ragged_fused.cu); the code below is the CPU implementation
+    auto r = rbx::fused_cutoff_cuda(values, offsets, {}, keep_lengths, drop_sides, pad_sides, false);
+    return {r.values, r.offsets, r.drop_nums, r.pad_nums};
+  }
   c10::OptionalDeviceGuard guard(dev);
   auto keep = keep_lengths.to(torch::kCPU, torch::kInt64).reshape(-1);
   auto dl = drop_sides.to(torch::kCPU, torch::kBool).reshape(-1);
@@ -240,6 +248,12 @@ fused_ragged_cutoff_3d(const std::vector<Tensor>& values, const std::vector<Tens
   const int T = (int)values.size();
   TORCH_CHECK(T > 0 && (int)outer_offsets.size() == T && (int)inner_offsets.size() == T);
   auto dev = values[0].device();
+  if (dev.is_cuda()) {
+    auto r = rbx::fused_cutoff_cuda(values, inner_offsets, outer_offsets, keep_lengths, drop_sides, pad_sides, true);
+    for (int t = 0; t < T; ++t)
+      if (r.outer[t].scalar_type() != outer_offsets[t].scalar_type()) r.outer[t] = r.outer[t].to(outer_offsets[t].scalar_type());
+    return {r.values, r.outer, r.offsets};
+  }
   c10::OptionalDeviceGuard guard(dev);
   auto keep = keep_lengths.to(torch::kCPU, torch::kInt64).reshape(-1);
   auto dl = drop_sides.to(torch::kCPU, torch::kBool).reshape(-1);
@@ -324,34 +338,75 @@ std::tuple<Tensor, Tensor, Tensor> feature_cross_ragged(const Tensor& xv, const 
   auto f32 = xval.options().dtype(torch::kFloat32);
   auto xwt = xw.has_value() && xw->defined() ? xw->to(torch::kFloat32).contiguous() : torch::ones({xval.numel()}, f32);
   auto ywt = yw.has_value() && yw->defined() ? yw->to(torch::kFloat32).contiguous() : torch::ones({yval.numel()}, f32);
-  auto first_flags = [&](const Tensor& vals, const Tensor& off) {
-    auto flag = torch::empty({vals.numel()}, vals.options());
-    const int64_t* v = vals.data_ptr<int64_t>(); const int64_t* o = off.data_ptr<int64_t>(); int64_t* f = flag.data_ptr<int64_t>();
-    const int64_t rows = off.numel() - 1;
-    for_each(dev, vals.numel(), [=] __host__ __device__(int64_t i) {
-      const int64_t row = find_row(o, rows, i);
-      int64_t first = 1;
-      for (int64_t j = o[row]; j < i; ++j) if (v[j] == v[i]) { first = 0; break; }
-      f[i] = first;
-    });
-    return flag;
+  // Per-row unique values by a segmented sort (the reference sorts too: DeviceSegmentedRadixSort + block unique,
+  // feature_cross_ragged_kernel.cu:22-125): rows come out ascending, a value that repeats keeps the weight of its first
+  // occurrence (the sort is stable). Work is O(n log n) whatever the row lengths are.
+  auto row_unique = [&](const Tensor& vals, const Tensor& off, const Tensor& w) {
+    const int64_t n = vals.numel();
+    auto sorted = torch::empty_like(vals);
+    auto order = torch::empty({n}, vals.options().dtype(torch::kInt32));
+    const int64_t* op = off.data_ptr<int64_t>();
+    if (dev.is_cuda()) {
+      auto iota = torch::arange(n, order.options());
+      auto st = at::cuda::getCurrentCUDAStream();
+      size_t bytes = 0;
+      cub::DeviceSegmentedSort::StableSortPairs(nullptr, bytes, vals.data_ptr<int64_t>(), sorted.data_ptr<int64_t>(), iota.data_ptr<int32_t>(),
+                                                order.data_ptr<int32_t>(), (int)n, (int)S, op, op + 1, st);
+      auto temp = torch::empty({(int64_t)bytes + 1}, vals.options().dtype(torch::kUInt8));
+      cub::DeviceSegmentedSort::StableSortPairs(temp.data_ptr(), bytes, vals.data_ptr<int64_t>(), sorted.data_ptr<int64_t>(),
+                                                iota.data_ptr<int32_t>(), order.data_ptr<int32_t>(), (int)n, (int)S, op, op + 1, st);
+      rb::note_launch();
+    } else {
+      const int64_t* v = vals.data_ptr<int64_t>(); int64_t* so = sorted.data_ptr<int64_t>(); int32_t* od = order.data_ptr<int32_t>();
+#pragma omp parallel for schedule(dynamic, 64) if (S > 256)
+      for (int64_t r = 0; r < S; ++r) {
+        std::vector<int32_t> idx((size_t)(op[r + 1] - op[r]));
+        for (size_t k = 0; k < idx.size(); ++k) idx[k] = (int32_t)(op[r] + k);
+        std::stable_sort(idx.begin(), idx.end(), [v](int32_t a, int32_t b) { return v[a] < v[b]; });
+        for (size_t k = 0; k < idx.size(); ++k) { so[op[r] + k] = v[idx[k]]; od[op[r] + k] = idx[k]; }
+      }
+    }
+    // head of every run of equal values inside a row
+    auto head = torch::empty({n}, vals.options());
+    {
+      const int64_t* so = sorted.data_ptr<int64_t>(); int64_t* h = head.data_ptr<int64_t>();
+      for_each(dev, n, [=] __host__ __device__(int64_t i) {
+        const int64_t row = find_row(op, S, i);
+        h[i] = (i == op[row] || so[i] != so[i - 1]) ? 1 : 0;
+      });
+    }
+    auto rank = head.cumsum(0);                                         // inclusive: rank[i] - 1 = position among the uniques
+    auto uoff = torch::zeros({S + 1}, vals.options());
+    {
+      const int64_t* rk = rank.data_ptr<int64_t>(); int64_t* uo = uoff.data_ptr<int64_t>();
+      for_each(dev, S + 1, [=] __host__ __device__(int64_t r) { uo[r] = op[r] > 0 ? rk[op[r] - 1] : 0; });
+    }
+    return std::make_tuple(sorted, order, head, rank, uoff);
   };
-  auto fx = first_flags(xval, xoff), fy = first_flags(yval, yoff);
-  // rank of every first occurrence inside its row and unique count per row
-  auto cx = fx.cumsum(0), cy = fy.cumsum(0);
-  auto zero = torch::zeros({1}, xval.options());
-  auto cx0 = torch::cat({zero, cx}), cy0 = torch::cat({zero, cy});
-  auto ux = cx0.index_select(0, xoff.slice(0, 1)) - cx0.index_select(0, xoff.slice(0, 0, S));
-  auto uy = cy0.index_select(0, yoff.slice(0, 1)) - cy0.index_select(0, yoff.slice(0, 0, S));
+  auto [xs, xord, xh, xrank, xuo] = row_unique(xval, xoff, xwt);
+  auto [ys, yord, yh, yrank, yuo] = row_unique(yval, yoff, ywt);
+  // output offsets: unique(x) * unique(y) per row
   auto out_off = torch::zeros({S + 1}, xval.options());
-  out_off.slice(0, 1).copy_((ux * uy).cumsum(0));
-  const int64_t total = S > 0 ? out_off[S].item<int64_t>() : 0;
-  // compact unique values per side
-  auto xi = fx.nonzero().view(-1), yi = fy.nonzero().view(-1);
-  auto xu = xval.index_select(0, xi), yu = yval.index_select(0, yi);
-  auto xuw = xwt.index_select(0, xi), yuw = ywt.index_select(0, yi);
-  auto xuo = torch::zeros({S + 1}, xval.options()), yuo = torch::zeros({S + 1}, xval.options());
-  xuo.slice(0, 1).copy_(ux.cumsum(0)); yuo.slice(0, 1).copy_(uy.cumsum(0));
+  {
+    auto per_row = (xuo.slice(0, 1) - xuo.slice(0, 0, S)) * (yuo.slice(0, 1) - yuo.slice(0, 0, S));
+    out_off.slice(0, 1).copy_(per_row.cumsum(0));
+  }
+  const int64_t total = S > 0 ? out_off[S].item<int64_t>() : 0;          // the one host read: the size of the result
+  // compact the unique values and their weights
+  auto compact = [&](const Tensor& sorted, const Tensor& order, const Tensor& head, const Tensor& rank, const Tensor& w, int64_t n_u) {
+    auto uv = torch::empty({n_u}, sorted.options());
+    auto uw = torch::empty({n_u}, f32);
+    const int64_t* so = sorted.data_ptr<int64_t>(); const int32_t* od = order.data_ptr<int32_t>(); const int64_t* h = head.data_ptr<int64_t>();
+    const int64_t* rk = rank.data_ptr<int64_t>(); const float* wp = w.data_ptr<float>();
+    int64_t* uvp = uv.data_ptr<int64_t>(); float* uwp = uw.data_ptr<float>();
+    for_each(dev, sorted.numel(), [=] __host__ __device__(int64_t i) {
+      if (h[i]) { uvp[rk[i] - 1] = so[i]; uwp[rk[i] - 1] = wp[od[i]]; }
+    });
+    return std::make_pair(uv, uw);
+  };
+  // sizes of the compacted arrays are bounded by the inputs: no host read needed (the tails stay unused)
+  auto [xu, xuw] = compact(xs, xord, xh, xrank, xwt, xval.numel());
+  auto [yu, yuw] = compact(ys, yord, yh, yrank, ywt, yval.numel());
   auto out_v = torch::empty({total}, xval.options());
   auto out_w = torch::empty({total}, f32);
   const int64_t *oo = out_off.data_ptr<int64_t>(), *xo_ = xuo.data_ptr<int64_t>(), *yo_ = yuo.data_ptr<int64_t>(), *xp = xu.data_ptr<int64_t>(),

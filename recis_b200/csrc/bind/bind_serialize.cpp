@@ -63,7 +63,6 @@ void write_all(FileOutputBuffer* f, const void* p, size_t n, const std::string& 
 void write_gather_block(FileOutputBuffer* f, const Block& b, const std::string& path) {
   const int64_t n = b.rows.numel();
   if (n == 0) return;
-  const bool is_f32 = b.tensor.scalar_type() == torch::kFloat32;
   const int64_t D = b.tensor.dim() == 2 ? b.tensor.size(1) : 1;
   const int64_t esz = b.tensor.element_size();
   const int64_t chunk = std::min<int64_t>(env_rows("RECIS_BLOCK_WRITE_SIZE"), n);
@@ -87,12 +86,8 @@ void write_gather_block(FileOutputBuffer* f, const Block& b, const std::string& 
   }
   auto issue = [&](int64_t s, int slot) {
     const int64_t m = std::min(chunk, n - s);
-    if (is_f32) {
-      rb_gather_rows(b.tensor.data_ptr<float>(), b.rows.data_ptr<int32_t>() + s, m, nullptr, (int)D, stage_dev[slot].data_ptr<float>(), stream);
-    } else {
-      auto part = b.tensor.index_select(0, b.rows.narrow(0, s, m).to(torch::kInt64));
-      stage_dev[slot].view({-1}).narrow(0, 0, m * D).copy_(part.reshape({-1}), true);
-    }
+    // rows are gathered as bytes: any slab type (fp32 / fp16 / bf16 / int8 rows, int64 per-row counters)
+    rb_gather_rows(b.tensor.data_ptr(), b.rows.data_ptr<int32_t>() + s, m, nullptr, D * esz, stage_dev[slot].data_ptr(), stream);
     cuda_ok(cudaMemcpyAsync(stage_host[slot].data_ptr(), stage_dev[slot].data_ptr(), (size_t)m * D * esz, cudaMemcpyDeviceToHost, stream),
             "device-to-host copy of a checkpoint chunk");
     cuda_ok(cudaEventRecord(done[slot], stream), "cudaEventRecord");

@@ -7,6 +7,7 @@
 #include "../kernels/rb_kernels.h"
 #include "store.h"
 #include "../common/rb_launch.h"
+#include "bind_shared.h"
 
 namespace py = pybind11;
 using torch::Tensor;
@@ -81,29 +82,33 @@ std::tuple<Tensor, Tensor> encode_merge(const Tensor& desc, const Tensor& table_
   return {ids, offs};
 }
 
+// out[i] = src[rows[i]] (zeros where rows[i] < 0); rows of any element type, the result has the type of src
 Tensor gather_rows(const Tensor& src, const Tensor& rows, OptT n_dev) {
-  TORCH_CHECK(src.dim() == 2 && src.is_contiguous() && src.scalar_type() == torch::kFloat32 && rows.scalar_type() == torch::kInt32);
-  const int64_t n = rows.numel(); const int D = (int)src.size(1);
+  TORCH_CHECK(src.dim() == 2 && src.is_contiguous() && rows.scalar_type() == torch::kInt32);
+  const int64_t n = rows.numel(); const int64_t D = src.size(1);
   auto out = n_dev.has_value() ? torch::zeros({n, D}, src.options()) : torch::empty({n, D}, src.options());
   if (n == 0) return out;
+  const int64_t row_bytes = D * src.element_size();
   if (src.is_cuda()) {
     c10::cuda::CUDAGuard g(src.device());
-    rb_gather_rows(src.data_ptr<float>(), rows.data_ptr<int32_t>(), n, opt_i32(n_dev), D, out.data_ptr<float>(), cur_stream());
+    rb_gather_rows(src.data_ptr(), rows.data_ptr<int32_t>(), n, opt_i32(n_dev), row_bytes, out.data_ptr(), cur_stream());
   } else {
-    rbc_gather_rows(src.data_ptr<float>(), rows.data_ptr<int32_t>(), n, opt_i32(n_dev), D, out.data_ptr<float>());
+    rbc_gather_rows(src.data_ptr(), rows.data_ptr<int32_t>(), n, opt_i32(n_dev), row_bytes, out.data_ptr());
   }
   return out;
 }
 
+// dst[rows[i]] = src[i] (or src[0] when broadcast); src must have the element type of dst
 void scatter_rows(Tensor dst, const Tensor& rows, const Tensor& src, bool broadcast) {
   TORCH_CHECK(dst.dim() == 2 && dst.is_contiguous() && src.is_contiguous() && rows.scalar_type() == torch::kInt32);
-  const int64_t n = rows.numel(); const int D = (int)dst.size(1);
+  TORCH_CHECK(src.scalar_type() == dst.scalar_type(), "scatter_rows: source rows are ", src.scalar_type(), ", the table stores ", dst.scalar_type());
+  const int64_t n = rows.numel(); const int64_t row_bytes = dst.size(1) * dst.element_size();
   if (n == 0) return;
   if (dst.is_cuda()) {
     c10::cuda::CUDAGuard g(dst.device());
-    rb_scatter_rows(dst.data_ptr<float>(), rows.data_ptr<int32_t>(), n, D, src.data_ptr<float>(), broadcast, cur_stream());
+    rb_scatter_rows(dst.data_ptr(), rows.data_ptr<int32_t>(), n, row_bytes, src.data_ptr(), broadcast, cur_stream());
   } else {
-    rbc_scatter_rows(dst.data_ptr<float>(), rows.data_ptr<int32_t>(), n, D, src.data_ptr<float>(), broadcast);
+    rbc_scatter_rows(dst.data_ptr(), rows.data_ptr<int32_t>(), n, row_bytes, src.data_ptr(), broadcast);
   }
 }
 
@@ -123,7 +128,8 @@ void fill_rows_i64(Tensor dst, const Tensor& rows, int64_t value) {
 std::tuple<Tensor, Tensor, Tensor> pool_forward(const Tensor& base, OptT rows, const Tensor& rev, const Tensor& offsets, OptT weights,
                                                 int64_t mode, int64_t perm_b, int64_t perm_f, bool need_grad, OptT out_opt,
                                                 int64_t perm_off, int64_t perm_total) {
-  TORCH_CHECK(base.dim() == 2 && base.is_contiguous() && base.scalar_type() == torch::kFloat32);
+  TORCH_CHECK(base.dim() == 2 && base.is_contiguous());
+  const int base_dtype = rbx::row_dtype_of(base);
   TORCH_CHECK(rev.scalar_type() == torch::kInt32 && offsets.scalar_type() == torch::kInt32);
   const int64_t n_seg = offsets.numel() - 1, n = rev.numel(); const int D = (int)base.size(1);
   if (perm_f > 0) TORCH_CHECK(perm_b * perm_f == n_seg, "permuted pooling output needs n_seg == batch * features");
@@ -139,21 +145,21 @@ std::tuple<Tensor, Tensor, Tensor> pool_forward(const Tensor& base, OptT rows, c
     }
   } else {
     perm_off = 0; perm_total = perm_f;
-    out = torch::empty({n_seg, D}, base.options());
+    out = torch::empty({n_seg, D}, base.options().dtype(torch::kFloat32));
   }
   Tensor gsrc, gscale;
   if (need_grad) {
     gsrc = torch::empty({n}, rev.options());
-    gscale = torch::empty({n}, base.options());
+    gscale = torch::empty({n}, base.options().dtype(torch::kFloat32));
   }
   int32_t* gp = need_grad ? gsrc.data_ptr<int32_t>() : nullptr;
   float* gs = need_grad ? gscale.data_ptr<float>() : nullptr;
   if (base.is_cuda()) {
     c10::cuda::CUDAGuard g(base.device());
-    rb_pool_forward(base.data_ptr<float>(), opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg, D,
+    rb_pool_forward(base.data_ptr(), base_dtype, opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg, D,
                     (int)mode, (int)perm_b, (int)perm_f, (int)perm_off, (int)perm_total, out.data_ptr<float>(), gp, gs, cur_stream());
   } else {
-    rbc_pool_forward(base.data_ptr<float>(), opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg,
+    rbc_pool_forward(base.data_ptr(), base_dtype, opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg,
                      D, (int)mode, (int)perm_b, (int)perm_f, (int)perm_off, (int)perm_total, out.data_ptr<float>(), gp, gs);
   }
   return {out, gsrc, gscale};
@@ -161,19 +167,21 @@ std::tuple<Tensor, Tensor, Tensor> pool_forward(const Tensor& base, OptT rows, c
 
 std::tuple<Tensor, Tensor, Tensor> tile_forward(const Tensor& base, OptT rows, const Tensor& rev, const Tensor& offsets, OptT weights,
                                                 int64_t tile_len, bool need_grad) {
-  TORCH_CHECK(base.dim() == 2 && base.is_contiguous() && base.scalar_type() == torch::kFloat32);
+  TORCH_CHECK(base.dim() == 2 && base.is_contiguous());
+  const int base_dtype = rbx::row_dtype_of(base);
   const int64_t n_seg = offsets.numel() - 1, n = rev.numel(); const int D = (int)base.size(1);
-  auto out = torch::empty({n_seg, tile_len * D}, base.options());
+  auto f32 = base.options().dtype(torch::kFloat32);
+  auto out = torch::empty({n_seg, tile_len * D}, f32);
   Tensor gsrc, gscale;
-  if (need_grad) { gsrc = torch::empty({n}, rev.options()); gscale = torch::empty({n}, base.options()); }
+  if (need_grad) { gsrc = torch::empty({n}, rev.options()); gscale = torch::empty({n}, f32); }
   int32_t* gp = need_grad ? gsrc.data_ptr<int32_t>() : nullptr;
   float* gs = need_grad ? gscale.data_ptr<float>() : nullptr;
   if (base.is_cuda()) {
     c10::cuda::CUDAGuard g(base.device());
-    rb_tile_forward(base.data_ptr<float>(), opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg, D,
+    rb_tile_forward(base.data_ptr(), base_dtype, opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg, D,
                     (int)tile_len, out.data_ptr<float>(), gp, gs, cur_stream());
   } else {
-    rbc_tile_forward(base.data_ptr<float>(), opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg,
+    rbc_tile_forward(base.data_ptr(), base_dtype, opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg,
                      D, (int)tile_len, out.data_ptr<float>(), gp, gs);
   }
   return {out, gsrc, gscale};
@@ -207,16 +215,7 @@ std::tuple<Tensor, Tensor, Tensor> build_csr(const Tensor& reverse) {
 namespace {
 using rbx::build_csr;
 
-RbOpt make_opt(int64_t kind, double lr, double beta1, double beta2, double eps, double decay, double alpha, double grad_scale,
-               const OptT& w, const OptT& s1, const OptT& s2) {
-  RbOpt o;
-  o.kind = (int)kind; o.lr = (float)lr; o.beta1 = (float)beta1; o.beta2 = (float)beta2; o.eps = (float)eps; o.decay = (float)decay;
-  o.alpha = (float)alpha; o.grad_scale = (float)grad_scale;
-  o.w = w.has_value() && w->defined() ? w->data_ptr<float>() : nullptr;
-  o.s1 = s1.has_value() && s1->defined() ? s1->data_ptr<float>() : nullptr;
-  o.s2 = s2.has_value() && s2->defined() ? s2->data_ptr<float>() : nullptr;
-  return o;
-}
+using rbx::make_opt;
 
 // Per-unique gradient reduction. apply=false: returns gu [n_unique_max, D] (rows beyond the unique count are undefined).
 // apply=true: runs the optimizer on row rows[u] of (w, s1, s2) in the same kernel and returns an empty tensor.
@@ -264,13 +263,14 @@ void init_sparse(py::module& m) {
   using rbx::EmbeddingStore;
   py::class_<EmbeddingStore, std::shared_ptr<EmbeddingStore>>(m, "EmbeddingStore")
       .def(py::init([](int64_t dim, int64_t capacity, const std::string& device, int init_kind, double a, double b, double lo, double hi,
-                       int64_t seed, bool track_last_seen, bool growable, OptT emb_storage) {
+                       int64_t seed, bool track_last_seen, bool growable, OptT emb_storage, py::object emb_dtype) {
+             const torch::ScalarType dt = emb_dtype.is_none() ? torch::kFloat32 : torch::python::detail::py_object_to_dtype(emb_dtype);
              return std::make_shared<EmbeddingStore>(dim, capacity, torch::Device(device), init_kind, a, b, lo, hi, seed, track_last_seen,
-                                                     growable, emb_storage);
+                                                     growable, emb_storage, dt);
            }),
            py::arg("dim"), py::arg("capacity"), py::arg("device"), py::arg("init_kind"), py::arg("a"), py::arg("b"), py::arg("lo"),
            py::arg("hi"), py::arg("seed"), py::arg("track_last_seen") = true, py::arg("growable") = true,
-           py::arg("emb_storage") = py::none())
+           py::arg("emb_storage") = py::none(), py::arg("emb_dtype") = py::none())
       .def("lookup_or_insert", &EmbeddingStore::lookup_or_insert, py::arg("ids"), py::arg("n_dev") = py::none(),
            py::arg("step") = py::none(), py::arg("admit_threshold") = 1)
       .def("find", &EmbeddingStore::find, py::arg("ids"), py::arg("n_dev") = py::none())

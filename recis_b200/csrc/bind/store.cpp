@@ -12,6 +12,7 @@
 #include "../kernels/rb_kernels.h"
 #include "../cpu/rb_cpu.h"
 #include "store.h"
+#include "bind_shared.h"
 
 namespace rbx {
 
@@ -19,17 +20,19 @@ static int64_t pow2_at_least(int64_t x) { int64_t p = 1024; while (p < x) p <<= 
 
 EmbeddingStore::EmbeddingStore(int64_t dim, int64_t capacity, torch::Device device, int init_kind, double a, double b,
                                double lo, double hi, int64_t seed, bool track_last_seen, bool growable,
-                               c10::optional<torch::Tensor> emb_storage)
+                               c10::optional<torch::Tensor> emb_storage, torch::ScalarType emb_dtype)
     : dim_(dim), cap_rows_(std::max<int64_t>(capacity, 16)), device_(device), growable_(growable) {
   init_.kind = init_kind; init_.a = (float)a; init_.b = (float)b; init_.lo = (float)lo; init_.hi = (float)hi;
   init_.seed = (uint64_t)seed;
   auto f32 = torch::TensorOptions().dtype(torch::kFloat32).device(device_);
+  TORCH_CHECK(emb_dtype == torch::kFloat32 || emb_dtype == torch::kFloat16 || emb_dtype == torch::kBFloat16 || emb_dtype == torch::kInt8,
+              "embedding rows are stored as float32, float16, bfloat16 or int8");
   if (emb_storage.has_value()) {
-    TORCH_CHECK(emb_storage->numel() >= cap_rows_ * dim_ && emb_storage->scalar_type() == torch::kFloat32, "emb_storage too small");
+    TORCH_CHECK(emb_storage->numel() >= cap_rows_ * dim_ && emb_storage->scalar_type() == emb_dtype, "emb_storage too small or of the wrong type");
     emb_ = emb_storage->view({-1}).narrow(0, 0, cap_rows_ * dim_).view({cap_rows_, dim_});
     growable_ = false;  // externally owned (peer-mapped) storage cannot move
   } else {
-    emb_ = torch::empty({cap_rows_, dim_}, f32);
+    emb_ = torch::empty({cap_rows_, dim_}, f32.dtype(emb_dtype));     // rows in their storage type; slots (optimizer state) stay fp32
   }
   if (track_last_seen) last_seen_ = torch::zeros({cap_rows_}, f32.dtype(torch::kInt64));
   alloc_index(pow2_at_least(cap_rows_ * 2));
@@ -56,7 +59,7 @@ RbTable EmbeddingStore::view() const {
 
 void EmbeddingStore::add_slot(const std::string& name, double fill) {
   if (slots_.count(name)) return;
-  slots_[name] = torch::full({cap_rows_, dim_}, fill, emb_.options());
+  slots_[name] = torch::full({cap_rows_, dim_}, fill, emb_.options().dtype(torch::kFloat32));
   slot_fill_[name] = fill;
   slot_order_.push_back(name);
 }
@@ -250,11 +253,11 @@ torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::op
   if (device_.is_cuda()) {
     c10::cuda::CUDAGuard g(device_);
     rb_table_lookup_or_insert(view(), ids.data_ptr<int64_t>(), n, nd, slot_scratch.data_ptr<int32_t>(), new_rows.data_ptr<int32_t>(),
-                              new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr<float>(), (int)dim_, init_, ls,
+                              new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr(), rbx::row_dtype_of(emb_), (int)dim_, init_, ls,
                               sd, (int)admit_threshold, at::cuda::getCurrentCUDAStream());
   } else {
     rbc_table_lookup_or_insert(view(), ids.data_ptr<int64_t>(), n, nd, slot_scratch.data_ptr<int32_t>(), new_rows.data_ptr<int32_t>(),
-                               new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr<float>(), (int)dim_, init_, ls,
+                               new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr(), rbx::row_dtype_of(emb_), (int)dim_, init_, ls,
                                sd, (int)admit_threshold);
   }
   post_mirror(n_room, nd);
@@ -286,14 +289,14 @@ torch::Tensor EmbeddingStore::erase(const torch::Tensor& ids) {
     auto st = at::cuda::getCurrentCUDAStream();
     rb_table_erase(view(), ids.data_ptr<int64_t>(), n, nullptr, erased.data_ptr<int32_t>(), st);
     for (auto& kv : slots_) {
-      auto fillv = torch::full({dim_}, slot_fill_[kv.first], emb_.options());
-      rb_scatter_rows(kv.second.data_ptr<float>(), erased.data_ptr<int32_t>(), n, (int)dim_, fillv.data_ptr<float>(), 1, st);
+      auto fillv = torch::full({dim_}, slot_fill_[kv.first], kv.second.options());
+      rb_scatter_rows(kv.second.data_ptr(), erased.data_ptr<int32_t>(), n, dim_ * (int64_t)sizeof(float), fillv.data_ptr(), 1, st);
     }
   } else {
     rbc_table_erase(view(), ids.data_ptr<int64_t>(), n, nullptr, erased.data_ptr<int32_t>());
     for (auto& kv : slots_) {
-      auto fillv = torch::full({dim_}, slot_fill_[kv.first], emb_.options());
-      rbc_scatter_rows(kv.second.data_ptr<float>(), erased.data_ptr<int32_t>(), n, (int)dim_, fillv.data_ptr<float>(), 1);
+      auto fillv = torch::full({dim_}, slot_fill_[kv.first], kv.second.options());
+      rbc_scatter_rows(kv.second.data_ptr(), erased.data_ptr<int32_t>(), n, dim_ * (int64_t)sizeof(float), fillv.data_ptr(), 1);
     }
   }
   return erased;

@@ -10,7 +10,8 @@ namespace rbx {
 class EmbeddingStore {
  public:
   EmbeddingStore(int64_t dim, int64_t capacity, torch::Device device, int init_kind, double a, double b, double lo, double hi,
-                 int64_t seed, bool track_last_seen, bool growable, c10::optional<torch::Tensor> emb_storage);
+                 int64_t seed, bool track_last_seen, bool growable, c10::optional<torch::Tensor> emb_storage,
+                 torch::ScalarType emb_dtype = torch::kFloat32);
   ~EmbeddingStore();
   EmbeddingStore(const EmbeddingStore&) = delete;
   EmbeddingStore& operator=(const EmbeddingStore&) = delete;

@@ -128,6 +128,11 @@ __host__ __device__ inline void init_quad(const InitSpec& s, uint64_t key, uint3
   }
 }
 
+// Storage type of embedding rows. Rows may be kept in 32- or 16-bit floating point, or (read-only tables) as 8-bit integers;
+// optimizer state and every accumulation stay fp32. Codes are shared by the CUDA kernels, their CPU twins and the bindings.
+enum RowDType : int { kRowF32 = 0, kRowF16 = 1, kRowBF16 = 2, kRowI8 = 3 };
+__host__ __device__ __forceinline__ int row_elem_size(int dtype) { return dtype == kRowF32 ? 4 : (dtype == kRowI8 ? 1 : 2); }
+
 #ifdef __CUDACC__
 __device__ __forceinline__ float4 ld_f4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st_f4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
@@ -143,6 +148,78 @@ __device__ __forceinline__ void set_status(int64_t* status, int64_t bit) {
   if (status) atomicOr(reinterpret_cast<unsigned long long*>(status), (unsigned long long)bit);
 }
 #endif
+
+#ifdef __CUDACC__
+}  // namespace rb
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+namespace rb {
+// Four consecutive row elements <-> float4 (the address is aligned to four elements), and single elements.
+template <typename T> struct RowIO;
+template <> struct RowIO<float> {
+  static __device__ __forceinline__ float4 ld4(const float* p) { return ld_f4(p); }
+  static __device__ __forceinline__ void st4(float* p, float4 v) { st_f4(p, v); }
+  static __device__ __forceinline__ float ld1(const float* p) { return *p; }
+  static __device__ __forceinline__ void st1(float* p, float v) { *p = v; }
+};
+template <> struct RowIO<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+  static __device__ __forceinline__ float ld1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void st1(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+template <> struct RowIO<__half> {
+  static __device__ __forceinline__ float4 ld4(const __half* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void st4(__half* p, float4 v) {
+    uint2 raw;
+    *reinterpret_cast<__half2*>(&raw.x) = __floats2half2_rn(v.x, v.y);
+    *reinterpret_cast<__half2*>(&raw.y) = __floats2half2_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+  static __device__ __forceinline__ float ld1(const __half* p) { return __half2float(*p); }
+  static __device__ __forceinline__ void st1(__half* p, float v) { *p = __float2half_rn(v); }
+};
+template <> struct RowIO<int8_t> {
+  static __device__ __forceinline__ float4 ld4(const int8_t* p) {
+    const char4 c = *reinterpret_cast<const char4*>(p);
+    return make_float4((float)c.x, (float)c.y, (float)c.z, (float)c.w);
+  }
+  static __device__ __forceinline__ int8_t q(float v) { return (int8_t)max(-128, min(127, __float2int_rn(v))); }
+  static __device__ __forceinline__ void st4(int8_t* p, float4 v) {
+    char4 c; c.x = q(v.x); c.y = q(v.y); c.z = q(v.z); c.w = q(v.w);
+    *reinterpret_cast<char4*>(p) = c;
+  }
+  static __device__ __forceinline__ float ld1(const int8_t* p) { return (float)*p; }
+  static __device__ __forceinline__ void st1(int8_t* p, float v) { *p = q(v); }
+};
+#endif
+
+// Calls f(T{}) with T the row type of `dtype`. int8 rows are read-only: kernels that update rows pass with_i8 = false.
+#define RB_DISPATCH_ROW(dtype, with_i8, ...)                                             \
+  do {                                                                                   \
+    switch (dtype) {                                                                     \
+      case rb::kRowF32: { using T = float; __VA_ARGS__; } break;                         \
+      case rb::kRowF16: { using T = __half; __VA_ARGS__; } break;                        \
+      case rb::kRowBF16: { using T = __nv_bfloat16; __VA_ARGS__; } break;                \
+      case rb::kRowI8: if (with_i8) { using T = int8_t; __VA_ARGS__; } break;            \
+      default: break;                                                                    \
+    }                                                                                    \
+  } while (0)
 
 inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 

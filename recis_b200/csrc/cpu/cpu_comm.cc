@@ -8,6 +8,7 @@
 #include <thread>
 #include "rb_cpu.h"
 #include "rb_cpu_comm.h"
+#include "rb_cpu_row.h"
 
 namespace {
 
@@ -17,7 +18,7 @@ inline void set_status(int64_t* status, int64_t bit) { __atomic_fetch_or(status,
 
 inline void opt_update(const RbOpt& o, int64_t off, float g) {
   g *= o.grad_scale;
-  float w = o.w[off];
+  float w = rbcpu::row_ld(o.w, o.w_dtype, off);
   if (o.kind == RB_OPT_ADAM) {
     const float m = o.beta1 * o.s1[off] + (1.f - o.beta1) * g;
     const float v = o.beta2 * o.s2[off] + (1.f - o.beta2) * g * g;
@@ -30,7 +31,7 @@ inline void opt_update(const RbOpt& o, int64_t off, float g) {
   } else {
     w = w * o.decay - o.lr * g;
   }
-  o.w[off] = w;
+  rbcpu::row_st(o.w, o.w_dtype, off, w);
 }
 
 }  // namespace
@@ -124,16 +125,17 @@ void rbc_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_coun
   }
 }
 
-void rbc_comm_push_emb(const float* emb, const int32_t* rows_in, const int32_t* prefix, RbPeers peer_uemb, int me, int world, int D,
-                       int64_t in_cap) {
+void rbc_comm_push_emb(const void* emb, const int32_t* rows_in, const int32_t* prefix, RbPeers peer_uemb, int me, int world,
+                       int64_t row_bytes, int64_t in_cap) {
   (void)me;
+  const char* src = static_cast<const char*>(emb);
   for (int r = 0; r < world; ++r) {
-    float* dst = reinterpret_cast<float*>(peer_uemb.p[r]) + (int64_t)prefix[world + 1 + r] * D;
+    char* dst = reinterpret_cast<char*>(peer_uemb.p[r]) + (int64_t)prefix[world + 1 + r] * row_bytes;
     const int64_t beg = prefix[r], end = std::min<int64_t>(prefix[r + 1], in_cap);
     for (int64_t j = beg; j < end; ++j) {
       const int32_t row = rows_in[j];
-      if (row >= 0) std::memcpy(dst + (j - beg) * D, emb + (int64_t)row * D, sizeof(float) * D);
-      else std::memset(dst + (j - beg) * D, 0, sizeof(float) * D);
+      if (row >= 0) std::memcpy(dst + (j - beg) * row_bytes, src + (int64_t)row * row_bytes, (size_t)row_bytes);
+      else std::memset(dst + (j - beg) * row_bytes, 0, (size_t)row_bytes);
     }
   }
 }

@@ -8,6 +8,7 @@
 #include "../common/rb_common.cuh"
 #include "../kernels/rb_kernels.h"
 #include "rb_cpu.h"
+#include "rb_cpu_row.h"
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -29,7 +30,7 @@ inline int32_t cpu_alloc_row(RbTable& t, uint64_t key, int32_t* new_rows, int64_
 
 inline void cpu_opt_update(const RbOpt& o, int64_t off, float g) {
   g *= o.grad_scale;
-  float w = o.w[off];
+  float w = rbcpu::row_ld(o.w, o.w_dtype, off);
   if (o.kind == RB_OPT_ADAM) {
     const float m = o.beta1 * o.s1[off] + (1.f - o.beta1) * g;
     const float v = o.beta2 * o.s2[off] + (1.f - o.beta2) * g * g;
@@ -42,7 +43,7 @@ inline void cpu_opt_update(const RbOpt& o, int64_t off, float g) {
   } else {
     w = w * o.decay - o.lr * g;
   }
-  o.w[off] = w;
+  rbcpu::row_st(o.w, o.w_dtype, off, w);
 }
 inline int64_t out_row_of(int64_t s, int perm_b, int perm_f, int perm_off, int perm_total) {
   if (perm_f <= 0) return s + perm_off;
@@ -54,7 +55,7 @@ inline int64_t out_row_of(int64_t s, int perm_b, int perm_f, int perm_off, int p
 extern "C" {
 
 void rbc_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* slot_scratch,
-                                int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, float* emb, int D, RbInit init,
+                                int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, void* emb, int emb_dtype, int D, RbInit init,
                                 int64_t* last_seen, const int64_t* step_dev, int admit_threshold) {
   const int64_t n = eff_n(n_max, n_dev);
   for (int64_t i = 0; i < n; ++i) {
@@ -95,7 +96,7 @@ void rbc_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, co
     for (int q = 0; q < quads; ++q) {
       float v[4];
       init_quad(spec, (uint64_t)new_keys[r], (uint32_t)q, v);
-      for (int j = 0; j < 4 && q * 4 + j < D; ++j) emb[(int64_t)row * D + q * 4 + j] = v[j];
+      for (int j = 0; j < 4 && q * 4 + j < D; ++j) rbcpu::row_st(emb, emb_dtype, (int64_t)row * D + q * 4 + j, v[j]);
     }
   }
   const int64_t step = step_dev ? *step_dev : 0;
@@ -242,25 +243,27 @@ void rbc_encode_merge(const int64_t* desc, const int64_t* table_idx, int F, int6
   if (offsets_out) offsets_out[total_seg] = (int32_t)total_nnz;
 }
 
-void rbc_gather_rows(const float* src, const int32_t* rows, int64_t n_max, const int32_t* n_dev, int D, float* out) {
+void rbc_gather_rows(const void* src, const int32_t* rows, int64_t n_max, const int32_t* n_dev, int64_t row_bytes, void* out) {
   const int64_t n = eff_n(n_max, n_dev);
+  const char* s = static_cast<const char*>(src); char* o = static_cast<char*>(out);
 #pragma omp parallel for schedule(static)
   for (int64_t r = 0; r < n; ++r) {
-    if (rows[r] >= 0) std::memcpy(out + r * D, src + (int64_t)rows[r] * D, sizeof(float) * D);
-    else std::memset(out + r * D, 0, sizeof(float) * D);
+    if (rows[r] >= 0) std::memcpy(o + r * row_bytes, s + (int64_t)rows[r] * row_bytes, (size_t)row_bytes);
+    else std::memset(o + r * row_bytes, 0, (size_t)row_bytes);
   }
 }
 
-void rbc_scatter_rows(float* dst, const int32_t* rows, int64_t n, int D, const float* src, int src_broadcast) {
+void rbc_scatter_rows(void* dst, const int32_t* rows, int64_t n, int64_t row_bytes, const void* src, int src_broadcast) {
+  const char* s = static_cast<const char*>(src); char* d = static_cast<char*>(dst);
   for (int64_t r = 0; r < n; ++r)
-    if (rows[r] >= 0) std::memcpy(dst + (int64_t)rows[r] * D, src_broadcast ? src : src + r * D, sizeof(float) * D);
+    if (rows[r] >= 0) std::memcpy(d + (int64_t)rows[r] * row_bytes, src_broadcast ? s : s + r * row_bytes, (size_t)row_bytes);
 }
 
 void rbc_fill_rows_i64(int64_t* dst, const int32_t* rows, int64_t n, int64_t value) {
   for (int64_t i = 0; i < n; ++i) if (rows[i] >= 0) dst[rows[i]] = value;
 }
 
-void rbc_pool_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
+void rbc_pool_forward(const void* base, int base_dtype, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
                       int64_t n_seg, int D, int mode, int perm_b, int perm_f, int perm_off, int perm_total, float* out, int32_t* gsrc,
                       float* gscale) {
   if (perm_f > 0 && perm_total <= 0) { perm_total = perm_f; perm_off = 0; }
@@ -275,7 +278,10 @@ void rbc_pool_forward(const float* base, const int32_t* rows, const int32_t* rev
       const int32_t u = rev[i]; const int32_t r = rows ? rows[u] : u;
       const float wt = weights ? weights[i] : 1.f;
       wsum += wt;
-      if (r >= 0) { const float* e = base + (int64_t)r * D; for (int c = 0; c < D; ++c) o[c] += wt * e[c]; }
+      if (r >= 0) {
+        if (base_dtype == kRowF32) { const float* e = static_cast<const float*>(base) + (int64_t)r * D; for (int c = 0; c < D; ++c) o[c] += wt * e[c]; }
+        else for (int c = 0; c < D; ++c) o[c] += wt * rbcpu::row_ld(base, base_dtype, (int64_t)r * D + c);
+      }
     }
     float scale = 1.f;
     if (mode == 1) scale = end > beg ? 1.f / (float)(end - beg) : 0.f;
@@ -285,7 +291,7 @@ void rbc_pool_forward(const float* base, const int32_t* rows, const int32_t* rev
   }
 }
 
-void rbc_tile_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
+void rbc_tile_forward(const void* base, int base_dtype, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
                       int64_t n_seg, int D, int tile_len, float* out, int32_t* gsrc, float* gscale) {
 #pragma omp parallel for schedule(static)
   for (int64_t s = 0; s < n_seg; ++s) {
@@ -296,7 +302,7 @@ void rbc_tile_forward(const float* base, const int32_t* rows, const int32_t* rev
       if (beg + t < end) {
         const int32_t u = rev[beg + t]; const int32_t r = rows ? rows[u] : u;
         const float wt = weights ? weights[beg + t] : 1.f;
-        if (r >= 0) for (int c = 0; c < D; ++c) o[c] = wt * base[(int64_t)r * D + c];
+        if (r >= 0) for (int c = 0; c < D; ++c) o[c] = wt * rbcpu::row_ld(base, base_dtype, (int64_t)r * D + c);
         if (gsrc) { gsrc[beg + t] = (int32_t)(s * tile_len + t); gscale[beg + t] = wt; }
       }
     }

@@ -23,6 +23,7 @@
 // kStatusWaitTimeout in the status word and returns, so a missing peer can never hang a GPU.
 // No TMA multicast is used anywhere; peer memory is only touched by plain loads and stores.
 #include "../common/rb_common.cuh"
+#include "../common/rb_opt.cuh"
 #include "../common/rb_launch.h"
 #include "rb_comm.h"
 
@@ -181,12 +182,13 @@ pull_ids_kernel(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_counts, int
   }
 }
 
-// Owner: store the embedding row of incoming id j into its requester's unique-embedding buffer.
-// A work item is (k, column): it serves the k-th id of EVERY requester, so all peer links carry traffic for the whole
+// Owner: store the embedding row of incoming id j into its requester's unique-embedding buffer. Rows travel as bytes (q
+// 16-byte pieces per row), so one kernel serves fp32, fp16 and bf16 rows: the wire format is the storage format.
+// A work item is (k, piece): it serves the k-th id of EVERY requester, so all peer links carry traffic for the whole
 // kernel (instead of one requester after the other) and each thread has up to `world` independent load/store pairs in flight.
 __global__ void __launch_bounds__(kThreads)
-push_emb_kernel(const float* __restrict__ emb, const int32_t* __restrict__ rows_in, const int32_t* __restrict__ prefix_in,
-                RbPeers peer_uemb, int me, int world, int D) {
+push_emb_kernel(const uint4* __restrict__ emb, const int32_t* __restrict__ rows_in, const int32_t* __restrict__ prefix_in,
+                RbPeers peer_uemb, int me, int world, int q) {
   __shared__ int32_t prefix[RB_MAX_PEERS + 1];
   __shared__ int32_t dst_off[RB_MAX_PEERS];
   __shared__ int32_t max_cnt;
@@ -199,15 +201,15 @@ push_emb_kernel(const float* __restrict__ emb, const int32_t* __restrict__ rows_
     max_cnt = m;
   }
   __syncthreads();
-  const int q = D >> 2;                        // D % 4 == 0 is required by the fused path
   const int64_t total = (int64_t)max_cnt * q;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   constexpr int U = 4;                       // rows in flight per thread and requester
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   for (int64_t w0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w0 < total; w0 += stride * U) {
     for (int r0 = 0; r0 < world; ++r0) {
       const int r = (r0 + me + 1) % world;    // start with the right neighbour: ranks do not all hammer rank 0 first
       const int32_t cnt = prefix[r + 1] - prefix[r];
-      int32_t row[U]; int64_t k[U]; int c[U]; float4 v[U];
+      int32_t row[U]; int64_t k[U]; int c[U]; uint4 v[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int64_t w = w0 + u * stride;
@@ -215,67 +217,12 @@ push_emb_kernel(const float* __restrict__ emb, const int32_t* __restrict__ rows_
         row[u] = (w < total && k[u] < cnt) ? rows_in[prefix[r] + k[u]] : -2;
       }
 #pragma unroll
-      for (int u = 0; u < U; ++u) v[u] = row[u] >= 0 ? ld_f4(emb + (int64_t)row[u] * D + c[u] * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int u = 0; u < U; ++u) v[u] = row[u] >= 0 ? emb[(int64_t)row[u] * q + c[u]] : zero;
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (row[u] != -2) st_f4(reinterpret_cast<float*>(peer_uemb.p[r]) + ((int64_t)dst_off[r] + k[u]) * D + c[u] * 4, v[u]);
+        if (row[u] != -2) reinterpret_cast<uint4*>(peer_uemb.p[r])[((int64_t)dst_off[r] + k[u]) * q + c[u]] = v[u];
     }
   }
-}
-
-__device__ __forceinline__ void opt_update_f4(const RbOpt& o, int64_t off, float4 g) {
-  const float gs = o.grad_scale;
-  g.x *= gs; g.y *= gs; g.z *= gs; g.w *= gs;
-  float4 w = ld_f4(o.w + off);
-  if (o.kind == RB_OPT_ADAM) {
-    float4 m = ld_f4(o.s1 + off), v = ld_f4(o.s2 + off);
-    const float b1 = o.beta1, b2 = o.beta2, c1 = 1.f - o.beta1, c2 = 1.f - o.beta2;
-    m.x = b1 * m.x + c1 * g.x; m.y = b1 * m.y + c1 * g.y; m.z = b1 * m.z + c1 * g.z; m.w = b1 * m.w + c1 * g.w;
-    v.x = b2 * v.x + c2 * g.x * g.x; v.y = b2 * v.y + c2 * g.y * g.y; v.z = b2 * v.z + c2 * g.z * g.z; v.w = b2 * v.w + c2 * g.w * g.w;
-    w.x = w.x * o.decay + o.alpha * m.x / (sqrtf(v.x) + o.eps);
-    w.y = w.y * o.decay + o.alpha * m.y / (sqrtf(v.y) + o.eps);
-    w.z = w.z * o.decay + o.alpha * m.z / (sqrtf(v.z) + o.eps);
-    w.w = w.w * o.decay + o.alpha * m.w / (sqrtf(v.w) + o.eps);
-    st_f4(o.s1 + off, m); st_f4(o.s2 + off, v);
-  } else if (o.kind == RB_OPT_ADAGRAD) {
-    float4 a = ld_f4(o.s1 + off);
-    a.x += g.x * g.x; a.y += g.y * g.y; a.z += g.z * g.z; a.w += g.w * g.w;
-    w.x = w.x * o.decay - o.lr * g.x / (sqrtf(a.x) + o.eps);
-    w.y = w.y * o.decay - o.lr * g.y / (sqrtf(a.y) + o.eps);
-    w.z = w.z * o.decay - o.lr * g.z / (sqrtf(a.z) + o.eps);
-    w.w = w.w * o.decay - o.lr * g.w / (sqrtf(a.w) + o.eps);
-    st_f4(o.s1 + off, a);
-  } else {
-    w.x = w.x * o.decay - o.lr * g.x; w.y = w.y * o.decay - o.lr * g.y;
-    w.z = w.z * o.decay - o.lr * g.z; w.w = w.w * o.decay - o.lr * g.w;
-  }
-  st_f4(o.w + off, w);
-}
-
-__device__ __forceinline__ void opt_update_pre_f4(const RbOpt& o, int64_t off, float4 g, float4 w, float4 m, float4 v) {
-  const float gs = o.grad_scale;
-  g.x *= gs; g.y *= gs; g.z *= gs; g.w *= gs;
-  if (o.kind == RB_OPT_ADAM) {
-    const float b1 = o.beta1, b2 = o.beta2, c1 = 1.f - o.beta1, c2 = 1.f - o.beta2;
-    m.x = b1 * m.x + c1 * g.x; m.y = b1 * m.y + c1 * g.y; m.z = b1 * m.z + c1 * g.z; m.w = b1 * m.w + c1 * g.w;
-    v.x = b2 * v.x + c2 * g.x * g.x; v.y = b2 * v.y + c2 * g.y * g.y; v.z = b2 * v.z + c2 * g.z * g.z; v.w = b2 * v.w + c2 * g.w * g.w;
-    w.x = w.x * o.decay + o.alpha * m.x / (sqrtf(v.x) + o.eps);
-    w.y = w.y * o.decay + o.alpha * m.y / (sqrtf(v.y) + o.eps);
-    w.z = w.z * o.decay + o.alpha * m.z / (sqrtf(v.z) + o.eps);
-    w.w = w.w * o.decay + o.alpha * m.w / (sqrtf(v.w) + o.eps);
-    st_f4(o.s1 + off, m); st_f4(o.s2 + off, v);
-  } else if (o.kind == RB_OPT_ADAGRAD) {
-    m.x += g.x * g.x; m.y += g.y * g.y; m.z += g.z * g.z; m.w += g.w * g.w;
-    w.x = w.x * o.decay - o.lr * g.x / (sqrtf(m.x) + o.eps);
-    w.y = w.y * o.decay - o.lr * g.y / (sqrtf(m.y) + o.eps);
-    w.z = w.z * o.decay - o.lr * g.z / (sqrtf(m.z) + o.eps);
-    w.w = w.w * o.decay - o.lr * g.w / (sqrtf(m.w) + o.eps);
-    st_f4(o.s1 + off, m);
-  } else {
-    w.x = w.x * o.decay - o.lr * g.x; w.y = w.y * o.decay - o.lr * g.y;
-    w.z = w.z * o.decay - o.lr * g.z; w.w = w.w * o.decay - o.lr * g.w;
-  }
-  st_f4(o.w + off, w);
 }
 
 // Owner: chain together the incoming ids that resolved to the same table row (different requesters may ask for the
@@ -303,7 +250,7 @@ owner_unlink_kernel(const int32_t* __restrict__ rows_in, const int32_t* __restri
 // ascending j order so the result does not depend on scheduling), then updates the row (apply) or stores (row, gradient)
 // at position j (apply == 0; non-head positions get row -1). U independent items are in flight per thread: their index
 // reads, optimizer-state loads and gradient loads are all issued before any of them is consumed.
-template <int U>
+template <int U, typename T>
 __global__ void __launch_bounds__(kThreads)
 owner_reduce_kernel(const int32_t* __restrict__ rows_in, const int32_t* __restrict__ head, const int32_t* __restrict__ next,
                     const int32_t* __restrict__ prefix_in, const float* __restrict__ g_in, int world, int D,
@@ -334,7 +281,7 @@ owner_reduce_kernel(const int32_t* __restrict__ rows_in, const int32_t* __restri
       if (!is_head[u]) continue;
       const int64_t off = (int64_t)row[u] * D + c[u] * 4;
       if (apply) {
-        sw[u] = ld_f4(opt.w + off);
+        sw[u] = RowIO<T>::ld4(static_cast<const T*>(opt.w) + off);
         if (opt.kind != RB_OPT_SGD) s1v[u] = ld_f4(opt.s1 + off);
         if (opt.kind == RB_OPT_ADAM) s2v[u] = ld_f4(opt.s2 + off);
       }
@@ -364,7 +311,7 @@ owner_reduce_kernel(const int32_t* __restrict__ rows_in, const int32_t* __restri
       if (mean_by_id && cnt > 1) { const float sc = 1.f / (float)cnt; acc[u].x *= sc; acc[u].y *= sc; acc[u].z *= sc; acc[u].w *= sc; }
       const int64_t off = (int64_t)row[u] * D + c[u] * 4;
       if (apply) {
-        opt_update_pre_f4(opt, off, acc[u], sw[u], s1v[u], s2v[u]);
+        opt_update_pre_f4<T>(opt, off, acc[u], sw[u], s1v[u], s2v[u]);
       } else {
         if (c[u] == 0) out_rows[j0[u]] = row[u];
         const float gs = opt.grad_scale;
@@ -419,13 +366,14 @@ void rb_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_count
   rb::note_launch();
 }
 
-void rb_comm_push_emb(const float* emb, const int32_t* rows_in, const int32_t* prefix, RbPeers peer_uemb, int me, int world, int D,
-                      int64_t n_in_max, int blocks, cudaStream_t st) {
+void rb_comm_push_emb(const void* emb, const int32_t* rows_in, const int32_t* prefix, RbPeers peer_uemb, int me, int world,
+                      int64_t row_bytes, int64_t n_in_max, int blocks, cudaStream_t st) {
   // blocks > 0 caps the grid: the kernel is bound by NVLink, not by the SMs, and a small grid leaves the SMs to kernels of
   // other streams that run at the same time
-  int g = grid_stride_blocks(n_in_max * (D / 4));
+  const int q = (int)(row_bytes / 16);         // callers guarantee row_bytes % 16 == 0
+  int g = grid_stride_blocks(n_in_max * q);
   if (blocks > 0 && blocks < g) g = blocks;
-  push_emb_kernel<<<g, kThreads, 0, st>>>(emb, rows_in, prefix, peer_uemb, me, world, D);
+  push_emb_kernel<<<g, kThreads, 0, st>>>(static_cast<const uint4*>(emb), rows_in, prefix, peer_uemb, me, world, q);
   rb::note_launch();
 }
 
@@ -436,12 +384,15 @@ void rb_comm_owner_reduce(const int32_t* rows_in, int32_t* head, int32_t* next, 
   owner_link_kernel<<<g1, kThreads, 0, st>>>(rows_in, prefix, world, head, next);
   rb::note_launch();
   const int g2 = grid_stride_blocks(n_in_max * (D / 4) / 4 + 1);
-  if (unroll >= 4)
-    owner_reduce_kernel<4><<<g2, kThreads, 0, st>>>(rows_in, head, next, prefix, g_in, world, D, mean_by_id, apply, opt, out_rows, out_grads);
-  else if (unroll >= 2)
-    owner_reduce_kernel<2><<<g2, kThreads, 0, st>>>(rows_in, head, next, prefix, g_in, world, D, mean_by_id, apply, opt, out_rows, out_grads);
-  else
-    owner_reduce_kernel<1><<<g2, kThreads, 0, st>>>(rows_in, head, next, prefix, g_in, world, D, mean_by_id, apply, opt, out_rows, out_grads);
+  const int dtype = apply ? opt.w_dtype : (int)rb::kRowF32;      // without an update no row is touched
+  RB_DISPATCH_ROW(dtype, false, {
+    if (unroll >= 4)
+      owner_reduce_kernel<4, T><<<g2, kThreads, 0, st>>>(rows_in, head, next, prefix, g_in, world, D, mean_by_id, apply, opt, out_rows, out_grads);
+    else if (unroll >= 2)
+      owner_reduce_kernel<2, T><<<g2, kThreads, 0, st>>>(rows_in, head, next, prefix, g_in, world, D, mean_by_id, apply, opt, out_rows, out_grads);
+    else
+      owner_reduce_kernel<1, T><<<g2, kThreads, 0, st>>>(rows_in, head, next, prefix, g_in, world, D, mean_by_id, apply, opt, out_rows, out_grads);
+  });
   rb::note_launch();
   owner_unlink_kernel<<<g1, kThreads, 0, st>>>(rows_in, prefix, world, head);
   rb::note_launch();

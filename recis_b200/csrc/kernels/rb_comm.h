@@ -28,8 +28,9 @@ void rb_comm_pull_ids(RbPeers peer_ids, RbPeers peer_offsets, RbPeers peer_count
 // [world], for every owner o the first row of this rank's bucket inside o's incoming order [world], and a copy of this
 // rank's own bucket boundaries [world+1]
 // blocks > 0 caps the grid size (the kernel is NVLink-bound; a small grid leaves SMs to concurrent kernels)
-void rb_comm_push_emb(const float* emb, const int32_t* rows_in, const int32_t* prefix, RbPeers peer_uemb, int me, int world, int D,
-                      int64_t n_in_max, int blocks, cudaStream_t st);
+// rows travel as bytes: row_bytes = D * element size of the table's rows, a multiple of 16
+void rb_comm_push_emb(const void* emb, const int32_t* rows_in, const int32_t* prefix, RbPeers peer_uemb, int me, int world,
+                      int64_t row_bytes, int64_t n_in_max, int blocks, cudaStream_t st);
 // head: int32[table capacity], all -1 between calls; next: int32[n_in_max] scratch; g_in: this rank's gradient window
 // [n_in_max, D] filled by the requesters (rb_grad_reduce_push); unroll: 1, 2 or 4 work items in flight per thread.
 void rb_comm_owner_reduce(const int32_t* rows_in, int32_t* head, int32_t* next, const int32_t* prefix, const float* g_in, int world,

@@ -40,6 +40,8 @@ typedef struct RbInit {
 
 // row-wise sparse optimizers
 enum RbOptKind { RB_OPT_ADAM = 0, RB_OPT_ADAGRAD = 1, RB_OPT_SGD = 2 };
+// storage types of embedding rows (rb::RowDType): 0 fp32, 1 fp16, 2 bf16, 3 int8 (read-only tables)
+enum RbRowDType { RB_ROW_F32 = 0, RB_ROW_F16 = 1, RB_ROW_BF16 = 2, RB_ROW_I8 = 3 };
 typedef struct RbOpt {
   int kind;
   float lr;
@@ -47,7 +49,8 @@ typedef struct RbOpt {
   float decay;      // multiplicative weight decay factor applied to touched rows (1 = none)
   float alpha;      // Adam: -lr*sqrt(1-beta2^t)/(1-beta1^t)
   float grad_scale; // 1/(world * accumulation steps) etc.
-  float* w;         // [cap, D] embedding slab
+  void* w;          // [cap, D] embedding slab, elements of type w_dtype (fp32 / fp16 / bf16)
+  int w_dtype;      // RbRowDType of w; the state below and all arithmetic are fp32
   float* s1;        // Adam exp_avg    | Adagrad accumulator
   float* s2;        // Adam exp_avg_sq | unused
 } RbOpt;
@@ -65,7 +68,7 @@ typedef struct RbGuPush {
 
 // ---- table.cu
 void rb_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* slot_scratch,
-                               int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, float* emb, int D, RbInit init,
+                               int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, void* emb, int emb_dtype, int D, RbInit init,
                                int64_t* last_seen, const int64_t* step_dev, int admit_threshold, cudaStream_t st);
 void rb_table_find(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* rows_out, cudaStream_t st);
 void rb_table_erase(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* erased_rows, cudaStream_t st);
@@ -84,19 +87,21 @@ void rb_dedup_partition(const int64_t* ids, int64_t n, int world, uint64_t* set_
 // table_idx = int64[F].
 void rb_encode_merge(const int64_t* desc, const int64_t* table_idx, int F, int64_t total_nnz, int64_t total_seg,
                      int64_t* ids_out, int32_t* offsets_out, cudaStream_t st);
-void rb_gather_rows(const float* src, const int32_t* rows, int64_t n_max, const int32_t* n_dev, int D, float* out, cudaStream_t st);
-void rb_scatter_rows(float* dst, const int32_t* rows, int64_t n, int D, const float* src, int src_broadcast, cudaStream_t st);
+// Row copies work on bytes: row_bytes = D * element size, any element type (source and destination have the same).
+void rb_gather_rows(const void* src, const int32_t* rows, int64_t n_max, const int32_t* n_dev, int64_t row_bytes, void* out, cudaStream_t st);
+void rb_scatter_rows(void* dst, const int32_t* rows, int64_t n, int64_t row_bytes, const void* src, int src_broadcast, cudaStream_t st);
 void rb_fill_rows_i64(int64_t* dst, const int32_t* rows, int64_t n, int64_t value, cudaStream_t st);
 // Pooling: out[orow(s)] = sum_i scale_i * base[row_i]; row_i = rows ? rows[rev[i]] : rev[i].
 // mode 0 sum, 1 mean over length, 2 mean over weight sum. perm_f > 0 writes segment s=(f*perm_b+b) to row
 // b*perm_total + perm_off + f (perm_total <= 0 means perm_total = perm_f, perm_off = 0): several calls can fill disjoint
 // feature ranges of one [batch, perm_total, D] output. perm_f <= 0: segment s goes to row perm_off + s.
 // gsrc/gscale (nullable) record, per element, the output row and the scale for the backward pass.
-void rb_pool_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
+// base holds rows of type base_dtype (RbRowDType); sums and the output are fp32.
+void rb_pool_forward(const void* base, int base_dtype, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
                      int64_t n_seg, int D, int mode, int perm_b, int perm_f, int perm_off, int perm_total, float* out, int32_t* gsrc,
                      float* gscale, cudaStream_t st);
 // Tile combiner: out[s, t*D:(t+1)*D] = base[row of element t of segment s], t < tile_len, zero padded.
-void rb_tile_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
+void rb_tile_forward(const void* base, int base_dtype, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
                      int64_t n_seg, int D, int tile_len, float* out, int32_t* gsrc, float* gscale, cudaStream_t st);
 // Backward structure: stable radix sort of (reverse, element) pairs and per-unique start positions.
 size_t rb_sort_temp_bytes(int64_t n);

@@ -15,6 +15,7 @@
 // per-element atomic traffic and no intermediate gradient tensor on the single-GPU path.
 #include "../common/rb_common.cuh"
 #include "rb_kernels.h"
+#include "../common/rb_opt.cuh"
 #include "rb_comm.h"
 #include "../common/rb_launch.h"
 #include <cub/device/device_radix_sort.cuh>
@@ -132,36 +133,43 @@ encode_merge_kernel(const int64_t* __restrict__ desc, const int64_t* __restrict_
 }
 
 // ------------------------------------------------------------------ row gather / scatter
+// Rows are copied as bytes, V bytes per thread and access (V = the largest of 16, 8, 4, 2, 1 that divides the row size), so
+// that one pair of kernels serves rows of every element type.
+template <typename V>
 __global__ void __launch_bounds__(kThreads)
-gather_rows_kernel(const float* __restrict__ src, const int32_t* __restrict__ rows, int64_t n_max, const int32_t* __restrict__ n_dev,
-                   int D, float* __restrict__ out) {
+gather_rows_kernel(const V* __restrict__ src, const int32_t* __restrict__ rows, int64_t n_max, const int32_t* __restrict__ n_dev,
+                   int q, V* __restrict__ out) {
   const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
-  if ((D & 3) == 0) {
-    const int q = D >> 2; const int64_t total = n * q;
-    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
-      const int64_t r = w / q; const int c = (int)(w - r * q);
-      const int32_t row = rows[r];
-      st_f4(out + r * D + c * 4, row >= 0 ? ld_f4(src + (int64_t)row * D + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f));
-    }
-  } else {
-    const int64_t total = n * D;
-    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
-      const int64_t r = w / D; const int c = (int)(w - r * D);
-      const int32_t row = rows[r];
-      out[w] = row >= 0 ? src[(int64_t)row * D + c] : 0.f;
-    }
+  const int64_t total = n * q;
+  V zero; memset(&zero, 0, sizeof(V));
+  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = w / q; const int c = (int)(w - r * q);
+    const int32_t row = rows[r];
+    out[r * q + c] = row >= 0 ? src[(int64_t)row * q + c] : zero;
   }
 }
 
+template <typename V>
 __global__ void __launch_bounds__(kThreads)
-scatter_rows_kernel(float* __restrict__ dst, const int32_t* __restrict__ rows, int64_t n, int D, const float* __restrict__ src,
+scatter_rows_kernel(V* __restrict__ dst, const int32_t* __restrict__ rows, int64_t n, int q, const V* __restrict__ src,
                     int src_broadcast) {
-  const int64_t total = n * D;
+  const int64_t total = n * q;
   for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = w / D; const int c = (int)(w - r * D);
+    const int64_t r = w / q; const int c = (int)(w - r * q);
     const int32_t row = rows[r];
-    if (row >= 0) dst[(int64_t)row * D + c] = src_broadcast ? src[c] : src[w];
+    if (row >= 0) dst[(int64_t)row * q + c] = src_broadcast ? src[c] : src[w];
   }
+}
+
+// f(V{}, q) with V the widest vector type that divides row_bytes and keeps both base pointers aligned
+template <typename F>
+inline void dispatch_row_bytes(int64_t row_bytes, const void* a, const void* b, F&& f) {
+  const uintptr_t al = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | (uintptr_t)row_bytes;
+  if ((al & 15) == 0) f(uint4{}, (int)(row_bytes / 16));
+  else if ((al & 7) == 0) f(uint2{}, (int)(row_bytes / 8));
+  else if ((al & 3) == 0) f(uint32_t{}, (int)(row_bytes / 4));
+  else if ((al & 1) == 0) f(uint16_t{}, (int)(row_bytes / 2));
+  else f(uint8_t{}, (int)row_bytes);
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -181,9 +189,9 @@ __device__ __forceinline__ int64_t out_row_of(int64_t s, int perm_b, int perm_f,
 }
 
 // One group of G lanes per segment; each lane owns NACC float4 column slots (columns lane + a*G).
-template <int G, int NACC>
+template <int G, int NACC, typename T>
 __global__ void __launch_bounds__(kThreads)
-pool_forward_kernel(const float* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
+pool_forward_kernel(const T* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
                     const int32_t* __restrict__ offsets, const float* __restrict__ weights, int64_t n_seg, int D, int mode,
                     int perm_b, int perm_f, int perm_off, int perm_total, float* __restrict__ out, int32_t* __restrict__ gsrc,
                     float* __restrict__ gscale) {
@@ -214,7 +222,7 @@ pool_forward_kernel(const float* __restrict__ base, const int32_t* __restrict__ 
 #pragma unroll
         for (int a = 0; a < NACC; ++a) {
           const int c = lane + a * G;
-          v[j][a] = (r[j] >= 0 && c < cols) ? ld_f4(base + (int64_t)r[j] * D + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          v[j][a] = (r[j] >= 0 && c < cols) ? RowIO<T>::ld4(base + (int64_t)r[j] * D + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
       for (int j = 0; j < 4; ++j)
@@ -240,8 +248,9 @@ pool_forward_kernel(const float* __restrict__ base, const int32_t* __restrict__ 
 }
 
 // Any D (not a multiple of 4, or wider than 512): one thread per (segment, column).
+template <typename T>
 __global__ void __launch_bounds__(kThreads)
-pool_forward_scalar_kernel(const float* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
+pool_forward_scalar_kernel(const T* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
                            const int32_t* __restrict__ offsets, const float* __restrict__ weights, int64_t n_seg, int D, int mode,
                            int perm_b, int perm_f, int perm_off, int perm_total, float* __restrict__ out, int32_t* __restrict__ gsrc,
                            float* __restrict__ gscale) {
@@ -254,7 +263,7 @@ pool_forward_scalar_kernel(const float* __restrict__ base, const int32_t* __rest
       const int32_t u = rev[i]; const int32_t r = rows ? rows[u] : u;
       const float wt = weights ? weights[i] : 1.f;
       wsum += wt;
-      if (r >= 0) acc = fmaf(wt, base[(int64_t)r * D + c], acc);
+      if (r >= 0) acc = fmaf(wt, RowIO<T>::ld1(base + (int64_t)r * D + c), acc);
     }
     float scale = 1.f;
     if (mode == 1) scale = end > beg ? 1.f / (float)(end - beg) : 0.f;
@@ -266,8 +275,9 @@ pool_forward_scalar_kernel(const float* __restrict__ base, const int32_t* __rest
   }
 }
 
+template <typename T>
 __global__ void __launch_bounds__(kThreads)
-tile_forward_kernel(const float* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
+tile_forward_kernel(const T* __restrict__ base, const int32_t* __restrict__ rows, const int32_t* __restrict__ rev,
                     const int32_t* __restrict__ offsets, const float* __restrict__ weights, int64_t n_seg, int D, int tile_len,
                     float* __restrict__ out, int32_t* __restrict__ gsrc, float* __restrict__ gscale) {
   const int64_t total = n_seg * tile_len * (int64_t)D;
@@ -279,7 +289,7 @@ tile_forward_kernel(const float* __restrict__ base, const int32_t* __restrict__ 
     if (beg + t < end) {
       const int32_t u = rev[beg + t]; const int32_t r = rows ? rows[u] : u;
       const float wt = weights ? weights[beg + t] : 1.f;
-      if (r >= 0) v = wt * base[(int64_t)r * D + c];
+      if (r >= 0) v = wt * RowIO<T>::ld1(base + (int64_t)r * D + c);
       if (gsrc && c == 0) { gsrc[beg + t] = (int32_t)st; gscale[beg + t] = wt; }
     }
     out[w] = v;
@@ -302,81 +312,6 @@ __global__ void __launch_bounds__(kThreads) csr_heads_kernel(const int32_t* __re
   }
 }
 
-// ------------------------------------------------------------------ row-wise optimizer math
-__device__ __forceinline__ void opt_update_f4(const RbOpt& o, int64_t off, float4 g) {
-  const float gs = o.grad_scale;
-  g.x *= gs; g.y *= gs; g.z *= gs; g.w *= gs;
-  float4 w = ld_f4(o.w + off);
-  if (o.kind == RB_OPT_ADAM) {
-    float4 m = ld_f4(o.s1 + off), v = ld_f4(o.s2 + off);
-    const float b1 = o.beta1, b2 = o.beta2, c1 = 1.f - o.beta1, c2 = 1.f - o.beta2;
-    m.x = b1 * m.x + c1 * g.x; m.y = b1 * m.y + c1 * g.y; m.z = b1 * m.z + c1 * g.z; m.w = b1 * m.w + c1 * g.w;
-    v.x = b2 * v.x + c2 * g.x * g.x; v.y = b2 * v.y + c2 * g.y * g.y; v.z = b2 * v.z + c2 * g.z * g.z; v.w = b2 * v.w + c2 * g.w * g.w;
-    w.x = w.x * o.decay + o.alpha * m.x / (sqrtf(v.x) + o.eps);
-    w.y = w.y * o.decay + o.alpha * m.y / (sqrtf(v.y) + o.eps);
-    w.z = w.z * o.decay + o.alpha * m.z / (sqrtf(v.z) + o.eps);
-    w.w = w.w * o.decay + o.alpha * m.w / (sqrtf(v.w) + o.eps);
-    st_f4(o.s1 + off, m); st_f4(o.s2 + off, v);
-  } else if (o.kind == RB_OPT_ADAGRAD) {
-    float4 a = ld_f4(o.s1 + off);
-    a.x += g.x * g.x; a.y += g.y * g.y; a.z += g.z * g.z; a.w += g.w * g.w;
-    w.x = w.x * o.decay - o.lr * g.x / (sqrtf(a.x) + o.eps);
-    w.y = w.y * o.decay - o.lr * g.y / (sqrtf(a.y) + o.eps);
-    w.z = w.z * o.decay - o.lr * g.z / (sqrtf(a.z) + o.eps);
-    w.w = w.w * o.decay - o.lr * g.w / (sqrtf(a.w) + o.eps);
-    st_f4(o.s1 + off, a);
-  } else {
-    w.x = w.x * o.decay - o.lr * g.x; w.y = w.y * o.decay - o.lr * g.y;
-    w.z = w.z * o.decay - o.lr * g.z; w.w = w.w * o.decay - o.lr * g.w;
-  }
-  st_f4(o.w + off, w);
-}
-
-// Same update with the row's state already in registers (requested when the row's segment started).
-__device__ __forceinline__ void opt_update_pre_f4(const RbOpt& o, int64_t off, float4 g, float4 w, float4 m, float4 v) {
-  const float gs = o.grad_scale;
-  g.x *= gs; g.y *= gs; g.z *= gs; g.w *= gs;
-  if (o.kind == RB_OPT_ADAM) {
-    const float b1 = o.beta1, b2 = o.beta2, c1 = 1.f - o.beta1, c2 = 1.f - o.beta2;
-    m.x = b1 * m.x + c1 * g.x; m.y = b1 * m.y + c1 * g.y; m.z = b1 * m.z + c1 * g.z; m.w = b1 * m.w + c1 * g.w;
-    v.x = b2 * v.x + c2 * g.x * g.x; v.y = b2 * v.y + c2 * g.y * g.y; v.z = b2 * v.z + c2 * g.z * g.z; v.w = b2 * v.w + c2 * g.w * g.w;
-    w.x = w.x * o.decay + o.alpha * m.x / (sqrtf(v.x) + o.eps);
-    w.y = w.y * o.decay + o.alpha * m.y / (sqrtf(v.y) + o.eps);
-    w.z = w.z * o.decay + o.alpha * m.z / (sqrtf(v.z) + o.eps);
-    w.w = w.w * o.decay + o.alpha * m.w / (sqrtf(v.w) + o.eps);
-    st_f4(o.s1 + off, m); st_f4(o.s2 + off, v);
-  } else if (o.kind == RB_OPT_ADAGRAD) {
-    m.x += g.x * g.x; m.y += g.y * g.y; m.z += g.z * g.z; m.w += g.w * g.w;
-    w.x = w.x * o.decay - o.lr * g.x / (sqrtf(m.x) + o.eps);
-    w.y = w.y * o.decay - o.lr * g.y / (sqrtf(m.y) + o.eps);
-    w.z = w.z * o.decay - o.lr * g.z / (sqrtf(m.z) + o.eps);
-    w.w = w.w * o.decay - o.lr * g.w / (sqrtf(m.w) + o.eps);
-    st_f4(o.s1 + off, m);
-  } else {
-    w.x = w.x * o.decay - o.lr * g.x; w.y = w.y * o.decay - o.lr * g.y;
-    w.z = w.z * o.decay - o.lr * g.z; w.w = w.w * o.decay - o.lr * g.w;
-  }
-  st_f4(o.w + off, w);
-}
-
-__device__ __forceinline__ void opt_update_f1(const RbOpt& o, int64_t off, float g) {
-  g *= o.grad_scale;
-  float w = o.w[off];
-  if (o.kind == RB_OPT_ADAM) {
-    const float m = o.beta1 * o.s1[off] + (1.f - o.beta1) * g;
-    const float v = o.beta2 * o.s2[off] + (1.f - o.beta2) * g * g;
-    o.s1[off] = m; o.s2[off] = v;
-    w = w * o.decay + o.alpha * m / (sqrtf(v) + o.eps);
-  } else if (o.kind == RB_OPT_ADAGRAD) {
-    const float a = o.s1[off] + g * g;
-    o.s1[off] = a;
-    w = w * o.decay - o.lr * g / (sqrtf(a) + o.eps);
-  } else {
-    w = w * o.decay - o.lr * g;
-  }
-  o.w[off] = w;
-}
-
 // ------------------------------------------------------------------ chunked segmented gradient reduction
 // VEC = 4: float4 columns, G lanes x NACC slots per group. Work item = kChunk consecutive CSR positions.
 // Shared-memory copy of a push descriptor: row_ptr(u) is where the gradient of unique index u is stored (nullptr = dropped).
@@ -397,7 +332,7 @@ struct PushTable {
   }
 };
 
-template <int G, int NACC, bool PUSH>
+template <int G, int NACC, bool PUSH, typename T>
 __global__ void __launch_bounds__(kThreads)
 grad_reduce_kernel(const float* __restrict__ grad_out, const int32_t* __restrict__ gsrc, const float* __restrict__ gscale,
                    const int32_t* __restrict__ csr_u, const int32_t* __restrict__ csr_elem, const int32_t* __restrict__ start,
@@ -450,7 +385,7 @@ grad_reduce_kernel(const float* __restrict__ grad_out, const int32_t* __restrict
           const int col = lane + a * G;
           if (col < cols) {
             const int64_t off = (int64_t)row * D + col * 4;
-            sw[a] = ld_f4(opt.w + off);
+            sw[a] = RowIO<T>::ld4(static_cast<const T*>(opt.w) + off);
             if (opt.kind != RB_OPT_SGD) s1v[a] = ld_f4(opt.s1 + off);
             if (opt.kind == RB_OPT_ADAM) s2v[a] = ld_f4(opt.s2 + off);
           }
@@ -482,7 +417,7 @@ grad_reduce_kernel(const float* __restrict__ grad_out, const int32_t* __restrict
         const int col = lane + a * G;
         if (col >= cols) continue;
         if (row == -2) red_add_f4(span_acc + (int64_t)m_dst[j] * D + col * 4, acc[a]);
-        else if (upd) opt_update_pre_f4(opt, (int64_t)row * D + col * 4, acc[a], sw[a], s1v[a], s2v[a]);
+        else if (upd) opt_update_pre_f4<T>(opt, (int64_t)row * D + col * 4, acc[a], sw[a], s1v[a], s2v[a]);
         else if (!apply) {
           if (PUSH) {
             float* dstp = ptab.row_ptr(row, push.world, push.cap_rows, D);
@@ -500,7 +435,7 @@ grad_reduce_kernel(const float* __restrict__ grad_out, const int32_t* __restrict
 
 // Rows whose occurrences cross a chunk boundary were accumulated in span_acc[chunk of their first
 // occurrence]; finish them here and leave span_acc zeroed for the next step.
-template <int G, int NACC, bool PUSH>
+template <int G, int NACC, bool PUSH, typename T>
 __global__ void __launch_bounds__(kThreads)
 grad_span_finish_kernel(const int32_t* __restrict__ csr_u, const int32_t* __restrict__ start, int64_t n, int D,
                         float* __restrict__ span_acc, const int32_t* __restrict__ rows, float* __restrict__ gu, int apply, RbOpt opt,
@@ -524,7 +459,7 @@ grad_span_finish_kernel(const int32_t* __restrict__ csr_u, const int32_t* __rest
       if (col < cols) {
         const float4 g = ld_f4(src + col * 4);
         st_f4(src + col * 4, make_float4(0.f, 0.f, 0.f, 0.f));
-        if (apply) { if (row >= 0) opt_update_f4(opt, (int64_t)row * D + col * 4, g); }
+        if (apply) { if (row >= 0) opt_update_f4<T>(opt, (int64_t)row * D + col * 4, g); }
         else if (PUSH) {
           float* dstp = ptab.row_ptr(u, push.world, push.cap_rows, D);
           if (dstp) st_f4(dstp + col * 4, g);
@@ -535,6 +470,7 @@ grad_span_finish_kernel(const int32_t* __restrict__ csr_u, const int32_t* __rest
 }
 
 // Scalar variant for D not a multiple of 4: one thread per (unique row, column) walking its CSR range.
+template <typename T>
 __global__ void __launch_bounds__(kThreads)
 grad_reduce_scalar_kernel(const float* __restrict__ grad_out, const int32_t* __restrict__ gsrc, const float* __restrict__ gscale,
                           const int32_t* __restrict__ csr_u, const int32_t* __restrict__ csr_elem, const int32_t* __restrict__ start,
@@ -548,11 +484,12 @@ grad_reduce_scalar_kernel(const float* __restrict__ grad_out, const int32_t* __r
       const int32_t e = csr_elem[p]; const int32_t gs = gsrc[e];
       if (gs >= 0) acc = fmaf(gscale[e], grad_out[(int64_t)gs * D + c], acc);
     }
-    if (apply) { const int32_t row = rows ? rows[u] : u; if (row >= 0) opt_update_f1(opt, (int64_t)row * D + c, acc); }
+    if (apply) { const int32_t row = rows ? rows[u] : u; if (row >= 0) opt_update_f1<T>(opt, (int64_t)row * D + c, acc); }
     else gu[w] = acc;
   }
 }
 
+template <typename T>
 __global__ void __launch_bounds__(kThreads)
 sparse_apply_kernel(const int32_t* __restrict__ rows, const float* __restrict__ grads, int64_t n_max, const int32_t* __restrict__ n_dev,
                     int D, RbOpt opt) {
@@ -562,14 +499,14 @@ sparse_apply_kernel(const int32_t* __restrict__ rows, const float* __restrict__ 
     for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
       const int64_t r = w / q; const int c = (int)(w - r * q);
       const int32_t row = rows[r];
-      if (row >= 0) opt_update_f4(opt, (int64_t)row * D + c * 4, ld_f4(grads + r * D + c * 4));
+      if (row >= 0) opt_update_f4<T>(opt, (int64_t)row * D + c * 4, ld_f4(grads + r * D + c * 4));
     }
   } else {
     const int64_t total = n * D;
     for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
       const int64_t r = w / D; const int c = (int)(w - r * D);
       const int32_t row = rows[r];
-      if (row >= 0) opt_update_f1(opt, (int64_t)row * D + c, grads[w]);
+      if (row >= 0) opt_update_f1<T>(opt, (int64_t)row * D + c, grads[w]);
     }
   }
 }
@@ -615,15 +552,21 @@ void rb_encode_merge(const int64_t* desc, const int64_t* table_idx, int F, int64
   rb::note_launch();
 }
 
-void rb_gather_rows(const float* src, const int32_t* rows, int64_t n_max, const int32_t* n_dev, int D, float* out, cudaStream_t st) {
-  if (n_max <= 0) return;
-  gather_rows_kernel<<<grid_stride_blocks(n_max * ((D + 3) / 4)), kThreads, 0, st>>>(src, rows, n_max, n_dev, D, out);
+void rb_gather_rows(const void* src, const int32_t* rows, int64_t n_max, const int32_t* n_dev, int64_t row_bytes, void* out, cudaStream_t st) {
+  if (n_max <= 0 || row_bytes <= 0) return;
+  dispatch_row_bytes(row_bytes, src, out, [&](auto v, int q) {
+    using V = decltype(v);
+    gather_rows_kernel<V><<<grid_stride_blocks(n_max * q), kThreads, 0, st>>>(static_cast<const V*>(src), rows, n_max, n_dev, q, static_cast<V*>(out));
+  });
   rb::note_launch();
 }
 
-void rb_scatter_rows(float* dst, const int32_t* rows, int64_t n, int D, const float* src, int src_broadcast, cudaStream_t st) {
-  if (n <= 0) return;
-  scatter_rows_kernel<<<grid_stride_blocks(n * D), kThreads, 0, st>>>(dst, rows, n, D, src, src_broadcast);
+void rb_scatter_rows(void* dst, const int32_t* rows, int64_t n, int64_t row_bytes, const void* src, int src_broadcast, cudaStream_t st) {
+  if (n <= 0 || row_bytes <= 0) return;
+  dispatch_row_bytes(row_bytes, src, dst, [&](auto v, int q) {
+    using V = decltype(v);
+    scatter_rows_kernel<V><<<grid_stride_blocks(n * q), kThreads, 0, st>>>(static_cast<V*>(dst), rows, n, q, static_cast<const V*>(src), src_broadcast);
+  });
   rb::note_launch();
 }
 
@@ -633,30 +576,32 @@ void rb_fill_rows_i64(int64_t* dst, const int32_t* rows, int64_t n, int64_t valu
   rb::note_launch();
 }
 
-void rb_pool_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
+void rb_pool_forward(const void* base, int base_dtype, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
                      int64_t n_seg, int D, int mode, int perm_b, int perm_f, int perm_off, int perm_total, float* out, int32_t* gsrc,
                      float* gscale, cudaStream_t st) {
   if (n_seg <= 0) return;
   if (perm_f > 0 && perm_total <= 0) { perm_total = perm_f; perm_off = 0; }
-  const bool ok = dispatch_cols(D, [&](auto g, auto nacc) {
-    constexpr int G = decltype(g)::value, NACC = decltype(nacc)::value;
-    const int64_t blocks = (n_seg + (kThreads / G) - 1) / (kThreads / G);
-    pool_forward_kernel<G, NACC><<<(int)std::min<int64_t>(blocks, 148 * 64), kThreads, 0, st>>>(
-        base, rows, rev, offsets, weights, n_seg, D, mode, perm_b, perm_f, perm_off, perm_total, out, gsrc, gscale);
-        rb::note_launch();
+  RB_DISPATCH_ROW(base_dtype, true, {
+    const T* b = static_cast<const T*>(base);
+    const bool ok = dispatch_cols(D, [&](auto g, auto nacc) {
+      constexpr int G = decltype(g)::value, NACC = decltype(nacc)::value;
+      const int64_t blocks = (n_seg + (kThreads / G) - 1) / (kThreads / G);
+      pool_forward_kernel<G, NACC, T><<<(int)std::min<int64_t>(blocks, 148 * 64), kThreads, 0, st>>>(
+          b, rows, rev, offsets, weights, n_seg, D, mode, perm_b, perm_f, perm_off, perm_total, out, gsrc, gscale);
+    });
+    if (!ok)
+      pool_forward_scalar_kernel<T><<<grid_stride_blocks(n_seg * D), kThreads, 0, st>>>(b, rows, rev, offsets, weights, n_seg, D, mode,
+                                                                                       perm_b, perm_f, perm_off, perm_total, out, gsrc, gscale);
   });
-  if (!ok) {
-    pool_forward_scalar_kernel<<<grid_stride_blocks(n_seg * D), kThreads, 0, st>>>(base, rows, rev, offsets, weights, n_seg, D, mode,
-                                                                                  perm_b, perm_f, perm_off, perm_total, out, gsrc, gscale);
-    rb::note_launch();
-  }
+  rb::note_launch();
 }
 
-void rb_tile_forward(const float* base, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
+void rb_tile_forward(const void* base, int base_dtype, const int32_t* rows, const int32_t* rev, const int32_t* offsets, const float* weights,
                      int64_t n_seg, int D, int tile_len, float* out, int32_t* gsrc, float* gscale, cudaStream_t st) {
   if (n_seg <= 0) return;
-  tile_forward_kernel<<<grid_stride_blocks(n_seg * tile_len * D), kThreads, 0, st>>>(base, rows, rev, offsets, weights, n_seg, D,
-                                                                                    tile_len, out, gsrc, gscale);
+  RB_DISPATCH_ROW(base_dtype, true,
+                  (tile_forward_kernel<T><<<grid_stride_blocks(n_seg * tile_len * D), kThreads, 0, st>>>(
+                      static_cast<const T*>(base), rows, rev, offsets, weights, n_seg, D, tile_len, out, gsrc, gscale)));
   rb::note_launch();
 }
 
@@ -697,21 +642,24 @@ void rb_grad_reduce(const float* grad_out, const int32_t* gsrc, const float* gsc
                     cudaStream_t st) {
   if (n <= 0) return;
   const int64_t n_chunks = (n + kChunk - 1) / kChunk;
-  const bool ok = dispatch_cols(D, [&](auto g, auto nacc) {
-    constexpr int G = decltype(g)::value, NACC = decltype(nacc)::value;
-    const int64_t blocks = (n_chunks + (kThreads / G) - 1) / (kThreads / G);
-    const int grid = (int)std::min<int64_t>(blocks, 148 * 64);
-    grad_reduce_kernel<G, NACC, false><<<grid, kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, span_acc, rows,
-                                                                  gu, apply, opt, RbGuPush{});
-    rb::note_launch();
-    grad_span_finish_kernel<G, NACC, false><<<grid, kThreads, 0, st>>>(csr_u, start, n, D, span_acc, rows, gu, apply, opt, RbGuPush{});
-    rb::note_launch();
+  const int dtype = apply ? opt.w_dtype : (int)rb::kRowF32;      // without an update no row is touched: one instantiation serves
+  RB_DISPATCH_ROW(dtype, false, {
+    const bool ok = dispatch_cols(D, [&](auto g, auto nacc) {
+      constexpr int G = decltype(g)::value, NACC = decltype(nacc)::value;
+      const int64_t blocks = (n_chunks + (kThreads / G) - 1) / (kThreads / G);
+      const int grid = (int)std::min<int64_t>(blocks, 148 * 64);
+      grad_reduce_kernel<G, NACC, false, T><<<grid, kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, span_acc, rows,
+                                                                       gu, apply, opt, RbGuPush{});
+      rb::note_launch();
+      grad_span_finish_kernel<G, NACC, false, T><<<grid, kThreads, 0, st>>>(csr_u, start, n, D, span_acc, rows, gu, apply, opt, RbGuPush{});
+      rb::note_launch();
+    });
+    if (!ok) {
+      grad_reduce_scalar_kernel<T><<<grid_stride_blocks(n * D), kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, rows,
+                                                                                  gu, apply, opt);
+      rb::note_launch();
+    }
   });
-  if (!ok) {
-    grad_reduce_scalar_kernel<<<grid_stride_blocks(n * D), kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, rows,
-                                                                             gu, apply, opt);
-    rb::note_launch();
-  }
 }
 
 void rb_grad_reduce_push(const float* grad_out, const int32_t* gsrc, const float* gscale, const int32_t* csr_u, const int32_t* csr_elem,
@@ -724,17 +672,18 @@ void rb_grad_reduce_push(const float* grad_out, const int32_t* gsrc, const float
     const int64_t blocks = (n_chunks + (kThreads / G) - 1) / (kThreads / G);
     // max_blocks > 0 caps the grid (NVLink-bound kernel: a small grid leaves SMs to kernels of other streams)
     const int grid = (int)std::min<int64_t>(blocks, max_blocks > 0 ? max_blocks : 148 * 64);
-    grad_reduce_kernel<G, NACC, true><<<grid, kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, span_acc, nullptr,
-                                                                 nullptr, 0, opt, push);
+    grad_reduce_kernel<G, NACC, true, float><<<grid, kThreads, 0, st>>>(grad_out, gsrc, gscale, csr_u, csr_elem, start, n, D, span_acc, nullptr,
+                                                                        nullptr, 0, opt, push);
     rb::note_launch();
-    grad_span_finish_kernel<G, NACC, true><<<grid, kThreads, 0, st>>>(csr_u, start, n, D, span_acc, nullptr, nullptr, 0, opt, push);
+    grad_span_finish_kernel<G, NACC, true, float><<<grid, kThreads, 0, st>>>(csr_u, start, n, D, span_acc, nullptr, nullptr, 0, opt, push);
     rb::note_launch();
   });
 }
 
 void rb_sparse_apply(const int32_t* rows, const float* grads, int64_t n_max, const int32_t* n_dev, int D, RbOpt opt, cudaStream_t st) {
   if (n_max <= 0) return;
-  sparse_apply_kernel<<<grid_stride_blocks(n_max * ((D + 3) / 4)), kThreads, 0, st>>>(rows, grads, n_max, n_dev, D, opt);
+  RB_DISPATCH_ROW(opt.w_dtype, false,
+                  (sparse_apply_kernel<T><<<grid_stride_blocks(n_max * ((D + 3) / 4)), kThreads, 0, st>>>(rows, grads, n_max, n_dev, D, opt)));
   rb::note_launch();
 }
 

@@ -126,9 +126,10 @@ table_claim_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, co
 
 // Initialise the embedding of every row admitted by the preceding claim kernel.
 // Values are a function of (seed, id, column), see rb_common.cuh.
+template <typename T>
 __global__ void __launch_bounds__(kThreads)
 table_init_rows_kernel(RbTable t, const int32_t* __restrict__ new_rows, const int64_t* __restrict__ new_keys,
-                       float* __restrict__ emb, int D, InitSpec spec) {
+                       T* __restrict__ emb, int D, InitSpec spec) {
   const int64_t n_new = t.ctr[RB_CTR_NEW];
   const int quads = (D + 3) / 4;
   const int64_t total = n_new * quads;
@@ -138,9 +139,9 @@ table_init_rows_kernel(RbTable t, const int32_t* __restrict__ new_rows, const in
     if (row < 0) continue;
     float v[4];
     init_quad(spec, (uint64_t)new_keys[r], (uint32_t)q, v);
-    float* dst = emb + (int64_t)row * D + q * 4;
-    if ((D & 3) == 0) st_f4(dst, make_float4(v[0], v[1], v[2], v[3]));
-    else for (int j = 0; j < 4 && q * 4 + j < D; ++j) dst[j] = v[j];
+    T* dst = emb + (int64_t)row * D + q * 4;
+    if ((D & 3) == 0) RowIO<T>::st4(dst, make_float4(v[0], v[1], v[2], v[3]));
+    else for (int j = 0; j < 4 && q * 4 + j < D; ++j) RowIO<T>::st1(dst + j, v[j]);
   }
 }
 
@@ -279,14 +280,16 @@ inline int grid_for(int64_t n, int per_thread = 1) {
 extern "C" {
 
 void rb_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* slot_scratch,
-                               int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, float* emb, int D, RbInit init,
+                               int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, void* emb, int emb_dtype, int D, RbInit init,
                                int64_t* last_seen, const int64_t* step_dev, int admit_threshold, cudaStream_t st) {
   if (n_max <= 0) return;
   const int g = grid_for(n_max);
   InitSpec spec{init.kind, init.a, init.b, init.lo, init.hi, init.seed};
   table_claim_kernel<<<g, kThreads, 0, st>>>(t, ids, n_max, n_dev, slot_scratch, new_rows, new_keys, admit_threshold, 1);
   rb::note_launch();
-  table_init_rows_kernel<<<grid_for(n_max * ((D + 3) / 4), 4), kThreads, 0, st>>>(t, new_rows, new_keys, emb, D, spec);
+  RB_DISPATCH_ROW(emb_dtype, true,
+                  (table_init_rows_kernel<T><<<grid_for(n_max * ((D + 3) / 4), 4), kThreads, 0, st>>>(t, new_rows, new_keys,
+                                                                                                  static_cast<T*>(emb), D, spec)));
   rb::note_launch();
   table_resolve_kernel<<<g, kThreads, 0, st>>>(t, slot_scratch, n_max, n_dev, rows_out, last_seen, step_dev, 1);
   rb::note_launch();

@@ -20,6 +20,74 @@ from ..ragged import RaggedTensor
 from ..utils.data_utils import copy_data_to_device
 
 
+class PackedBatch:
+    """A batch (dict of tensors and RaggedTensors) whose tensors live in ONE host buffer, pinned by default.
+
+    Moving it to a device is a single copy of that buffer plus cheap views, instead of one copy per tensor (a batch of 26
+    ragged fields is 54 tensors: at ten microseconds of host time per copy that is half a millisecond per step spent issuing
+    copies). The reference's native packer emits batches the same way, as one allocation per batch
+    (``third_party/column-io``: ``dataset/packer.cc:61-113``). Pieces are aligned to 256 bytes, so every view is as aligned as a
+    fresh allocation. ``DevicePrefetcher`` understands packed batches; ``to(device)`` gives an ordinary dict."""
+
+    ALIGN = 256
+
+    def __init__(self, batch: dict, pin: bool = True):
+        self._plan = []           # (key, kind, pieces) with pieces = [(offset, dtype, shape)], in a fixed order per kind
+        pieces, off = [], 0
+
+        def add(t: torch.Tensor):
+            nonlocal off
+            t = t.detach().contiguous()
+            assert t.device.type == "cpu", "PackedBatch packs host tensors"
+            spec = (off, t.dtype, tuple(t.shape), t.numel() * t.element_size())
+            pieces.append((spec, t))
+            off = (off + spec[3] + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+            return spec
+
+        for k, v in batch.items():
+            if isinstance(v, torch.Tensor):
+                self._plan.append((k, "tensor", [add(v)], None))
+            elif isinstance(v, RaggedTensor):
+                specs = [add(v.values())] + [add(o) for o in v.offsets()]
+                has_w = v.weight() is not None
+                if has_w:
+                    specs.append(add(v.weight()))
+                self._plan.append((k, "ragged", specs, (len(v.offsets()), has_w, v._dense_shape if hasattr(v, "_dense_shape") else None)))
+            else:
+                self._plan.append((k, "other", [], v))
+        self.nbytes = max(off, self.ALIGN)
+        self.payload_bytes = sum(sp[3] for sp, _t in pieces)
+        self.buffer = torch.empty(self.nbytes, dtype=torch.uint8)
+        if pin and torch.cuda.is_available():
+            self.buffer = self.buffer.pin_memory()
+        for (o, _dt, _shape, n), t in pieces:
+            if n:
+                self.buffer[o:o + n].copy_(t.view(-1).view(torch.uint8))
+
+    def unpack(self, buf: torch.Tensor) -> dict:
+        """The batch as views of ``buf``, a byte tensor with this batch's layout (the host buffer or a device copy of it)."""
+        def view(spec):
+            o, dt, shape, n = spec
+            return buf[o:o + n].view(dt).view(shape)
+        out = {}
+        for k, kind, specs, extra in self._plan:
+            if kind == "tensor":
+                out[k] = view(specs[0])
+            elif kind == "ragged":
+                n_off, has_w, dense_shape = extra
+                out[k] = RaggedTensor(view(specs[0]), [view(s) for s in specs[1:1 + n_off]], weight=view(specs[-1]) if has_w else None,
+                                      dense_shape=dense_shape)
+            else:
+                out[k] = extra
+        return out
+
+    def to(self, device, non_blocking: bool = True) -> dict:
+        device = torch.device(device)
+        if device.type == "cpu":
+            return self.unpack(self.buffer)
+        return self.unpack(self.buffer.to(device, non_blocking=non_blocking))
+
+
 def _tensors(obj):
     if isinstance(obj, torch.Tensor):
         yield obj
@@ -59,7 +127,10 @@ class DevicePrefetcher:
             self.queue.append((host, None))
             return
         with torch.cuda.stream(self.stream):
-            dev = copy_data_to_device(host, self.device, non_blocking=True)
+            if isinstance(host, PackedBatch):
+                dev = (host, host.buffer.to(self.device, non_blocking=True))       # ONE copy for the whole batch
+            else:
+                dev = copy_data_to_device(host, self.device, non_blocking=True)
             ev = torch.cuda.Event()
             ev.record(self.stream)
         self.queue.append((dev, ev))
@@ -76,9 +147,14 @@ class DevicePrefetcher:
         if ev is not None:
             cur = torch.cuda.current_stream(self.device)
             cur.wait_event(ev)
+            if isinstance(batch, tuple) and isinstance(batch[0], PackedBatch):
+                batch[1].record_stream(cur)                   # one buffer backs every tensor of the batch
+                return batch[0].unpack(batch[1])
             for t in _tensors(batch):
                 if t.is_cuda:
                     t.record_stream(cur)
+        elif isinstance(batch, PackedBatch):
+            return batch.to("cpu")
         return batch
 
     def prefetch(self):

@@ -79,10 +79,11 @@ class EmbeddingOption:
             self.initializer = ConstantInitializer(init_val=0)
         if self.fp16_enabled:
             assert self.dtype in (torch.int8,), "only int8 emb can set fp16_enabled"
-        if self.dtype not in (torch.float32, torch.float16, torch.bfloat16):
-            # rows and optimizer state are kept in fp32; float16 / bfloat16 select the dtype of the lookup result only.
-            # Quantised (int8) tables, which the reference serves read-only with an fp16 upcast, are not implemented.
-            raise NotImplementedError(f"embedding dtype {self.dtype} is not supported (float32, float16, bfloat16 are)")
+        if self.dtype not in (torch.float32, torch.float16, torch.bfloat16, torch.int8):
+            # rows are stored in this dtype (optimizer state and accumulation stay fp32); int8 tables are read-only (filled by
+            # insert() or a checkpoint) and are served as float16 (fp16_enabled) or float32, as the reference does
+            # (recis/nn/modules/embedding.py:610-615)
+            raise NotImplementedError(f"embedding dtype {self.dtype} is not supported (float32, float16, bfloat16, int8 are)")
         assert self.combiner in ("sum", "mean", "tile"), \
             f"Hashtable combiner only support [sum/mean/tile], but got {self.combiner}"
         assert self.grad_reduce_by in ("worker", "id")
@@ -169,8 +170,8 @@ class _LookupPoolFn(torch.autograd.Function):
         o_n = o_offs[1:2]
         o_rows = store.find(o_uniq, o_n) if readonly else store.lookup_or_insert(o_uniq, o_n, step, threshold)
         rows_in = o_rows[o_rev.long()] if n_in else o_rows[:0]
-        emb_out = C.gather_rows(store.emb(), rows_in)
-        emb_back = torch.empty(n_u, D, dtype=torch.float32, device=ids.device)
+        emb_out = C.gather_rows(store.emb(), rows_in)                 # rows travel in their storage type
+        emb_back = torch.empty(n_u, D, dtype=emb_out.dtype, device=ids.device)
         tok = span_open("emb")
         _a2a(emb_back, emb_out, [s for s in send_splits], [r for r in recv_splits], pg)
         span_close(tok)
@@ -376,8 +377,14 @@ class DynamicEmbedding(torch.nn.Module):
             weights = weights.detach().reshape(-1).to(device=dev, dtype=torch.float32).contiguous()
         out = _LookupPoolFn.apply(self._holder, self, ids, offsets, weights, combiner, int(tile_len), perm, self.training,
                                   admit_hook if admit_hook is not None else self._emb_opt.admit_hook, lane, prepared)
-        # storage and pooling are fp32; a half-precision table dtype is the dtype the model sees
-        return out if self._emb_opt.dtype == torch.float32 else out.to(self._emb_opt.dtype)
+        return self._out_cast(out)
+
+    def _out_cast(self, out):
+        """Pooling accumulates in fp32; the model sees the table's dtype (int8 tables: float16 with ``fp16_enabled``, else float32)."""
+        dt = self._emb_opt.dtype
+        if dt == torch.int8:
+            return out.to(torch.float16) if self._emb_opt.fp16_enabled else out
+        return out if dt == torch.float32 else out.to(dt)
 
     def lookup_pool_group(self, parts, combiner: str, perm_b: int, perm_total: int, n_rows: int, admit_hook=None) -> torch.Tensor:
         """Pooled lookup of several lanes of one runtime group into ONE output ``[n_rows, D]`` (fused exchange only). ``parts``:
@@ -394,7 +401,7 @@ class DynamicEmbedding(torch.nn.Module):
         mode = 0 if combiner != "mean" else (2 if self._emb_opt.mean_by_weight else 1)
         out = _GroupLookupFn.apply(self._holder, self, parts, mode, int(perm_b), int(perm_total), int(n_rows), self.training,
                                    admit_hook if admit_hook is not None else self._emb_opt.admit_hook)
-        return out if self._emb_opt.dtype == torch.float32 else out.to(self._emb_opt.dtype)
+        return self._out_cast(out)
 
     # ---- the reference's three-stage interface (``recis/nn/modules/embedding.py:498-624``) on top of prepare_lookup / lookup_pool
     def exchange_ids(self, ids: torch.Tensor, offsets: torch.Tensor) -> "ExchangeIDsResults":

@@ -144,8 +144,13 @@ class HashtableImpl:
         cap = int(capacity) if capacity and capacity > 0 else 4096
         dev_str = str(self.device) if self.device.index is not None or self.device.type == "cpu" else (
             f"cuda:{torch.cuda.current_device()}")
+        # rows are stored in the table's dtype (float32 / float16 / bfloat16, or int8 for read-only tables); optimizer state
+        # slots and all accumulation are fp32 (the reference dispatches its row kernels over the same types,
+        # csrc/ops/block_ops_kernel.cu:236-273)
+        if dtype not in (torch.float32, torch.float16, torch.bfloat16, torch.int8):
+            raise NotImplementedError(f"embedding dtype {dtype} is not supported (float32, float16, bfloat16 and read-only int8 are)")
         self.store = native().EmbeddingStore(self.dim, cap, dev_str, kind, a, b, lo, hi, seed, track_last_seen, growable,
-                                             emb_storage)
+                                             emb_storage, dtype)
         self.store.set_name(name)
         self.device = torch.device(dev_str)
         self._records = []
@@ -171,7 +176,7 @@ class HashtableImpl:
     def insert(self, ids: torch.Tensor, embeddings: torch.Tensor):
         ids = ids.detach().reshape(-1).to(self.device).contiguous()
         rows = self.store.lookup_or_insert(ids, None, None, 1)
-        native().scatter_rows(self.store.emb(), rows, embeddings.to(self.device, torch.float32).contiguous(), False)
+        native().scatter_rows(self.store.emb(), rows, embeddings.to(self.device, self.store.emb().dtype).contiguous(), False)
         return rows
 
     def insert_lookup_index(self, ids: torch.Tensor):
@@ -244,7 +249,7 @@ class HashtableImpl:
         if not rows_l:
             return None, None
         rows = torch.cat(rows_l)
-        grads = torch.cat(grad_l)
+        grads = torch.cat([g.to(torch.float32) for g in grad_l])
         keep = rows >= 0  # unknown / not admitted ids, and the padding past a record's unique count
         rows, grads = rows[keep], grads[keep]
         uniq, inv = torch.unique(rows, return_inverse=True)

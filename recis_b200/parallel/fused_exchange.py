@@ -53,6 +53,10 @@ GROW_AT = 0.8           # grow when the demand exceeds this fraction of a window
 HEADROOM = 1.5          # new size = demand * HEADROOM
 
 
+# element size of the row types the exchange carries; the wire format of a row is its storage format
+_ROW_BYTES = {torch.float32: 4, torch.float16: 2, torch.bfloat16: 2, torch.int8: 1}
+
+
 def _round_up(x: int, q: int = 1024) -> int:
     return (int(x) + q - 1) // q * q
 
@@ -98,7 +102,7 @@ class _Lane:
             "offsets": (torch.int32, W + 1),
             "counts": (torch.int32, W),
             "ids": (torch.int64, self.send_cap),
-            "uemb": (torch.float32, self.send_cap * D),
+            "uemb": (ex.opt.dtype, self.send_cap * D),
             "gin": (torch.float32, self.in_cap * D),
         }, ex.device, ex.pg)
         counters = (0, 0, 0, 0) if self.native is None else (self.epoch, self.steps, self.last_train_epoch, self.pending_grad_epoch)
@@ -145,8 +149,10 @@ class _Lane:
 class FusedExchange:
     @staticmethod
     def create(emb_opt, pg, world, rank):
-        if emb_opt.embedding_dim % 4 != 0 or emb_opt.embedding_dim > 512 or emb_opt.dtype != torch.float32:
+        if emb_opt.dtype not in _ROW_BYTES or emb_opt.embedding_dim % 4 != 0 or emb_opt.embedding_dim > 512:
             return None
+        if (emb_opt.embedding_dim * _ROW_BYTES[emb_opt.dtype]) % 16 != 0:
+            return None                  # rows travel in 16-byte pieces
         if world > native().MAX_PEERS:
             return None
         return FusedExchange(emb_opt, pg, world, rank)

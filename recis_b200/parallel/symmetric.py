@@ -14,7 +14,7 @@ import torch.distributed as dist
 
 from .. import native
 
-_DT_SIZE = {torch.int64: 8, torch.int32: 4, torch.float32: 4, torch.uint8: 1, torch.bfloat16: 2}
+_DT_SIZE = {torch.int64: 8, torch.int32: 4, torch.float32: 4, torch.uint8: 1, torch.int8: 1, torch.bfloat16: 2, torch.float16: 2}
 
 
 def single_node(world: int) -> bool:

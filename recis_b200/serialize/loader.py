@@ -105,10 +105,16 @@ class Loader:
                             continue
                         pending[slot] = pool.submit(self.index.read, sdisk, r0, r1)
                     rows = impl.store.lookup_or_insert(enc.to(dev).contiguous(), None, None, 1)
+                    if bool((rows < 0).any()):
+                        # the table could not take every id of the checkpoint (fixed storage that is too small, or a full index)
+                        raise RuntimeError(
+                            f"checkpoint does not fit: table '{impl.name}' (child '{child}') holds {impl.size()} rows of "
+                            f"{impl.store.capacity()} and could not admit {int((rows < 0).sum())} of {rows.numel()} ids of this "
+                            "chunk; create the table with a larger capacity")
                     for slot, fut in pending.items():
                         data = fut.result()[keep]
                         if slot == N.FILTER_SLOT:
                             impl.store.last_seen().index_copy_(0, rows.long(), data.view(-1).to(dev))
                         else:
                             slab = impl.store.emb() if slot == N.EMB_SLOT else impl.store.slot(slot)
-                            C.scatter_rows(slab, rows, data.to(dev, torch.float32).contiguous(), False)
+                            C.scatter_rows(slab, rows, data.to(dev, slab.dtype).contiguous(), False)      # rows in the table's storage type

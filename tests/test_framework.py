@@ -469,3 +469,34 @@ def test_jobs_that_span_machines_do_not_use_peer_memory(monkeypatch):
     assert single_node(8)                                   # ranks spawned by hand on one machine
     monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
     assert single_node(8) and not single_node(16)           # 2 machines x 8 ranks
+
+
+def test_packed_batch_round_trip_and_prefetcher():
+    """A packed host batch (one buffer for all tensors) unpacks to the same batch, directly and through the prefetcher."""
+    from recis_b200.io import DevicePrefetcher, PackedBatch, SparseFieldSpec, SyntheticSpec, make_batch
+    from recis_b200.ragged import RaggedTensor
+    spec = SyntheticSpec(batch=16, dense_dim=5, label_rate=0.3, seed=3,
+                         sparse=[SparseFieldSpec(f, zipf_a=1.1, id_bits=20, universe=500, length="poisson", mean_len=3) for f in ("a", "b")])
+    batches = [make_batch(spec, i) for i in range(3)]
+    batches[1]["w"] = RaggedTensor(torch.arange(6), [torch.tensor([0, 2, 6], dtype=torch.int32)], weight=torch.rand(6))
+    batches[1]["note"] = "not a tensor"
+    packed = [PackedBatch(b, pin=False) for b in batches]
+
+    def same(x, y):
+        if isinstance(x, RaggedTensor):
+            assert torch.equal(x.values(), y.values()) and all(torch.equal(a, b) for a, b in zip(x.offsets(), y.offsets()))
+            assert (x.weight() is None) == (y.weight() is None) and (x.weight() is None or torch.equal(x.weight(), y.weight()))
+            assert x._dense_shape == y._dense_shape
+        elif isinstance(x, torch.Tensor):
+            assert x.dtype == y.dtype and torch.equal(x, y)
+        else:
+            assert x == y
+    for b, p in zip(batches, packed):
+        assert p.payload_bytes <= p.nbytes
+        got = p.to("cpu")
+        assert list(got) == list(b)
+        for k in b:
+            same(got[k], b[k])
+    for b, got in zip(batches, DevicePrefetcher(packed, "cpu")):
+        for k in b:
+            same(got[k], b[k])

@@ -152,10 +152,10 @@ def test_half_precision_table_dtype_is_the_output_dtype():
     out.float().sum().backward()
     opt.step()
     (t,) = eng.tables().values()
-    assert t.impl.store.emb().dtype == torch.float32                      # rows and optimizer state stay fp32
+    assert t.impl.store.emb().dtype == torch.bfloat16                     # rows are stored in the table dtype (2 bytes each)
     assert torch.allclose(eng({"a": torch.arange(3)})["a"].float(), torch.full((3, 4), -0.25))
     with pytest.raises(NotImplementedError):
-        EmbeddingOption(embedding_dim=4, dtype=torch.int8, device="cpu")
+        EmbeddingOption(embedding_dim=4, dtype=torch.float64, device="cpu")
 
 
 def test_reference_submodule_import_paths_exist():

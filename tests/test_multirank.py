@@ -408,6 +408,48 @@ def test_strict_exchange_repeats_the_id_phase_instead_of_dropping_ids():
         assert all(r["same"]) and all(e is None for e in r["errs"]) and r["grown"] >= 1
 
 
+def _bf16_rows_fn(rank, world, lanes):
+    """bf16 rows through the exchange: the wire format of a row is its 2-byte storage format."""
+    import torch
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.optim import SparseAdam
+    torch.manual_seed(17)
+    init = NormalInitializer(0, 0.05)
+    names = ["h0", "h1", "h2"]
+    eng = EmbeddingEngine({n: EmbeddingOption(embedding_dim=8, shared_name=n, combiner="sum", initializer=init, dtype=torch.bfloat16)
+                           for n in names}, interleave=True, exchange_lanes=lanes)
+    opt = SparseAdam(filter_out_sparse_param(eng), lr=0.05)
+    outs = []
+    for step in range(3):
+        g = torch.Generator().manual_seed(10 * step + rank)
+        feats = {n: torch.randint(0, 60, (12, 2), generator=g) * 7919 for n in names}
+        coef = {n: torch.randn(12, 8, generator=g) for n in names}
+        opt.zero_grad()
+        out = eng(feats)
+        sum((out[n].float() * coef[n]).sum() for n in names).backward()
+        opt.step()
+        outs.append({n: out[n].detach().float().clone() for n in names})
+    (table,) = eng.tables().values()
+    if table.fused is not None:
+        table.fused.check()
+        (lane, *_rest) = table.fused.lanes.values()
+        assert lane.heap["uemb"].tensor.dtype == torch.bfloat16
+    assert table.impl.store.emb().dtype == torch.bfloat16
+    ids, rows = table.impl.ids_map()
+    order = torch.argsort(ids)
+    return {"outs": outs, "ids": ids[order], "emb": table.impl.store.emb()[rows[order]].float().clone()}
+
+
+def test_bf16_rows_through_the_fused_exchange_match_the_collective_exchange():
+    fused = run_ranks(_bf16_rows_fn, 2, "gloo", args=(2,), env={"RECIS_COMM": "fused", "RECIS_WAIT_TIMEOUT_S": "60"})
+    coll = run_ranks(_bf16_rows_fn, 2, "gloo", args=(1,), env={"RECIS_COMM": "nccl"})
+    for a, b in zip(fused, coll):
+        assert torch.equal(a["ids"], b["ids"]) and torch.allclose(a["emb"], b["emb"], atol=2e-3)
+        for x, y in zip(a["outs"], b["outs"]):
+            assert all(torch.allclose(x[n], y[n], atol=2e-2) for n in x)
+
+
 def _skewed_fn(rank, world, jitter):
     """Many short steps with random delays in front of every flag signal and every pull / push: the ranks drift apart as far as
     the protocol lets them. Returns the final rows."""
