@@ -83,6 +83,98 @@ std::tuple<Tensor, Tensor> encode_merge(const Tensor& desc, const Tensor& table_
 }
 
 // out[i] = src[rows[i]] (zeros where rows[i] < 0); rows of any element type, the result has the type of src
+// encode_merge for several feature lists at once (the lanes of one runtime group): the descriptor tables of all lists are
+// written into one pinned staging buffer (a small ring, reused once its copy has completed) and travel to the device in ONE
+// asynchronous copy, then one kernel per list prefixes ids with the 12-bit child index and rebases offsets. Everything a
+// Python implementation would spend on building small tensors per list happens here instead.
+struct DescRing {
+  static constexpr int kSlots = 8;
+  Tensor buf[kSlots];
+  cudaEvent_t ev[kSlots] = {};
+  bool used[kSlots] = {};
+  int head = 0;
+};
+
+std::vector<std::tuple<Tensor, Tensor>> coalesce_lanes(const std::vector<std::vector<Tensor>>& ids, const std::vector<std::vector<Tensor>>& offsets,
+                                                       const std::vector<std::vector<int64_t>>& children) {
+  const size_t L = ids.size();
+  TORCH_CHECK(L > 0 && offsets.size() == L && children.size() == L, "coalesce_lanes: one list of ids / offsets / children per lane");
+  const auto dev = ids[0][0].device();
+  int64_t words = 0;
+  for (size_t l = 0; l < L; ++l) {
+    TORCH_CHECK(!ids[l].empty() && offsets[l].size() == ids[l].size() && children[l].size() == ids[l].size(), "coalesce_lanes: ragged lists");
+    words += 5 * ((int64_t)ids[l].size() + 1);
+  }
+  int64_t* host = nullptr;
+  Tensor host_t;
+  static DescRing rings[64];
+  DescRing* ring = nullptr;
+  int slot = 0;
+  if (dev.is_cuda()) {
+    ring = &rings[dev.index() % 64];
+    slot = ring->head++ % DescRing::kSlots;
+    if (ring->used[slot]) cudaEventSynchronize(ring->ev[slot]);          // issued eight uses ago: long finished
+    if (!ring->buf[slot].defined() || ring->buf[slot].numel() < words) {
+      ring->buf[slot] = torch::empty({std::max<int64_t>(words, 1024)}, torch::TensorOptions().dtype(torch::kInt64).pinned_memory(true));
+      if (!ring->used[slot]) cudaEventCreateWithFlags(&ring->ev[slot], cudaEventDisableTiming);
+    }
+    host = ring->buf[slot].data_ptr<int64_t>();
+  } else {
+    host_t = torch::empty({words}, torch::TensorOptions().dtype(torch::kInt64));
+    host = host_t.data_ptr<int64_t>();
+  }
+  struct Meta { int64_t F, nnz, segs, pos; };
+  std::vector<Meta> meta(L);
+  int64_t pos = 0;
+  for (size_t l = 0; l < L; ++l) {
+    const int64_t F = (int64_t)ids[l].size();
+    int64_t* d = host + pos;                                   // [5][F + 1]: id pointers, nnz prefix, offset pointers, segment prefix, child
+    int64_t nnz = 0, segs = 0;
+    for (int64_t f = 0; f < F; ++f) {
+      const Tensor& v = ids[l][f]; const Tensor& o = offsets[l][f];
+      TORCH_CHECK(v.scalar_type() == torch::kInt64 && v.is_contiguous() && o.scalar_type() == torch::kInt32 && o.is_contiguous() &&
+                  v.device() == dev && o.device() == dev, "coalesce_lanes: ids int64, offsets int32, contiguous, on one device");
+      d[f] = reinterpret_cast<int64_t>(v.data_ptr());
+      d[(F + 1) + f] = nnz;
+      d[2 * (F + 1) + f] = reinterpret_cast<int64_t>(o.data_ptr());
+      d[3 * (F + 1) + f] = segs;
+      d[4 * (F + 1) + f] = children[l][f];
+      nnz += v.numel(); segs += o.numel() - 1;
+    }
+    d[F] = 0; d[(F + 1) + F] = nnz; d[2 * (F + 1) + F] = 0; d[3 * (F + 1) + F] = segs; d[4 * (F + 1) + F] = 0;
+    meta[l] = {F, nnz, segs, pos};
+    pos += 5 * (F + 1);
+  }
+  std::vector<std::tuple<Tensor, Tensor>> out;
+  auto i64 = torch::TensorOptions().dtype(torch::kInt64).device(dev);
+  if (dev.is_cuda()) {
+    c10::cuda::CUDAGuard g(dev);
+    auto st = cur_stream();
+    auto desc = torch::empty({words}, i64);
+    TORCH_CHECK(cudaMemcpyAsync(desc.data_ptr(), host, sizeof(int64_t) * words, cudaMemcpyHostToDevice, st) == cudaSuccess, "descriptor upload failed");
+    cudaEventRecord(ring->ev[slot], st);
+    ring->used[slot] = true;
+    for (size_t l = 0; l < L; ++l) {
+      const Meta& m = meta[l];
+      auto o_ids = torch::empty({m.nnz}, i64);
+      auto o_off = torch::empty({m.segs + 1}, i64.dtype(torch::kInt32));
+      const int64_t* d = desc.data_ptr<int64_t>() + m.pos;
+      rb_encode_merge(d, d + 4 * (m.F + 1), (int)m.F, m.nnz, m.segs, o_ids.data_ptr<int64_t>(), o_off.data_ptr<int32_t>(), st);
+      out.emplace_back(o_ids, o_off);
+    }
+  } else {
+    for (size_t l = 0; l < L; ++l) {
+      const Meta& m = meta[l];
+      auto o_ids = torch::empty({m.nnz}, i64);
+      auto o_off = torch::empty({m.segs + 1}, i64.dtype(torch::kInt32));
+      const int64_t* d = host + m.pos;
+      rbc_encode_merge(d, d + 4 * (m.F + 1), (int)m.F, m.nnz, m.segs, o_ids.data_ptr<int64_t>(), o_off.data_ptr<int32_t>());
+      out.emplace_back(o_ids, o_off);
+    }
+  }
+  return out;
+}
+
 Tensor gather_rows(const Tensor& src, const Tensor& rows, OptT n_dev) {
   TORCH_CHECK(src.dim() == 2 && src.is_contiguous() && rows.scalar_type() == torch::kInt32);
   const int64_t n = rows.numel(); const int64_t D = src.size(1);
@@ -298,6 +390,7 @@ void init_sparse(py::module& m) {
   m.def("dedup_partition", &dedup_partition, py::arg("ids"), py::arg("world"), py::arg("unique_out") = py::none(),
         py::arg("offsets_out") = py::none(), py::arg("status") = py::none(), py::arg("counts_out") = py::none());
   m.def("encode_merge", &encode_merge);
+  m.def("coalesce_lanes", &coalesce_lanes);
   m.def("gather_rows", &gather_rows, py::arg("src"), py::arg("rows"), py::arg("n_dev") = py::none());
   m.def("scatter_rows", &scatter_rows);
   m.def("fill_rows_i64", &fill_rows_i64);

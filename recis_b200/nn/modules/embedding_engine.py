@@ -158,39 +158,13 @@ class EmbeddingEngine(nn.Module):
         return self._coalesce_many([feats], device)[0]
 
     def _coalesce_many(self, parts, device):
-        """``_coalesce`` for several feature lists at once (the lanes of one runtime group): the descriptor tables of all of them
-        travel to the device in ONE asynchronous copy, then one kernel per list prefixes ids and rebases offsets."""
-        blocks, metas = [], []
-        for feats in parts:
-            F = len(feats)
-            nnz_prefix, seg_prefix = [0], [0]
-            for f in feats:
-                nnz_prefix.append(nnz_prefix[-1] + f["ids"].numel())
-                seg_prefix.append(seg_prefix[-1] + f["n_seg"])
-            blocks.append([f["ids"].data_ptr() for f in feats] + [0] + nnz_prefix + [f["offsets"].data_ptr() for f in feats] + [0]
-                          + seg_prefix + [f["child"] for f in feats] + [0])
-            metas.append((F, nnz_prefix[-1], seg_prefix[-1]))
-        flat = [x for b in blocks for x in b]
-        if device.type == "cuda":
-            # descriptor tables: a small ring of pinned staging buffers (no pinned allocation per step), copied asynchronously
-            ring = self._desc_ring.setdefault((len(flat), device), dict(bufs=[torch.empty(len(flat), dtype=torch.int64).pin_memory() for _ in range(4)],
-                                                                        evs=[None] * 4, head=0))
-            k = ring["head"] % 4
-            ring["head"] += 1
-            if ring["evs"][k] is not None:
-                ring["evs"][k].synchronize()          # the copy issued four uses ago has long finished; this never waits in practice
-            ring["bufs"][k].copy_(torch.tensor(flat, dtype=torch.int64))
-            both = ring["bufs"][k].to(device, non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record()
-            ring["evs"][k] = ev
-        else:
-            both = torch.tensor(flat, dtype=torch.int64)
-        out, pos = [], 0
-        for feats, (F, nnz, segs) in zip(parts, metas):
-            blk = both[pos:pos + 5 * (F + 1)].view(5, F + 1)
-            pos += 5 * (F + 1)
-            ids, offsets = native().encode_merge(blk[:4], blk[4, :F], F, nnz, segs, True)
+        """``_coalesce`` for several feature lists at once (the lanes of one runtime group), in one native call: the descriptor
+        tables of all of them travel to the device in ONE asynchronous copy, then one kernel per list prefixes ids and rebases
+        offsets."""
+        merged = native().coalesce_lanes([[f["ids"] for f in feats] for feats in parts], [[f["offsets"] for f in feats] for feats in parts],
+                                         [[int(f["child"]) for f in feats] for feats in parts])
+        out = []
+        for feats, (ids, offsets) in zip(parts, merged):
             weights = None
             if any(f["weight"] is not None for f in feats):
                 ws = [f["weight"] if f["weight"] is not None else torch.ones(f["ids"].numel(), device=device) for f in feats]
