@@ -182,7 +182,7 @@ Tensor lane_lookup(ExLane& l, rbx::EmbeddingStore& store, bool readonly, int64_t
   if (threshold > 1) {
     // count-based admission counts ONE sighting per id and step, whoever asks: dedup the incoming ids before the table sees them
     auto d = rbx::dedup_partition(l.ids_in, 1, c10::nullopt, c10::nullopt, c10::nullopt, c10::nullopt);
-    auto o_rows = store.lookup_or_insert(std::get<0>(d), std::get<3>(d).narrow(0, 1, 1), step, threshold);
+    auto o_rows = store.lookup_or_insert(std::get<0>(d), std::get<3>(d).narrow(0, 1, 1), step, threshold, /*ids_unique=*/true);
     return o_rows.index_select(0, std::get<1>(d).to(torch::kInt64)).contiguous();
   }
   return store.lookup_or_insert(l.ids_in, l.n_in, step, threshold);

@@ -364,7 +364,7 @@ void init_sparse(py::module& m) {
            py::arg("hi"), py::arg("seed"), py::arg("track_last_seen") = true, py::arg("growable") = true,
            py::arg("emb_storage") = py::none(), py::arg("emb_dtype") = py::none())
       .def("lookup_or_insert", &EmbeddingStore::lookup_or_insert, py::arg("ids"), py::arg("n_dev") = py::none(),
-           py::arg("step") = py::none(), py::arg("admit_threshold") = 1)
+           py::arg("step") = py::none(), py::arg("admit_threshold") = 1, py::arg("ids_unique") = false)
       .def("find", &EmbeddingStore::find, py::arg("ids"), py::arg("n_dev") = py::none())
       .def("erase", &EmbeddingStore::erase)
       .def("snapshot", &EmbeddingStore::snapshot, py::arg("expired_only") = false, py::arg("threshold") = 0)
@@ -380,6 +380,7 @@ void init_sparse(py::module& m) {
       .def("free_list", &EmbeddingStore::free_list)
       .def("counters", &EmbeddingStore::counters)
       .def("reserve", &EmbeddingStore::reserve)
+      .def("grows_in_place", &EmbeddingStore::grows_in_place)
       .def("rebuild_index", &EmbeddingStore::rebuild_index)
       .def("clear", &EmbeddingStore::clear)
       .def("size", &EmbeddingStore::size)

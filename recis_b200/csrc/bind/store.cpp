@@ -12,6 +12,8 @@
 #include "../kernels/rb_kernels.h"
 #include "../cpu/rb_cpu.h"
 #include "store.h"
+#include <climits>
+#include <cstdlib>
 #include "bind_shared.h"
 
 namespace rbx {
@@ -31,13 +33,48 @@ EmbeddingStore::EmbeddingStore(int64_t dim, int64_t capacity, torch::Device devi
     TORCH_CHECK(emb_storage->numel() >= cap_rows_ * dim_ && emb_storage->scalar_type() == emb_dtype, "emb_storage too small or of the wrong type");
     emb_ = emb_storage->view({-1}).narrow(0, 0, cap_rows_ * dim_).view({cap_rows_, dim_});
     growable_ = false;  // externally owned (peer-mapped) storage cannot move
-  } else {
-    emb_ = torch::empty({cap_rows_, dim_}, f32.dtype(emb_dtype));     // rows in their storage type; slots (optimizer state) stay fp32
   }
-  if (track_last_seen) last_seen_ = torch::zeros({cap_rows_}, f32.dtype(torch::kInt64));
+  // Growable tables on a GPU keep their per-row arrays in reserved virtual ranges that grow in place (vmm_slab.h): room is
+  // reserved for max_rows_ rows (RECIS_TABLE_MAX_ROWS, default 16 x the initial capacity, at least 64 Mi rows), physical
+  // memory is only mapped for the current capacity. RECIS_TABLE_VMM=0 switches back to allocate + copy.
+  const char* vmm_env = std::getenv("RECIS_TABLE_VMM");
+  use_vmm_ = device_.is_cuda() && growable_ && !(vmm_env && std::string(vmm_env) == "0");
+  const char* max_env = std::getenv("RECIS_TABLE_MAX_ROWS");
+  max_rows_ = max_env ? std::atoll(max_env) : std::max<int64_t>(cap_rows_ * 16, (int64_t)1 << 26);
+  max_rows_ = std::min<int64_t>(std::max<int64_t>(max_rows_, cap_rows_), (int64_t)INT32_MAX - 1024);
+  if (!emb_storage.has_value()) emb_ = alloc_slab("embedding", cap_rows_, dim_, emb_dtype);   // rows in their storage type; slots stay fp32
+  if (track_last_seen) { last_seen_ = alloc_slab("last_seen", cap_rows_, 0, torch::kInt64); last_seen_.zero_(); }
   alloc_index(pow2_at_least(cap_rows_ * 2));
   ctr_ = torch::zeros({RB_CTR_COUNT}, f32.dtype(torch::kInt64));
-  free_list_ = torch::empty({cap_rows_}, f32.dtype(torch::kInt32));
+  free_list_ = alloc_slab("free_list", cap_rows_, 0, torch::kInt32);
+}
+
+// width == 0: a 1-D array [rows]; else [rows, width]
+torch::Tensor EmbeddingStore::alloc_slab(const std::string& key, int64_t rows, int64_t width, torch::ScalarType dtype) {
+  std::vector<int64_t> shape = width > 0 ? std::vector<int64_t>{rows, width} : std::vector<int64_t>{rows};
+  if (use_vmm_) {
+    const size_t row_bytes = (size_t)std::max<int64_t>(width, 1) * c10::elementSize(dtype);
+    auto slab = VmmSlab::create(device_.index(), (size_t)max_rows_ * row_bytes);
+    if (slab && slab->ensure((size_t)rows * row_bytes)) {
+      vmm_[key] = slab;
+      return slab->view(shape, dtype);
+    }
+    use_vmm_ = !vmm_.empty();          // the first failure switches the whole table to plain tensors; later ones fall back singly
+  }
+  return torch::empty(shape, torch::TensorOptions().dtype(dtype).device(device_));
+}
+
+// more rows for a slab that lives in a virtual range: map pages, re-create the view; false when the slab is a plain tensor
+bool EmbeddingStore::grow_slab_in_place(const std::string& key, torch::Tensor& t, int64_t new_rows) {
+  auto it = vmm_.find(key);
+  if (it == vmm_.end()) return false;
+  std::vector<int64_t> shape = t.sizes().vec();
+  int64_t per_row = 1;
+  for (size_t i = 1; i < shape.size(); ++i) per_row *= shape[i];
+  if (!it->second->ensure((size_t)new_rows * per_row * t.element_size())) return false;
+  shape[0] = new_rows;
+  t = it->second->view(shape, t.scalar_type());
+  return true;
 }
 
 void EmbeddingStore::alloc_index(int64_t nslots) {
@@ -59,7 +96,8 @@ RbTable EmbeddingStore::view() const {
 
 void EmbeddingStore::add_slot(const std::string& name, double fill) {
   if (slots_.count(name)) return;
-  slots_[name] = torch::full({cap_rows_, dim_}, fill, emb_.options().dtype(torch::kFloat32));
+  slots_[name] = alloc_slab("slot:" + name, cap_rows_, dim_, torch::kFloat32);
+  slots_[name].fill_(fill);
   slot_fill_[name] = fill;
   slot_order_.push_back(name);
 }
@@ -82,6 +120,7 @@ void EmbeddingStore::refresh_bounds() {
   if (rows_upper_ < 0) rows_upper_ = 0;
   bump_upper_ = c[RB_CTR_BUMP];
   index_upper_ = c[RB_CTR_LIVE] + c[RB_CTR_TOMBSTONES] + c[RB_CTR_PROBATION];
+  tomb_seen_ = c[RB_CTR_TOMBSTONES];
   absorbed_issued_ = issued_total_;
   TORCH_CHECK((c[RB_CTR_STATUS] & 3) == 0, "embedding store reported status ", c[RB_CTR_STATUS],
               " (1 = row arena exhausted, 2 = index full); raise the capacity");
@@ -147,6 +186,7 @@ void EmbeddingStore::absorb_mirror() {
     rows_prev_ = rows_now; index_prev_ = index_now; calls_prev_ = mirror_calls_[slot];
     rows_upper_ = rows_now + pending;
     index_upper_ = index_now + pending;
+    tomb_seen_ = c[RB_CTR_TOMBSTONES];
     absorbed_issued_ = mirror_issued_[slot];
     break;
   }
@@ -171,7 +211,15 @@ void EmbeddingStore::ensure_room(int64_t n_incoming) {
         reserve(nc);
       }
     }
-    if (index_upper_ + n_incoming > (int64_t)(0.65 * keys_.numel())) rebuild_index(pow2_at_least((index_upper_ + n_incoming) * 2));
+    if (index_upper_ + n_incoming > (int64_t)(0.65 * keys_.numel())) {
+      // Erased slots do not survive a rebuild: size the new index for what is live (and on probation) only, never smaller than
+      // the old one. A table whose eviction keeps pace with its inserts is rebuilt at the same size - a clean-up - instead of
+      // doubling every time the tombstones pile up.
+      const int64_t need = pow2_at_least((std::max<int64_t>(index_upper_ - tomb_seen_, 0) + n_incoming) * 2);
+      rebuild_index(std::max<int64_t>(need, keys_.numel()));
+      index_upper_ = std::max<int64_t>(index_upper_ - tomb_seen_, 0);
+      tomb_seen_ = 0;
+    }
   }
   rows_upper_ += n_incoming; index_upper_ += n_incoming;
 }
@@ -195,24 +243,30 @@ void EmbeddingStore::rebuild_index(int64_t nslots) {
 void EmbeddingStore::reserve(int64_t new_cap) {
   if (new_cap <= cap_rows_) return;
   TORCH_CHECK(growable_, "store has fixed storage");
-  auto grow = [&](torch::Tensor& t, double fill, bool do_fill) {
-    std::vector<int64_t> shape = t.sizes().vec();
-    shape[0] = new_cap;
-    auto nt = torch::empty(shape, t.options());
-    nt.narrow(0, 0, cap_rows_).copy_(t);
-    if (do_fill) nt.narrow(0, cap_rows_, new_cap - cap_rows_).fill_(fill);
-    t = nt;
+  // in place where the slab lives in a virtual range (pages are mapped behind the old end, nothing moves), else a new tensor
+  // and a copy of the old rows
+  auto grow = [&](const std::string& key, torch::Tensor& t, double fill, bool do_fill) {
+    if (!grow_slab_in_place(key, t, new_cap)) {
+      TORCH_CHECK(vmm_.find(key) == vmm_.end(), "embedding store '", name_, "': cannot grow to ", new_cap, " rows in place (the reserved range "
+                  "holds ", max_rows_, " rows or the device is out of memory); raise RECIS_TABLE_MAX_ROWS or set RECIS_TABLE_VMM=0");
+      std::vector<int64_t> shape = t.sizes().vec();
+      shape[0] = new_cap;
+      auto nt = torch::empty(shape, t.options());
+      nt.narrow(0, 0, cap_rows_).copy_(t);
+      t = nt;
+    }
+    if (do_fill) t.narrow(0, cap_rows_, new_cap - cap_rows_).fill_(fill);
   };
-  grow(emb_, 0.0, false);
-  for (auto& kv : slots_) grow(kv.second, slot_fill_[kv.first], true);
-  if (last_seen_.defined()) grow(last_seen_, 0.0, true);
-  grow(free_list_, 0.0, false);
+  grow("embedding", emb_, 0.0, false);
+  for (auto& kv : slots_) grow("slot:" + kv.first, kv.second, slot_fill_[kv.first], true);
+  if (last_seen_.defined()) grow("last_seen", last_seen_, 0.0, true);
+  grow("free_list", free_list_, 0.0, false);
   cap_rows_ = new_cap;
   if (keys_.numel() < 2 * new_cap) rebuild_index(pow2_at_least(2 * new_cap));
 }
 
 torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::optional<torch::Tensor> n_dev,
-                                               c10::optional<torch::Tensor> step, int64_t admit_threshold) {
+                                               c10::optional<torch::Tensor> step, int64_t admit_threshold, bool ids_unique) {
   TORCH_CHECK(ids.scalar_type() == torch::kInt64 && ids.is_contiguous() && ids.device() == device_, "ids must be contiguous int64 on the store's device");
   const int64_t n = ids.numel();
   auto i32 = torch::TensorOptions().dtype(torch::kInt32).device(device_);
@@ -254,11 +308,11 @@ torch::Tensor EmbeddingStore::lookup_or_insert(const torch::Tensor& ids, c10::op
     c10::cuda::CUDAGuard g(device_);
     rb_table_lookup_or_insert(view(), ids.data_ptr<int64_t>(), n, nd, slot_scratch.data_ptr<int32_t>(), new_rows.data_ptr<int32_t>(),
                               new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr(), rbx::row_dtype_of(emb_), (int)dim_, init_, ls,
-                              sd, (int)admit_threshold, at::cuda::getCurrentCUDAStream());
+                              sd, (int)admit_threshold, ids_unique ? 1 : 0, at::cuda::getCurrentCUDAStream());
   } else {
     rbc_table_lookup_or_insert(view(), ids.data_ptr<int64_t>(), n, nd, slot_scratch.data_ptr<int32_t>(), new_rows.data_ptr<int32_t>(),
                                new_keys.data_ptr<int64_t>(), rows_out.data_ptr<int32_t>(), emb_.data_ptr(), rbx::row_dtype_of(emb_), (int)dim_, init_, ls,
-                               sd, (int)admit_threshold);
+                               sd, (int)admit_threshold, ids_unique ? 1 : 0);
   }
   post_mirror(n_room, nd);
   return rows_out;

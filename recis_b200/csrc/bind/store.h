@@ -4,6 +4,7 @@
 #include <string>
 #include <vector>
 #include "../kernels/rb_kernels.h"
+#include "vmm_slab.h"
 
 namespace rbx {
 
@@ -15,8 +16,9 @@ class EmbeddingStore {
   ~EmbeddingStore();
   EmbeddingStore(const EmbeddingStore&) = delete;
   EmbeddingStore& operator=(const EmbeddingStore&) = delete;
+  // ids_unique: no id occurs twice in `ids` (new ids may then reuse erased index slots)
   torch::Tensor lookup_or_insert(const torch::Tensor& ids, c10::optional<torch::Tensor> n_dev, c10::optional<torch::Tensor> step,
-                                 int64_t admit_threshold);
+                                 int64_t admit_threshold, bool ids_unique = false);
   torch::Tensor find(const torch::Tensor& ids, c10::optional<torch::Tensor> n_dev);
   torch::Tensor erase(const torch::Tensor& ids);
   std::tuple<torch::Tensor, torch::Tensor> snapshot(bool expired_only, int64_t threshold);
@@ -32,6 +34,7 @@ class EmbeddingStore {
   torch::Tensor free_list() const { return free_list_; }
   std::vector<int64_t> counters() const;
   void reserve(int64_t new_cap);
+  bool grows_in_place() const { return use_vmm_ && !vmm_.empty(); }
   void rebuild_index(int64_t nslots);
   void ensure_room(int64_t n_incoming);
   void clear();
@@ -45,6 +48,12 @@ class EmbeddingStore {
  private:
   void alloc_index(int64_t nslots);
   void refresh_bounds();
+  // one per-row array [rows, ...]: backed by a growable virtual range on CUDA (grows in place), else a plain tensor
+  torch::Tensor alloc_slab(const std::string& key, int64_t rows, int64_t width, torch::ScalarType dtype);
+  bool grow_slab_in_place(const std::string& key, torch::Tensor& t, int64_t new_rows);
+  std::map<std::string, std::shared_ptr<VmmSlab>> vmm_;
+  bool use_vmm_ = false;
+  int64_t max_rows_ = 0;
   int64_t dim_, cap_rows_;
   torch::Device device_;
   bool growable_;
@@ -55,6 +64,7 @@ class EmbeddingStore {
   std::map<std::string, double> slot_fill_;
   std::vector<std::string> slot_order_;
   int64_t rows_upper_ = 0, bump_upper_ = 0, index_upper_ = 0;
+  int64_t tomb_seen_ = 0;           // erased index slots as of the newest counters the host has seen
   // asynchronous counter mirror (pinned host copies of the device counters, see store.cpp)
   static constexpr int kMirror = 8;
   static constexpr int kMirrorStride = RB_CTR_COUNT + 1;

@@ -56,16 +56,20 @@ extern "C" {
 
 void rbc_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* slot_scratch,
                                 int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, void* emb, int emb_dtype, int D, RbInit init,
-                                int64_t* last_seen, const int64_t* step_dev, int admit_threshold) {
+                                int64_t* last_seen, const int64_t* step_dev, int admit_threshold, int ids_unique) {
+  (void)ids_unique;        // inserts run one after the other here: an erased slot on the probe path can always be taken
   const int64_t n = eff_n(n_max, n_dev);
   for (int64_t i = 0; i < n; ++i) {
     const uint64_t key = (uint64_t)ids[i];
     int32_t slot = -1;
     if (key < kErasedKey) {
       uint64_t h = mix64(key) & t.mask;
+      int64_t tomb = -1;
       for (uint64_t probe = 0; probe <= t.mask; ++probe, h = (h + 1) & t.mask) {
         const uint64_t k = t.keys[h];
+        if (k == kErasedKey && tomb < 0) tomb = (int64_t)h;
         if (k == kEmptyKey) {
+          if (tomb >= 0) { h = (uint64_t)tomb; t.ctr[RB_CTR_TOMBSTONES]--; }
           t.keys[h] = key; slot = (int32_t)h;
           if (admit_threshold <= 1) t.rows[h] = cpu_alloc_row(t, key, new_rows, new_keys);
           else { t.rows[h] = -2; t.ctr[RB_CTR_PROBATION]++; }

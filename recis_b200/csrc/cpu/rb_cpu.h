@@ -8,7 +8,7 @@ extern "C" {
 
 void rbc_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* slot_scratch,
                                 int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, void* emb, int emb_dtype, int D, RbInit init,
-                                int64_t* last_seen, const int64_t* step_dev, int admit_threshold);
+                                int64_t* last_seen, const int64_t* step_dev, int admit_threshold, int ids_unique);
 void rbc_table_find(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* rows_out);
 void rbc_table_erase(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* erased_rows);
 void rbc_table_snapshot(RbTable t, int64_t* ids_out, int32_t* rows_out, int64_t out_cap, int64_t* counter,

@@ -43,7 +43,7 @@ __device__ __forceinline__ int32_t alloc_row(const RbTable& t, uint64_t key, int
 __global__ void __launch_bounds__(kThreads)
 table_claim_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, const int32_t* __restrict__ n_dev,
                    int32_t* __restrict__ slot_out, int32_t* __restrict__ new_rows, int64_t* __restrict__ new_keys,
-                   int admit_threshold, int insert) {
+                   int admit_threshold, int insert, int reuse_tombstones) {
   __shared__ int32_t warp_cnt[kThreads / 32];
   __shared__ unsigned long long block_base;
   const int64_t n = n_dev ? min((int64_t)*n_dev, n_max) : n_max;
@@ -58,14 +58,30 @@ table_claim_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, co
       key = (uint64_t)ids[i];
       if (key < kErasedKey) {
         h = mix64(key) & t.mask;
+        int64_t tomb = -1;                      // first erased slot on the probe path (only looked at when reuse is allowed)
         for (uint32_t probe = 0; probe < kMaxProbe; ++probe, h = (h + 1) & t.mask) {
           uint64_t k = *reinterpret_cast<volatile uint64_t*>(&t.keys[h]);
           bool won = false;
+          if (reuse_tombstones && k == kErasedKey && tomb < 0) tomb = (int64_t)h;
           if (k == kEmptyKey) {
             if (!insert) break;
-            k = atomicCAS(reinterpret_cast<unsigned long long*>(&t.keys[h]), (unsigned long long)kEmptyKey, (unsigned long long)key);
-            won = (k == kEmptyKey);
-            if (won) k = key;
+            if (tomb >= 0) {
+              // The key is not in the table (the chain ends here). Take the erased slot met on the way instead of making the
+              // chain longer. Safe only because the ids of this call are distinct: no other thread can be inserting this key
+              // into a different slot at the same time.
+              const uint64_t prev = atomicCAS(reinterpret_cast<unsigned long long*>(&t.keys[tomb]), (unsigned long long)kErasedKey,
+                                              (unsigned long long)key);
+              if (prev == kErasedKey) {
+                won = true; k = key; h = (uint64_t)tomb;
+                atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_TOMBSTONES]), (unsigned long long)(-1ll));
+              }
+              tomb = -1;                        // taken by another key's thread: fall through to the empty slot
+            }
+            if (!won) {
+              k = atomicCAS(reinterpret_cast<unsigned long long*>(&t.keys[h]), (unsigned long long)kEmptyKey, (unsigned long long)key);
+              won = (k == kEmptyKey);
+              if (won) k = key;
+            }
           }
           if (k != key) {
             if (probe + 1 == kMaxProbe || probe >= t.mask) { set_status(&t.ctr[RB_CTR_STATUS], kStatusIndexFull); break; }
@@ -281,11 +297,11 @@ extern "C" {
 
 void rb_table_lookup_or_insert(RbTable t, const int64_t* ids, int64_t n_max, const int32_t* n_dev, int32_t* slot_scratch,
                                int32_t* new_rows, int64_t* new_keys, int32_t* rows_out, void* emb, int emb_dtype, int D, RbInit init,
-                               int64_t* last_seen, const int64_t* step_dev, int admit_threshold, cudaStream_t st) {
+                               int64_t* last_seen, const int64_t* step_dev, int admit_threshold, int ids_unique, cudaStream_t st) {
   if (n_max <= 0) return;
   const int g = grid_for(n_max);
   InitSpec spec{init.kind, init.a, init.b, init.lo, init.hi, init.seed};
-  table_claim_kernel<<<g, kThreads, 0, st>>>(t, ids, n_max, n_dev, slot_scratch, new_rows, new_keys, admit_threshold, 1);
+  table_claim_kernel<<<g, kThreads, 0, st>>>(t, ids, n_max, n_dev, slot_scratch, new_rows, new_keys, admit_threshold, 1, ids_unique);
   rb::note_launch();
   RB_DISPATCH_ROW(emb_dtype, true,
                   (table_init_rows_kernel<T><<<grid_for(n_max * ((D + 3) / 4), 4), kThreads, 0, st>>>(t, new_rows, new_keys,

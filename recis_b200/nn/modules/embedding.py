@@ -145,7 +145,7 @@ class _LookupPoolFn(torch.autograd.Function):
         if W == 1:
             uniq, rev, _counts, offs = C.dedup_partition(ids, 1)
             n_dev = offs[1:2]
-            rows = store.find(uniq, n_dev) if readonly else store.lookup_or_insert(uniq, n_dev, step, threshold)
+            rows = store.find(uniq, n_dev) if readonly else store.lookup_or_insert(uniq, n_dev, step, threshold, True)
             out, gsrc, gscale = pool(store.emb(), rows, rev)
             if train:
                 ctx.saved = dict(rev=rev, gsrc=gsrc, gscale=gscale, rows=rows)
@@ -168,7 +168,7 @@ class _LookupPoolFn(torch.autograd.Function):
         # owner side: different requesters may ask for the same id
         o_uniq, o_rev, _c, o_offs = C.dedup_partition(ids_in, 1)
         o_n = o_offs[1:2]
-        o_rows = store.find(o_uniq, o_n) if readonly else store.lookup_or_insert(o_uniq, o_n, step, threshold)
+        o_rows = store.find(o_uniq, o_n) if readonly else store.lookup_or_insert(o_uniq, o_n, step, threshold, True)
         rows_in = o_rows[o_rev.long()] if n_in else o_rows[:0]
         emb_out = C.gather_rows(store.emb(), rows_in)                 # rows travel in their storage type
         emb_back = torch.empty(n_u, D, dtype=emb_out.dtype, device=ids.device)

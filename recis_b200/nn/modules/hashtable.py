@@ -300,7 +300,7 @@ class _LookupFn(torch.autograd.Function):
         if readonly:
             rows_u = impl.store.find(uniq, n_dev)
         else:
-            rows_u = impl.store.lookup_or_insert(uniq, n_dev, step, admit_threshold)
+            rows_u = impl.store.lookup_or_insert(uniq, n_dev, step, admit_threshold, True)      # distinct ids: erased slots may be reused
         rows = rows_u[rev.long()] if rev.numel() else rows_u[:0]
         ctx.impl, ctx.scale = impl, scale
         ctx.save_for_backward(rows)

@@ -5,9 +5,9 @@
 
 Two implementations:
 * the tensor-core kernels (``csrc/kernels/attention_tcgen05.cu``): no padding, one CTA per (sequence, head, 128-row tile),
-  forward and backward, head width 64; opt-in with ``RECIS_ATTENTION=tcgen05`` (not yet validated on hardware);
+  forward and backward, head width 64: what CUDA training uses;
 * the padded path: scatter into ``[batch, max_len, heads, head_dim]``, ``F.scaled_dot_product_attention`` with a key-padding
-  mask, gather the valid positions back. Differentiable; what training uses; runs on CPU as well.
+  mask, gather the valid positions back. Differentiable; other head widths, CPU tensors, ``RECIS_ATTENTION=padded``.
 """
 from __future__ import annotations
 
@@ -17,6 +17,12 @@ import torch
 import torch.nn.functional as F
 
 from .. import native
+
+
+def _use_kernels() -> bool:
+    """The tensor-core kernels serve CUDA inputs with head width 64 unless ``RECIS_ATTENTION=padded`` asks for the padded
+    library path (kept as the fallback for other head widths, CPU tensors, and as a comparison arm)."""
+    return os.environ.get("RECIS_ATTENTION", "tcgen05") != "padded"
 
 
 def _padded(qkv, seg, pos, lengths, max_len, heads):
@@ -54,7 +60,7 @@ def ragged_self_attention(qkv: torch.Tensor, offsets: torch.Tensor, heads: int, 
     ``seg`` / ``pos`` (sequence index and position of every token) are derived from ``offsets`` when not given."""
     hidden = qkv.shape[1] // 3
     hd = hidden // heads
-    if os.environ.get("RECIS_ATTENTION") == "tcgen05" and qkv.is_cuda and hd == 64:
+    if _use_kernels() and qkv.is_cuda and hd == 64:
         out = _RaggedAttnFn.apply(qkv.to(torch.bfloat16).contiguous(), offsets.to(torch.int32).contiguous(), heads, int(max_len),
                                   float(hd) ** -0.5)
         return out.to(qkv.dtype)

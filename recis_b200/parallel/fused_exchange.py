@@ -327,7 +327,7 @@ class FusedExchange:
             # window goes through the dedup (its size is fixed, the valid count lives on the device); the tail is one more "id"
             # that resolves to no row.
             o_uniq, o_rev, _c, o_offs = C.dedup_partition(lane.ids_in, 1)
-            o_rows = store.lookup_or_insert(o_uniq, o_offs[1:2], step, threshold)
+            o_rows = store.lookup_or_insert(o_uniq, o_offs[1:2], step, threshold, True)
             rows_in = o_rows[o_rev.long()].contiguous()
         else:
             rows_in = store.lookup_or_insert(lane.ids_in, lane.n_in, step, threshold)

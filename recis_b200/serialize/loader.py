@@ -104,7 +104,7 @@ class Loader:
                                 raise KeyError(f"{sdisk} missing from the checkpoint")
                             continue
                         pending[slot] = pool.submit(self.index.read, sdisk, r0, r1)
-                    rows = impl.store.lookup_or_insert(enc.to(dev).contiguous(), None, None, 1)
+                    rows = impl.store.lookup_or_insert(enc.to(dev).contiguous(), None, None, 1, True)
                     if bool((rows < 0).any()):
                         # the table could not take every id of the checkpoint (fixed storage that is too small, or a full index)
                         raise RuntimeError(

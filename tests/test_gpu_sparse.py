@@ -262,3 +262,37 @@ def test_store_grows_from_mirrored_history_with_device_counts():
     assert st.size() == all_ids.numel()
     assert int(st.find(all_ids.to(DEV), None).min()) >= 0
     assert st.capacity() >= all_ids.numel()
+
+
+def test_table_grows_in_place_without_copying():
+    """Row slabs live in reserved virtual ranges: growing maps pages behind the old end. The base address stays, the rows stay,
+    and the time to grow does not depend on how many rows are live (an allocate-and-copy store pays for every live row)."""
+    import time
+    C = recis_b200.native()
+    dim = 32
+
+    def grow_time(fill_rows):
+        store = C.EmbeddingStore(dim, 1_000_000, DEV, 2, 0.0, 0.05, 0.0, 0.0, 7, True, True, None)
+        store.add_slot("state", 0.5)
+        assert store.grows_in_place()
+        ids = torch.arange(fill_rows, dtype=torch.int64, device=DEV) * 7919
+        rows = store.lookup_or_insert(ids, None, None, 1) if fill_rows else None
+        ptr = store.emb().data_ptr()
+        probe = store.emb()[rows[:1000].long()].clone() if fill_rows else None
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        store.reserve(8_000_000)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        assert store.capacity() == 8_000_000 and store.emb().shape[0] == 8_000_000
+        assert store.emb().data_ptr() == ptr                                   # nothing moved
+        if fill_rows:
+            assert torch.equal(store.emb()[rows[:1000].long()], probe)         # old rows intact
+            assert torch.equal(store.find(ids[:1000]), rows[:1000])
+            more = torch.arange(fill_rows, fill_rows + 3_000_000, dtype=torch.int64, device=DEV) * 7919
+            r2 = store.lookup_or_insert(more, None, None, 1)
+            assert int(r2.min()) >= 0 and int(r2.max()) < 8_000_000 and store.size() == fill_rows + 3_000_000
+            assert float(store.slot("state")[r2[-1].long()].min()) == 0.5      # new rows of a slot carry its fill value
+        return dt
+    t_full, t_empty = grow_time(900_000), grow_time(0)
+    assert t_full < 3 * t_empty + 0.02, (t_full, t_empty)

@@ -330,3 +330,27 @@ def test_exchange_host_twins_overflow_is_clamped(world, dim):
     """Every id goes to logical rank 0, whose receive window is too small: boundaries are clamped, guard rows stay untouched."""
     from loopback_case import run_loopback_overflow
     run_loopback_overflow(torch.device("cpu"), world, dim)
+
+
+def test_erased_index_slots_are_reused_by_inserts_of_distinct_ids():
+    """Steady eviction must not fill the index with tombstones: new ids (distinct within a call) take erased slots on their
+    probe path, so churn of a fixed working set leaves the tombstone count near zero instead of growing by the set size per round."""
+    C = recis_b200.native()
+    store = C.EmbeddingStore(8, 4096, "cpu", 0, 0.0, 0.0, 0.0, 0.0, 1, True, True, None)
+    live = torch.arange(0, 3000, dtype=torch.int64)
+    store.lookup_or_insert(live, None, None, 1, True)
+    slots0 = store.keys().numel()
+    for rnd in range(1, 30):
+        store.erase(live[:1500].contiguous())
+        assert store.counters()[5] == 1500 or rnd > 1                      # tombstones right after an eviction
+        fresh = torch.arange(100_000 * rnd, 100_000 * rnd + 1500, dtype=torch.int64)
+        rows = store.lookup_or_insert(fresh, None, None, 1, True)
+        assert int(rows.min()) >= 0
+        assert torch.equal(store.find(fresh), rows)
+        live = torch.cat([fresh, live[1500:]])
+        assert store.size() == 3000
+        assert torch.all(store.find(live) >= 0)
+    c = store.counters()
+    # 29 rounds erased 43,500 ids: without reuse and clean-up the index would hold as many tombstones (and would have doubled
+    # several times); it keeps its size and the erased slots stay a fraction of it
+    assert c[5] < 0.65 * slots0 and store.keys().numel() == slots0, (c[5], store.keys().numel())
