@@ -67,6 +67,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--comm", default=None, choices=["fused", "nccl"])
     ap.add_argument("--capacity", type=int, default=0, help="table rows per rank (0: from the data)")
+    ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16", "fp16"], help="storage (and wire) type of the embedding rows")
     args = ap.parse_args()
     if args.comm:
         os.environ["RECIS_COMM"] = args.comm
@@ -107,9 +108,11 @@ def main():
     xcap = int(uniq_max * 1.15) + 1024
     rows = args.capacity or int(min(xcap * (n_batches + 2), 120e9 / (args.dim * 8)) )
     per_table = max(rows // args.tables, 1)
+    row_dtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[args.dtype]
+    # the exchange windows size themselves from the first batch's measured demand and grow with it
     opts = {f"t{t}": EmbeddingOption(embedding_dim=args.dim, shared_name=f"t{t}", combiner="sum", use_weight=False, device=dev,
-                                     initializer=NormalInitializer(0.0, 0.01), capacity=per_table,
-                                     exchange_capacity=xcap // args.tables + 1) for t in range(args.tables)}
+                                     initializer=NormalInitializer(0.0, 0.01), capacity=per_table, dtype=row_dtype)
+            for t in range(args.tables)}
     engine = EmbeddingEngine(opts, interleave=True)
     opt = SparseAdagrad(filter_out_sparse_param(engine), lr=0.01)
     gout = None
@@ -141,7 +144,7 @@ def main():
         (cube, _names), = engine.packed.values()
         e1.record()
         if gout is None:
-            gout = torch.randn_like(cube) * 1e-3
+            gout = (torch.randn_like(cube.float()) * 1e-3).to(cube.dtype)
         cube.backward(gout)
         opt.step()
         opt.zero_grad()
@@ -165,12 +168,13 @@ def main():
     bwd = max_over_ranks(sum(bwd_ms) / len(bwd_ms))
     # bytes this rank receives in the forward phase (= sends in the backward phase): unique rows owned elsewhere
     remote_rows = uniq_max * (world - 1) / max(world, 1)
-    row_bytes = args.dim * 4
+    row_bytes = args.dim * torch.empty(0, dtype=row_dtype).element_size()      # forward: rows travel in their storage type
     xbytes = remote_rows * row_bytes
+    xbytes_bwd = remote_rows * args.dim * 4                                     # backward: per-unique gradients travel as fp32
     nccl_ms = None
     if world > 1:
         n = int(remote_rows) * args.dim // world * world
-        src = torch.empty(n, dtype=torch.float32, device=dev)
+        src = torch.empty(n, dtype=row_dtype, device=dev)
         dst = torch.empty_like(src)
         for _ in range(3):
             dist.all_to_all_single(dst, src)
@@ -189,9 +193,9 @@ def main():
             "ids_per_rank": nnz_max, "unique_per_rank": uniq_max, "duplicate_ratio": 1.0 - uniq_max / max(nnz_max, 1),
             "forward_ms": fwd, "backward_update_ms": bwd,
             "samples_per_s": args.batch * world / ((fwd + bwd) / 1e3),
-            "exchange_bytes_per_rank_per_phase": xbytes,
+            "row_dtype": args.dtype, "forward_exchange_bytes_per_rank": xbytes, "backward_exchange_bytes_per_rank": xbytes_bwd,
             "forward_exchange_gbs": xbytes / (fwd / 1e3) / 1e9 if world > 1 else None,
-            "backward_exchange_gbs": xbytes / (bwd / 1e3) / 1e9 if world > 1 else None,
+            "backward_exchange_gbs": xbytes_bwd / (bwd / 1e3) / 1e9 if world > 1 else None,
             "bare_nccl_all_to_all_ms": nccl_ms,
             "bare_nccl_all_to_all_gbs": xbytes / (nccl_ms / 1e3) / 1e9 if nccl_ms else None,
             "timing": "CUDA events, max over ranks, inputs device resident, table rows + state far larger than L2",

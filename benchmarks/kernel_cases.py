@@ -119,7 +119,29 @@ def main():
     run("grad_reduce_adam_d128", lambda: C.grad_reduce(gout, gsrc, gscale, csr[0], csr[1], csr[2], 128, rows_id, True, 0, 1e-3, 0.9, 0.999,
                                                        1e-8, 1.0, -1e-3, 1.0, w, m1, m2, 0),
         bytes_=touched * 512 * 6 + nnz * 512)
-    del uemb, w, m1, m2
+    # ---- the same pooling and update on bf16 rows (half the row bytes; state and accumulation stay fp32)
+    uemb_h = uemb.to(torch.bfloat16)
+    run("pool_forward_sum_d128_bf16rows", lambda: C.pool_forward(uemb_h, None, rev, offs, None, 0, 0, 0, True),
+        bytes_=nnz * 256 + n_seg * 512 + nnz * 12)
+    w_h = w.to(torch.bfloat16)
+    run("grad_reduce_adam_d128_bf16rows", lambda: C.grad_reduce(gout, gsrc, gscale, csr[0], csr[1], csr[2], 128, rows_id, True, 0, 1e-3, 0.9,
+                                                                0.999, 1e-8, 1.0, -1e-3, 1.0, w_h, m1, m2, 0),
+        bytes_=touched * (256 * 2 + 512 * 4) + nnz * 512)
+    del uemb, w, m1, m2, uemb_h, w_h
+
+    # ---- sequence truncation of 256 ragged features at once (three launches, one host read): 8192 rows each, keep 20 of ~50
+    from recis_b200.nn.functional import ragged_ops
+    n_feat, rows_c = 256 // small, 8192
+    lens_c = torch.randint(0, 100, (n_feat, rows_c), device=dev)
+    offs_c = torch.zeros(n_feat, rows_c + 1, dtype=torch.int32, device=dev)
+    offs_c[:, 1:] = lens_c.cumsum(1)
+    vals_c = [torch.randint(0, 1 << 40, (int(offs_c[f, -1]),), device=dev) for f in range(n_feat)]
+    offl_c = [offs_c[f].contiguous() for f in range(n_feat)]
+    keep_c = torch.full((n_feat,), 20, dtype=torch.int32)
+    kept = int(lens_c.clamp(max=20).sum())
+    run("fused_cutoff_2d_%dx8192_keep20" % n_feat, lambda: ragged_ops.fused_ragged_cutoff_2D(vals_c, offl_c, keep_c),
+        bytes_=kept * 16 + n_feat * rows_c * 44, flush_l2=True)
+    del vals_c, offl_c, offs_c, lens_c
 
     # ---- feature ops: 32 features x 1 M values each, one fused launch per op type
     vals = [torch.randint(0, 1 << 48, (1_000_000,), device=dev) for _ in range(32)]
@@ -157,6 +179,45 @@ def main():
     gemm_case("gemm_tcgen05_8192x1024x1024", 8192, 1024, 1024)
     gemm_case("gemm_tcgen05_16384x2048x4096", 16384, 2048, 4096)
     gemm_case("gemm_tcgen05_8192x8192x8192", 8192, 8192, 8192)
+
+    # ---- the library GEMM on the same shapes (what the reference's nn.Linear runs): the bar for the kernel above
+    def lib_case(name, M, N, K):
+        a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        b = torch.randn(N, K, device=dev).to(torch.bfloat16)
+        run(name, lambda: torch.matmul(a, b.t()), bytes_=(M * K + N * K + M * N) * 2, flops=2.0 * M * N * K)
+    lib_case("library_matmul_8192x1024x512", 8192, 1024, 512)
+    lib_case("library_matmul_8192x1024x1024", 8192, 1024, 1024)
+    lib_case("library_matmul_8192x8192x8192", 8192, 8192, 8192)
+
+    # ---- ragged self-attention, head width 64: 512 sequences of 50..1000 tokens, 4 heads (config 4's encoder shape), forward and
+    # backward, and the padded library path on the same data
+    import torch.nn.functional as F
+    g = torch.Generator(device="cpu").manual_seed(0)
+    n_seq = 512 // (4 * small - 3)
+    lens_a = torch.randint(50, 1001, (n_seq,), generator=g)
+    offs_a = torch.zeros(n_seq + 1, dtype=torch.int32)
+    offs_a[1:] = lens_a.cumsum(0)
+    T_a, H_a, Lmax = int(offs_a[-1]), 4, int(lens_a.max())
+    qkv = (torch.randn(T_a, 3 * H_a * 64, device=dev) * 0.5).to(torch.bfloat16)
+    offs_ad = offs_a.to(dev)
+    att_flops = 4.0 * 64 * H_a * float((lens_a.double() ** 2).sum())
+    run("ragged_attention_fwd_512seq_h4", lambda: C.ragged_attention_fwd(qkv, offs_ad, H_a, Lmax, 0.125), flops=att_flops,
+        bytes_=T_a * H_a * 64 * 2 * 4)
+    out_a, lse_a = C.ragged_attention_fwd(qkv, offs_ad, H_a, Lmax, 0.125)
+    d_out = torch.randn_like(out_a)
+    run("ragged_attention_bwd_512seq_h4", lambda: C.ragged_attention_bwd(qkv, out_a, d_out, lse_a, offs_ad, H_a, Lmax, 0.125),
+        flops=2.5 * att_flops, bytes_=T_a * H_a * 64 * (2 * 5 + 4 * 3))
+    seg = torch.repeat_interleave(torch.arange(n_seq), lens_a.long()).to(dev)
+    pos = (torch.arange(T_a) - offs_a[:-1].long()[seg.cpu()]).to(dev)
+    key_ok = (torch.arange(Lmax, device=dev)[None, :] < lens_a.to(dev)[:, None])[:, None, None, :]
+
+    def padded_sdpa():
+        padded = qkv.new_zeros(n_seq, Lmax, 3 * H_a * 64)
+        padded[seg, pos] = qkv
+        q, k, v = padded.view(n_seq, Lmax, 3, H_a, 64).permute(2, 0, 3, 1, 4)
+        return F.scaled_dot_product_attention(q, k, v, attn_mask=key_ok).permute(0, 2, 1, 3).reshape(n_seq, Lmax, H_a * 64)[seg, pos]
+    run("padded_library_sdpa_fwd_512seq_h4", padded_sdpa, flops=att_flops)
+    del qkv, out_a, lse_a, d_out
 
     # ---- dense Adam over 24 tensors of 1 M floats
     ws = [torch.randn(1_000_000, device=dev) for _ in range(24)]

@@ -177,6 +177,36 @@ std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_backward(const 
   return {dx, dws, dbs};
 }
 
+// (interest [B, H], lse [B]) of the target attention over packed sequences
+std::tuple<Tensor, Tensor> target_attention_fwd(const Tensor& x, const Tensor& q, const Tensor& offsets, double scale) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kFloat32 && x.is_contiguous() && x.dim() == 2, "x: contiguous fp32 [tokens, hidden] on CUDA");
+  TORCH_CHECK(q.scalar_type() == torch::kFloat32 && q.is_contiguous() && q.dim() == 2 && q.size(1) == x.size(1), "q: contiguous fp32 [batch, hidden]");
+  TORCH_CHECK(offsets.scalar_type() == torch::kInt32 && offsets.is_contiguous() && offsets.numel() == q.size(0) + 1, "offsets: int32 [batch + 1]");
+  c10::cuda::CUDAGuard g(x.device());
+  const int B = (int)q.size(0), H = (int)q.size(1);
+  auto interest = torch::empty({B, H}, x.options());
+  auto lse = torch::empty({B}, x.options());
+  const int rc = rb_target_attention_fwd(x.data_ptr<float>(), q.data_ptr<float>(), offsets.data_ptr<int32_t>(), B, H, (float)scale,
+                                         interest.data_ptr<float>(), lse.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(rc == 0, "target_attention: hidden width must be a multiple of 4 and at most 1024");
+  return {interest, lse};
+}
+
+// (dx [T, H], dq [B, H])
+std::tuple<Tensor, Tensor> target_attention_bwd(const Tensor& x, const Tensor& q, const Tensor& offsets, const Tensor& interest, const Tensor& lse,
+                                                const Tensor& d_interest, double scale) {
+  TORCH_CHECK(d_interest.scalar_type() == torch::kFloat32 && d_interest.is_contiguous() && d_interest.sizes() == interest.sizes());
+  c10::cuda::CUDAGuard g(x.device());
+  const int B = (int)q.size(0), H = (int)q.size(1);
+  auto dx = torch::zeros_like(x);          // tokens outside every sequence (none in a well-formed batch) keep a zero gradient
+  auto dq = torch::empty_like(q);
+  const int rc = rb_target_attention_bwd(x.data_ptr<float>(), q.data_ptr<float>(), offsets.data_ptr<int32_t>(), interest.data_ptr<float>(),
+                                         lse.data_ptr<float>(), d_interest.data_ptr<float>(), B, H, (float)scale, dx.data_ptr<float>(),
+                                         dq.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(rc == 0, "target_attention backward: hidden width must be a multiple of 4 and at most 1024");
+  return {dx, dq};
+}
+
 int64_t dense_status(const std::string& device) { return status_word(torch::Device(device)).item<int64_t>(); }
 
 }  // namespace
@@ -185,6 +215,8 @@ void init_dense(py::module& m) {
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("bias") = py::none(), py::arg("relu") = false,
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none());
   m.def("dense_status", &dense_status);
+  m.def("target_attention_fwd", &target_attention_fwd);
+  m.def("target_attention_bwd", &target_attention_bwd);
   m.def("mlp_forward", &mlp_forward);
   m.def("mlp_backward", &mlp_backward);
   m.def("dot_interaction_fwd", &dot_interaction_fwd);

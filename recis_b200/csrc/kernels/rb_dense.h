@@ -65,6 +65,14 @@ typedef struct RbDenseAdamArgs {
 } RbDenseAdamArgs;
 void rb_dense_adam(const RbDenseAdamArgs* args, float beta1, float beta2, float eps, float decay, float step_size, float inv_sqrt_bc2,
                    float l2, cudaStream_t st);
+// ---- seq_ops.cu: target attention over packed sequences (one query per sequence), forward and backward, one pass each.
+// x: fp32 [T, H] packed tokens, q: fp32 [B, H], offsets: int32 [B + 1]; interest: fp32 [B, H]; lse: fp32 [B] (log-sum-exp of the
+// scaled scores, kept for the backward pass). Return 1 when H is outside the kernels' range (multiple of 4, at most 1024).
+int rb_target_attention_fwd(const float* x, const float* q, const int32_t* offsets, int B, int H, float scale, float* interest,
+                            float* lse, cudaStream_t st);
+int rb_target_attention_bwd(const float* x, const float* q, const int32_t* offsets, const float* interest, const float* lse,
+                            const float* d_interest, int B, int H, float scale, float* dx, float* dq, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,12 +8,12 @@ Layout decisions:
 * Sequences stay PACKED (``[total_tokens, hidden]``) everywhere except inside the attention core: the per-token embedding
   lookup feeds the id values as a flat batch of one-id bags, so the exchange moves unique ids only and nothing is padded;
   all projections and the FFN run on the packed tokens through the tensor-core GEMM (``ops.dense.Linear``).
-* Target attention is computed on the packed layout with segment reductions (one query per sequence).
-* The encoder's attention core is ``ops.attention.ragged_self_attention``: for training it scatters the packed Q/K/V into
-  ``[batch, max_len, heads, head_dim]`` and calls ``F.scaled_dot_product_attention`` with a key-padding mask, then gathers the
-  valid positions back (the reference's sequence example does the same on fully padded tensors under bf16 autocast,
-  ``examples/seq2seq/transformer.py:36-38`` and ``seq2seq_model.py:87-91``); without gradients it can run the ragged
-  tensor-core kernel instead (opt-in).
+* Target attention (one query per sequence) is ``ops.attention.target_attention`` on the packed layout: one kernel per
+  direction on CUDA, segment reductions with tensor ops elsewhere.
+* The encoder's attention core is ``ops.attention.ragged_self_attention``: on CUDA the ragged tensor-core kernels (no padding,
+  forward and backward); elsewhere it scatters the packed Q/K/V into ``[batch, max_len, heads, head_dim]`` and calls
+  ``F.scaled_dot_product_attention`` with a key-padding mask (the reference's sequence example does that on fully padded
+  tensors under bf16 autocast, ``examples/seq2seq/transformer.py:36-38`` and ``seq2seq_model.py:87-91``).
 """
 from __future__ import annotations
 
@@ -25,7 +25,7 @@ from torch import nn
 from ..nn import EmbeddingEngine, EmbeddingOption
 from ..nn.functional.ragged_ops import gen_segment_indices
 from ..nn.initializers import NormalInitializer
-from ..ops.attention import ragged_self_attention
+from ..ops.attention import ragged_self_attention, target_attention
 from ..ops.dense import MLP, Linear
 from ..ragged import RaggedTensor
 
@@ -112,9 +112,7 @@ class SequenceModel(nn.Module):
         pos = torch.arange(T, device=dev) - offsets[:-1].long()[seg]
         max_len = min(self.max_len, int(batch.get("max_len", self.max_len)))
         # ---- target attention: one query per sequence, softmax over its tokens
-        scores = (x * q[seg]).sum(-1) * (self.hidden ** -0.5)
-        att = segment_softmax(scores, seg, B)
-        interest = torch.zeros(B, self.hidden, dtype=x.dtype, device=dev).index_add_(0, seg, x * att[:, None])
+        interest = target_attention(x, q, offsets, seg, self.hidden ** -0.5)
         # ---- encoder over the sequence
         h = x
         for layer in self.layers:

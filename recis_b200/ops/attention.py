@@ -70,3 +70,39 @@ def ragged_self_attention(qkv: torch.Tensor, offsets: torch.Tensor, heads: int, 
     if pos is None:
         pos = torch.arange(qkv.shape[0], device=qkv.device) - offsets[:-1].long()[seg]
     return _padded(qkv, seg, pos, lengths, int(max_len), heads)
+
+
+class _TargetAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, q, offsets, scale):
+        interest, lse = native().target_attention_fwd(x, q, offsets, scale)
+        ctx.save_for_backward(x, q, offsets, interest, lse)
+        ctx.scale = scale
+        return interest
+
+    @staticmethod
+    def backward(ctx, d_interest):
+        x, q, offsets, interest, lse = ctx.saved_tensors
+        dx, dq = native().target_attention_bwd(x, q, offsets, interest, lse, d_interest.contiguous().float(), ctx.scale)
+        return dx, dq, None, None
+
+
+def target_attention(x: torch.Tensor, q: torch.Tensor, offsets: torch.Tensor, seg: torch.Tensor = None, scale: float = None) -> torch.Tensor:
+    """One query per sequence over packed tokens: ``interest[b] = sum_t softmax_t(scale * <x_t, q_b>) x_t`` for the tokens ``t``
+    of sequence ``b``. ``x``: ``[T, hidden]``, ``q``: ``[B, hidden]``, ``offsets``: ``[B + 1]``. On CUDA (fp32, hidden a multiple
+    of 4 up to 1024) the forward and the backward are one kernel each (``csrc/kernels/seq_ops.cu``); otherwise, and as the
+    oracle in the tests, segment reductions with tensor ops."""
+    hidden = x.shape[1]
+    scale = float(hidden) ** -0.5 if scale is None else float(scale)
+    if x.is_cuda and hidden % 4 == 0 and hidden <= 1024 and os.environ.get("RECIS_TARGET_ATTENTION", "kernel") != "eager":
+        return _TargetAttnFn.apply(x.float().contiguous(), q.float().contiguous(), offsets.to(torch.int32).contiguous(), scale)
+    B = q.shape[0]
+    if seg is None:
+        lengths = (offsets[1:] - offsets[:-1]).long()
+        seg = torch.repeat_interleave(torch.arange(B, device=x.device), lengths)
+    scores = (x * q[seg]).sum(-1) * scale
+    m = torch.full((B,), -float("inf"), dtype=scores.dtype, device=x.device).scatter_reduce(0, seg, scores, "amax")
+    e = torch.exp(scores - m[seg])
+    z = torch.zeros(B, dtype=scores.dtype, device=x.device).index_add_(0, seg, e)
+    att = e / z[seg].clamp_min(1e-30)
+    return torch.zeros(B, hidden, dtype=x.dtype, device=x.device).index_add_(0, seg, x * att[:, None])

@@ -95,3 +95,30 @@ def test_module_path_uses_the_kernels_and_matches_the_padded_path():
             os.environ["RECIS_ATTENTION"] = prev
     assert (out.float() - ref).norm() / ref.norm() < 1e-2
     assert (a.grad.float() - b.grad).norm() / b.grad.norm() < 2e-2
+
+
+@pytest.mark.parametrize("lens,hidden", [([5, 1, 300], 256), ([0, 17, 1000, 0, 64], 64), ([33] * 40, 128), ([700, 2], 1024), ([9], 8)])
+def test_target_attention_kernels_match_tensor_ops(lens, hidden):
+    """One query per sequence over packed tokens, forward and backward, against the segment-reduction formulation in fp32."""
+    import os
+    from recis_b200.ops import attention
+    g = torch.Generator().manual_seed(len(lens) + hidden)
+    T, B = sum(lens), len(lens)
+    offs = torch.zeros(B + 1, dtype=torch.int32)
+    offs[1:] = torch.tensor(lens).cumsum(0)
+    x = torch.randn(T, hidden, generator=g)
+    q = torch.randn(B, hidden, generator=g)
+    go = torch.randn(B, hidden, generator=g)
+    a, b = x.to(DEV).requires_grad_(True), q.to(DEV).requires_grad_(True)
+    out = attention.target_attention(a, b, offs.to(DEV))
+    out.backward(go.to(DEV))
+    os.environ["RECIS_TARGET_ATTENTION"] = "eager"
+    try:
+        c, d = x.clone().requires_grad_(True), q.clone().requires_grad_(True)
+        ref = attention.target_attention(c, d, offs)
+        ref.backward(go)
+    finally:
+        os.environ.pop("RECIS_TARGET_ATTENTION", None)
+    assert torch.allclose(out.cpu(), ref, atol=2e-5, rtol=1e-4), float((out.cpu() - ref).abs().max())
+    assert torch.allclose(a.grad.cpu(), c.grad, atol=5e-5, rtol=1e-3), float((a.grad.cpu() - c.grad).abs().max())
+    assert torch.allclose(b.grad.cpu(), d.grad, atol=5e-5, rtol=1e-3), float((b.grad.cpu() - d.grad).abs().max())

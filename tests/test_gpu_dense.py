@@ -28,13 +28,18 @@ def test_dot_interaction_fwd_bwd(B, F, Dm):
     out = D.dot_interaction(xg, cg)
     n = ref.shape[1]
     assert out.shape[1] % 8 == 0 and out.shape[1] >= n
-    assert torch.allclose(out[:, :n].float().cpu(), ref, atol=0.15, rtol=2e-2)
-    assert float(out[:, n:].abs().sum()) == 0
+    got = out[:, :n].detach().float().cpu()
+    assert torch.allclose(got, ref.detach(), atol=0.15, rtol=2e-2)
+    # relative norm: a dropped 16-column k-block of the D = 128 reduction would cost about 1/8 of every entry's terms
+    assert float((got - ref.detach()).norm() / ref.detach().norm()) < 1e-2
+    assert float(out[:, n:].detach().abs().sum()) == 0
     go = torch.randn(B, out.shape[1]).to(torch.bfloat16)
     out.backward(go.to(DEV))
     ref.backward(go[:, :n].float())
     assert torch.allclose(cg.grad.cpu(), cr.grad, atol=0.1, rtol=2e-2)
     assert torch.allclose(xg.grad.float().cpu(), xr.grad, atol=0.3, rtol=3e-2)
+    assert float((cg.grad.cpu() - cr.grad).norm() / cr.grad.norm()) < 1e-2
+    assert float((xg.grad.float().cpu() - xr.grad).norm() / xr.grad.norm()) < 1.5e-2
 
 
 def test_fm_interaction():
