@@ -35,7 +35,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--once", action="store_true")
-    ap.add_argument("--only", default=None)
+    ap.add_argument("--only", default=None, help="comma-separated case names or name prefixes")
     args = ap.parse_args()
     if args.once:
         args.iters, args.warmup = 1, 0
@@ -52,7 +52,7 @@ def main():
     results = []
 
     def run(name, fn, bytes_=0.0, flops=0.0, flush_l2=False):
-        if args.only and args.only != name:
+        if args.only and not any(name == o or name.startswith(o) for o in args.only.split(",")):
             return
         for _ in range(args.warmup):
             fn()

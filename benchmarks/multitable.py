@@ -170,7 +170,8 @@ def main():
         b, n = make_batch(plan, args.batch, args.zipf, dev, 7919 * rank + i)
         batches.append(b)
         nnz = max(nnz, n)
-    rows = args.rows or int(nnz * min(n_batches, 6) * 0.6) + 4096
+    # admission keeps most ids of a step out of the tables, and the tables grow in place when they fill up: start small
+    rows = args.rows or nnz // 4 + 4096
     torch.manual_seed(99)
     model = build_model(plan, dev, rows, int(nnz * 1.05) + 4096, args.admit, args.ttl)
     sparse_opt = SparseAdam(filter_out_sparse_param(model), lr=1e-3)

@@ -53,6 +53,7 @@ def main():
     ap.add_argument("--hidden", type=int, default=256)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--profile", type=int, default=0, help="after the timed steps, list the N kernels with the most device time in one more step")
     ap.add_argument("--comm", default=None, choices=["fused", "nccl"])
     ap.add_argument("--stage-exchange", action="store_true",
                     help="fused exchange: issue every table group's id phase and owner side before the first wait (RECIS_STAGE_EXCHANGE=1)")
@@ -139,12 +140,27 @@ def main():
         _ex = getattr(_tb, "fused", None)
         if _ex is not None:
             _ex.check()          # a timed-out wait or an overflowing window invalidates the measurement: fail instead of reporting it
+    top = None
+    if args.profile and on_gpu:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step(batches[-1])
+            torch.cuda.synchronize()
+        rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+        total = sum(e.device_time_total for e in rows)
+        top = {"kernel_ms_total": total / 1e3,
+               "kernels": [{"name": e.key[:90], "ms": round(e.device_time_total / 1e3, 3), "launches": e.count} for e in rows[:args.profile]]}
+    from recis_b200.ops import attention as _att
+    core = ("ragged tcgen05 attention kernels (no padding), one-kernel target attention" if on_gpu and _att._use_kernels()
+            else "F.scaled_dot_product_attention on the padded view")
     if rank == 0:
+        if top is not None:
+            print(json.dumps({"profile": top}), flush=True)
         print(json.dumps({
             "bench": "sequence_model", "n_gpus": world, "per_rank_batch": args.batch, "global_batch": args.batch * world,
             "tokens_per_rank_per_step": tokens, "hidden": args.hidden, "ms_per_step": ms,
             "samples_per_s": args.batch * world / (ms / 1e3), "tokens_per_s": tokens * world / (ms / 1e3), "last_loss": float(loss),
-            "attention_core": "F.scaled_dot_product_attention on the padded view; projections and FFN on the tcgen05 GEMM",
+            "attention_core": core + "; projections and FFN on the tcgen05 GEMM",
             "timing": "CUDA events, max over ranks" if on_gpu else "host clock (CPU run)",
         }), flush=True)
     if world > 1:

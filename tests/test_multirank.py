@@ -714,6 +714,79 @@ def test_p2p_dense_allreduce():
     _check_allreduce(results, world)
 
 
+def _bucketed_backward_fn(rank, world, device_kind, comm):
+    """A four-layer tower whose gradients are averaged bucket by bucket from backward's hooks; one parameter takes no part in
+    the graph, and the second step is an accumulation of two micro-batches with the division folded into the average."""
+    import torch
+    from recis_b200.parallel.dense_reducer import DenseGradReducer
+    dev = torch.device("cuda", rank) if device_kind == "cuda" else torch.device("cpu")
+    torch.manual_seed(1)
+    layers = torch.nn.ModuleList([torch.nn.Linear(24, 40), torch.nn.Linear(40, 40), torch.nn.Linear(40, 33), torch.nn.Linear(33, 1)]).to(dev)
+    unused = torch.nn.Parameter(torch.ones(7, device=dev))
+    params = list(layers.parameters()) + [unused]
+    red = DenseGradReducer(params, world, bucket_mb=40 * 40 * 4 / (1 << 20))
+    assert red.p2p == (comm == "fused") and len(red.buckets) >= 3
+
+    def loss_of(step, r, micro):
+        g = torch.Generator().manual_seed(1000 * step + 10 * r + micro)
+        x = torch.randn(16, 24, generator=g).to(dev)
+        for l in layers[:-1]:
+            x = torch.relu(l(x))
+        return layers[-1](x).square().mean()
+
+    out = []
+    for step, accum in ((0, 1), (1, 1), (2, 2)):
+        red.flat.zero_()
+        red.grad_scale = 1.0 / accum
+        for micro in range(accum):
+            red.armed = micro == accum - 1
+            loss_of(step, rank, micro).backward()
+        started_in_backward = sum(b.launched for b in red.buckets)
+        red.all_reduce_async()
+        red.wait()
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        got = [p.grad.detach().cpu().clone() for p in params]
+        # the oracle: every rank's gradients computed here, without the reducer
+        red.armed = False
+        for p in params:
+            p.grad = None
+        want = [torch.zeros(p.shape) for p in params]
+        for r in range(world):
+            for micro in range(accum):
+                loss_of(step, r, micro).backward()
+        for k, p in enumerate(params):
+            if p.grad is not None:
+                want[k] = p.grad.detach().cpu() / (world * accum)
+        out.append((got, want, started_in_backward))
+        # back to views of the flat buffer for the next step
+        for p, start in red._placement:
+            p.grad = red.flat[start:start + p.numel()].view_as(p)
+    red.check()
+    return out
+
+
+@pytest.mark.parametrize("comm", ["fused", "nccl"])
+def test_dense_buckets_start_from_backward_hooks_on_cpu_ranks(comm):
+    results = run_ranks(_bucketed_backward_fn, 2, "gloo", args=("cpu", comm), env={"RECIS_COMM": comm, "RECIS_WAIT_TIMEOUT_S": "60"})
+    for res in results:
+        for step, (got, want, started) in enumerate(res):
+            assert started == 0 if step == 0 else started >= 3      # the first step learns which parameters get gradients
+            for a, b in zip(got, want):
+                assert torch.allclose(a, b, atol=1e-6), float((a - b).abs().max())
+
+
+@pytest.mark.gpu
+def test_gpu_dense_buckets_start_from_backward_hooks():
+    _need_gpus(2)
+    results = run_ranks(_bucketed_backward_fn, 2, "nccl", args=("cuda", "fused"), env={"RECIS_COMM": "fused", "NCCL_NVLS_ENABLE": "0"})
+    for res in results:
+        for step, (got, want, started) in enumerate(res):
+            assert started == 0 if step == 0 else started >= 3
+            for a, b in zip(got, want):
+                assert torch.allclose(a, b, atol=1e-5), float((a - b).abs().max())
+
+
 def _staged_fn(rank, world):
     """Two tables looked up through the three-stage interface with both id exchanges started before either is finished."""
     import torch
