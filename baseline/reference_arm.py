@@ -129,6 +129,8 @@ class ReferenceArm:
         for b in host_batches:
             yield self.to_device(b, dev)
 
+    LOSS_READ = "every step: float(loss) at the end of the step"
+
     def step(self, st, batch):
         embs = st["sparse"]({f: batch[f] for f in st["fields"]})
         logit = st["dense"](batch["dense"], [embs[f] for f in st["fields"]])

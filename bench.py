@@ -196,10 +196,11 @@ def run(args, arm):
         e0.record()
         feeder = arm.feeder(host[first:first + count], dev)       # created inside the region: all `count` copies are timed
         for batch in feeder:
-            loss = arm.step(state, batch)
+            loss = arm.step_e2e(state, batch) if hasattr(arm, "step_e2e") else arm.step(state, batch)
             if hasattr(feeder, "prefetch"):
                 feeder.prefetch()            # next batches' copies are issued while the GPU works on this step
-            losses.append(float(loss))       # device -> host read of the step's result
+            # device -> host read of the step's result, every step
+            losses.append(arm.read_loss(state, loss) if hasattr(arm, "read_loss") else float(loss))
         e1.record()
         torch.cuda.synchronize()
         ms_ = e0.elapsed_time(e1)
@@ -269,6 +270,7 @@ def run(args, arm):
                         "new_rows_per_step": new_a, "reported": ia},
             "e2e": {"value": value_e2e, "unit": "samples/s", "ms_per_step": ms_e2e / K, "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": 4, "last_loss": losses[-1] if losses else None,
+                    "loss_read": arm.LOSS_READ,
                     "regions": {"ms_per_step": per_step(ms_e), "spread": round((max(ms_e) - min(ms_e)) / ms_e2e, 4),
                                 "new_rows_per_step": new_e, "reported": ie}},
             "gpu_launches": launches[ia],
@@ -303,7 +305,8 @@ class OursArm:
         from recis_b200.optim import DenseAdam
         dense_opt = DenseAdam(dense_params, lr=1e-3)
         reducer = DenseGradReducer(dense_params, world) if world > 1 else None
-        return dict(model=model, sparse_opt=sparse_opt, dense_opt=dense_opt, reducer=reducer)
+        from recis_b200.utils import AsyncScalarReader
+        return dict(model=model, sparse_opt=sparse_opt, dense_opt=dense_opt, reducer=reducer, loss_reader=AsyncScalarReader(dev))
 
     def wrap_host(self, arrays, batch):
         """The batch as the framework's packed host batch: every tensor of it inside one pinned buffer (``recis_b200.io.PackedBatch``)."""
@@ -329,8 +332,20 @@ class OursArm:
         from recis_b200.io import DevicePrefetcher
         return DevicePrefetcher(host_batches, dev, depth=2)
 
-    def step(self, st, batch):
+    LOSS_READ = ("every step: the loss is copied to pinned host memory on a side stream as soon as the forward pass has produced "
+                 "it, and the host reads that step's value at the end of the step")
+
+    def step_e2e(self, st, batch):
+        """The same step; the loss starts its way to the host as soon as the forward pass has produced it."""
+        return self.step(st, batch, post_loss=True)
+
+    def read_loss(self, st, ticket):
+        return st["loss_reader"].get(ticket)
+
+    def step(self, st, batch, post_loss=False):
         loss, _ = st["model"](batch)
+        if post_loss:
+            ticket = st["loss_reader"].post(loss)
         st["dense_opt"].zero_grad(set_to_none=False) if st["reducer"] is not None else st["dense_opt"].zero_grad()
         st["sparse_opt"].zero_grad()
         loss.backward()
@@ -340,7 +355,7 @@ class OursArm:
         if st["reducer"] is not None:
             st["reducer"].wait()
         st["dense_opt"].step()
-        return loss.detach()
+        return ticket if post_loss else loss.detach()
 
     def launches(self):
         import recis_b200

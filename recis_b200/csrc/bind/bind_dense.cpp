@@ -115,8 +115,10 @@ std::tuple<Tensor, Tensor> relu_bwd_bias(const Tensor& y, const Tensor& dout, bo
   const int M = (int)dout.size(0), N = (int)dout.size(1);
   Tensor dy = relu ? torch::empty_like(dout) : dout;
   auto db = torch::zeros({N}, dout.options().dtype(torch::kFloat32));
-  rb_relu_bwd_bias(relu ? y.data_ptr() : nullptr, dout.data_ptr(), M, N, relu, relu ? dy.data_ptr() : nullptr, db.data_ptr<float>(),
-                   at::cuda::getCurrentCUDAStream());
+  if (rb_relu_bwd_bias_vec(relu ? y.data_ptr() : nullptr, dout.data_ptr(), M, N, relu, relu ? dy.data_ptr() : nullptr, db.data_ptr<float>(),
+                           at::cuda::getCurrentCUDAStream()) == 1)
+    rb_relu_bwd_bias(relu ? y.data_ptr() : nullptr, dout.data_ptr(), M, N, relu, relu ? dy.data_ptr() : nullptr, db.data_ptr<float>(),
+                     at::cuda::getCurrentCUDAStream());
   return {dy, db};
 }
 
@@ -177,6 +179,60 @@ std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_backward(const 
   return {dx, dws, dbs};
 }
 
+// out (fp32) = a b^T + bias + residual: a projection added onto the fp32 residual stream in the GEMM's epilogue
+Tensor gemm_bf16_residual(const Tensor& a, const Tensor& b, OptT bias, const Tensor& residual) {
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16 && a.dim() == 2 && b.dim() == 2 &&
+              a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1), "bf16 [M, K] and [N, K] operands expected");
+  const int64_t MM = a.size(0), NN = b.size(0), KK = a.size(1);
+  TORCH_CHECK(residual.scalar_type() == torch::kFloat32 && residual.is_contiguous() && residual.dim() == 2 && residual.size(0) == MM &&
+              residual.size(1) == NN, "residual: contiguous fp32 [M, N]");
+  c10::cuda::CUDAGuard g(a.device());
+  auto out = torch::empty({MM, NN}, a.options().dtype(torch::kFloat32));
+  const float* bp = nullptr;
+  Tensor bias_f;
+  if (bias.has_value() && bias->defined()) {
+    bias_f = bias->scalar_type() == torch::kFloat32 ? bias->contiguous() : bias->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(bias_f.numel() == NN);
+    bp = bias_f.data_ptr<float>();
+  }
+  Tensor& st = status_word(a.device());
+  const int rc = rb_gemm_bf16(a.data_ptr(), a.stride(0), 0, b.data_ptr(), b.stride(0), 0, out.data_ptr(), out.stride(0), 1, bp,
+                              residual.data_ptr<float>(), (int)MM, (int)NN, (int)KK, 0, 1, st.data_ptr<int64_t>(),
+                              at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(rc == 0, "rb_gemm_bf16 failed with code ", rc);
+  return out;
+}
+
+// (y [rows, H] bf16 or fp32, stats [rows, 2] = mean and rstd)
+std::tuple<Tensor, Tensor> layer_norm_fwd(const Tensor& x, const Tensor& gamma, const Tensor& beta, double eps, bool out_bf16) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kFloat32 && x.is_contiguous() && x.dim() == 2, "x: contiguous fp32 [rows, hidden] on CUDA");
+  const int64_t rows = x.size(0), H = x.size(1);
+  TORCH_CHECK(gamma.scalar_type() == torch::kFloat32 && beta.scalar_type() == torch::kFloat32 && gamma.is_contiguous() && beta.is_contiguous() &&
+              gamma.numel() == H && beta.numel() == H, "gamma, beta: contiguous fp32 [hidden]");
+  c10::cuda::CUDAGuard g(x.device());
+  auto y = torch::empty({rows, H}, x.options().dtype(out_bf16 ? torch::kBFloat16 : torch::kFloat32));
+  auto stats = torch::empty({rows, 2}, x.options());
+  const int rc = rb_layer_norm_fwd(x.data_ptr<float>(), gamma.data_ptr<float>(), beta.data_ptr<float>(), rows, (int)H, (float)eps, y.data_ptr(),
+                                   out_bf16, stats.data_ptr<float>(), at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(rc == 0, "layer_norm: hidden width must be a multiple of 4 and at most 1024");
+  return {y, stats};
+}
+
+// (dx fp32 [rows, H], dgamma [H], dbeta [H])
+std::tuple<Tensor, Tensor, Tensor> layer_norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& stats, const Tensor& gamma) {
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && dy.sizes() == x.sizes() &&
+              (dy.scalar_type() == torch::kFloat32 || dy.scalar_type() == torch::kBFloat16), "dy: contiguous fp32 or bf16, shaped like x");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t rows = x.size(0), H = x.size(1);
+  auto dx = torch::empty_like(x);
+  auto dgb = torch::zeros({2, H}, x.options());
+  const int rc = rb_layer_norm_bwd(dy.data_ptr(), dy.scalar_type() == torch::kBFloat16, x.data_ptr<float>(), stats.data_ptr<float>(),
+                                   gamma.data_ptr<float>(), rows, (int)H, dx.data_ptr<float>(), dgb.data_ptr<float>(),
+                                   dgb.data_ptr<float>() + H, at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(rc == 0, "layer_norm backward: hidden width must be a multiple of 4 and at most 1024");
+  return {dx, dgb.select(0, 0), dgb.select(0, 1)};
+}
+
 // (interest [B, H], lse [B]) of the target attention over packed sequences
 std::tuple<Tensor, Tensor> target_attention_fwd(const Tensor& x, const Tensor& q, const Tensor& offsets, double scale) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kFloat32 && x.is_contiguous() && x.dim() == 2, "x: contiguous fp32 [tokens, hidden] on CUDA");
@@ -215,6 +271,9 @@ void init_dense(py::module& m) {
   m.def("gemm_bf16", &gemm_bf16, py::arg("a"), py::arg("b"), py::arg("bias") = py::none(), py::arg("relu") = false,
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none());
   m.def("dense_status", &dense_status);
+  m.def("gemm_bf16_residual", &gemm_bf16_residual);
+  m.def("layer_norm_fwd", &layer_norm_fwd);
+  m.def("layer_norm_bwd", &layer_norm_bwd);
   m.def("target_attention_fwd", &target_attention_fwd);
   m.def("target_attention_bwd", &target_attention_bwd);
   m.def("mlp_forward", &mlp_forward);

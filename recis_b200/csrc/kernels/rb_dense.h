@@ -73,6 +73,17 @@ int rb_target_attention_fwd(const float* x, const float* q, const int32_t* offse
 int rb_target_attention_bwd(const float* x, const float* q, const int32_t* offsets, const float* interest, const float* lse,
                             const float* d_interest, int B, int H, float scale, float* dx, float* dq, cudaStream_t st);
 
+// ---- norm_ops.cu: LayerNorm over the last dimension of fp32 [rows, H] (H a multiple of 4, at most 1024; otherwise 1 is returned).
+// forward writes y as bf16 (y_bf16 != 0) or fp32 and stats[rows][2] = (mean, rstd); backward takes dy as bf16 or fp32 and ADDS the
+// weight gradients to dgamma / dbeta (zero them first).
+int rb_layer_norm_fwd(const float* x, const float* gamma, const float* beta, int64_t rows, int H, float eps, void* y, int y_bf16,
+                      float* stats, cudaStream_t st);
+int rb_layer_norm_bwd(const void* dy, int dy_bf16, const float* x, const float* stats, const float* gamma, int64_t rows, int H, float* dx,
+                      float* dgamma, float* dbeta, cudaStream_t st);
+// ReLU backward + bias gradient with 16-byte accesses; returns 1 when the width does not suit it (not a multiple of 8, or neither
+// a power of two below 256 nor a multiple of 256), and the caller falls back to rb_relu_bwd_bias.
+int rb_relu_bwd_bias_vec(const void* y, const void* dout, int64_t M, int N, int relu, void* dy, float* db, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -26,7 +26,7 @@ from ..nn import EmbeddingEngine, EmbeddingOption
 from ..nn.functional.ragged_ops import gen_segment_indices
 from ..nn.initializers import NormalInitializer
 from ..ops.attention import ragged_self_attention, target_attention
-from ..ops.dense import MLP, Linear
+from ..ops.dense import MLP, LayerNorm, Linear
 from ..ragged import RaggedTensor
 
 
@@ -44,21 +44,23 @@ class EncoderLayer(nn.Module):
     def __init__(self, hidden: int, heads: int, ffn: int, dtype):
         super().__init__()
         self.hidden, self.heads = hidden, heads
-        self.norm1, self.norm2 = nn.LayerNorm(hidden), nn.LayerNorm(hidden)
+        self.norm1, self.norm2 = LayerNorm(hidden), LayerNorm(hidden)
         self.qkv = Linear(hidden, 3 * hidden, dtype=dtype)
         self.proj = Linear(hidden, hidden, dtype=dtype)
         self.ffn = MLP([hidden, ffn, hidden], final_act=False, dtype=dtype)
 
     def forward(self, x, seg, pos, lengths, max_len, offsets=None):
-        h = self.norm1(x)
+        # on CUDA the activations between the kernels stay bf16 and the two additions onto the fp32 residual stream happen in
+        # the epilogues of the projection GEMMs
+        h = self.norm1(x, out_bf16=x.is_cuda)
         qkv = self.qkv(h)                                                      # [T, 3 * hidden] packed
         qkv = qkv.to(torch.bfloat16) if x.is_cuda else qkv.float()
         if offsets is None:
             offsets = torch.cat([lengths.new_zeros(1), lengths.cumsum(0)])
-        o = ragged_self_attention(qkv, offsets, self.heads, max_len, seg, pos).float()
-        x = x + self.proj(o).float()
-        x = x + self.ffn(self.norm2(x)).float()
-        return x
+        o = ragged_self_attention(qkv, offsets, self.heads, max_len, seg, pos)
+        x = self.proj.forward_residual(o, x)
+        f = self.ffn.layers[0](self.norm2(x, out_bf16=x.is_cuda))
+        return self.ffn.layers[1].forward_residual(f, x)
 
 
 class SequenceModel(nn.Module):
@@ -87,7 +89,7 @@ class SequenceModel(nn.Module):
         self.token_proj = Linear(2 * emb_dim, hidden, dtype=compute_dtype)
         self.query_proj = Linear(2 * emb_dim, hidden, dtype=compute_dtype)
         self.layers = nn.ModuleList([EncoderLayer(hidden, heads, ffn, compute_dtype) for _ in range(layers)])
-        self.final_norm = nn.LayerNorm(hidden)
+        self.final_norm = LayerNorm(hidden)
         self.head = MLP([3 * hidden + len(self.profile_fields) * profile_dim] + list(head_mlp), final_act=False, dtype=compute_dtype)
         self.loss_fn = nn.BCEWithLogitsLoss()
 

@@ -53,6 +53,60 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw[:N, :K], db[:N], None
 
 
+class _LinearResidualFn(torch.autograd.Function):
+    """out (fp32) = residual + x W^T + b with the addition in the GEMM's epilogue (no separate cast and add kernels)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual):
+        C = native()
+        N, K = weight.shape
+        assert N % 8 == 0 and x.shape[1] == _pad8(K) and x.dtype == torch.bfloat16
+        wb = C.cast_pad_bf16(weight, N, _pad8(K))
+        ctx.save_for_backward(x, wb)
+        ctx.shape = (N, K)
+        return C.gemm_bf16_residual(x, wb, bias, residual.contiguous())
+
+    @staticmethod
+    def backward(ctx, dout):
+        C = native()
+        x, wb = ctx.saved_tensors
+        N, K = ctx.shape
+        dob = dout.to(torch.bfloat16).contiguous()
+        dy, db = C.relu_bwd_bias(dob, dob, False)
+        dx = C.gemm_bf16(dy, wb, None, False, False, True, False, None) if ctx.needs_input_grad[0] else None
+        dw = C.gemm_bf16(dy, x, None, False, True, True, True, None)
+        return dx, dw[:N, :K], db[:N], dout
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps, out_bf16):
+        y, stats = native().layer_norm_fwd(x, gamma, beta, eps, out_bf16)
+        ctx.save_for_backward(x, stats, gamma)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, stats, gamma = ctx.saved_tensors
+        dx, dgamma, dbeta = native().layer_norm_bwd(dy.contiguous(), x, stats, gamma)
+        return dx, dgamma, dbeta, None, None
+
+
+class LayerNorm(nn.LayerNorm):
+    """``nn.LayerNorm`` over the last dimension of ``[rows, hidden]``. On CUDA (fp32 input, hidden a multiple of 4 up to 1024)
+    the forward is one kernel that can write bf16 directly (``out_bf16``: the output then feeds a GEMM without a separate
+    cast) and the backward is one pass that produces the input gradient and both weight gradients
+    (``csrc/kernels/norm_ops.cu``). Elsewhere it is the library's layer norm."""
+
+    def forward(self, x, out_bf16: bool = False):
+        H = x.shape[-1]
+        if (x.is_cuda and x.dim() == 2 and x.dtype == torch.float32 and H % 4 == 0 and H <= 1024 and self.elementwise_affine
+                and self.bias is not None):
+            return _LayerNormFn.apply(x.contiguous(), self.weight, self.bias, self.eps, out_bf16)
+        y = super().forward(x)
+        return y.to(torch.bfloat16) if out_bf16 and x.is_cuda else y
+
+
 class Linear(nn.Module):
     """``y = act(x W^T + b)``; fp32 master weights, bf16 compute on CUDA. Output width is padded to a multiple of 8
     (``out_pad``) so that it can feed the next layer's TMA loads directly; ``forward`` slices the padding off when asked."""
@@ -75,6 +129,14 @@ class Linear(nn.Module):
             return y if keep_pad or y.shape[1] == self.out_features else y[:, :self.out_features]
         y = F.linear(x.float()[:, :self.in_features], self.weight, self.bias)
         return F.relu(y) if self.act else y
+
+    def forward_residual(self, x, residual):
+        """``residual + x W^T + b`` in fp32 (no activation): on CUDA the sum is formed in the GEMM's epilogue."""
+        assert not self.act
+        if (x.is_cuda and self.dtype == torch.bfloat16 and self.out_features % 8 == 0 and residual.dtype == torch.float32
+                and x.shape[1] == _pad8(self.in_features)):
+            return _LinearResidualFn.apply(x.to(torch.bfloat16).contiguous(), self.weight, self.bias, residual)
+        return residual + self.forward(x).float()
 
 
 class _MLPFn(torch.autograd.Function):

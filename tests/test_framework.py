@@ -500,3 +500,15 @@ def test_packed_batch_round_trip_and_prefetcher():
     for b, got in zip(batches, DevicePrefetcher(packed, "cpu")):
         for k in b:
             same(got[k], b[k])
+
+
+def test_async_scalar_reader_returns_every_posted_value():
+    """Tickets come back with the value posted, in any order within the ring, on the host path (the CUDA path is in the GPU tests)."""
+    from recis_b200.utils import AsyncScalarReader
+    r = AsyncScalarReader("cpu", slots=4)
+    t = [r.post(torch.tensor(float(i) * 0.5)) for i in range(4)]
+    assert [r.get(k) for k in reversed(t)] == [1.5, 1.0, 0.5, 0.0]
+    t5 = r.post(torch.tensor(7.0))
+    assert r.get(t5) == 7.0
+    with pytest.raises(AssertionError):
+        r.get(t[0])

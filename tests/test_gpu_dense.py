@@ -136,3 +136,70 @@ def test_adamw_tf_native_matches_cpu_foreach():
         o2.step()
     for a, b in zip(cpu, gpu):
         torch.testing.assert_close(a, b.cpu(), rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("rows,hidden,out_bf16", [(1000, 256, True), (333, 64, False), (77, 1024, True), (4097, 36, False), (5, 512, False)])
+def test_layer_norm_kernels_match_fp32_reference(rows, hidden, out_bf16):
+    """Forward (bf16 or fp32 output) and the one-pass backward (input gradient and both weight gradients) against torch's
+    layer norm in fp32 on the CPU."""
+    from recis_b200.ops.dense import LayerNorm
+    g = torch.Generator().manual_seed(rows + hidden)
+    x = torch.randn(rows, hidden, generator=g) * 2 + 0.5
+    go = torch.randn(rows, hidden, generator=g)
+    ref = torch.nn.LayerNorm(hidden)
+    with torch.no_grad():
+        ref.weight.copy_(torch.randn(hidden, generator=g) * 0.5 + 1)
+        ref.bias.copy_(torch.randn(hidden, generator=g) * 0.1)
+    ours = LayerNorm(hidden).to(DEV)
+    ours.load_state_dict(ref.state_dict())
+    xr = x.clone().requires_grad_(True)
+    yr = ref(xr)
+    yr.backward(go)
+    xo = x.to(DEV).requires_grad_(True)
+    yo = ours(xo, out_bf16=out_bf16)
+    assert yo.dtype == (torch.bfloat16 if out_bf16 else torch.float32)
+    yo.backward(go.to(DEV).to(yo.dtype))
+    rel = lambda a, b: float((a.float().cpu() - b).norm() / b.norm().clamp(min=1e-12))
+    tol = 6e-3 if out_bf16 else 2e-5           # bf16 output and bf16 upstream gradient round at 2^-9
+    assert rel(yo.detach(), yr.detach()) < tol
+    assert rel(xo.grad, xr.grad) < tol
+    assert rel(ours.weight.grad, ref.weight.grad) < tol
+    assert rel(ours.bias.grad, ref.bias.grad) < tol
+
+
+@pytest.mark.parametrize("M,N,relu", [(5000, 256, True), (777, 1024, True), (4096, 768, False), (100, 8, True), (300, 64, True), (64, 24, True)])
+def test_relu_backward_with_bias_gradient_all_widths(M, N, relu):
+    """Widths served by the 16-byte kernel (powers of two below 256, multiples of 256) and one that falls back (24)."""
+    C = recis_b200.native()
+    g = torch.Generator().manual_seed(M + N)
+    y = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    dout = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    dy, db = C.relu_bwd_bias(y.to(DEV), dout.to(DEV), relu)
+    want = dout.float() * ((y.float() > 0).float() if relu else 1.0)
+    assert torch.equal(dy.cpu().float(), want.to(torch.bfloat16).float())
+    ref_db = want.to(torch.bfloat16).float().sum(0)
+    assert float((db.cpu() - ref_db).norm() / ref_db.norm().clamp(min=1e-6)) < 1e-5
+
+
+def test_linear_with_residual_in_the_epilogue_matches_fp32_reference():
+    from recis_b200.ops.dense import Linear
+    g = torch.Generator().manual_seed(3)
+    M, K, N = 1000, 256, 256
+    lin = Linear(K, N).to(DEV)
+    x = torch.randn(M, K, generator=g)
+    res = torch.randn(M, N, generator=g)
+    go = torch.randn(M, N, generator=g)
+    xo = x.to(DEV).to(torch.bfloat16).requires_grad_(True)
+    ro = res.to(DEV).requires_grad_(True)
+    out = lin.forward_residual(xo, ro)
+    assert out.dtype == torch.float32
+    out.backward(go.to(DEV))
+    xb = x.to(torch.bfloat16).float().requires_grad_(True)
+    rr = res.clone().requires_grad_(True)
+    W, b = lin.weight.detach().cpu().to(torch.bfloat16).float().requires_grad_(True), lin.bias.detach().cpu().clone().requires_grad_(True)
+    ref = rr + xb @ W.t() + b
+    ref.backward(go)
+    rel = lambda a, b_: float((a.float().cpu() - b_).norm() / b_.norm().clamp(min=1e-12))
+    assert rel(out.detach(), ref.detach()) < 1e-5
+    assert torch.equal(ro.grad.cpu(), go)
+    assert rel(xo.grad, xb.grad) < 8e-3 and rel(lin.weight.grad, W.grad) < 8e-3 and rel(lin.bias.grad, b.grad) < 8e-3
