@@ -22,7 +22,9 @@
 #include "../common/rb_launch.h"
 #include "../common/rb_tcgen05.cuh"
 #include "rb_dense.h"
+#include <cuda.h>
 #include <cuda_bf16.h>
+#include <cstring>
 
 namespace {
 
@@ -33,13 +35,18 @@ constexpr int kHead = 64;                  // head width (one 128-byte swizzle r
 constexpr int kBlk = kTile * 128;          // bytes of one [128 rows x 64 bf16] swizzled block
 constexpr uint32_t kTmemCols = 256;        // S: columns 0..127, PV: columns 128..191
 
-// Copy one row of 64 bf16 (128 bytes) from global memory (or zeros) into row r of a swizzled block.
-__device__ __forceinline__ void stage_row(uint8_t* blk, int r, const __nv_bfloat16* src) {
+// A [128 rows x 64 bf16] tile moves through registers in two steps, so that the loads of the next tile can be in flight while
+// the current one is being computed on: eight lanes read one row's eight 16-byte chunks (a warp-wide load covers four whole
+// rows), thread t holds chunk (t & 7) of rows (t >> 3) + 16 i. Rows at or past rows_valid read as zeros.
+__device__ __forceinline__ void tile_load(uint4 (&v)[8], const __nv_bfloat16* base, int64_t ld, int rows_valid, int t) {
+  const __nv_bfloat16* p = base + (int64_t)(t >> 3) * ld + (t & 7) * 8;
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const uint4 v = src ? reinterpret_cast<const uint4*>(src)[c] : make_uint4(0u, 0u, 0u, 0u);
-    *reinterpret_cast<uint4*>(blk + swizzle128_offset(r, c * 8)) = v;
-  }
+  for (int i = 0; i < 8; ++i)
+    v[i] = ((t >> 3) + 16 * i < rows_valid) ? __ldg(reinterpret_cast<const uint4*>(p + (int64_t)(16 * i) * ld)) : make_uint4(0u, 0u, 0u, 0u);
+}
+__device__ __forceinline__ void tile_store(uint8_t* blk, const uint4 (&v)[8], int t) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(blk + swizzle128_offset((t >> 3) + 16 * i, (t & 7) * 8)) = v[i];
 }
 
 __global__ void __launch_bounds__(128, 2)
@@ -65,7 +72,11 @@ ragged_attention_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t
 
   const int q = qt * kTile + t;
   const bool q_ok = q < L;
-  stage_row(qtile, t, q_ok ? qkv + (int64_t)(s0 + q) * ld + h * kHead : nullptr);
+  uint4 kreg[8], vreg[8];
+  tile_load(kreg, qkv + (int64_t)(s0 + qt * kTile) * ld + h * kHead, ld, L - qt * kTile, t);
+  tile_store(qtile, kreg, t);
+  tile_load(kreg, qkv + (int64_t)s0 * ld + (H + h) * kHead, ld, L, t);
+  tile_load(vreg, qkv + (int64_t)s0 * ld + (2 * H + h) * kHead, ld, L, t);
 
   float o[kHead];
 #pragma unroll
@@ -82,10 +93,9 @@ ragged_attention_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t
 
   const int n_kv = (L + kTile - 1) / kTile;
   for (int j = 0; j < n_kv && ok; ++j) {
-    const int key = j * kTile + t;
-    const __nv_bfloat16* krow = key < L ? qkv + (int64_t)(s0 + key) * ld + (H + h) * kHead : nullptr;
-    stage_row(ktile, t, krow);
-    stage_row(vtile, t, krow ? krow + H * kHead : nullptr);
+    // the previous step's MMAs have completed (bar_o), so the K and V tiles can be overwritten with what the registers hold
+    tile_store(ktile, kreg, t);
+    tile_store(vtile, vreg, t);
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
@@ -96,6 +106,12 @@ ragged_attention_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t
       for (int k = 0; k < kHead / 16; ++k)
         umma_bf16(tmem, make_desc(sq + k * 32, 16, 1024), make_desc(sk + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
       umma_commit(&bar_s);
+    }
+    if (j + 1 < n_kv) {
+      // the next tile's loads travel while this tile's softmax and MMAs run
+      const int64_t row0 = s0 + (j + 1) * kTile;
+      tile_load(kreg, qkv + row0 * ld + (H + h) * kHead, ld, L - (j + 1) * kTile, t);
+      tile_load(vreg, qkv + row0 * ld + (2 * H + h) * kHead, ld, L - (j + 1) * kTile, t);
     }
     // the outcome of a bounded wait is made uniform for the CTA: every thread takes the same path through the barriers below
     ok = __syncthreads_and(mbar_wait(&bar_s, (uint32_t)(j & 1), &abort_flag) ? 1 : 0) != 0;
@@ -217,7 +233,8 @@ constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 320, kColDQ =
 __global__ void __launch_bounds__(128, 1)
 ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse2,
                             const float* __restrict__ delta, const int32_t* __restrict__ offsets, int H, float scale, float scale_log2,
-                            float* __restrict__ dqkv, int64_t* __restrict__ status) {
+                            float* __restrict__ dqkv, const __grid_constant__ CUtensorMap map_dq, int dq_tma,
+                            int64_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar1, bar2;
   __shared__ uint32_t tmem_slot;
@@ -233,6 +250,7 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
   uint8_t* dotile = smem + 3 * kBlk;       // [128 q][64 d]
   uint8_t* ptile = smem + 4 * kBlk;        // 2 x [128 q][64 keys]
   uint8_t* dstile = smem + 6 * kBlk;       // 2 x [128 q][64 keys]
+  uint8_t* dqstage = smem + 8 * kBlk;      // 2 x [128 q][32 d] fp32: the dQ tile on its way out (two 128-byte-wide boxes)
   const int t = threadIdx.x, warp = t >> 5;
   const int64_t ld = (int64_t)3 * H * kHead;
   if (t == 0) { abort_flag = 0; mbar_init(&bar1, 1); mbar_init(&bar2, 1); mbar_fence_init(); }
@@ -240,11 +258,19 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
 
   const int key = kt * kTile + t;
   const bool key_ok = key < L;
+  uint4 qreg[8], dreg[8];
   {
-    const __nv_bfloat16* krow = key_ok ? qkv + (int64_t)(s0 + key) * ld + (H + h) * kHead : nullptr;
-    stage_row(ktile, t, krow);
-    stage_row(vtile, t, krow ? krow + H * kHead : nullptr);
+    const int64_t row0 = s0 + kt * kTile;
+    tile_load(qreg, qkv + row0 * ld + (H + h) * kHead, ld, L - kt * kTile, t);
+    tile_load(dreg, qkv + row0 * ld + (2 * H + h) * kHead, ld, L - kt * kTile, t);
+    tile_store(ktile, qreg, t);
+    tile_store(vtile, dreg, t);
   }
+  // the first query tile's rows, its softmax statistics and correction terms
+  tile_load(qreg, qkv + (int64_t)s0 * ld + h * kHead, ld, L, t);
+  tile_load(dreg, d_o + (int64_t)s0 * H * kHead + h * kHead, (int64_t)H * kHead, L, t);
+  float lse_next = t < L ? lse2[(int64_t)(s0 + t) * H + h] : 0.f;
+  float delta_next = t < L ? delta[(int64_t)(s0 + t) * H + h] : 0.f;
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
@@ -261,10 +287,10 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
     const int q = i * kTile + t;
     const bool q_ok = q < L;
     const int64_t tok = s0 + q;
-    stage_row(qtile, t, q_ok ? qkv + tok * ld + h * kHead : nullptr);
-    stage_row(dotile, t, q_ok ? d_o + tok * H * kHead + h * kHead : nullptr);
-    const float lse_q = q_ok ? lse2[tok * H + h] : 0.f;
-    const float delta_q = q_ok ? delta[tok * H + h] : 0.f;
+    // the previous step's MMAs have completed (bar2) and its dQ tile has been read by the copy engine (thread 0 waited below)
+    tile_store(qtile, qreg, t);
+    tile_store(dotile, dreg, t);
+    const float lse_q = lse_next, delta_q = delta_next;
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
@@ -278,6 +304,15 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
       for (int k = 0; k < kHead / 16; ++k)
         umma_bf16(tmem + kColDP, make_desc(sdo + k * 32, 16, 1024), make_desc(sv + k * 32, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
       umma_commit(&bar1);
+    }
+    if (i + 1 < n_q) {
+      // the next query tile's loads travel while this tile is being computed
+      const int64_t row0 = s0 + (i + 1) * kTile;
+      const int left = L - (i + 1) * kTile;
+      tile_load(qreg, qkv + row0 * ld + h * kHead, ld, left, t);
+      tile_load(dreg, d_o + row0 * H * kHead + h * kHead, (int64_t)H * kHead, left, t);
+      lse_next = t < left ? lse2[(row0 + t) * H + h] : 0.f;
+      delta_next = t < left ? delta[(row0 + t) * H + h] : 0.f;
     }
     ok = __syncthreads_and(mbar_wait(&bar1, (uint32_t)(i & 1), &abort_flag) ? 1 : 0) != 0;
     fence_after_sync();
@@ -330,6 +365,8 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
         umma_bf16(tmem + kColDQ, make_desc(sds + (k >> 2) * kBlk + (k & 3) * 32, 16, 1024), make_desc(sk + k * 2048, kBlk, 1024), idesc_km,
                   k > 0 ? 1u : 0u);
       umma_commit(&bar2);
+      // the previous step's dQ tile must have been read before this step's is written over it (after the barrier below)
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
     ok = __syncthreads_and(mbar_wait(&bar2, (uint32_t)(i & 1), &abort_flag) ? 1 : 0) != 0;
     fence_after_sync();
@@ -338,7 +375,14 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
       uint32_t r[32];
       tmem_ld32(tmem + lane_base + kColDQ + (uint32_t)c0, r);
       tmem_ld_wait();
-      if (q_ok) {
+      if (dq_tma) {
+        // row t of a 32-column fp32 box: eight 16-byte chunks in the 128-byte swizzle
+        uint8_t* row = dqstage + (c0 >> 5) * kBlk + t * 128;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          *reinterpret_cast<float4*>(row + ((e ^ (t & 7)) << 4)) = make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]),
+                                                                               __uint_as_float(r[4 * e + 2]), __uint_as_float(r[4 * e + 3]));
+      } else if (q_ok) {
         float* dst = dqkv + tok * ld + h * kHead + c0;
 #pragma unroll
         for (int e = 0; e < 8; ++e)
@@ -346,7 +390,22 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
                                                                     __uint_as_float(r[4 * e + 2]), __uint_as_float(r[4 * e + 3])));
       }
     }
+    if (dq_tma) {
+      // The tile leaves as two add-reductions of [128 rows x 32 columns]. Rows past the end of this sequence hold exact zeros
+      // (their P and dS were masked), so adding them onto the next sequence's rows changes nothing; rows past the end of the
+      // matrix are clipped by the copy.
+      fence_smem_to_async();
+      __syncthreads();
+      if (t == 0) {
+#pragma unroll
+        for (int bx = 0; bx < 2; ++bx)
+          asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                       ::"l"(&map_dq), "r"(smem_u32(dqstage + bx * kBlk)), "r"(h * kHead + bx * 32), "r"(s0 + i * kTile) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
   }
+  if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the copies that read it
 
   if (ok) {
     for (int c0 = 0; c0 < kHead; c0 += 32) {
@@ -409,7 +468,11 @@ extern "C" int rb_ragged_attention_bwd(const void* qkv, const void* out, const v
   attention_delta_kernel<<<(int)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(out),
                                                                                    reinterpret_cast<const __nv_bfloat16*>(d_out), rows, delta);
   rb::note_launch();
-  const size_t smem = 1024 + 8 * (size_t)kBlk;
+  const size_t smem = 1024 + 10 * (size_t)kBlk;
+  // dQ leaves as TMA add-reductions of [128 x 32] fp32 boxes when a tensor map can be made; otherwise as per-row reductions
+  CUtensorMap map_dq;
+  const int dq_tma = rb_tensor_map_2d(&map_dq, dqkv, T, (int64_t)3 * H * kHead, (int64_t)3 * H * kHead, 32, kTile, 1) == 0 ? 1 : 0;
+  if (!dq_tma) memset(&map_dq, 0, sizeof(map_dq));
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(ragged_attention_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 3;
@@ -417,7 +480,7 @@ extern "C" int rb_ragged_attention_bwd(const void* qkv, const void* out, const v
   }
   dim3 grid((max_len + kTile - 1) / kTile, B, H);
   ragged_attention_bwd_kernel<<<grid, 128, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const __nv_bfloat16*>(d_out),
-                                                       lse2, delta, offsets, H, scale, scale * 1.4426950408889634f, dqkv, status);
+                                                       lse2, delta, offsets, H, scale, scale * 1.4426950408889634f, dqkv, map_dq, dq_tma, status);
   rb::note_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }

@@ -539,6 +539,11 @@ bool persistent_enabled() {
 
 }  // namespace
 
+extern "C" int rb_tensor_map_2d(void* out_map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows, int fp32) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * (fp32 ? 4 : 2)) % 16) return 1;
+  return get_map(reinterpret_cast<CUtensorMap*>(out_map), base, rows, cols, ld, box_cols, box_rows, fp32 != 0) ? 0 : 2;
+}
+
 extern "C" int rb_gemm_splits(int MM, int NN, int KK) {
   // few output tiles and a long reduction (weight gradients): spread the reduction over about two waves of CTAs
   const int tiles = ((NN + BN - 1) / BN) * ((MM + BM - 1) / BM);

@@ -16,7 +16,10 @@ extern "C" {
 int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo, int out_fp32,
                  const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int splits, int64_t* status,
                  cudaStream_t st);
-int rb_gemm_splits(int MM, int NN, int KK);   // heuristic split count for a weight-gradient shaped problem
+int rb_gemm_splits(int MM, int NN, int KK);
+// A (cached) TMA descriptor of a 2-D bf16 or fp32 matrix [rows][cols] with row pitch ld elements, box {box_cols, box_rows}, 128-byte
+// swizzle, written to out_map (a CUtensorMap, 128 bytes). 0 on success, 1 = base or pitch not 16-byte aligned, 2 = encode failed.
+int rb_tensor_map_2d(void* out_map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_cols, int box_rows, int fp32);   // heuristic split count for a weight-gradient shaped problem
 
 #ifdef __cplusplus
 }
