@@ -289,30 +289,45 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (threadIdx.x == 0 && abort_flag) rb::set_status(status, rb::kStatusWaitTimeout);
 }
 
-// ---------------------------------------------------------------------- persistent variant (opt-in: RECIS_GEMM_PERSISTENT=1)
-// One CTA per tile slot walks a strided list of output tiles. Two accumulator stages live in tensor memory (2 x BN columns):
-// while the epilogue warps drain the accumulator of tile i (tcgen05.ld, bias/ReLU, stores), the MMA warp already fills the
-// other accumulator with tile i+1, and the TMA warp runs ahead through the shared-memory ring across tile boundaries. This
-// hides the per-tile prologue and epilogue that dominate the short reductions (K = 512 .. 1024) of recommendation MLPs.
-// No split-K here (weight gradients keep the kernel above).
+// ---------------------------------------------------------------------- persistent variant
+// One CTA per SM walks a strided list of output tiles. Two accumulator stages live in tensor memory (2 x BN columns): while the
+// epilogue warps drain the accumulator of tile i (tcgen05.ld, bias / residual / ReLU, staging, TMA store), the MMA warp already
+// fills the other accumulator with tile i+1, and the TMA warp runs ahead through the shared-memory ring across tile
+// boundaries. With the whole SM to itself the CTA has a deeper ring (six stages for bf16 output, five for fp32) and a
+// staging area of its own, so a tile's prologue and epilogue cost nothing after the first tile - which is what the short
+// reductions (K = 512 .. 1024) of recommendation MLPs were expected to need. Measured, it is slower than two co-resident
+// one-tile CTAs (8192^3: 0.90 against 1.16 PFLOP/s; 8192 x 1024 x 1024: 36 against 31 microseconds): with 128 x 128 tiles the
+// tensor core's operand reads and the TMA fills together ask for twice the shared-memory bandwidth of an SM, and two independent
+// producer / consumer chains use what there is better than one deep ring. Opt-in (RECIS_GEMM_PERSISTENT=1), kept for
+// comparison; it needs an output that can leave through TMA stores, and split reductions keep the kernel above.
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+template <typename OutT> struct PersistentCfg;
+template <> struct PersistentCfg<__nv_bfloat16> { static constexpr int kStagesP = 6; static constexpr uint32_t kStagingBytes = BM * BN * 2; };
+template <> struct PersistentCfg<float> { static constexpr int kStagesP = 5; static constexpr uint32_t kStagingBytes = BM * BN * 4; };
+template <typename OutT> constexpr uint32_t persistent_smem_bytes() {
+  return PersistentCfg<OutT>::kStagesP * kStageBytes + PersistentCfg<OutT>::kStagingBytes + 1024;
+}
+
 template <bool A_MN, bool B_MN, typename OutT>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                                    OutT* __restrict__ out, const float* __restrict__ bias, const float* __restrict__ beta_src,
-                                    int MM, int NN, int KK, int ldo, int relu, int64_t* __restrict__ status) {
+                                    const __grid_constant__ CUtensorMap map_o, const float* __restrict__ bias,
+                                    const float* __restrict__ beta_src, int MM, int NN, int KK, int ldo, int relu,
+                                    int64_t* __restrict__ status) {
+  constexpr int S = PersistentCfg<OutT>::kStagesP;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[kStages];
-  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t full_bar[S];
+  __shared__ __align__(8) uint64_t empty_bar[S];
   __shared__ __align__(8) uint64_t acc_full_bar[2];
   __shared__ __align__(8) uint64_t acc_empty_bar[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = smem + S * kStageBytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (NN + BN - 1) / BN, tiles_m = (MM + BM - 1) / BM;
   const int num_tiles = tiles_n * tiles_m;
@@ -320,7 +335,7 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full_bar[a], 1); mbar_init(&acc_empty_bar[a], 4); }   // 4 epilogue warps release a stage
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -343,8 +358,8 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
       for (int kb = 0; kb < total_kb; ++kb, ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1u;
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1u;
         ok = mbar_wait(&empty_bar[s], ph ^ 1u, &abort_flag);
         if (!ok) break;
         uint8_t* sa = smem + s * kStageBytes;
@@ -360,10 +375,10 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
     }
     if (!ok) {
       // drain: copies already issued must land before this CTA's shared memory goes away
-      const uint32_t first = issued > (uint32_t)kStages ? issued - kStages : 0u;
+      const uint32_t first = issued > (uint32_t)S ? issued - S : 0u;
       for (uint32_t j = first; j < issued; ++j) {
-        const int s = j % kStages;
-        const uint32_t ph = (j / kStages) & 1u;
+        const int s = j % S;
+        const uint32_t ph = (j / S) & 1u;
         for (uint32_t spin = 0; spin < kSpinLimit; ++spin) if (mbar_try_wait(&full_bar[s], ph)) break;
       }
     }
@@ -380,8 +395,8 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t tmem_acc = tmem_base + acc * (uint32_t)BN;
       for (int kb = 0; kb < total_kb; ++kb, ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1u;
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1u;
         ok = mbar_wait(&full_bar[s], ph, &abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -399,40 +414,74 @@ gemm_bf16_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
   } else if (warp >= 2) {
     // ------------------------------------------------------------------ epilogue: drains accumulator j & 1 of every tile
     const int q = warp & 3;
-    const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+    constexpr int kBoxes = BN / Store<OutT>::kBoxCols;
+    uint8_t* slab = staging + q * kBoxes * 4096;          // this warp's 32 rows, as boxes of 32 rows x 128 bytes
     uint32_t j = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
       const uint32_t acc = j & 1u, acc_ph = (j >> 1) & 1u;
-      if (!mbar_wait(&acc_full_bar[acc], acc_ph, &abort_flag)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
       const int row = m0 + q * 32 + lane;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= NN) break;
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * (uint32_t)BN + (uint32_t)c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < MM) {
+      // this tile's bias for the lane's four column chunks, fetched before the accumulator is waited for
+      float bias_r[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) bias_r[c] = (bias != nullptr && n0 + c * 32 + lane < NN) ? bias[n0 + c * 32 + lane] : 0.f;
+      if (!mbar_wait(&acc_full_bar[acc], acc_ph, &abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // the previous tile's stores must have read the slab before it is written again
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int c0 = c * 32;
+        if (n0 + c0 < NN) {                                  // uniform for the warp
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * (uint32_t)BN + (uint32_t)c0, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           float v[32];
           const int valid = min(32, NN - (n0 + c0));
+          const float* brow = beta_src + (int64_t)row * ldo + n0 + c0;
+          const bool beta_here = beta_src != nullptr && row < MM;
+          const bool beta_vec = beta_here && valid == 32 && (ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(beta_src) & 15) == 0);
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) {
-            float x = __uint_as_float(r[jj]);
-            if (jj < valid) {
-              if (bias) x += bias[n0 + c0 + jj];
-              if (beta_src) x += beta_src[(int64_t)row * ldo + n0 + c0 + jj];
+          for (int j4 = 0; j4 < 32; j4 += 4) {
+            float4 bt = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (beta_vec) bt = *reinterpret_cast<const float4*>(brow + j4);
+            else if (beta_here) {
+              if (j4 + 0 < valid) bt.x = brow[j4 + 0];
+              if (j4 + 1 < valid) bt.y = brow[j4 + 1];
+              if (j4 + 2 < valid) bt.z = brow[j4 + 2];
+              if (j4 + 3 < valid) bt.w = brow[j4 + 3];
             }
-            v[jj] = relu ? fmaxf(x, 0.f) : x;
+            // column c0 + j's bias sits in lane j's register
+            const float x0 = __uint_as_float(r[j4 + 0]) + __shfl_sync(0xffffffffu, bias_r[c], j4 + 0) + bt.x;
+            const float x1 = __uint_as_float(r[j4 + 1]) + __shfl_sync(0xffffffffu, bias_r[c], j4 + 1) + bt.y;
+            const float x2 = __uint_as_float(r[j4 + 2]) + __shfl_sync(0xffffffffu, bias_r[c], j4 + 2) + bt.z;
+            const float x3 = __uint_as_float(r[j4 + 3]) + __shfl_sync(0xffffffffu, bias_r[c], j4 + 3) + bt.w;
+            v[j4 + 0] = relu ? fmaxf(x0, 0.f) : x0; v[j4 + 1] = relu ? fmaxf(x1, 0.f) : x1;
+            v[j4 + 2] = relu ? fmaxf(x2, 0.f) : x2; v[j4 + 3] = relu ? fmaxf(x3, 0.f) : x3;
           }
-          Store<OutT>::row32(out + (int64_t)row * ldo + n0 + c0, v, valid, vec_ok);
+          Store<OutT>::stage32(slab, lane, c0, v);
         }
       }
-      // every lane's tcgen05.ld has completed (wait::ld above); order them before the release of the accumulator
+      // every lane's tcgen05.ld has completed (wait::ld above): the accumulator goes back to the MMA warp before the stores
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+      if (lane == 0) {
+        mbar_arrive(&acc_empty_bar[acc]);
+        if (m0 + q * 32 < MM) {
+#pragma unroll
+          for (int bx = 0; bx < kBoxes; ++bx) {
+            const int col = n0 + bx * Store<OutT>::kBoxCols;
+            if (col >= NN) break;
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(&map_o), "r"(smem_u32(slab + bx * 4096)), "r"(col), "r"(m0 + q * 32) : "memory");
+          }
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the stores' reads
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -517,17 +566,18 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, 
 }
 
 template <bool A_MN, bool B_MN, typename OutT>
-int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const float* bias, const float* beta_src, int MM, int NN,
-                      int KK, int ldo, int relu, int64_t* status, cudaStream_t st) {
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const float* bias, const float* beta_src, int MM,
+                      int NN, int KK, int ldo, int relu, int64_t* status, cudaStream_t st) {
   auto kern = gemm_bf16_tcgen05_persistent_kernel<A_MN, B_MN, OutT>;
+  constexpr uint32_t smem = persistent_smem_bytes<OutT>();
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess) return 3;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 3;
     attr_set = true;
   }
   const int tiles = ((NN + BN - 1) / BN) * ((MM + BM - 1) / BM);
-  const int grid = std::min(tiles, 148 * 2);          // two CTAs (2 x 256 tensor-memory columns, 2 x 97 KB) per SM
-  kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, reinterpret_cast<OutT*>(out), bias, beta_src, MM, NN, KK, ldo, relu, status);
+  const int grid = std::min(tiles, 148);               // one CTA per SM (2 x 128 tensor-memory columns, about 225 KB shared memory)
+  kern<<<grid, kThreads, smem, st>>>(ma, mb, mo, bias, beta_src, MM, NN, KK, ldo, relu, status);
   rb::note_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
@@ -571,11 +621,11 @@ extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b,
   else
     mo = ma;
   if (splits > 1 && (!out_fp32 || relu)) return 6;   // partial tiles are accumulated with fp32 reductions into a zeroed output
-  if (persistent_enabled() && splits <= 1 && KK > 0) {
+  if (persistent_enabled() && tma_out && splits <= 1 && KK > 0) {
 #define RB_GEMM_PCASE(AM, BMJ)                                                                                                  \
   if ((a_mn != 0) == AM && (b_mn != 0) == BMJ)                                                                                  \
-    return out_fp32 ? launch_persistent<AM, BMJ, float>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st)            \
-                    : launch_persistent<AM, BMJ, __nv_bfloat16>(ma, mb, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st);
+    return out_fp32 ? launch_persistent<AM, BMJ, float>(ma, mb, mo, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st)             \
+                    : launch_persistent<AM, BMJ, __nv_bfloat16>(ma, mb, mo, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st);
     RB_GEMM_PCASE(false, false)
     RB_GEMM_PCASE(false, true)
     RB_GEMM_PCASE(true, false)

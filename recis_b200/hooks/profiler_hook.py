@@ -1,9 +1,12 @@
 """torch.profiler schedule driven from the step hook; writes a chrome trace per active window
-(``recis/hooks/profiler_hook.py:46-116``). Sparse-path kernels show up under their own names; NVTX ranges can be added
-around steps with ``nvtx=True``."""
+(``recis/hooks/profiler_hook.py:46-116``). ``output_dir`` may be a local directory or any URL that fsspec understands
+(``hdfs://``, ``s3://``, ``memory://`` ...): the trace is exported to a local temporary file and put there through the
+file system of the URL, as the reference does with its own file-system lookup (``recis/hooks/profiler_hook.py:71-116``).
+Sparse-path kernels show up under their own names; NVTX ranges can be added around steps with ``nvtx=True``."""
 from __future__ import annotations
 
 import os
+import tempfile
 
 import torch
 
@@ -15,7 +18,14 @@ class ProfilerHook(Hook):
                  with_stack=False, with_flops=False, nvtx=False):
         self.output_dir = output_dir
         self.app_id = os.environ.get("APP_ID", "recis_b200")
-        os.makedirs(output_dir, exist_ok=True)
+        self.remote = "://" in str(output_dir) and not str(output_dir).startswith("file://")
+        if self.remote:
+            import fsspec
+            self.fs, self.root = fsspec.core.url_to_fs(output_dir)
+            self.fs.makedirs(self.root, exist_ok=True)
+        else:
+            self.fs, self.root = None, str(output_dir)[7:] if str(output_dir).startswith("file://") else output_dir
+            os.makedirs(self.root, exist_ok=True)
         acts = [torch.profiler.ProfilerActivity.CPU]
         if torch.cuda.is_available():
             acts.append(torch.profiler.ProfilerActivity.CUDA)
@@ -36,8 +46,16 @@ class ProfilerHook(Hook):
         return self._on_trace
 
     def _on_trace(self, prof):
-        path = os.path.join(self.output_dir, f"{self.app_id}-timeline-{self._step}.json")
-        prof.export_chrome_trace(path)
+        name = f"{self.app_id}-timeline-{self._step}.json"
+        if not self.remote:
+            path = os.path.join(self.root, name)
+            prof.export_chrome_trace(path)
+        else:
+            path = self.root.rstrip("/") + "/" + name
+            with tempfile.TemporaryDirectory() as tmp:
+                local = os.path.join(tmp, name)
+                prof.export_chrome_trace(local)
+                self.fs.put_file(local, path)
         self.traces.append(path)
 
     def after_step(self, metrics=None, global_step=0):

@@ -310,6 +310,23 @@ def test_profiler_hook_writes_a_chrome_trace(tmp_path):
     assert hook.traces == [str(tmp_path / traces[0])]
 
 
+def test_profiler_hook_puts_traces_through_fsspec_for_url_output_dirs():
+    """An output directory given as a URL: the trace is exported locally and put through the URL's file system."""
+    import fsspec
+    from recis_b200.hooks import ProfilerHook
+    hook = ProfilerHook(wait=0, warmup=1, active=1, repeat=1, output_dir="memory://traces/job7")
+    x = torch.randn(32, 32)
+    for step in range(4):
+        (x @ x).sum()
+        hook.after_step({}, step)
+    hook.end()
+    fs = fsspec.filesystem("memory")
+    files = fs.ls("/traces/job7", detail=False)
+    assert len(files) == 1 and files[0].endswith(".json") and "-timeline-" in files[0] and fs.size(files[0]) > 100
+    assert hook.traces == [files[0]]
+    fs.rm("/traces", recursive=True)
+
+
 def test_prefetch_dataset_order_errors_and_early_exit():
     import threading
     import time
