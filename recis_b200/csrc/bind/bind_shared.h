@@ -1,11 +1,35 @@
 // Functions of one binding file that other binding files call directly (no trip through Python).
 #pragma once
+#include <cstdlib>
 #include <torch/extension.h>
 #include <tuple>
 #include <vector>
 #include "../kernels/rb_kernels.h"
 
 namespace rbx {
+
+// RECIS_DEBUG_BOUNDS=1: the bindings of the row-indexing kernels validate their index tensors on the device before they launch
+// (one reduction and one host read per call: a debugging mode) and raise instead of launching a kernel that would leave its
+// buffers. Nothing traps on the device.
+inline bool debug_bounds() {
+  static const bool on = [] { const char* e = std::getenv("RECIS_DEBUG_BOUNDS"); return e != nullptr && e[0] == '1'; }();
+  return on;
+}
+inline void debug_check_range(const char* what, const torch::Tensor& idx, int64_t lo, int64_t hi) {
+  if (!debug_bounds() || !idx.defined() || idx.numel() == 0) return;
+  auto flat = idx.reshape({-1});
+  auto bad = flat.lt(lo).logical_or(flat.ge(hi));
+  if (bad.any().item<bool>()) {
+    const int64_t pos = bad.nonzero().select(1, 0)[0].item<int64_t>();
+    TORCH_CHECK(false, what, ": index ", flat[pos].item<int64_t>(), " at position ", pos, " of ", flat.numel(), " is outside [", lo, ", ", hi, ")");
+  }
+}
+// the first n_dev[0] entries of idx (all of them without n_dev)
+inline torch::Tensor debug_prefix(const torch::Tensor& idx, const c10::optional<torch::Tensor>& n_dev) {
+  if (!debug_bounds() || !n_dev.has_value() || !n_dev->defined()) return idx;
+  const int64_t n = std::min<int64_t>(std::max<int64_t>(n_dev->reshape({-1})[0].item<int64_t>(), 0), idx.numel());
+  return idx.reshape({-1}).narrow(0, 0, n);
+}
 
 // storage type code (RbRowDType) of a tensor of embedding rows; raises for anything but fp32 / fp16 / bf16 / int8
 inline int row_dtype_of(const torch::Tensor& t) {

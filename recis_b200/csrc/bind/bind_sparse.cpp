@@ -180,6 +180,7 @@ Tensor gather_rows(const Tensor& src, const Tensor& rows, OptT n_dev) {
   const int64_t n = rows.numel(); const int64_t D = src.size(1);
   auto out = n_dev.has_value() ? torch::zeros({n, D}, src.options()) : torch::empty({n, D}, src.options());
   if (n == 0) return out;
+  rbx::debug_check_range("gather_rows: rows", rbx::debug_prefix(rows, n_dev), -1, src.size(0));
   const int64_t row_bytes = D * src.element_size();
   if (src.is_cuda()) {
     c10::cuda::CUDAGuard g(src.device());
@@ -196,6 +197,9 @@ void scatter_rows(Tensor dst, const Tensor& rows, const Tensor& src, bool broadc
   TORCH_CHECK(src.scalar_type() == dst.scalar_type(), "scatter_rows: source rows are ", src.scalar_type(), ", the table stores ", dst.scalar_type());
   const int64_t n = rows.numel(); const int64_t row_bytes = dst.size(1) * dst.element_size();
   if (n == 0) return;
+  rbx::debug_check_range("scatter_rows: rows", rows, -1, dst.size(0));
+  TORCH_CHECK(!rbx::debug_bounds() || broadcast || src.numel() >= n * dst.size(1), "scatter_rows: ", src.numel() / std::max<int64_t>(dst.size(1), 1),
+              " source rows for ", n, " indices");
   if (dst.is_cuda()) {
     c10::cuda::CUDAGuard g(dst.device());
     rb_scatter_rows(dst.data_ptr(), rows.data_ptr<int32_t>(), n, row_bytes, src.data_ptr(), broadcast, cur_stream());
@@ -207,6 +211,7 @@ void scatter_rows(Tensor dst, const Tensor& rows, const Tensor& src, bool broadc
 void fill_rows_i64(Tensor dst, const Tensor& rows, int64_t value) {
   const int64_t n = rows.numel();
   if (n == 0) return;
+  rbx::debug_check_range("fill_rows_i64: rows", rows, -1, dst.numel());
   if (dst.is_cuda()) {
     c10::cuda::CUDAGuard g(dst.device());
     rb_fill_rows_i64(dst.data_ptr<int64_t>(), rows.data_ptr<int32_t>(), n, value, cur_stream());
@@ -246,6 +251,12 @@ std::tuple<Tensor, Tensor, Tensor> pool_forward(const Tensor& base, OptT rows, c
   }
   int32_t* gp = need_grad ? gsrc.data_ptr<int32_t>() : nullptr;
   float* gs = need_grad ? gscale.data_ptr<float>() : nullptr;
+  if (rbx::debug_bounds() && n > 0) {
+    const bool via = rows.has_value() && rows->defined();
+    rbx::debug_check_range("pool_forward: reverse index", rev, 0, via ? rows->numel() : base.size(0));
+    if (via) rbx::debug_check_range("pool_forward: table rows of the referenced unique ids", rows->index_select(0, rev.to(torch::kInt64)), -1, base.size(0));
+    rbx::debug_check_range("pool_forward: offsets", offsets, 0, n + 1);
+  }
   if (base.is_cuda()) {
     c10::cuda::CUDAGuard g(base.device());
     rb_pool_forward(base.data_ptr(), base_dtype, opt_i32(rows), rev.data_ptr<int32_t>(), offsets.data_ptr<int32_t>(), opt_f32(weights), n_seg, D,
@@ -340,6 +351,7 @@ void sparse_apply(const Tensor& rows, const Tensor& grads, OptT n_dev, int64_t k
   TORCH_CHECK(rows.scalar_type() == torch::kInt32 && grads.is_contiguous() && grads.scalar_type() == torch::kFloat32);
   const int64_t n = rows.numel(); const int D = (int)w.size(1);
   if (n == 0) return;
+  rbx::debug_check_range("sparse_apply: rows", rbx::debug_prefix(rows, n_dev), -1, w.size(0));
   RbOpt opt = make_opt(kind, lr, beta1, beta2, eps, decay, alpha, grad_scale, w, s1, s2);
   if (w.is_cuda()) {
     c10::cuda::CUDAGuard g(w.device());

@@ -22,6 +22,7 @@
 #include "../common/rb_launch.h"
 #include "../common/rb_tcgen05.cuh"
 #include "rb_dense.h"
+#include "rb_gemm_store.cuh"
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <algorithm>
@@ -43,71 +44,7 @@ constexpr uint32_t kTileBytes = BM * BK * 2;                    // 16 KB per ope
 constexpr uint32_t kStageBytes = 2 * kTileBytes;
 constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;   // + slack for 1024-byte alignment
 
-template <typename OutT> struct Store;
-template <> struct Store<__nv_bfloat16> {
-  static __device__ __forceinline__ void row32(__nv_bfloat16* dst, const float (&v)[32], int valid, bool vec_ok) {
-    if (vec_ok && valid == 32) {
-      uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]), p1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
-        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]), p3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
-        uint4 u;
-        u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
-        u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
-        d4[q] = u;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) if (j < valid) dst[j] = __float2bfloat16_rn(v[j]);
-    }
-  }
-  static __device__ __forceinline__ void red32(__nv_bfloat16*, const float (&)[32], int, bool) {}   // split-K needs fp32 output
-  // 32 consecutive columns of one row into the swizzled staging slab: box of 64 columns, four 16-byte chunks
-  static constexpr int kBoxCols = 64;
-  static __device__ __forceinline__ void stage32(uint8_t* slab, int lane, int c0, const float (&v)[32]) {
-    uint8_t* row = slab + (c0 >> 6) * 4096 + lane * 128;
-    const int jbase = (c0 & 63) >> 3;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      __nv_bfloat162 p0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]), p1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
-      __nv_bfloat162 p2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]), p3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
-      uint4 u;
-      u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
-      u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
-      *reinterpret_cast<uint4*>(row + (((jbase + q) ^ (lane & 7)) << 4)) = u;
-    }
-  }
-};
-template <> struct Store<float> {
-  static __device__ __forceinline__ void row32(float* dst, const float (&v)[32], int valid, bool vec_ok) {
-    if (vec_ok && valid == 32) {
-      float4* d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) d4[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) if (j < valid) dst[j] = v[j];
-    }
-  }
-  static __device__ __forceinline__ void red32(float* dst, const float (&v)[32], int valid, bool vec_ok) {
-    if (vec_ok && valid == 32) {
-#pragma unroll
-      for (int q = 0; q < 8; ++q) atomicAdd(reinterpret_cast<float4*>(dst) + q, make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) if (j < valid) atomicAdd(dst + j, v[j]);
-    }
-  }
-  // 32 consecutive columns of one row = one full 128-byte row of a 32-column box: eight 16-byte chunks
-  static constexpr int kBoxCols = 32;
-  static __device__ __forceinline__ void stage32(uint8_t* slab, int lane, int c0, const float (&v)[32]) {
-    uint8_t* row = slab + (c0 >> 5) * 4096 + lane * 128;
-#pragma unroll
-    for (int q = 0; q < 8; ++q)
-      *reinterpret_cast<float4*>(row + ((q ^ (lane & 7)) << 4)) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-  }
-};
+using rb::gemm::Store;
 
 template <bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -582,6 +519,13 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
+// RECIS_GEMM_2CTA: unset = the kernel that pairs two SMs on a 256 x 256 tile takes the problems that fill the GPU with such
+// tiles, 1 = every problem of at least 192 x 192, 0 = never
+int pair_mode() {
+  static const int mode = [] { const char* e = std::getenv("RECIS_GEMM_2CTA"); return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0); }();
+  return mode;
+}
+
 bool persistent_enabled() {
   static const bool on = [] { const char* e = std::getenv("RECIS_GEMM_PERSISTENT"); return e != nullptr && e[0] == '1'; }();
   return on;
@@ -609,6 +553,20 @@ extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b,
   if (MM <= 0 || NN <= 0) return 0;
   // TMA constraints: 16-byte aligned base, row pitch a multiple of 16 bytes
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (lda % 8) || (ldb % 8)) return 1;
+  // Pairs of SMs on 256 x 256 tiles when that fills the GPU: at least 192 CTAs (a split reduction is cut finer to get there)
+  const int pmode = pair_mode();
+  if (pmode != 0 && MM >= 192 && NN >= 192) {
+    const int pairs = ((MM + 255) / 256) * ((NN + 255) / 256);
+    int psplits = 1;
+    if (splits > 1) {
+      const int total_kb = (KK + BK - 1) / BK;
+      psplits = std::max(1, std::min((256 + 2 * pairs - 1) / (2 * pairs), total_kb / 4));
+    }
+    if (pmode == 1 || 2 * pairs * psplits >= 192) {
+      const int rc = rb_gemm_bf16_pair(a, lda, a_mn, b, ldb, b_mn, out, ldo, out_fp32, bias, beta_src, MM, NN, KK, relu, psplits, status, st);
+      if (rc != 7) return rc;
+    }
+  }
   CUtensorMap ma, mb, mo;
   const bool oka = a_mn ? get_map(&ma, a, KK, MM, lda, 64, BK, false) : get_map(&ma, a, MM, KK, lda, BK, BM, false);
   const bool okb = b_mn ? get_map(&mb, b, KK, NN, ldb, 64, BK, false) : get_map(&mb, b, NN, KK, ldb, BK, BN, false);

@@ -354,3 +354,39 @@ def test_erased_index_slots_are_reused_by_inserts_of_distinct_ids():
     # 29 rounds erased 43,500 ids: without reuse and clean-up the index would hold as many tombstones (and would have doubled
     # several times); it keeps its size and the erased slots stay a fraction of it
     assert c[5] < 0.65 * slots0 and store.keys().numel() == slots0, (c[5], store.keys().numel())
+
+
+def test_debug_bounds_mode_rejects_bad_row_indices_before_the_kernel_runs():
+    """With RECIS_DEBUG_BOUNDS=1 the bindings of the row-indexing kernels validate their index tensors and raise; nothing reads
+    or writes outside its buffers. The switch is read once per process, so the check runs in a child."""
+    import subprocess
+    import sys
+    code = r"""
+import torch, recis_b200
+C = recis_b200.native()
+src = torch.arange(12, dtype=torch.float32).view(4, 3)
+ok = C.gather_rows(src, torch.tensor([0, -1, 3], dtype=torch.int32), None)
+assert ok[1].abs().sum() == 0 and torch.equal(ok[2], src[3])
+def raises(fn, what):
+    try:
+        fn()
+    except RuntimeError as e:
+        assert what in str(e), str(e)
+        return
+    raise AssertionError("no error for " + what)
+raises(lambda: C.gather_rows(src, torch.tensor([0, 4], dtype=torch.int32), None), "gather_rows: rows")
+raises(lambda: C.scatter_rows(src.clone(), torch.tensor([7], dtype=torch.int32), torch.zeros(1, 3), False), "scatter_rows: rows")
+# entries past the device-side count are not looked at
+n_dev = torch.tensor([1], dtype=torch.int32)
+C.gather_rows(src, torch.tensor([2, 99], dtype=torch.int32), n_dev)
+rev = torch.tensor([0, 1, 5], dtype=torch.int32)
+offs = torch.tensor([0, 2, 3], dtype=torch.int32)
+raises(lambda: C.pool_forward(src, torch.tensor([0, 1], dtype=torch.int32), rev, offs, None, 0, 0, 0, False, None, 0, 0), "pool_forward: reverse index")
+raises(lambda: C.pool_forward(src, torch.tensor([0, 9], dtype=torch.int32), torch.tensor([0, 1, 1], dtype=torch.int32), offs, None, 0, 0, 0, False,
+                              None, 0, 0), "pool_forward: table rows")
+print("ok")
+"""
+    import os
+    env = dict(os.environ, RECIS_DEBUG_BOUNDS="1")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stdout + out.stderr
