@@ -35,6 +35,19 @@ constexpr int kHead = 64;                  // head width (one 128-byte swizzle r
 constexpr int kBlk = kTile * 128;          // bytes of one [128 rows x 64 bf16] swizzled block
 constexpr uint32_t kTmemCols = 256;        // S: columns 0..127, PV: columns 128..191
 
+// 2^x on the special-function unit: one instruction, flushes denormals, 2^-inf = 0 (which is how masked entries become zero)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// two floats -> packed bf16x2 (round to nearest even), first argument in the low half
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
 // A [128 rows x 64 bf16] tile moves through registers in two steps, so that the loads of the next tile can be in flight while
 // the current one is being computed on: eight lanes read one row's eight 16-byte chunks (a warp-wide load covers four whole
 // rows), thread t holds chunk (t & 7) of rows (t >> 3) + 16 i. Rows at or past rows_valid read as zeros.
@@ -125,12 +138,12 @@ ragged_attention_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t
       uint32_t r[32];
       tmem_ld32(tmem + lane_base + (uint32_t)c0, r);
       tmem_ld_wait();
+      // masking is a select on the value (no branch per element); scale_log2 > 0, so the maximum can be taken before scaling
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (c0 + i < valid) mx = fmaxf(mx, __uint_as_float(r[i]) * scale_log2);
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c0 + i < valid) ? __uint_as_float(r[i]) : -INFINITY);
     }
-    const float m_new = fmaxf(m, mx);
-    const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+    const float m_new = fmaxf(m, mx * scale_log2);
+    const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
     float rowsum = 0.f;
     for (int c0 = 0; c0 < kTile; c0 += 32) {
       uint32_t r[32];
@@ -139,12 +152,12 @@ ragged_attention_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t
       uint32_t pk[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float p0 = (c0 + 2 * i < valid) ? exp2f(__uint_as_float(r[2 * i]) * scale_log2 - m_new) : 0.f;
-        const float p1 = (c0 + 2 * i + 1 < valid) ? exp2f(__uint_as_float(r[2 * i + 1]) * scale_log2 - m_new) : 0.f;
-        const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-        // the sum uses the rounded values, so that l matches what the tensor core multiplies with
-        rowsum += __bfloat162float(pb.x) + __bfloat162float(pb.y);
-        pk[i] = *reinterpret_cast<const uint32_t*>(&pb);
+        // a masked key enters as -inf and leaves as an exact zero
+        const float x0 = (c0 + 2 * i < valid) ? fmaf(__uint_as_float(r[2 * i]), scale_log2, -m_new) : -INFINITY;
+        const float x1 = (c0 + 2 * i + 1 < valid) ? fmaf(__uint_as_float(r[2 * i + 1]), scale_log2, -m_new) : -INFINITY;
+        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+        rowsum += p0 + p1;
+        pk[i] = pack_bf16x2(p0, p1);
       }
       uint8_t* blk = ptile + (c0 >> 6) * kBlk;
 #pragma unroll
@@ -330,13 +343,13 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int c = c0 + 2 * e + u;
-          const bool on = q_ok && c < valid_keys;
-          p[u] = on ? exp2f(__uint_as_float(rs[2 * e + u]) * scale_log2 - lse_q) : 0.f;
-          ds[u] = on ? p[u] * (__uint_as_float(rp[2 * e + u]) - delta_q) * scale : 0.f;
+          // a masked entry enters the exponential as -inf: P and dS are exact zeros there (dP and delta are finite)
+          const float x = (q_ok && c < valid_keys) ? fmaf(__uint_as_float(rs[2 * e + u]), scale_log2, -lse_q) : -INFINITY;
+          p[u] = fast_exp2(x);
+          ds[u] = p[u] * (__uint_as_float(rp[2 * e + u]) - delta_q) * scale;
         }
-        const __nv_bfloat162 pb = __floats2bfloat162_rn(p[0], p[1]), db = __floats2bfloat162_rn(ds[0], ds[1]);
-        pk[e] = *reinterpret_cast<const uint32_t*>(&pb);
-        dk[e] = *reinterpret_cast<const uint32_t*>(&db);
+        pk[e] = pack_bf16x2(p[0], p[1]);
+        dk[e] = pack_bf16x2(ds[0], ds[1]);
       }
       const uint32_t boff = (uint32_t)(c0 >> 6) * kBlk;
 #pragma unroll
