@@ -293,7 +293,7 @@ void init_dense(py::module& m) {
     const int64_t T = qkv.size(0), B = offsets.numel() - 1;
     auto out = torch::zeros({T, H * 64}, qkv.options());
     auto lse = torch::zeros({T, H}, qkv.options().dtype(torch::kFloat32));
-    const int rc = rb_ragged_attention_fwd(qkv.data_ptr(), offsets.data_ptr<int32_t>(), (int)B, (int)H, (int)max_len, (float)scale,
+    const int rc = rb_ragged_attention_fwd(qkv.data_ptr(), offsets.data_ptr<int32_t>(), T, (int)B, (int)H, (int)max_len, (float)scale,
                                            out.data_ptr(), lse.data_ptr<float>(), status_word(qkv.device()).data_ptr<int64_t>(),
                                            at::cuda::getCurrentCUDAStream());
     TORCH_CHECK(rc == 0, "ragged_attention_fwd failed (code ", rc, ")");

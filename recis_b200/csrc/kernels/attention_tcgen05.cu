@@ -4,8 +4,9 @@
 // sequence boundaries offsets [B + 1]; no padding exists anywhere. One CTA (128 threads) owns one (sequence, head, 128-query
 // tile) and walks the sequence's keys in tiles of 128 with the usual online softmax:
 //
-//   S  = Q K^T        tcgen05.mma, A = Q tile, B = K tile, both K-major, staged in shared memory in the 128-byte swizzle by
-//                     ordinary 16-byte stores (rows past the end of the sequence are zero); fp32 result in tensor memory
+//   S  = Q K^T        tcgen05.mma, A = Q tile, B = K tile, both K-major; the tiles arrive by TMA straight from the packed matrix
+//                     in the 128-byte swizzle (the next K tile as soon as S is complete, the next V tile as soon as P V is);
+//                     fp32 result in tensor memory
 //   P  = exp2(S * scale * log2 e - m)   each thread owns one query row: it reads its row of S back with tcgen05.ld, keeps the
 //                     running maximum m and sum l in registers and writes P (bf16) into shared memory as the next A operand
 //   PV = P V          tcgen05.mma, B = the V tile read as an MN-major operand (N = head column, K = key row)
@@ -17,7 +18,8 @@
 //
 // The reference has no attention kernel; its sequence example pads to the longest sequence and calls the library SDPA
 // (examples/seq2seq/transformer.py:36-38). Waits are bounded; a timeout sets the status word and the CTA frees its tensor
-// memory and returns. This kernel is opt-in (RECIS_ATTENTION=tcgen05) until it has been validated on hardware.
+// memory and returns. These kernels are what ops/attention.py runs on CUDA for head width 64 (RECIS_ATTENTION=padded selects
+// the padded library path).
 #include "../common/rb_common.cuh"
 #include "../common/rb_launch.h"
 #include "../common/rb_tcgen05.cuh"
@@ -48,25 +50,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
-// A [128 rows x 64 bf16] tile moves through registers in two steps, so that the loads of the next tile can be in flight while
-// the current one is being computed on: eight lanes read one row's eight 16-byte chunks (a warp-wide load covers four whole
-// rows), thread t holds chunk (t & 7) of rows (t >> 3) + 16 i. Rows at or past rows_valid read as zeros.
-__device__ __forceinline__ void tile_load(uint4 (&v)[8], const __nv_bfloat16* base, int64_t ld, int rows_valid, int t) {
-  const __nv_bfloat16* p = base + (int64_t)(t >> 3) * ld + (t & 7) * 8;
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-    v[i] = ((t >> 3) + 16 * i < rows_valid) ? __ldg(reinterpret_cast<const uint4*>(p + (int64_t)(16 * i) * ld)) : make_uint4(0u, 0u, 0u, 0u);
-}
-__device__ __forceinline__ void tile_store(uint8_t* blk, const uint4 (&v)[8], int t) {
-#pragma unroll
-  for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(blk + swizzle128_offset((t >> 3) + 16 * i, (t & 7) * 8)) = v[i];
-}
-
 __global__ void __launch_bounds__(128, 2)
-ragged_attention_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t* __restrict__ offsets, int H, float scale_log2,
+ragged_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const int32_t* __restrict__ offsets, int H, float scale_log2,
                             __nv_bfloat16* __restrict__ out, float* __restrict__ lse2, int64_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar_s, bar_o;
+  __shared__ __align__(8) uint64_t bar_q, bar_k, bar_v, bar_s, bar_o;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   const int b = blockIdx.y, h = blockIdx.z, qt = blockIdx.x;
@@ -79,18 +67,24 @@ ragged_attention_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t
   uint8_t* vtile = smem + 2 * kBlk;       // [128 keys][64 d]   MN-major B of PV (N = d, K = key)
   uint8_t* ptile = smem + 3 * kBlk;       // 2 x [128 q][64 keys] K-major A of PV
   const int t = threadIdx.x, warp = t >> 5;
-  const int64_t ld = (int64_t)3 * H * kHead;
-  if (t == 0) { abort_flag = 0; mbar_init(&bar_s, 1); mbar_init(&bar_o, 1); mbar_fence_init(); }
+  // Q, K and V tiles arrive by TMA straight from the packed [T, 3 * H * 64] matrix (box of 128 rows x 64 columns, 128-byte
+  // swizzle). Rows past the end of the sequence belong to the next sequence (or read as zeros past the end of the matrix):
+  // surplus query rows are computed and never stored, surplus keys are masked in the softmax, and the surplus rows of the V
+  // tile are zeroed in shared memory, so that a zero probability never meets a non-finite value.
+  const int xq = h * kHead, xk = (H + h) * kHead, xv = (2 * H + h) * kHead;
+  if (t == 0) {
+    abort_flag = 0;
+    mbar_init(&bar_q, 1); mbar_init(&bar_k, 1); mbar_init(&bar_v, 1); mbar_init(&bar_s, 1); mbar_init(&bar_o, 1);
+    mbar_fence_init();
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_qkv) : "memory");
+    mbar_expect_tx(&bar_q, kBlk); tma_load_2d(qtile, &map_qkv, xq, s0 + qt * kTile, &bar_q);
+    mbar_expect_tx(&bar_k, kBlk); tma_load_2d(ktile, &map_qkv, xk, s0, &bar_k);
+    mbar_expect_tx(&bar_v, kBlk); tma_load_2d(vtile, &map_qkv, xv, s0, &bar_v);
+  }
   if (warp == 0) tmem_alloc(&tmem_slot, kTmemCols);
 
   const int q = qt * kTile + t;
   const bool q_ok = q < L;
-  uint4 kreg[8], vreg[8];
-  tile_load(kreg, qkv + (int64_t)(s0 + qt * kTile) * ld + h * kHead, ld, L - qt * kTile, t);
-  tile_store(qtile, kreg, t);
-  tile_load(kreg, qkv + (int64_t)s0 * ld + (H + h) * kHead, ld, L, t);
-  tile_load(vreg, qkv + (int64_t)s0 * ld + (2 * H + h) * kHead, ld, L, t);
-
   float o[kHead];
 #pragma unroll
   for (int d = 0; d < kHead; ++d) o[d] = 0.f;
@@ -106,91 +100,111 @@ ragged_attention_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t
 
   const int n_kv = (L + kTile - 1) / kTile;
   for (int j = 0; j < n_kv && ok; ++j) {
-    // the previous step's MMAs have completed (bar_o), so the K and V tiles can be overwritten with what the registers hold
-    tile_store(ktile, kreg, t);
-    tile_store(vtile, vreg, t);
-    fence_smem_to_async();
-    fence_before_sync();
-    __syncthreads();
-    fence_after_sync();
+    const uint32_t ph = (uint32_t)(j & 1);
     if (t == 0) {
-      const uint32_t sq = smem_u32(qtile), sk = smem_u32(ktile);
+      bool got = (j > 0 || mbar_wait(&bar_q, 0, &abort_flag)) && mbar_wait(&bar_k, ph, &abort_flag);
+      if (got) {
+        fence_after_sync();
+        const uint32_t sq = smem_u32(qtile), sk = smem_u32(ktile);
 #pragma unroll
-      for (int k = 0; k < kHead / 16; ++k)
-        umma_bf16(tmem, make_desc(sq + k * 32, 16, 1024), make_desc(sk + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
-      umma_commit(&bar_s);
-    }
-    if (j + 1 < n_kv) {
-      // the next tile's loads travel while this tile's softmax and MMAs run
-      const int64_t row0 = s0 + (j + 1) * kTile;
-      tile_load(kreg, qkv + row0 * ld + (H + h) * kHead, ld, L - (j + 1) * kTile, t);
-      tile_load(vreg, qkv + row0 * ld + (2 * H + h) * kHead, ld, L - (j + 1) * kTile, t);
+        for (int k = 0; k < kHead / 16; ++k)
+          umma_bf16(tmem, make_desc(sq + k * 32, 16, 1024), make_desc(sk + k * 32, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+        umma_commit(&bar_s);
+      }
     }
     // the outcome of a bounded wait is made uniform for the CTA: every thread takes the same path through the barriers below
-    ok = __syncthreads_and(mbar_wait(&bar_s, (uint32_t)(j & 1), &abort_flag) ? 1 : 0) != 0;
+    ok = __syncthreads_and(mbar_wait(&bar_s, ph, &abort_flag) ? 1 : 0) != 0;
     fence_after_sync();
     if (!ok) break;
+    // S is complete, so the K tile is free: the next one travels while this tile's softmax and P V run
+    if (t == 0 && j + 1 < n_kv) { mbar_expect_tx(&bar_k, kBlk); tma_load_2d(ktile, &map_qkv, xk, s0 + (j + 1) * kTile, &bar_k); }
 
-    // ---- online softmax on this thread's row of S
+    // ---- online softmax on this thread's row of S (two 32-column reads of tensor memory in flight at a time)
     const int valid = min(kTile, L - j * kTile);                 // key columns of this tile that exist
     float mx = -INFINITY;
-    for (int c0 = 0; c0 < kTile; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(tmem + lane_base + (uint32_t)c0, r);
+#pragma unroll
+    for (int c0 = 0; c0 < kTile; c0 += 64) {
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tmem + lane_base + (uint32_t)c0, r0);
+      tmem_ld32(tmem + lane_base + (uint32_t)c0 + 32u, r1);
       tmem_ld_wait();
       // masking is a select on the value (no branch per element); scale_log2 > 0, so the maximum can be taken before scaling
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c0 + i < valid) ? __uint_as_float(r[i]) : -INFINITY);
+      for (int i = 0; i < 32; ++i) {
+        mx = fmaxf(mx, (c0 + i < valid) ? __uint_as_float(r0[i]) : -INFINITY);
+        mx = fmaxf(mx, (c0 + 32 + i < valid) ? __uint_as_float(r1[i]) : -INFINITY);
+      }
     }
     const float m_new = fmaxf(m, mx * scale_log2);
     const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
     float rowsum = 0.f;
-    for (int c0 = 0; c0 < kTile; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(tmem + lane_base + (uint32_t)c0, r);
-      tmem_ld_wait();
-      uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        // a masked key enters as -inf and leaves as an exact zero
-        const float x0 = (c0 + 2 * i < valid) ? fmaf(__uint_as_float(r[2 * i]), scale_log2, -m_new) : -INFINITY;
-        const float x1 = (c0 + 2 * i + 1 < valid) ? fmaf(__uint_as_float(r[2 * i + 1]), scale_log2, -m_new) : -INFINITY;
-        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-        rowsum += p0 + p1;
-        pk[i] = pack_bf16x2(p0, p1);
-      }
+    for (int c0 = 0; c0 < kTile; c0 += 64) {
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tmem + lane_base + (uint32_t)c0, r0);
+      tmem_ld32(tmem + lane_base + (uint32_t)c0 + 32u, r1);
+      tmem_ld_wait();
       uint8_t* blk = ptile + (c0 >> 6) * kBlk;
 #pragma unroll
-      for (int cq = 0; cq < 4; ++cq)
-        *reinterpret_cast<uint4*>(blk + swizzle128_offset(t, (c0 & 63) + cq * 8)) =
-            make_uint4(pk[cq * 4], pk[cq * 4 + 1], pk[cq * 4 + 2], pk[cq * 4 + 3]);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          // a masked key enters as -inf and leaves as an exact zero
+          const int c = c0 + half * 32 + 2 * i;
+          const float s_a = __uint_as_float(half ? r1[2 * i] : r0[2 * i]), s_b = __uint_as_float(half ? r1[2 * i + 1] : r0[2 * i + 1]);
+          const float p0 = fast_exp2((c < valid) ? fmaf(s_a, scale_log2, -m_new) : -INFINITY);
+          const float p1 = fast_exp2((c + 1 < valid) ? fmaf(s_b, scale_log2, -m_new) : -INFINITY);
+          rowsum += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+#pragma unroll
+        for (int cq = 0; cq < 4; ++cq)
+          *reinterpret_cast<uint4*>(blk + swizzle128_offset(t, half * 32 + cq * 8)) =
+              make_uint4(pk[cq * 4], pk[cq * 4 + 1], pk[cq * 4 + 2], pk[cq * 4 + 3]);
+      }
     }
     l = l * alpha + rowsum;
     m = m_new;
 #pragma unroll
     for (int d = 0; d < kHead; ++d) o[d] *= alpha;
 
+    if (valid < kTile) {
+      // last, partial tile: the V rows past the end of the sequence become zeros (this thread's row, once V has landed)
+      ok = mbar_wait(&bar_v, ph, &abort_flag);
+      if (ok && t >= valid) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(vtile + swizzle128_offset(t, c * 8)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
     fence_smem_to_async();
     fence_before_sync();
-    __syncthreads();
-    fence_after_sync();
-    if (t == 0) {
-      const uint32_t sp = smem_u32(ptile), sv = smem_u32(vtile);
-#pragma unroll
-      for (int k = 0; k < kTile / 16; ++k)
-        umma_bf16(tmem + 128u, make_desc(sp + (k >> 2) * kBlk + (k & 3) * 32, 16, 1024), make_desc(sv + k * 2048, kBlk, 1024), idesc_o,
-                  k > 0 ? 1u : 0u);
-      umma_commit(&bar_o);
-    }
-    ok = __syncthreads_and(mbar_wait(&bar_o, (uint32_t)(j & 1), &abort_flag) ? 1 : 0) != 0;
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
     fence_after_sync();
     if (!ok) break;
-    for (int c0 = 0; c0 < kHead; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(tmem + lane_base + 128u + (uint32_t)c0, r);
+    if (t == 0) {
+      if (mbar_wait(&bar_v, ph, &abort_flag)) {
+        fence_after_sync();
+        const uint32_t sp = smem_u32(ptile), sv = smem_u32(vtile);
+#pragma unroll
+        for (int k = 0; k < kTile / 16; ++k)
+          umma_bf16(tmem + 128u, make_desc(sp + (k >> 2) * kBlk + (k & 3) * 32, 16, 1024), make_desc(sv + k * 2048, kBlk, 1024), idesc_o,
+                    k > 0 ? 1u : 0u);
+        umma_commit(&bar_o);
+      }
+    }
+    ok = __syncthreads_and(mbar_wait(&bar_o, ph, &abort_flag) ? 1 : 0) != 0;
+    fence_after_sync();
+    if (!ok) break;
+    // P V is complete, so the V tile is free
+    if (t == 0 && j + 1 < n_kv) { mbar_expect_tx(&bar_v, kBlk); tma_load_2d(vtile, &map_qkv, xv, s0 + (j + 1) * kTile, &bar_v); }
+    {
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tmem + lane_base + 128u, r0);
+      tmem_ld32(tmem + lane_base + 160u, r1);
       tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(r[i]);
+      for (int i = 0; i < 32; ++i) { o[i] += __uint_as_float(r0[i]); o[32 + i] += __uint_as_float(r1[i]); }
     }
   }
 
@@ -198,16 +212,14 @@ ragged_attention_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t
     const float inv = l > 0.f ? 1.f / l : 0.f;
     __nv_bfloat16* dst = out + (int64_t)(s0 + q) * H * kHead + h * kHead;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      uint32_t w[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const __nv_bfloat162 v = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
-        w[i] = *reinterpret_cast<const uint32_t*>(&v);
-      }
-      reinterpret_cast<uint4*>(dst)[c] = make_uint4(w[0], w[1], w[2], w[3]);
-    }
+    for (int c = 0; c < 8; ++c)
+      reinterpret_cast<uint4*>(dst)[c] = make_uint4(pack_bf16x2(o[c * 8] * inv, o[c * 8 + 1] * inv), pack_bf16x2(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv),
+                                                    pack_bf16x2(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv), pack_bf16x2(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv));
     if (lse2) lse2[(int64_t)(s0 + q) * H + h] = m + log2f(l);
+  }
+  if (abort_flag) {
+    // a wait ran out: a copy may still be on its way into shared memory; give it time before the memory goes away
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
   fence_before_sync();
   __syncthreads();
@@ -244,12 +256,12 @@ attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
 constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 320, kColDQ = 384;
 
 __global__ void __launch_bounds__(128, 1)
-ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ d_o, const float* __restrict__ lse2,
-                            const float* __restrict__ delta, const int32_t* __restrict__ offsets, int H, float scale, float scale_log2,
-                            float* __restrict__ dqkv, const __grid_constant__ CUtensorMap map_dq, int dq_tma,
+ragged_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do,
+                            const float* __restrict__ lse2, const float* __restrict__ delta, const int32_t* __restrict__ offsets, int H,
+                            float scale, float scale_log2, float* __restrict__ dqkv, const __grid_constant__ CUtensorMap map_dq, int dq_tma,
                             int64_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bar1, bar2;
+  __shared__ __align__(8) uint64_t bar1, bar2, bar_kv, bar_in[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   const int b = blockIdx.y, h = blockIdx.z, kt = blockIdx.x;
@@ -259,73 +271,106 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* ktile = smem;                   // [128 keys][64 d]
   uint8_t* vtile = smem + kBlk;            // [128 keys][64 d]
-  uint8_t* qtile = smem + 2 * kBlk;        // [128 q][64 d]
-  uint8_t* dotile = smem + 3 * kBlk;       // [128 q][64 d]
-  uint8_t* ptile = smem + 4 * kBlk;        // 2 x [128 q][64 keys]
-  uint8_t* dstile = smem + 6 * kBlk;       // 2 x [128 q][64 keys]
-  uint8_t* dqstage = smem + 8 * kBlk;      // 2 x [128 q][32 d] fp32: the dQ tile on its way out (two 128-byte-wide boxes)
+  uint8_t* qtiles = smem + 2 * kBlk;       // 2 x [128 q][64 d]: this step's tile and the next one's, arriving
+  uint8_t* dotiles = smem + 4 * kBlk;      // 2 x [128 q][64 d]
+  uint8_t* ptile = smem + 6 * kBlk;        // 2 x [128 q][64 keys]
+  uint8_t* dstile = smem + 8 * kBlk;       // 2 x [128 q][64 keys]
+  uint8_t* dqstage = smem + 10 * kBlk;     // 2 x [128 q][32 d] fp32: the dQ tile on its way out (two 128-byte-wide boxes)
   const int t = threadIdx.x, warp = t >> 5;
   const int64_t ld = (int64_t)3 * H * kHead;
-  if (t == 0) { abort_flag = 0; mbar_init(&bar1, 1); mbar_init(&bar2, 1); mbar_fence_init(); }
+  // All tiles arrive by TMA (boxes of 128 rows x 64 columns of the packed matrices, 128-byte swizzle). Rows past the end of the
+  // sequence belong to the next sequence: every such key and query is masked in P and dS below, and the surplus rows of the
+  // tiles are zeroed in shared memory, so that the zeros of P and dS never meet a non-finite value.
+  const int xq = h * kHead, xk = (H + h) * kHead, xv = (2 * H + h) * kHead;
+  if (t == 0) {
+    abort_flag = 0;
+    mbar_init(&bar1, 1); mbar_init(&bar2, 1); mbar_init(&bar_kv, 1); mbar_init(&bar_in[0], 1); mbar_init(&bar_in[1], 1);
+    mbar_fence_init();
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_qkv) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_do) : "memory");
+    mbar_expect_tx(&bar_kv, 2 * kBlk);
+    tma_load_2d(ktile, &map_qkv, xk, s0 + kt * kTile, &bar_kv);
+    tma_load_2d(vtile, &map_qkv, xv, s0 + kt * kTile, &bar_kv);
+    mbar_expect_tx(&bar_in[0], 2 * kBlk);
+    tma_load_2d(qtiles, &map_qkv, xq, s0, &bar_in[0]);
+    tma_load_2d(dotiles, &map_do, xq, s0, &bar_in[0]);
+  }
   if (warp == 0) tmem_alloc(&tmem_slot, 512);
 
   const int key = kt * kTile + t;
   const bool key_ok = key < L;
-  uint4 qreg[8], dreg[8];
-  {
-    const int64_t row0 = s0 + kt * kTile;
-    tile_load(qreg, qkv + row0 * ld + (H + h) * kHead, ld, L - kt * kTile, t);
-    tile_load(dreg, qkv + row0 * ld + (2 * H + h) * kHead, ld, L - kt * kTile, t);
-    tile_store(ktile, qreg, t);
-    tile_store(vtile, dreg, t);
-  }
-  // the first query tile's rows, its softmax statistics and correction terms
-  tile_load(qreg, qkv + (int64_t)s0 * ld + h * kHead, ld, L, t);
-  tile_load(dreg, d_o + (int64_t)s0 * H * kHead + h * kHead, (int64_t)H * kHead, L, t);
+  const int valid_keys = min(kTile, L - kt * kTile);
+  // the first query tile's softmax statistics and correction terms
   float lse_next = t < L ? lse2[(int64_t)(s0 + t) * H + h] : 0.f;
   float delta_next = t < L ? delta[(int64_t)(s0 + t) * H + h] : 0.f;
+  bool ok = mbar_wait(&bar_kv, 0, &abort_flag);
+  if (ok && !key_ok) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      *reinterpret_cast<uint4*>(ktile + swizzle128_offset(t, c * 8)) = make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(vtile + swizzle128_offset(t, c * 8)) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  fence_smem_to_async();
   fence_before_sync();
-  __syncthreads();
+  ok = __syncthreads_and(ok ? 1 : 0) != 0;
   fence_after_sync();
   const uint32_t tmem = tmem_slot;
   const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
   const uint32_t idesc_kk = make_idesc_bf16(kTile, kTile, false, false);    // S, dP: both operands K-major
   const uint32_t idesc_mm = make_idesc_bf16(kTile, kHead, true, true);      // dV, dK: both operands MN-major
   const uint32_t idesc_km = make_idesc_bf16(kTile, kHead, false, true);     // dQ: A K-major, B MN-major
-  const int valid_keys = min(kTile, L - kt * kTile);
-  bool ok = true;
 
   const int n_q = (L + kTile - 1) / kTile;
   for (int i = 0; i < n_q && ok; ++i) {
     const int q = i * kTile + t;
     const bool q_ok = q < L;
     const int64_t tok = s0 + q;
-    // the previous step's MMAs have completed (bar2) and its dQ tile has been read by the copy engine (thread 0 waited below)
-    tile_store(qtile, qreg, t);
-    tile_store(dotile, dreg, t);
+    const int buf = i & 1;
+    const uint32_t ph_in = (uint32_t)(i >> 1) & 1u;
+    uint8_t* qtile = qtiles + buf * kBlk;
+    uint8_t* dotile = dotiles + buf * kBlk;
     const float lse_q = lse_next, delta_q = delta_next;
-    fence_smem_to_async();
-    fence_before_sync();
-    __syncthreads();
-    fence_after_sync();
-    if (t == 0) {
-      const uint32_t sq = smem_u32(qtile), sk = smem_u32(ktile), sdo = smem_u32(dotile), sv = smem_u32(vtile);
-#pragma unroll
-      for (int k = 0; k < kHead / 16; ++k)
-        umma_bf16(tmem + kColS, make_desc(sq + k * 32, 16, 1024), make_desc(sk + k * 32, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
-#pragma unroll
-      for (int k = 0; k < kHead / 16; ++k)
-        umma_bf16(tmem + kColDP, make_desc(sdo + k * 32, 16, 1024), make_desc(sv + k * 32, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
-      umma_commit(&bar1);
-    }
     if (i + 1 < n_q) {
-      // the next query tile's loads travel while this tile is being computed
+      // the next query tile travels while this one is computed; its buffer was last read by the MMAs of step i - 1 (bar2)
       const int64_t row0 = s0 + (i + 1) * kTile;
       const int left = L - (i + 1) * kTile;
-      tile_load(qreg, qkv + row0 * ld + h * kHead, ld, left, t);
-      tile_load(dreg, d_o + row0 * H * kHead + h * kHead, (int64_t)H * kHead, left, t);
+      if (t == 0) {
+        mbar_expect_tx(&bar_in[buf ^ 1], 2 * kBlk);
+        tma_load_2d(qtiles + (buf ^ 1) * kBlk, &map_qkv, xq, (int)row0, &bar_in[buf ^ 1]);
+        tma_load_2d(dotiles + (buf ^ 1) * kBlk, &map_do, xq, (int)row0, &bar_in[buf ^ 1]);
+      }
       lse_next = t < left ? lse2[(row0 + t) * H + h] : 0.f;
       delta_next = t < left ? delta[(row0 + t) * H + h] : 0.f;
+    }
+    if (L - i * kTile < kTile) {
+      // last, partial query tile: its surplus rows become zeros (this thread's row, once the tile has landed)
+      ok = mbar_wait(&bar_in[buf], ph_in, &abort_flag);
+      if (ok && !q_ok) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          *reinterpret_cast<uint4*>(qtile + swizzle128_offset(t, c * 8)) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(dotile + swizzle128_offset(t, c * 8)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      fence_smem_to_async();
+      fence_before_sync();
+      ok = __syncthreads_and(ok ? 1 : 0) != 0;
+      fence_after_sync();
+      if (!ok) break;
+    }
+    if (t == 0) {
+      if (mbar_wait(&bar_in[buf], ph_in, &abort_flag)) {
+        fence_after_sync();
+        const uint32_t sq = smem_u32(qtile), sk = smem_u32(ktile), sdo = smem_u32(dotile), sv = smem_u32(vtile);
+#pragma unroll
+        for (int k = 0; k < kHead / 16; ++k)
+          umma_bf16(tmem + kColS, make_desc(sq + k * 32, 16, 1024), make_desc(sk + k * 32, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < kHead / 16; ++k)
+          umma_bf16(tmem + kColDP, make_desc(sdo + k * 32, 16, 1024), make_desc(sv + k * 32, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
+        umma_commit(&bar1);
+      }
     }
     ok = __syncthreads_and(mbar_wait(&bar1, (uint32_t)(i & 1), &abort_flag) ? 1 : 0) != 0;
     fence_after_sync();
@@ -419,6 +464,10 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
     }
   }
   if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the copies that read it
+  if (abort_flag) {
+    // a wait ran out: a tile may still be on its way into shared memory; give it time before the memory goes away
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
 
   if (ok) {
     for (int c0 = 0; c0 < kHead; c0 += 32) {
@@ -447,13 +496,15 @@ ragged_attention_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bf
 
 }  // namespace
 
-// qkv: bf16 [T, 3 * H * 64] packed (q | k | v, each H heads of 64), offsets: int32 [B + 1] on the device, max_len: an upper bound
+// qkv: bf16 [T, 3 * H * 64] packed (q | k | v, each H heads of 64), T tokens, offsets: int32 [B + 1] on the device, max_len: an upper bound
 // of the sequence lengths (sizes the grid), out: bf16 [T, H * 64], lse2: fp32 [T, H] or null (log2-domain log-sum-exp).
 // Returns 0 on launch, 1 when the arguments are outside the kernel's range (alignment), > 1 on a launch error.
-extern "C" int rb_ragged_attention_fwd(const void* qkv, const int32_t* offsets, int B, int H, int max_len, float scale, void* out, float* lse2,
-                                       int64_t* status, cudaStream_t st) {
-  if (B <= 0 || H <= 0 || max_len <= 0) return 0;
+extern "C" int rb_ragged_attention_fwd(const void* qkv, const int32_t* offsets, int64_t T, int B, int H, int max_len, float scale, void* out,
+                                       float* lse2, int64_t* status, cudaStream_t st) {
+  if (B <= 0 || H <= 0 || max_len <= 0 || T <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return 1;
+  CUtensorMap map_qkv;
+  if (rb_tensor_map_2d(&map_qkv, qkv, T, (int64_t)3 * H * kHead, (int64_t)3 * H * kHead, kHead, kTile, 0) != 0) return 1;
   const size_t smem = 1024 + 5 * (size_t)kBlk;
   static bool attr = false;
   if (!attr) {
@@ -461,7 +512,7 @@ extern "C" int rb_ragged_attention_fwd(const void* qkv, const int32_t* offsets, 
     attr = true;
   }
   dim3 grid((max_len + kTile - 1) / kTile, B, H);
-  ragged_attention_fwd_kernel<<<grid, 128, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(qkv), offsets, H, scale * 1.4426950408889634f,
+  ragged_attention_fwd_kernel<<<grid, 128, smem, st>>>(map_qkv, offsets, H, scale * 1.4426950408889634f,
                                                        reinterpret_cast<__nv_bfloat16*>(out), lse2, status);
   rb::note_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
@@ -481,7 +532,11 @@ extern "C" int rb_ragged_attention_bwd(const void* qkv, const void* out, const v
   attention_delta_kernel<<<(int)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(out),
                                                                                    reinterpret_cast<const __nv_bfloat16*>(d_out), rows, delta);
   rb::note_launch();
-  const size_t smem = 1024 + 10 * (size_t)kBlk;
+  const size_t smem = 1024 + 12 * (size_t)kBlk;
+  CUtensorMap map_qkv, map_do;
+  if (rb_tensor_map_2d(&map_qkv, qkv, T, (int64_t)3 * H * kHead, (int64_t)3 * H * kHead, kHead, kTile, 0) != 0 ||
+      rb_tensor_map_2d(&map_do, d_out, T, (int64_t)H * kHead, (int64_t)H * kHead, kHead, kTile, 0) != 0)
+    return 1;
   // dQ leaves as TMA add-reductions of [128 x 32] fp32 boxes when a tensor map can be made; otherwise as per-row reductions
   CUtensorMap map_dq;
   const int dq_tma = rb_tensor_map_2d(&map_dq, dqkv, T, (int64_t)3 * H * kHead, (int64_t)3 * H * kHead, 32, kTile, 1) == 0 ? 1 : 0;
@@ -492,8 +547,8 @@ extern "C" int rb_ragged_attention_bwd(const void* qkv, const void* out, const v
     attr = true;
   }
   dim3 grid((max_len + kTile - 1) / kTile, B, H);
-  ragged_attention_bwd_kernel<<<grid, 128, smem, st>>>(reinterpret_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const __nv_bfloat16*>(d_out),
-                                                       lse2, delta, offsets, H, scale, scale * 1.4426950408889634f, dqkv, map_dq, dq_tma, status);
+  ragged_attention_bwd_kernel<<<grid, 128, smem, st>>>(map_qkv, map_do, lse2, delta, offsets, H, scale, scale * 1.4426950408889634f, dqkv,
+                                                       map_dq, dq_tma, status);
   rb::note_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }

@@ -45,8 +45,8 @@ int rb_dot_interaction_tc_bwd(const void* x, const float* cube, const void* dout
                               float* dcube, int64_t* status, cudaStream_t st);
 // Ragged multi-head self-attention forward, head width 64 (attention_tcgen05.cu). qkv: bf16 [T, 3 * H * 64] packed, offsets:
 // int32 [B + 1] (device), out: bf16 [T, H * 64], lse2: fp32 [T, H] or null. 0 = launched, 1 = unsuitable arguments, > 1 = error.
-int rb_ragged_attention_fwd(const void* qkv, const int32_t* offsets, int B, int H, int max_len, float scale, void* out, float* lse2,
-                            int64_t* status, cudaStream_t st);
+int rb_ragged_attention_fwd(const void* qkv, const int32_t* offsets, int64_t T, int B, int H, int max_len, float scale, void* out,
+                            float* lse2, int64_t* status, cudaStream_t st);
 // Backward: out / d_out bf16 [T, H * 64], lse2 from the forward, delta fp32 [T, H] scratch, dqkv fp32 [T, 3 * H * 64] zeroed.
 int rb_ragged_attention_bwd(const void* qkv, const void* out, const void* d_out, const float* lse2, float* delta, const int32_t* offsets,
                             int64_t T, int B, int H, int max_len, float scale, float* dqkv, int64_t* status, cudaStream_t st);
