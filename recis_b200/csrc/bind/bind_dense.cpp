@@ -156,6 +156,29 @@ std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_forward(const T
   return {x, ys, wbs};
 }
 
+// (dx bf16 [M, K], column sums of dx fp32 [K]) with dx = (dy [M, N] . W [N, K]) set to zero where mask [M, K] <= 0: the input gradient
+// of a layer, already passed through the ReLU of the layer below, and that layer's bias gradient, all in the GEMM's epilogue.
+std::tuple<Tensor, Tensor> gemm_dgrad_fused(const Tensor& dy, const Tensor& w, OptT mask) {
+  TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16 && dy.dim() == 2 && w.dim() == 2 &&
+              dy.stride(1) == 1 && w.stride(1) == 1 && dy.size(1) == w.size(0), "bf16 dy [M, N] and W [N, K] expected");
+  const int64_t MM = dy.size(0), KK = dy.size(1), NN = w.size(1);
+  c10::cuda::CUDAGuard g(dy.device());
+  auto out = torch::empty({MM, NN}, dy.options());
+  auto db = torch::zeros({NN}, dy.options().dtype(torch::kFloat32));
+  RbGemmEpilogue epi{nullptr, 0, db.data_ptr<float>()};
+  if (mask.has_value() && mask->defined()) {
+    TORCH_CHECK(mask->scalar_type() == torch::kBFloat16 && mask->dim() == 2 && mask->stride(1) == 1 && mask->size(0) == MM && mask->size(1) == NN,
+                "mask: bf16 [M, K]");
+    epi.mask_src = mask->data_ptr();
+    epi.mask_ld = mask->stride(0);
+  }
+  Tensor& st = status_word(dy.device());
+  const int rc = rb_gemm_bf16_ex(dy.data_ptr(), dy.stride(0), 0, w.data_ptr(), w.stride(0), 1, out.data_ptr(), out.stride(0), 0, nullptr, nullptr,
+                                 &epi, (int)MM, (int)NN, (int)KK, 0, 1, st.data_ptr<int64_t>(), at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(rc == 0, "rb_gemm_bf16_ex failed with code ", rc);
+  return {out, db};
+}
+
 // Whole MLP backward in one call. dout: bf16 [M, pad8(N_last)]. Returns (dx or undefined, weight grads fp32 [N, K], bias grads fp32 [N]).
 std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_backward(const Tensor& dout_in, const Tensor& x, const std::vector<Tensor>& ys,
                                                                           const std::vector<Tensor>& wbs, const std::vector<bool>& relu,
@@ -165,15 +188,20 @@ std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_backward(const 
   std::vector<Tensor> dws(L), dbs(L);
   Tensor dout = dout_in.contiguous();
   Tensor dx;
+  // The last layer's pre-activation gradient comes from one element-wise kernel; below it, every layer's comes out of the GEMM
+  // above it: dy_{l-1} = (dy_l W_l) with the ReLU mask of y_{l-1} applied and its column sums (the bias gradient) taken in the
+  // epilogue, so a layer costs two GEMMs and nothing else.
+  Tensor dy, db;
+  std::tie(dy, db) = relu_bwd_bias(ys[L - 1], dout, relu[L - 1]);
   for (int l = L - 1; l >= 0; --l) {
-    auto [dy, db] = relu_bwd_bias(ys[l], dout, relu[l]);
     const Tensor& h_in = l == 0 ? x : ys[l - 1];
     Tensor dw = gemm_bf16(dy, h_in, c10::nullopt, false, true, true, true, c10::nullopt);   // dy^T . h  (both MN-major, split-K)
     dws[l] = dw.narrow(0, 0, shapes[l][0]).narrow(1, 0, shapes[l][1]);
     dbs[l] = db.narrow(0, 0, shapes[l][0]);
-    if (l > 0 || need_dx) {
-      dout = gemm_bf16(dy, wbs[l], c10::nullopt, false, false, true, false, c10::nullopt);    // dy . W  (W read MN-major)
-      if (l == 0) dx = dout;
+    if (l > 0) {
+      std::tie(dy, db) = gemm_dgrad_fused(dy, wbs[l], relu[l - 1] ? c10::optional<Tensor>(ys[l - 1]) : c10::nullopt);
+    } else if (need_dx) {
+      dx = gemm_bf16(dy, wbs[0], c10::nullopt, false, false, true, false, c10::nullopt);    // dy . W  (W read MN-major)
     }
   }
   return {dx, dws, dbs};
@@ -272,6 +300,7 @@ void init_dense(py::module& m) {
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none());
   m.def("dense_status", &dense_status);
   m.def("gemm_bf16_residual", &gemm_bf16_residual);
+  m.def("gemm_dgrad_fused", &gemm_dgrad_fused);
   m.def("layer_norm_fwd", &layer_norm_fwd);
   m.def("layer_norm_bwd", &layer_norm_bwd);
   m.def("target_attention_fwd", &target_attention_fwd);

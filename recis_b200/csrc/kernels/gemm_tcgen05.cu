@@ -50,7 +50,7 @@ template <bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_o, int tma_out, OutT* __restrict__ out,
-                         const float* __restrict__ bias, const float* __restrict__ beta_src,
+                         const float* __restrict__ bias, const float* __restrict__ beta_src, const RbGemmEpilogue epi,
                          int MM, int NN, int KK, int ldo, int relu, int64_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
@@ -188,10 +188,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           v[j4 + 0] = relu ? fmaxf(x0, 0.f) : x0; v[j4 + 1] = relu ? fmaxf(x1, 0.f) : x1;
           v[j4 + 2] = relu ? fmaxf(x2, 0.f) : x2; v[j4 + 3] = relu ? fmaxf(x3, 0.f) : x3;
         }
+        if (epi.mask_src != nullptr)
+          rb::gemm::apply_mask32(v, reinterpret_cast<const __nv_bfloat16*>(epi.mask_src) + (int64_t)row * epi.mask_ld + n0 + c0, valid, row < MM);
         if (tma_out) Store<OutT>::stage32(slab, lane, c0, v);
         else if (row < MM) {
           if (split) Store<OutT>::red32(out + (int64_t)row * ldo + n0 + c0, v, valid, vec_ok);
           else Store<OutT>::row32(out + (int64_t)row * ldo + n0 + c0, v, valid, vec_ok);
+        }
+        if (epi.colsum != nullptr) {
+          if (row >= MM) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
+          rb::gemm::column_sums32(v, lane, valid, epi.colsum + n0 + c0);
         }
       }
       if (tma_out) {
@@ -489,7 +498,7 @@ bool get_map(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int
 
 template <bool A_MN, bool B_MN, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, int tma_out, void* out, const float* bias, const float* beta_src,
-           int MM, int NN, int KK, int ldo, int relu, int splits, int64_t* status, cudaStream_t st) {
+           const RbGemmEpilogue& epi, int MM, int NN, int KK, int ldo, int relu, int splits, int64_t* status, cudaStream_t st) {
   auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -497,7 +506,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, 
     attr_set = true;
   }
   dim3 grid((NN + BN - 1) / BN, (MM + BM - 1) / BM, splits);
-  kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, mo, tma_out, reinterpret_cast<OutT*>(out), bias, beta_src, MM, NN, KK, ldo, relu, status);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, mo, tma_out, reinterpret_cast<OutT*>(out), bias, beta_src, epi, MM, NN, KK, ldo, relu, status);
   rb::note_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
@@ -550,6 +559,16 @@ extern "C" int rb_gemm_splits(int MM, int NN, int KK) {
 extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo,
                             int out_fp32, const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int splits,
                             int64_t* status, cudaStream_t st) {
+  return rb_gemm_bf16_ex(a, lda, a_mn, b, ldb, b_mn, out, ldo, out_fp32, bias, beta_src, nullptr, MM, NN, KK, relu, splits, status, st);
+}
+
+extern "C" int rb_gemm_bf16_ex(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo,
+                               int out_fp32, const float* bias, const float* beta_src, const RbGemmEpilogue* epi_in, int MM, int NN, int KK,
+                               int relu, int splits, int64_t* status, cudaStream_t st) {
+  RbGemmEpilogue epi{nullptr, 0, nullptr};
+  if (epi_in != nullptr) epi = *epi_in;
+  const bool extra = epi.mask_src != nullptr || epi.colsum != nullptr;
+  if (extra && splits > 1) return 6;                 // a mask or column sums need the whole reduction in one CTA
   if (MM <= 0 || NN <= 0) return 0;
   // TMA constraints: 16-byte aligned base, row pitch a multiple of 16 bytes
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (lda % 8) || (ldb % 8)) return 1;
@@ -563,7 +582,7 @@ extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b,
       psplits = std::max(1, std::min((256 + 2 * pairs - 1) / (2 * pairs), total_kb / 4));
     }
     if (pmode == 1 || 2 * pairs * psplits >= 192) {
-      const int rc = rb_gemm_bf16_pair(a, lda, a_mn, b, ldb, b_mn, out, ldo, out_fp32, bias, beta_src, MM, NN, KK, relu, psplits, status, st);
+      const int rc = rb_gemm_bf16_pair(a, lda, a_mn, b, ldb, b_mn, out, ldo, out_fp32, bias, beta_src, &epi, MM, NN, KK, relu, psplits, status, st);
       if (rc != 7) return rc;
     }
   }
@@ -579,7 +598,7 @@ extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b,
   else
     mo = ma;
   if (splits > 1 && (!out_fp32 || relu)) return 6;   // partial tiles are accumulated with fp32 reductions into a zeroed output
-  if (persistent_enabled() && tma_out && splits <= 1 && KK > 0) {
+  if (persistent_enabled() && tma_out && splits <= 1 && KK > 0 && !extra) {
 #define RB_GEMM_PCASE(AM, BMJ)                                                                                                  \
   if ((a_mn != 0) == AM && (b_mn != 0) == BMJ)                                                                                  \
     return out_fp32 ? launch_persistent<AM, BMJ, float>(ma, mb, mo, bias, beta_src, MM, NN, KK, (int)ldo, relu, status, st)             \
@@ -592,8 +611,8 @@ extern "C" int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b,
   }
 #define RB_GEMM_CASE(AM, BMJ)                                                                                                   \
   if ((a_mn != 0) == AM && (b_mn != 0) == BMJ)                                                                                  \
-    return out_fp32 ? launch<AM, BMJ, float>(ma, mb, mo, tma_out, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, splits, status, st)  \
-                    : launch<AM, BMJ, __nv_bfloat16>(ma, mb, mo, tma_out, out, bias, beta_src, MM, NN, KK, (int)ldo, relu, 1, status, st);
+    return out_fp32 ? launch<AM, BMJ, float>(ma, mb, mo, tma_out, out, bias, beta_src, epi, MM, NN, KK, (int)ldo, relu, splits, status, st)  \
+                    : launch<AM, BMJ, __nv_bfloat16>(ma, mb, mo, tma_out, out, bias, beta_src, epi, MM, NN, KK, (int)ldo, relu, 1, status, st);
   RB_GEMM_CASE(false, false)
   RB_GEMM_CASE(false, true)
   RB_GEMM_CASE(true, false)

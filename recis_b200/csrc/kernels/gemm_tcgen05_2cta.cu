@@ -74,7 +74,7 @@ template <bool A_MN, bool B_MN, typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 2)
 gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                               const __grid_constant__ CUtensorMap map_o, const float* __restrict__ bias,
-                              const float* __restrict__ beta_src, int MM, int NN, int KK, int ldo, int relu,
+                              const float* __restrict__ beta_src, const RbGemmEpilogue epi, int MM, int NN, int KK, int ldo, int relu,
                               int64_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
@@ -211,7 +211,16 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const _
             v[j4 + 0] = relu ? fmaxf(x0, 0.f) : x0; v[j4 + 1] = relu ? fmaxf(x1, 0.f) : x1;
             v[j4 + 2] = relu ? fmaxf(x2, 0.f) : x2; v[j4 + 3] = relu ? fmaxf(x3, 0.f) : x3;
           }
+          if (epi.mask_src != nullptr)
+            rb::gemm::apply_mask32(v, reinterpret_cast<const __nv_bfloat16*>(epi.mask_src) + (int64_t)row * epi.mask_ld + n0 + c0, valid, row < MM);
           Store<OutT>::stage32(slab, lane, c0 - p0, v);
+          if (epi.colsum != nullptr) {
+            if (row >= MM) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            }
+            rb::gemm::column_sums32(v, lane, valid, epi.colsum + n0 + c0);
+          }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
@@ -249,8 +258,8 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const _
 }
 
 template <bool A_MN, bool B_MN, typename OutT>
-int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const float* bias, const float* beta_src, int MM,
-                int NN, int KK, int ldo, int relu, int splits, int64_t* status, cudaStream_t st) {
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const float* bias, const float* beta_src,
+                const RbGemmEpilogue& epi, int MM, int NN, int KK, int ldo, int relu, int splits, int64_t* status, cudaStream_t st) {
   auto kern = gemm_bf16_tcgen05_2cta_kernel<A_MN, B_MN, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -258,7 +267,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     attr_set = true;
   }
   dim3 grid(2 * ((MM + 2 * TM - 1) / (2 * TM)), (NN + TN - 1) / TN, splits);
-  kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, mo, bias, beta_src, MM, NN, KK, ldo, relu, status);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, mo, bias, beta_src, epi, MM, NN, KK, ldo, relu, status);
   rb::note_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
@@ -268,8 +277,11 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
 // Same contract as rb_gemm_bf16 (rb_dense.h), for outputs that can leave through TMA stores (base and row pitch 16-byte aligned).
 // Returns 7 when the problem does not suit the pair kernel (the caller then uses the one-CTA kernel).
 extern "C" int rb_gemm_bf16_pair(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo,
-                                 int out_fp32, const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int splits,
-                                 int64_t* status, cudaStream_t st) {
+                                 int out_fp32, const float* bias, const float* beta_src, const RbGemmEpilogue* epi_in, int MM, int NN, int KK,
+                                 int relu, int splits, int64_t* status, cudaStream_t st) {
+  RbGemmEpilogue epi{nullptr, 0, nullptr};
+  if (epi_in != nullptr) epi = *epi_in;
+  if ((epi.mask_src != nullptr || epi.colsum != nullptr) && splits > 1) return 6;
   if (MM < 192 || NN < 192 || KK <= 0) return 7;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) || (lda % 8) || (ldb % 8)) return 1;
   const int es = out_fp32 ? 4 : 2;
@@ -283,8 +295,8 @@ extern "C" int rb_gemm_bf16_pair(const void* a, int64_t lda, int a_mn, const voi
   if (ra || rbm || ro) return 2;
 #define RB_PAIR_CASE(AM, BMJ)                                                                                                    \
   if ((a_mn != 0) == AM && (b_mn != 0) == BMJ)                                                                                   \
-    return out_fp32 ? launch_pair<AM, BMJ, float>(ma, mb, mo, bias, beta_src, MM, NN, KK, (int)ldo, relu, splits, status, st)    \
-                    : launch_pair<AM, BMJ, __nv_bfloat16>(ma, mb, mo, bias, beta_src, MM, NN, KK, (int)ldo, relu, 1, status, st);
+    return out_fp32 ? launch_pair<AM, BMJ, float>(ma, mb, mo, bias, beta_src, epi, MM, NN, KK, (int)ldo, relu, splits, status, st)    \
+                    : launch_pair<AM, BMJ, __nv_bfloat16>(ma, mb, mo, bias, beta_src, epi, MM, NN, KK, (int)ldo, relu, 1, status, st);
   RB_PAIR_CASE(false, false)
   RB_PAIR_CASE(false, true)
   RB_PAIR_CASE(true, false)

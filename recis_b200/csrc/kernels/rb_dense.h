@@ -16,11 +16,23 @@ extern "C" {
 int rb_gemm_bf16(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo, int out_fp32,
                  const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int splits, int64_t* status,
                  cudaStream_t st);
+// Optional extra epilogue work, applied after bias / residual / ReLU:
+//   mask_src  bf16 [MM, mask_ld]: D[m, n] is set to zero where mask_src[m, n] <= 0 (the ReLU backward of the layer below, when D
+//             is the gradient of that layer's output);
+//   colsum    fp32 [NN]: the column sums of the final D are ADDED to it (the bias gradient of the layer below); zero it first.
+typedef struct {
+  const void* mask_src;
+  int64_t mask_ld;
+  float* colsum;
+} RbGemmEpilogue;
+int rb_gemm_bf16_ex(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo, int out_fp32,
+                    const float* bias, const float* beta_src, const RbGemmEpilogue* epi, int MM, int NN, int KK, int relu, int splits,
+                    int64_t* status, cudaStream_t st);
 // The same GEMM on pairs of SMs (256 x 256 tiles, tcgen05 cta_group::2; gemm_tcgen05_2cta.cu). Returns 7 when the problem does not
 // suit it (fewer than 192 rows or columns, output not TMA-storable); rb_gemm_bf16 tries it first when RECIS_GEMM_2CTA allows.
 int rb_gemm_bf16_pair(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, void* out, int64_t ldo, int out_fp32,
-                      const float* bias, const float* beta_src, int MM, int NN, int KK, int relu, int splits, int64_t* status,
-                      cudaStream_t st);
+                      const float* bias, const float* beta_src, const RbGemmEpilogue* epi, int MM, int NN, int KK, int relu, int splits,
+                      int64_t* status, cudaStream_t st);
 int rb_gemm_splits(int MM, int NN, int KK);
 // A (cached) TMA descriptor of a 2-D bf16 or fp32 matrix [rows][cols] with row pitch ld elements, box {box_cols, box_rows}, 128-byte
 // swizzle, written to out_map (a CUtensorMap, 128 bytes). 0 on success, 1 = base or pitch not 16-byte aligned, 2 = encode failed.

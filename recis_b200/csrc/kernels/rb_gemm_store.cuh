@@ -74,5 +74,47 @@ template <> struct Store<float> {
   }
 };
 
+// v[j] = 0 where the mask row (32 bf16 starting at mrow) is not positive; a row outside the matrix becomes all zeros
+__device__ __forceinline__ void apply_mask32(float (&v)[32], const __nv_bfloat16* mrow, int valid, bool row_ok) {
+  if (!row_ok) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+    return;
+  }
+  if (valid == 32 && (reinterpret_cast<uintptr_t>(mrow) & 15) == 0) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 u = reinterpret_cast<const uint4*>(mrow)[q];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 y = __bfloat1622float2(h[e]);
+        if (!(y.x > 0.f)) v[q * 8 + 2 * e] = 0.f;
+        if (!(y.y > 0.f)) v[q * 8 + 2 * e + 1] = 0.f;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid && !(__bfloat162float(mrow[j]) > 0.f)) v[j] = 0.f;
+  }
+}
+
+// Column sums of a 32 x 32 block held one row per lane: after five exchange steps lane l holds the sum of column l over the warp's
+// 32 rows (each step keeps half of the columns and adds the other lane's copy of them), which it adds to dst[l]. Destroys v.
+__device__ __forceinline__ void column_sums32(float (&v)[32], int lane, int valid, float* dst) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    const bool up = (lane & off) != 0;
+#pragma unroll
+    for (int j = 0; j < off; ++j) {
+      const float keep = up ? v[j + off] : v[j];
+      const float give = up ? v[j] : v[j + off];
+      v[j] = keep + __shfl_xor_sync(0xffffffffu, give, off);
+    }
+  }
+  if (lane < valid) atomicAdd(dst + lane, v[0]);
+}
+
 }  // namespace gemm
 }  // namespace rb

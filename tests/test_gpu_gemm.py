@@ -49,3 +49,24 @@ def test_gemm_accumulate():
     out = C.gemm_bf16(a, b, None, False, False, False, True, acc)
     assert out.data_ptr() == acc.data_ptr()
     assert torch.allclose(out, ref, atol=1e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("M,N,K,masked", [(8192, 1024, 512, True), (1000, 264, 520, True), (300, 64, 128, False), (8192, 512, 1024, True), (77, 8, 24, True)])
+def test_dgrad_with_relu_mask_and_bias_gradient_in_the_epilogue(M, N, K, masked):
+    """dx = (dy W) masked by the ReLU of the layer below, and its column sums, from one GEMM: against fp32 matmul + mask + sum,
+    on shapes that take the one-CTA kernel and shapes that take the pair kernel."""
+    C = recis_b200.native()
+    g = torch.Generator().manual_seed(M + N + K)
+    dy = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    y_below = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    dx, db = C.gemm_dgrad_fused(dy.to(DEV), w.to(DEV), y_below.to(DEV) if masked else None)
+    ref = dy.float() @ w.float()
+    if masked:
+        ref = ref * (y_below.float() > 0).float()
+    rel = lambda a, b: float((a.float().cpu() - b).norm() / b.norm().clamp(min=1e-12))
+    assert dx.dtype == torch.bfloat16 and rel(dx, ref) < 6e-3
+    if masked:
+        assert float(dx.float().cpu()[(y_below.float() <= 0)].abs().max()) == 0.0       # masked entries are exact zeros
+    assert rel(db, ref.sum(0)) < 2e-3
+    assert C.dense_status(DEV) == 0
