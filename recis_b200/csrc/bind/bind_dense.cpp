@@ -135,9 +135,13 @@ inline int64_t pad8(int64_t n) { return (n + 7) / 8 * 8; }
 
 // Whole MLP forward in one call: per layer cast+pad the fp32 master weight to bf16, then GEMM with fused bias (+ReLU).
 // x: [M, K0] any float dtype (cast / zero-padded to bf16 [M, pad8(K0)] here). Returns (padded bf16 input, layer outputs, bf16 weights).
+// wb_cached: empty, or per layer an up-to-date bf16 copy [pad8(N), pad8(K)] of the weight (kept by the caller across steps and
+// rewritten by the dense optimizer) that replaces the cast.
 std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_forward(const Tensor& x_in, const std::vector<Tensor>& weights,
-                                                                         const std::vector<Tensor>& biases, const std::vector<bool>& relu) {
+                                                                         const std::vector<Tensor>& biases, const std::vector<bool>& relu,
+                                                                         const std::vector<c10::optional<Tensor>>& wb_cached) {
   TORCH_CHECK(x_in.is_cuda() && x_in.dim() == 2 && weights.size() == biases.size() && weights.size() == relu.size());
+  TORCH_CHECK(wb_cached.empty() || wb_cached.size() == weights.size(), "wb_cached must be empty or hold one entry per layer");
   c10::cuda::CUDAGuard g(x_in.device());
   const int64_t K0p = pad8(weights[0].size(1));
   Tensor x = x_in.scalar_type() == torch::kBFloat16 ? x_in : x_in.to(torch::kBFloat16);
@@ -148,7 +152,14 @@ std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_forward(const T
   for (size_t l = 0; l < weights.size(); ++l) {
     const int64_t N = weights[l].size(0), K = weights[l].size(1), Np = pad8(N), Kp = pad8(K);
     TORCH_CHECK(h.size(1) == Kp, "layer ", l, ": input width ", h.size(1), " does not match the padded weight width ", Kp);
-    Tensor wb = cast_pad_bf16(weights[l], Np, Kp);
+    Tensor wb;
+    if (!wb_cached.empty() && wb_cached[l].has_value() && wb_cached[l]->defined()) {
+      wb = *wb_cached[l];
+      TORCH_CHECK(wb.scalar_type() == torch::kBFloat16 && wb.is_contiguous() && wb.dim() == 2 && wb.size(0) == Np && wb.size(1) == Kp &&
+                      wb.device() == x.device(), "layer ", l, ": the cached bf16 weight must be contiguous [", Np, ", ", Kp, "]");
+    } else {
+      wb = cast_pad_bf16(weights[l], Np, Kp);
+    }
     Tensor bp = Np == N ? biases[l] : torch::constant_pad_nd(biases[l], {0, Np - N});
     h = gemm_bf16(h, wb, bp, relu[l], false, false, false, c10::nullopt);
     ys.push_back(h); wbs.push_back(wb);
@@ -305,7 +316,8 @@ void init_dense(py::module& m) {
   m.def("layer_norm_bwd", &layer_norm_bwd);
   m.def("target_attention_fwd", &target_attention_fwd);
   m.def("target_attention_bwd", &target_attention_bwd);
-  m.def("mlp_forward", &mlp_forward);
+  m.def("mlp_forward", &mlp_forward, py::arg("x"), py::arg("weights"), py::arg("biases"), py::arg("relu"),
+        py::arg("wb_cached") = std::vector<c10::optional<Tensor>>());
   m.def("mlp_backward", &mlp_backward);
   m.def("dot_interaction_fwd", &dot_interaction_fwd);
   m.def("dot_interaction_bwd", &dot_interaction_bwd);

@@ -22,6 +22,23 @@ def _pad8(n: int) -> int:
     return (n + 7) // 8 * 8
 
 
+def bf16_shadow(weight: torch.Tensor):
+    """The bf16 copy of ``weight`` that the last forward pass made (or the dense optimizer rewrote), if it still matches the
+    weight: same storage and no in-place change through torch since. Native optimizer steps rewrite weight and copy in one
+    kernel and leave the version counter alone, so the copy stays valid across steps; anything else that touches the weight
+    (another optimizer, ``load_state_dict``, ``copy_``) bumps the counter and the next forward pass casts again."""
+    rec = getattr(weight, "_rb_bf16", None)
+    if rec is not None and rec[1] == weight._version and rec[2] == weight.data_ptr() and rec[0].device == weight.device:
+        return rec[0]
+    return None
+
+
+def keep_bf16_shadow(weight: torch.Tensor, wb: torch.Tensor):
+    """Remember ``wb`` as the bf16 copy of ``weight`` (only copies without padding can be rewritten by the optimizer)."""
+    if tuple(wb.shape) == tuple(weight.shape):
+        weight._rb_bf16 = (wb, weight._version, weight.data_ptr())
+
+
 class _LinearFn(torch.autograd.Function):
     """y[M, Np] = act(x[M, Kp] W^T + b) with W given as fp32 [N, K] (padded + cast to bf16 here)."""
 
@@ -31,7 +48,10 @@ class _LinearFn(torch.autograd.Function):
         N, K = weight.shape
         Np, Kp = _pad8(N), _pad8(K)
         assert x.shape[1] == Kp and x.dtype == torch.bfloat16
-        wb = C.cast_pad_bf16(weight, Np, Kp)
+        wb = bf16_shadow(weight)
+        if wb is None:
+            wb = C.cast_pad_bf16(weight, Np, Kp)
+            keep_bf16_shadow(weight, wb)
         bp = bias if Np == N else F.pad(bias, (0, Np - N))
         y = C.gemm_bf16(x, wb, bp, relu, False, False, False, None)
         ctx.save_for_backward(x, wb, y)
@@ -61,7 +81,10 @@ class _LinearResidualFn(torch.autograd.Function):
         C = native()
         N, K = weight.shape
         assert N % 8 == 0 and x.shape[1] == _pad8(K) and x.dtype == torch.bfloat16
-        wb = C.cast_pad_bf16(weight, N, _pad8(K))
+        wb = bf16_shadow(weight)
+        if wb is None:
+            wb = C.cast_pad_bf16(weight, N, _pad8(K))
+            keep_bf16_shadow(weight, wb)
         ctx.save_for_backward(x, wb)
         ctx.shape = (N, K)
         return C.gemm_bf16_residual(x, wb, bias, residual.contiguous())
@@ -147,7 +170,9 @@ class _MLPFn(torch.autograd.Function):
     def forward(ctx, x, relu, *params):
         n = len(params) // 2
         weights, biases = list(params[:n]), list(params[n:])
-        xp, ys, wbs = native().mlp_forward(x, weights, biases, list(relu))
+        xp, ys, wbs = native().mlp_forward(x, weights, biases, list(relu), [bf16_shadow(w) for w in weights])
+        for w, wb in zip(weights, wbs):
+            keep_bf16_shadow(w, wb)
         ctx.relu, ctx.shapes, ctx.n = list(relu), [list(w.shape) for w in weights], n
         ctx.x_shape, ctx.x_dtype = x.shape, x.dtype
         ctx.save_for_backward(xp, *ys, *wbs)

@@ -14,6 +14,8 @@ import math
 import torch
 from torch.optim import Optimizer
 
+from .dense_adam import _shadows
+
 
 class AdamWTF(Optimizer):
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, use_nesterov: bool = False, *,
@@ -59,7 +61,7 @@ class AdamWTF(Optimizer):
             if group["fuse"] and same_step and all(p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and
                                                    g.is_contiguous() for p, g in zip(params, grads)):
                 from .. import native
-                native().dense_adam(params, grads, ms, vs, [], beta1, beta2, group["eps"], 1 - group["weight_decay"], alpha, 1.0, 0.0)
+                native().dense_adam(params, grads, ms, vs, _shadows(params), beta1, beta2, group["eps"], 1 - group["weight_decay"], alpha, 1.0, 0.0)
             elif group["fuse"] and same_step:
                 torch._foreach_mul_(params, 1 - group["weight_decay"])
                 torch._foreach_lerp_(ms, grads, 1 - beta1)

@@ -15,6 +15,14 @@ import torch
 from torch.optim import Optimizer
 
 
+def _shadows(params):
+    """Per parameter, the bf16 copy that the forward pass keeps of it (``ops.dense.bf16_shadow``) or None; the update kernel
+    writes the rounded new weights into these copies, so the next forward pass needs no cast. An empty list when there is none."""
+    from ..ops.dense import bf16_shadow
+    out = [bf16_shadow(p) for p in params]
+    return out if any(o is not None for o in out) else []
+
+
 class DenseAdam(Optimizer):
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, decoupled=False):
         if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1 or weight_decay < 0:
@@ -50,7 +58,7 @@ class DenseAdam(Optimizer):
                 l2 = 0.0 if group["decoupled"] else wd
                 if all(p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and g.is_contiguous() for p, g in zip(ps, gs)):
                     from .. import native
-                    native().dense_adam(ps, gs, ms, vs, [], b1, b2, group["eps"], decay, lr / bc1, 1.0 / math.sqrt(bc2), l2)
+                    native().dense_adam(ps, gs, ms, vs, _shadows(ps), b1, b2, group["eps"], decay, lr / bc1, 1.0 / math.sqrt(bc2), l2)
                     continue
                 if l2:
                     gs = torch._foreach_add(gs, ps, alpha=l2)

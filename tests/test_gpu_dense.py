@@ -203,3 +203,37 @@ def test_linear_with_residual_in_the_epilogue_matches_fp32_reference():
     assert rel(out.detach(), ref.detach()) < 1e-5
     assert torch.equal(ro.grad.cpu(), go)
     assert rel(xo.grad, xb.grad) < 8e-3 and rel(lin.weight.grad, W.grad) < 8e-3 and rel(lin.bias.grad, b.grad) < 8e-3
+
+
+def test_bf16_weight_copies_follow_the_optimizer_and_any_other_change():
+    """The forward pass keeps a bf16 copy of every unpadded weight; the native dense optimizer rewrites it together with the
+    weight (no cast in the next forward), and a change made through torch invalidates it."""
+    from recis_b200.optim import DenseAdam
+    torch.manual_seed(0)
+    mlp = D.MLP([64, 128, 24, 1]).to(DEV)
+    opt = DenseAdam(mlp.parameters(), lr=1e-2)
+    x = torch.randn(256, 64, device=DEV)
+    C = recis_b200.native()
+    for step in range(3):
+        before = C.launch_count()
+        loss = mlp(x)[:, :1].float().square().mean()
+        launches_fwd = C.launch_count() - before
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        for layer in mlp.layers:
+            sh = D.bf16_shadow(layer.weight)
+            if layer.weight.shape[0] % 8 == 0 and layer.weight.shape[1] % 8 == 0:
+                assert sh is not None and torch.equal(sh, layer.weight.detach().to(torch.bfloat16))      # rewritten by the optimizer
+            else:
+                assert sh is None                                                                       # padded copies are not kept
+        if step == 0:
+            first = launches_fwd
+        else:
+            assert launches_fwd == first - 2          # the two unpadded layers no longer cast
+    with torch.no_grad():
+        mlp.layers[0].weight.mul_(0.5)
+    assert D.bf16_shadow(mlp.layers[0].weight) is None
+    ref = torch.relu(torch.relu(x.to(torch.bfloat16).float() @ mlp.layers[0].weight.detach().to(torch.bfloat16).float().t() + mlp.layers[0].bias))
+    out = mlp.layers[0](x.to(torch.bfloat16)).float()
+    assert float((out - ref).norm() / ref.norm()) < 1e-2
