@@ -12,6 +12,7 @@
 #include "../kernels/rb_kernels.h"
 #include "../cpu/rb_cpu.h"
 #include "store.h"
+#include <c10/cuda/CUDACachingAllocator.h>
 #include <climits>
 #include <cstdlib>
 #include "bind_shared.h"
@@ -208,7 +209,7 @@ void EmbeddingStore::ensure_room(int64_t n_incoming) {
       } else {
         int64_t nc = cap_rows_;
         while (rows_upper_ + n_incoming > nc) nc = nc + nc / 2 + 1024;
-        reserve(nc);
+        reserve(fit_growth(nc, rows_upper_ + n_incoming));
       }
     }
     if (index_upper_ + n_incoming > (int64_t)(0.65 * keys_.numel())) {
@@ -238,6 +239,36 @@ void EmbeddingStore::rebuild_index(int64_t nslots) {
   ctr_.select(0, RB_CTR_TOMBSTONES).zero_();
   // the tombstones are gone; with mirrored history the (pessimistic) bounds stay as they are until the next mirror lands
   if (!(device_.is_cuda() && est_new_ >= 0)) refresh_bounds();
+}
+
+// Growth by half is the policy while memory is plentiful. Close to the device's limit (a table that is most of the GPU's memory)
+// the step shrinks to what the free memory can hold, down to just the rows that are needed: a table must not fail at 1.5 x its
+// size when 1.1 x would have fitted.
+int64_t EmbeddingStore::fit_growth(int64_t wanted, int64_t needed) {
+  if (!device_.is_cuda() || !use_vmm_) return wanted;
+  int64_t row_bytes = 0;
+  auto add = [&](const torch::Tensor& t) { if (t.defined() && t.size(0) > 0) row_bytes += t.numel() / t.size(0) * (int64_t)t.element_size(); };
+  add(emb_);
+  for (auto& kv : slots_) add(kv.second);
+  add(last_seen_);
+  add(free_list_);
+  if (row_bytes <= 0) return wanted;
+  c10::cuda::CUDAGuard g(device_);
+  size_t free_b = 0, total_b = 0;
+  if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) return wanted;
+  // kept free: 2 GiB for an index rebuild and odd allocations, and what the tensor allocator holds now (the step's activations
+  // and workspaces will be asked for again after its cache has been emptied below)
+  const int64_t held = (int64_t)c10::cuda::CUDACachingAllocator::getDeviceStats(device_.index()).reserved_bytes[0].current;
+  int64_t margin = (int64_t)2 << 30;
+  auto rows_that_fit = [&](size_t fb) { return std::max<int64_t>(((int64_t)fb - margin) / row_bytes, 0); };
+  if (cap_rows_ + rows_that_fit(free_b) < wanted) {
+    c10::cuda::CUDACachingAllocator::emptyCache();                // blocks the tensor allocator caches cannot back a mapped range
+    if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) return wanted;
+    margin += held;
+  }
+  const int64_t fits = cap_rows_ + rows_that_fit(free_b);
+  if (fits >= wanted) return wanted;
+  return std::max<int64_t>(needed + needed / 64 + 1024, std::min(fits, wanted));   // below `needed` the reservation itself reports the failure
 }
 
 void EmbeddingStore::reserve(int64_t new_cap) {

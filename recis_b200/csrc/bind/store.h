@@ -34,6 +34,7 @@ class EmbeddingStore {
   torch::Tensor free_list() const { return free_list_; }
   std::vector<int64_t> counters() const;
   void reserve(int64_t new_cap);
+  int64_t fit_growth(int64_t wanted, int64_t needed);   // `wanted` rows, or fewer (but at least `needed`) when the device's free memory says so
   bool grows_in_place() const { return use_vmm_ && !vmm_.empty(); }
   void rebuild_index(int64_t nslots);
   void ensure_room(int64_t n_incoming);
