@@ -93,18 +93,20 @@ cutoff_scan_kernel(const RbCutoffFeature* __restrict__ feats, const int64_t* __r
   if (threadIdx.x == 0) { st_off(f.out_offsets, f.off_is_i64, f.n_out_rows, carry); totals[blockIdx.x] = carry; }
 }
 
-// (tiles, features) grid: output element i of feature t comes from src_beg[row] + (i - new_offsets[row])
+// (row tiles, features) grid: eight lanes copy one output row, from src_beg[row] to new_offsets[row]. No search: a row knows where
+// it starts on both sides (a lookup of the row by element position, as a flat loop over the elements needs, costs a binary search
+// of 13 dependent loads per element at 8192 rows).
 template <typename V>
 __device__ __forceinline__ void copy_feature(const RbCutoffFeature& f, void* out_values, const int64_t* __restrict__ src_beg, int64_t total) {
   const V* src = static_cast<const V*>(f.values); V* dst = static_cast<V*>(out_values);
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t lo = 0, hi = f.n_out_rows;                           // new_offsets[lo] <= i < new_offsets[hi]
-    while (hi - lo > 1) {
-      const int64_t mid = (lo + hi) >> 1;
-      if (ld_off(f.out_offsets, f.off_is_i64, mid) <= i) lo = mid; else hi = mid;
-    }
-    dst[i] = src[src_beg[f.row_prefix + lo] + (i - ld_off(f.out_offsets, f.off_is_i64, lo))];
+  const int sub = threadIdx.x & 7;
+  const int64_t groups = ((int64_t)gridDim.x * blockDim.x) >> 3;
+  for (int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3; r < f.n_out_rows; r += groups) {
+    const int64_t o0 = ld_off(f.out_offsets, f.off_is_i64, r), len = ld_off(f.out_offsets, f.off_is_i64, r + 1) - o0;
+    const int64_t s0 = src_beg[f.row_prefix + r];
+    for (int64_t j = sub; j < len; j += 8) dst[o0 + j] = src[s0 + j];
   }
+  (void)total;
 }
 
 __global__ void __launch_bounds__(kThreads)
