@@ -190,7 +190,9 @@ def run(args, arm):
     n_batches = W + e2e_warm + 2 * R * K
     # rows per GPU: what the run can touch (with a few GPUs the run ends long before the 1e8-row universe is covered) plus head-room
     # for the rows the allocator sets aside for calls still in flight
-    capacity = args.capacity or min(int(1.15 * UNIVERSE / world) + 8_000_000, 96_000_000)
+    # (one GPU: the whole 1e8-id universe plus the rows set aside for the calls in flight, 167 GB of rows and optimizer state; the
+    # table never has to grow inside a timed region however long the run is)
+    capacity = args.capacity or min(int(1.15 * UNIVERSE / world) + 8_000_000, 108_000_000)
     state = arm.build(fields, dev, world, rank, capacity)
 
     from recis_b200.io.synthetic import make_batch_arrays

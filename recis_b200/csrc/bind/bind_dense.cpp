@@ -108,13 +108,14 @@ Tensor fm_bwd(const Tensor& cube, const Tensor& gout) {
 }
 
 // returns (dy bf16 [M, N], db fp32 [N])
-std::tuple<Tensor, Tensor> relu_bwd_bias(const Tensor& y, const Tensor& dout, bool relu) {
+std::tuple<Tensor, Tensor> relu_bwd_bias(const Tensor& y, const Tensor& dout, bool relu, OptT db_out = c10::nullopt) {
   TORCH_CHECK(dout.is_cuda() && dout.scalar_type() == torch::kBFloat16 && dout.is_contiguous() && dout.dim() == 2);
   TORCH_CHECK(!relu || (y.scalar_type() == torch::kBFloat16 && y.is_contiguous() && y.sizes() == dout.sizes()));
   c10::cuda::CUDAGuard g(dout.device());
   const int M = (int)dout.size(0), N = (int)dout.size(1);
   Tensor dy = relu ? torch::empty_like(dout) : dout;
-  auto db = torch::zeros({N}, dout.options().dtype(torch::kFloat32));
+  // db_out: a zeroed fp32 [N] to add the column sums to (a caller that batches its zero-fills); else a fresh one
+  auto db = db_out.has_value() && db_out->defined() ? *db_out : torch::zeros({N}, dout.options().dtype(torch::kFloat32));
   if (rb_relu_bwd_bias_vec(relu ? y.data_ptr() : nullptr, dout.data_ptr(), M, N, relu, relu ? dy.data_ptr() : nullptr, db.data_ptr<float>(),
                            at::cuda::getCurrentCUDAStream()) == 1)
     rb_relu_bwd_bias(relu ? y.data_ptr() : nullptr, dout.data_ptr(), M, N, relu, relu ? dy.data_ptr() : nullptr, db.data_ptr<float>(),
@@ -169,13 +170,14 @@ std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_forward(const T
 
 // (dx bf16 [M, K], column sums of dx fp32 [K]) with dx = (dy [M, N] . W [N, K]) set to zero where mask [M, K] <= 0: the input gradient
 // of a layer, already passed through the ReLU of the layer below, and that layer's bias gradient, all in the GEMM's epilogue.
-std::tuple<Tensor, Tensor> gemm_dgrad_fused(const Tensor& dy, const Tensor& w, OptT mask) {
+std::tuple<Tensor, Tensor> gemm_dgrad_fused(const Tensor& dy, const Tensor& w, OptT mask, OptT db_out = c10::nullopt) {
   TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16 && dy.dim() == 2 && w.dim() == 2 &&
               dy.stride(1) == 1 && w.stride(1) == 1 && dy.size(1) == w.size(0), "bf16 dy [M, N] and W [N, K] expected");
   const int64_t MM = dy.size(0), KK = dy.size(1), NN = w.size(1);
   c10::cuda::CUDAGuard g(dy.device());
   auto out = torch::empty({MM, NN}, dy.options());
-  auto db = torch::zeros({NN}, dy.options().dtype(torch::kFloat32));
+  auto db = db_out.has_value() && db_out->defined() ? *db_out : torch::zeros({NN}, dy.options().dtype(torch::kFloat32));
+  TORCH_CHECK(db.scalar_type() == torch::kFloat32 && db.is_contiguous() && db.numel() == NN, "db_out: contiguous fp32 [K]");
   RbGemmEpilogue epi{nullptr, 0, db.data_ptr<float>()};
   if (mask.has_value() && mask->defined()) {
     TORCH_CHECK(mask->scalar_type() == torch::kBFloat16 && mask->dim() == 2 && mask->stride(1) == 1 && mask->size(0) == MM && mask->size(1) == NN,
@@ -202,15 +204,27 @@ std::tuple<Tensor, std::vector<Tensor>, std::vector<Tensor>> mlp_backward(const 
   // The last layer's pre-activation gradient comes from one element-wise kernel; below it, every layer's comes out of the GEMM
   // above it: dy_{l-1} = (dy_l W_l) with the ReLU mask of y_{l-1} applied and its column sums (the bias gradient) taken in the
   // epilogue, so a layer costs two GEMMs and nothing else.
+  // Weight gradients (split reductions add into their output) and bias gradients (column sums are added) all start from zero:
+  // one buffer, one fill for the whole call, instead of two per layer.
+  std::vector<int64_t> w_off(L), b_off(L);
+  int64_t total = 0;
+  auto up64 = [](int64_t n) { return (n + 63) / 64 * 64; };          // every piece starts 256-byte aligned
+  for (int l = 0; l < L; ++l) {
+    w_off[l] = total; total += up64(wbs[l].size(0) * wbs[l].size(1));
+    b_off[l] = total; total += up64(wbs[l].size(0));
+  }
+  Tensor zero = torch::zeros({total}, x.options().dtype(torch::kFloat32));
+  auto dw_view = [&](int l) { return zero.narrow(0, w_off[l], wbs[l].size(0) * wbs[l].size(1)).view({wbs[l].size(0), wbs[l].size(1)}); };
+  auto db_view = [&](int l) { return zero.narrow(0, b_off[l], wbs[l].size(0)); };
   Tensor dy, db;
-  std::tie(dy, db) = relu_bwd_bias(ys[L - 1], dout, relu[L - 1]);
+  std::tie(dy, db) = relu_bwd_bias(ys[L - 1], dout, relu[L - 1], db_view(L - 1));
   for (int l = L - 1; l >= 0; --l) {
     const Tensor& h_in = l == 0 ? x : ys[l - 1];
-    Tensor dw = gemm_bf16(dy, h_in, c10::nullopt, false, true, true, true, c10::nullopt);   // dy^T . h  (both MN-major, split-K)
+    Tensor dw = gemm_bf16(dy, h_in, c10::nullopt, false, true, true, true, dw_view(l));   // dy^T . h  (both MN-major, split-K)
     dws[l] = dw.narrow(0, 0, shapes[l][0]).narrow(1, 0, shapes[l][1]);
     dbs[l] = db.narrow(0, 0, shapes[l][0]);
     if (l > 0) {
-      std::tie(dy, db) = gemm_dgrad_fused(dy, wbs[l], relu[l - 1] ? c10::optional<Tensor>(ys[l - 1]) : c10::nullopt);
+      std::tie(dy, db) = gemm_dgrad_fused(dy, wbs[l], relu[l - 1] ? c10::optional<Tensor>(ys[l - 1]) : c10::nullopt, db_view(l - 1));
     } else if (need_dx) {
       dx = gemm_bf16(dy, wbs[0], c10::nullopt, false, false, true, false, c10::nullopt);    // dy . W  (W read MN-major)
     }
@@ -311,7 +325,7 @@ void init_dense(py::module& m) {
         py::arg("a_mn") = false, py::arg("b_mn") = false, py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none());
   m.def("dense_status", &dense_status);
   m.def("gemm_bf16_residual", &gemm_bf16_residual);
-  m.def("gemm_dgrad_fused", &gemm_dgrad_fused);
+  m.def("gemm_dgrad_fused", &gemm_dgrad_fused, py::arg("dy"), py::arg("w"), py::arg("mask"), py::arg("db_out") = c10::nullopt);
   m.def("layer_norm_fwd", &layer_norm_fwd);
   m.def("layer_norm_bwd", &layer_norm_bwd);
   m.def("target_attention_fwd", &target_attention_fwd);
@@ -323,7 +337,7 @@ void init_dense(py::module& m) {
   m.def("dot_interaction_bwd", &dot_interaction_bwd);
   m.def("fm_fwd", &fm_fwd);
   m.def("fm_bwd", &fm_bwd);
-  m.def("relu_bwd_bias", &relu_bwd_bias);
+  m.def("relu_bwd_bias", &relu_bwd_bias, py::arg("y"), py::arg("dout"), py::arg("relu"), py::arg("db_out") = c10::nullopt);
   m.def("cast_pad_bf16", &cast_pad_bf16);
   // Ragged self-attention forward on the tensor cores (head width 64): returns (out bf16 [T, H * 64], lse2 fp32 [T, H]).
   m.def("ragged_attention_fwd", [](const Tensor& qkv, const Tensor& offsets, int64_t H, int64_t max_len, double scale) {
