@@ -393,9 +393,17 @@ void init_dense(py::module& m) {
         a.w[k] = w.data_ptr<float>(); a.g[k] = g.data_ptr<float>(); a.m[k] = mm.data_ptr<float>(); a.v[k] = vv.data_ptr<float>();
         a.n[k] = w.numel();
         a.w_bf16[k] = nullptr;
+        a.cols[k] = 0; a.bf16_ld[k] = 0;
         if (!w_bf16.empty() && w_bf16[i0 + k].has_value() && w_bf16[i0 + k]->defined()) {
           const Tensor& wb = *w_bf16[i0 + k];
-          TORCH_CHECK(wb.scalar_type() == torch::kBFloat16 && wb.is_contiguous() && wb.numel() == w.numel(), "bf16 shadow mismatch");
+          TORCH_CHECK(wb.scalar_type() == torch::kBFloat16 && wb.is_contiguous(), "the bf16 copy must be contiguous bf16");
+          if (wb.numel() != w.numel()) {
+            // a copy padded for the GEMM: [rows_padded, cols_padded] of a 2-D weight [rows, cols]; the padding stays zero
+            TORCH_CHECK(w.dim() == 2 && wb.dim() == 2 && wb.size(0) >= w.size(0) && wb.size(1) >= w.size(1), "bf16 copy: shape ", wb.sizes(),
+                        " cannot hold the weight ", w.sizes());
+            a.cols[k] = (int32_t)w.size(1);
+            a.bf16_ld[k] = (int32_t)wb.size(1);
+          }
           a.w_bf16[k] = wb.data_ptr();
         }
       }

@@ -305,6 +305,8 @@ dense_adam_kernel(const __grid_constant__ RbDenseAdamArgs a, float b1, float b2,
   float* __restrict__ v = a.v[t];
   __nv_bfloat16* __restrict__ wb = reinterpret_cast<__nv_bfloat16*>(a.w_bf16[t]);
   const int64_t n = a.n[t];
+  const int cols = a.cols[t], ld = a.bf16_ld[t];
+  const bool padded = wb != nullptr && ld > 0 && ld != cols;          // the bf16 copy has a wider row pitch than the weight
   const float c1 = 1.f - b1, c2 = 1.f - b2;
   auto upd = [&](float& wi, float gi, float& mi, float& vi) {
     gi += l2 * wi;
@@ -315,7 +317,9 @@ dense_adam_kernel(const __grid_constant__ RbDenseAdamArgs a, float b1, float b2,
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   const bool vec = ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
-                     reinterpret_cast<uintptr_t>(v)) & 15) == 0 && (wb == nullptr || (reinterpret_cast<uintptr_t>(wb) & 7) == 0);
+                     reinterpret_cast<uintptr_t>(v)) & 15) == 0 && (wb == nullptr || (reinterpret_cast<uintptr_t>(wb) & 7) == 0) &&
+                   (!padded || ((cols & 3) == 0 && (ld & 3) == 0));    // four consecutive elements stay in one row of the copy
+  auto bf16_index = [&](int64_t i) { return padded ? (i / cols) * (int64_t)ld + (i % cols) : i; };
   const int64_t n4 = vec ? n >> 2 : 0;
   for (int64_t i = tid; i < n4; i += stride) {
     float4 wi = reinterpret_cast<float4*>(w)[i], mi = reinterpret_cast<float4*>(m)[i], vi = reinterpret_cast<float4*>(v)[i];
@@ -325,14 +329,14 @@ dense_adam_kernel(const __grid_constant__ RbDenseAdamArgs a, float b1, float b2,
     if (wb) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(wi.x, wi.y), hi = __floats2bfloat162_rn(wi.z, wi.w);
       uint2 pk; pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
-      reinterpret_cast<uint2*>(wb)[i] = pk;
+      *reinterpret_cast<uint2*>(wb + bf16_index(i << 2)) = pk;
     }
   }
   for (int64_t i = (n4 << 2) + tid; i < n; i += stride) {
     float wi = w[i], mi = m[i], vi = v[i];
     upd(wi, g[i], mi, vi);
     w[i] = wi; m[i] = mi; v[i] = vi;
-    if (wb) wb[i] = __float2bfloat16_rn(wi);
+    if (wb) wb[bf16_index(i)] = __float2bfloat16_rn(wi);
   }
 }
 }  // namespace

@@ -80,6 +80,8 @@ typedef struct RbDenseAdamArgs {
   float* m[RB_DENSE_ADAM_MAX];
   float* v[RB_DENSE_ADAM_MAX];
   void* w_bf16[RB_DENSE_ADAM_MAX];
+  int32_t cols[RB_DENSE_ADAM_MAX];       // columns of the weight (its last dimension); used with bf16_ld
+  int32_t bf16_ld[RB_DENSE_ADAM_MAX];    // row pitch of the bf16 copy in elements (a copy padded for TMA); 0 or == cols: same layout as w
   int64_t n[RB_DENSE_ADAM_MAX];
   int count;
 } RbDenseAdamArgs;

@@ -34,9 +34,9 @@ def bf16_shadow(weight: torch.Tensor):
 
 
 def keep_bf16_shadow(weight: torch.Tensor, wb: torch.Tensor):
-    """Remember ``wb`` as the bf16 copy of ``weight`` (only copies without padding can be rewritten by the optimizer)."""
-    if tuple(wb.shape) == tuple(weight.shape):
-        weight._rb_bf16 = (wb, weight._version, weight.data_ptr())
+    """Remember ``wb`` (the weight cast to bf16, zero-padded to multiples of 8 in both dimensions) as the copy of ``weight``; the
+    dense optimizer's kernel rewrites it in that layout together with the weight."""
+    weight._rb_bf16 = (wb, weight._version, weight.data_ptr())
 
 
 class _LinearFn(torch.autograd.Function):

@@ -206,8 +206,8 @@ def test_linear_with_residual_in_the_epilogue_matches_fp32_reference():
 
 
 def test_bf16_weight_copies_follow_the_optimizer_and_any_other_change():
-    """The forward pass keeps a bf16 copy of every unpadded weight; the native dense optimizer rewrites it together with the
-    weight (no cast in the next forward), and a change made through torch invalidates it."""
+    """The forward pass keeps a bf16 copy (padded to multiples of 8) of every weight; the native dense optimizer rewrites it
+    together with the weight (no cast in the next forward), and a change made through torch invalidates it."""
     from recis_b200.optim import DenseAdam
     torch.manual_seed(0)
     mlp = D.MLP([64, 128, 24, 1]).to(DEV)
@@ -223,14 +223,14 @@ def test_bf16_weight_copies_follow_the_optimizer_and_any_other_change():
         opt.step()
         for layer in mlp.layers:
             sh = D.bf16_shadow(layer.weight)
-            if layer.weight.shape[0] % 8 == 0 and layer.weight.shape[1] % 8 == 0:
-                assert sh is not None and torch.equal(sh, layer.weight.detach().to(torch.bfloat16))      # rewritten by the optimizer
-            else:
-                assert sh is None                                                                       # padded copies are not kept
+            N, K = layer.weight.shape
+            assert sh is not None and sh.shape == ((N + 7) // 8 * 8, (K + 7) // 8 * 8)
+            assert torch.equal(sh[:N, :K], layer.weight.detach().to(torch.bfloat16))            # rewritten by the optimizer
+            assert float(sh[N:].abs().sum()) == 0.0 and float(sh[:, K:].abs().sum()) == 0.0     # the padding stays zero
         if step == 0:
             first = launches_fwd
         else:
-            assert launches_fwd == first - 2          # the two unpadded layers no longer cast
+            assert launches_fwd == first - 3          # no layer casts its weight any more
     with torch.no_grad():
         mlp.layers[0].weight.mul_(0.5)
     assert D.bf16_shadow(mlp.layers[0].weight) is None
