@@ -134,6 +134,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--rows", type=int, default=0, help="table rows per rank over all tables (0: from the data)")
     ap.add_argument("--ckpt-dir", default=None)
+    ap.add_argument("--profile", type=int, default=0, help="after the timed steps, list the N kernels with the most device time in one more step")
     ap.add_argument("--comm", default=None, choices=["fused", "nccl"])
     ap.add_argument("--stage-exchange", action="store_true",
                     help="fused exchange: issue every table group's id phase and owner side before the first wait (RECIS_STAGE_EXCHANGE=1)")
@@ -221,6 +222,16 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item()) / args.steps
+
+    if args.profile and on_gpu:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step(batches[-1])
+            torch.cuda.synchronize()
+        kernels = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+        if rank == 0:
+            print(json.dumps({"profile": {"kernel_ms_total": sum(e.device_time_total for e in kernels) / 1e3, "kernels": [
+                {"name": e.key[:90], "ms": round(e.device_time_total / 1e3, 3), "launches": e.count} for e in kernels[:args.profile]]}}), flush=True)
 
     tables = model.embedding_engine.tables()
     for _tb in tables.values():
