@@ -52,6 +52,7 @@ table_claim_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, co
     const int64_t i = i0 + threadIdx.x;
     int32_t slot = -1;
     bool need_row = false;
+    int prob_delta = 0;                          // change of the probation counter caused by this thread (added once per warp below)
     uint64_t key = kEmptyKey;
     uint64_t h = 0;
     if (i < n) {
@@ -93,7 +94,7 @@ table_claim_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, co
               need_row = true;                                       // ticket comes from the block-wide hand-out below
             } else {
               *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = -2;  // probation, seen once
-              atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_PROBATION]), 1ull);
+              prob_delta = 1;
             }
           } else if (insert && admit_threshold > 1) {
             // key exists; if it is on probation, count this occurrence and admit at the threshold.
@@ -105,7 +106,7 @@ table_claim_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, co
                 if (atomicCAS(&t.rows[h], v, kRowPending) == v) {
                   const int32_t row = alloc_row(t, key, new_rows, new_keys);
                   *reinterpret_cast<volatile int32_t*>(&t.rows[h]) = row >= 0 ? row : -1;
-                  atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_PROBATION]), (unsigned long long)(-1ll));
+                  prob_delta = -1;
                   break;
                 }
               } else if (atomicCAS(&t.rows[h], v, v - 1) == v) {
@@ -117,6 +118,12 @@ table_claim_kernel(RbTable t, const int64_t* __restrict__ ids, int64_t n_max, co
         }
       }
       slot_out[i] = slot;
+    }
+    // ---- the probation counter moves once per warp: with an admission threshold most ids of a step are new to the table, and one
+    // atomic per id on a single counter serialises tens of millions of them
+    {
+      const int wsum = __reduce_add_sync(0xffffffffu, prob_delta);
+      if (lane == 0 && wsum != 0) atomicAdd(reinterpret_cast<unsigned long long*>(&t.ctr[RB_CTR_PROBATION]), (unsigned long long)(long long)wsum);
     }
     // ---- block-wide ticket hand-out
     const unsigned ballot = __ballot_sync(0xffffffffu, need_row);
