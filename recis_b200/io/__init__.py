@@ -5,3 +5,11 @@ from .synthetic import SparseFieldSpec, SyntheticSpec, make_batch, make_batch_ar
 
 __all__ = ["DatasetBase", "OrcDataset", "SyntheticDataset", "TensorDataset", "MapDataset", "FilterDataset", "PrefetchDataset",
            "StateDataset", "WrapEndDataset", "SyntheticSpec", "SparseFieldSpec", "make_batch", "make_batch_arrays", "to_device", "DevicePrefetcher", "PackedBatch"]
+
+# The reference keeps each dataset class in a module of its own (recis/io/orc_dataset.py, dataset_base.py, state_dataset.py,
+# map_dataset.py, wrap_end_dataset.py, filter_dataset.py); here they share io/dataset.py. The old import paths resolve to it, so
+# `from recis_b200.io.orc_dataset import OrcDataset` works with only the package name changed.
+import sys as _sys
+from . import dataset as _dataset
+for _alias in ("orc_dataset", "dataset_base", "state_dataset", "map_dataset", "wrap_end_dataset", "filter_dataset"):
+    _sys.modules.setdefault(__name__ + "." + _alias, _dataset)
