@@ -134,6 +134,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--rows", type=int, default=0, help="table rows per rank over all tables (0: from the data)")
     ap.add_argument("--ckpt-dir", default=None)
+    ap.add_argument("--skip-checkpoint", action="store_true", help="time the training steps only (the round trip writes tens of GB per rank)")
     ap.add_argument("--profile", type=int, default=0, help="after the timed steps, list the N kernels with the most device time in one more step")
     ap.add_argument("--comm", default=None, choices=["fused", "nccl"])
     ap.add_argument("--stage-exchange", action="store_true",
@@ -240,38 +241,40 @@ def main():
             _ex.check()          # a timed-out wait or an overflowing window invalidates the measurement: fail instead of reporting it
     sizes = {str(tb.impl.dim): int(tb.impl.size()) for tb in tables.values()}
 
-    # ---- sparse checkpoint round trip into a freshly built model
-    ckpt = args.ckpt_dir or tempfile.mkdtemp(prefix="recis_b200_ckpt_")
-    if world > 1:
-        box = [ckpt]
-        dist.broadcast_object_list(box, src=0)
-        ckpt = box[0]
-    os.makedirs(ckpt, exist_ok=True)
-    probe = batches[-1]
-    model.eval()
-    with torch.no_grad():
-        ref = model.embed(probe)
-    sync()
-    t0 = time.perf_counter()
-    dense_state = {k: v for k, v in model.state_dict().items() if isinstance(v, torch.Tensor)} if rank == 0 else {}
-    Saver(rank, world, 4, ckpt, filter_out_sparse_param(model), dense_state).save()
-    sync()
-    save_s = time.perf_counter() - t0
-    ckpt_bytes = sum(os.path.getsize(os.path.join(ckpt, f)) for f in os.listdir(ckpt)) if rank == 0 else 0
-    HashtableRegister().clear()
-    model2 = build_model(plan, dev, rows, int(nnz * 1.05) + 4096, args.admit, args.ttl)
-    t0 = time.perf_counter()
-    Loader(ckpt, filter_out_sparse_param(model2), {}).load()
-    sync()
-    load_s = time.perf_counter() - t0
-    model2.eval()
-    with torch.no_grad():
-        got = model2.embed(probe)
-    sizes2 = {str(tb.impl.dim): int(tb.impl.size()) for tb in model2.embedding_engine.tables().values()}
-    same = bool(torch.equal(ref, got)) and sizes == sizes2
-    sync()
-    if rank == 0 and args.ckpt_dir is None:
-        shutil.rmtree(ckpt, ignore_errors=True)
+    save_s = load_s = ckpt_bytes = same = None
+    if not args.skip_checkpoint:
+        # ---- sparse checkpoint round trip into a freshly built model
+        ckpt = args.ckpt_dir or tempfile.mkdtemp(prefix="recis_b200_ckpt_")
+        if world > 1:
+            box = [ckpt]
+            dist.broadcast_object_list(box, src=0)
+            ckpt = box[0]
+        os.makedirs(ckpt, exist_ok=True)
+        probe = batches[-1]
+        model.eval()
+        with torch.no_grad():
+            ref = model.embed(probe)
+        sync()
+        t0 = time.perf_counter()
+        dense_state = {k: v for k, v in model.state_dict().items() if isinstance(v, torch.Tensor)} if rank == 0 else {}
+        Saver(rank, world, 4, ckpt, filter_out_sparse_param(model), dense_state).save()
+        sync()
+        save_s = time.perf_counter() - t0
+        ckpt_bytes = sum(os.path.getsize(os.path.join(ckpt, f)) for f in os.listdir(ckpt)) if rank == 0 else 0
+        HashtableRegister().clear()
+        model2 = build_model(plan, dev, rows, int(nnz * 1.05) + 4096, args.admit, args.ttl)
+        t0 = time.perf_counter()
+        Loader(ckpt, filter_out_sparse_param(model2), {}).load()
+        sync()
+        load_s = time.perf_counter() - t0
+        model2.eval()
+        with torch.no_grad():
+            got = model2.embed(probe)
+        sizes2 = {str(tb.impl.dim): int(tb.impl.size()) for tb in model2.embedding_engine.tables().values()}
+        same = bool(torch.equal(ref, got)) and sizes == sizes2
+        sync()
+        if rank == 0 and args.ckpt_dir is None:
+            shutil.rmtree(ckpt, ignore_errors=True)
 
     if rank == 0:
         print(json.dumps({
