@@ -529,3 +529,33 @@ def test_async_scalar_reader_returns_every_posted_value():
     assert r.get(t5) == 7.0
     with pytest.raises(AssertionError):
         r.get(t[0])
+
+
+def test_bf16_weight_copy_bookkeeping_follows_versions_and_storage():
+    """The kept bf16 copy of a weight is valid only for the same storage and version counter (the CUDA kernels that use it are
+    covered by the GPU tests; the bookkeeping is plain Python)."""
+    from recis_b200.ops.dense import bf16_shadow, keep_bf16_shadow
+    w = torch.nn.Parameter(torch.randn(8, 16))
+    assert bf16_shadow(w) is None
+    keep_bf16_shadow(w, w.detach().to(torch.bfloat16))
+    assert bf16_shadow(w) is not None
+    with torch.no_grad():
+        w.add_(1.0)                                   # an in-place change through torch bumps the version counter
+    assert bf16_shadow(w) is None
+    keep_bf16_shadow(w, w.detach().to(torch.bfloat16))
+    w.data = torch.randn(8, 16)                       # new storage under the same Parameter object
+    assert bf16_shadow(w) is None
+
+
+def test_dense_reducer_single_rank_applies_the_accumulation_scale():
+    """With one rank there is nothing to reduce, but the division by the accumulation count still happens in the reducer."""
+    from recis_b200.parallel import DenseGradReducer
+    lin = torch.nn.Linear(4, 3)
+    red = DenseGradReducer(list(lin.parameters()), world=1)
+    red.grad_scale = 0.5
+    for _ in range(2):
+        lin(torch.ones(2, 4)).sum().backward()
+    red.all_reduce_async()
+    red.wait()
+    assert torch.allclose(lin.bias.grad, torch.full((3,), 2.0))       # (2 + 2) * 0.5
+    assert lin.weight.grad.data_ptr() == red.flat[:0].data_ptr() or lin.weight.grad.untyped_storage().data_ptr() == red.flat.untyped_storage().data_ptr()
