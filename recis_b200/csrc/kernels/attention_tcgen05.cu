@@ -50,6 +50,66 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
+// One thread's row of a 128-key tile of S (tensor memory at `trow`): new running maximum and sum, P = 2^(S * scale_log2 - m)
+// written as bf16 into the two K-major blocks of `ptile`. Returns the factor by which what was accumulated under the old
+// maximum shrinks. kMask selects whether key columns >= valid are masked: a full tile pays for no compare or select.
+// The row is read from tensor memory once (four 32-column reads in flight) and stays in registers for both passes; the
+// maximum and the sum run as four independent chains each, since one warp per scheduler hides no dependent latency.
+template <bool kMask>
+__device__ __forceinline__ float softmax_row(uint32_t trow, int valid, float scale_log2, int t, uint8_t* ptile, float& m, float& l) {
+  uint32_t s0[32], s1[32], s2[32], s3[32];
+  tmem_ld32(trow, s0);
+  tmem_ld32(trow + 32u, s1);
+  tmem_ld32(trow + 64u, s2);
+  tmem_ld32(trow + 96u, s3);
+  tmem_ld_wait();
+  // masking is a select on the value (no branch per element): a masked key becomes -inf here and an exact zero after the
+  // exponential; scale_log2 > 0, so the maximum can be taken before scaling
+  if (kMask) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (i >= valid) s0[i] = 0xff800000u;
+      if (32 + i >= valid) s1[i] = 0xff800000u;
+      if (64 + i >= valid) s2[i] = 0xff800000u;
+      if (96 + i >= valid) s3[i] = 0xff800000u;
+    }
+  }
+  float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
+    mx1 = fmaxf(mx1, __uint_as_float(s1[i]));
+    mx2 = fmaxf(mx2, __uint_as_float(s2[i]));
+    mx3 = fmaxf(mx3, __uint_as_float(s3[i]));
+  }
+  const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+  const float m_new = fmaxf(m, mx * scale_log2);
+  const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
+  float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+  for (int q4 = 0; q4 < 4; ++q4) {                 // 32 key columns per quarter; two quarters per 64-wide K-major block
+    uint8_t* blk = ptile + (q4 >> 1) * kBlk;
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t ua = q4 == 0 ? s0[2 * i] : q4 == 1 ? s1[2 * i] : q4 == 2 ? s2[2 * i] : s3[2 * i];
+      const uint32_t ub = q4 == 0 ? s0[2 * i + 1] : q4 == 1 ? s1[2 * i + 1] : q4 == 2 ? s2[2 * i + 1] : s3[2 * i + 1];
+      // -inf * scale_log2 - m_new = -inf (m_new is finite whenever the tile has one existing key): 2^-inf = 0
+      const float p0 = fast_exp2(fmaf(__uint_as_float(ua), scale_log2, -m_new));
+      const float p1 = fast_exp2(fmaf(__uint_as_float(ub), scale_log2, -m_new));
+      if (i & 1) { sum1 += p0; sum3 += p1; } else { sum0 += p0; sum2 += p1; }
+      pk[i] = pack_bf16x2(p0, p1);
+    }
+#pragma unroll
+    for (int cq = 0; cq < 4; ++cq)
+      *reinterpret_cast<uint4*>(blk + swizzle128_offset(t, (q4 & 1) * 32 + cq * 8)) =
+          make_uint4(pk[cq * 4], pk[cq * 4 + 1], pk[cq * 4 + 2], pk[cq * 4 + 3]);
+  }
+  l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
+  m = m_new;
+  return alpha;
+}
+
 __global__ void __launch_bounds__(128, 2)
 ragged_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const int32_t* __restrict__ offsets, int H, float scale_log2,
                             __nv_bfloat16* __restrict__ out, float* __restrict__ lse2, int64_t* __restrict__ status) {
@@ -119,55 +179,11 @@ ragged_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const i
     // S is complete, so the K tile is free: the next one travels while this tile's softmax and P V run
     if (t == 0 && j + 1 < n_kv) { mbar_expect_tx(&bar_k, kBlk); tma_load_2d(ktile, &map_qkv, xk, s0 + (j + 1) * kTile, &bar_k); }
 
-    // ---- online softmax on this thread's row of S (two 32-column reads of tensor memory in flight at a time)
+    // ---- online softmax on this thread's row of S; only the sequence's last key tile can hold keys that do not exist
     const int valid = min(kTile, L - j * kTile);                 // key columns of this tile that exist
-    float mx = -INFINITY;
-#pragma unroll
-    for (int c0 = 0; c0 < kTile; c0 += 64) {
-      uint32_t r0[32], r1[32];
-      tmem_ld32(tmem + lane_base + (uint32_t)c0, r0);
-      tmem_ld32(tmem + lane_base + (uint32_t)c0 + 32u, r1);
-      tmem_ld_wait();
-      // masking is a select on the value (no branch per element); scale_log2 > 0, so the maximum can be taken before scaling
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        mx = fmaxf(mx, (c0 + i < valid) ? __uint_as_float(r0[i]) : -INFINITY);
-        mx = fmaxf(mx, (c0 + 32 + i < valid) ? __uint_as_float(r1[i]) : -INFINITY);
-      }
-    }
-    const float m_new = fmaxf(m, mx * scale_log2);
-    const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
-    float rowsum = 0.f;
-#pragma unroll
-    for (int c0 = 0; c0 < kTile; c0 += 64) {
-      uint32_t r0[32], r1[32];
-      tmem_ld32(tmem + lane_base + (uint32_t)c0, r0);
-      tmem_ld32(tmem + lane_base + (uint32_t)c0 + 32u, r1);
-      tmem_ld_wait();
-      uint8_t* blk = ptile + (c0 >> 6) * kBlk;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          // a masked key enters as -inf and leaves as an exact zero
-          const int c = c0 + half * 32 + 2 * i;
-          const float s_a = __uint_as_float(half ? r1[2 * i] : r0[2 * i]), s_b = __uint_as_float(half ? r1[2 * i + 1] : r0[2 * i + 1]);
-          const float p0 = fast_exp2((c < valid) ? fmaf(s_a, scale_log2, -m_new) : -INFINITY);
-          const float p1 = fast_exp2((c + 1 < valid) ? fmaf(s_b, scale_log2, -m_new) : -INFINITY);
-          rowsum += p0 + p1;
-          pk[i] = pack_bf16x2(p0, p1);
-        }
-#pragma unroll
-        for (int cq = 0; cq < 4; ++cq)
-          *reinterpret_cast<uint4*>(blk + swizzle128_offset(t, half * 32 + cq * 8)) =
-              make_uint4(pk[cq * 4], pk[cq * 4 + 1], pk[cq * 4 + 2], pk[cq * 4 + 3]);
-      }
-    }
-    l = l * alpha + rowsum;
-    m = m_new;
-#pragma unroll
-    for (int d = 0; d < kHead; ++d) o[d] *= alpha;
+    float alpha;
+    if (valid == kTile) alpha = softmax_row<false>(tmem + lane_base, kTile, scale_log2, t, ptile, m, l);
+    else alpha = softmax_row<true>(tmem + lane_base, valid, scale_log2, t, ptile, m, l);
 
     if (valid < kTile) {
       // last, partial tile: the V rows past the end of the sequence become zeros (this thread's row, once V has landed)
@@ -204,7 +220,10 @@ ragged_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const i
       tmem_ld32(tmem + lane_base + 160u, r1);
       tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) { o[i] += __uint_as_float(r0[i]); o[32 + i] += __uint_as_float(r1[i]); }
+      for (int i = 0; i < 32; ++i) {           // O = O * alpha + P V, one multiply-add per element
+        o[i] = fmaf(o[i], alpha, __uint_as_float(r0[i]));
+        o[32 + i] = fmaf(o[32 + i], alpha, __uint_as_float(r1[i]));
+      }
     }
   }
 
@@ -254,6 +273,60 @@ attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
 // dK and dV of the tile's keys are stored once at the end. Gradients go to dqkv [T, 3 * H * 64] in fp32 (the q part must be
 // zero on entry).
 constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 320, kColDQ = 384;
+
+// One thread's query row of a [128 q x 128 keys] tile in the backward: P = 2^(S * scale_log2 - lse) and
+// dS = P * (dP - delta) * scale, written as bf16 into the [q][key] tiles. kMask selects whether key columns >= valid are
+// masked (a masked entry enters the exponential as -inf, so P and dS are exact zeros there; dP and delta are finite).
+template <bool kMask>
+__device__ __forceinline__ void p_ds_chunk(const uint32_t (&rs)[32], const uint32_t (&rp)[32], int c0, int valid, float scale, float scale_log2,
+                                           float lse_q, float nds, int t, uint8_t* ptile, uint8_t* dstile) {
+  uint32_t pk[16], dk[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    float p[2], ds[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int c = c0 + 2 * e + u;
+      const float x = (!kMask || c < valid) ? fmaf(__uint_as_float(rs[2 * e + u]), scale_log2, -lse_q) : -INFINITY;
+      p[u] = fast_exp2(x);
+      ds[u] = p[u] * fmaf(__uint_as_float(rp[2 * e + u]), scale, nds);
+    }
+    pk[e] = pack_bf16x2(p[0], p[1]);
+    dk[e] = pack_bf16x2(ds[0], ds[1]);
+  }
+  const uint32_t boff = (uint32_t)(c0 >> 6) * kBlk;
+#pragma unroll
+  for (int cq = 0; cq < 4; ++cq) {
+    const uint32_t off = boff + swizzle128_offset(t, (c0 & 63) + cq * 8);
+    *reinterpret_cast<uint4*>(ptile + off) = make_uint4(pk[cq * 4], pk[cq * 4 + 1], pk[cq * 4 + 2], pk[cq * 4 + 3]);
+    *reinterpret_cast<uint4*>(dstile + off) = make_uint4(dk[cq * 4], dk[cq * 4 + 1], dk[cq * 4 + 2], dk[cq * 4 + 3]);
+  }
+}
+
+// The row is walked in four chunks of 32 key columns with two register sets: the next chunk's S and dP travel from tensor
+// memory while the current chunk is computed.
+template <bool kMask>
+__device__ __forceinline__ void p_ds_row(uint32_t trow, int valid, float scale, float scale_log2, float lse_q, float delta_q, int t,
+                                         uint8_t* ptile, uint8_t* dstile) {
+  const float nds = -delta_q * scale;                              // (dP - delta) * scale = dP * scale + nds
+  uint32_t sa[32], pa[32], sb[32], pb[32];
+  tmem_ld32(trow + kColS, sa);
+  tmem_ld32(trow + kColDP, pa);
+  tmem_ld_wait();
+  tmem_ld32(trow + kColS + 32u, sb);
+  tmem_ld32(trow + kColDP + 32u, pb);
+  p_ds_chunk<kMask>(sa, pa, 0, valid, scale, scale_log2, lse_q, nds, t, ptile, dstile);
+  tmem_ld_wait();
+  tmem_ld32(trow + kColS + 64u, sa);
+  tmem_ld32(trow + kColDP + 64u, pa);
+  p_ds_chunk<kMask>(sb, pb, 32, valid, scale, scale_log2, lse_q, nds, t, ptile, dstile);
+  tmem_ld_wait();
+  tmem_ld32(trow + kColS + 96u, sb);
+  tmem_ld32(trow + kColDP + 96u, pb);
+  p_ds_chunk<kMask>(sa, pa, 64, valid, scale, scale_log2, lse_q, nds, t, ptile, dstile);
+  tmem_ld_wait();
+  p_ds_chunk<kMask>(sb, pb, 96, valid, scale, scale_log2, lse_q, nds, t, ptile, dstile);
+}
 
 __global__ void __launch_bounds__(128, 1)
 ragged_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do,
@@ -376,34 +449,12 @@ ragged_attention_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const _
     fence_after_sync();
     if (!ok) break;
 
-    for (int c0 = 0; c0 < kTile; c0 += 32) {
-      uint32_t rs[32], rp[32];
-      tmem_ld32(tmem + lane_base + kColS + (uint32_t)c0, rs);
-      tmem_ld32(tmem + lane_base + kColDP + (uint32_t)c0, rp);
-      tmem_ld_wait();
-      uint32_t pk[16], dk[16];
-#pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        float p[2], ds[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int c = c0 + 2 * e + u;
-          // a masked entry enters the exponential as -inf: P and dS are exact zeros there (dP and delta are finite)
-          const float x = (q_ok && c < valid_keys) ? fmaf(__uint_as_float(rs[2 * e + u]), scale_log2, -lse_q) : -INFINITY;
-          p[u] = fast_exp2(x);
-          ds[u] = p[u] * (__uint_as_float(rp[2 * e + u]) - delta_q) * scale;
-        }
-        pk[e] = pack_bf16x2(p[0], p[1]);
-        dk[e] = pack_bf16x2(ds[0], ds[1]);
-      }
-      const uint32_t boff = (uint32_t)(c0 >> 6) * kBlk;
-#pragma unroll
-      for (int cq = 0; cq < 4; ++cq) {
-        const uint32_t off = boff + swizzle128_offset(t, (c0 & 63) + cq * 8);
-        *reinterpret_cast<uint4*>(ptile + off) = make_uint4(pk[cq * 4], pk[cq * 4 + 1], pk[cq * 4 + 2], pk[cq * 4 + 3]);
-        *reinterpret_cast<uint4*>(dstile + off) = make_uint4(dk[cq * 4], dk[cq * 4 + 1], dk[cq * 4 + 2], dk[cq * 4 + 3]);
-      }
-    }
+    // masking is needed only where the tile holds a key or a query that does not exist (the sequence's last tiles)
+    const int vk = q_ok ? valid_keys : 0;                          // key columns of this thread's row that count
+    if (valid_keys == kTile && L - i * kTile >= kTile)
+      p_ds_row<false>(tmem + lane_base, kTile, scale, scale_log2, lse_q, delta_q, t, ptile, dstile);
+    else
+      p_ds_row<true>(tmem + lane_base, vk, scale, scale_log2, lse_q, delta_q, t, ptile, dstile);
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
