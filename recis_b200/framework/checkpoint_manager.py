@@ -19,6 +19,7 @@ import torch.distributed as dist
 from ..nn.modules.hashtable import split_sparse_dense_state_dict
 from ..serialize import Loader as SLoader, Saver as SSaver
 from ..utils.logger import Logger
+from ..utils.mos import Mos
 
 logger = Logger(__name__)
 
@@ -31,7 +32,10 @@ class Saver:
         self._checkpoint_version_list = []
         self._max_keep = max_keep
         self._extra_save_dict = {}
-        self._output_dir = output_dir
+        # an output_dir of the form model.<project>.<name>[/version=...] is a model-store URI: the run writes into the version's
+        # directory and every checkpoint saved or removed is recorded there (``recis/framework/checkpoint_manager.py:73-78``)
+        self._mos = Mos(output_dir) if str(output_dir).startswith("model.") else None
+        self._output_dir = self._mos.real_physical_path if self._mos else output_dir
         self._sparse_optim = sparse_optim
         self._concurrency = concurrency
         self._io_state = {}
@@ -92,6 +96,10 @@ class Saver:
                     remains = [l.strip() for l in f.read().split("\n") if l.strip() and l.strip() != old]
                 with open(os.path.join(self._output_dir, self._checkpoint_file), "w") as f:
                     f.writelines(r + "\n" for r in remains)
+                if self._mos:
+                    self._mos.ckpt_update(ckpt_id=old, path=os.path.join(self._output_dir, old), is_delete=True)
+            if self._mos:
+                self._mos.ckpt_update(ckpt_id=ckpt_id, path=ckpt_path)
         if torch.cuda.is_available():
             torch.cuda.synchronize()
 
@@ -236,7 +244,10 @@ class CheckpointManager:
 
     def load_model_bank(self, model_bank_conf):
         for mbc in model_bank_conf or []:
-            self._saver.load(ckpt_path=mbc["path"], load_conf=mbc, shard_id=self._rank, direct_path=True)
+            path = mbc["path"]
+            if path is not None and str(path).startswith("model."):      # a model-store URI names the checkpoint
+                path = Mos(path, True).real_physical_path
+            self._saver.load(ckpt_path=path, load_conf=mbc, shard_id=self._rank, direct_path=True)
 
     def restore(self, global_step: Optional[int] = None):
         self._saver.load(ckpt_id=None if global_step is None else f"ckpt_{global_step}", shard_id=self._rank)

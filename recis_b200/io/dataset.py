@@ -34,7 +34,9 @@ class DatasetBase:
     every batch goes through the map functions in registration order; a batch for which ANY filter function returns True is
     skipped. Both return the dataset, so calls can be chained."""
 
-    _pipeline_inline = False          # True: the class applies the registered functions itself, at its own place in __iter__
+    # True: the class (and, by inheritance, classes built on its batch conversion) applies the registered functions itself,
+    # at its own place in __iter__
+    _pipeline_inline = False
 
     def map(self, map_func):
         self.__dict__.setdefault("_map_funcs", []).append(map_func)
@@ -61,7 +63,7 @@ class DatasetBase:
     def __init_subclass__(cls, **kwargs):
         super().__init_subclass__(**kwargs)
         raw = cls.__dict__.get("__iter__")
-        if raw is not None and not cls.__dict__.get("_pipeline_inline", False):
+        if raw is not None and not getattr(cls, "_pipeline_inline", False):
             def __iter__(self, _raw=raw):
                 if self.__dict__.get("_map_funcs") or self.__dict__.get("_filter_funcs"):
                     return self._through_pipeline(_raw(self))

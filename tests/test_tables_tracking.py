@@ -1,0 +1,362 @@
+"""Row-addressable tables, time-addressable streams and their windowed datasets; sample-level trace tables; experiment tracking;
+the model store. All on CPU: the services of the reference's internal build are replaced by files and by fakes registered as
+sources."""
+import json
+import os
+
+import numpy as np
+import pyarrow as pa
+import pyarrow.dataset as pads
+import pyarrow.orc as orc
+import pyarrow.parquet as pq
+import pytest
+import torch
+
+from recis_b200.io import (OdpsDataset, get_table_size, make_lake_stream_window_io, make_odps_sample_io, make_odps_window_io,
+                           register_table_source)
+from recis_b200.io.window_io import (TableSheet, _build_shard, _parse_proportion, _shard_sheets_by_row_num, _shard_table_by_subprocess,
+                                     _str_to_timestamp)
+
+
+def _write_table(dirname, base, nfiles, rows):
+    os.makedirs(dirname, exist_ok=True)
+    r = base
+    for i in range(nfiles):
+        t = pa.table({"uid": pa.array(np.arange(r, r + rows), pa.int64()),
+                      "items": pa.array([[int(x), int(x) + 1] for x in range(r, r + rows)], pa.list_(pa.int64())),
+                      "score": pa.array(np.arange(r, r + rows, dtype=np.float64))})
+        if i % 2 == 0:
+            pq.write_table(t, f"{dirname}/part-{i:03d}.parquet")
+        else:
+            orc.write_table(t, f"{dirname}/part-{i:03d}.orc")
+        r += rows
+
+
+# ------------------------------------------------------------------------------------------------------------ sharding math
+def test_build_shard_spreads_the_surplus():
+    shards, off = _build_shard(0, 100, 3)
+    assert shards == [(0, 34), (34, 67), (67, 100)] and off == 1
+    shards, off = _build_shard(100, 100, 3, off)          # the longer shard moves on
+    assert [e - s for s, e in shards] == [33, 34, 33] and shards[0][0] == 100 and shards[-1][1] == 200 and off == 2
+
+
+def test_parse_proportion():
+    assert _parse_proportion(6, [(2, 3), (1, 3)]) == ([4, 2], 6)
+    assert _parse_proportion(4, [(1, 1)]) == ([4], 4)
+    with pytest.raises(ValueError):
+        _parse_proportion(4, [(1, 2), (1, 3)])
+    with pytest.raises(ValueError):
+        _parse_proportion(4, [(2, 3), (2, 3)])
+
+
+def test_subprocess_shares_cover_each_sheet():
+    sheets = [TableSheet("t", 0, 10), TableSheet("t", 10, 17)]
+    parts = [_shard_table_by_subprocess(sheets, i, 3) for i in range(3)]
+    for k, sh in enumerate(sheets):
+        rows = []
+        for p in parts:
+            s = TableSheet.parse(p[k])
+            rows += list(range(s.start, s.end))
+        assert rows == list(range(sh.start, sh.end))
+
+
+def test_row_num_sheets_partition_the_table(tmp_path):
+    _write_table(str(tmp_path / "t"), 0, 3, 111)
+    rows = []
+    for w in range(2):
+        sheets, _ = _shard_sheets_by_row_num(str(tmp_path / "t"), w, 2, 2, 50, 0)
+        for s in sheets:
+            rows += list(range(s.start, s.end))
+    assert sorted(rows) == list(range(333))
+
+
+# ------------------------------------------------------------------------------------------------------------ table dataset
+def test_table_dataset_reads_every_row_once_across_workers(tmp_path):
+    table = str(tmp_path / "t1")
+    _write_table(table, 0, 4, 250)
+    assert get_table_size(table) == 1000
+    seen = []
+    for w in range(2):
+        ds = OdpsDataset(64, worker_idx=w, worker_num=2, read_threads_num=2)
+        ds.add_path(table)
+        ds.varlen_feature("items")
+        ds.fixedlen_feature("uid")
+        ds.fixedlen_feature("score")
+        for b in ds:
+            uid = b["uid"].flatten()
+            assert torch.equal(b["items"].values().view(-1, 2)[:, 0], uid) and torch.equal(b["score"].flatten().long(), uid)
+            seen += uid.tolist()
+    assert sorted(seen) == list(range(1000))
+
+
+def test_table_dataset_resumes_from_io_state(tmp_path):
+    table = str(tmp_path / "t1")
+    _write_table(table, 0, 2, 300)
+
+    def make():
+        ds = OdpsDataset(50, read_threads_num=2)
+        ds.add_path(table)
+        ds.fixedlen_feature("uid")
+        return ds
+
+    full = [b["uid"].flatten().tolist() for b in make()]
+    ds = make()
+    it = iter(ds)
+    head = [next(it)["uid"].flatten().tolist() for _ in range(4)]
+    state = ds.dump_io_state()
+    ds2 = make()
+    ds2.load_io_state(state)
+    tail = [b["uid"].flatten().tolist() for b in ds2]
+    assert head + tail == full
+
+
+def test_registered_source_stands_in_for_a_table_service():
+    class FakeService:
+        def __init__(self):
+            self.calls = []
+
+        def size(self, table):
+            return 500
+
+        def read(self, table, start, end, columns):
+            self.calls.append((table, start, end))
+            return pa.table({"uid": pa.array(np.arange(start, end), pa.int64())}).select(columns)
+
+    svc = FakeService()
+    register_table_source("faketables", svc)
+    ds = OdpsDataset(128, worker_idx=1, worker_num=2, read_threads_num=1)
+    ds.add_path("faketables://proj.clicks")
+    ds.fixedlen_feature("uid")
+    rows = torch.cat([b["uid"].flatten() for b in ds]).tolist()
+    assert rows == list(range(250, 500)) and all(c[0] == "proj.clicks" for c in svc.calls)
+
+
+# ---------------------------------------------------------------------------------------------------------------- windows
+def test_window_io_mixes_tables_in_proportion_and_reads_all(tmp_path):
+    t1, t2 = str(tmp_path / "t1"), str(tmp_path / "t2")
+    _write_table(t1, 0, 4, 250)
+    _write_table(t2, 100000, 2, 250)
+    ds = make_odps_window_io(split_num=4)(90, read_threads_num=3)
+    ds.add_path(t1, (2, 3))
+    ds.add_path(t2, (1, 3))
+    ds.fixedlen_feature("uid")
+    got, windows, shares = [], 0, []
+    while True:
+        try:
+            if ds.next_window():
+                continue
+        except StopIteration:
+            break
+        windows += 1
+        for b in ds:
+            u = b["uid"].flatten()
+            got += u.tolist()
+            if len(u) == 90:
+                shares.append(float((u < 100000).float().mean()))
+    assert windows == 4 and sorted(got) == list(range(1000)) + list(range(100000, 100500))
+    assert shares and all(abs(s - 2 / 3) < 1e-6 for s in shares)
+    ds.reset()
+    assert ds.next_window() is False
+
+
+def test_window_io_state_resumes_at_the_next_window(tmp_path):
+    table = str(tmp_path / "t")
+    _write_table(table, 0, 2, 200)
+
+    def make():
+        ds = make_odps_window_io(row_num=100)(32, read_threads_num=2)
+        ds.add_path(table)
+        ds.fixedlen_feature("uid")
+        return ds
+
+    def drain(ds, limit=None):
+        out, n = [], 0
+        while limit is None or n < limit:
+            try:
+                if ds.next_window():
+                    continue
+            except StopIteration:
+                break
+            out.append(sorted(torch.cat([b["uid"].flatten() for b in ds]).tolist()))
+            n += 1
+        return out
+
+    full = drain(make())
+    assert sorted(sum(full, [])) == list(range(400))
+    a = make()
+    first = drain(a, 2)
+    b = make()
+    b.load_state_dict(a.state_dict())
+    assert first + drain(b) == full
+    with pytest.raises(ValueError):
+        make_odps_window_io(split_num=2, row_num=10)
+    with pytest.raises(ValueError):
+        make_odps_window_io()
+
+
+def test_sample_io_reads_one_contiguous_sample(tmp_path):
+    table = str(tmp_path / "t")
+    _write_table(table, 0, 2, 500)
+    ds = make_odps_sample_io(row_num=100, seed=3)(32, read_threads_num=2)
+    ds.add_path(table)
+    ds.fixedlen_feature("uid")
+    assert ds.next_window() is False
+    u = torch.cat([b["uid"].flatten() for b in ds])
+    assert len(u) == 100 and int(u.max() - u.min()) == 99
+    with pytest.raises(StopIteration):
+        ds.next_window()
+
+
+def test_stream_window_moves_forward_in_time(tmp_path):
+    stream = str(tmp_path / "stream")
+    for hh in range(4):
+        _write_table(f"{stream}/20250101{hh:02d}00", hh * 1000, 1, 100)
+    ds = make_lake_stream_window_io(step_mins=60, repeat_mins=60)(64)
+    ds.add_path(stream, _str_to_timestamp("20250101000000"), 120)
+    ds.fixedlen_feature("uid")
+    spans = []
+    for _ in range(5):
+        empty = ds.next_window()
+        u = [] if empty else torch.cat([b["uid"].flatten() for b in ds]).tolist()
+        spans.append((empty, len(u), (min(u), max(u)) if u else None))
+    assert spans[0] == (False, 200, (0, 1099)) and spans[1] == (False, 200, (1000, 2099)) and spans[3] == (False, 100, (3000, 3099))
+    assert spans[4] == (True, 0, None)                  # no data there yet: an empty window, not the end of the stream
+    # two workers split a window's entries between them
+    parts = []
+    for w in range(2):
+        d2 = make_lake_stream_window_io(step_mins=60)(64, worker_idx=w, worker_num=2)
+        d2.add_path(stream, _str_to_timestamp("20250101000000"), 240)
+        d2.fixedlen_feature("uid")
+        assert d2.next_window() is False
+        parts.append(torch.cat([b["uid"].flatten() for b in d2]).tolist())
+    assert sorted(parts[0] + parts[1]) == sorted(sum([list(range(h * 1000, h * 1000 + 100)) for h in range(4)], []))
+    assert parts[0] and parts[1]
+
+
+# ------------------------------------------------------------------------------------------------------------- trace table
+def test_trace_hook_writes_the_declared_table(tmp_path):
+    from recis_b200.hooks import TraceToOdpsHook, add_to_trace
+    import recis_b200.hooks.trace_to_odps_hook as same_module
+    assert same_module.TraceToOdpsHook is TraceToOdpsHook
+    out = str(tmp_path / "trace")
+    hook = TraceToOdpsHook({"output_dir": out, "partition": "dt=20250101,hh=10"}, ["uid", "score", "emb", "tag"],
+                           ["bigint", "double", "array<float>", "string"], worker_num=2, size_threshold=1000)
+    for s in range(5):
+        add_to_trace("uid", torch.arange(8) + s * 8)
+        add_to_trace("score", np.arange(8, dtype=np.float64) + s * 8)
+        add_to_trace("emb", (torch.arange(32).view(8, 4) + s).bfloat16())
+        add_to_trace("tag", [f"t{i}" for i in range(8)])
+        hook.after_step()
+    hook.end()
+    t = pads.dataset(os.path.join(out, "dt=20250101", "hh=10"), format="parquet").to_table().sort_by("uid")
+    assert t.num_rows == 40 == hook.rows_written and t.schema.names == ["uid", "score", "emb", "tag"]
+    assert t["uid"].to_pylist() == list(range(40)) and t["score"].to_pylist() == [float(i) for i in range(40)]
+    assert t.schema.field("emb").type == pa.list_(pa.float32()) and t["emb"][9].as_py() == [5.0, 6.0, 7.0, 8.0]
+    assert not [f for f in os.listdir(os.path.join(out, "dt=20250101", "hh=10")) if f.endswith(".tmp")]
+
+
+def test_trace_hook_reports_a_failing_writer(tmp_path):
+    from recis_b200.hooks.trace_hook import TraceToOdpsHook, add_to_trace, clear_trace_map
+
+    class BrokenSink:
+        def write_block(self, table):
+            raise IOError("sink is down")
+
+        def commit(self):
+            pass
+
+    import recis_b200.hooks.trace_hook as th
+    hook = TraceToOdpsHook({"sink": BrokenSink()}, ["uid"], ["bigint"], size_threshold=1)
+    for w in hook.writers:                       # no ten-second pauses between the retries in a test
+        w._write_block = lambda table, _w=w: _w.sink.write_block(table)
+    add_to_trace("uid", [1, 2, 3])
+    hook.after_step()
+    for w in hook.writers:
+        w.join(timeout=10)
+    add_to_trace("uid", [4])
+    with pytest.raises(ValueError):
+        hook.after_step()
+    clear_trace_map()
+    with pytest.raises(ValueError):
+        th.add_to_trace("x", 3.0)                # only tensors, arrays and lists are rows
+
+
+def test_trace_rejects_ragged_row_counts():
+    from recis_b200.hooks.trace_hook import rows_to_table
+    with pytest.raises(ValueError):
+        rows_to_table({"a": [1, 2, 3], "b": [1.0]}, ["a", "b"], ["bigint", "double"])
+    with pytest.raises(KeyError):
+        rows_to_table({"a": [1]}, ["a", "b"], ["bigint", "double"])
+
+
+@pytest.mark.gpu
+def test_trace_takes_device_tensors_without_blocking():
+    from recis_b200.hooks.trace_hook import add_to_trace, clear_trace_map, get_trace_map
+    x = torch.arange(1 << 16, device="cuda", dtype=torch.float32)
+    add_to_trace("x", x * 2)
+    got = get_trace_map()["x"]
+    assert isinstance(got, np.ndarray) and got[-1] == 2.0 * ((1 << 16) - 1)
+    clear_trace_map()
+
+
+# --------------------------------------------------------------------------------------------------------------- tracking
+def test_ml_tracker_hook_logs_steps_to_files(tmp_path):
+    from recis_b200.hooks import MLTrackerHook, add_to_ml_tracker
+    hook = MLTrackerHook("proj", "run", {"lr": 0.1, "layers": [512, 256]}, id="a1", root=str(tmp_path), log_metrics=True)
+    for step in range(3):
+        add_to_ml_tracker("loss", torch.tensor(0.5 / (step + 1)))
+        add_to_ml_tracker("hist", np.arange(3))
+        hook.after_step({"auc": 0.7 + step / 10}, step)
+    hook.end()
+    run = tmp_path / "proj" / "run-a1"
+    lines = [json.loads(l) for l in open(run / "metrics.jsonl")]
+    assert [l["step"] for l in lines] == [0, 1, 2] and lines[1]["loss"] == 0.25 and lines[2]["hist"] == [0, 1, 2]
+    assert abs(lines[2]["auc"] - 0.9) < 1e-9
+    cfg = json.load(open(run / "config.json"))
+    assert cfg["config"] == {"lr": 0.1, "layers": [512, 256]} and cfg["id"] == "a1"
+    assert json.load(open(run / "finished"))["steps"] == 3
+
+
+# ------------------------------------------------------------------------------------------------------------ model store
+def test_model_uri_parsing():
+    from recis_b200.utils.mos import parse_uri
+    assert parse_uri("model.rec.user_emb")["level"] == "model"
+    v = parse_uri("model.rec.user_emb/version=v1")
+    assert (v["level"], v["project"], v["model_name"], v["version"], v["ckpt_id"]) == ("version", "rec", "user_emb", "v1", None)
+    c = parse_uri("model.rec.user_emb/version=v1/ckpt_id=ckpt_10")
+    assert (c["level"], c["ckpt_id"]) == ("ckpt_id", "ckpt_10")
+    assert parse_uri("model.rec.user_emb/version=dt_max_pt/ckpt_id=x")["level"] == "version"
+    auto = parse_uri("model.rec.user_emb", auto_version=True)
+    assert len(auto["version"]) == 14 and auto["uri"].endswith("/version=" + auto["version"])
+    for bad in ("rec.user_emb", "model.rec", "model.rec.user emb", ""):
+        with pytest.raises(ValueError):
+            parse_uri(bad)
+
+
+def test_checkpoints_saved_under_a_model_uri_load_back_as_model_bank(tmp_path, monkeypatch):
+    from recis_b200.framework.checkpoint_manager import CheckpointManager, Saver
+    from recis_b200.utils.mos import Mos
+    monkeypatch.setenv("RECIS_MODEL_STORE", str(tmp_path / "store"))
+    torch.manual_seed(0)
+    model = torch.nn.Linear(4, 3)
+    saver = Saver(model, output_dir="model.rec.tower/version=v7", max_keep=2)
+    assert saver._output_dir == str(tmp_path / "store" / "rec" / "tower" / "version=v7")
+    for step in (10, 20, 30):
+        with torch.no_grad():
+            model.weight.fill_(float(step))
+        saver.save(f"ckpt_{step}")
+    store = Mos("model.rec.tower/version=v7", model_bank_path=True)
+    assert store.list_ckpts() == ["ckpt_20", "ckpt_30"] and store.real_physical_path.endswith("ckpt_30")
+    assert Mos("model.rec.tower", True).uri_info["version"] == "v7"                  # newest version, newest checkpoint
+    assert Mos("model.rec.tower/version=v7/ckpt_id=ckpt_20", True).real_physical_path.endswith("ckpt_20")
+    with pytest.raises(FileNotFoundError):
+        Mos("model.rec.tower/version=v7/ckpt_id=ckpt_10", True)                      # removed by max_keep, and forgotten
+    other = torch.nn.Linear(4, 3)
+    mgr = CheckpointManager(Saver(other, output_dir=str(tmp_path / "elsewhere")), save_interval=100)
+    mgr.load_model_bank([{"path": "model.rec.tower/version=v7/ckpt_id=ckpt_20", "load": ["dense"]}])
+    assert float(other.weight.detach()[0, 0]) == 20.0
+
+
+def test_info_module_matches_the_reference_names():
+    import recis_b200.__info__ as info
+    assert info.is_internal_enabled() == 0 and isinstance(info.INTERVAL_VERSION, str)
