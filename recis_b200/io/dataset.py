@@ -27,6 +27,11 @@ from .synthetic import SyntheticSpec
 _LEN_KIND = {"fixed": 0, "poisson": 1, "geometric": 2, "uniform": 3}
 
 
+def is_string_dtype(arr) -> bool:
+    """Whether a numpy array holds strings: unicode, bytes or objects (``recis/io/dataset_base.py:23-31``)."""
+    return arr.dtype.kind in ("U", "S", "O")
+
+
 class DatasetBase:
     """Iterable of batches with a restorable position.
 

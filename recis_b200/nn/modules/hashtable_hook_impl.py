@@ -14,7 +14,29 @@ import torch
 from ..hashtable_hook import AdmitHook, FilterHook
 
 
-class ReadOnlyHookImpl:
+class BaseAdmitHookImpl:
+    """Base of admission policies (``recis/nn/modules/hashtable_hook_impl.py:193-210``). A policy is two attributes that the
+    table's lookup reads: ``readonly`` (never insert) and ``threshold`` (occurrences before an id is given a row)."""
+
+    readonly = False
+    threshold = 1
+
+    def __init__(self, **kwargs) -> None:
+        pass
+
+
+class BaseFilterHookImpl:
+    """Base of eviction policies (``recis/nn/modules/hashtable_hook_impl.py:259-290``): ``before_lookup`` sees the ids of a
+    lookup, ``do_filter`` removes what has expired."""
+
+    def before_lookup(self, *args, **kwargs):
+        pass
+
+    def do_filter(self, *args, **kwargs):
+        pass
+
+
+class ReadOnlyHookImpl(BaseAdmitHookImpl):
     """Lookups do not insert; unknown ids read as zeros and receive no gradient."""
 
     readonly = True
@@ -24,7 +46,7 @@ class ReadOnlyHookImpl:
         pass
 
 
-class CountAdmitHookImpl:
+class CountAdmitHookImpl(BaseAdmitHookImpl):
     """An id is given a row at its ``threshold``-th occurrence; before that it reads as zeros."""
 
     readonly = False
@@ -42,7 +64,7 @@ def admit_params(hook):
     return bool(hook.readonly), int(hook.threshold)
 
 
-class GlobalStepFilterHookImpl(torch.nn.Module):
+class GlobalStepFilterHookImpl(torch.nn.Module, BaseFilterHookImpl):
     """TTL eviction: a row is expired when ``last_seen < global_step - filter_step``.
 
     ``update_step`` advances the global step (a device scalar the lookup kernel reads, and a host mirror so

@@ -15,6 +15,17 @@ class _MaxLevel(logging.Filter):
         return record.levelno <= self.level
 
 
+class SingleLevelFilter(logging.Filter):
+    """Passes only records of ``passlevel``, or with ``reject`` everything but them (``recis/utils/logger.py:6-48``)."""
+
+    def __init__(self, passlevel, reject):
+        super().__init__()
+        self.passlevel, self.reject = passlevel, reject
+
+    def filter(self, record):
+        return (record.levelno != self.passlevel) if self.reject else (record.levelno == self.passlevel)
+
+
 class Logger:
     _FMT = "%(asctime)s %(levelname)s [%(name)s] %(message)s"
 
