@@ -360,3 +360,20 @@ def test_checkpoints_saved_under_a_model_uri_load_back_as_model_bank(tmp_path, m
 def test_info_module_matches_the_reference_names():
     import recis_b200.__info__ as info
     assert info.is_internal_enabled() == 0 and isinstance(info.INTERVAL_VERSION, str)
+
+
+def test_table_export_to_orc_shards_round_trips(tmp_path):
+    from recis_b200.io import OrcDataset
+    from recis_b200.io.table_to_orc import main
+    table = str(tmp_path / "t")
+    _write_table(table, 0, 3, 100)
+    out = str(tmp_path / "out")
+    main(["--table", table, "--output", out, "--nfiles", "4", "--threads", "2"])
+    files = sorted(os.listdir(out))
+    assert files == [f"part-{i:05d}.orc" for i in range(4)]
+    ds = OrcDataset(64, native_reader=False)
+    ds.add_paths([os.path.join(out, f) for f in files])
+    ds.fixedlen_feature("uid")
+    ds.varlen_feature("items")
+    rows = torch.cat([b["uid"].flatten() for b in ds]).tolist()
+    assert rows == list(range(300))
