@@ -40,6 +40,7 @@ class TrainingArguments:
     max_to_keep: int = 5
     save_concurrency_per_rank: int = 4
     stop_check_interval: int = 1
+    max_empty_windows: int = 1000      # windowed datasets: this many empty windows in a row end the data (streams have no last window)
     heartbeat_timeout: float = 0.0     # > 0: ranks exchange heartbeats; a peer silent for this many seconds raises PeerLostError
 
 
@@ -92,6 +93,12 @@ class Trainer:
         self.checkpoint_manager = CheckpointManager(saver=saver, save_interval=args.save_steps)
         if self.train_dataset is not None and hasattr(self.train_dataset, "dump_io_state"):
             saver.register_io_state("train_io", self.train_dataset)
+        # a windowed dataset's position (which window comes next) is saved with the checkpoint and restored with it
+        # (``recis/framework/trainer.py:199-208``)
+        if self._windowed(self.train_dataset):
+            saver.register_for_checkpointing("train_window_io", self.train_dataset)
+        if self._windowed(self.eval_dataset):
+            saver.register_for_checkpointing("eval_window_io", self.eval_dataset)
         if self.dense_optimizer is not None:
             saver.register_for_checkpointing("dense_optimizer", self.dense_optimizer)
         if self.dense_lr_scheduler is not None:
@@ -116,6 +123,8 @@ class Trainer:
         for hook in self.hooks:
             hook.before_train()
         for epoch in range(self.args.train_epoch or 1):
+            if epoch > 0 and self._windowed(self.train_dataset) and hasattr(self.train_dataset, "reset"):
+                self.train_dataset.reset()          # a further epoch starts at the first window again
             for hook in self.hooks:
                 hook.before_epoch()
             self._train_loop(self.args.train_steps if train_steps is None else train_steps, epoch=epoch)
@@ -151,16 +160,56 @@ class Trainer:
             return bool(item[0]), item[1]
         return False, item
 
+    # ---- windowed datasets (``next_window()`` until StopIteration; ``recis/framework/trainer.py:322-345``)
+    @staticmethod
+    def _windowed(dataset) -> bool:
+        return dataset is not None and hasattr(dataset, "next_window")
+
+    def get_new_window_iter(self, dataset):
+        """Iterator over the next window that has data, or None when the dataset has no further window. A stream has no last
+        window: after ``max_empty_windows`` (a ``TrainingArguments`` field or 1000) empty ones in a row the data is taken to
+        have ended rather than skipping ahead for ever."""
+        if not self._windowed(dataset):
+            raise TypeError("dataset must be window_io")
+        limit = int(getattr(self.args, "max_empty_windows", 1000) or 1000)
+        empty = 0
+        while True:
+            try:
+                need_skip = dataset.next_window()
+            except StopIteration:
+                logger.info("Window IO Finish")
+                return None
+            offset = int(dataset._read_offset[0]) if hasattr(dataset, "_read_offset") else -1
+            if not need_skip:
+                logger.info(f"Next window, offset = {offset}")
+                return iter(dataset)
+            logger.info(f"Skip for window, offset = {offset}")
+            empty += 1
+            if empty >= limit:
+                logger.warning(f"{empty} empty windows in a row: treating the data as finished")
+                return None
+
+    def _first_iter(self, dataset):
+        return self.get_new_window_iter(dataset) if self._windowed(dataset) else iter(dataset)
+
+    def _next_of(self, dataset, iterator):
+        """``(stop, batch, iterator)``: the next batch, moving on to the dataset's next window when the current one ends."""
+        while True:
+            stop, data = (True, None) if iterator is None else self._next(iterator)
+            if not stop or not self._windowed(dataset) or iterator is None:
+                return stop, data, iterator
+            iterator = self.get_new_window_iter(dataset)
+
     def evaluate(self, eval_steps=None, _end_hooks=True):
         self.restore()
-        iterator = iter(self.eval_dataset)
+        iterator = self._first_iter(self.eval_dataset)
         eval_steps = self.args.eval_steps if eval_steps is None else eval_steps
         lstep = 0
         for hook in self.hooks:
             hook.before_evaluate()
         self.model.eval()
         while eval_steps is None or lstep < eval_steps:
-            stop, data = self._next(iterator)
+            stop, data, iterator = self._next_of(self.eval_dataset, iterator)
             if self.sync_exit_flag(stop):
                 break
             if self.data_to_cuda:
@@ -178,11 +227,11 @@ class Trainer:
 
     def _train_loop(self, max_steps=None, epoch=1):
         self.model.train()
-        iterator = iter(self.train_dataset)
+        iterator = self._first_iter(self.train_dataset)
         lstep = 0
         check = max(int(self.args.stop_check_interval), 1)
         while max_steps is None or lstep < max_steps:
-            stop, data = self._next(iterator)
+            stop, data, iterator = self._next_of(self.train_dataset, iterator)
             if lstep % check == 0 or stop:
                 stop = self.sync_exit_flag(stop)
             if stop:

@@ -377,3 +377,82 @@ def test_table_export_to_orc_shards_round_trips(tmp_path):
     ds.varlen_feature("items")
     rows = torch.cat([b["uid"].flatten() for b in ds]).tolist()
     assert rows == list(range(300))
+
+
+# ------------------------------------------------------------------------------------------------- trainer over windows
+def _window_trainer(tmp_path, table, out, seen, train_steps=None, hooks=()):
+    from recis_b200.framework.trainer import Trainer, TrainingArguments
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption, filter_out_sparse_param
+    from recis_b200.nn.modules.hashtable import HashtableRegister
+    from recis_b200.nn.initializers import ConstantInitializer
+    from recis_b200.optim import SparseAdagrad
+    HashtableRegister().clear()
+    torch.manual_seed(0)
+
+    class Model(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = EmbeddingEngine({"items": EmbeddingOption(embedding_dim=4, shared_name="items", device="cpu", combiner="sum",
+                                                                 initializer=ConstantInitializer(0.1))})
+            self.head = torch.nn.Linear(4, 1)
+
+        def forward(self, batch):
+            seen.extend(batch["uid"].flatten().tolist())
+            e = self.emb({"items": batch["items"]})["items"]
+            return (self.head(e).squeeze(-1) - batch["score"].flatten() * 1e-3).pow(2).mean()
+
+    ds = make_odps_window_io(row_num=100)(32, read_threads_num=2)
+    ds.add_path(table)
+    ds.varlen_feature("items")
+    ds.fixedlen_feature("uid")
+    ds.fixedlen_feature("score")
+    model = Model()
+    args = TrainingArguments(output_dir=out, train_steps=train_steps, save_steps=1000, log_steps=1000)
+    return Trainer(model=model, args=args, train_dataset=ds, dense_optimizers=(torch.optim.SGD(model.head.parameters(), lr=1e-3), None),
+                   sparse_optimizer=SparseAdagrad(filter_out_sparse_param(model), lr=0.01), hooks=list(hooks)), ds
+
+
+def test_trainer_walks_every_window_and_resumes_at_the_next_one(tmp_path):
+    table = str(tmp_path / "t")
+    _write_table(table, 0, 2, 200)
+    seen = []
+    trainer, ds = _window_trainer(tmp_path, table, str(tmp_path / "run_all"), seen)
+    trainer.train()
+    assert sorted(seen) == list(range(400))                          # four windows of 100 rows, every row once
+
+    # stop after the first window's batches; the checkpoint carries the window position
+    first = []
+    trainer, ds = _window_trainer(tmp_path, table, str(tmp_path / "run_split"), first, train_steps=4)
+    trainer.train()
+    assert sorted(first) == list(range(100)) and int(ds.state_dict()["read_offset"][0]) == 2
+    rest = []
+    trainer, ds = _window_trainer(tmp_path, table, str(tmp_path / "run_split"), rest)
+    trainer.train()
+    assert sorted(rest) == list(range(100, 400))
+
+
+def test_trainer_traces_and_tracks_through_hooks(tmp_path):
+    from recis_b200.hooks import Hook, MLTrackerHook, TraceToOdpsHook, add_to_ml_tracker, add_to_trace
+    table = str(tmp_path / "t")
+    _write_table(table, 0, 1, 128)
+    seen = []
+
+    class Name(Hook):
+        """Names the step's values before the trace and tracker hooks (registered after it) collect them."""
+        done = 0
+
+        def after_step(self, metrics=None, global_step=0):
+            rows = seen[Name.done:]                       # this step's samples
+            Name.done = len(seen)
+            add_to_trace("uid", rows)
+            add_to_trace("loss", [float(metrics["loss"])] * len(rows))
+            add_to_ml_tracker("loss", metrics["loss"])
+
+    hooks = [Name(), TraceToOdpsHook({"output_dir": str(tmp_path / "trace")}, ["uid", "loss"], ["bigint", "double"]),
+             MLTrackerHook("p", "r", {}, id="1", root=str(tmp_path / "track"))]
+    trainer, _ = _window_trainer(tmp_path, table, str(tmp_path / "run"), seen, hooks=hooks)
+    trainer.train()
+    t = pads.dataset(str(tmp_path / "trace"), format="parquet").to_table()
+    assert sorted(t["uid"].to_pylist()) == list(range(128))
+    lines = [json.loads(l) for l in open(tmp_path / "track" / "p" / "r-1" / "metrics.jsonl")]
+    assert len(lines) == 5 and all("loss" in l for l in lines)          # windows of 100 and 28 rows: 4 + 1 batches of up to 32
