@@ -130,12 +130,18 @@ class FileStreamSource:
                 out.append((ts, os.path.join(path, name)))
         return sorted(out)
 
+    def read_entry(self, entry: str, columns: Optional[Sequence[str]] = None):
+        """One listed entry (a file, or a directory of files) as a table; None when it holds nothing."""
+        import pyarrow as pa
+        parts = [_read_file(f, columns) for f in _columnar_files(entry)]
+        if not parts:
+            return None
+        return pa.concat_tables(parts) if len(parts) > 1 else parts[0]
+
     def read_range(self, path: str, begin_us: int, end_us: int, columns: Optional[Sequence[str]] = None):
         import pyarrow as pa
-        parts = []
-        for ts, entry in self.entries(path):
-            if begin_us <= ts < end_us:
-                parts += [_read_file(f, columns) for f in _columnar_files(entry)]
+        parts = [self.read_entry(entry, columns) for ts, entry in self.entries(path) if begin_us <= ts < end_us]
+        parts = [p for p in parts if p is not None]
         if not parts:
             return None
         return pa.concat_tables(parts) if len(parts) > 1 else parts[0]

@@ -371,12 +371,12 @@ class LakeStreamDataset(OrcDataset):
         ``worker_num``-th block of rows."""
         import pyarrow as pa
         src, name = resolve_stream_source(path)
-        if hasattr(src, "entries"):
+        if hasattr(src, "entries") and hasattr(src, "read_entry"):
             entries = [e for e in src.entries(name) if begin <= e[0] < end]
             if self.shuffle:
                 random.Random(self._shuffle_seed * 1000003 + begin // US).shuffle(entries)
             mine = entries[self.worker_idx::self.worker_num]
-            parts = [src.read_range(name, ts, ts + 1, self._columns()) for ts, _ in mine]
+            parts = [src.read_entry(entry, self._columns()) for _ts, entry in mine]
             parts = [p for p in parts if p is not None and p.num_rows]
             return pa.concat_tables(parts) if parts else None
         table = src.read_range(name, begin, end, self._columns())
