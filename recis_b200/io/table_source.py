@@ -61,8 +61,27 @@ def _read_file(path: str, columns: Optional[Sequence[str]]):
 class FileTableSource:
     """Columnar files as one row-numbered table."""
 
+    _CACHED_FILES = 4                # decoded files kept: consecutive slices of one file decode it once
+
     def __init__(self):
+        import collections
+        import threading
         self._index: Dict[str, Tuple[List[str], List[int]]] = {}     # table -> (files, cumulative row counts)
+        self._decoded = collections.OrderedDict()                     # (file, columns) -> pyarrow.Table, most recent last
+        self._lock = threading.Lock()
+
+    def _file_table(self, path: str, columns: Optional[Sequence[str]]):
+        key = (path, tuple(columns) if columns else None)
+        with self._lock:
+            if key in self._decoded:
+                self._decoded.move_to_end(key)
+                return self._decoded[key]
+        table = _read_file(path, columns)
+        with self._lock:
+            self._decoded[key] = table
+            while len(self._decoded) > self._CACHED_FILES:
+                self._decoded.popitem(last=False)
+        return table
 
     def _files(self, table: str):
         if table not in self._index:
@@ -89,11 +108,11 @@ class FileTableSource:
         while i < len(files) and start < end:
             base = cum[i - 1] if i else 0
             take = min(end, cum[i]) - start
-            parts.append(_read_file(files[i], columns).slice(start - base, take))
+            parts.append(self._file_table(files[i], columns).slice(start - base, take))
             start += take
             i += 1
         if not parts:
-            return _read_file(files[0], columns).slice(0, 0)
+            return self._file_table(files[0], columns).slice(0, 0)
         return pa.concat_tables(parts) if len(parts) > 1 else parts[0]
 
 
