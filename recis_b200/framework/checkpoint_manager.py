@@ -6,11 +6,20 @@ Directory layout (same as the reference):
 ``model.pt`` (dense state dict), ``extra.pt`` (registered extras incl. ``global_step`` and the dense optimizer),
 ``io_state_<rank>.pt`` + ``io_state_count``. ``load_by_config`` takes ``{"load": [...], "exclude": [...], "strict": bool}``
 over the parts ``sparse, dense, extra, sparse_opt, io_state``.
+
+``output_dir`` (and a model-bank ``path``) may also be a URL of any file system that fsspec knows (``hdfs://``, ``s3://``,
+``memory://`` ...); the reference routes its Python-side files through fsspec but registers the local file system only
+(``recis/framework/filesystem.py:18-64``). The native writers and readers work on local files, so a remote directory is served
+through a staging directory (``$RECIS_STAGING_DIR`` or a temporary one, one sub-directory per rank): a checkpoint is written
+there, every rank uploads the files it wrote, rank 0 uploads the ``checkpoint`` listing last (after a barrier), and pruned
+checkpoints are removed remotely as well; loading downloads the listing and the wanted checkpoint first.
 """
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
+import tempfile
 from typing import Optional
 
 import torch
@@ -22,6 +31,35 @@ from ..utils.logger import Logger
 from ..utils.mos import Mos
 
 logger = Logger(__name__)
+
+
+def _is_remote(path) -> bool:
+    p = str(path)
+    return "://" in p and not p.startswith("file://")
+
+
+def _remote_fs(url: str):
+    import fsspec
+    fs, root = fsspec.core.url_to_fs(str(url))
+    return fs, root.rstrip("/")
+
+
+_STAGING = None
+
+
+def _staging_root() -> str:
+    """Local directory that stands in for remote ones, one per rank and process tree: ``$RECIS_STAGING_DIR/rank<r>`` or a
+    temporary directory."""
+    global _STAGING
+    if _STAGING is None:
+        base = os.environ.get("RECIS_STAGING_DIR")
+        rank = os.environ.get("RANK", "0")
+        if base:
+            _STAGING = os.path.join(base, f"rank{rank}")
+            os.makedirs(_STAGING, exist_ok=True)
+        else:
+            _STAGING = tempfile.mkdtemp(prefix=f"recis_staging_rank{rank}_")
+    return _STAGING
 
 
 class Saver:
@@ -36,6 +74,11 @@ class Saver:
         # directory and every checkpoint saved or removed is recorded there (``recis/framework/checkpoint_manager.py:73-78``)
         self._mos = Mos(output_dir) if str(output_dir).startswith("model.") else None
         self._output_dir = self._mos.real_physical_path if self._mos else output_dir
+        self._remote = None                                   # (fsspec file system, root path) of a remote output_dir
+        if _is_remote(self._output_dir):
+            self._remote = _remote_fs(self._output_dir)
+            self._output_dir = os.path.join(_staging_root(), "out-" + hashlib.sha1(str(output_dir).encode()).hexdigest()[:12])
+            os.makedirs(self._output_dir, exist_ok=True)
         self._sparse_optim = sparse_optim
         self._concurrency = concurrency
         self._io_state = {}
@@ -92,6 +135,10 @@ class Saver:
                 old = self._checkpoint_version_list.pop(0)
                 logger.info(f"Remove checkpoint {os.path.join(self._output_dir, old)}")
                 shutil.rmtree(os.path.join(self._output_dir, old), ignore_errors=True)
+                if self._remote:
+                    fs, root = self._remote
+                    if fs.exists(f"{root}/{old}"):
+                        fs.rm(f"{root}/{old}", recursive=True)
                 with open(os.path.join(self._output_dir, self._checkpoint_file)) as f:
                     remains = [l.strip() for l in f.read().split("\n") if l.strip() and l.strip() != old]
                 with open(os.path.join(self._output_dir, self._checkpoint_file), "w") as f:
@@ -102,6 +149,49 @@ class Saver:
                 self._mos.ckpt_update(ckpt_id=ckpt_id, path=ckpt_path)
         if torch.cuda.is_available():
             torch.cuda.synchronize()
+        if self._remote:
+            self._upload(ckpt_id, shard_id)
+
+    def _upload(self, ckpt_id: str, shard_id: int):
+        """Copy what this rank wrote of ``ckpt_id`` to the remote directory; the listing goes last, from rank 0, once every rank
+        has uploaded (a reader that sees a checkpoint listed finds all of its files)."""
+        fs, root = self._remote
+        local = os.path.join(self._output_dir, ckpt_id)
+        for dirpath, _dirs, files in os.walk(local):
+            rel = os.path.relpath(dirpath, self._output_dir)
+            fs.makedirs(f"{root}/{rel}", exist_ok=True)
+            for f in files:
+                fs.put_file(os.path.join(dirpath, f), f"{root}/{rel}/{f}")
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier()
+        if shard_id == 0:
+            fs.put_file(os.path.join(self._output_dir, self._checkpoint_file), f"{root}/{self._checkpoint_file}")
+
+    def _download(self, fs, root: str, ckpt_id: Optional[str], local_root: str) -> Optional[str]:
+        """Bring the listing and one checkpoint (the last listed when ``ckpt_id`` is None) from ``root`` into ``local_root``;
+        returns the checkpoint id, or None when the remote directory lists none."""
+        os.makedirs(local_root, exist_ok=True)
+        listing = f"{root}/{self._checkpoint_file}"
+        if ckpt_id is None:
+            if not fs.exists(listing):
+                return None
+            fs.get_file(listing, os.path.join(local_root, self._checkpoint_file))
+            lines = [l.strip() for l in open(os.path.join(local_root, self._checkpoint_file)).read().split("\n") if l.strip()]
+            if not lines:
+                return None
+            ckpt_id = lines[-1]
+        if not fs.exists(f"{root}/{ckpt_id}"):
+            return None
+        for dirpath, _dirs, files in fs.walk(f"{root}/{ckpt_id}"):
+            # file systems differ in whether listed paths keep the leading slash: compare without it
+            base, here = root.strip("/"), dirpath.strip("/")
+            rel = here[len(base):].strip("/") if here.startswith(base) else ckpt_id
+            os.makedirs(os.path.join(local_root, rel), exist_ok=True)
+            for f in files:
+                target = os.path.join(local_root, rel, f)
+                if not os.path.exists(target) or os.path.getsize(target) != fs.size(f"{dirpath}/{f}"):
+                    fs.get_file(f"{dirpath}/{f}", target)
+        return ckpt_id
 
     # ---- the pieces of save(), callable on their own as in the reference (``recis/framework/checkpoint_manager.py:222-274``)
     def save_sparse_params(self, shard_id: int, shard_num: int, ckpt_path: str, sparse_state_dict: dict, concurrent: int = 16,
@@ -170,7 +260,21 @@ class Saver:
         if direct_path:
             if not ckpt_path:
                 return False
+            if _is_remote(ckpt_path):                       # a model bank on a remote file system: fetch it, then load locally
+                fs, root = _remote_fs(ckpt_path)
+                parent, name = root.rstrip("/").rsplit("/", 1)
+                local_root = os.path.join(_staging_root(), "bank-" + hashlib.sha1(str(ckpt_path).encode()).hexdigest()[:12])
+                if self._download(fs, parent, name, local_root) is None:
+                    raise FileNotFoundError(f"no checkpoint at {ckpt_path}")
+                ckpt_path = os.path.join(local_root, name)
         else:
+            if ckpt_path is None and self._remote:
+                fs, root = self._remote
+                found = self._download(fs, root, ckpt_id, self._output_dir)
+                if found is None:
+                    logger.info(f"Checkpoint not found in {root}")
+                    return False
+                ckpt_id = found
             ckpt_path = ckpt_path or self._output_dir
             if ckpt_id is None:
                 listing = os.path.join(ckpt_path, self._checkpoint_file)

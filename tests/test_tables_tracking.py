@@ -456,3 +456,53 @@ def test_trainer_traces_and_tracks_through_hooks(tmp_path):
     assert sorted(t["uid"].to_pylist()) == list(range(128))
     lines = [json.loads(l) for l in open(tmp_path / "track" / "p" / "r-1" / "metrics.jsonl")]
     assert len(lines) == 5 and all("loss" in l for l in lines)          # windows of 100 and 28 rows: 4 + 1 batches of up to 32
+
+
+# ------------------------------------------------------------------------------------------ checkpoints on a remote file system
+def test_checkpoints_on_a_remote_file_system_round_trip(tmp_path, monkeypatch):
+    import fsspec
+    from recis_b200.framework.checkpoint_manager import CheckpointManager, Saver
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.nn.modules.hashtable import HashtableRegister
+    from recis_b200.ragged import RaggedTensor
+    import recis_b200.framework.checkpoint_manager as cm
+    fs = fsspec.filesystem("memory")
+    url = "memory://ckpts/run1"
+
+    def build(stage):
+        monkeypatch.setattr(cm, "_STAGING", str(tmp_path / stage))
+        os.makedirs(tmp_path / stage, exist_ok=True)
+        HashtableRegister().clear()
+        torch.manual_seed(0)
+
+        class M(torch.nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.emb = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=4, shared_name="a", device="cpu", initializer=NormalInitializer(0, 1))})
+                self.head = torch.nn.Linear(4, 1)
+
+        return M()
+
+    ids = RaggedTensor(torch.arange(20, dtype=torch.int64), [torch.arange(21, dtype=torch.int32)])
+    m = build("stage_a")
+    rows = m.emb({"a": ids})["a"].detach().clone()
+    saver = Saver(m, output_dir=url, max_keep=2)
+    for step in (1, 2, 3):
+        with torch.no_grad():
+            m.head.weight.fill_(float(step))
+        saver.save(f"ckpt_{step}")
+    assert fs.cat("/ckpts/run1/checkpoint").decode().split() == ["ckpt_2", "ckpt_3"]
+    assert not fs.exists("/ckpts/run1/ckpt_1") and fs.exists("/ckpts/run1/ckpt_3/model.pt")
+    assert any(f.endswith(".safetensors") for f in fs.ls("/ckpts/run1/ckpt_3", detail=False))
+
+    # a fresh process (an empty staging directory) restores from the remote directory
+    m2 = build("stage_b")
+    mgr = CheckpointManager(Saver(m2, output_dir=url), save_interval=100)
+    mgr.restore()
+    assert float(m2.head.weight.detach()[0, 0]) == 3.0
+    assert torch.equal(m2.emb({"a": ids})["a"].detach(), rows)
+    # and an older checkpoint of it serves as a model bank for another model
+    m3 = build("stage_c")
+    CheckpointManager(Saver(m3, output_dir=str(tmp_path / "local_out")), 100).load_model_bank([{"path": url + "/ckpt_2", "load": ["dense"]}])
+    assert float(m3.head.weight.detach()[0, 0]) == 2.0
