@@ -506,3 +506,73 @@ def test_checkpoints_on_a_remote_file_system_round_trip(tmp_path, monkeypatch):
     m3 = build("stage_c")
     CheckpointManager(Saver(m3, output_dir=str(tmp_path / "local_out")), 100).load_model_bank([{"path": url + "/ckpt_2", "load": ["dense"]}])
     assert float(m3.head.weight.detach()[0, 0]) == 2.0
+
+
+def _register_shared_fs():
+    """A second name for the local file system, so that child processes share a 'remote' directory the checkpoint code treats as
+    remote (a URL that is not file://)."""
+    import fsspec
+    from fsspec.implementations.local import LocalFileSystem
+
+    class SharedFS(LocalFileSystem):
+        protocol = "sharedtest"
+
+        @classmethod
+        def _strip_protocol(cls, path):
+            path = str(path)
+            return super()._strip_protocol(path[len("sharedtest://"):] if path.startswith("sharedtest://") else path)
+
+    fsspec.register_implementation("sharedtest", SharedFS, clobber=True)
+
+
+def _remote_ckpt_ranks_fn(rank, world, remote_dir, stage_dir):
+    import torch
+    import recis_b200.framework.checkpoint_manager as cm
+    from recis_b200.framework.checkpoint_manager import CheckpointManager, Saver
+    from recis_b200.nn import EmbeddingEngine, EmbeddingOption
+    from recis_b200.nn.initializers import NormalInitializer
+    from recis_b200.nn.modules.hashtable import HashtableRegister
+    from recis_b200.ragged import RaggedTensor
+    _register_shared_fs()
+    url = "sharedtest://" + remote_dir
+
+    def build():
+        HashtableRegister().clear()
+        torch.manual_seed(3)
+
+        class M(torch.nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.emb = EmbeddingEngine({"a": EmbeddingOption(embedding_dim=4, shared_name="a", device="cpu", initializer=NormalInitializer(0, 1))})
+                self.head = torch.nn.Linear(4, 1)
+
+        return M()
+
+    ids = RaggedTensor(torch.arange(40, dtype=torch.int64) * 7 + rank, [torch.arange(41, dtype=torch.int32)])
+    cm._STAGING = os.path.join(stage_dir, f"save_rank{rank}")
+    os.makedirs(cm._STAGING, exist_ok=True)
+    m = build()
+    rows = m.emb({"a": ids})["a"].detach().clone()
+    with torch.no_grad():
+        m.head.weight.fill_(5.0)
+    CheckpointManager(Saver(m, output_dir=url), save_interval=100).save()
+    cm._STAGING = os.path.join(stage_dir, f"load_rank{rank}")          # as a fresh job: nothing staged locally
+    os.makedirs(cm._STAGING, exist_ok=True)
+    m2 = build()
+    CheckpointManager(Saver(m2, output_dir=url), save_interval=100).restore()
+    again = m2.emb({"a": ids})["a"].detach()
+    return {"same_rows": bool(torch.equal(rows, again)), "weight": float(m2.head.weight.detach()[0, 0]),
+            "remote": sorted(os.listdir(os.path.join(remote_dir, "ckpt_0")))}
+
+
+def test_two_ranks_checkpoint_through_a_remote_directory(tmp_path):
+    import sys
+    sys.path.insert(0, os.path.dirname(__file__))
+    from multirank import run_ranks
+    remote, stage = str(tmp_path / "remote"), str(tmp_path / "stage")
+    os.makedirs(remote)
+    res = run_ranks(_remote_ckpt_ranks_fn, 2, "gloo", args=(remote, stage), env={"RECIS_COMM": "nccl"})
+    assert all(r["same_rows"] and r["weight"] == 5.0 for r in res)
+    files = res[0]["remote"]
+    assert "model.pt" in files and "index" in files and sum(f.endswith(".safetensors") for f in files) >= 2
+    assert open(os.path.join(remote, "checkpoint")).read().split() == ["ckpt_0"]
