@@ -576,3 +576,28 @@ def test_two_ranks_checkpoint_through_a_remote_directory(tmp_path):
     files = res[0]["remote"]
     assert "model.pt" in files and "index" in files and sum(f.endswith(".safetensors") for f in files) >= 2
     assert open(os.path.join(remote, "checkpoint")).read().split() == ["ckpt_0"]
+
+
+def test_trace_and_tracker_write_to_object_stores():
+    """Stores without rename-in-place or append (here fsspec's in-memory one) get whole parts and a rewritten log."""
+    import fsspec
+    from recis_b200.hooks import MLTrackerHook, TraceToOdpsHook, add_to_ml_tracker, add_to_trace
+    fs = fsspec.filesystem("memory")
+    hook = TraceToOdpsHook({"output_dir": "memory://traces/run", "partition": "dt=1"}, ["uid"], ["bigint"], size_threshold=1)
+    for s in range(3):
+        add_to_trace("uid", [s * 2, s * 2 + 1])
+        hook.after_step()
+    hook.end()
+    parts = [p for p in fs.ls("/traces/run/dt=1", detail=False) if p.endswith(".parquet")]
+    rows = []
+    for p in parts:
+        with fs.open(p, "rb") as f:
+            rows += pq.read_table(f)["uid"].to_pylist()
+    assert len(parts) == 3 and sorted(rows) == list(range(6))
+    tracker = MLTrackerHook("p", "r", {"k": 1}, id="7", root="memory://tracking")
+    for step in range(3):
+        add_to_ml_tracker("v", step * 1.5)
+        tracker.after_step(None, step)
+    tracker.end()
+    lines = [json.loads(l) for l in fs.cat("/tracking/p/r-7/metrics.jsonl").decode().splitlines()]
+    assert [l["v"] for l in lines] == [0.0, 1.5, 3.0] and fs.exists("/tracking/p/r-7/finished")
