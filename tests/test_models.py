@@ -104,6 +104,10 @@ def test_examples_run_on_cpu(tmp_path):
     log = _run_example("examples/deepctr/run.py", "--data", str(tmp_path / "orc"), "--device", "cpu", "--batch", "64",
                        "--output-dir", str(tmp_path / "ctr"))
     assert "CoalescedHashtable_" in log
+    log = _run_example("examples/deepctr/run.py", "--data", str(tmp_path / "orc"), "--device", "cpu", "--batch", "64", "--windows", "2",
+                       "--trace-dir", str(tmp_path / "trace"), "--output-dir", str(tmp_path / "ctr_windows"))
+    import pyarrow.dataset as pads
+    assert "Window IO Finish" in log and pads.dataset(str(tmp_path / "trace" / "rank=0"), format="parquet").count_rows() == 512
     log = _run_example("examples/seq2seq/run.py", "--device", "cpu", "--steps", "3", "--batch", "4", "--max-len", "16")
     assert "step    2" in log
 
@@ -175,3 +179,9 @@ def test_examples_run_as_two_cpu_ranks(tmp_path):
     _run_example("examples/deepctr/make_orc_data.py", "--out", str(tmp_path / "orc"), "--shards", "2", "--rows", "128")
     log = launch("examples/deepctr/run.py", "--data", str(tmp_path / "orc"), "--device", "cpu", "--batch", "32")
     assert "CoalescedHashtable_" in log
+    # windows are walked in step by both ranks, each reading its share of every window and tracing its own samples
+    log = launch("examples/deepctr/run.py", "--data", str(tmp_path / "orc"), "--device", "cpu", "--batch", "32", "--windows", "2",
+                 "--trace-dir", str(tmp_path / "trace"), "--output-dir", str(tmp_path / "ctr_windows"))
+    import pyarrow.dataset as pads
+    counts = [pads.dataset(str(tmp_path / "trace" / f"rank={r}"), format="parquet").count_rows() for r in range(2)]
+    assert "Window IO Finish" in log and counts == [128, 128]
