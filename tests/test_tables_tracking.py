@@ -601,3 +601,34 @@ def test_trace_and_tracker_write_to_object_stores():
     tracker.end()
     lines = [json.loads(l) for l in fs.cat("/tracking/p/r-7/metrics.jsonl").decode().splitlines()]
     assert [l["v"] for l in lines] == [0.0, 1.5, 3.0] and fs.exists("/tracking/p/r-7/finished")
+
+
+def test_window_sharding_covers_every_row_exactly_once_property():
+    """For random table sizes, worker counts, thread counts and window settings: the sheets of all workers and windows partition
+    the table, and the sub-process shares partition each sheet."""
+    from hypothesis import given, settings, strategies as st
+    import recis_b200.io.window_io as wio
+    from recis_b200.io.window_io import _shard_sheets_by_split_num
+
+    @settings(max_examples=150, deadline=None)
+    @given(size=st.integers(0, 5000), workers=st.integers(1, 5), threads=st.integers(1, 4), split=st.integers(1, 6),
+           row_num=st.integers(1, 700), subs=st.integers(1, 3))
+    def check(size, workers, threads, split, row_num, subs):
+        orig = wio.get_table_size
+        wio.get_table_size = lambda table: size
+        try:
+            for sheets_of in (lambda w: _shard_sheets_by_split_num("t", w, workers, threads, split, 0)[0],
+                              lambda w: _shard_sheets_by_row_num("t", w, workers, threads, row_num, 0)[0]):
+                rows = []
+                for w in range(workers):
+                    sheets = sheets_of(w)
+                    for sub in range(subs):
+                        for text in _shard_table_by_subprocess(sheets, sub, subs):
+                            s = TableSheet.parse(text)
+                            assert s.start <= s.end
+                            rows += range(s.start, s.end)
+                assert sorted(rows) == list(range(size))
+        finally:
+            wio.get_table_size = orig
+
+    check()
