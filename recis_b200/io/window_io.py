@@ -144,12 +144,30 @@ class OdpsDataset(OrcDataset):
 
     # ---- reading
     def _sheet_tables(self, sheet: TableSheet, from_row: int):
+        """The sheet's rows as Arrow tables of up to ``_READ_CHUNK_ROWS`` rows, in order. Up to ``read_threads_num`` requests are
+        in flight on reader threads (sources release the interpreter lock while they read and decode), so the consumer finds the
+        next chunk ready; the order of the results, and with it the batch sequence and the resumable position, does not depend
+        on which request finishes first."""
         src, name = resolve_table_source(sheet.table)
-        row = sheet.start + from_row
-        while row < sheet.end:
-            stop = min(row + _READ_CHUNK_ROWS, sheet.end)
-            yield src.read(name, row, stop, self._columns())
-            row = stop
+        columns = self._columns()
+        chunks = [(row, min(row + _READ_CHUNK_ROWS, sheet.end)) for row in range(sheet.start + from_row, sheet.end, _READ_CHUNK_ROWS)]
+        depth = max(int(self.read_threads_num), 1)
+        if depth == 1 or len(chunks) <= 1:
+            for lo, hi in chunks:
+                yield src.read(name, lo, hi, columns)
+            return
+        from collections import deque
+        from concurrent.futures import ThreadPoolExecutor
+        pool = ThreadPoolExecutor(max_workers=depth, thread_name_prefix="table-read")
+        try:
+            pending, nxt = deque(), 0
+            while pending or nxt < len(chunks):
+                while nxt < len(chunks) and len(pending) < depth:
+                    pending.append(pool.submit(src.read, name, chunks[nxt][0], chunks[nxt][1], columns))
+                    nxt += 1
+                yield pending.popleft().result()
+        finally:
+            pool.shutdown(wait=False, cancel_futures=True)
 
     def _sheet_batches(self, sheet: TableSheet, from_row: int, rows_per_batch: int):
         """Arrow tables of up to ``rows_per_batch`` rows from one sheet, in order."""

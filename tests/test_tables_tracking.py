@@ -632,3 +632,27 @@ def test_window_sharding_covers_every_row_exactly_once_property():
             wio.get_table_size = orig
 
     check()
+
+
+def test_reader_threads_keep_the_row_order(monkeypatch):
+    """Several requests in flight, finishing out of order: batches still come in row order."""
+    import time
+    import recis_b200.io.window_io as wio
+
+    class SlowFirst:
+        def size(self, table):
+            return 1000
+
+        def read(self, table, start, end, columns):
+            time.sleep(0.05 if start == 0 else 0.0)          # the first chunk is the slowest
+            return pa.table({"uid": pa.array(np.arange(start, end), pa.int64())})
+
+    register_table_source("slowfirst", SlowFirst())
+    monkeypatch.setattr(wio, "_READ_CHUNK_ROWS", 100)
+    ds = OdpsDataset(64, read_threads_num=4)
+    ds.add_path("slowfirst://t")
+    ds.fixedlen_feature("uid")
+    rows = torch.cat([b["uid"].flatten() for b in ds]).tolist()
+    assert sorted(rows) == list(range(1000))
+    # four sheets of 250 rows, each read in order
+    assert all(rows[i * 250:(i + 1) * 250] == list(range(i * 250, (i + 1) * 250)) for i in range(4))
