@@ -12,6 +12,8 @@
 //   next()           pops one batch (the GIL is released while waiting).
 // The position after the last batch handed to the caller (file index, row inside the file) is the iterator state: `state()`
 // returns it, `restore()` restarts the pipeline from it, so a resumed job continues with the batch it would have seen next.
+// Every path may come with a row range [begin, end) of the file (end < 0: to the end of the file): this is how row-addressed
+// tables are read (a slice of a table is a list of file segments); rows in the state are always rows of the file.
 //
 // Same role as the reference's column-io graph (third_party/column-io: ParallelDataset, Packer, PrefetchDataset and
 // LocalOrcDataset with read-time hashing, dataset/packer.cc and dataset_impl/local_orc_dataset.cc) with a fixed,
@@ -53,10 +55,11 @@ using TablePtr = std::shared_ptr<arrow::Table>;
 class ColumnarReader {
  public:
   ColumnarReader(std::vector<std::string> paths, int64_t batch_size, std::vector<VarCol> var, std::vector<FixCol> fix, int threads,
-                 int prefetch, bool drop_remainder, bool pin)
-      : paths_(std::move(paths)), batch_size_(batch_size), var_(std::move(var)), fix_(std::move(fix)), threads_(std::max(threads, 1)),
-        prefetch_(std::max(prefetch, 1)), drop_remainder_(drop_remainder), pin_(pin) {
+                 int prefetch, bool drop_remainder, bool pin, std::vector<std::pair<int64_t, int64_t>> ranges = {})
+      : paths_(std::move(paths)), ranges_(std::move(ranges)), batch_size_(batch_size), var_(std::move(var)), fix_(std::move(fix)),
+        threads_(std::max(threads, 1)), prefetch_(std::max(prefetch, 1)), drop_remainder_(drop_remainder), pin_(pin) {
     TORCH_CHECK(batch_size_ > 0, "batch_size must be positive");
+    TORCH_CHECK(ranges_.empty() || ranges_.size() == paths_.size(), "one row range per path, or none");
     for (auto& v : var_) names_.push_back(v.name);
     for (auto& f : fix_) names_.push_back(f.name);
     start(0, 0);
@@ -182,8 +185,11 @@ class ColumnarReader {
       }
       cv_tab_.notify_all();
       if (!item.second.empty()) { Batch b; b.error = item.second; push(std::move(b)); break; }
-      const int64_t n = item.first->num_rows();
-      for (int64_t r0 = (f == start_file_ ? first_row_ : 0); r0 < n; r0 += batch_size_) {
+      // this entry's rows of the file: everything, or the entry's [begin, end)
+      const int64_t n_file = item.first->num_rows();
+      const int64_t lo = ranges_.empty() ? 0 : std::min(std::max<int64_t>(ranges_[f].first, 0), n_file);
+      const int64_t n = ranges_.empty() || ranges_[f].second < 0 ? n_file : std::min(ranges_[f].second, n_file);
+      for (int64_t r0 = (f == start_file_ ? std::max(first_row_, lo) : lo); r0 < n; r0 += batch_size_) {
         const int64_t r1 = std::min(r0 + batch_size_, n);
         if (drop_remainder_ && r1 - r0 < batch_size_) break;
         Batch b;
@@ -308,6 +314,7 @@ class ColumnarReader {
   }
 
   std::vector<std::string> paths_;
+  std::vector<std::pair<int64_t, int64_t>> ranges_;       // per path: rows [begin, end) of the file; empty: whole files
   int64_t batch_size_;
   std::vector<VarCol> var_;
   std::vector<FixCol> fix_;
@@ -331,15 +338,17 @@ class ColumnarReader {
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   py::class_<ColumnarReader>(m, "ColumnarReader")
       .def(py::init([](std::vector<std::string> paths, int64_t batch_size, std::vector<std::tuple<std::string, int, int64_t, bool>> var,
-                       std::vector<std::tuple<std::string, double>> fix, int threads, int prefetch, bool drop_remainder, bool pin) {
+                       std::vector<std::tuple<std::string, double>> fix, int threads, int prefetch, bool drop_remainder, bool pin,
+                       std::vector<std::pair<int64_t, int64_t>> ranges) {
              std::vector<VarCol> v;
              for (auto& t : var) v.push_back({std::get<0>(t), std::get<1>(t), std::get<2>(t), std::get<3>(t)});
              std::vector<FixCol> f;
              for (auto& t : fix) f.push_back({std::get<0>(t), std::get<1>(t)});
-             return new ColumnarReader(std::move(paths), batch_size, std::move(v), std::move(f), threads, prefetch, drop_remainder, pin);
+             return new ColumnarReader(std::move(paths), batch_size, std::move(v), std::move(f), threads, prefetch, drop_remainder, pin,
+                                       std::move(ranges));
            }),
            py::arg("paths"), py::arg("batch_size"), py::arg("varlen"), py::arg("fixed"), py::arg("threads") = 2, py::arg("prefetch") = 2,
-           py::arg("drop_remainder") = false, py::arg("pin") = false)
+           py::arg("drop_remainder") = false, py::arg("pin") = false, py::arg("ranges") = std::vector<std::pair<int64_t, int64_t>>{})
       .def("next", [](ColumnarReader& r) -> py::object {
              Batch b;
              bool ok;

@@ -50,12 +50,29 @@ def _file_rows(path: str) -> int:
     return orc.ORCFile(path).nrows
 
 
+def _plain_type(t):
+    """List types with the default child field name, at any depth: Parquet names a list's child ``element``, ORC ``item``,
+    and tables that differ only in that do not concatenate."""
+    import pyarrow as pa
+    if pa.types.is_list(t) or pa.types.is_large_list(t):
+        return pa.list_(_plain_type(t.value_type))
+    return t
+
+
 def _read_file(path: str, columns: Optional[Sequence[str]]):
+    """The file's columns as a table: the requested columns in the requested order (readers differ: ORC returns file order), list
+    types normalised, so that pieces of a table that come from files of both formats concatenate."""
+    import pyarrow as pa
     if path.endswith(".parquet"):
         import pyarrow.parquet as pq
-        return pq.read_table(path, columns=list(columns) if columns else None)
-    import pyarrow.orc as orc
-    return orc.ORCFile(path).read(columns=list(columns) if columns else None)
+        table = pq.read_table(path, columns=list(columns) if columns else None)
+    else:
+        import pyarrow.orc as orc
+        table = orc.ORCFile(path).read(columns=list(columns) if columns else None)
+    if columns:
+        table = table.select(list(columns))
+    want = pa.schema([pa.field(f.name, _plain_type(f.type)) for f in table.schema])
+    return table if want.equals(table.schema) else table.cast(want)
 
 
 class FileTableSource:

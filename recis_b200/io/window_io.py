@@ -25,6 +25,7 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
+from ..ragged import RaggedTensor
 from ..utils.logger import Logger
 from .dataset import OrcDataset
 from .table_source import US, get_table_size, resolve_stream_source, resolve_table_source, us_to_stamp
@@ -194,6 +195,86 @@ class OdpsDataset(OrcDataset):
             self.batch_size = old
         return None
 
+    # ---- the native reader, when every sheet is a slice of columnar files
+    def _file_segments(self, sheets):
+        """``[(sheet index, rows of the sheet before the segment, file, first row, end row)]`` covering the sheets in order, or
+        None when a sheet is not backed by files."""
+        from .table_source import FileTableSource
+        import bisect
+        segs = []
+        for si, sh in enumerate(sheets):
+            src, name = resolve_table_source(sh.table)
+            if not isinstance(src, FileTableSource):
+                return None
+            files, cum = src._files(name)
+            row, end = sh.start, min(sh.end, cum[-1] if cum else 0)
+            i = bisect.bisect_right(cum, row)
+            while i < len(files) and row < end:
+                base = cum[i - 1] if i else 0
+                take = min(end, cum[i]) - row
+                segs.append((si, row - sh.start, files[i], row - base, row - base + take))
+                row += take
+                i += 1
+        return segs
+
+    def _iter_native(self, sheets):
+        """Batches of the sheets through the C++ reader (reader threads, packer, prefetch queue), or None when it does not apply.
+        A batch never spans two file segments, so batches at segment ends are short; the position kept for ``dump_io_state`` is
+        the same (sheet, row in sheet) pair as on the Python path."""
+        if not self.native_reader or not sheets:
+            return None
+        segs = self._file_segments(sheets)
+        if not segs or not all(seg[2].endswith((".orc", ".parquet")) for seg in segs):
+            return None
+        from .._ext_io import load
+        mod = load()
+        if mod is None:
+            return None
+        var = [(n, -1 if not c["hash_type"] else (0 if c["hash_type"] == "farm" else 1), int(c["hash_bucket"] or 0), bool(c["trans_int8"]))
+               for n, c in self._varlen.items()]
+        fix = [(n, float(d)) for n, d in self._fixed.items()]
+        try:
+            reader = mod.ColumnarReader([seg[2] for seg in segs], self.batch_size, var, fix, max(self.read_threads_num, 1), max(self.prefetch, 1),
+                                        self.drop_remainder, self.pin, ranges=[(seg[3], seg[4]) for seg in segs])
+        except TypeError:                      # a reader built before row ranges existed
+            return None
+        # resume: the segment that holds (sheet, row in sheet)
+        start = next((k for k, seg in enumerate(segs) if seg[0] == self._sheet_idx and seg[1] + (seg[4] - seg[3]) > self._row_in_sheet),
+                     next((k for k, seg in enumerate(segs) if seg[0] > self._sheet_idx), len(segs)))
+        if start >= len(segs):
+            return iter(())
+        if start or self._row_in_sheet:
+            seg = segs[start]
+            reader.restore(start, seg[3] + max(self._row_in_sheet - seg[1], 0) if seg[0] == self._sheet_idx else seg[3])
+
+        def run():
+            while True:
+                item = reader.next()
+                if item is None:
+                    self._sheet_idx, self._row_in_sheet = len(sheets), 0
+                    return
+                rows, cols = item
+                batch = {}
+                for name in list(self._varlen) + list(self._fixed):
+                    c = cols[name]
+                    if c[0] == 0:
+                        batch[name] = RaggedTensor(c[1], [c[2]], dense_shape=(rows, -1))
+                    elif c[0] == 1:
+                        batch[name] = RaggedTensor(c[1], [c[2], c[3]])
+                    else:
+                        batch[name] = c[1].to(self.dtype) if c[1].is_floating_point() else c[1]
+                batch = self._finish(self._place(batch))
+                k, row = reader.state()
+                if k < len(segs):
+                    seg = segs[k]
+                    self._sheet_idx, self._row_in_sheet = seg[0], seg[1] + max(row - seg[3], 0)
+                else:
+                    self._sheet_idx, self._row_in_sheet = len(sheets), 0
+                if batch is not None:
+                    yield batch
+
+        return run()
+
     def __iter__(self):
         import pyarrow as pa
         if self._shard_paths is None:
@@ -202,6 +283,11 @@ class OdpsDataset(OrcDataset):
         width = max(self._stream_width, 1)
         if self._sheet_idx >= len(sheets):
             self._sheet_idx, self._row_in_sheet = 0, 0
+        if width == 1:
+            native = self._iter_native(sheets)
+            if native is not None:
+                yield from native
+                return
         while self._sheet_idx < len(sheets):
             group = sheets[self._sheet_idx:self._sheet_idx + width]
             per = int(math.ceil(self.batch_size / len(group))) if width > 1 else self.batch_size
