@@ -28,6 +28,7 @@
 #include <atomic>
 #include <condition_variable>
 #include <deque>
+#include <limits>
 #include <map>
 #include <mutex>
 #include <thread>
@@ -51,6 +52,9 @@ struct Batch {
 };
 
 using TablePtr = std::shared_ptr<arrow::Table>;
+// What a reader thread hands to the packer: the decoded rows [base, base + table->num_rows()) of a file of n_file rows. An entry
+// with a row range decodes only the Parquet row groups / ORC stripes that overlap the range.
+struct Decoded { TablePtr table; std::string err; int64_t base = 0; int64_t n_file = 0; };
 
 class ColumnarReader {
  public:
@@ -117,6 +121,10 @@ class ColumnarReader {
       }
       TablePtr table;
       std::string err;
+      int64_t base = 0, n_file = 0;
+      // rows of the file this entry wants (everything without a range; an end below zero means the end of the file)
+      const int64_t want_lo = ranges_.empty() ? 0 : std::max<int64_t>(ranges_[idx].first, 0);
+      const int64_t want_hi = ranges_.empty() || ranges_[idx].second < 0 ? std::numeric_limits<int64_t>::max() : ranges_[idx].second;
       auto file = arrow::io::ReadableFile::Open(paths_[idx]);
       const std::string& path = paths_[idx];
       const bool is_parquet = path.size() >= 8 && path.compare(path.size() - 8, 8, ".parquet") == 0;
@@ -137,7 +145,22 @@ class ColumnarReader {
             }
           }
           std::shared_ptr<arrow::Table> t;
-          if (st.ok()) st = (*reader)->ReadTable(cols, &t);
+          auto md = (*reader)->parquet_reader()->metadata();
+          n_file = md->num_rows();
+          if (st.ok() && want_hi > want_lo && (want_lo > 0 || want_hi < n_file)) {
+            // row groups that overlap [want_lo, want_hi)
+            std::vector<int> groups;
+            int64_t acc = 0;
+            for (int g = 0; g < md->num_row_groups(); ++g) {
+              const int64_t n = md->RowGroup(g)->num_rows();
+              if (acc + n > want_lo && acc < want_hi) { if (groups.empty()) base = acc; groups.push_back(g); }
+              acc += n;
+            }
+            if (groups.empty()) { base = 0; st = (*reader)->ReadTable(cols, &t); }      // a range past the end: nothing will be packed
+            else st = (*reader)->ReadRowGroups(groups, cols, &t);
+          } else if (st.ok()) {
+            st = (*reader)->ReadTable(cols, &t);
+          }
           if (!st.ok()) err = st.ToString();
           else {
             auto c = t->CombineChunks(arrow::default_memory_pool());
@@ -148,17 +171,36 @@ class ColumnarReader {
         auto reader = arrow::adapters::orc::ORCFileReader::Open(*file, arrow::default_memory_pool());
         if (!reader.ok()) err = reader.status().ToString();
         else {
-          auto t = (*reader)->Read(names_);
-          if (!t.ok()) err = t.status().ToString();
+          n_file = (*reader)->NumberOfRows();
+          std::shared_ptr<arrow::Table> t;
+          arrow::Status st;
+          std::vector<std::shared_ptr<arrow::RecordBatch>> parts;
+          if (want_hi > want_lo && (want_lo > 0 || want_hi < n_file)) {
+            // stripes that overlap [want_lo, want_hi)
+            bool first = true;
+            for (int64_t k = 0; k < (*reader)->NumberOfStripes() && st.ok(); ++k) {
+              const auto info = (*reader)->GetStripeInformation(k);
+              if (info.first_row_id + info.num_rows <= want_lo || info.first_row_id >= want_hi) continue;
+              if (first) { base = info.first_row_id; first = false; }
+              auto rb = (*reader)->ReadStripe(k, names_);
+              if (!rb.ok()) st = rb.status(); else parts.push_back(*rb);
+            }
+          }
+          if (st.ok()) {
+            auto r = parts.empty() ? (*reader)->Read(names_) : arrow::Table::FromRecordBatches(parts);
+            if (parts.empty()) base = 0;
+            if (!r.ok()) st = r.status(); else t = *r;
+          }
+          if (!st.ok()) err = st.ToString();
           else {
-            auto c = (*t)->CombineChunks(arrow::default_memory_pool());
+            auto c = t->CombineChunks(arrow::default_memory_pool());
             if (!c.ok()) err = c.status().ToString(); else table = *c;
           }
         }
       }
       {
         std::lock_guard<std::mutex> lk(mu_);
-        tables_[idx] = {table, err.empty() ? "" : ("reading " + paths_[idx] + ": " + err)};
+        tables_[idx] = Decoded{table, err.empty() ? "" : ("reading " + paths_[idx] + ": " + err), base, n_file};
       }
       cv_tab_.notify_all();
     }
@@ -174,7 +216,7 @@ class ColumnarReader {
   }
   void pack_loop() {
     for (int64_t f = next_file_to_pack_; f < (int64_t)paths_.size(); ++f) {
-      std::pair<TablePtr, std::string> item;
+      Decoded item;
       {
         std::unique_lock<std::mutex> lk(mu_);
         cv_tab_.wait(lk, [&] { return stop_ || tables_.count(f) > 0; });
@@ -184,9 +226,10 @@ class ColumnarReader {
         next_file_to_pack_ = f + 1;
       }
       cv_tab_.notify_all();
-      if (!item.second.empty()) { Batch b; b.error = item.second; push(std::move(b)); break; }
-      // this entry's rows of the file: everything, or the entry's [begin, end)
-      const int64_t n_file = item.first->num_rows();
+      if (!item.err.empty()) { Batch b; b.error = item.err; push(std::move(b)); break; }
+      // this entry's rows of the file: everything, or the entry's [begin, end); the decoded table starts at row item.base
+      const int64_t n_file = item.n_file;
+      const int64_t base = item.base;
       const int64_t lo = ranges_.empty() ? 0 : std::min(std::max<int64_t>(ranges_[f].first, 0), n_file);
       const int64_t n = ranges_.empty() || ranges_[f].second < 0 ? n_file : std::min(ranges_[f].second, n_file);
       for (int64_t r0 = (f == start_file_ ? std::max(first_row_, lo) : lo); r0 < n; r0 += batch_size_) {
@@ -195,8 +238,8 @@ class ColumnarReader {
         Batch b;
         b.rows = r1 - r0; b.file_idx = r1 < n ? f : f + 1; b.next_row = r1 < n ? r1 : 0;
         try {
-          for (auto& v : var_) b.cols[v.name] = pack_var(*item.first, v, r0, r1);
-          for (auto& c : fix_) b.cols[c.name] = pack_fix(*item.first, c, r0, r1);
+          for (auto& v : var_) b.cols[v.name] = pack_var(*item.table, v, r0 - base, r1 - base);
+          for (auto& c : fix_) b.cols[c.name] = pack_fix(*item.table, c, r0 - base, r1 - base);
         } catch (const std::exception& e) {
           b.error = std::string("packing ") + paths_[f] + ": " + e.what();
         }
@@ -325,7 +368,7 @@ class ColumnarReader {
   std::mutex mu_;
   std::condition_variable cv_in_, cv_out_, cv_tab_;
   std::deque<Batch> queue_;
-  std::map<int64_t, std::pair<TablePtr, std::string>> tables_;
+  std::map<int64_t, Decoded> tables_;
   std::vector<std::thread> workers_;
   std::thread packer_;
   bool stop_ = false;

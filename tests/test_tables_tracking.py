@@ -691,3 +691,32 @@ def test_native_reader_serves_file_backed_sheets_and_resumes_anywhere(tmp_path):
             d2.load_io_state(state)
             rest = [x for b in d2 for x in b["uid"].flatten().tolist()]
             assert native_rows[:seen] + rest == native_rows, (seen, native)
+
+
+def test_native_reader_row_ranges_decode_only_what_overlaps(tmp_path):
+    """Ranges that start and end inside Parquet row groups and ORC stripes give exactly their rows."""
+    from recis_b200._ext_io import load
+    mod = load()
+    if mod is None:
+        pytest.skip("native reader not built here")
+    n = 20000
+    t = pa.table({"uid": pa.array(np.arange(n), pa.int64()), "items": pa.array([[i, i + 1] for i in range(n)], pa.list_(pa.int64()))})
+    pq_path, orc_path = str(tmp_path / "a.parquet"), str(tmp_path / "b.orc")
+    pq.write_table(t, pq_path, row_group_size=1500)
+    orc.write_table(t, orc_path, stripe_size=16 * 1024, batch_size=512)
+    assert pq.ParquetFile(pq_path).metadata.num_row_groups > 5 and orc.ORCFile(orc_path).nstripes > 1
+    for path in (pq_path, orc_path):
+        for lo, hi in ((0, n), (1499, 1501), (1500, 3000), (4321, 17777), (19990, -1), (0, 1), (n, n + 5)):
+            reader = mod.ColumnarReader([path, path], 700, [("items", -1, 0, False)], [("uid", 0.0)], 2, 2, False, False,
+                                        ranges=[(lo, hi), (10, 12)])
+            rows = []
+            while True:
+                item = reader.next()
+                if item is None:
+                    break
+                count, cols = item
+                uid = cols["uid"][1].flatten().long()
+                assert count == len(uid) and torch.equal(cols["items"][1].view(-1, 2)[:, 0], uid)
+                rows += uid.tolist()
+            want = list(range(lo, n if hi < 0 else min(hi, n))) + [10, 11]
+            assert rows == want, (path, lo, hi)
