@@ -304,6 +304,29 @@ class OrcDataset(DatasetBase):
             reader.restore(self._file_idx, self._row_in_file)
         return reader
 
+    def _drain_native(self, reader, moved=None):
+        """Batches of a native reader until it is exhausted: packed columns become RaggedTensors / dense tensors, then placement,
+        map / transform / filter functions. ``moved(state)`` is told the reader's position after every batch handed out."""
+        while True:
+            item = reader.next()
+            if item is None:
+                return
+            rows, cols = item
+            batch = {}
+            for name in list(self._varlen) + list(self._fixed):
+                c = cols[name]
+                if c[0] == 0:
+                    batch[name] = RaggedTensor(c[1], [c[2]], dense_shape=(rows, -1))
+                elif c[0] == 1:
+                    batch[name] = RaggedTensor(c[1], [c[2], c[3]])
+                else:
+                    batch[name] = c[1].to(self.dtype) if c[1].is_floating_point() else c[1]
+            batch = self._finish(self._place(batch))
+            if moved is not None:
+                moved(reader.state())
+            if batch is not None:
+                yield batch
+
     def __iter__(self):
         paths = self._my_paths()
         if self._file_idx >= len(paths):
@@ -312,25 +335,10 @@ class OrcDataset(DatasetBase):
             self._file_idx, self._row_in_file = 0, 0
         reader = self._native(paths)
         if reader is not None:
-            while True:
-                item = reader.next()
-                if item is None:
-                    return
-                rows, cols = item
-                batch = {}
-                for name in list(self._varlen) + list(self._fixed):
-                    c = cols[name]
-                    if c[0] == 0:
-                        batch[name] = RaggedTensor(c[1], [c[2]], dense_shape=(rows, -1))
-                    elif c[0] == 1:
-                        batch[name] = RaggedTensor(c[1], [c[2], c[3]])
-                    else:
-                        batch[name] = c[1].to(self.dtype) if c[1].is_floating_point() else c[1]
-                batch = self._place(batch)
-                batch = self._finish(batch)
-                self._file_idx, self._row_in_file = reader.state()
-                if batch is not None:
-                    yield batch
+            def moved(state):
+                self._file_idx, self._row_in_file = state
+            yield from self._drain_native(reader, moved)
+            return
         while self._file_idx < len(paths):
             table = self._read_table(paths[self._file_idx])
             yield from self._batches_of(table, self._row_in_file)

@@ -247,31 +247,17 @@ class OdpsDataset(OrcDataset):
             seg = segs[start]
             reader.restore(start, seg[3] + max(self._row_in_sheet - seg[1], 0) if seg[0] == self._sheet_idx else seg[3])
 
+        def moved(state):
+            k, row = state
+            if k < len(segs):
+                seg = segs[k]
+                self._sheet_idx, self._row_in_sheet = seg[0], seg[1] + max(row - seg[3], 0)
+            else:
+                self._sheet_idx, self._row_in_sheet = len(sheets), 0
+
         def run():
-            while True:
-                item = reader.next()
-                if item is None:
-                    self._sheet_idx, self._row_in_sheet = len(sheets), 0
-                    return
-                rows, cols = item
-                batch = {}
-                for name in list(self._varlen) + list(self._fixed):
-                    c = cols[name]
-                    if c[0] == 0:
-                        batch[name] = RaggedTensor(c[1], [c[2]], dense_shape=(rows, -1))
-                    elif c[0] == 1:
-                        batch[name] = RaggedTensor(c[1], [c[2], c[3]])
-                    else:
-                        batch[name] = c[1].to(self.dtype) if c[1].is_floating_point() else c[1]
-                batch = self._finish(self._place(batch))
-                k, row = reader.state()
-                if k < len(segs):
-                    seg = segs[k]
-                    self._sheet_idx, self._row_in_sheet = seg[0], seg[1] + max(row - seg[3], 0)
-                else:
-                    self._sheet_idx, self._row_in_sheet = len(sheets), 0
-                if batch is not None:
-                    yield batch
+            yield from self._drain_native(reader, moved)
+            self._sheet_idx, self._row_in_sheet = len(sheets), 0
 
         return run()
 
@@ -470,16 +456,33 @@ class LakeStreamDataset(OrcDataset):
     def _shard_path(self, sub_id: int = 0, sub_num: int = 1):
         self._ranges = list(zip(self._paths, self._begins, self._ends))
 
+    def _my_entries(self, src, name: str, begin: int, end: int):
+        entries = [e for e in src.entries(name) if begin <= e[0] < end]
+        if self.shuffle:
+            random.Random(self._shuffle_seed * 1000003 + begin // US).shuffle(entries)
+        return entries[self.worker_idx::self.worker_num]
+
+    def _range_files(self, path: str, begin: int, end: int) -> List[str]:
+        """The columnar files behind this worker's entries of a time range, in reading order; empty when the source is not one
+        of files (the range is then read through the source)."""
+        from .table_source import FileStreamSource, _columnar_files
+        src, name = resolve_stream_source(path)
+        if not isinstance(src, FileStreamSource):
+            return []
+        return [f for _ts, entry in self._my_entries(src, name, begin, end) for f in _columnar_files(entry)]
+
+    def _native(self, paths):
+        # a range is read as a whole: the position inside it is not part of this dataset's state
+        self._file_idx, self._row_in_file = 0, 0
+        return super()._native(paths)
+
     def _range_table(self, path: str, begin: int, end: int):
         """This worker's rows of one time range: its share of the range's entries when the source lists entries, else every
         ``worker_num``-th block of rows."""
         import pyarrow as pa
         src, name = resolve_stream_source(path)
         if hasattr(src, "entries") and hasattr(src, "read_entry"):
-            entries = [e for e in src.entries(name) if begin <= e[0] < end]
-            if self.shuffle:
-                random.Random(self._shuffle_seed * 1000003 + begin // US).shuffle(entries)
-            mine = entries[self.worker_idx::self.worker_num]
+            mine = self._my_entries(src, name, begin, end)
             parts = [src.read_entry(entry, self._columns()) for _ts, entry in mine]
             parts = [p for p in parts if p is not None and p.num_rows]
             return pa.concat_tables(parts) if parts else None
@@ -499,8 +502,12 @@ class LakeStreamDataset(OrcDataset):
             self._range_idx = 0
         while self._range_idx < len(self._ranges):
             path, begin, end = self._ranges[self._range_idx]
-            table = self._range_table(path, begin, end)
             self._range_idx += 1
+            reader = self._native(self._range_files(path, begin, end))
+            if reader is not None:                 # this worker's entries are columnar files: the C++ reader serves them
+                yield from self._drain_native(reader)
+                continue
+            table = self._range_table(path, begin, end)
             if table is not None and table.num_rows:
                 yield from self._batches_of(table, 0)
 
