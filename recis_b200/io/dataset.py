@@ -304,6 +304,19 @@ class OrcDataset(DatasetBase):
             reader.restore(self._file_idx, self._row_in_file)
         return reader
 
+    def _unpack_native(self, rows, cols):
+        """One packed batch of the native reader as the batch dict (before placement and user functions)."""
+        batch = {}
+        for name in list(self._varlen) + list(self._fixed):
+            c = cols[name]
+            if c[0] == 0:
+                batch[name] = RaggedTensor(c[1], [c[2]], dense_shape=(rows, -1))
+            elif c[0] == 1:
+                batch[name] = RaggedTensor(c[1], [c[2], c[3]])
+            else:
+                batch[name] = c[1].to(self.dtype) if c[1].is_floating_point() else c[1]
+        return batch
+
     def _drain_native(self, reader, moved=None):
         """Batches of a native reader until it is exhausted: packed columns become RaggedTensors / dense tensors, then placement,
         map / transform / filter functions. ``moved(state)`` is told the reader's position after every batch handed out."""
@@ -311,17 +324,7 @@ class OrcDataset(DatasetBase):
             item = reader.next()
             if item is None:
                 return
-            rows, cols = item
-            batch = {}
-            for name in list(self._varlen) + list(self._fixed):
-                c = cols[name]
-                if c[0] == 0:
-                    batch[name] = RaggedTensor(c[1], [c[2]], dense_shape=(rows, -1))
-                elif c[0] == 1:
-                    batch[name] = RaggedTensor(c[1], [c[2], c[3]])
-                else:
-                    batch[name] = c[1].to(self.dtype) if c[1].is_floating_point() else c[1]
-            batch = self._finish(self._place(batch))
+            batch = self._finish(self._place(self._unpack_native(*item)))
             if moved is not None:
                 moved(reader.state())
             if batch is not None:

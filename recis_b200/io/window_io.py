@@ -217,6 +217,106 @@ class OdpsDataset(OrcDataset):
                 i += 1
         return segs
 
+    def _segment_reader(self, mod, segs, batch_size, threads, drop_remainder):
+        var = [(n, -1 if not c["hash_type"] else (0 if c["hash_type"] == "farm" else 1), int(c["hash_bucket"] or 0), bool(c["trans_int8"]))
+               for n, c in self._varlen.items()]
+        fix = [(n, float(d)) for n, d in self._fixed.items()]
+        try:
+            return mod.ColumnarReader([seg[2] for seg in segs], batch_size, var, fix, threads, max(self.prefetch, 1), drop_remainder, self.pin,
+                                      ranges=[(seg[3], seg[4]) for seg in segs])
+        except TypeError:                      # a reader built before row ranges existed
+            return None
+
+    def _iter_native_wide(self, group, per):
+        """A window's sheets read side by side by one native reader each: a batch is one packed piece of ``per`` rows from every
+        sheet that still has rows, concatenated in sheet order. None when the native reader does not apply."""
+        if not self.native_reader:
+            return None
+        from .._ext_io import load
+        mod = load()
+        if mod is None:
+            return None
+        readers = []
+        for sh in group:
+            segs = self._file_segments([sh])
+            if segs is None or not all(seg[2].endswith((".orc", ".parquet")) for seg in segs):
+                return None
+            if segs:
+                r = self._segment_reader(mod, segs, per, 1, False)
+                if r is None:
+                    return None
+                readers.append(r)
+
+        def pieces(reader):
+            """Packed pieces of exactly ``per`` rows (the last one shorter): the reader cuts a piece at every file boundary, so
+            short pieces are joined up, as the Python path does."""
+            held, held_rows = [], 0
+            while True:
+                item = reader.next()
+                if item is None:
+                    break
+                held.append(self._unpack_native(*item))
+                held_rows += item[0]
+                while held_rows >= per:
+                    whole = self._merge_pieces(held)
+                    yield self._slice_rows(whole, 0, per)
+                    rest = self._slice_rows(whole, per, held_rows)
+                    held_rows -= per
+                    held = [rest] if held_rows else []
+            if held_rows:
+                yield self._merge_pieces(held)
+
+        def run():
+            streams = [pieces(r) for r in readers]
+            while streams:
+                parts, alive = [], []
+                for s in streams:
+                    piece = next(s, None)
+                    if piece is not None:
+                        parts.append(piece)
+                        alive.append(s)
+                streams = alive
+                if not parts:
+                    return
+                merged = self._merge_pieces(parts)
+                rows = next(iter(merged.values()))
+                n = rows.offsets()[0].numel() - 1 if isinstance(rows, RaggedTensor) else rows.shape[0]
+                if self.drop_remainder and n < self.batch_size:
+                    continue
+                batch = self._finish(self._place(merged))
+                if batch is not None:
+                    yield batch
+
+        return run()
+
+    @staticmethod
+    def _merge_pieces(parts):
+        if len(parts) == 1:
+            return parts[0]
+        return {k: (RaggedTensor.concat([p[k] for p in parts]) if isinstance(parts[0][k], RaggedTensor) else torch.cat([p[k] for p in parts]))
+                for k in parts[0]}
+
+    @staticmethod
+    def _slice_rows(batch, lo, hi):
+        """Rows ``[lo, hi)`` of an unpacked batch."""
+        out = {}
+        for k, v in batch.items():
+            if not isinstance(v, RaggedTensor):
+                out[k] = v[lo:hi]
+                continue
+            offs = v.offsets()
+            a, b = lo, hi
+            new_offs = []
+            for o in offs:                         # outer to inner: the row range becomes a range of the next level
+                piece = o[a:b + 1]
+                a2, b2 = int(piece[0]), int(piece[-1])
+                new_offs.append(piece - piece[0])
+                a, b = a2, b2
+            w = v.weight()
+            out[k] = RaggedTensor(v.values()[a:b], new_offs, weight=None if w is None else w[a:b],
+                                  dense_shape=(hi - lo,) + tuple(v._dense_shape[1:]))
+        return out
+
     def _iter_native(self, sheets):
         """Batches of the sheets through the C++ reader (reader threads, packer, prefetch queue), or None when it does not apply.
         A batch never spans two file segments, so batches at segment ends are short; the position kept for ``dump_io_state`` is
@@ -230,13 +330,8 @@ class OdpsDataset(OrcDataset):
         mod = load()
         if mod is None:
             return None
-        var = [(n, -1 if not c["hash_type"] else (0 if c["hash_type"] == "farm" else 1), int(c["hash_bucket"] or 0), bool(c["trans_int8"]))
-               for n, c in self._varlen.items()]
-        fix = [(n, float(d)) for n, d in self._fixed.items()]
-        try:
-            reader = mod.ColumnarReader([seg[2] for seg in segs], self.batch_size, var, fix, max(self.read_threads_num, 1), max(self.prefetch, 1),
-                                        self.drop_remainder, self.pin, ranges=[(seg[3], seg[4]) for seg in segs])
-        except TypeError:                      # a reader built before row ranges existed
+        reader = self._segment_reader(mod, segs, self.batch_size, max(self.read_threads_num, 1), self.drop_remainder)
+        if reader is None:
             return None
         # resume: the segment that holds (sheet, row in sheet)
         start = next((k for k, seg in enumerate(segs) if seg[0] == self._sheet_idx and seg[1] + (seg[4] - seg[3]) > self._row_in_sheet),
@@ -277,6 +372,13 @@ class OdpsDataset(OrcDataset):
         while self._sheet_idx < len(sheets):
             group = sheets[self._sheet_idx:self._sheet_idx + width]
             per = int(math.ceil(self.batch_size / len(group))) if width > 1 else self.batch_size
+            if width > 1:
+                native = self._iter_native_wide(group, per)
+                if native is not None:
+                    yield from native
+                    self._sheet_idx += len(group)
+                    self._row_in_sheet = 0
+                    continue
             streams = [self._sheet_batches(sh, self._row_in_sheet if width == 1 else 0, per) for sh in group]
             while streams:
                 parts, alive = [], []

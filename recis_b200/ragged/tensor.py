@@ -136,6 +136,31 @@ class RaggedTensor:
     def from_numpy(values: np.ndarray, offsets: List[np.ndarray]):
         return RaggedTensor(torch.from_numpy(values), [torch.from_numpy(np.ascontiguousarray(o)) for o in offsets])
 
+    @staticmethod
+    def concat(parts: List["RaggedTensor"]) -> "RaggedTensor":
+        """Row-wise concatenation: the rows of ``parts[0]``, then those of ``parts[1]`` ... All parts have the same number of
+        offset levels; weights are kept when every part has them. (A new helper: batches assembled from several readers, as the
+        proportional window datasets do, need it.)"""
+        if len(parts) == 1:
+            return parts[0]
+        levels = len(parts[0]._offsets)
+        assert all(len(p._offsets) == levels for p in parts), "parts differ in ragged depth"
+        values = torch.cat([p._values for p in parts])
+        offsets = []
+        for lv in range(levels):
+            pieces, shift = [parts[0]._offsets[lv]], parts[0]._offsets[lv][-1]
+            for p in parts[1:]:
+                pieces.append(p._offsets[lv][1:] + shift)
+                shift = shift + p._offsets[lv][-1]
+            offsets.append(torch.cat(pieces))
+        weight = torch.cat([p._weight for p in parts]) if all(p._weight is not None for p in parts) else None
+        shape = list(parts[0]._dense_shape)
+        shape[0] = sum(int(p._offsets[0].numel()) - 1 for p in parts)
+        for d in range(1, len(shape)):
+            dims = [p._dense_shape[d] for p in parts]
+            shape[d] = -1 if any(x == -1 for x in dims) else max(dims)
+        return RaggedTensor(values, offsets, weight=weight, dense_shape=tuple(shape))
+
     def pin_memory(self):
         return RaggedTensor(self._values.pin_memory(), [o.pin_memory() for o in self._offsets],
                             self._weight.pin_memory() if self._weight is not None else None,

@@ -720,3 +720,54 @@ def test_native_reader_row_ranges_decode_only_what_overlaps(tmp_path):
                 rows += uid.tolist()
             want = list(range(lo, n if hi < 0 else min(hi, n))) + [10, 11]
             assert rows == want, (path, lo, hi)
+
+
+def test_ragged_concat_joins_rows_levels_and_weights():
+    from recis_b200.ragged import RaggedTensor
+    a = RaggedTensor(torch.tensor([1, 2, 3]), [torch.tensor([0, 2, 3], dtype=torch.int32)], weight=torch.tensor([.1, .2, .3]))
+    b = RaggedTensor(torch.tensor([4]), [torch.tensor([0, 0, 1], dtype=torch.int32)], weight=torch.tensor([.4]))
+    c = RaggedTensor.concat([a, b])
+    assert c.values().tolist() == [1, 2, 3, 4] and c.offsets()[0].tolist() == [0, 2, 3, 3, 4] and c.get_shape(0) == 4
+    assert torch.allclose(c.weight(), torch.tensor([.1, .2, .3, .4]))
+    # two levels (rows -> strings -> bytes)
+    s1 = RaggedTensor(torch.arange(5, dtype=torch.int8), [torch.tensor([0, 1, 2], dtype=torch.int32), torch.tensor([0, 2, 5], dtype=torch.int32)])
+    s2 = RaggedTensor(torch.arange(3, dtype=torch.int8), [torch.tensor([0, 2], dtype=torch.int32), torch.tensor([0, 1, 3], dtype=torch.int32)])
+    j = RaggedTensor.concat([s1, s2])
+    assert j.offsets()[0].tolist() == [0, 1, 2, 4] and j.offsets()[1].tolist() == [0, 2, 5, 6, 8] and j.values().numel() == 8
+    assert RaggedTensor.concat([a]) is a
+
+
+def test_proportional_windows_natively_equal_the_python_path(tmp_path):
+    from recis_b200._ext_io import load
+    if load() is None:
+        pytest.skip("native reader not built here")
+    t1, t2 = str(tmp_path / "t1"), str(tmp_path / "t2")
+    _write_table(t1, 0, 3, 170)                       # sheets cross file boundaries and formats
+    _write_table(t2, 100000, 2, 120)
+
+    def run(native):
+        ds = make_odps_window_io(split_num=2)(60, read_threads_num=3, native_reader=native)
+        ds.add_path(t1, (2, 3))
+        ds.add_path(t2, (1, 3))
+        ds.varlen_feature("items")
+        ds.fixedlen_feature("uid")
+        ds.fixedlen_feature("score")
+        used = []
+        if native:
+            orig = ds._iter_native_wide
+            ds._iter_native_wide = lambda group, per: (used.append(1), orig(group, per))[1]
+        out = []
+        while True:
+            try:
+                if ds.next_window():
+                    continue
+            except StopIteration:
+                break
+            for b in ds:
+                out.append((b["uid"].flatten().tolist(), b["items"].values().tolist(), b["items"].offsets()[0].tolist(),
+                            b["score"].flatten().tolist()))
+        return out, used
+
+    nat, used = run(True)
+    py, _ = run(False)
+    assert used and nat == py and sum(len(b[0]) for b in nat) == 510 + 240
