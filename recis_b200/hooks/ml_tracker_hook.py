@@ -7,7 +7,8 @@ same interface here over a tracker object with ``log(data, step)`` / ``finish()`
 * the ``ml_tracker`` package, when it is installed (``ml_tracker.init(project=, name=, id=, config=)``);
 * otherwise ``FileTracker``: one run directory ``<root>/<project>/<name>-<id>/`` with ``config.json`` and ``metrics.jsonl``
   (one JSON object per step: ``{"step": n, "time": t, ...values}``), ``root`` being ``$RECIS_TRACKER_DIR`` or
-  ``./ml_tracker``. Any fsspec URL works as the root. Only rank 0 writes unless ``all_ranks=True``.
+  ``./ml_tracker``. Any fsspec URL works as the root (on stores without append the log is written in parts, flushed every few
+  steps). Only rank 0 writes unless ``all_ranks=True``.
 
 Scalars on the GPU are read in ``after_step`` (one small device-to-host copy per named value and step); tensors with more than
 one element are logged as lists.
@@ -73,8 +74,12 @@ class FileTracker:
         self.fs.makedirs(self.dir, exist_ok=True)
         with self.fs.open(self.dir + "/config.json", "w") as f:
             json.dump({"project": project, "name": name, "id": self.id, "config": _plain(config or {}), "started": time.time()}, f, indent=1)
-        self._lines = []            # object stores cannot append: the whole log is rewritten there, appended on real file systems
+        # Real file systems append a line per step. Object stores cannot append: there the log is written in parts of
+        # ``part_lines`` lines (``metrics-00000.jsonl``, ...), the part in progress being rewritten every ``flush_every`` steps
+        # and at the end, so the cost per step does not grow with the length of the run.
         self._append = getattr(self.fs, "protocol", "file") in ("file", ("file", "local"), "local")
+        self._lines, self._part, self._dirty = [], 0, 0
+        self.part_lines, self.flush_every = 10_000, 20
         self.steps = 0
 
     def log(self, data: Dict, step: int):
@@ -86,11 +91,26 @@ class FileTracker:
                 f.write(line)
         else:
             self._lines.append(line)
-            with self.fs.open(self.dir + "/metrics.jsonl", "w") as f:
-                f.writelines(self._lines)
+            self._dirty += 1
+            if self._dirty >= self.flush_every or len(self._lines) >= self.part_lines:
+                self._write_part()
         self.steps += 1
 
+    def _part_name(self):
+        # the first part keeps the plain name, so that short runs look the same on every file system
+        return "/metrics.jsonl" if self._part == 0 else f"/metrics-{self._part:05d}.jsonl"
+
+    def _write_part(self):
+        if self._lines:
+            with self.fs.open(self.dir + self._part_name(), "w") as f:
+                f.writelines(self._lines)
+        self._dirty = 0
+        if len(self._lines) >= self.part_lines:
+            self._lines, self._part = [], self._part + 1
+
     def finish(self):
+        if not self._append:
+            self._write_part()
         with self.fs.open(self.dir + "/finished", "w") as f:
             f.write(json.dumps({"steps": self.steps, "time": time.time()}))
 

@@ -771,3 +771,20 @@ def test_proportional_windows_natively_equal_the_python_path(tmp_path):
     nat, used = run(True)
     py, _ = run(False)
     assert used and nat == py and sum(len(b[0]) for b in nat) == 510 + 240
+
+
+def test_tracker_log_on_object_stores_is_written_in_parts():
+    import fsspec
+    from recis_b200.hooks.ml_tracker_hook import FileTracker
+    fs = fsspec.filesystem("memory")
+    tr = FileTracker("pp", "run", id="x", root="memory://parts")
+    tr.part_lines, tr.flush_every = 5, 2
+    for step in range(12):
+        tr.log({"v": step}, step)
+    tr.finish()
+    names = sorted(n.rsplit("/", 1)[1] for n in fs.ls("/parts/pp/run-x", detail=False) if "metrics" in n)
+    assert names == ["metrics-00001.jsonl", "metrics-00002.jsonl", "metrics.jsonl"]
+    got = []
+    for n in ["metrics.jsonl", "metrics-00001.jsonl", "metrics-00002.jsonl"]:
+        got += [json.loads(l)["v"] for l in fs.cat("/parts/pp/run-x/" + n).decode().splitlines()]
+    assert got == list(range(12))
