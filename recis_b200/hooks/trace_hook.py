@@ -18,6 +18,7 @@ nothing is pickled across processes and no second CUDA context appears.
 """
 from __future__ import annotations
 
+import atexit
 import functools
 import os
 import queue
@@ -294,6 +295,16 @@ class TraceToOdpsHook(Hook):
         self.writers = [TraceWriter(config, fields, types, i, self.queue, size_threshold) for i in range(worker_num)]
         for w in self.writers:
             w.start()
+        # a run that ends without calling end() (an exception in the loop) still flushes what the writers hold
+        self._ended = False
+        atexit.register(self._end_at_exit)
+
+    def _end_at_exit(self):
+        if not self._ended:
+            try:
+                self.end()
+            except Exception as e:      # noqa: BLE001 - the interpreter is going down; report and carry on
+                logger.error(f"trace hook: flush at exit failed: {e!r}")
 
     def check_alive(self) -> bool:
         return all(w.is_alive() and w.error is None for w in self.writers)
@@ -324,6 +335,9 @@ class TraceToOdpsHook(Hook):
         clear_trace_map()
 
     def end(self):
+        if self._ended:
+            return
+        self._ended = True
         for w in self.writers:
             if w.is_alive():
                 self._put(None)
