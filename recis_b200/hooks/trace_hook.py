@@ -300,11 +300,13 @@ class TraceToOdpsHook(Hook):
         atexit.register(self._end_at_exit)
 
     def _end_at_exit(self):
-        if not self._ended:
-            try:
-                self.end()
-            except Exception as e:      # noqa: BLE001 - the interpreter is going down; report and carry on
-                logger.error(f"trace hook: flush at exit failed: {e!r}")
+        # writers that already failed were reported in after_step; there is nothing left to flush for them
+        if self._ended or any(w.error is not None for w in self.writers):
+            return
+        try:
+            self.end()
+        except Exception:       # noqa: BLE001 - the interpreter is going down and its log streams may be closed already
+            pass
 
     def check_alive(self) -> bool:
         return all(w.is_alive() and w.error is None for w in self.writers)
