@@ -1,5 +1,5 @@
 """recis_b200: a Blackwell-native (sm_100a) sparse + dense recommendation training framework."""
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 from . import _ext  # noqa: F401
 
