@@ -227,6 +227,39 @@ class OdpsDataset(OrcDataset):
         except TypeError:                      # a reader built before row ranges existed
             return None
 
+    def _joined_pieces(self, reader, per, segs=None):
+        """``(sheet, unpacked piece)`` of exactly ``per`` rows each (the last one of a sheet shorter). The reader cuts a piece at
+        every file boundary; short pieces are joined up, as the Python path does. With ``segs`` the pieces of different sheets
+        are never joined (``sheet`` is the index of the sheet a piece comes from, else None)."""
+        held, held_rows, cur = [], 0, None
+        pos = reader.state()                      # (entry, row) of the piece that comes next
+        while True:
+            entry = pos[0]
+            item = reader.next()
+            if item is None:
+                break
+            sheet = segs[entry][0] if segs is not None and entry < len(segs) else None
+            if held_rows and sheet != cur:
+                yield cur, self._merge_pieces(held)
+                held, held_rows = [], 0
+            cur = sheet
+            held.append(self._unpack_native(*item))
+            held_rows += item[0]
+            while held_rows >= per:
+                whole = self._merge_pieces(held)
+                yield cur, self._slice_rows(whole, 0, per)
+                rest = self._slice_rows(whole, per, held_rows)
+                held_rows -= per
+                held = [rest] if held_rows else []
+            pos = reader.state()
+        if held_rows:
+            yield cur, self._merge_pieces(held)
+
+    @staticmethod
+    def _piece_rows(piece) -> int:
+        first = next(iter(piece.values()))
+        return first.offsets()[0].numel() - 1 if isinstance(first, RaggedTensor) else first.shape[0]
+
     def _iter_native_wide(self, group, per):
         """A window's sheets read side by side by one native reader each: a batch is one packed piece of ``per`` rows from every
         sheet that still has rows, concatenated in sheet order. None when the native reader does not apply."""
@@ -247,41 +280,20 @@ class OdpsDataset(OrcDataset):
                     return None
                 readers.append(r)
 
-        def pieces(reader):
-            """Packed pieces of exactly ``per`` rows (the last one shorter): the reader cuts a piece at every file boundary, so
-            short pieces are joined up, as the Python path does."""
-            held, held_rows = [], 0
-            while True:
-                item = reader.next()
-                if item is None:
-                    break
-                held.append(self._unpack_native(*item))
-                held_rows += item[0]
-                while held_rows >= per:
-                    whole = self._merge_pieces(held)
-                    yield self._slice_rows(whole, 0, per)
-                    rest = self._slice_rows(whole, per, held_rows)
-                    held_rows -= per
-                    held = [rest] if held_rows else []
-            if held_rows:
-                yield self._merge_pieces(held)
-
         def run():
-            streams = [pieces(r) for r in readers]
+            streams = [self._joined_pieces(r, per) for r in readers]
             while streams:
                 parts, alive = [], []
                 for s in streams:
-                    piece = next(s, None)
-                    if piece is not None:
-                        parts.append(piece)
+                    got = next(s, None)
+                    if got is not None:
+                        parts.append(got[1])
                         alive.append(s)
                 streams = alive
                 if not parts:
                     return
                 merged = self._merge_pieces(parts)
-                rows = next(iter(merged.values()))
-                n = rows.offsets()[0].numel() - 1 if isinstance(rows, RaggedTensor) else rows.shape[0]
-                if self.drop_remainder and n < self.batch_size:
+                if self.drop_remainder and self._piece_rows(merged) < self.batch_size:
                     continue
                 batch = self._finish(self._place(merged))
                 if batch is not None:
@@ -319,8 +331,9 @@ class OdpsDataset(OrcDataset):
 
     def _iter_native(self, sheets):
         """Batches of the sheets through the C++ reader (reader threads, packer, prefetch queue), or None when it does not apply.
-        A batch never spans two file segments, so batches at segment ends are short; the position kept for ``dump_io_state`` is
-        the same (sheet, row in sheet) pair as on the Python path."""
+        The reader cuts at file boundaries; its pieces are joined into the same batches as on the Python path (full batches
+        within a sheet, a shorter one at a sheet's end), and the position kept for ``dump_io_state`` is the same (sheet, row in
+        sheet) pair."""
         if not self.native_reader or not sheets:
             return None
         segs = self._file_segments(sheets)
@@ -330,7 +343,8 @@ class OdpsDataset(OrcDataset):
         mod = load()
         if mod is None:
             return None
-        reader = self._segment_reader(mod, segs, self.batch_size, max(self.read_threads_num, 1), self.drop_remainder)
+        # (remainders are dropped below, after joining: the reader would drop one at every file boundary)
+        reader = self._segment_reader(mod, segs, self.batch_size, max(self.read_threads_num, 1), False)
         if reader is None:
             return None
         # resume: the segment that holds (sheet, row in sheet)
@@ -342,16 +356,20 @@ class OdpsDataset(OrcDataset):
             seg = segs[start]
             reader.restore(start, seg[3] + max(self._row_in_sheet - seg[1], 0) if seg[0] == self._sheet_idx else seg[3])
 
-        def moved(state):
-            k, row = state
-            if k < len(segs):
-                seg = segs[k]
-                self._sheet_idx, self._row_in_sheet = seg[0], seg[1] + max(row - seg[3], 0)
-            else:
-                self._sheet_idx, self._row_in_sheet = len(sheets), 0
+        first_sheet, first_row = self._sheet_idx, self._row_in_sheet
 
         def run():
-            yield from self._drain_native(reader, moved)
+            done = {}                                  # rows handed out per sheet in this pass
+            for sheet, piece in self._joined_pieces(reader, self.batch_size, segs):
+                n = self._piece_rows(piece)
+                done[sheet] = done.get(sheet, first_row if sheet == first_sheet else 0) + n
+                size = sheets[sheet].end - sheets[sheet].start
+                self._sheet_idx, self._row_in_sheet = (sheet + 1, 0) if done[sheet] >= size else (sheet, done[sheet])
+                if self.drop_remainder and n < self.batch_size:
+                    continue
+                batch = self._finish(self._place(piece))
+                if batch is not None:
+                    yield batch
             self._sheet_idx, self._row_in_sheet = len(sheets), 0
 
         return run()

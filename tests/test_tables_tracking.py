@@ -678,13 +678,19 @@ def test_native_reader_serves_file_backed_sheets_and_resumes_anywhere(tmp_path):
     ds = make(True)
     orig = ds._iter_native
     ds._iter_native = lambda sheets: (used.append(1), orig(sheets))[1]
-    native_rows, states = [], []
+    native_rows, states, native_sizes = [], [], []
     for b in ds:
         assert torch.equal(b["items"].values().view(-1, 2)[:, 0], b["uid"].flatten())
         native_rows += b["uid"].flatten().tolist()
+        native_sizes.append(b["uid"].shape[0])
         states.append((len(native_rows), ds.dump_io_state()))
-    python_rows = torch.cat([b["uid"].flatten() for b in make(False)]).tolist()
+    python_batches = [b["uid"].flatten().tolist() for b in make(False)]
+    python_rows = sum(python_batches, [])
     assert used and native_rows == python_rows and len(native_rows) == 325
+    assert native_sizes == [len(b) for b in python_batches]          # the same batches, not only the same rows
+    dropped = make(True)
+    dropped.drop_remainder = True
+    assert all(b["uid"].shape[0] == 48 for b in dropped)
     for seen, state in states[:-1][::2]:               # resume after every other batch, on either path (a finished pass starts over)
         for native in (True, False):
             d2 = make(native)
