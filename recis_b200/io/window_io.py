@@ -245,6 +245,9 @@ class OdpsDataset(OrcDataset):
             cur = sheet
             held.append(self._unpack_native(*item))
             held_rows += item[0]
+            if held_rows == per and len(held) == 1:        # the common case: a full piece, nothing to join or cut
+                yield cur, held[0]
+                held, held_rows = [], 0
             while held_rows >= per:
                 whole = self._merge_pieces(held)
                 yield cur, self._slice_rows(whole, 0, per)
